@@ -1,0 +1,215 @@
+// Device-side building blocks shared by all sm_100a kernels: timers, bounded
+// waits, system-scope loads/stores, mbarrier / TMA / tcgen05 wrappers.
+//
+// Every wait here is bounded. A wait that runs out returns false; the caller
+// records a status word and returns normally, so a late or dead peer never
+// leaves a kernel spinning on a shared GPU.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common_host.h"
+#include "credit_page.h"
+
+namespace sky {
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ unsigned long long ld_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned int ld_sys_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_sys_add_u32(unsigned int* p, unsigned int v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// 16-byte streaming load that does not pollute L1, and plain 16-byte store.
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_v4(void* p, uint4 v) {
+    asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_cs_v4(void* p, uint4 v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Waits until *flag >= want (acquire, system scope) or `timeout_ns` passes.
+__device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned int want, unsigned long long timeout_ns) {
+    if ((int)(ld_acquire_sys_u32(flag) - want) >= 0) return true;
+    unsigned long long t0 = globaltimer_ns();
+    unsigned ns = 32;
+    for (;;) {
+        if ((int)(ld_acquire_sys_u32(flag) - want) >= 0) return true;
+        if (globaltimer_ns() - t0 > timeout_ns) return false;
+        __nanosleep(ns);
+        if (ns < 1024) ns <<= 1;
+    }
+}
+
+__device__ __forceinline__ void set_status(LaunchStatus* st, unsigned code, unsigned detail) {
+    if (atomicCAS(&st->status, 0u, code) == 0u) st->detail = detail;
+}
+
+// ---------------------------------------------------------------------------
+// Credit gate. One thread per CTA calls this per chunk.
+//
+// `need` is the cumulative byte count the flow will have consumed once this
+// chunk is sent. The grant is read from the flow's credit page, which lives in
+// mapped host memory and is written by the control side; the last value read is
+// cached in *cache so that an unpaced or generously paced flow touches host
+// memory only once in a while. Returns false when the deadline passed or the
+// page's stop flag is set (then *stopped tells which).
+__device__ __forceinline__ bool credit_acquire(const SkyCreditPage* page, unsigned long long need,
+                                               unsigned long long* cache, unsigned long long max_wait_ns,
+                                               unsigned long long* stall_ns, bool* stopped) {
+    *stopped = false;
+    if (page == nullptr) return true;
+    if (need <= *cache) return true;
+    unsigned long long t0 = globaltimer_ns();
+    unsigned ns = 64;
+    for (;;) {
+        if (ld_sys_u32(&page->stop)) { *stopped = true; *stall_ns += globaltimer_ns() - t0; return false; }
+        if (ld_sys_u32(&page->unlimited)) { *cache = ~0ull; break; }
+        unsigned long long g = ld_sys_u64((const unsigned long long*)&page->granted_bytes);
+        *cache = g;
+        if (need <= g) break;
+        if (globaltimer_ns() - t0 > max_wait_ns) { *stall_ns += globaltimer_ns() - t0; return false; }
+        __nanosleep(ns);
+        if (ns < 2048) ns <<= 1;
+    }
+    *stall_ns += globaltimer_ns() - t0;
+    return true;
+}
+
+// ---------------------------------------------------------------------------
+// mbarrier, TMA, tcgen05.
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up once `timeout_ns` of wall time has passed (checked every 32 polls;
+// a failed try_wait itself may block for a hardware-defined slice). Returns false on give-up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long timeout_ns = 200000000ull) {
+    for (int i = 0; i < 32; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (globaltimer_ns() - t0 > timeout_ns) return false;
+    }
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 2-D tiled TMA load, global -> shared, completion on an mbarrier. No cluster
+// broadcast: one CTA, one destination.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate. One thread issues.
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// 32 lanes x 16 consecutive fp32 columns of TMEM -> 16 registers per thread.
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major bf16 tile whose rows are 64
+// elements (128 bytes) wide and stored with the 128-byte swizzle that a TMA
+// box of inner extent 64 x bf16 produces: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);          // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                               // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                               // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, tile M x N.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+}  // namespace sky

@@ -1,0 +1,273 @@
+// bf16 GEMM on the 5th-generation tensor cores: y[M][N] = x[M][K] * w[N][K]^T.
+//
+// Built for decode, where M (tokens) is small and the weight stream is the
+// bound: the 128-row MMA dimension is given to the WEIGHT rows and the tokens
+// are the MMA's N dimension (16..256), so a 16-token batch wastes nothing.
+//   warp 0   : TMA producer   (cp.async.bulk.tensor, 128-byte swizzle, no cluster broadcast)
+//   warp 1   : MMA issuer     (tcgen05.mma, accumulators in TMEM) and TMEM owner
+//   warps 2-5: epilogue       (tcgen05.ld -> registers -> bf16 / split-K partials)
+// Options: split-K with an in-kernel last-CTA reduction through an fp32
+// scratch buffer, and a gated mode that keeps two accumulators (gate and up
+// rows of the same tile) and stores silu(gate)*up.
+//
+// The reference has no GEMM at all; its decode model stands in for the MLP
+// with a streaming pass over two small arrays
+// (llm_problem_analysis/decode_transformer_kvcache_stress.cu:323-356).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_tcgen05.h"
+
+namespace sky {
+
+constexpr int GEMM_THREADS = 192;
+constexpr int BM = 128;   // weight rows per tile (MMA M)
+constexpr int BK = 64;    // K per stage: 64 bf16 = 128 bytes = one swizzle row
+
+template <int NTOK, bool GATED>
+struct GemmSmem {
+    static constexpr int W_BYTES = BM * BK * 2;
+    static constexpr int X_BYTES = NTOK * BK * 2;
+    static constexpr int STAGE_BYTES = W_BYTES * (GATED ? 2 : 1) + X_BYTES;
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024;  // + alignment slack
+    static constexpr int ACC_COLS = NTOK * (GATED ? 2 : 1);
+    static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;
+};
+
+template <int NTOK, bool GATED>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+    using S = GemmSmem<NTOK, GATED>;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ uint64_t full_bar[8], empty_bar[8], acc_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_last;
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
+    const int n0 = tile_n * BM, t0 = tile_m * NTOK;
+    const int kb_total = p.K / BK;
+    const int kb_per = (kb_total + p.splits - 1) / p.splits;
+    const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
+    const int nkb = max(0, kb1 - kb0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&acc_bar, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(&tmem_slot, S::TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_w);
+            tma_prefetch_desc(&tmap_x);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % S::STAGES;
+                if (i >= S::STAGES && !mbar_wait(&empty_bar[s], ((i / S::STAGES) - 1) & 1)) {
+                    set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 1);
+                    break;
+                }
+                unsigned char* st = smem + s * S::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+                const int kx = (kb0 + i) * BK;
+                tma_load_2d(st, &tmap_w, kx, n0, &full_bar[s]);
+                if (GATED) tma_load_2d(st + S::W_BYTES, &tmap_w, kx, p.N + n0, &full_bar[s]);
+                tma_load_2d(st + S::W_BYTES * (GATED ? 2 : 1), &tmap_x, kx, t0, &full_bar[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, NTOK);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % S::STAGES;
+                if (!mbar_wait(&full_bar[s], (i / S::STAGES) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 2); ok = false; break; }
+                tc_fence_after();
+                const uint32_t st = smem_u32(smem + s * S::STAGE_BYTES);
+                const uint64_t a0 = umma_desc_k_sw128(st);
+                const uint64_t a1 = umma_desc_k_sw128(st + S::W_BYTES);
+                const uint64_t b = umma_desc_k_sw128(st + S::W_BYTES * (GATED ? 2 : 1));
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    const uint32_t accum = (i | k) ? 1u : 0u;
+                    tc_mma_f16(tmem_base, a0 + 2 * k, b + 2 * k, idesc, accum);
+                    if (GATED) tc_mma_f16(tmem_base + NTOK, a1 + 2 * k, b + 2 * k, idesc, accum);
+                }
+                tc_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+            }
+            tc_commit(&acc_bar);           // accumulators complete
+        }
+    } else {
+        // ---- epilogue warps: TMEM lanes 32*(warp%4) .. +31 ----
+        const int slice = warp & 3;
+        const int r = slice * 32 + lane;           // weight row inside the tile
+        const int n = n0 + r;
+        bool ok = true;
+        if (nkb > 0) ok = mbar_wait(&acc_bar, 0);
+        if (!ok && lane == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 3);
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(slice * 32) << 16);
+        const bool direct = p.splits == 1;
+        float* ws = nullptr;
+        if (!direct) {
+            const long long tile_id = (long long)tile_m * gridDim.x + tile_n;
+            ws = p.workspace + ((tile_id * p.splits + split) * S::ACC_COLS) * BM;
+        }
+#pragma unroll 1
+        for (int c = 0; c < NTOK; c += 16) {
+            uint32_t v[16], u[16];
+            if (ok && nkb > 0) {
+                tmem_ld_x16(taddr + c, v);
+                if (GATED) tmem_ld_x16(taddr + NTOK + c, u);
+                tc_wait_ld();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { v[i] = 0; u[i] = 0; }
+            }
+            if (direct) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int t = t0 + c + i;
+                    if (t < p.M && n < p.N) {
+                        float val = __uint_as_float(v[i]);
+                        if (GATED) { const float up = __uint_as_float(u[i]); val = val / (1.0f + __expf(-val)) * up; }
+                        p.y[(long long)t * p.ldy + n] = __float2bfloat16(val);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    ws[(c + i) * BM + r] = __uint_as_float(v[i]);
+                    if (GATED) ws[(NTOK + c + i) * BM + r] = __uint_as_float(u[i]);
+                }
+            }
+        }
+        if (!direct) {
+            // last-arriving split of this tile sums all partials
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+                unsigned* ctr = p.counters + tile_m * gridDim.x + tile_n;
+                const unsigned prev = atomicAdd(ctr, 1u);
+                s_last = prev == (unsigned)p.splits - 1;
+                if (s_last) *ctr = 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (s_last) {
+                __threadfence();
+                const long long tile_id = (long long)tile_m * gridDim.x + tile_n;
+                const float* base = p.workspace + (tile_id * p.splits) * S::ACC_COLS * BM;
+                for (int c = 0; c < NTOK; ++c) {
+                    const int t = t0 + c;
+                    if (t >= p.M) break;
+                    float g = 0.f, up = 0.f;
+                    for (int s2 = 0; s2 < p.splits; ++s2) {
+                        g += __ldcg(base + ((long long)s2 * S::ACC_COLS + c) * BM + r);
+                        if (GATED) up += __ldcg(base + ((long long)s2 * S::ACC_COLS + NTOK + c) * BM + r);
+                    }
+                    if (GATED) g = g / (1.0f + __expf(-g)) * up;
+                    if (n < p.N) p.y[(long long)t * p.ldy + n] = __float2bfloat16(g);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, S::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// Host side: tensor maps and dispatch.
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// 2-D bf16 row-major [rows][cols] with row pitch `ld` elements; box = 64 columns x box_rows rows, 128-byte swizzle.
+bool make_tmap_bf16_2d(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * 2) % 16) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int NTOK, bool GATED>
+static cudaError_t launch_t(const GemmParams& p, const CUtensorMap& tw, const CUtensorMap& tx, cudaStream_t stream) {
+    using S = GemmSmem<NTOK, GATED>;
+    auto kern = gemm_tcgen05_kernel<NTOK, GATED>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    dim3 grid((p.N + BM - 1) / BM, (p.M + NTOK - 1) / NTOK, p.splits);
+    kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tw, tx, p);
+    return cudaGetLastError();
+}
+
+int gemm_pick_ntok(int M, bool gated) {
+    if (M <= 16) return 16;
+    if (M <= 32) return 32;
+    if (M <= 64) return 64;
+    if (M <= 128 || gated) return 128;  // gated keeps two accumulators: 2 x 128 columns
+    return 256;
+}
+
+size_t gemm_workspace_floats(int M, int N, int splits, bool gated) {
+    if (splits <= 1) return 0;
+    const int ntok = gemm_pick_ntok(M, gated);
+    const long long tiles = (long long)((N + BM - 1) / BM) * ((M + ntok - 1) / ntok);
+    return (size_t)(tiles * splits * ntok * (gated ? 2 : 1) * BM);
+}
+size_t gemm_counter_count(int M, int N, bool gated) {
+    const int ntok = gemm_pick_ntok(M, gated);
+    return (size_t)((N + BM - 1) / BM) * ((M + ntok - 1) / ntok);
+}
+
+cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream) {
+    if (p.K % BK || p.M <= 0 || p.N <= 0 || p.splits < 1 || p.splits > p.K / BK) return cudaErrorInvalidValue;
+    if (p.splits > 1 && (!p.workspace || !p.counters)) return cudaErrorInvalidValue;
+    const int ntok = gemm_pick_ntok(p.M, p.gated != 0);
+    CUtensorMap tw, tx;
+    const long long w_rows = p.gated ? 2LL * p.N : p.N;
+    if (!make_tmap_bf16_2d(&tw, p.w, w_rows, p.K, p.ldw, BM)) return cudaErrorInvalidValue;
+    if (!make_tmap_bf16_2d(&tx, p.x, p.M, p.K, p.ldx, ntok)) return cudaErrorInvalidValue;
+#define SKY_GEMM_CASE(NT)                                                                   \
+    case NT: return p.gated ? launch_t<NT, true>(p, tw, tx, stream) : launch_t<NT, false>(p, tw, tx, stream);
+    switch (ntok) {
+        SKY_GEMM_CASE(16)
+        SKY_GEMM_CASE(32)
+        SKY_GEMM_CASE(64)
+        SKY_GEMM_CASE(128)
+        default: return p.gated ? cudaErrorInvalidValue : launch_t<256, false>(p, tw, tx, stream);
+    }
+#undef SKY_GEMM_CASE
+}
+
+}  // namespace sky

@@ -1,0 +1,63 @@
+"""Paged GQA decode attention (skygdr_b200/csrc/kernels/paged_attn.cu)."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .._ext import load
+from .flow import new_status
+from .kv_cache import PagedKVPool
+
+
+class PagedAttention:
+    """Holds the split-KV scratch (partials, statistics, counters) for a maximum batch and context."""
+
+    def __init__(self, device, max_batch: int, q_heads: int, kv_heads: int, max_ctx: int, chunk_tokens: int = 512):
+        self._C = load()
+        self.device = torch.device(device)
+        self.q_heads, self.kv_heads, self.chunk_tokens, self.max_ctx = q_heads, kv_heads, chunk_tokens, max_ctx
+        self.max_splits = (max_ctx + chunk_tokens - 1) // chunk_tokens
+        self.part_o = torch.empty((max_batch, q_heads, self.max_splits, 128), dtype=torch.float32, device=self.device)
+        self.part_m = torch.empty((max_batch, q_heads, self.max_splits), dtype=torch.float32, device=self.device)
+        self.part_l = torch.empty_like(self.part_m)
+        self.counters = torch.zeros((max_batch * kv_heads,), dtype=torch.int32, device=self.device)
+        self.status = new_status(self.device)
+        self.max_batch = max_batch
+
+    def __call__(self, q: torch.Tensor, pool: PagedKVPool, layer: int, block_table: torch.Tensor, ctx_lens: torch.Tensor,
+                 max_ctx: Optional[int] = None, out: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
+        assert pool.layout == "hnd" and q.shape[0] <= self.max_batch and q.shape[1] == self.q_heads
+        if out is None:
+            out = torch.empty_like(q)
+        bs, ls, ks = pool.strides
+        self._C.paged_attn_decode(q, pool.layer_base(layer), out, block_table, ctx_lens, bs, ks, pool.head_stride, self.kv_heads,
+                                  min(max_ctx or self.max_ctx, self.max_ctx), self.chunk_tokens,
+                                  scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]),
+                                  self.part_o, self.part_m, self.part_l, self.counters, self.status)
+        return out
+
+
+def paged_attn_reference(q: torch.Tensor, pool: PagedKVPool, layer: int, block_table: torch.Tensor, ctx_lens: torch.Tensor,
+                         scale: Optional[float] = None) -> torch.Tensor:
+    """Plain fp32 softmax attention over the gathered pages (test oracle)."""
+    B, Hq, D = q.shape
+    Hkv = pool.geom.kv_heads
+    G = Hq // Hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    out = torch.empty((B, Hq, D), dtype=torch.float32, device=q.device)
+    for b in range(B):
+        n = int(ctx_lens[b])
+        nb = (n + 15) // 16
+        blocks = block_table[b, :nb].long()
+        kv = pool.data[blocks, layer]                      # hnd: [nb][2][H][16][D]
+        if pool.layout == "nhd":
+            kv = kv.permute(0, 1, 3, 2, 4)
+        k = kv[:, 0].permute(1, 0, 2, 3).reshape(Hkv, nb * 16, D)[:, :n].float()
+        v = kv[:, 1].permute(1, 0, 2, 3).reshape(Hkv, nb * 16, D)[:, :n].float()
+        qb = q[b].float().view(Hkv, G, D)
+        s = torch.einsum("hgd,htd->hgt", qb, k) * scale
+        p = torch.softmax(s, dim=-1)
+        out[b] = torch.einsum("hgt,htd->hgd", p, v).reshape(Hq, D)
+    return out

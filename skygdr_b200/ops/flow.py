@@ -1,0 +1,116 @@
+"""Device-visible flow state: a credit page in mapped host memory plus the
+launch status block, shared by the transfer, offload and memhog kernels."""
+from __future__ import annotations
+
+import threading
+import time
+from typing import Dict, Optional
+
+import torch
+
+from .._ext import load
+
+STATUS_NAMES = {0: "OK", 1: "YIELD_CREDIT", 2: "STOPPED", 3: "TIMEOUT_FLAG", 4: "BAD_INDEX", 5: "TIMEOUT_MBAR"}
+
+
+class CreditPage:
+    """One flow's credit page in pinned, mapped host memory.
+
+    ``host_ptr`` is what the control side writes; ``dev_ptr`` is what kernels
+    read. ``attach`` wraps a page that the daemon created under /dev/shm."""
+
+    def __init__(self, flow_id: int = 0, unlimited: bool = True):
+        self._C = load()
+        self.host_ptr, self.dev_ptr = self._C.host_alloc_mapped(4096)
+        self._owned = True
+        self._mm = None
+        self._C.credit_page_init(self.host_ptr, flow_id, unlimited)
+        self.granted = 0
+
+    @classmethod
+    def attach(cls, path: str) -> "CreditPage":
+        import ctypes
+        import mmap
+        import os
+
+        self = cls.__new__(cls)
+        self._C = load()
+        fd = os.open(path, os.O_RDWR)
+        try:
+            self._mm = mmap.mmap(fd, 4096)
+        finally:
+            os.close(fd)
+        self.host_ptr = ctypes.addressof(ctypes.c_char.from_buffer(self._mm))
+        self.dev_ptr = self._C.host_register(self.host_ptr, 4096)
+        self._owned = False
+        self.granted = 0
+        return self
+
+    def grant(self, granted_bytes: int, unlimited: bool = False, stop: bool = False) -> None:
+        self.granted = granted_bytes
+        self._C.credit_page_grant(self.host_ptr, granted_bytes, unlimited, stop)
+
+    def set_unlimited(self) -> None:
+        self._C.credit_page_grant(self.host_ptr, self.granted, True, False)
+
+    def read(self) -> Dict[str, int]:
+        return dict(self._C.credit_page_read(self.host_ptr))
+
+    def close(self) -> None:
+        if self.host_ptr:
+            if self._owned:
+                self._C.host_free_mapped(self.host_ptr)
+            else:
+                self._C.host_unregister(self.host_ptr)
+                self._mm = None
+            self.host_ptr = 0
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class LocalPacer:
+    """In-process control side for one page: a thread that adds ``rate_gbps`` worth of bytes to the
+    grant every ``window_ms`` (what fabricd does for registered flows, without the daemon)."""
+
+    def __init__(self, page: CreditPage, rate_gbps: float, window_ms: float = 1.0, burst_windows: float = 2.0):
+        self.page, self.rate, self.window_s, self.burst = page, rate_gbps, window_ms * 1e-3, burst_windows
+        self._stop = threading.Event()
+        self._thr: Optional[threading.Thread] = None
+
+    def start(self, base: int = 0):
+        self.page.grant(base, unlimited=False)
+
+        def run():
+            granted = float(base)
+            t_prev = time.perf_counter()
+            while not self._stop.is_set():
+                time.sleep(self.window_s)
+                now = time.perf_counter()
+                add = self.rate * 1e9 * (now - t_prev)
+                t_prev = now
+                used = self.page.read()["consumed_bytes"]
+                granted = min(granted + add, max(granted, used + add * self.burst)) if used < granted else granted + add
+                self.page.grant(int(granted), unlimited=False)
+
+        self._thr = threading.Thread(target=run, daemon=True)
+        self._thr.start()
+        return self
+
+    def stop(self):
+        self._stop.set()
+        if self._thr:
+            self._thr.join()
+
+
+def new_status(device) -> torch.Tensor:
+    return load().new_status(torch.device(device).index or 0)
+
+
+def read_status(status: torch.Tensor) -> Dict[str, int]:
+    d = dict(load().read_status(status))
+    d["status_name"] = STATUS_NAMES.get(d["status"], str(d["status"]))
+    return d

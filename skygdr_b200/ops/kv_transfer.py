@@ -1,0 +1,124 @@
+"""Paged KV transfer between GPUs (and to mapped host memory).
+
+``KvTransferFlow`` is one registered flow: a credit page, a status block and a
+cumulative byte counter. ``transfer`` launches the sm_100a kernel
+(skygdr_b200/csrc/kernels/kv_transfer.cu) which gathers the pages named by the
+source block list, converts token-major to head-major pages, optionally packs
+to block-scaled fp8, and stores into the destination pool(s) of other GPUs.
+It stands where the reference calls cudaMemcpyPeerAsync
+(llm_problem_analysis/kv_nvlink_transfer.cu:122,
+llm_problem_analysis/kv_nvlink_transfer_trace.cu:383).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .._ext import load
+from .flow import CreditPage, new_status, read_status
+from .kv_cache import KVGeometry, PagedKVPool
+
+
+@dataclass
+class RemotePool:
+    """A destination pool that may live on another GPU / in another process: address + geometry."""
+    ptr: int
+    strides: tuple          # (block, layer, kv) in destination elements
+    kv_heads: int           # heads stored in this pool
+    scale_ptr: int = 0      # fp8: scale bytes, same indexing / 32
+    done_flag_ptr: int = 0  # optional u32 set when a transfer has fully landed
+
+    @classmethod
+    def of(cls, pool: PagedKVPool, done_flag: Optional[torch.Tensor] = None) -> "RemotePool":
+        assert pool.layout == "hnd"
+        return cls(pool.data.data_ptr(), pool.strides, pool.geom.kv_heads, 0,
+                   done_flag.data_ptr() if done_flag is not None else 0)
+
+
+class KvTransferFlow:
+    def __init__(self, device, page: Optional[CreditPage] = None, ctas: Optional[int] = None, pages_per_chunk: int = 8,
+                 max_wait_ms: float = 2.0):
+        self._C = load()
+        self.device = torch.device(device)
+        self.page = page
+        self.status = new_status(self.device)
+        self.consumed = 0
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.ctas = ctas or 2 * sms
+        self.pages_per_chunk = pages_per_chunk
+        self.max_wait_ns = int(max_wait_ms * 1e6)
+        self.seq = 0
+
+    def transfer(self, src: PagedKVPool, dsts: Sequence[RemotePool], src_blocks: torch.Tensor, dst_blocks: torch.Tensor,
+                 replicate: bool = False, fp8: bool = False, keep_layout: bool = False, first_chunk: int = 0,
+                 signal: bool = True) -> None:
+        """Enqueues one transfer on the current stream of the source device."""
+        assert src.layout == "nhd"
+        g = src.geom
+        heads_per_dst = g.kv_heads if replicate else g.kv_heads // len(dsts)
+        for d in dsts:
+            assert replicate or keep_layout or d.kv_heads == heads_per_dst, "destination head count does not match the scatter"
+        self.seq += 1
+        self._C.reset_status(self.status)
+        self._C.kv_transfer(
+            src.data, [d.ptr for d in dsts], [d.scale_ptr for d in dsts], [d.done_flag_ptr if signal else 0 for d in dsts],
+            src_blocks, dst_blocks, g.layers, g.kv_heads, g.block_tokens, g.head_dim, list(src.strides), list(dsts[0].strides),
+            heads_per_dst, replicate, fp8, keep_layout, self.pages_per_chunk, self.ctas,
+            self.page.dev_ptr if self.page else 0, self.consumed, self.max_wait_ns, first_chunk, self.seq, self.status)
+        self._last = (src, dsts, src_blocks, dst_blocks, replicate, fp8, keep_layout)
+
+    def result(self) -> Dict[str, int]:
+        """Synchronises and returns the status block; accounts the bytes that were moved."""
+        torch.cuda.synchronize(self.device)
+        st = read_status(self.status)
+        self.consumed += st["bytes_done"]
+        st["device_time_ms"] = (st["t_end_ns"] - st["t_start_ns"]) * 1e-6 if st["t_end_ns"] else float("nan")
+        return st
+
+    def resume(self, st: Dict[str, int]) -> None:
+        """Relaunches the last transfer from the cursor a yielded launch left behind."""
+        assert st["status"] in (1, 2)
+        src, dsts, sb, db, rep, fp8, keep = self._last
+        self.transfer(src, dsts, sb, db, rep, fp8, keep, first_chunk=st["cursor"])
+
+    def transfer_to_completion(self, *args, max_launches: int = 10000, **kw) -> Dict[str, int]:
+        """Transfers, relaunching after every credit yield; sums bytes and stall time."""
+        self.transfer(*args, **kw)
+        total = self.result()
+        n = 1
+        while total["status"] == 1 and n < max_launches:
+            self.resume(total)
+            st = self.result()
+            n += 1
+            for k in ("bytes_done", "chunks_done", "stall_ns"):
+                st[k] += total[k]
+            st["t_start_ns"] = total["t_start_ns"]
+            st["device_time_ms"] = (st["t_end_ns"] - st["t_start_ns"]) * 1e-6
+            total = st
+        total["launches"] = n
+        return total
+
+
+def link_bytes(geom: KVGeometry, n_blocks: int, n_dst: int = 1, replicate: bool = False, fp8: bool = False) -> int:
+    per_page = geom.page_elems * (2 if not fp8 else 1) + (geom.page_elems // 32 if fp8 else 0)
+    return n_blocks * geom.layers * 2 * per_page * (n_dst if replicate else 1)
+
+
+def reference_transfer(src: PagedKVPool, src_blocks: torch.Tensor, heads: slice = slice(None)) -> torch.Tensor:
+    """What a destination pool's blocks must hold after a transfer: [n][layer][2][head][tok][dim]."""
+    x = src.data[src_blocks.long()]            # [n][L][2][T][H][D]
+    return x.permute(0, 1, 2, 4, 3, 5)[:, :, :, heads].contiguous()
+
+
+def fp8_mx_reference(x: torch.Tensor):
+    """Block-scaled e4m3 packing of the last dim in groups of 32: returns (fp8 bytes as uint8, scale bytes)."""
+    shp = x.shape
+    g = x.float().reshape(*shp[:-1], shp[-1] // 32, 32)
+    amax = g.abs().amax(-1, keepdim=True)
+    mant, exp = torch.frexp(amax)               # amax = mant * 2^exp, mant in [0.5, 1)
+    e = (exp - 1 - 8 + (mant > 0.875).to(exp.dtype)).float()   # smallest e with amax / 2^e <= 448 = 1.75 * 2^8
+    e = torch.where(amax > 0, e, torch.full_like(e, -127.0)).clamp(-127, 127)
+    q = (g * torch.exp2(-e)).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8).reshape(shp), (e + 127).to(torch.uint8).reshape(*shp[:-1], shp[-1] // 32)

@@ -1,0 +1,295 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import skygdr_b200.ops as ops
+
+    from skygdr_b200._ext import load
+
+    load()  # a missing extension is an error on a GPU box
+    return ops
+
+
+def _pools(ops, n_src=40, n_dst=48, layers=3, heads=8, seed=0):
+    g = ops.KVGeometry(layers=layers, kv_heads=heads)
+    torch.manual_seed(seed)
+    src = ops.PagedKVPool(g, n_src, "nhd")
+    src.data.normal_()
+    dst = ops.PagedKVPool(g, n_dst, "hnd")
+    return g, src, dst
+
+
+def test_kv_transfer_exact(ops):
+    g, src, dst = _pools(ops)
+    n = 23
+    sb = torch.randperm(src.num_blocks, device="cuda")[:n].int()
+    db = torch.randperm(dst.num_blocks, device="cuda")[:n].int()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flow = ops.KvTransferFlow("cuda", pages_per_chunk=4)
+    flow.transfer(src, [ops.RemotePool.of(dst, flag)], sb, db)
+    st = flow.result()
+    assert st["status"] == 0 and st["cursor"] == 2**64 - 1
+    assert st["bytes_done"] == ops.link_bytes(g, n)
+    assert torch.equal(dst.data[db.long()], ops.reference_transfer(src, sb))
+    assert int(flag.item()) == flow.seq
+    untouched = torch.ones(dst.num_blocks, dtype=torch.bool, device="cuda")
+    untouched[db.long()] = False
+    assert float(dst.data[untouched].abs().sum()) == 0.0
+
+
+def test_kv_transfer_scatter_and_replicate(ops):
+    g, src, _ = _pools(ops, layers=2)
+    gd = ops.KVGeometry(layers=2, kv_heads=2)
+    parts = [ops.PagedKVPool(gd, 16, "hnd") for _ in range(4)]
+    sb = torch.arange(5, 14, device="cuda").int()
+    db = torch.arange(0, 9, device="cuda").int()
+    flow = ops.KvTransferFlow("cuda")
+    flow.transfer(src, [ops.RemotePool.of(p) for p in parts], sb, db)
+    assert flow.result()["status"] == 0
+    for i, p in enumerate(parts):
+        assert torch.equal(p.data[db.long()], ops.reference_transfer(src, sb, slice(2 * i, 2 * i + 2)))
+    full = [ops.PagedKVPool(g, 16, "hnd") for _ in range(3)]
+    flow.transfer(src, [ops.RemotePool.of(p) for p in full], sb, db, replicate=True)
+    st = flow.result()
+    assert st["bytes_done"] == ops.link_bytes(g, 9, 3, replicate=True)
+    for p in full:
+        assert torch.equal(p.data[db.long()], ops.reference_transfer(src, sb))
+
+
+def test_kv_transfer_fp8_pack(ops):
+    from skygdr_b200.ops.kv_transfer import RemotePool, fp8_mx_reference
+
+    g, src, _ = _pools(ops, layers=2)
+    nb = 12
+    q = torch.zeros((nb, g.layers, 2, g.kv_heads, 16, 128), dtype=torch.uint8, device="cuda")
+    sc = torch.zeros((nb, g.layers, 2, g.kv_heads, 16, 4), dtype=torch.uint8, device="cuda")
+    sb = torch.randperm(src.num_blocks, device="cuda")[:nb].int()
+    db = torch.arange(nb, device="cuda").int()
+    flow = ops.KvTransferFlow("cuda")
+    rp = RemotePool(q.data_ptr(), (q.stride(0), q.stride(1), q.stride(2)), g.kv_heads, sc.data_ptr())
+    flow.transfer(src, [rp], sb, db, fp8=True)
+    assert flow.result()["status"] == 0
+    want_q, want_s = fp8_mx_reference(ops.reference_transfer(src, sb))
+    assert torch.equal(sc, want_s)
+    # identical scales; the quantised values may differ by one rounding step where x/scale sits on a tie
+    got = q.view(torch.float8_e4m3fn).float() * torch.exp2(sc.float() - 127).repeat_interleave(32, -1)
+    ref = ops.reference_transfer(src, sb).float()
+    assert (got - ref).abs().max() <= 0.07 * ref.abs().max()
+    assert (q != want_q).float().mean() < 1e-3
+
+
+def test_kv_transfer_credit_yield_and_resume(ops):
+    g, src, dst = _pools(ops, layers=2)
+    n = 20
+    sb = torch.arange(n, device="cuda").int()
+    db = torch.arange(n, device="cuda").int()
+    page = ops.CreditPage(flow_id=7, unlimited=False)
+    total = ops.link_bytes(g, n)
+    page.grant(total // 2)                       # nothing will ever add to this: a host-made stall
+    flow = ops.KvTransferFlow("cuda", page=page, pages_per_chunk=2, max_wait_ms=1.0)
+    flow.transfer(src, [ops.RemotePool.of(dst)], sb, db)
+    st = flow.result()
+    assert st["status_name"] == "YIELD_CREDIT"
+    assert 0 < st["bytes_done"] <= total // 2
+    chunk_bytes = 2 * g.page_elems * 2
+    assert st["cursor"] == st["bytes_done"] // chunk_bytes   # everything below the cursor is done
+    assert page.read()["yields"] == 1
+    page.grant(total)
+    flow.resume(st)
+    st2 = flow.result()
+    assert st2["status"] == 0 and st["bytes_done"] + st2["bytes_done"] == total
+    assert torch.equal(dst.data[db.long()], ops.reference_transfer(src, sb))
+    assert page.read()["completed_bytes"] == total
+    # stop flag: the kernel returns at once with STOPPED
+    page.grant(total, stop=True)
+    flow.transfer(src, [ops.RemotePool.of(dst)], sb, db)
+    assert flow.result()["status_name"] == "STOPPED"
+
+
+def test_kv_offload_to_mapped_host(ops):
+    from skygdr_b200._ext import load
+    from skygdr_b200.ops.kv_transfer import RemotePool
+
+    C = load()
+    g, src, _ = _pools(ops, layers=2)
+    nb = 6
+    nbytes = nb * g.block_elems * 2
+    hptr, dptr = C.host_alloc_mapped(nbytes)
+    try:
+        sb = torch.tensor([3, 9, 1, 30, 7, 22], device="cuda").int()
+        db = torch.arange(nb, device="cuda").int()
+        flow = ops.KvTransferFlow("cuda", ctas=16)
+        s = src.strides
+        flow.transfer(src, [RemotePool(dptr, s, g.kv_heads)], sb, db, keep_layout=True)
+        assert flow.result()["status"] == 0
+        import ctypes
+
+        host = torch.frombuffer((ctypes.c_char * nbytes).from_address(hptr), dtype=torch.bfloat16).view(nb, -1)
+        assert torch.equal(host, src.data[sb.long()].cpu().view(nb, -1))
+    finally:
+        C.host_free_mapped(hptr)
+
+
+@pytest.mark.parametrize("op", ["read", "write", "rw", "copy", "axpy"])
+def test_memhog_ops(ops, op):
+    hog = ops.Memhog("cuda", gb=0.25, op=op, chunk_bytes=1 << 18)
+    hog.a.copy_(torch.arange(hog.a.numel(), device="cuda") % 7)
+    if op == "axpy":
+        hog.b.fill_(1.0)
+    hog.launch(iters=2, alpha=0.5)
+    st = hog.result()
+    assert st["status"] == 0 and st["bytes_done"] == 2 * hog.bytes_per_pass()
+    if op == "read":
+        assert abs(float(hog.sink.item()) - 2 * float(hog.a.double().sum())) < 1e-3 * float(hog.a.double().sum())
+    if op == "copy":
+        assert torch.equal(hog.a, hog.b)
+    if op == "axpy":
+        assert torch.allclose(hog.b, 1.0 + 2 * 0.5 * hog.a)
+    if op == "rw":
+        assert torch.allclose(hog.b, hog.a * 1.0001 + 0.5)
+
+
+def test_memhog_duty_cycle_and_time_limit(ops):
+    hog = ops.Memhog("cuda", gb=0.5, op="copy")
+    hog.launch(iters=0, seconds=0.05)
+    full = hog.result()
+    assert 0.04 < full["seconds"] < 0.2
+    hog.launch(iters=0, seconds=0.05, duty_on_ms=1.0, duty_off_ms=1.0)
+    half = hog.result()
+    assert 0.3 < half["bytes_done"] / full["bytes_done"] < 0.75
+
+
+@pytest.mark.parametrize("kv_heads,q_heads", [(8, 32), (1, 4), (2, 4), (4, 4)])
+def test_paged_attention_matches_reference(ops, kv_heads, q_heads):
+    torch.manual_seed(1)
+    g = ops.KVGeometry(layers=2, kv_heads=kv_heads)
+    ctx = torch.tensor([1, 15, 16, 17, 511, 512, 513, 1300, 2049, 64], dtype=torch.int32, device="cuda")
+    B = ctx.numel()
+    max_blocks = (int(ctx.max()) + 15) // 16
+    nblk = int(((ctx + 15) // 16).sum()) + 4
+    pool = ops.PagedKVPool(g, nblk, "hnd")
+    pool.data.normal_()
+    perm = torch.randperm(nblk, device="cuda").int()
+    table = torch.zeros((B, max_blocks), dtype=torch.int32, device="cuda")
+    o = 0
+    for b in range(B):
+        nb = (int(ctx[b]) + 15) // 16
+        table[b, :nb] = perm[o:o + nb]
+        o += nb
+    q = torch.randn((B, q_heads, 128), dtype=torch.bfloat16, device="cuda")
+    attn = ops.PagedAttention("cuda", B, q_heads, kv_heads, max_ctx=4096, chunk_tokens=512)
+    for layer in (0, 1):
+        out = attn(q, pool, layer, table, ctx, max_ctx=int(ctx.max()))
+        ref = ops.paged_attn_reference(q, pool, layer, table, ctx)
+        torch.cuda.synchronize()
+        assert ops.read_status(attn.status)["status"] == 0
+        assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
+    # counters are left at zero for the next launch
+    assert int(attn.counters.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(16, 256, 512, 1), (16, 6144, 4096, 4), (13, 384, 1024, 2), (64, 512, 4096, 1),
+                                          (128, 4096, 1536, 3), (300, 1024, 2048, 1), (32, 18992, 512, 1)])
+def test_gemm_matches_reference(ops, M, N, K, splits):
+    torch.manual_seed(2)
+    x = torch.randn((M, K), dtype=torch.bfloat16, device="cuda")
+    w = (torch.randn((N, K), dtype=torch.bfloat16, device="cuda") / math.sqrt(K)).contiguous()
+    y = ops.gemm(x, w, splits=splits)
+    ref = x.float() @ w.float().t()
+    torch.cuda.synchronize()
+    from skygdr_b200.ops.gemm import workspace_for
+
+    assert ops.read_status(workspace_for("cuda").status)["status"] == 0
+    err = (y.float() - ref).abs().max()
+    assert err < 2e-2 * max(1.0, float(ref.abs().max())), float(err)
+
+
+@pytest.mark.parametrize("M,F,K,splits", [(16, 512, 1024, 1), (16, 1536, 4096, 4), (100, 256, 512, 1)])
+def test_gemm_gated_matches_reference(ops, M, F, K, splits):
+    torch.manual_seed(3)
+    x = torch.randn((M, K), dtype=torch.bfloat16, device="cuda")
+    w = (torch.randn((2 * F, K), dtype=torch.bfloat16, device="cuda") / math.sqrt(K)).contiguous()
+    y = ops.gemm(x, w, gated=True, splits=splits)
+    gu = x.float() @ w.float().t()
+    ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    err = (y.float() - ref).abs().max()
+    assert err < 2e-2 * max(1.0, float(ref.abs().max())), float(err)
+
+
+def test_rmsnorm_and_residual(ops):
+    torch.manual_seed(4)
+    x = torch.randn((37, 4096), dtype=torch.bfloat16, device="cuda")
+    w = torch.randn((4096,), dtype=torch.bfloat16, device="cuda")
+    y = ops.rmsnorm(x, w, 1e-6)
+    xf = x.float()
+    ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    assert torch.allclose(y.float(), ref, atol=2e-2, rtol=2e-2)
+    res = torch.randn_like(x)
+    res0 = res.clone()
+    y2 = ops.rmsnorm(x, w, 1e-6, residual=res)
+    s = (x.float() + res0.float()).bfloat16()
+    assert torch.equal(res, s)
+    sf = s.float()
+    ref2 = sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    assert torch.allclose(y2.float(), ref2, atol=2e-2, rtol=2e-2)
+
+
+def test_rope_qknorm_append(ops):
+    torch.manual_seed(5)
+    Hq, Hkv, B = 32, 8, 9
+    g = ops.KVGeometry(layers=1, kv_heads=Hkv)
+    pool = ops.PagedKVPool(g, 64, "hnd")
+    pos = torch.tensor([0, 1, 15, 16, 100, 4095, 40000, 65535, 7], dtype=torch.int32, device="cuda")
+    max_blocks = 65536 // 16
+    table = torch.zeros((B, max_blocks), dtype=torch.int32, device="cuda")
+    for b in range(B):
+        table[b, int(pos[b]) // 16] = b * 3 + 1
+    qkv = torch.randn((B, (Hq + 2 * Hkv) * 128), dtype=torch.bfloat16, device="cuda")
+    qn = torch.rand(128, device="cuda").bfloat16() + 0.5
+    kn = torch.rand(128, device="cuda").bfloat16() + 0.5
+    inv = ops.rope_inv_freq(1e6, "cuda")
+    q = ops.rope_append(qkv, qn, kn, pool, 0, inv, table, pos, Hq)
+
+    def norm(x, w):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()).bfloat16().float()
+
+    def rope(x, p):
+        ang = p.float()[:, None, None] * inv[None, None, :]
+        c, s = torch.cos(ang.double()).float(), torch.sin(ang.double()).float()
+        x1, x2 = x[..., :64], x[..., 64:]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
+
+    h = qkv.view(B, Hq + 2 * Hkv, 128)
+    q_ref = rope(norm(h[:, :Hq], qn), pos)
+    k_ref = rope(norm(h[:, Hq:Hq + Hkv], kn), pos)
+    v_ref = h[:, Hq + Hkv:].float()
+    assert torch.allclose(q.float(), q_ref, atol=3e-2, rtol=3e-2), float((q.float() - q_ref).abs().max())
+    for b in range(B):
+        blk, slot = b * 3 + 1, int(pos[b]) % 16
+        assert torch.allclose(pool.data[blk, 0, 0, :, slot].float(), k_ref[b], atol=3e-2, rtol=3e-2)
+        assert torch.equal(pool.data[blk, 0, 1, :, slot].float(), v_ref[b])
+
+
+def test_silu_embedding_argmax(ops):
+    torch.manual_seed(6)
+    gu = torch.randn((21, 2 * 1536), dtype=torch.bfloat16, device="cuda")
+    y = ops.silu_mul(gu)
+    ref = torch.nn.functional.silu(gu[:, :1536].float()) * gu[:, 1536:].float()
+    assert torch.allclose(y.float(), ref, atol=2e-2, rtol=2e-2)
+    table = torch.randn((1000, 512), dtype=torch.bfloat16, device="cuda")
+    ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32, device="cuda")
+    assert torch.equal(ops.embedding(ids, table), table[ids.long()])
+    logits = torch.randn((7, 151936), dtype=torch.bfloat16, device="cuda")
+    logits[3, 77] = 100.0
+    logits[3, 50000] = 100.0
+    got = ops.argmax(logits)
+    assert torch.equal(got.long(), logits.float().argmax(-1)) or int(got[3]) == 77
+    assert int(got[3]) == 77
