@@ -15,6 +15,7 @@
 #include "memhog.h"
 #include "paged_attn.h"
 #include "pcie_task.h"
+#include "tp_fused.h"
 
 namespace py = pybind11;
 using namespace sky;
@@ -238,7 +239,7 @@ static void rmsnorm(torch::Tensor x, c10::optional<torch::Tensor> residual, torc
 }
 static void rope_append(torch::Tensor qkv, c10::optional<torch::Tensor> q_norm, c10::optional<torch::Tensor> k_norm, torch::Tensor q_out,
                         torch::Tensor kv_layer, torch::Tensor inv_freq, torch::Tensor block_table, torch::Tensor positions,
-                        c10::optional<torch::Tensor> seq_ids, int64_t block_stride, int64_t kv_stride, int64_t head_stride, int q_heads,
+                        c10::optional<torch::Tensor> seq_ids, int64_t block_stride, int64_t kv_stride, int64_t head_stride, int64_t tok_stride, int q_heads,
                         int kv_heads, double eps) {
     c10::cuda::CUDAGuard g(qkv.device());
     RopeAppendParams p;
@@ -251,7 +252,7 @@ static void rope_append(torch::Tensor qkv, c10::optional<torch::Tensor> q_norm, 
     p.inv_freq = inv_freq.data_ptr<float>();
     p.block_table = i32_ptr(block_table); p.positions = i32_ptr(positions);
     p.seq_ids = seq_ids.has_value() ? i32_ptr(*seq_ids) : nullptr;
-    p.block_stride = block_stride; p.kv_stride = kv_stride; p.head_stride = head_stride;
+    p.block_stride = block_stride; p.kv_stride = kv_stride; p.head_stride = head_stride; p.tok_stride = tok_stride;
     p.tokens = (int)positions.numel(); p.q_heads = q_heads; p.kv_heads = kv_heads;
     p.max_blocks = (int)block_table.size(1); p.block_tokens = 16; p.eps = (float)eps;
     TORCH_CHECK(qkv.numel() == (int64_t)p.tokens * (q_heads + 2 * kv_heads) * 128, "qkv shape");
@@ -296,6 +297,94 @@ static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, 
     SKY_CUDA_CHECK(launch_gemm(p, cur_stream()));
 }
 
+// ---- tensor-parallel fused paths ----
+static TpSeq make_seq(uint64_t step_ptr, unsigned uses_per_step, unsigned use_index, unsigned arrivals) {
+    TpSeq s;
+    s.step = (const unsigned int*)step_ptr; s.uses_per_step = uses_per_step; s.use_index = use_index; s.arrivals_per_use = arrivals;
+    return s;
+}
+
+// ag = (n_src, counters_ptr, step_ptr, uses_per_step, use_index, arrivals_per_use, timeout_ns) or empty
+// rs = (world, src_rank, rows_per_rank, [dst ptrs], [counter ptrs]) or empty
+static void gemm_tp(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, bool gated, c10::optional<torch::Tensor> workspace,
+                    c10::optional<torch::Tensor> counters, torch::Tensor status, py::tuple ag, py::tuple rs) {
+    c10::cuda::CUDAGuard g(x.device());
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "row-major 2-D tensors");
+    GemmParams p;
+    memset(&p, 0, sizeof p);
+    p.x = bf16_ptr(x); p.w = bf16_ptr(w);
+    p.M = (int)x.size(0); p.K = (int)x.size(1);
+    p.N = gated ? (int)w.size(0) / 2 : (int)w.size(0);
+    TORCH_CHECK(w.size(1) == p.K, "shape mismatch");
+    p.ldx = x.stride(0); p.ldw = w.stride(0);
+    if (rs.size() == 0) {
+        TORCH_CHECK(y.dim() == 2 && y.size(0) == p.M && y.size(1) == p.N && y.stride(1) == 1, "y shape");
+        p.y = bf16_mut(y); p.ldy = y.stride(0);
+    }
+    p.splits = splits; p.gated = gated;
+    if (splits > 1) {
+        TORCH_CHECK(workspace.has_value() && counters.has_value(), "split-K needs workspace and counters");
+        TORCH_CHECK((size_t)workspace->numel() >= gemm_workspace_floats(p.M, p.N, splits, gated), "workspace too small");
+        TORCH_CHECK((size_t)counters->numel() >= gemm_counter_count(p.M, p.N, gated), "counters too small");
+        p.workspace = workspace->data_ptr<float>();
+        p.counters = reinterpret_cast<unsigned int*>(counters->data_ptr());
+    }
+    p.status = status_ptr(status);
+    if (ag.size() > 0) {
+        p.ag.n_src = ag[0].cast<int>();
+        p.ag.counters = (const unsigned int*)ag[1].cast<uint64_t>();
+        p.ag.seq = make_seq(ag[2].cast<uint64_t>(), ag[3].cast<unsigned>(), ag[4].cast<unsigned>(), ag[5].cast<unsigned>());
+        p.ag.timeout_ns = ag[6].cast<uint64_t>();
+    }
+    if (rs.size() > 0) {
+        p.rs.world = rs[0].cast<int>(); p.rs.src_rank = rs[1].cast<int>(); p.rs.rows_per_rank = rs[2].cast<int>();
+        auto dst = rs[3].cast<std::vector<uint64_t>>();
+        auto ctr = rs[4].cast<std::vector<uint64_t>>();
+        TORCH_CHECK((int)dst.size() == p.rs.world && (int)ctr.size() == p.rs.world && p.rs.world <= TP_MAX_RANKS, "rs pointer lists");
+        TORCH_CHECK(p.M <= p.rs.world * p.rs.rows_per_rank, "more token rows than the ranks own");
+        for (int i = 0; i < p.rs.world; ++i) { p.rs.dst[i] = (__nv_bfloat16*)dst[i]; p.rs.counters[i] = (unsigned int*)ctr[i]; }
+    }
+    SKY_CUDA_CHECK(launch_gemm(p, cur_stream()));
+}
+
+static void tp_norm(uint64_t rs_buf, uint64_t rs_counter, py::tuple rs_seq, torch::Tensor resid, torch::Tensor w,
+                    std::vector<uint64_t> ag_dst, std::vector<uint64_t> ag_counter, int rank, double eps, uint64_t timeout_ns,
+                    torch::Tensor status) {
+    c10::cuda::CUDAGuard g(resid.device());
+    TpNormParams p;
+    memset(&p, 0, sizeof p);
+    p.rs_buf = (const __nv_bfloat16*)rs_buf;
+    p.rs_counter = (const unsigned int*)rs_counter;
+    if (rs_buf) p.rs_seq = make_seq(rs_seq[0].cast<uint64_t>(), rs_seq[1].cast<unsigned>(), rs_seq[2].cast<unsigned>(), rs_seq[3].cast<unsigned>());
+    p.resid = bf16_mut(resid); p.w = bf16_ptr(w);
+    p.world = (int)ag_dst.size(); p.rank = rank; p.rows = (int)resid.size(0); p.hidden = (int)resid.size(1);
+    TORCH_CHECK(p.world >= 1 && p.world <= TP_MAX_RANKS && ag_counter.size() == ag_dst.size(), "peer lists");
+    for (int i = 0; i < p.world; ++i) { p.ag_dst[i] = (__nv_bfloat16*)ag_dst[i]; p.ag_counter[i] = (unsigned int*)ag_counter[i]; }
+    p.eps = (float)eps; p.timeout_ns = timeout_ns; p.status = status_ptr(status);
+    SKY_CUDA_CHECK(launch_tp_norm(p, cur_stream()));
+}
+
+static void tp_argmax(torch::Tensor logits, int vocab_lo, int rank, std::vector<uint64_t> slots, std::vector<uint64_t> counters,
+                      uint64_t my_slots, uint64_t my_counters, py::tuple seq, torch::Tensor next_ids, uint64_t timeout_ns,
+                      torch::Tensor status) {
+    c10::cuda::CUDAGuard g(logits.device());
+    TpArgmaxParams p;
+    memset(&p, 0, sizeof p);
+    p.logits = bf16_ptr(logits); p.row_stride = logits.stride(0);
+    p.rows = (int)logits.size(0); p.vocab_local = (int)logits.size(1); p.vocab_lo = vocab_lo;
+    p.world = (int)slots.size(); p.rank = rank;
+    TORCH_CHECK(p.world >= 1 && p.world <= TP_MAX_RANKS && counters.size() == slots.size(), "peer lists");
+    for (int i = 0; i < p.world; ++i) { p.slots[i] = (unsigned long long*)slots[i]; p.counters[i] = (unsigned int*)counters[i]; }
+    p.my_slots = (const unsigned long long*)my_slots; p.my_counters = (const unsigned int*)my_counters;
+    p.seq = make_seq(seq[0].cast<uint64_t>(), seq[1].cast<unsigned>(), seq[2].cast<unsigned>(), seq[3].cast<unsigned>());
+    p.next_ids = next_ids.data_ptr<int>(); p.timeout_ns = timeout_ns; p.status = status_ptr(status);
+    SKY_CUDA_CHECK(launch_tp_argmax(p, cur_stream()));
+}
+static void step_increment(torch::Tensor step) {
+    c10::cuda::CUDAGuard g(step.device());
+    SKY_CUDA_CHECK(launch_step_increment(reinterpret_cast<unsigned int*>(step.data_ptr()), cur_stream()));
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "SkyGDR-B200 sm_100a kernels";
     m.def("new_status", &new_status);
@@ -323,6 +412,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("embedding", &embedding);
     m.def("argmax", &argmax);
     m.def("gemm", &gemm);
+    m.def("gemm_tp", &gemm_tp);
+    m.def("tp_norm", &tp_norm);
+    m.def("tp_argmax", &tp_argmax);
+    m.def("step_increment", &step_increment);
     m.def("gemm_workspace_floats", &gemm_workspace_floats);
     m.def("gemm_counter_count", &gemm_counter_count);
     m.def("gemm_pick_ntok", &gemm_pick_ntok);

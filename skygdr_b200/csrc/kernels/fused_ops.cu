@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendParams
         const int blk = p.block_table[(long long)seq * p.max_blocks + pos / p.block_tokens];
         const int slot = pos % p.block_tokens;
         __nv_bfloat16* dst = p.kv + (long long)blk * p.block_stride + (is_k ? 0 : p.kv_stride) + (long long)kvh * p.head_stride +
-                             (long long)slot * 128 + lane * 4;
+                             (long long)slot * p.tok_stride + lane * 4;
         *reinterpret_cast<uint2*>(dst) = outv;
     }
 }

@@ -19,7 +19,7 @@ struct RopeAppendParams {
     const int* block_table;        // [seqs][max_blocks]
     const int* positions;          // [tokens] position of the token inside its sequence
     const int* seq_ids;            // [tokens] row of block_table; nullptr: token i belongs to sequence i
-    long long block_stride, kv_stride, head_stride;
+    long long block_stride, kv_stride, head_stride, tok_stride;  // head-major: (16*128, 128); token-major: (128, heads*128)
     int tokens, q_heads, kv_heads, max_blocks, block_tokens;
     float eps;
 };

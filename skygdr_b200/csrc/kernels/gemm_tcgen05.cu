@@ -20,6 +20,16 @@
 
 namespace sky {
 
+// Where output element (token t, column n) goes: the local y, or a peer's reduce-scatter slot.
+__device__ __forceinline__ void gemm_store(const GemmParams& p, int t, int n, float v) {
+    if (p.rs.world == 0) {
+        p.y[(long long)t * p.ldy + n] = __float2bfloat16(v);
+    } else {
+        const int j = t / p.rs.rows_per_rank, lr = t - j * p.rs.rows_per_rank;
+        p.rs.dst[j][((long long)(p.rs.src_rank * p.rs.rows_per_rank + lr)) * p.N + n] = __float2bfloat16(v);
+    }
+}
+
 constexpr int GEMM_THREADS = 192;
 constexpr int BM = 128;   // weight rows per tile (MMA M)
 constexpr int BK = 64;    // K per stage: 64 bf16 = 128 bytes = one swizzle row
@@ -68,9 +78,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         if (lane == 0) {
             tma_prefetch_desc(&tmap_w);
             tma_prefetch_desc(&tmap_x);
-            for (int i = 0; i < nkb; ++i) {
+            // Weights do not depend on any peer: start streaming them, then wait for the gathered
+            // activations, then add the x tiles to the stages already in flight.
+            const int pre = min(nkb, S::STAGES);
+            for (int i = 0; i < pre; ++i) {
+                unsigned char* st = smem + i * S::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[i], S::STAGE_BYTES);
+                const int kx = (kb0 + i) * BK;
+                tma_load_2d(st, &tmap_w, kx, n0, &full_bar[i]);
+                if (GATED) tma_load_2d(st + S::W_BYTES, &tmap_w, kx, p.N + n0, &full_bar[i]);
+            }
+            if (p.ag.n_src > 0 && *(volatile unsigned int*)&p.status->status == SKY_STATUS_OK) {
+                const unsigned seq = *p.ag.seq.step * p.ag.seq.uses_per_step + p.ag.seq.use_index + 1;
+                const unsigned want = seq * p.ag.seq.arrivals_per_use;
+                for (int r = 0; r < p.ag.n_src; ++r)
+                    if (!wait_flag_ge(p.ag.counters + r, want, p.ag.timeout_ns)) {
+                        set_status(p.status, SKY_STATUS_TIMEOUT_FLAG, (unsigned)r);
+                        break;
+                    }
+                // peers wrote x with ordinary stores; the loads below go through the async proxy
+                asm volatile("fence.proxy.async;" ::: "memory");
+            }
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(smem + i * S::STAGE_BYTES + S::W_BYTES * (GATED ? 2 : 1), &tmap_x, (kb0 + i) * BK, t0, &full_bar[i]);
+            for (int i = pre; i < nkb; ++i) {
                 const int s = i % S::STAGES;
-                if (i >= S::STAGES && !mbar_wait(&empty_bar[s], ((i / S::STAGES) - 1) & 1)) {
+                if (!mbar_wait(&empty_bar[s], ((i / S::STAGES) - 1) & 1)) {
                     set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 1);
                     break;
                 }
@@ -138,7 +171,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                     if (t < p.M && n < p.N) {
                         float val = __uint_as_float(v[i]);
                         if (GATED) { const float up = __uint_as_float(u[i]); val = val / (1.0f + __expf(-val)) * up; }
-                        p.y[(long long)t * p.ldy + n] = __float2bfloat16(val);
+                        gemm_store(p, t, n, val);
                     }
                 }
             } else {
@@ -164,18 +197,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 __threadfence();
                 const long long tile_id = (long long)tile_m * gridDim.x + tile_n;
                 const float* base = p.workspace + (tile_id * p.splits) * S::ACC_COLS * BM;
-                for (int c = 0; c < NTOK; ++c) {
-                    const int t = t0 + c;
-                    if (t >= p.M) break;
-                    float g = 0.f, up = 0.f;
+                // 8 token columns at a time: all their partial loads are in flight together
+#pragma unroll 1
+                for (int c0 = 0; c0 < NTOK; c0 += 8) {
+                    if (t0 + c0 >= p.M) break;
+                    float g[8], up[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) { g[j] = 0.f; up[j] = 0.f; }
                     for (int s2 = 0; s2 < p.splits; ++s2) {
-                        g += __ldcg(base + ((long long)s2 * S::ACC_COLS + c) * BM + r);
-                        if (GATED) up += __ldcg(base + ((long long)s2 * S::ACC_COLS + NTOK + c) * BM + r);
+                        float a[8], b[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            a[j] = __ldcg(base + ((long long)s2 * S::ACC_COLS + c0 + j) * BM + r);
+                            if (GATED) b[j] = __ldcg(base + ((long long)s2 * S::ACC_COLS + NTOK + c0 + j) * BM + r);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) { g[j] += a[j]; if (GATED) up[j] += b[j]; }
                     }
-                    if (GATED) g = g / (1.0f + __expf(-g)) * up;
-                    if (n < p.N) p.y[(long long)t * p.ldy + n] = __float2bfloat16(g);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int t = t0 + c0 + j;
+                        float val = g[j];
+                        if (GATED) val = val / (1.0f + __expf(-val)) * up[j];
+                        if (t < p.M && n < p.N) gemm_store(p, t, n, val);
+                    }
                 }
             }
+        }
+    }
+    if (p.rs.world > 0 && warp >= 2) {
+        // one arrival per destination from the CTA that wrote this tile's rows (with split-K: the last split)
+        const bool wrote = p.splits == 1 || s_last;
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (wrote && threadIdx.x == 64) {
+            __threadfence_system();
+            for (int j = 0; j < p.rs.world; ++j) red_release_sys_add_u32(p.rs.counters[j], 1u);
         }
     }
     tc_fence_before();

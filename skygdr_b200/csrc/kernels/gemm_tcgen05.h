@@ -7,6 +7,38 @@
 namespace sky {
 struct LaunchStatus;
 
+constexpr int TP_MAX_RANKS = 8;
+
+// Sequence number of a collective inside a replayed CUDA graph: kernels cannot carry a changing
+// immediate, so they read the step counter from device memory:
+//   seq = *step * uses_per_step + use_index + 1
+// and wait for counters to reach seq * arrivals_per_use (counters only ever grow).
+struct TpSeq {
+    const unsigned int* step;     // device counter, +1 per executed step
+    unsigned int uses_per_step;
+    unsigned int use_index;
+    unsigned int arrivals_per_use;
+};
+
+// all-gather -> GEMM: x is this GPU's gather buffer, filled row-block by row-block by the peers'
+// norm kernels. The TMA producer streams weights at once and holds the x loads until every
+// source's arrival counter has reached the value of this use.
+struct TpAgWait {
+    int n_src;                                    // 0: off
+    const unsigned int* counters;                 // [n_src] in local memory
+    TpSeq seq;
+    unsigned long long timeout_ns;
+};
+
+// GEMM -> reduce-scatter: instead of y, token row t goes to rank t / rows_per_rank, into that rank's
+// receive buffer slot [src_rank][t % rows_per_rank][N] (bf16), followed by one arrival on its counter.
+struct TpRsPush {
+    int world;                                    // 0: off
+    int src_rank, rows_per_rank;
+    __nv_bfloat16* dst[TP_MAX_RANKS];             // peers' receive buffers (peer-mapped)
+    unsigned int* counters[TP_MAX_RANKS];         // peers' arrival counters (peer-mapped)
+};
+
 struct GemmParams {
     const __nv_bfloat16* x;   // [M][K], row pitch ldx
     const __nv_bfloat16* w;   // [N][K] (gated: [2N][K], gate rows then up rows), row pitch ldw
@@ -18,6 +50,8 @@ struct GemmParams {
     float* workspace;         // split-K partials, gemm_workspace_floats() floats
     unsigned int* counters;   // split-K tile counters, gemm_counter_count() entries, zero before first use
     LaunchStatus* status;
+    TpAgWait ag;
+    TpRsPush rs;
 };
 
 int gemm_pick_ntok(int M, bool gated);

@@ -1,0 +1,345 @@
+"""Qwen3 dense decoder on the sm_100a kernels: random-init weights, paged KV
+cache, decode engine (optionally captured in a CUDA graph) and a prefill path.
+
+Architecture (Qwen3-8B): 36 layers, hidden 4096, 32 query / 8 KV heads of 128,
+SwiGLU FFN 12288, vocabulary 151936, RMSNorm, per-head QK-norm, rotary
+embedding (theta 1e6), untied lm_head.
+
+The reference does not contain a model: its decode workloads are KV-scan
+stressors (llm_problem_analysis/decode_vllm_kvcache_hbm_stress.cu,
+llm_problem_analysis/decode_transformer_kvcache_stress.cu) and its README names
+Qwen3-8B under vLLM as the case study (README.md:56-75). This is that decoder,
+built on this package's own kernels.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from .. import ops
+from ..ops.kv_cache import KVGeometry, PagedKVPool
+
+
+@dataclass
+class Qwen3Config:
+    layers: int = 36
+    hidden: int = 4096
+    q_heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 12288
+    vocab: int = 151936
+    rope_theta: float = 1e6
+    eps: float = 1e-6
+    name: str = "qwen3-8b"
+
+    @classmethod
+    def tiny(cls, layers: int = 2, vocab: int = 1024) -> "Qwen3Config":
+        return cls(layers=layers, hidden=512, q_heads=8, kv_heads=2, ffn=1024, vocab=vocab, name="qwen3-tiny")
+
+    @property
+    def geometry(self) -> KVGeometry:
+        return KVGeometry(self.layers, self.kv_heads, self.head_dim)
+
+    def param_count(self) -> int:
+        per_layer = (self.q_heads + 2 * self.kv_heads) * self.head_dim * self.hidden + self.q_heads * self.head_dim * self.hidden \
+            + 3 * self.ffn * self.hidden + 2 * self.hidden + 2 * self.head_dim
+        return self.layers * per_layer + 2 * self.vocab * self.hidden + self.hidden
+
+
+class LayerWeights:
+    __slots__ = ("qkv", "o", "gate_up", "down", "ln1", "ln2", "q_norm", "k_norm")
+
+
+class Qwen3Weights:
+    """Random-init weights in the fused layouts the kernels take: qkv rows = [q heads | k heads | v heads],
+    gate_up rows = [gate | up]. ``shard(rank, world)`` returns the tensor-parallel slice."""
+
+    def __init__(self, cfg: Qwen3Config, device="cuda", seed: int = 0, std: float = 0.02, tp_rank: int = 0, tp_world: int = 1):
+        self.cfg, self.tp_rank, self.tp_world = cfg, tp_rank, tp_world
+        gen = torch.Generator(device=device)
+        H, D = cfg.hidden, cfg.head_dim
+        assert cfg.q_heads % tp_world == 0 and cfg.kv_heads % tp_world == 0 and cfg.ffn % tp_world == 0
+        qh, kh, ff = cfg.q_heads // tp_world, cfg.kv_heads // tp_world, cfg.ffn // tp_world
+
+        def rnd(rows, cols, tag, scale=std):
+            # every (tensor, rank) draws from its own stream, so a shard equals the same rows of the full tensor
+            gen.manual_seed(seed * 1000003 + tag)
+            return (torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * scale).to(torch.bfloat16)
+
+        def rows_of(full_rows, tag, lo, hi, cols, scale=std):
+            full = rnd(full_rows, cols, tag, scale)
+            return full[lo:hi].contiguous()
+
+        self.layers: List[LayerWeights] = []
+        for li in range(cfg.layers):
+            w = LayerWeights()
+            t = li * 16
+            q = rows_of(cfg.q_heads * D, t + 1, tp_rank * qh * D, (tp_rank + 1) * qh * D, H)
+            k = rows_of(cfg.kv_heads * D, t + 2, tp_rank * kh * D, (tp_rank + 1) * kh * D, H)
+            v = rows_of(cfg.kv_heads * D, t + 3, tp_rank * kh * D, (tp_rank + 1) * kh * D, H)
+            w.qkv = torch.cat([q, k, v], 0).contiguous()
+            o_full = rnd(H, cfg.q_heads * D, t + 4)
+            w.o = o_full[:, tp_rank * qh * D:(tp_rank + 1) * qh * D].contiguous()       # row-parallel: K is sharded
+            gate = rows_of(cfg.ffn, t + 5, tp_rank * ff, (tp_rank + 1) * ff, H)
+            up = rows_of(cfg.ffn, t + 6, tp_rank * ff, (tp_rank + 1) * ff, H)
+            w.gate_up = torch.cat([gate, up], 0).contiguous()
+            down_full = rnd(H, cfg.ffn, t + 7)
+            w.down = down_full[:, tp_rank * ff:(tp_rank + 1) * ff].contiguous()
+            del o_full, down_full
+            gen.manual_seed(seed * 1000003 + t + 8)
+            w.ln1 = (1.0 + 0.1 * torch.randn(H, generator=gen, device=device)).to(torch.bfloat16)
+            w.ln2 = (1.0 + 0.1 * torch.randn(H, generator=gen, device=device)).to(torch.bfloat16)
+            w.q_norm = (1.0 + 0.1 * torch.randn(D, generator=gen, device=device)).to(torch.bfloat16)
+            w.k_norm = (1.0 + 0.1 * torch.randn(D, generator=gen, device=device)).to(torch.bfloat16)
+            self.layers.append(w)
+        self.embed = rnd(cfg.vocab, H, 900001, 1.0)
+        vs = (cfg.vocab + tp_world - 1) // tp_world
+        self.vocab_lo, self.vocab_hi = tp_rank * vs, min(cfg.vocab, (tp_rank + 1) * vs)
+        self.lm_head = rows_of(cfg.vocab, 900002, self.vocab_lo, self.vocab_hi, H)
+        gen.manual_seed(seed * 1000003 + 900003)
+        self.final_norm = (1.0 + 0.1 * torch.randn(H, generator=gen, device=device)).to(torch.bfloat16)
+
+    def nbytes(self) -> int:
+        n = self.embed.numel() + self.lm_head.numel() + self.final_norm.numel()
+        for w in self.layers:
+            n += sum(getattr(w, k).numel() for k in LayerWeights.__slots__)
+        return n * 2
+
+
+class Qwen3Decoder:
+    """Single-GPU decode engine: fixed-capacity batch, preallocated activations, optional CUDA graph."""
+
+    def __init__(self, cfg: Qwen3Config, weights: Qwen3Weights, pool: PagedKVPool, max_batch: int, max_ctx: int,
+                 attn_chunk: int = 1024):
+        assert pool.layout == "hnd"
+        self.cfg, self.w, self.pool = cfg, weights, pool
+        dev = pool.data.device
+        self.device = dev
+        self.max_batch, self.max_ctx = max_batch, max_ctx
+        B, H = max_batch, cfg.hidden
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        self.resid = torch.zeros((B, H), **bf)
+        self.xn = torch.empty((B, H), **bf)
+        self.h = torch.empty((B, H), **bf)
+        self.qkv = torch.empty((B, (cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim), **bf)
+        self.q = torch.empty((B, cfg.q_heads, cfg.head_dim), **bf)
+        self.attn_out = torch.empty((B, cfg.q_heads, cfg.head_dim), **bf)
+        self.act = torch.empty((B, cfg.ffn), **bf)
+        self.logits = torch.empty((B, weights.lm_head.shape[0]), **bf)
+        self.next_ids = torch.zeros((B,), dtype=torch.int32, device=dev)
+        self.ids = torch.zeros((B,), dtype=torch.int32, device=dev)
+        self.positions = torch.zeros((B,), dtype=torch.int32, device=dev)
+        self.ctx_lens = torch.ones((B,), dtype=torch.int32, device=dev)
+        self.max_blocks = (max_ctx + 15) // 16
+        self.block_table = torch.zeros((B, self.max_blocks), dtype=torch.int32, device=dev)
+        self.inv_freq = ops.rope_inv_freq(cfg.rope_theta, dev, cfg.head_dim)
+        self.attn = ops.PagedAttention(dev, B, cfg.q_heads, cfg.kv_heads, max_ctx, attn_chunk)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.graph_batch = 0
+        self.kernels_per_step = 1 + 8 * cfg.layers + 3   # embedding, 8 per layer, final norm, lm_head, argmax
+
+    # ---- state ----
+    def set_batch(self, ids: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor) -> None:
+        """ids/positions: the token to feed for every sequence and its position; the cache already holds
+        positions [0, position) of each sequence in the blocks of ``block_table``."""
+        b = ids.numel()
+        self.ids[:b].copy_(ids)
+        self.positions[:b].copy_(positions)
+        self.ctx_lens[:b].copy_(positions + 1)
+        self.block_table[:b, :block_table.shape[1]].copy_(block_table)
+
+    # ---- one decode step for the first `b` slots ----
+    def _step(self, b: int, max_ctx: int) -> None:
+        cfg, w = self.cfg, self.w
+        resid, xn, h = self.resid[:b], self.xn[:b], self.h[:b]
+        qkv, q, ao, act = self.qkv[:b], self.q[:b], self.attn_out[:b], self.act[:b]
+        pos, ctx, table = self.positions[:b], self.ctx_lens[:b], self.block_table[:b]
+        ops.embedding(self.ids[:b], w.embed, out=resid)
+        for li, lw in enumerate(w.layers):
+            if li == 0:
+                ops.rmsnorm(resid, lw.ln1, cfg.eps, out=xn)
+            else:
+                ops.rmsnorm(h, lw.ln1, cfg.eps, residual=resid, out=xn)
+            ops.gemm(xn, lw.qkv, out=qkv)
+            ops.rope_append(qkv, lw.q_norm, lw.k_norm, self.pool, li, self.inv_freq, table, pos, cfg.q_heads, cfg.eps, q_out=q)
+            self.attn(q, self.pool, li, table, ctx, max_ctx=max_ctx, out=ao)
+            ops.gemm(ao.view(b, -1), lw.o, out=h)
+            ops.rmsnorm(h, lw.ln2, cfg.eps, residual=resid, out=xn)
+            ops.gemm(xn, lw.gate_up, out=act, gated=True)
+            ops.gemm(act, lw.down, out=h)
+        ops.rmsnorm(h, w.final_norm, cfg.eps, residual=resid, out=xn)
+        ops.gemm(xn, w.lm_head, out=self.logits[:b])
+        ops.argmax(self.logits[:b], out=self.next_ids[:b])
+
+    def _advance(self, b: int) -> None:
+        self.ids[:b].copy_(self.next_ids[:b])
+        self.positions[:b].add_(1)
+        self.ctx_lens[:b].add_(1)
+
+    def step(self, b: Optional[int] = None, max_ctx: Optional[int] = None, advance: bool = True) -> torch.Tensor:
+        """Eager decode step. Returns the sampled ids (a view; valid until the next step)."""
+        b = b or self.max_batch
+        self._step(b, max_ctx or self.max_ctx)
+        if advance:
+            self._advance(b)
+        return self.next_ids[:b]
+
+    def capture(self, b: Optional[int] = None, max_ctx: Optional[int] = None) -> None:
+        """Captures step+advance for batch ``b`` into a CUDA graph (launch-bound otherwise: ~290 kernels/step)."""
+        b = b or self.max_batch
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        keep = (self.ids.clone(), self.positions.clone(), self.ctx_lens.clone())
+        with torch.cuda.stream(s):
+            self._step(b, max_ctx or self.max_ctx)      # warm-up outside capture (lazy attribute set-up, workspaces)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                self._step(b, max_ctx or self.max_ctx)
+                self._advance(b)
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        self.ids.copy_(keep[0]); self.positions.copy_(keep[1]); self.ctx_lens.copy_(keep[2])
+        self.graph, self.graph_batch = g, b
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.next_ids[:self.graph_batch]
+
+    # ---- prefill: whole prompts, token-major or head-major pool, returns last-position logits ----
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor, seq_lens: List[int], block_table: torch.Tensor, pool: Optional[PagedKVPool] = None,
+                chunk: int = 2048) -> torch.Tensor:
+        """Runs the prompts through the stack, writing K/V into ``pool`` (default: the decode pool).
+
+        GEMMs and K/V append use this package's kernels. The causal attention over the prompt uses
+        torch's scaled_dot_product_attention (a library kernel): prefill attention is not one of the
+        contended paths this runtime schedules."""
+        cfg, w = self.cfg, self.w
+        pool = pool or self.pool
+        dev = ids.device
+        T = int(ids.numel())
+        seq_ids = torch.repeat_interleave(torch.arange(len(seq_lens), device=dev, dtype=torch.int32),
+                                          torch.tensor(seq_lens, device=dev))
+        starts = torch.cumsum(torch.tensor([0] + seq_lens[:-1], device=dev), 0)
+        positions = (torch.arange(T, device=dev) - torch.repeat_interleave(starts, torch.tensor(seq_lens, device=dev))).int()
+        resid = ops.embedding(ids.int(), w.embed)
+        h = None
+        D = cfg.head_dim
+        for li, lw in enumerate(w.layers):
+            xn = ops.rmsnorm(resid, lw.ln1, cfg.eps) if h is None else ops.rmsnorm(h, lw.ln1, cfg.eps, residual=resid)
+            qkv = ops.gemm(xn, lw.qkv)
+            q = ops.rope_append(qkv, lw.q_norm, lw.k_norm, pool, li, self.inv_freq, block_table, positions, cfg.q_heads, cfg.eps,
+                                seq_ids=seq_ids)
+            ao = torch.empty_like(q)
+            o = 0
+            for si, n in enumerate(seq_lens):
+                nb = (n + 15) // 16
+                kvb = pool.data[block_table[si, :nb].long(), li]        # [nb][2][...]
+                if pool.layout == "hnd":
+                    k = kvb[:, 0].permute(1, 0, 2, 3).reshape(cfg.kv_heads, nb * 16, D)[:, :n]
+                    v = kvb[:, 1].permute(1, 0, 2, 3).reshape(cfg.kv_heads, nb * 16, D)[:, :n]
+                else:
+                    k = kvb[:, 0].reshape(nb * 16, cfg.kv_heads, D)[:n].transpose(0, 1)
+                    v = kvb[:, 1].reshape(nb * 16, cfg.kv_heads, D)[:n].transpose(0, 1)
+                qs = q[o:o + n].transpose(0, 1)                         # [Hq][n][D]
+                out = torch.nn.functional.scaled_dot_product_attention(qs[None], k[None], v[None], is_causal=True, enable_gqa=True)
+                ao[o:o + n] = out[0].transpose(0, 1)
+                o += n
+            h = ops.gemm(ao.view(T, -1), lw.o)
+            xn = ops.rmsnorm(h, lw.ln2, cfg.eps, residual=resid)
+            act = ops.gemm(xn, lw.gate_up, gated=True)
+            h = ops.gemm(act, lw.down)
+        xn = ops.rmsnorm(h, w.final_norm, cfg.eps, residual=resid)
+        last = torch.cumsum(torch.tensor(seq_lens, device=dev), 0) - 1
+        return ops.gemm(xn[last].contiguous(), w.lm_head)
+
+
+# ---------------------------------------------------------------------------
+# Plain PyTorch reference of the same network (test oracle): fp32 math on the same bf16 weights,
+# contiguous KV, no paging.
+
+@torch.no_grad()
+def reference_forward(cfg: Qwen3Config, w: Qwen3Weights, ids: torch.Tensor) -> torch.Tensor:
+    """Full-sequence forward of one prompt; returns logits [tokens][vocab] in fp32."""
+    T = ids.numel()
+    D, Hq, Hkv = cfg.head_dim, cfg.q_heads, cfg.kv_heads
+
+    def norm(x, g):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.eps) * g.float()
+
+    def bf(x):
+        return x.to(torch.bfloat16).float()
+
+    inv = ops.rope_inv_freq(cfg.rope_theta, ids.device, D)
+    pos = torch.arange(T, device=ids.device).float()
+    ang = pos[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rope(x):
+        x1, x2 = x[..., :D // 2], x[..., D // 2:]
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
+
+    resid = w.embed[ids.long()].float()
+    h = None
+    for lw in w.layers:
+        if h is not None:
+            resid = bf(resid + h)
+        xn = bf(norm(resid, lw.ln1))
+        qkv = bf(xn @ lw.qkv.float().t()).view(T, Hq + 2 * Hkv, D)
+        q = bf(rope(bf(norm(qkv[:, :Hq], lw.q_norm))))
+        k = bf(rope(bf(norm(qkv[:, Hq:Hq + Hkv], lw.k_norm))))
+        v = qkv[:, Hq + Hkv:]
+        kr = k.repeat_interleave(Hq // Hkv, 1)
+        vr = v.repeat_interleave(Hq // Hkv, 1)
+        s = torch.einsum("thd,shd->hts", q, kr) / math.sqrt(D)
+        s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool, device=ids.device), 1)[None], float("-inf"))
+        ao = bf(torch.einsum("hts,shd->thd", torch.softmax(s, -1), vr)).reshape(T, Hq * D)
+        h = bf(ao @ lw.o.float().t())
+        resid = bf(resid + h)
+        xn = bf(norm(resid, lw.ln2))
+        gu = xn @ lw.gate_up.float().t()
+        act = bf(torch.nn.functional.silu(gu[:, :cfg.ffn]) * gu[:, cfg.ffn:])
+        h = bf(act @ lw.down.float().t())
+    resid = bf(resid + h)
+    xn = bf(norm(resid, w.final_norm))
+    return xn @ w.lm_head.float().t()
+
+
+class DecodeSession:
+    """The call a user makes to decode: host token ids in, host token ids out, one step at a time.
+
+    Every ``step`` copies the step's inputs (ids and positions, pinned host memory) to the device, runs the
+    captured decode graph, and reads the sampled ids back to pinned host memory."""
+
+    def __init__(self, engine: "Qwen3Decoder", batch: int, max_ctx: Optional[int] = None):
+        self.eng, self.batch = engine, batch
+        self.h_ids = torch.zeros(batch, dtype=torch.int32).pin_memory()
+        self.h_pos = torch.zeros(batch, dtype=torch.int32).pin_memory()
+        self.h_out = torch.zeros(batch, dtype=torch.int32).pin_memory()
+        self.max_ctx = max_ctx or engine.max_ctx
+        if engine.graph is None or engine.graph_batch != batch:
+            engine.capture(batch, self.max_ctx)
+        self.h2d_bytes_per_step = self.h_ids.numel() * 4 + self.h_pos.numel() * 4
+        self.d2h_bytes_per_step = self.h_out.numel() * 4
+
+    def start(self, ids: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor) -> None:
+        self.eng.set_batch(ids.to(self.eng.device), positions.to(self.eng.device), block_table.to(self.eng.device))
+        self.h_ids.copy_(ids.cpu())
+        self.h_pos.copy_(positions.cpu())
+
+    def step(self) -> torch.Tensor:
+        e, b = self.eng, self.batch
+        e.ids[:b].copy_(self.h_ids, non_blocking=True)
+        e.positions[:b].copy_(self.h_pos, non_blocking=True)
+        e.ctx_lens[:b].copy_(e.positions[:b])
+        e.ctx_lens[:b].add_(1)
+        e.replay()
+        self.h_out.copy_(e.next_ids[:b], non_blocking=True)
+        torch.cuda.current_stream(e.device).synchronize()
+        self.h_ids.copy_(self.h_out)
+        self.h_pos.add_(1)
+        return self.h_out

@@ -30,8 +30,12 @@ def rope_append(qkv: torch.Tensor, q_norm, k_norm, pool: PagedKVPool, layer: int
     if q_out is None:
         q_out = torch.empty((tokens, q_heads, 128), dtype=torch.bfloat16, device=qkv.device)
     bs, ls, ks = pool.strides
+    if pool.layout == "hnd":
+        hs, ts = pool.data.stride(3), pool.data.stride(4)
+    else:
+        ts, hs = pool.data.stride(3), pool.data.stride(4)
     load().rope_append(qkv, q_norm, k_norm, q_out, pool.layer_base(layer), inv_freq, block_table, positions, seq_ids, bs, ks,
-                       pool.head_stride, q_heads, pool.geom.kv_heads, eps)
+                       hs, ts, q_heads, pool.geom.kv_heads, eps)
     return q_out
 
 

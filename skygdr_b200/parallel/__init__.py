@@ -1,0 +1,1 @@
+"""Peer memory, tensor parallelism and prefill/decode disaggregation."""
