@@ -59,7 +59,7 @@ public:
         if (!policy_) policy_ = make_policy("none", cfg.pcfg);
     }
     ~DaemonCore() {
-        for (auto& kv : state_) release_page(kv.second);
+        for (auto& kv : state_) release_page(kv.second, /*at_exit=*/true);
     }
 
     struct WindowLog {
@@ -212,6 +212,8 @@ public:
                 pg->unlimited = 1;
                 pg->budget_per_window = 0;
             } else {
+                // Leaving the unlimited state: bytes taken while ungated were never counted against a grant.
+                if (pg->unlimited && pg->consumed_bytes > st.bucket.granted) st.bucket.granted = pg->consumed_bytes;
                 uint64_t g = st.bucket.refill(budget, (uint64_t)(dt * 1e9), pg->consumed_bytes);
                 pg->budget_per_window = (uint64_t)(budget * 1e9 * double(cfg_.window_ns) * 1e-9);
                 __atomic_store_n(&pg->granted_bytes, g, __ATOMIC_RELEASE);
@@ -360,10 +362,12 @@ private:
         st.ctl.enable();
         __atomic_store_n(&st.page->magic, SKYGDR_CREDIT_MAGIC, __ATOMIC_RELEASE);
     }
-    void release_page(FlowState& st) {
+    // A flow that is dropped (unregistered, lease expired) loses its page file; at daemon exit the files
+    // stay when a snapshot is kept, so that a restarted daemon finds them.
+    void release_page(FlowState& st, bool at_exit = false) {
         if (!st.page) return;
         if (st.heap) free(st.page);
-        else { unmap_credit_page(st.page); if (!st.path.empty() && !keep_pages_) unlink(st.path.c_str()); }
+        else { unmap_credit_page(st.page); if (!st.path.empty() && !(at_exit && keep_pages_)) unlink(st.path.c_str()); }
         st.page = nullptr;
     }
     void drop_state(uint32_t id) {

@@ -35,6 +35,22 @@ __device__ __forceinline__ void cvt8(uint4 v, float* f) {
     f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
 }
 
+// Two fp32 FMAs in one instruction (Blackwell packed-fp32 pipe): d = a * b + c on register pairs.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+          "l"(*reinterpret_cast<unsigned long long*>(&c)));
+    return d;
+}
+__device__ __forceinline__ void cvt8x2(uint4 v, float2* f) {
+    f[0] = make_float2(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u));
+    f[1] = make_float2(__uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+    f[2] = make_float2(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u));
+    f[3] = make_float2(__uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
+}
+
 // T = tokens per page (16), G = query heads per kv head, STAGES = ring depth per warp.
 template <int G, int T, int STAGES>
 __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const PagedAttnParams p) {
@@ -65,7 +81,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
     __syncwarp();
 
     // q, pre-scaled by scale*log2(e): lane holds dims [dl*8, dl*8+8) and [64+dl*8, 64+dl*8+8) of each head
-    float q[G][16];
+    float2 q[G][8];
     {
         const float qs = p.scale * 1.4426950408889634f;
 #pragma unroll
@@ -73,10 +89,10 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
             const __nv_bfloat16* qp = p.q + ((long long)b * p.q_heads + kvh * G + g) * ATT_D;
             uint4 a = *reinterpret_cast<const uint4*>(qp + dl * 8);
             uint4 c = *reinterpret_cast<const uint4*>(qp + 64 + dl * 8);
-            cvt8(a, q[g]);
-            cvt8(c, q[g] + 8);
+            cvt8x2(a, q[g]);
+            cvt8x2(c, q[g] + 4);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) q[g][i] *= qs;
+            for (int i = 0; i < 8; ++i) { q[g][i].x *= qs; q[g][i].y *= qs; }
         }
     }
 
@@ -95,12 +111,13 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
     if (lane == 0)
         for (int j = 0; j < min(STAGES, my_n); ++j) issue(j);
 
-    float m[G], l[G], acc[G][16];
+    float m[G], l[G];
+    float2 acc[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         m[g] = -INFINITY; l[g] = 0.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) acc[g][i] = 0.f;
+        for (int i = 0; i < 8; ++i) acc[g][i] = make_float2(0.f, 0.f);
     }
 
     bool failed = false;
@@ -116,14 +133,15 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
 #pragma unroll
         for (int it = 0; it < ITERS; ++it) {
             const int t = it * 4 + ts;
-            float k[16];
-            cvt8(*reinterpret_cast<const uint4*>(kpage + t * 256 + dl * 16), k);
-            cvt8(*reinterpret_cast<const uint4*>(kpage + t * 256 + 128 + dl * 16), k + 8);
+            float2 k[8];
+            cvt8x2(*reinterpret_cast<const uint4*>(kpage + t * 256 + dl * 16), k);
+            cvt8x2(*reinterpret_cast<const uint4*>(kpage + t * 256 + 128 + dl * 16), k + 4);
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                float a = 0.f;
+                float2 a2 = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) a = fmaf(q[g][i], k[i], a);
+                for (int i = 0; i < 8; ++i) a2 = ffma2(q[g][i], k[i], a2);
+                float a = a2.x + a2.y;
                 a += __shfl_xor_sync(0xffffffffu, a, 1);
                 a += __shfl_xor_sync(0xffffffffu, a, 2);
                 a += __shfl_xor_sync(0xffffffffu, a, 4);
@@ -144,7 +162,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
                 const float r = exp2f(m[g] - mn);  // 0 when m was -inf
                 l[g] *= r;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) acc[g][i] *= r;
+                for (int i = 0; i < 8; ++i) { acc[g][i].x *= r; acc[g][i].y *= r; }
                 m[g] = mn;
             }
         }
@@ -152,15 +170,16 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
 #pragma unroll
         for (int it = 0; it < ITERS; ++it) {
             const int t = it * 4 + ts;
-            float v[16];
-            cvt8(*reinterpret_cast<const uint4*>(vpage + t * 256 + dl * 16), v);
-            cvt8(*reinterpret_cast<const uint4*>(vpage + t * 256 + 128 + dl * 16), v + 8);
+            float2 v[8];
+            cvt8x2(*reinterpret_cast<const uint4*>(vpage + t * 256 + dl * 16), v);
+            cvt8x2(*reinterpret_cast<const uint4*>(vpage + t * 256 + 128 + dl * 16), v + 4);
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 const float pr = m[g] == -INFINITY ? 0.f : exp2f(sc[it][g] - m[g]);
                 l[g] += pr;
+                const float2 pr2 = make_float2(pr, pr);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) acc[g][i] = fmaf(pr, v[i], acc[g][i]);
+                for (int i = 0; i < 8; ++i) acc[g][i] = ffma2(pr2, v[i], acc[g][i]);
             }
         }
         __syncwarp();
@@ -178,9 +197,11 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
         l[g] += __shfl_xor_sync(0xffffffffu, l[g], 8);
         l[g] += __shfl_xor_sync(0xffffffffu, l[g], 16);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            acc[g][i] += __shfl_xor_sync(0xffffffffu, acc[g][i], 8);
-            acc[g][i] += __shfl_xor_sync(0xffffffffu, acc[g][i], 16);
+        for (int i = 0; i < 8; ++i) {
+            acc[g][i].x += __shfl_xor_sync(0xffffffffu, acc[g][i].x, 8);
+            acc[g][i].x += __shfl_xor_sync(0xffffffffu, acc[g][i].x, 16);
+            acc[g][i].y += __shfl_xor_sync(0xffffffffu, acc[g][i].y, 8);
+            acc[g][i].y += __shfl_xor_sync(0xffffffffu, acc[g][i].y, 16);
         }
     }
     // ---- merge the warps through shared memory (the ring is idle now) ----
@@ -193,9 +214,11 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
         for (int g = 0; g < G; ++g) {
             if (dl == 0) { sm_m[warp * G + g] = m[g]; sm_l[warp * G + g] = l[g]; }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                sm_o[(warp * G + g) * ATT_D + dl * 8 + i] = acc[g][i];
-                sm_o[(warp * G + g) * ATT_D + 64 + dl * 8 + i] = acc[g][8 + i];
+            for (int i = 0; i < 4; ++i) {
+                sm_o[(warp * G + g) * ATT_D + dl * 8 + 2 * i] = acc[g][i].x;
+                sm_o[(warp * G + g) * ATT_D + dl * 8 + 2 * i + 1] = acc[g][i].y;
+                sm_o[(warp * G + g) * ATT_D + 64 + dl * 8 + 2 * i] = acc[g][4 + i].x;
+                sm_o[(warp * G + g) * ATT_D + 64 + dl * 8 + 2 * i + 1] = acc[g][4 + i].y;
             }
         }
     }

@@ -19,15 +19,30 @@ def _sms(device) -> int:
 
 
 def pick_splits(M: int, N: int, K: int, sms: int, gated: bool = False) -> int:
-    """Split-K factor that brings the CTA count close to the SM count for small-M GEMMs."""
+    """Split-K factor for weight-streaming GEMMs: one CTA occupies one SM, so the CTA count should fill
+    whole waves of ``sms``. Picks the factor (each split keeps at least 4 k-blocks of 64) whose last wave is
+    fullest; ties go to the smaller factor."""
     C = load()
     ntok = C.gemm_pick_ntok(M, gated)
     tiles = ((N + 127) // 128) * ((M + ntok - 1) // ntok)
     kb = K // 64
-    if tiles >= sms or kb < 8:
+    if tiles >= 4 * sms or M > 128:
         return 1
-    s = max(1, min(sms // tiles, kb // 4, 8))
-    return s
+    best, best_eff = 1, 0.0
+    for s in range(1, 17):
+        if s > 1 and kb // s < 4:
+            break
+        per = (kb + s - 1) // s
+        s_eff = (kb + per - 1) // per          # splits that actually get work
+        ctas = tiles * s_eff
+        waves = (ctas + sms - 1) // sms
+        # time ~ waves * per (k-blocks streamed back to back by the busiest SM)
+        eff = (tiles * kb) / (waves * per * sms)
+        if s > 1:
+            eff /= 1.0 + s_eff * ntok * 4.0 / K      # fp32 partials written and re-read, relative to the weight bytes
+        if eff > best_eff + 0.03:
+            best, best_eff = s, eff
+    return best
 
 
 class GemmWorkspace:

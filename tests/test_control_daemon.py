@@ -1,0 +1,153 @@
+"""fabricd as a process: registration over TCP, grants in shared pages, leases, crash and restart,
+legacy one-command clients. Also the NVML signal collectors against a fake NVML.
+
+Every failure here is made on the host: a client that stops renewing, a daemon that is killed."""
+import os
+import time
+
+import pytest
+
+from skygdr_b200.control import FabricClient, FabricDaemon, send_control
+from skygdr_b200.control.client import parse_reply
+
+
+@pytest.fixture()
+def daemon(tmp_path):
+    d = FabricDaemon(policy="target_track", window_us=2000, capacity_gbps=64.0, lease_ms=600,
+                     log=str(tmp_path / "windows.csv"), snapshot=str(tmp_path / "snap.json"))
+    yield d
+    d.stop()
+
+
+def _wait(pred, timeout=3.0):
+    t0 = time.time()
+    while time.time() - t0 < timeout:
+        if pred():
+            return True
+        time.sleep(0.01)
+    return False
+
+
+def test_register_and_grants_flow_through_shared_pages(daemon, tmp_path):
+    with FabricClient(port=daemon.port) as c:
+        kv = c.register("kv_transfer", "high", 40.0)
+        off = c.register("kv_offload", "besteffort", 0.0)
+        assert kv.flow_id == 1 and off.page_path and os.path.exists(off.page_path)
+        assert _wait(lambda: off.grant()["epoch"] > 3)
+        assert off.grant()["unlimited"] == 1 and kv.grant()["target_gbps"] == 40.0
+        # the protected flow reports backlog; the offload reports heavy use: its page turns to a finite grant
+        moved = 0
+        def pump():
+            nonlocal moved
+            moved += 200_000_000
+            off.report(moved, moved, 1 << 40)
+            kv.report(0, 0, 500_000_000)
+            c.renew(kv); c.renew(off)
+            return off.grant()["unlimited"] == 0
+        assert _wait(pump)
+        g1 = off.grant()["granted_bytes"]
+        assert g1 >= moved - 200_000_000 and off.grant()["mode"] == 6          # CUSTOM: a computed budget
+        b = c.budget(off)
+        assert b["status"] == "OK" and float(b["budget_gbps"]) > 0
+        # protected flow done -> released
+        kv.report(500_000_000, 500_000_000, 0)
+        assert _wait(lambda: (c.renew(off), c.renew(kv), off.grant()["unlimited"] == 1)[2])
+        # legacy single-command client against the daemon's flow addressing
+        rep = send_control("127.0.0.1", daemon.port, f"FLOW {off.flow_id} LOW1")
+        assert rep.startswith("OK mode=LOW1")
+        assert _wait(lambda: (c.renew(off), off.grant()["mode"] == 2 and off.grant()["unlimited"] == 0)[1])
+        assert parse_reply(send_control("127.0.0.1", daemon.port, "PING"))["status"] == "OK"
+    daemon.stop()
+    rows = open(tmp_path / "windows.csv").read().splitlines()
+    assert rows[0].startswith("ts_unix_ms,window_id,flow_id,flow,mode,decision,budget_bytes") and len(rows) > 10
+    assert any(",MANUAL," in r for r in rows)
+
+
+def test_lease_expiry_collects_a_silent_flow(daemon):
+    with FabricClient(port=daemon.port) as c:
+        a = c.register("kv_offload", "besteffort", 0.0)
+        b = c.register("kv_transfer", "high", 40.0)
+        path = a.page_path
+        t0 = time.time()
+        while time.time() - t0 < 1.5:          # renew only b; a's client has gone silent
+            c.renew(b)
+            time.sleep(0.05)
+        flows = c.request("FLOWS")
+        assert flows.startswith("OK n=1 ") and "kv_transfer" in flows
+        assert a.grant()["stop"] == 1           # a data path still running on the dead lease is told to drain
+        assert not os.path.exists(path)
+        assert c.request(f"RENEW {a.flow_id}") == "ERR unknown_flow"
+
+
+def test_daemon_crash_leaves_last_grant_and_restart_restores_flows(tmp_path):
+    snap = str(tmp_path / "snap.json")
+    d = FabricDaemon(window_us=2000, lease_ms=5000, snapshot=snap)
+    with FabricClient(port=d.port) as c:
+        off = c.register("kv_offload", "besteffort", 0.0)
+        kv = c.register("kv_transfer", "high", 40.0)
+        off.report(10**9, 10**9, 1 << 40)
+        kv.report(0, 0, 10**9)
+        assert _wait(lambda: off.grant()["unlimited"] == 0)
+    port = d.port
+    d.stop()                                    # SIGTERM: snapshot written, pages kept
+    assert os.path.exists(snap) and os.path.exists(off.page_path)
+    e0 = off.grant()["epoch"]
+    time.sleep(0.05)
+    assert off.grant()["epoch"] == e0           # heartbeat stopped: a data path can see the daemon is gone
+    granted = off.grant()["granted_bytes"]
+    d2 = FabricDaemon(port=port, window_us=2000, lease_ms=5000, snapshot=snap, restore=snap)
+    try:
+        with FabricClient(port=d2.port) as c:
+            assert c.request("FLOWS").startswith("OK n=2 ")
+            assert _wait(lambda: off.grant()["epoch"] > e0)
+            assert off.grant()["granted_bytes"] >= granted
+            assert c.renew(off) and c.unregister(kv)
+    finally:
+        d2.stop()
+
+
+def test_killed_daemon_is_detected_by_clients(tmp_path):
+    d = FabricDaemon(window_us=2000)
+    c = FabricClient(port=d.port)
+    f = c.register("kv_offload", "besteffort", 0.0)
+    d.kill()
+    with pytest.raises((ConnectionError, OSError)):
+        for _ in range(3):
+            c.renew(f)
+    with pytest.raises(OSError):
+        send_control("127.0.0.1", d.port, "PING", timeout_s=0.5)
+    c.sock.close()
+    if f.page_path and os.path.exists(f.page_path):
+        os.unlink(f.page_path)
+
+
+def test_signals_with_fake_nvml(ctl):
+    state = {"tx": 10 * 1024 * 1024, "rx": 40 * 1024 * 1024, "mem": 50, "nv": [0, 0]}
+    fake = {"name": "NVIDIA B200", "pcie_gen": 5, "pcie_width": 16,
+            "pcie": lambda c: state["tx"] if c == 0 else state["rx"], "util": lambda: (90, state["mem"]),
+            "nvlink": lambda: tuple(state["nv"])}
+    sig = ctl.GpuSignals(0, fake)
+    assert sig.available and sig.name == "NVIDIA B200"
+    assert sig.pcie_peak_gib_s == pytest.approx(3.938 * 16 * 1e9 / 2**30)
+    s = sig.sample_pcie()
+    assert s.valid and s.tx_gib_s == pytest.approx(10.0) and s.rx_gib_s == pytest.approx(40.0)
+    assert s.rx_util_pct == pytest.approx(100 * 40.0 / sig.pcie_peak_gib_s)
+    state["rx"] = 20 * 1024 * 1024
+    s2 = sig.sample_pcie()
+    assert s2.rx_peak_util_pct == pytest.approx(s.rx_util_pct) and s2.rx_util_pct < s.rx_util_pct
+    assert ctl.GpuSignals.pcie_csv_header() == ("ts_unix_ms,t_ms,pcie_tx_GiB_s,pcie_rx_GiB_s,pcie_tx_util_pct,pcie_rx_util_pct,"
+                                                "pcie_tx_peak_util_pct,pcie_rx_peak_util_pct")
+    assert len(s2.csv().split(",")) == 8
+    h = sig.sample_hbm()
+    assert h.valid and h.peak_gb_s == 7700 and h.estimated_gb_s == pytest.approx(3850)
+    assert ctl.GpuSignals.hbm_csv_header().startswith("ts_unix_ms,elapsed_ms,memory_util_pct,estimated_mem_bw_GB_s")
+    assert h.csv().endswith(",0,NVIDIA B200")
+    assert not sig.sample_nvlink().valid            # first sample has no delta yet
+    state["nv"] = [1_000_000, 3_000_000]
+    time.sleep(0.02)
+    n = sig.sample_nvlink()
+    assert n.valid and n.rx_gb_s == pytest.approx(3 * n.tx_gb_s, rel=1e-6) and n.tx_gb_s > 0
+    failing = ctl.GpuSignals(0, {"name": "x", "pcie": lambda c: None})
+    assert not failing.sample_pcie().valid          # an NVML error gives an invalid sample, not an exception
+    assert ctl.hbm_peak_gbs("NVIDIA H200") == 4800 and ctl.hbm_peak_gbs("unknown") == 0
+    assert ctl.pcie_lane_gbs(4) == pytest.approx(1.969)

@@ -1,0 +1,170 @@
+"""Legacy control protocol (golden strings), registry, daemon core, token bucket."""
+import math
+
+import pytest
+
+
+def test_parse_size_binary_suffixes(ctl):
+    assert ctl.parse_size("64") == 64
+    assert ctl.parse_size("128K") == 128 << 10
+    assert ctl.parse_size("4M") == 4 << 20
+    assert ctl.parse_size("2G") == 2 << 30
+    assert ctl.parse_size("1GiB") == 1 << 30
+    assert ctl.parse_size("x") is None and ctl.parse_size("") is None and ctl.parse_size("12Q") is None
+    assert ctl.parse_size("99999999999999999999999") is None
+
+
+def test_percentile_linear_interpolation(ctl):
+    v = [10.0, 20.0, 30.0, 40.0]
+    assert ctl.percentile(v, 0.5) == pytest.approx(25.0)
+    assert ctl.percentile(v, 0.0) == 10.0 and ctl.percentile(v, 1.0) == 40.0
+    assert ctl.percentile(v, 0.99) == pytest.approx(39.7)
+    assert ctl.percentile([], 0.5) == 0.0
+
+
+def test_legacy_replies_are_byte_exact(ctl):
+    s = ctl.ControlState()
+    s.configure(0, 100)
+    s.enable()
+    tail = "high_sleep_us=0 low1_sleep_us=100 low2_sleep_us=125 low3_sleep_us=150 low4_sleep_us=175"
+    assert s.handle("STATUS\n") == f"OK mode=HIGH sleep_us=0 {tail} commands=0 stop=0\n"
+    assert s.handle("LOW") == f"OK mode=LOW1 sleep_us=100 {tail} commands=1 stop=0\n"
+    assert s.handle("  LOW3 \r\n") == f"OK mode=LOW3 sleep_us=150 {tail} commands=2 stop=0\n"
+    assert s.handle("SLEEP 42") == f"OK mode=CUSTOM sleep_us=42 {tail} commands=3 stop=0\n"
+    assert s.handle("STATUS") == f"OK mode=CUSTOM sleep_us=42 {tail} commands=3 stop=0\n"      # STATUS is not counted
+    assert s.handle("bogus") == f"ERR unknown_cmd mode=CUSTOM sleep_us=42 {tail} commands=3 stop=0\n"
+    assert s.handle("   ") == f"ERR empty mode=CUSTOM sleep_us=42 {tail} commands=3 stop=0\n"
+    assert s.handle("STOP") == f"OK mode=CUSTOM sleep_us=42 {tail} commands=4 stop=1\n"
+    assert s.handle("HIGH") == f"OK mode=HIGH sleep_us=0 {tail} commands=5 stop=1\n"
+    assert s.stop_requested and s.mode == 1
+
+
+def test_ladder_presets_can_be_overridden(ctl):
+    s = ctl.ControlState()
+    s.configure(5, 200, low2_us=300, low4_us=1000)
+    s.enable()
+    assert "low2_sleep_us=300 low3_sleep_us=300 low4_sleep_us=1000" in s.handle("STATUS")
+    assert "sleep_us=5 " in s.handle("HIGH")
+
+
+def test_ladder_fraction_follows_the_sleep_ladder(ctl):
+    f1 = 0.5
+    assert ctl.ladder_fraction(1, f1) == 1.0
+    assert ctl.ladder_fraction(2, f1) == pytest.approx(0.5)
+    assert ctl.ladder_fraction(3, f1) == pytest.approx(1 / 2.25)
+    assert ctl.ladder_fraction(5, f1) == pytest.approx(1 / 2.75)
+    assert [ctl.next_protect_mode(m) for m in (1, 2, 3, 4, 5, 0, 6)] == [2, 3, 4, 5, 5, 1, 1]
+
+
+def _core(ctl, **kw):
+    cfg = ctl.DaemonConfig()
+    cfg.page_dir = ""            # pages on the heap: no files
+    cfg.capacity_gbps = 64.0
+    cfg.window_ns = 5_000_000
+    for k, v in kw.items():
+        setattr(cfg, k, v)
+    return ctl.DaemonCore(cfg)
+
+
+def test_register_budget_unregister(ctl):
+    d = _core(ctl)
+    r = d.handle_line("REGISTER kv_transfer high 40 kv_transfer", 0)
+    assert r.startswith("OK flow_id=1 page=- lease_ms=5000 window_us=5000")
+    assert d.handle_line("REGISTER kv_offload besteffort 0", 0).startswith("OK flow_id=2")
+    assert d.handle_line("REGISTER x bad 1", 0) == "ERR bad_priority\n"
+    assert d.handle_line("REGISTER x high nan", 0) == "ERR bad_target\n"
+    assert d.handle_line("REGISTER x", 0).startswith("ERR usage")
+    flows = d.handle_line("FLOWS", 0)
+    assert flows.startswith("OK n=2 1:kv_transfer:100:40:kv_transfer:HIGH 2:kv_offload:0:0:kv_offload:HIGH")
+    assert d.handle_line("BUDGET 2", 0).startswith("OK flow_id=2 mode=HIGH budget_gbps=-1")
+    assert d.handle_line("BUDGET 9", 0) == "ERR unknown_flow\n"
+    assert d.handle_line("UNREGISTER 2", 0) == "OK\n" and d.n_flows == 1
+    assert d.handle_line("nonsense", 0) == "ERR unknown_cmd\n"
+    assert d.handle_line("POLICY ladder", 0) == "OK policy=ladder\n" and d.policy_name == "ladder"
+    assert d.handle_line("POLICY nope", 0) == "ERR unknown_policy\n"
+    assert d.handle_line("WINDOW 1000", 0) == "OK window_us=1000\n"
+    assert d.handle_line("WINDOW 5", 0) == "ERR bad_window\n"
+
+
+def test_window_step_writes_grants_and_reserves_for_the_protected_flow(ctl):
+    d = _core(ctl)
+    d.handle_line("REGISTER kv_transfer high 40", 0)
+    d.handle_line("REGISTER kv_offload besteffort 0", 0)
+    win = 5_000_000
+    # nothing to protect: both unlimited
+    logs = d.step_window(win)
+    assert [l.budget_bytes for l in logs] == [-1.0, -1.0]
+    assert d.page_fields(2)["unlimited"] == 1 and d.page_fields(2)["epoch"] == 1
+    # the protected flow has backlog, the best-effort flow is eating the link
+    d.report_usage(1, 0, 0, 400_000_000)
+    d.report_usage(2, 320_000_000, 320_000_000, 1 << 40)
+    logs = d.step_window(2 * win)
+    off = [l for l in logs if l.flow == "kv_offload"][0]
+    assert off.decision in ("RESERVE", "DECREASE") and off.budget_bytes == pytest.approx((64 - 40) * 1e9 * 0.005, rel=0.6)
+    f = d.page_fields(2)
+    assert f["unlimited"] == 0 and f["granted_bytes"] > 320_000_000 and f["epoch"] == 2
+    assert d.page_fields(1)["unlimited"] == 1
+    # protected flow drains: release in one window
+    d.report_usage(1, 400_000_000, 400_000_000, 0)
+    logs = d.step_window(3 * win)
+    assert d.page_fields(2)["unlimited"] == 1
+    assert logs[1].csv().count(",") == ctl.DaemonCore.csv_header().count(",")
+
+
+def test_manual_override_pins_a_flow_until_high(ctl):
+    d = _core(ctl)
+    d.handle_line("REGISTER kv_offload besteffort 0", 0)
+    rep = d.handle_line("FLOW 1 LOW2", 0)
+    assert rep.startswith("OK mode=LOW2 sleep_us=125")
+    logs = d.step_window(5_000_000)
+    assert logs[0].decision == "MANUAL" and logs[0].budget_bytes == pytest.approx(64e9 * 0.005 / 2.25, rel=1e-6)
+    assert d.handle_line("FLOW 1 STOP", 0).endswith("stop=1\n") and d.page_fields(1)["stop"] == 1
+    d.handle_line("FLOW 1 HIGH", 0)
+    assert d.step_window(10_000_000)[0].decision != "MANUAL"
+    assert d.handle_line("FLOW 7 HIGH", 0) == "ERR unknown_flow\n"
+
+
+def test_leases_expire_and_renew(ctl):
+    d = _core(ctl, lease_ns=1_000_000_000)
+    d.handle_line("REGISTER a high 10", 0)
+    d.handle_line("REGISTER b low 0", 0)
+    assert d.handle_line("RENEW 1", 900_000_000) == "OK\n"
+    d.step_window(1_100_000_000)            # b's lease (deadline 1.0 s) ran out, a's was renewed to 1.9 s
+    assert d.n_flows == 1 and d.expired == 1
+    assert d.handle_line("RENEW 2", 1_100_000_000) == "ERR unknown_flow\n"
+    d.step_window(2_000_000_000)
+    assert d.n_flows == 0 and d.expired == 2
+
+
+def test_snapshot_restore_round_trip(ctl, tmp_path):
+    d = _core(ctl, page_dir=str(tmp_path), tag="t")
+    d.keep_pages_on_exit(True)
+    d.handle_line("REGISTER kv_transfer high 40", 0)
+    d.handle_line("REGISTER kv_offload besteffort 0", 0)
+    d.handle_line("POLICY ladder", 0)
+    d.report_usage(1, 0, 0, 1 << 30)
+    d.report_usage(2, 10, 10, 1 << 40)
+    d.step_window(5_000_000)
+    snap = d.snapshot_json()
+    assert '"policy":"ladder"' in snap and '"name":"kv_offload"' in snap
+    granted = d.page_fields(2)["granted_bytes"]
+    del d
+    d2 = _core(ctl, page_dir=str(tmp_path), tag="t")
+    assert d2.restore_json(snap, 0) and d2.n_flows == 2 and d2.policy_name == "ladder"
+    assert d2.page_fields(2)["granted_bytes"] == granted       # the page survived the daemon
+    assert d2.handle_line("REGISTER c low 0", 0).startswith("OK flow_id=3")
+    assert not d2.restore_json("{}", 0)
+
+
+def test_token_bucket(ctl):
+    b = ctl.TokenBucket()
+    b.burst_windows = 2.0
+    w = 5_000_000
+    assert b.refill(10.0, w, 0) == 50_000_000
+    assert b.refill(10.0, w, 0) == 100_000_000           # one window of unused credit may be carried
+    assert b.refill(10.0, w, 0) == 100_000_000           # ... but not more than burst_windows
+    assert b.refill(10.0, w, 100_000_000) == 150_000_000  # all spent: one more window
+    assert b.refill(10.0, w, 170_000_000) == 200_000_000  # tickets beyond the grant are waiting, not spent
+    assert b.refill(-1.0, w, 0) == 200_000_000            # unlimited leaves the counter alone
+    g = b.refill(1.0, w, 200_000_000)
+    assert g == 205_000_000 and b.refill(0.0, w, 205_000_000) == 205_000_000
