@@ -26,7 +26,9 @@ def pick_splits(M: int, N: int, K: int, sms: int, gated: bool = False) -> int:
     ntok = C.gemm_pick_ntok(M, gated)
     tiles = ((N + 127) // 128) * ((M + ntok - 1) // ntok)
     kb = K // 64
-    if tiles >= 4 * sms or M > 128:
+    # Measured on B200: with more than half a wave of tiles, the prologue/epilogue each extra CTA pays
+    # (barrier and TMEM set-up, pipeline fill, partial write + reduce) costs more than the idle SMs.
+    if 2 * tiles > sms or M > 128:
         return 1
     best, best_eff = 1, 0.0
     for s in range(1, 17):
