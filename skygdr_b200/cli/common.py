@@ -1,0 +1,52 @@
+"""Shared bits of the command-line programs: size parsing, environment capture."""
+from __future__ import annotations
+
+import json
+import os
+import platform
+import subprocess
+import time
+from typing import Dict
+
+
+def parse_size(text: str) -> int:
+    from skygdr_b200.control import ctl
+
+    v = ctl.parse_size(str(text))
+    if v is None:
+        raise ValueError(f"bad size: {text!r}")
+    return v
+
+
+def env_info() -> Dict:
+    """What every benchmark result embeds: GPU, driver, clocks, git revision (the reference writes an
+    env_info.txt per run, llm_problem_analysis/final_run_vllm_decode_kv_colocation_bench.sh:185-215)."""
+    info = {"time_unix": time.time(), "host": platform.node(), "python": platform.python_version()}
+    try:
+        import torch
+
+        info["torch"] = torch.__version__
+        if torch.cuda.is_available():
+            p = torch.cuda.get_device_properties(0)
+            info.update(gpu=p.name, sms=p.multi_processor_count, hbm_gb=round(p.total_memory / 1e9, 1), n_gpus=torch.cuda.device_count())
+    except Exception as exc:  # pragma: no cover
+        info["torch_error"] = repr(exc)
+    try:
+        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        info["git"] = subprocess.run(["git", "-C", root, "rev-parse", "--short", "HEAD"], capture_output=True, text=True, timeout=5).stdout.strip()
+    except Exception:
+        pass
+    try:
+        out = subprocess.run(["nvidia-smi", "--query-gpu=driver_version,clocks.sm,clocks.max.sm,power.limit", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=10).stdout.strip().splitlines()
+        if out:
+            info["nvidia_smi"] = out[0]
+    except Exception:
+        pass
+    return info
+
+
+def dump_json(path: str, obj) -> None:
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    with open(path, "w") as f:
+        json.dump(obj, f, indent=1)

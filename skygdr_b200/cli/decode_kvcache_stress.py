@@ -1,0 +1,100 @@
+"""decode_vllm_kvcache_hbm_stress / decode_transformer_kvcache_stress on this runtime's kernels.
+
+    python -m skygdr_b200.cli.decode_kvcache_stress --gpu 0 --layers 36 --kv-heads 8 --head-dim 128 --context 8192
+           --gen 128 --batch 16 [--q-heads 32] [--mode attention|model] [--ffn-dim 12288] [--report-every 16]
+
+`--mode attention` (default) is the reference's batched KV-scan workload
+(llm_problem_analysis/decode_vllm_kvcache_hbm_stress.cu:51-76,396-509) done as real paged GQA decode attention on a
+bf16 cache: per generated token, every layer appends K/V and attends over the whole history. `--mode model` adds
+the decoder's GEMMs (the transformer-style stressor of llm_problem_analysis/decode_transformer_kvcache_stress.cu
+models them as a streaming pass, :323-356). Prints the reference's summary block: Time, tokens/s, seq-tokens/s,
+modelled KV traffic and GiB/s.
+"""
+from __future__ import annotations
+
+import argparse
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpu", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--q-heads", type=int, default=0)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--gen", type=int, default=128)
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--tile-tokens", type=int, default=1024)
+    ap.add_argument("--ffn-dim", type=int, default=12288)
+    ap.add_argument("--threads", type=int, default=128)
+    ap.add_argument("--report-every", type=int, default=16)
+    ap.add_argument("--mode", default="attention", choices=["attention", "model"])
+    a = ap.parse_args(argv)
+    import torch
+
+    from skygdr_b200 import ops
+    from skygdr_b200.models import Qwen3Config
+    from skygdr_b200.parallel.tp import build_decode_engine
+
+    torch.cuda.set_device(a.gpu)
+    dev = torch.device("cuda", a.gpu)
+    qh = a.q_heads or 4 * a.kv_heads
+    ctx = torch.full((a.batch,), a.context, dtype=torch.int64)
+    kv_bytes_tok = a.layers * 2 * a.kv_heads * a.head_dim * 2
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if a.mode == "model":
+        cfg = Qwen3Config(layers=a.layers, q_heads=qh, kv_heads=a.kv_heads, ffn=a.ffn_dim)
+        eng, table = build_decode_engine(cfg, dev, 0, 1, ctx, a.gen + 8, attn_chunk=a.tile_tokens)
+        eng.set_batch(torch.zeros(a.batch, dtype=torch.int32, device=dev), ctx.int().to(dev), table.to(dev))
+        eng.capture(a.batch)
+        eng.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for step in range(a.gen):
+            eng.replay()
+        e1.record()
+    else:
+        geom = ops.KVGeometry(a.layers, a.kv_heads, a.head_dim)
+        nb = a.batch * geom.blocks_for(a.context + a.gen + 1) + 1
+        pool = ops.PagedKVPool(geom, nb, "hnd", device=dev)
+        for i in range(0, nb, 256):
+            pool.data[i:i + 256].normal_()
+        mb = geom.blocks_for(a.context + a.gen + 1)
+        table = (torch.randperm(nb - 1)[: a.batch * mb] + 1).int().view(a.batch, mb).to(dev)
+        attn = ops.PagedAttention(dev, a.batch, qh, a.kv_heads, a.context + a.gen + 1, a.tile_tokens)
+        q = torch.randn((a.batch, qh, 128), dtype=torch.bfloat16, device=dev)
+        qkv = torch.randn((a.batch, (qh + 2 * a.kv_heads) * 128), dtype=torch.bfloat16, device=dev)
+        out = torch.empty_like(q)
+        inv = ops.rope_inv_freq(1e6, dev)
+        pos = ctx.int().to(dev)
+        lens = (ctx + 1).int().to(dev)
+
+        def step():
+            for layer in range(a.layers):
+                ops.rope_append(qkv, None, None, pool, layer, inv, table, pos, qh, q_out=q)
+                attn(q, pool, layer, table, lens, out=out)
+            pos.add_(1)
+            lens.add_(1)
+
+        step()
+        torch.cuda.synchronize()
+        e0.record()
+        for s in range(a.gen):
+            step()
+        e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) * 1e-3
+    traffic = sum((a.context + s) for s in range(a.gen)) * a.batch * kv_bytes_tok
+    print("Decode KV-cache stress done:")
+    print(f"  mode:          {a.mode} (bf16 paged cache, {a.layers} layers, {qh}/{a.kv_heads} heads, batch {a.batch}, context {a.context})")
+    print(f"  Time:          {sec:.3f} s")
+    print(f"  tokens/s:      {a.gen / sec:.2f}")
+    print(f"  seq-tokens/s:  {a.gen * a.batch / sec:.2f}")
+    print(f"  KV traffic:    {traffic / 2**30:.2f} GiB")
+    print(f"  KV bandwidth:  {traffic / 2**30 / sec:.2f} GiB/s ({traffic / 1e9 / sec:.2f} GB/s)")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

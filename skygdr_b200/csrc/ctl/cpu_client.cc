@@ -1,0 +1,295 @@
+// cpu_client: load generator and action end-point of one flow.
+//
+//   cpu_client <server_ip|-> <tcp_port> <fabric:tcp|sim[:gbps]> <iters> <msg_bytes> <op:write|read> <port> <gid_idx>
+//              [qd=64] [span] [pattern:random|seq=random] [align=256] [mtu=1024] [sample=1] [max_samples=0]
+//              [ts_ms=0] [ts_out=] [write_ack=1] [read_min_qd=16] [rd_atomic=0] [qps=1]
+//
+// Command line, environment (SKYGDR_CTRL_PORT, SKYGDR_CTRL_{HIGH,LOW,LOW2,LOW3,LOW4}_SLEEP_US,
+// SKYGDR_CTRL_BIND_IP, SKYGDR_READ_MIN_QD, SKYGDR_RD_ATOMIC, SKYGDR_QPS), argument rules, exit codes, the
+// per-window CSV and the three final lines follow the reference's client (src/cpu_client.cc:388-545,
+// 805-823, 883-941, 1251-1296) so that its sweep and analysis tools keep working. The control port is the
+// same one-command-per-connection listener (src/cpu_client.cc:238-315).
+//
+// What differs: the third argument names a fabric instead of an InfiniBand device. `tcp` moves the payload
+// to gpu_server over the session socket; `sim[:gbps]` charges each message its service time on a simulated
+// link (server_ip "-" then needs no server at all). And the flow can register with fabricd
+// (SKYGDR_DAEMON=host:port, SKYGDR_FLOW_NAME/PRIORITY/TARGET_GBPS): it then obeys the byte grants of its
+// credit page in addition to the legacy sleep pacing, and publishes its progress there.
+#include <signal.h>
+#include <sys/select.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <thread>
+#include <vector>
+
+#include "daemon_core.hpp"
+#include "protocol.hpp"
+#include "util.hpp"
+#include "wire.hpp"
+#include "workload.hpp"
+
+using namespace skygdr;
+
+static std::atomic<int> g_shutdown{0};
+
+static void control_server(ControlState* ctl, std::string bind_ip, int port) {
+    int ls = tcp_listen(bind_ip, port, 16);
+    if (ls < 0) { perror("[client] control listen"); return; }
+    while (!g_shutdown.load()) {
+        fd_set rf;
+        FD_ZERO(&rf);
+        FD_SET(ls, &rf);
+        timeval tv{0, 200000};
+        if (select(ls + 1, &rf, nullptr, nullptr, &tv) <= 0) continue;
+        int c = accept(ls, nullptr, nullptr);
+        if (c < 0) continue;
+        timeval rto{1, 0};
+        setsockopt(c, SOL_SOCKET, SO_RCVTIMEO, &rto, sizeof rto);
+        char buf[256];
+        ssize_t n = recv(c, buf, sizeof buf - 1, 0);
+        if (n > 0) {
+            buf[n] = 0;
+            std::string rep = ctl->handle(buf);
+            send_all(c, rep.data(), rep.size());
+        }
+        close(c);
+    }
+    close(ls);
+}
+
+static uint32_t env_u32(const char* name, uint32_t dflt) {
+    const char* v = getenv(name);
+    return v && *v ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
+}
+
+int main(int argc, char** argv) {
+    if (argc < 9) {
+        fprintf(stderr,
+                "usage: %s <server_ip|-> <tcp_port> <fabric:tcp|sim[:gbps]> <iters> <msg_bytes> <op:write|read> <port> <gid_idx> "
+                "[qd=64] [span] [pattern:random|seq] [align=256] [mtu=1024] [sample=1] [max_samples=0] [ts_ms=0] [ts_out=] "
+                "[write_ack=1] [read_min_qd=16] [rd_atomic=0] [qps=1]\n", argv[0]);
+        return 1;
+    }
+    const std::string server_ip = argv[1];
+    const int tcp_port = atoi(argv[2]);
+    const std::string fabric = argv[3];
+    const uint64_t iters = strtoull(argv[4], nullptr, 10);
+    uint64_t msg = 0, span = 0;
+    if (!parse_size(argv[5], &msg)) { fprintf(stderr, "[client] bad msg_bytes\n"); return 2; }
+    const bool is_read = std::string(argv[6]) == "read";
+    auto arg = [&](int i, const char* d) { return argc > i ? argv[i] : d; };
+    int qd = atoi(arg(9, "64"));
+    if (argc > 10 && !parse_size(argv[10], &span)) { fprintf(stderr, "[client] bad span\n"); return 2; }
+    const std::string pattern = arg(11, "random");
+    uint64_t align = strtoull(arg(12, "256"), nullptr, 10);
+    if (align == 0 || (align & (align - 1))) align = 256;
+    const uint64_t sample = std::max<uint64_t>(1, strtoull(arg(14, "1"), nullptr, 10));
+    const uint64_t max_samples = strtoull(arg(15, "0"), nullptr, 10);
+    const int ts_ms = atoi(arg(16, "0"));
+    const std::string ts_out = arg(17, "");
+    int write_ack = atoi(arg(18, "1"));
+    int read_min_qd = (int)env_u32("SKYGDR_READ_MIN_QD", (uint32_t)atoi(arg(19, "16")));
+    int qps = (int)env_u32("SKYGDR_QPS", (uint32_t)atoi(arg(21, "1")));
+    if (qps < 1) qps = 1;
+    if (is_read) write_ack = 0;                          // reads are never acknowledged separately
+    if (write_ack && qps > 1) qps = 1;                   // the ack path is single-connection
+    if (is_read && qd < read_min_qd) qd = read_min_qd;
+
+    const bool sim = fabric.rfind("sim", 0) == 0;
+    double sim_gbps = 64.0;
+    if (sim && fabric.size() > 4) sim_gbps = atof(fabric.c_str() + 4);
+    if (sim_gbps <= 0) sim_gbps = 64.0;
+
+    // ---- control state ----
+    ControlState ctl;
+    const int ctrl_port = (int)env_u32("SKYGDR_CTRL_PORT", 0);
+    {
+        const char* l2 = getenv("SKYGDR_CTRL_LOW2_SLEEP_US");
+        const char* l3 = getenv("SKYGDR_CTRL_LOW3_SLEEP_US");
+        const char* l4 = getenv("SKYGDR_CTRL_LOW4_SLEEP_US");
+        ctl.configure(env_u32("SKYGDR_CTRL_HIGH_SLEEP_US", 0), env_u32("SKYGDR_CTRL_LOW_SLEEP_US", 100),
+                      l2 ? atol(l2) : -1, l3 ? atol(l3) : -1, l4 ? atol(l4) : -1);
+    }
+    std::thread ctl_thread;
+    if (ctrl_port > 0 && ctrl_port < 65536) {
+        ctl.enable();
+        const char* bind_ip = getenv("SKYGDR_CTRL_BIND_IP");
+        ctl_thread = std::thread(control_server, &ctl, std::string(bind_ip && *bind_ip ? bind_ip : "0.0.0.0"), ctrl_port);
+    }
+    auto finish = [&](int code) {
+        g_shutdown.store(1);
+        if (ctl_thread.joinable()) ctl_thread.join();
+        return code;
+    };
+
+    // ---- session set-up ----
+    int s = -1;
+    RemoteInfo ri{0, 0, 1ull << 30};
+    if (server_ip != "-") {
+        s = tcp_connect(server_ip, tcp_port);
+        if (s < 0) { perror("[client] connect"); return finish(1); }
+        ConnInfo mine{}, peer{};
+        mine.qpn = 1;
+        ClientParams cp{(uint8_t)(is_read ? 0 : 1), (uint8_t)write_ack, 0, (uint32_t)qd, (uint32_t)qps};
+        char ready = 0;
+        bool ok = send_all(s, &mine, sizeof mine) && recv_all(s, &peer, sizeof peer) && recv_all(s, &ri, sizeof ri) &&
+                  send_all(s, &cp, sizeof cp);
+        for (int q = 1; ok && q < qps; ++q) ok = send_all(s, &mine, sizeof mine) && recv_all(s, &peer, sizeof peer);
+        ok = ok && recv_all(s, &ready, 1);
+        if (!ok) { fprintf(stderr, "[client] handshake failed\n"); return finish(1); }
+    } else if (!sim) {
+        fprintf(stderr, "[client] server_ip '-' needs the sim fabric\n");
+        return finish(1);
+    }
+    if (msg == 0 || msg > ri.len) { fprintf(stderr, "[client] msg_bytes=%llu does not fit the remote region (%llu)\n",
+                                            (unsigned long long)msg, (unsigned long long)ri.len); return finish(2); }
+    if (span == 0 || span > ri.len) span = ri.len;
+    if (span < msg) span = msg;
+
+    // ---- optional registration with the daemon ----
+    int dsock = -1;
+    SkyCreditPage* page = nullptr;
+    uint32_t flow_id = 0;
+    if (const char* d = getenv("SKYGDR_DAEMON")) {
+        std::string hp = d;
+        size_t colon = hp.rfind(':');
+        if (colon != std::string::npos) dsock = tcp_connect(hp.substr(0, colon), atoi(hp.c_str() + colon + 1));
+        if (dsock >= 0) {
+            const char* nm = getenv("SKYGDR_FLOW_NAME");
+            const char* pr = getenv("SKYGDR_FLOW_PRIORITY");
+            const char* tg = getenv("SKYGDR_FLOW_TARGET_GBPS");
+            std::string line = std::string("REGISTER ") + (nm ? nm : "kv_offload") + " " + (pr ? pr : "besteffort") + " " + (tg ? tg : "0") + "\n";
+            char buf[512] = {0};
+            if (send_all(dsock, line.data(), line.size()) && recv(dsock, buf, sizeof buf - 1, 0) > 0) {
+                std::string rep = buf;
+                size_t p1 = rep.find("flow_id="), p2 = rep.find("page=");
+                if (p1 != std::string::npos) flow_id = (uint32_t)strtoul(rep.c_str() + p1 + 8, nullptr, 10);
+                if (p2 != std::string::npos) {
+                    std::string path = rep.substr(p2 + 5, rep.find(' ', p2) - p2 - 5);
+                    if (path != "-") page = map_credit_page(path, false);
+                }
+                fprintf(stderr, "[client] registered with fabricd: %s", buf);
+            }
+        } else {
+            fprintf(stderr, "[client] SKYGDR_DAEMON=%s not reachable; running unregistered\n", d);
+        }
+    }
+
+    // ---- buffers, samples, time series ----
+    std::vector<unsigned char> buf(sim ? 0 : msg, 0x5a);
+    std::vector<double> lat_us, lat_win;
+    FILE* ts_fp = nullptr;
+    if (ts_ms > 0) {
+        ts_fp = (!ts_out.empty() && ts_out != "-") ? fopen(ts_out.c_str(), "w") : stdout;
+        if (ts_fp) {
+            fprintf(ts_fp, "ts_unix_ms,window_ms,window_us,ops,ops_per_s,throughput_gib_s,p50_us,p90_us,p99_us,p999_us,min_us,max_us,"
+                           "samples,control_mode,pace_sleep_us,control_commands\n");
+            fflush(ts_fp);
+        } else fprintf(stderr, "[client] failed to open ts_out=%s\n", ts_out.c_str());
+    }
+    uint64_t completed = 0, win_completed0 = 0, seen = 0, seq_off = 0, consumed = 0, renew_at = mono_ns();
+    Rng rng(mono_ns() ^ (uint64_t)getpid());
+    uint64_t t_start = mono_ns(), win_start = t_start;
+    auto flush_window = [&](bool force) {
+        if (!ts_fp) return;
+        uint64_t now = mono_ns();
+        uint64_t dt_us = (now - win_start) / 1000;
+        if (!force && dt_us < (uint64_t)ts_ms * 1000) return;
+        uint64_t ops = completed - win_completed0;
+        if (ops == 0 && lat_win.empty()) { win_start = now; return; }
+        std::sort(lat_win.begin(), lat_win.end());
+        double sec = dt_us * 1e-6;
+        fprintf(ts_fp, "%llu,%llu,%llu,%llu,%.6f,%.6f,%.3f,%.3f,%.3f,%.3f,%.3f,%.3f,%zu,%s,%u,%llu\n", (unsigned long long)unix_ms(),
+                (unsigned long long)(dt_us / 1000), (unsigned long long)dt_us, (unsigned long long)ops, sec > 0 ? ops / sec : 0.0,
+                sec > 0 ? double(ops) * double(msg) / kGiB / sec : 0.0, percentile_sorted(lat_win, 0.5), percentile_sorted(lat_win, 0.9),
+                percentile_sorted(lat_win, 0.99), percentile_sorted(lat_win, 0.999), lat_win.empty() ? 0.0 : lat_win.front(),
+                lat_win.empty() ? 0.0 : lat_win.back(), lat_win.size(), mode_name(ctl.mode()), ctl.sleep_us(),
+                (unsigned long long)ctl.commands());
+        fflush(ts_fp);
+        lat_win.clear();
+        win_start = now;
+        win_completed0 = completed;
+    };
+
+    // ---- data loop: one message in flight (the reference's write-with-ack path, src/cpu_client.cc:1088-1249) ----
+    int rc = 0;
+    for (uint64_t i = 0; i < iters && !ctl.stop_requested(); ++i) {
+        uint64_t off;
+        if (pattern == "seq") { off = seq_off; seq_off += msg; if (seq_off + msg > span) seq_off = 0; }
+        else off = span > msg ? (uint64_t)(rng.uniform() * double(span - msg)) : 0;
+        off &= ~(align - 1);
+        if (page) {                                      // byte grant of the flow, if it has one
+            while (!page->unlimited && consumed + msg > __atomic_load_n(&page->granted_bytes, __ATOMIC_ACQUIRE) &&
+                   !page->stop && !ctl.stop_requested())
+                std::this_thread::sleep_for(std::chrono::microseconds(50));
+            if (page->stop) break;
+            consumed += msg;
+            page->consumed_bytes = consumed;
+        }
+        uint64_t t0 = mono_ns();
+        if (sim) {
+            uint64_t service_ns = (uint64_t)(double(msg) / (sim_gbps * 1e9) * 1e9);
+            if (s >= 0) {                                // server in the loop, payload not moved
+                MsgHeader h{off, (uint32_t)msg, (uint32_t)i, is_read ? 1u : 0u, 0};
+                uint32_t tag = 0;
+                if (!send_all(s, &h, sizeof h) || ((write_ack || is_read) && !recv_all(s, &tag, 4))) { rc = 4; break; }
+            }
+            while (mono_ns() - t0 < service_ns) { /* the link is busy with this message */ }
+        } else {
+            MsgHeader h{off, (uint32_t)msg, (uint32_t)i, is_read ? 1u : 0u, 0};
+            if (!send_all(s, &h, sizeof h)) { rc = 3; break; }
+            if (is_read) { if (!recv_all(s, buf.data(), msg)) { rc = 4; break; } }
+            else {
+                if (!send_all(s, buf.data(), msg)) { rc = 3; break; }
+                if (write_ack) {
+                    uint32_t tag = 0;
+                    if (!recv_all(s, &tag, 4)) { rc = 4; break; }
+                    if (tag != (uint32_t)i) { fprintf(stderr, "[client] unexpected ACK tag %u (want %u)\n", tag, (uint32_t)i); rc = 4; break; }
+                }
+            }
+        }
+        uint64_t t1 = mono_ns();
+        ++completed;
+        if (page) { page->completed_bytes = consumed; page->last_ts_ns = t1; }
+        if ((seen++ % sample) == 0) {
+            double us = (t1 - t0) * 1e-3;
+            if (max_samples == 0 || lat_us.size() < max_samples) lat_us.push_back(us);
+            lat_win.push_back(us);
+        }
+        uint32_t pace = ctl.sleep_us();                 // legacy pacing: sleep after each post
+        if (pace) std::this_thread::sleep_for(std::chrono::microseconds(pace));
+        flush_window(false);
+        if (dsock >= 0 && t1 - renew_at > 500000000ull) {
+            char line[64], rep[64];
+            int n = snprintf(line, sizeof line, "RENEW %u\n", flow_id);
+            if (send_all(dsock, line, (size_t)n)) { ssize_t k = recv(dsock, rep, sizeof rep, 0); (void)k; }
+            renew_at = t1;
+        }
+    }
+    double sec = (mono_ns() - t_start) * 1e-9;
+    flush_window(true);
+    if (ts_fp && ts_fp != stdout) fclose(ts_fp);
+    printf("[client] done: iters=%llu msg=%llu qd=%d qps=%d span=%llu pattern=%s\n", (unsigned long long)iters, (unsigned long long)msg, qd,
+           qps, (unsigned long long)span, pattern.c_str());
+    printf("[client] elapsed=%.3f s  ops=%.0f ops/s  throughput=%.2f GiB/s\n", sec, sec > 0 ? completed / sec : 0.0,
+           sec > 0 ? double(msg) * double(completed) / kGiB / sec : 0.0);
+    if (ctl.stop_requested()) printf("[client] control_stop=1 mode=%s pace_sleep_us=%u\n", mode_name(ctl.mode()), ctl.sleep_us());
+    if (!lat_us.empty()) {
+        std::sort(lat_us.begin(), lat_us.end());
+        printf("[client] latency_us samples=%zu p50=%.3f p90=%.3f p99=%.3f p999=%.3f min=%.3f max=%.3f\n", lat_us.size(),
+               percentile_sorted(lat_us, 0.5), percentile_sorted(lat_us, 0.9), percentile_sorted(lat_us, 0.99),
+               percentile_sorted(lat_us, 0.999), lat_us.front(), lat_us.back());
+    } else printf("[client] latency_us samples=0\n");
+    fflush(stdout);
+    if (s >= 0) { MsgHeader h{0, 0, 0, 2, 0}; send_all(s, &h, sizeof h); close(s); }
+    if (dsock >= 0) {
+        char line[64];
+        int n = snprintf(line, sizeof line, "UNREGISTER %u\nQUIT\n", flow_id);
+        send_all(dsock, line, (size_t)n);
+        close(dsock);
+    }
+    return finish(rc);
+}

@@ -1,0 +1,87 @@
+// gpu_server: the target end of a flow. Exposes a memory region, serves clients one after another,
+// and acknowledges a write only after its bytes are in place.
+//
+//   gpu_server <fabric:tcp|sim> <mr_size> <tcp_port> <port> <gid_idx> [mtu=1024]
+//
+// Same command line and session order as the reference's server (src/gpu_server.cu:8,215-530:
+// handshake, region info, client parameters, ready byte, then either idle until "done" or the
+// write-with-ack loop with a 4-byte ACK per tag). The reference registers cudaMalloc'd memory with
+// an RNIC and must flush GPUDirect writes before the ACK (:54-80,426-436); here the first argument
+// names the fabric instead of an InfiniBand device: `tcp` receives the payload on the session socket
+// into the region (the ACK follows the last byte, so it has the same meaning), `sim` moves no payload.
+// GPU-resident pools between processes are exposed by skygdr_b200.parallel.symm (CUDA IPC) instead.
+#include <signal.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#include "util.hpp"
+#include "wire.hpp"
+
+using namespace skygdr;
+
+static volatile sig_atomic_t g_stop = 0;
+static void on_sig(int) { g_stop = 1; }
+
+int main(int argc, char** argv) {
+    if (argc < 6) {
+        fprintf(stderr, "usage: %s <fabric:tcp|sim> <mr_size> <tcp_port> <port> <gid_idx> [mtu=1024]\n", argv[0]);
+        return 1;
+    }
+    std::string fabric = argv[1];
+    uint64_t mr_size = 0;
+    if (!parse_size(argv[2], &mr_size) || mr_size == 0) { fprintf(stderr, "[server] bad mr_size\n"); return 2; }
+    int tcp_port = atoi(argv[3]);
+    bool sim = fabric.rfind("sim", 0) == 0;
+    std::vector<unsigned char> region;
+    if (!sim) region.resize(mr_size);
+    struct sigaction sa{};
+    sa.sa_handler = on_sig;
+    sigaction(SIGINT, &sa, nullptr);
+    sigaction(SIGTERM, &sa, nullptr);
+    signal(SIGPIPE, SIG_IGN);
+    int ls = tcp_listen("0.0.0.0", tcp_port, 1);
+    if (ls < 0) { perror("[server] listen"); return 1; }
+    printf("[server] fabric=%s mr_size=%llu listening on %d\n", fabric.c_str(), (unsigned long long)mr_size, tcp_port);
+    fflush(stdout);
+    uint32_t serial = 1;
+    while (!g_stop) {
+        int c = accept(ls, nullptr, nullptr);
+        if (c < 0) { if (g_stop) break; continue; }
+        int yes = 1;
+        setsockopt(c, IPPROTO_TCP, TCP_NODELAY, &yes, sizeof yes);
+        ConnInfo peer{}, mine{};
+        mine.qpn = serial++;
+        RemoteInfo ri{0x5359u, 0, mr_size};
+        ClientParams cp{};
+        char ready = 1;
+        bool ok = recv_all(c, &peer, sizeof peer) && send_all(c, &mine, sizeof mine) && send_all(c, &ri, sizeof ri) &&
+                  recv_all(c, &cp, sizeof cp);
+        for (uint32_t q = 1; ok && q < cp.qps; ++q) ok = recv_all(c, &peer, sizeof peer) && send_all(c, &mine, sizeof mine);
+        ok = ok && send_all(c, &ready, 1);
+        uint64_t msgs = 0, bytes = 0;
+        std::vector<unsigned char> scratch;
+        while (ok && !g_stop) {
+            MsgHeader h;
+            if (!recv_all(c, &h, sizeof h)) break;
+            if (h.kind == 2) break;                                  // client is done
+            if (h.offset + h.len > mr_size) { fprintf(stderr, "[server] access outside the region\n"); break; }
+            if (h.kind == 0) {                                       // write (+ optional ack)
+                if (!sim) { if (!recv_all(c, region.data() + h.offset, h.len)) break; }
+                ++msgs; bytes += h.len;
+                if (cp.write_ack) { uint32_t tag = h.tag; if (!send_all(c, &tag, 4)) break; }
+            } else if (h.kind == 1) {                                // read: send the bytes back
+                if (!sim) { if (!send_all(c, region.data() + h.offset, h.len)) break; }
+                else { uint32_t tag = h.tag; if (!send_all(c, &tag, 4)) break; }
+                ++msgs; bytes += h.len;
+            }
+        }
+        printf("[server] session closed: msgs=%llu bytes=%llu op=%s write_ack=%u qd=%u qps=%u\n", (unsigned long long)msgs,
+               (unsigned long long)bytes, cp.op ? "write" : "read", cp.write_ack, cp.qd, cp.qps);
+        fflush(stdout);
+        close(c);
+    }
+    close(ls);
+    return 0;
+}

@@ -1,0 +1,215 @@
+"""Flow end-points and tools as processes on CPU: cpu_client / gpu_server, control port, daemon registration,
+message-size sweep, the policy-loop program with stand-in signal sources, analysis joins."""
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+import time
+
+import pytest
+
+from skygdr_b200 import build
+from skygdr_b200.control import FabricClient, FabricDaemon, send_control, wait_for_control
+
+BIN = str(build.build_bin())
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ENV = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+
+
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.fixture()
+def server():
+    port = free_port()
+    p = subprocess.Popen([f"{BIN}/gpu_server", "tcp", "8M", str(port), "1", "0"], stdout=subprocess.PIPE, text=True)
+    assert "listening" in p.stdout.readline()
+    yield port, p
+    p.terminate()
+    p.wait(timeout=3)
+
+
+def client(args, env=None, **kw):
+    return subprocess.run([f"{BIN}/cpu_client", *map(str, args)], capture_output=True, text=True, env=env or ENV, timeout=60, **kw)
+
+
+def test_write_ack_session_and_output_format(server, tmp_path):
+    from skygdr_b200.cli.msgsize_sweep import parse_client_output
+
+    port, proc = server
+    ts = tmp_path / "ts.csv"
+    r = client(["127.0.0.1", port, "tcp", 300, "32K", "write", 1, 0, 64, 0, "random", 256, 1024, 2, 0, 20, ts, 1])
+    assert r.returncode == 0, r.stderr
+    lines = r.stdout.splitlines()
+    assert lines[0] == "[client] done: iters=300 msg=32768 qd=64 qps=1 span=8388608 pattern=random"
+    out = parse_client_output(r.stdout)
+    assert out["samples"] == 150 and out["throughput_gib_s"] > 0 and out["p50_us"] <= out["p99_us"] <= out["max_us"]
+    rows = ts.read_text().splitlines()
+    assert rows[0].startswith("ts_unix_ms,window_ms,window_us,ops,ops_per_s,throughput_gib_s,p50_us") and len(rows) >= 2
+    assert rows[1].split(",")[13] == "DISABLED"            # no control port configured
+    assert "msgs=300 bytes=9830400 op=write write_ack=1" in proc.stdout.readline()
+
+
+def test_read_and_argument_rules(server):
+    port, proc = server
+    r = client(["127.0.0.1", port, "tcp", 50, "64K", "read", 1, 0, 4, "1M", "seq"])
+    assert r.returncode == 0 and "qd=16" in r.stdout and "span=1048576 pattern=seq" in r.stdout      # read raises qd to read_min_qd
+    assert "write_ack=0" in proc.stdout.readline()
+    r = client(["127.0.0.1", port, "tcp", 5, "16M", "write", 1, 0])
+    assert r.returncode == 2 and "does not fit" in r.stderr                                         # message larger than the region
+    r = client(["127.0.0.1", port, "tcp", 5, "junk", "write", 1, 0])
+    assert r.returncode == 2
+    assert client(["127.0.0.1", port]).returncode == 1                                              # usage
+    r = client(["127.0.0.1", port, "tcp", 20, "4K", "write", 1, 0, 64, "1K"])
+    assert "span=4096" in r.stdout                                                                  # span raised to the message size
+
+
+def test_control_port_paces_and_stops_a_flow():
+    cport = free_port()
+    env = dict(ENV, SKYGDR_CTRL_PORT=str(cport), SKYGDR_CTRL_LOW_SLEEP_US="2000", SKYGDR_CTRL_BIND_IP="127.0.0.1")
+    p = subprocess.Popen([f"{BIN}/cpu_client", "-", "0", "sim:1", "1000000", "64K", "write", "1", "0"], stdout=subprocess.PIPE, text=True, env=env)
+    try:
+        rep = wait_for_control("127.0.0.1", cport, 5.0)
+        assert rep.startswith("OK mode=HIGH sleep_us=0 high_sleep_us=0 low1_sleep_us=2000 low2_sleep_us=2500")
+        assert send_control("127.0.0.1", cport, "LOW3").startswith("OK mode=LOW3 sleep_us=3000")
+        time.sleep(0.3)
+        assert "stop=1" in send_control("127.0.0.1", cport, "STOP")
+        out, _ = p.communicate(timeout=10)
+    finally:
+        if p.poll() is None:
+            p.kill()
+    assert p.returncode == 0 and "[client] control_stop=1 mode=LOW3 pace_sleep_us=3000" in out
+    done = int(out.split("samples=")[1].split()[0])
+    assert 20 <= done < 1000000                                     # it ran, paced, and stopped early
+
+
+def test_flow_registers_with_the_daemon_and_obeys_its_grant():
+    with FabricDaemon(window_us=2000, capacity_gbps=1.0, lease_ms=3000) as d:
+        env = dict(ENV, SKYGDR_DAEMON=f"127.0.0.1:{d.port}", SKYGDR_FLOW_NAME="kv_offload", SKYGDR_FLOW_PRIORITY="besteffort")
+        p = subprocess.Popen([f"{BIN}/cpu_client", "-", "0", "sim:1", "4000", "64K", "write", "1", "0"], stdout=subprocess.PIPE,
+                             stderr=subprocess.PIPE, text=True, env=env)
+        with FabricClient(port=d.port) as c:
+            t0 = time.time()
+            while "kv_offload" not in c.request("FLOWS") and time.time() - t0 < 5:
+                time.sleep(0.02)
+            assert "1:kv_offload:0:0:kv_offload" in c.request("FLOWS")
+            c.request("FLOW 1 LOW4")                                # pin the flow to the lowest ladder step: 1/2.75 of 1 GB/s
+            out, err = p.communicate(timeout=60)
+        assert p.returncode == 0 and "registered with fabricd: OK flow_id=1" in err
+        gib_s = float(out.split("throughput=")[1].split()[0])
+        assert 0.15 < gib_s * 1.0737 < 0.75                         # clearly below the 1 GB/s the fabric could give
+        with FabricClient(port=d.port) as c:
+            assert c.request("FLOWS").startswith("OK n=0")          # it unregistered on exit
+
+
+def test_msgsize_sweep_writes_one_row_per_size(tmp_path):
+    out = tmp_path / "sweep.csv"
+    r = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.msgsize_sweep", "--fabric", "sim:8", "--iters", "200", "--warmup_iters", "20",
+                        "--msg_sizes", "4K,64K,1M", "--out", str(out)], capture_output=True, text=True, env=ENV, timeout=120)
+    assert r.returncode == 0, r.stderr
+    import csv
+
+    rows = list(csv.DictReader(open(out)))
+    assert [int(x["msg_bytes"]) for x in rows] == [4096, 65536, 1 << 20]
+    assert all(x["rc"] == "0" and float(x["p50_us"]) > 0 for x in rows)
+    assert float(rows[2]["throughput_gib_s"]) == pytest.approx(8 / 1.0737, rel=0.15)          # large messages reach the link rate
+
+
+def test_policy_loop_program_end_to_end(tmp_path):
+    """Background flow = cpu_client with a control port; protected flow and PCIe signal = stand-in scripts that write
+    the same CSVs the real tools write. The loop must escalate, release when the restore is done, then STOP."""
+    cport = free_port()
+    env = dict(ENV, SKYGDR_CTRL_PORT=str(cport), SKYGDR_CTRL_LOW_SLEEP_US="500", SKYGDR_CTRL_BIND_IP="127.0.0.1")
+    bg_ts = tmp_path / "bg_ts.csv"
+    bg = subprocess.Popen([f"{BIN}/cpu_client", "-", "0", "sim:2", "100000000", "64K", "write", "1", "0", "64", "0", "random", "256", "1024",
+                           "1", "1000", "50", str(bg_ts)], stdout=subprocess.PIPE, text=True, env=env)
+    restore = tmp_path / "fake_restore.py"
+    restore.write_text(textwrap.dedent("""
+        import sys, time
+        out = sys.argv[1]
+        hdr = "ts_unix_ms,elapsed_ms,issued_bytes,completed_bytes,remaining_bytes,window_bytes,inst_bw_gib_s,smooth_bw_gib_s,avg_bw_gib_s,done"
+        total, done, t0 = 1000, 0, time.time()
+        with open(out, "w") as f:
+            f.write(hdr + "\\n"); f.flush()
+            while done < total:
+                time.sleep(0.02); done = min(total, done + 40)
+                bw = 5.0                      # far below the 20 GiB/s baseline: the loop must protect it
+                f.write(f"{int(time.time()*1000)},{int((time.time()-t0)*1000)},{done},{done},{total-done},40,{bw},{bw},{bw},{int(done>=total)}\\n"); f.flush()
+        time.sleep(1.0)
+    """))
+    metrics = tmp_path / "fake_metrics.py"
+    metrics.write_text(textwrap.dedent("""
+        import sys, time
+        with open(sys.argv[1], "w") as f:
+            f.write("ts_unix_ms,t_ms,pcie_tx_GiB_s,pcie_rx_GiB_s,pcie_tx_util_pct,pcie_rx_util_pct,pcie_tx_peak_util_pct,pcie_rx_peak_util_pct\\n")
+            t0 = time.time()
+            while time.time() - t0 < 10:
+                f.write(f"{int(time.time()*1000)},{(time.time()-t0)*1000:.1f},1,25,5,95,5,95\\n"); f.flush(); time.sleep(0.01)
+    """))
+    try:
+        wait_for_control("127.0.0.1", cport, 5.0)
+        r = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.controller", "--cpu_control_host", "127.0.0.1", "--cpu_control_port", str(cport),
+                            "--baseline_restore_gib_s", "20", "--log_dir", str(tmp_path), "--tag", "t", "--poll_ms", "20", "--warmup_ms", "50",
+                            "--post_restore_ms", "100", "--restore_total_bytes", "1000", "--policy", "ladder",
+                            "--restore_cmd", f"{sys.executable} {restore} {{progress}}", "--metrics_cmd", f"{sys.executable} {metrics} {{metrics}}"],
+                           capture_output=True, text=True, env=ENV, timeout=60)
+        assert r.returncode == 0, r.stderr
+        out, _ = bg.communicate(timeout=10)
+    finally:
+        if bg.poll() is None:
+            bg.kill()
+    import csv
+
+    rows = list(csv.DictReader(open(tmp_path / "t_controller.csv")))
+    decisions = [x["decision"] for x in rows if x["decision"] != "HOLD"]
+    assert decisions[:4] == ["SWITCH_LOW1", "ESCALATE_LOW2", "ESCALATE_LOW3", "ESCALATE_LOW4"]
+    assert decisions[-2:] == ["RESTORE_DONE_HIGH", "STOP"]
+    assert list(rows[0].keys())[:4] == ["ts_unix_ms", "mode", "decision", "restore_done"] and len(rows[0]) == 18
+    assert any(x["control_response"].startswith("OK mode=LOW4") for x in rows)
+    assert "control_stop=1" in out                                  # the background flow obeyed STOP
+    # the analysis tool joins the two files (same host: offset near zero) and reports the finish time
+    a = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.case_study_analyze", "--controller_csv", str(tmp_path / "t_controller.csv"),
+                        "--bg_ts_csv", str(bg_ts), "--out_csv", str(tmp_path / "merged.csv")], capture_output=True, text=True, env=ENV, timeout=60)
+    assert a.returncode == 0, a.stderr
+    kv = dict(l.split("=", 1) for l in a.stdout.splitlines() if "=" in l)
+    assert abs(float(kv["clock_offset_ms"])) < 500 and int(kv["low_samples"]) > 3 and float(kv["restore_finish_ms"]) > 0
+    assert "bg_control_mode" in open(tmp_path / "merged.csv").readline()
+
+
+def test_controller_gives_up_when_the_end_point_is_unreachable(tmp_path):
+    r = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.controller", "--cpu_control_host", "127.0.0.1", "--cpu_control_port", str(free_port()),
+                        "--baseline_restore_gib_s", "20", "--log_dir", str(tmp_path), "--control_timeout_s", "1"],
+                       capture_output=True, text=True, env=ENV, timeout=30)
+    assert r.returncode == 2 and "not reachable" in r.stderr
+
+
+def test_csv_tail_reader_and_stale_guard(tmp_path):
+    from skygdr_b200.cli.controller import fresh_row, read_last_csv_row
+
+    p = tmp_path / "x.csv"
+    assert read_last_csv_row(str(p)) is None
+    p.write_text("ts_unix_ms,a\n")
+    assert read_last_csv_row(str(p)) is None
+    p.write_text("ts_unix_ms,a\n100,1\n200,2\n300,")                  # last line half-written
+    assert read_last_csv_row(str(p)) == {"ts_unix_ms": "200", "a": "2"}
+    assert fresh_row({"ts_unix_ms": "200"}, 150) and fresh_row({"ts_unix_ms": "100"}, 150) is None
+    assert fresh_row({"ts_unix_ms": "junk"}, 0) is None and fresh_row(None, 0) is None
+
+
+def test_bandwidth_join_and_clock_offset_units():
+    from skygdr_b200.cli.case_study_analyze import estimate_clock_offset_ms
+    from skygdr_b200.cli.run_pcie_memcpy_with_bandwidth import asof_join, parse_pcie_lines
+
+    text = ("[pcie] t=1.00s dir=h2d bw_gib_s=20.500 bytes=100 streams=8 batch=8 inflight=8 chunk_bytes=1 pinned=1 issued_total=1 completed_total=1 remaining_bytes=0\n"
+            "noise\n[pcie] t=2.00s dir=h2d bw_gib_s=21.000 bytes=200 streams=8\n")
+    rows = parse_pcie_lines(text)
+    assert [r["bw_gib_s"] for r in rows] == [20.5, 21.0]
+    j = asof_join(rows, [{"t_s": 0.5, "memory_util_pct": 10, "estimated_mem_bw_GB_s": 1}, {"t_s": 1.5, "memory_util_pct": 20, "estimated_mem_bw_GB_s": 2}])
+    assert [r["memory_util_pct"] for r in j] == [10, 20]
+    ctrl = [{"ts_unix_ms": "1000", "mode": "HIGH"}, {"ts_unix_ms": "2000", "mode": "LOW1"}, {"ts_unix_ms": "3000", "mode": "LOW2"}]
+    bg = [{"ts_unix_ms": "6000", "control_mode": "HIGH"}, {"ts_unix_ms": "7010", "control_mode": "LOW1"}, {"ts_unix_ms": "8020", "control_mode": "LOW2"}]
+    assert estimate_clock_offset_ms(ctrl, bg) == pytest.approx(5015, abs=6)
