@@ -70,6 +70,7 @@ def main():
     ap.add_argument("--op", default="axpy")
     ap.add_argument("--rows", type=int, default=16)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--impl", default="simt", choices=["simt", "tc"])
     a = ap.parse_args()
     dev = "cuda"
     hbm, tf, src = peaks()
@@ -91,11 +92,12 @@ def main():
             table[b, :nb] = perm[o:o + nb]
             o += nb
         q = torch.randn((a.batch, a.q_heads, 128), dtype=torch.bfloat16, device=dev)
-        attn = ops.PagedAttention(dev, a.batch, a.q_heads, a.kv_heads, max_ctx=a.ctx, chunk_tokens=a.chunk)
+        attn = ops.PagedAttention(dev, a.batch, a.q_heads, a.kv_heads, max_ctx=a.ctx, chunk_tokens=a.chunk, impl=a.impl)
         o_ = torch.empty_like(q)
         ms, best = timed(lambda: attn(q, pool, 0, table, ctx, max_ctx=int(ctx.max()), out=o_), a.warm, a.iters, flush)
         byt = int(ctx.sum()) * a.kv_heads * 128 * 2 * 2
-        out.update(ms=ms, best_ms=best, kv_bytes=byt, gbs=byt / ms / 1e6, frac_hbm=byt / ms / 1e6 / hbm, tokens=int(ctx.sum()))
+        out.update(ms=ms, best_ms=best, kv_bytes=byt, gbs=byt / ms / 1e6, frac_hbm=byt / ms / 1e6 / hbm, tokens=int(ctx.sum()), impl=a.impl,
+                   status=ops.read_status(attn.status)["status_name"])
     elif a.case == "gemm":
         x = torch.randn((a.m, a.k), dtype=torch.bfloat16, device=dev)
         w = torch.randn((a.n * (2 if a.gated else 1), a.k), dtype=torch.bfloat16, device=dev) / 64

@@ -209,7 +209,7 @@ static void memhog(torch::Tensor a, torch::Tensor b, int op, int iters, uint64_t
 static void paged_attn_decode(torch::Tensor q, torch::Tensor kv_layer, torch::Tensor out, torch::Tensor block_table, torch::Tensor ctx_lens,
                               int64_t block_stride, int64_t kv_stride, int64_t head_stride, int kv_heads, int max_ctx, int chunk_tokens,
                               double scale, torch::Tensor part_o, torch::Tensor part_m, torch::Tensor part_l, torch::Tensor counters,
-                              torch::Tensor status) {
+                              torch::Tensor status, int64_t pool_rows) {
     c10::cuda::CUDAGuard g(q.device());
     TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && out.is_contiguous(), "q/out: contiguous [batch][heads][128]");
     PagedAttnParams p;
@@ -226,7 +226,8 @@ static void paged_attn_decode(torch::Tensor q, torch::Tensor kv_layer, torch::Te
     p.part_o = part_o.data_ptr<float>(); p.part_m = part_m.data_ptr<float>(); p.part_l = part_l.data_ptr<float>();
     p.counters = reinterpret_cast<unsigned int*>(counters.data_ptr());
     p.status = status_ptr(status);
-    SKY_CUDA_CHECK(launch_paged_attn_decode(p, cur_stream()));
+    if (pool_rows > 0) SKY_CUDA_CHECK(launch_paged_attn_decode_tc(p, pool_rows, cur_stream()));
+    else SKY_CUDA_CHECK(launch_paged_attn_decode(p, cur_stream()));
 }
 
 // ---- small ops ----

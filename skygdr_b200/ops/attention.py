@@ -14,7 +14,10 @@ from .kv_cache import PagedKVPool
 class PagedAttention:
     """Holds the split-KV scratch (partials, statistics, counters) for a maximum batch and context."""
 
-    def __init__(self, device, max_batch: int, q_heads: int, kv_heads: int, max_ctx: int, chunk_tokens: int = 512):
+    def __init__(self, device, max_batch: int, q_heads: int, kv_heads: int, max_ctx: int, chunk_tokens: int = 512, impl: str = "simt"):
+        """impl: "simt" (CUDA cores, paged_attn.cu) or "tc" (tcgen05 tensor cores, paged_attn_tc.cu; chunk_tokens % 128 == 0)."""
+        assert impl in ("simt", "tc") and (impl == "simt" or chunk_tokens % 128 == 0)
+        self.impl = impl
         self._C = load()
         self.device = torch.device(device)
         self.q_heads, self.kv_heads, self.chunk_tokens, self.max_ctx = q_heads, kv_heads, chunk_tokens, max_ctx
@@ -35,7 +38,8 @@ class PagedAttention:
         self._C.paged_attn_decode(q, pool.layer_base(layer), out, block_table, ctx_lens, bs, ks, pool.head_stride, self.kv_heads,
                                   min(max_ctx or self.max_ctx, self.max_ctx), self.chunk_tokens,
                                   scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]),
-                                  self.part_o, self.part_m, self.part_l, self.counters, self.status)
+                                  self.part_o, self.part_m, self.part_l, self.counters, self.status,
+                                  (pool.data.numel() - layer * ls) // 128 if self.impl == "tc" else 0)
         return out
 
 

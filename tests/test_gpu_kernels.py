@@ -166,8 +166,9 @@ def test_memhog_duty_cycle_and_time_limit(ops):
     assert 0.3 < half["bytes_done"] / full["bytes_done"] < 0.75
 
 
-@pytest.mark.parametrize("kv_heads,q_heads", [(8, 32), (1, 4), (2, 4), (4, 4)])
-def test_paged_attention_matches_reference(ops, kv_heads, q_heads):
+@pytest.mark.parametrize("impl", ["simt", "tc"])
+@pytest.mark.parametrize("kv_heads,q_heads", [(8, 32), (1, 4), (2, 4), (4, 4), (1, 8)])
+def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
     torch.manual_seed(1)
     g = ops.KVGeometry(layers=2, kv_heads=kv_heads)
     ctx = torch.tensor([1, 15, 16, 17, 511, 512, 513, 1300, 2049, 64], dtype=torch.int32, device="cuda")
@@ -184,7 +185,7 @@ def test_paged_attention_matches_reference(ops, kv_heads, q_heads):
         table[b, :nb] = perm[o:o + nb]
         o += nb
     q = torch.randn((B, q_heads, 128), dtype=torch.bfloat16, device="cuda")
-    attn = ops.PagedAttention("cuda", B, q_heads, kv_heads, max_ctx=4096, chunk_tokens=512)
+    attn = ops.PagedAttention("cuda", B, q_heads, kv_heads, max_ctx=4096, chunk_tokens=512, impl=impl)
     for layer in (0, 1):
         out = attn(q, pool, layer, table, ctx, max_ctx=int(ctx.max()))
         ref = ops.paged_attn_reference(q, pool, layer, table, ctx)
