@@ -37,7 +37,8 @@ constexpr int HALF_BYTES = TILE_TOK * 64 * 2;       // one [128 tok][64 dim] swi
 constexpr int KV_TILE_BYTES = 2 * HALF_BYTES;       // K or V tile: 32 KB
 constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES;      // K + V: 64 KB
 constexpr int QP_BYTES = 2 * 16 * 128;              // [16 rows][128 cols] bf16 as two swizzled [16][64] sub-tiles: 4 KB
-constexpr int TC_SMEM = TC_STAGES * STAGE_BYTES + 2 * QP_BYTES + 1024;
+constexpr int TC_SMEM = TC_STAGES * STAGE_BYTES + 3 * QP_BYTES + 1024;     // ring + Q^T + two P^T buffers
+constexpr int MAX_CHUNK_PAGES = 512;                                      // chunk_tokens <= 8192
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
 // Byte offset of element (row, col) in a [rows][64] bf16 tile stored with the 128-byte swizzle.
@@ -79,11 +80,12 @@ template <int G>
 __global__ void __launch_bounds__(TC_THREADS, 1) paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PagedAttnParams p) {
     constexpr int GL = G <= 4 ? 4 : 8;               // columns read per TMEM access
     extern __shared__ unsigned char smem_raw[];
-    __shared__ uint64_t full_bar[TC_STAGES], empty_bar[TC_STAGES], s_ready[2], p_ready, o_done;
+    __shared__ uint64_t full_bar[TC_STAGES], empty_bar[TC_STAGES], s_ready[2], p_ready[2], o_done[2];
     __shared__ uint32_t tmem_slot;
     __shared__ float xch[2][4][8];                    // tile max exchange: [parity][warp][head]
     __shared__ float lsum[4][8];
     __shared__ int s_last;
+    __shared__ int s_blocks[MAX_CHUNK_PAGES];            // this CTA's slice of the block table
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* q_sm = smem + TC_STAGES * STAGE_BYTES;
     unsigned char* p_sm = q_sm + QP_BYTES;
@@ -101,13 +103,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) paged_attn_tc_kernel(const __gr
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&s_ready[0], 1); mbar_init(&s_ready[1], 1);
-        mbar_init(&p_ready, 128);
-        mbar_init(&o_done, 1);
+        mbar_init(&p_ready[0], 128); mbar_init(&p_ready[1], 128);
+        mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
         fence_barrier_init();
     }
     if (warp == 5) { tmem_alloc(&tmem_slot, 64); tmem_relinquish(); }
     // Q^T and P^T operand tiles: zero everything (rows G..15 stay zero), then Q rows 0..G-1 in swizzled order
-    for (int i = threadIdx.x; i < 2 * QP_BYTES / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_sm)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < 3 * QP_BYTES / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_sm)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < n_tiles * 8; i += TC_THREADS) {       // coalesced; entries past the table read block 0
+        const int e = (tok0 >> 4) + i;
+        s_blocks[i] = e < p.max_blocks ? __ldg(table + e) : 0;
+    }
     __syncthreads();
     for (int i = threadIdx.x; i < G * 16; i += TC_THREADS) {        // 16-byte chunks: G rows x 16 chunks
         const int g = i >> 4, c = i & 15;
@@ -128,28 +134,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) paged_attn_tc_kernel(const __gr
     bool ok = true;
 
     if (warp == 4) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            tma_prefetch_desc(&tmap);
-            const long long head_rows = (long long)kvh * (p.head_stride >> 7);
-            for (int i = 0; i < n_tiles; ++i) {
-                const int s = i % TC_STAGES;
-                if (i >= TC_STAGES && !mbar_wait(&empty_bar[s], ((i / TC_STAGES) - 1) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 11); break; }
-                unsigned char* st = smem + s * STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                const int pg0 = (tok0 + i * TILE_TOK) >> 4;
-#pragma unroll 1
-                for (int pg = 0; pg < 8; ++pg) {
-                    const int e = pg0 + pg;
-                    const int blk = e < p.max_blocks ? __ldg(table + e) : 0;
-                    const long long krow = ((long long)blk * p.block_stride >> 7) + head_rows;
-                    const long long vrow = krow + (p.kv_stride >> 7);
-                    tma_load_2d(st + pg * 2048, &tmap, 0, (int)krow, &full_bar[s]);
-                    tma_load_2d(st + HALF_BYTES + pg * 2048, &tmap, 64, (int)krow, &full_bar[s]);
-                    tma_load_2d(st + KV_TILE_BYTES + pg * 2048, &tmap, 0, (int)vrow, &full_bar[s]);
-                    tma_load_2d(st + KV_TILE_BYTES + HALF_BYTES + pg * 2048, &tmap, 64, (int)vrow, &full_bar[s]);
-                }
+        // ---------------- TMA producer: lane l issues box l of the tile (page l/4; K lo, K hi, V lo, V hi) ----------------
+        if (lane == 0) tma_prefetch_desc(&tmap);
+        const long long head_rows = (long long)kvh * (p.head_stride >> 7);
+        const int pg = lane >> 2, part = lane & 3;
+        for (int i = 0; i < n_tiles; ++i) {
+            const int s = i % TC_STAGES;
+            if (i >= TC_STAGES && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ((i / TC_STAGES) - 1) & 1))) {
+                if (lane == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 11);
+                break;
             }
+            unsigned char* st = smem + s * STAGE_BYTES;
+            if (lane == 0) mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            __syncwarp();
+            const int blk = s_blocks[i * 8 + pg];
+            const long long row = ((long long)blk * p.block_stride >> 7) + head_rows + ((part >> 1) ? (p.kv_stride >> 7) : 0);
+            tma_load_2d(st + (part >> 1) * KV_TILE_BYTES + (part & 1) * HALF_BYTES + pg * 2048, &tmap, (part & 1) * 64, (int)row, &full_bar[s]);
         }
     } else if (warp == 5) {
         // ---------------- MMA issuer ----------------
@@ -175,18 +175,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) paged_attn_tc_kernel(const __gr
             for (int i = 0; i < n_tiles && good; ++i) {
                 if (i + 1 < n_tiles) good = issue_s(i + 1);
                 if (!good) break;
-                if (!mbar_wait(&p_ready, i & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 13); break; }
+                if (!mbar_wait(&p_ready[i & 1], (i >> 1) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 13); break; }
                 tc_fence_after();
                 const int s = i % TC_STAGES;
                 const uint32_t v_addr = smem_u32(smem + s * STAGE_BYTES + KV_TILE_BYTES);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const uint64_t a = umma_desc_mn_sw128(v_addr + j * 2048, HALF_BYTES, 1024);
-                    const uint64_t bp = umma_desc_k_sw128(p_addr + (j >> 2) * 2048 + (j & 3) * 32);
+                    const uint64_t bp = umma_desc_k_sw128(p_addr + (i & 1) * QP_BYTES + (j >> 2) * 2048 + (j & 3) * 32);
                     tc_mma_f16(tm_o, a, bp, idesc_o, (i | j) ? 1u : 0u);
                 }
                 tc_commit(&empty_bar[s]);     // K and V of this stage are free again
-                tc_commit(&o_done);           // accumulator and P buffer are free again
+                tc_commit(&o_done[i & 1]);    // this tile's P buffer is free again; the accumulator may be touched
             }
         }
     } else {
@@ -233,8 +233,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) paged_attn_tc_kernel(const __gr
                 pr[g] = (g < G && valid) ? exp2f(sc[g] - m_ref[g]) : 0.f;
                 if (g < G) l_part[g] = l_part[g] * alpha[g] + pr[g];
             }
-            // the previous tile's P.V must be complete before P is overwritten or O rescaled
-            if (i > 0 && !mbar_wait(&o_done, (i - 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 15); ok = false; break; }
+            // P^T is double-buffered: buffer i&1 was last read by tile i-2's P.V. A rescale of the accumulator has to
+            // wait for tile i-1's P.V too (which, issued in order, also covers tile i-2). o_done[k] completes once per
+            // tile of parity k, so tile j is completion number j>>1 of o_done[j&1].
+            if (rescale && i > 0) {
+                if (!mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 15); ok = false; break; }
+            } else if (i > 1) {
+                if (!mbar_wait(&o_done[i & 1], ((i - 2) >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 15); ok = false; break; }
+            }
             if (rescale && i > 0) {
                 tc_fence_after();
                 uint32_t o[GL];
@@ -247,13 +253,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) paged_attn_tc_kernel(const __gr
             }
 #pragma unroll
             for (int g = 0; g < G; ++g)
-                *reinterpret_cast<__nv_bfloat16*>(p_sm + (t >> 6) * 2048 + sw128_off(g, t & 63)) = __float2bfloat16(pr[g]);
+                *reinterpret_cast<__nv_bfloat16*>(p_sm + (i & 1) * QP_BYTES + (t >> 6) * 2048 + sw128_off(g, t & 63)) = __float2bfloat16(pr[g]);
             fence_proxy_async();
             tc_fence_before();
-            mbar_arrive(&p_ready);
+            mbar_arrive(&p_ready[i & 1]);     // one barrier per P buffer: the softmax may run a tile ahead of the MMA thread
         }
         // the last P.V
-        if (ok && !mbar_wait(&o_done, (n_tiles - 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 16); ok = false; }
+        if (ok && !mbar_wait(&o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 16); ok = false; }
         tc_fence_after();
     }
 
