@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--ctx-hi", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=36, help="for smoke runs only; the benchmark uses 36")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--attn-impl", default="tc", choices=["tc", "simt"])
+    ap.add_argument("--attn-chunk", type=int, default=1024)
     return ap.parse_args()
 
 
@@ -83,9 +85,11 @@ def main() -> int:
     ctx = torch.randint(args.ctx_lo, args.ctx_hi + 1, (batch,), generator=g)
     total_steps = 2 * (args.steps + args.warmup) + 8
     max_ctx = int(ctx.max()) + total_steps + 1
-    eng, table = build_decode_engine(cfg, dev, rank, world, ctx, total_steps, seed=args.seed, kv_init="normal")
+    eng, table = build_decode_engine(cfg, dev, rank, world, ctx, total_steps, seed=args.seed, kv_init="normal",
+                                     attn_chunk=args.attn_chunk, attn_impl=args.attn_impl)
 
     ids0 = torch.randint(0, cfg.vocab, (batch,), generator=g).int()
+    eng.set_batch(ids0.to(dev), ctx.int().to(dev), table.to(dev))
     sess = DecodeSession(eng, batch, max_ctx)          # captures the step into a CUDA graph
     sess.start(ids0, ctx.int(), table)
 
@@ -134,7 +138,7 @@ def main() -> int:
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random-init weights, N(0,1) KV, uniform context lengths)",
             "config": {"model": cfg.name if args.layers == 36 else f"{cfg.name}-{args.layers}L", "global_batch": batch,
                        "seq_len": f"context uniform {args.ctx_lo}-{args.ctx_hi}, 1 new token per step",
-                       "parallelism": f"tp{world}", "kv_block_tokens": 16, "sampling": "greedy",
+                       "parallelism": f"tp{world}", "kv_block_tokens": 16, "sampling": "greedy", "attention": f"{args.attn_impl}, {args.attn_chunk}-token splits",
                        "l2": "inputs larger than L2: each step streams %.1f GB of weights and KV per GPU" % (step_bytes / 1e9)},
             "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": sess.h2d_bytes_per_step, "d2h_bytes_per_step": sess.d2h_bytes_per_step},

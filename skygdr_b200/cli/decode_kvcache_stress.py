@@ -62,7 +62,7 @@ def main(argv=None) -> int:
             pool.data[i:i + 256].normal_()
         mb = geom.blocks_for(a.context + a.gen + 1)
         table = (torch.randperm(nb - 1)[: a.batch * mb] + 1).int().view(a.batch, mb).to(dev)
-        attn = ops.PagedAttention(dev, a.batch, qh, a.kv_heads, a.context + a.gen + 1, a.tile_tokens)
+        attn = ops.PagedAttention(dev, a.batch, qh, a.kv_heads, a.context + a.gen + 1, a.tile_tokens, impl="tc")
         q = torch.randn((a.batch, qh, 128), dtype=torch.bfloat16, device=dev)
         qkv = torch.randn((a.batch, (qh + 2 * a.kv_heads) * 128), dtype=torch.bfloat16, device=dev)
         out = torch.empty_like(q)

@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "common_host.h"
 #include "credit_page.h"
 
@@ -75,6 +77,15 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned 
 __device__ __forceinline__ void set_status(LaunchStatus* st, unsigned code, unsigned detail) {
     if (atomicCAS(&st->status, 0u, code) == 0u) st->detail = detail;
 }
+
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch. A kernel launched with launch_pdl() may begin while the kernel before
+// it in the stream is still draining; pdl_wait() blocks until that kernel has completed and its writes
+// are visible, so it must come before the first read of anything an earlier kernel produced and before
+// the first global write. pdl_trigger() lets the NEXT kernel's CTAs start as soon as every CTA of this
+// kernel has called it (or exited); it does not publish any data.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------
 // Credit gate. One thread per CTA calls this per chunk.
@@ -210,6 +221,21 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
 // Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, tile M x N.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+
+// Host: launch with the programmatic-stream-serialization attribute (set SKYGDR_PDL=0 to launch plainly).
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 
 }  // namespace sky

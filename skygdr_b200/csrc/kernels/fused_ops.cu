@@ -41,6 +41,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
                                                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                                        int hidden, float eps) {
     __shared__ float red[8];
+    pdl_trigger();
+    pdl_wait();
     const long long row = blockIdx.x;
     const int nvec = hidden / 8;
     float vals[4][8];
@@ -81,13 +83,14 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
 cudaError_t launch_rmsnorm(const __nv_bfloat16* x, __nv_bfloat16* residual, const __nv_bfloat16* w, __nv_bfloat16* y,
                            int rows, int hidden, float eps, cudaStream_t stream) {
     if (hidden % 8 || hidden > 8192 || rows <= 0) return cudaErrorInvalidValue;
-    rmsnorm_kernel<<<rows, 256, 0, stream>>>(x, residual, w, y, hidden, eps);
-    return cudaGetLastError();
+    return launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, stream, x, residual, w, y, hidden, eps);
 }
 
 // One warp per (token, head) over q heads, k heads and v heads; lane owns dims [4*lane, 4*lane+4).
 // Rotation pairs dim i with dim i+64, i.e. lane L with lane L^16.
 __global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendParams p) {
+    pdl_trigger();
+    pdl_wait();
     const int heads_total = p.q_heads + 2 * p.kv_heads;
     const long long gw = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (gw >= (long long)p.tokens * heads_total) return;
@@ -145,8 +148,7 @@ __global__ void __launch_bounds__(128) rope_append_kernel(const RopeAppendParams
 cudaError_t launch_rope_append(const RopeAppendParams& p, cudaStream_t stream) {
     if (p.tokens <= 0) return cudaErrorInvalidValue;
     const long long warps = (long long)p.tokens * (p.q_heads + 2 * p.kv_heads);
-    rope_append_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(rope_append_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, p);
 }
 
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
@@ -172,6 +174,8 @@ cudaError_t launch_silu_mul(const __nv_bfloat16* gate_up, __nv_bfloat16* out, in
 
 __global__ void __launch_bounds__(128) embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                                          __nv_bfloat16* __restrict__ out, int hidden, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     const int tok = blockIdx.x;
     int id = ids[tok];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -183,14 +187,15 @@ __global__ void __launch_bounds__(128) embedding_kernel(const int* __restrict__ 
 cudaError_t launch_embedding(const int* ids, const __nv_bfloat16* table, __nv_bfloat16* out, int tokens, int hidden, int vocab,
                              cudaStream_t stream) {
     if (hidden % 8 || tokens <= 0) return cudaErrorInvalidValue;
-    embedding_kernel<<<tokens, 128, 0, stream>>>(ids, table, out, hidden, vocab);
-    return cudaGetLastError();
+    return launch_pdl(embedding_kernel, dim3(tokens), dim3(128), 0, stream, ids, table, out, hidden, vocab);
 }
 
 __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, int vocab,
                                                        long long row_stride) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_trigger();
+    pdl_wait();
     const __nv_bfloat16* row = logits + (long long)blockIdx.x * row_stride;
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -218,8 +223,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __res
 
 cudaError_t launch_argmax(const __nv_bfloat16* logits, int* out, int rows, int vocab, long long row_stride, cudaStream_t stream) {
     if (rows <= 0 || vocab <= 0) return cudaErrorInvalidValue;
-    argmax_kernel<<<rows, 1024, 0, stream>>>(logits, out, vocab, row_stride);
-    return cudaGetLastError();
+    return launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, stream, logits, out, vocab, row_stride);
 }
 
 }  // namespace sky

@@ -15,10 +15,18 @@
 // (llm_problem_analysis/decode_transformer_kvcache_stress.cu:323-356).
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm_tcgen05.h"
 
 namespace sky {
+
+bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("SKYGDR_PDL"); on = (e && e[0] == '0') ? 0 : 1; }
+    return on == 1;
+}
 
 // Where output element (token t, column n) goes: the local y, or a peer's reduce-scatter slot.
 __device__ __forceinline__ void gemm_store(const GemmParams& p, int t, int n, float v) {
@@ -55,6 +63,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     __shared__ int s_last;
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
+    pdl_trigger();     // the next kernel may start its own prologue while this one streams
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
     const int n0 = tile_n * BM, t0 = tile_m * NTOK;
@@ -88,6 +97,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 tma_load_2d(st, &tmap_w, kx, n0, &full_bar[i]);
                 if (GATED) tma_load_2d(st + S::W_BYTES, &tmap_w, kx, p.N + n0, &full_bar[i]);
             }
+            // Weights are constants, so the loads above ran ahead of the previous kernel; x is that kernel's output.
+            pdl_wait();
             if (p.ag.n_src > 0 && *(volatile unsigned int*)&p.status->status == SKY_STATUS_OK) {
                 const unsigned seq = *p.ag.seq.step * p.ag.seq.uses_per_step + p.ag.seq.use_index + 1;
                 const unsigned want = seq * p.ag.seq.arrivals_per_use;
@@ -143,6 +154,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const int r = slice * 32 + lane;           // weight row inside the tile
         const int n = n0 + r;
         bool ok = true;
+        pdl_wait();     // nothing is written before the previous kernel has finished reading its inputs
         if (nkb > 0) ok = mbar_wait(&acc_bar, 0);
         if (!ok && lane == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 3);
         tc_fence_after();
@@ -283,8 +295,7 @@ static cudaError_t launch_t(const GemmParams& p, const CUtensorMap& tw, const CU
         attr_done = true;
     }
     dim3 grid((p.N + BM - 1) / BM, (p.M + NTOK - 1) / NTOK, p.splits);
-    kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tw, tx, p);
-    return cudaGetLastError();
+    return launch_pdl(kern, grid, dim3(GEMM_THREADS), (size_t)S::TOTAL, stream, tw, tx, p);
 }
 
 int gemm_pick_ntok(int M, bool gated) {

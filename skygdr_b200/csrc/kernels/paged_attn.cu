@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
     __shared__ uint64_t bars[ATT_WARPS * STAGES];
     __shared__ int s_last;
 
+    pdl_trigger();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ts = lane >> 3, dl = lane & 7;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -291,8 +293,7 @@ static cudaError_t launch_g(const PagedAttnParams& p, cudaStream_t stream) {
         attr_done = true;
     }
     dim3 grid((p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens, p.kv_heads, p.batch);
-    kern<<<grid, ATT_WARPS * 32, smem_bytes, stream>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(kern, grid, dim3(ATT_WARPS * 32), (size_t)smem_bytes, stream, p);
 }
 
 cudaError_t launch_paged_attn_decode(const PagedAttnParams& p, cudaStream_t stream) {

@@ -4,7 +4,8 @@
 // bf16 head-major pages of 16 tokens, split-KV with an in-kernel last-CTA combine), different engine:
 //
 //   warp 4   : TMA producer. Per 128-token tile, 16 + 16 tensor-map boxes ([16 tokens] x [64 dims], 128-byte
-//              swizzle; one box per page and half of head_dim) land K and V in a 3-stage ring. No cluster broadcast.
+//              swizzle; one box per page and half of head_dim) land K and V in a ring of three 32 KB units
+//              (K0, V0, K1, ...), small enough for two CTAs per SM. No cluster broadcast.
 //   warp 5   : MMA issuer and TMEM owner.
 //                S^T[128 tok x 16] = K_tile[128 x 128] . Q^T           (A, B K-major; tokens are the MMA's M)
 //                O^T[128 dim x 16] += V_tile^T[128 x 128] . P^T        (A = V as stored, MN-major; B = P^T K-major)
@@ -32,12 +33,11 @@ namespace {
 
 constexpr int TC_THREADS = 192;
 constexpr int TILE_TOK = 128;
-constexpr int TC_STAGES = 3;
+constexpr int TC_UNITS = 3;                         // ring of 32 KB units: K0, V0, K1, V1, ... (unit u holds tile u/2's K or V)
 constexpr int HALF_BYTES = TILE_TOK * 64 * 2;       // one [128 tok][64 dim] swizzled sub-tile: 16 KB
 constexpr int KV_TILE_BYTES = 2 * HALF_BYTES;       // K or V tile: 32 KB
-constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES;      // K + V: 64 KB
 constexpr int QP_BYTES = 2 * 16 * 128;              // [16 rows][128 cols] bf16 as two swizzled [16][64] sub-tiles: 4 KB
-constexpr int TC_SMEM = TC_STAGES * STAGE_BYTES + 3 * QP_BYTES + 1024;     // ring + Q^T + two P^T buffers
+constexpr int TC_SMEM = TC_UNITS * KV_TILE_BYTES + 3 * QP_BYTES + 1024;    // ring + Q^T + two P^T buffers: two CTAs fit one SM
 constexpr int MAX_CHUNK_PAGES = 512;                                      // chunk_tokens <= 8192
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
@@ -77,21 +77,32 @@ __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sy
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <int G>
-__global__ void __launch_bounds__(TC_THREADS, 1) paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PagedAttnParams p) {
+__global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const PagedAttnParams p) {
     constexpr int GL = G <= 4 ? 4 : 8;               // columns read per TMEM access
     extern __shared__ unsigned char smem_raw[];
-    __shared__ uint64_t full_bar[TC_STAGES], empty_bar[TC_STAGES], s_ready[2], p_ready[2], o_done[2];
+    __shared__ uint64_t full_bar[TC_UNITS], empty_bar[TC_UNITS], s_ready[2], p_ready[2], o_done[2];
     __shared__ uint32_t tmem_slot;
     __shared__ float xch[2][4][8];                    // tile max exchange: [parity][warp][head]
     __shared__ float lsum[4][8];
     __shared__ int s_last;
     __shared__ int s_blocks[MAX_CHUNK_PAGES];            // this CTA's slice of the block table
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* q_sm = smem + TC_STAGES * STAGE_BYTES;
+    unsigned char* q_sm = smem + TC_UNITS * KV_TILE_BYTES;
     unsigned char* p_sm = q_sm + QP_BYTES;
 
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    // Everything up to pdl_wait() touches only this CTA's shared memory, so it may overlap the previous kernel's tail.
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_UNITS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&s_ready[0], 1); mbar_init(&s_ready[1], 1);
+        mbar_init(&p_ready[0], 128); mbar_init(&p_ready[1], 128);
+        mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
+        fence_barrier_init();
+    }
+    for (int i = threadIdx.x; i < 3 * QP_BYTES / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_sm)[i] = make_uint4(0, 0, 0, 0);
+    pdl_wait();
     const int ctx = p.ctx_lens[b];
     const int tok0 = split * p.chunk_tokens;
     if (tok0 >= ctx) return;
@@ -100,16 +111,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) paged_attn_tc_kernel(const __gr
     const int n_splits = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
     const int* table = p.block_table + (long long)b * p.max_blocks;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(&s_ready[0], 1); mbar_init(&s_ready[1], 1);
-        mbar_init(&p_ready[0], 128); mbar_init(&p_ready[1], 128);
-        mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
-        fence_barrier_init();
-    }
     if (warp == 5) { tmem_alloc(&tmem_slot, 64); tmem_relinquish(); }
     // Q^T and P^T operand tiles: zero everything (rows G..15 stay zero), then Q rows 0..G-1 in swizzled order
-    for (int i = threadIdx.x; i < 3 * QP_BYTES / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_sm)[i] = make_uint4(0, 0, 0, 0);
     for (int i = threadIdx.x; i < n_tiles * 8; i += TC_THREADS) {       // coalesced; entries past the table read block 0
         const int e = (tok0 >> 4) + i;
         s_blocks[i] = e < p.max_blocks ? __ldg(table + e) : 0;
@@ -134,22 +137,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) paged_attn_tc_kernel(const __gr
     bool ok = true;
 
     if (warp == 4) {
-        // ---------------- TMA producer: lane l issues box l of the tile (page l/4; K lo, K hi, V lo, V hi) ----------------
+        // ---------------- TMA producer ----------------
         if (lane == 0) tma_prefetch_desc(&tmap);
         const long long head_rows = (long long)kvh * (p.head_stride >> 7);
-        const int pg = lane >> 2, part = lane & 3;
-        for (int i = 0; i < n_tiles; ++i) {
-            const int s = i % TC_STAGES;
-            if (i >= TC_STAGES && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ((i / TC_STAGES) - 1) & 1))) {
+        // unit u = 2*tile + (0: K, 1: V); lanes 0-15 issue its 16 boxes (page l/2, dim half l&1)
+        const int pg = lane >> 1, half = lane & 1;
+        for (int u = 0; u < 2 * n_tiles; ++u) {
+            const int s = u % TC_UNITS;
+            if (u >= TC_UNITS && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ((u / TC_UNITS) - 1) & 1))) {
                 if (lane == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 11);
                 break;
             }
-            unsigned char* st = smem + s * STAGE_BYTES;
-            if (lane == 0) mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            unsigned char* st = smem + s * KV_TILE_BYTES;
+            if (lane == 0) mbar_expect_tx(&full_bar[s], KV_TILE_BYTES);
             __syncwarp();
-            const int blk = s_blocks[i * 8 + pg];
-            const long long row = ((long long)blk * p.block_stride >> 7) + head_rows + ((part >> 1) ? (p.kv_stride >> 7) : 0);
-            tma_load_2d(st + (part >> 1) * KV_TILE_BYTES + (part & 1) * HALF_BYTES + pg * 2048, &tmap, (part & 1) * 64, (int)row, &full_bar[s]);
+            if (lane < 16) {
+                const int blk = s_blocks[(u >> 1) * 8 + pg];
+                const long long row = ((long long)blk * p.block_stride >> 7) + head_rows + ((u & 1) ? (p.kv_stride >> 7) : 0);
+                tma_load_2d(st + half * HALF_BYTES + pg * 2048, &tmap, half * 64, (int)row, &full_bar[s]);
+            }
         }
     } else if (warp == 5) {
         // ---------------- MMA issuer ----------------
@@ -158,16 +164,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) paged_attn_tc_kernel(const __gr
             constexpr uint32_t idesc_o = umma_idesc_bf16(128, 16) | (1u << 15);         // A is MN-major
             const uint32_t q_addr = smem_u32(q_sm), p_addr = smem_u32(p_sm);
             auto issue_s = [&](int i) -> bool {
-                const int s = i % TC_STAGES;
-                if (!mbar_wait(&full_bar[s], (i / TC_STAGES) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 12); return false; }
+                const int u = 2 * i, s = u % TC_UNITS;
+                if (!mbar_wait(&full_bar[s], (u / TC_UNITS) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 12); return false; }
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(smem + s * STAGE_BYTES);
+                const uint32_t k_addr = smem_u32(smem + s * KV_TILE_BYTES);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const uint64_t a = umma_desc_k_sw128(k_addr + (j >> 2) * HALF_BYTES + (j & 3) * 32);
                     const uint64_t bq = umma_desc_k_sw128(q_addr + (j >> 2) * 2048 + (j & 3) * 32);
                     tc_mma_f16(tm_s[i & 1], a, bq, idesc_s, j ? 1u : 0u);
                 }
+                tc_commit(&empty_bar[s]);     // K of this tile is free once the scores are done
                 tc_commit(&s_ready[i & 1]);
                 return true;
             };
@@ -176,16 +183,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) paged_attn_tc_kernel(const __gr
                 if (i + 1 < n_tiles) good = issue_s(i + 1);
                 if (!good) break;
                 if (!mbar_wait(&p_ready[i & 1], (i >> 1) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 13); break; }
+                const int u = 2 * i + 1, s = u % TC_UNITS;
+                if (!mbar_wait(&full_bar[s], (u / TC_UNITS) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 17); break; }
                 tc_fence_after();
-                const int s = i % TC_STAGES;
-                const uint32_t v_addr = smem_u32(smem + s * STAGE_BYTES + KV_TILE_BYTES);
+                const uint32_t v_addr = smem_u32(smem + s * KV_TILE_BYTES);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const uint64_t a = umma_desc_mn_sw128(v_addr + j * 2048, HALF_BYTES, 1024);
                     const uint64_t bp = umma_desc_k_sw128(p_addr + (i & 1) * QP_BYTES + (j >> 2) * 2048 + (j & 3) * 32);
                     tc_mma_f16(tm_o, a, bp, idesc_o, (i | j) ? 1u : 0u);
                 }
-                tc_commit(&empty_bar[s]);     // K and V of this stage are free again
+                tc_commit(&empty_bar[s]);     // V of this tile is free again
                 tc_commit(&o_done[i & 1]);    // this tile's P buffer is free again; the accumulator may be touched
             }
         }
@@ -335,8 +343,7 @@ cudaError_t launch_tc_g(const PagedAttnParams& p, const CUtensorMap& tm, cudaStr
         attr_done = true;
     }
     dim3 grid((p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens, p.kv_heads, p.batch);
-    kern<<<grid, TC_THREADS, TC_SMEM, stream>>>(tm, p);
-    return cudaGetLastError();
+    return launch_pdl(kern, grid, dim3(TC_THREADS), (size_t)TC_SMEM, stream, tm, p);
 }
 
 }  // namespace

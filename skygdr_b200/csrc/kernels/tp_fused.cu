@@ -32,6 +32,8 @@ __device__ __forceinline__ unsigned tp_seq(const TpSeq& s) { return *s.step * s.
 __global__ void __launch_bounds__(256) tp_norm_kernel(const TpNormParams p) {
     __shared__ float red[8];
     __shared__ int s_ok;
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     const int nvec = p.hidden / 8;
     if (threadIdx.x == 0) {
@@ -97,8 +99,7 @@ __global__ void __launch_bounds__(256) tp_norm_kernel(const TpNormParams p) {
 
 cudaError_t launch_tp_norm(const TpNormParams& p, cudaStream_t stream) {
     if (p.hidden % 8 || p.hidden > 8192 || p.rows <= 0 || p.world < 1 || p.world > TP_MAX_RANKS) return cudaErrorInvalidValue;
-    tp_norm_kernel<<<p.rows, 256, 0, stream>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(tp_norm_kernel, dim3(p.rows), dim3(256), 0, stream, p);
 }
 
 // Orders floats as unsigned integers: larger float <=> larger key.
@@ -110,6 +111,8 @@ __device__ __forceinline__ unsigned float_key(float f) {
 __global__ void __launch_bounds__(256) tp_argmax_kernel(const TpArgmaxParams p) {
     __shared__ unsigned long long best_s[8];
     __shared__ int s_ok;
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     const __nv_bfloat16* lg = p.logits + (long long)row * p.row_stride;
     // candidate = (ordered value, inverted global index): the maximum prefers the larger value, then the lower index
@@ -151,14 +154,12 @@ __global__ void __launch_bounds__(256) tp_argmax_kernel(const TpArgmaxParams p) 
 
 cudaError_t launch_tp_argmax(const TpArgmaxParams& p, cudaStream_t stream) {
     if (p.rows <= 0 || p.world < 1 || p.world > TP_MAX_RANKS) return cudaErrorInvalidValue;
-    tp_argmax_kernel<<<p.rows, 256, 0, stream>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(tp_argmax_kernel, dim3(p.rows), dim3(256), 0, stream, p);
 }
 
-__global__ void step_increment_kernel(unsigned int* step) { *step += 1; }
+__global__ void step_increment_kernel(unsigned int* step) { pdl_wait(); *step += 1; }
 cudaError_t launch_step_increment(unsigned int* step, cudaStream_t stream) {
-    step_increment_kernel<<<1, 1, 0, stream>>>(step);
-    return cudaGetLastError();
+    return launch_pdl(step_increment_kernel, dim3(1), dim3(1), 0, stream, step);
 }
 
 }  // namespace sky

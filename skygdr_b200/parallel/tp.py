@@ -31,7 +31,7 @@ TIMEOUT_NS = 2_000_000_000
 
 class TPDecoder:
     def __init__(self, cfg: Qwen3Config, weights: Qwen3Weights, pool: PagedKVPool, batch: int, max_ctx: int, rank: int, world: int,
-                 attn_chunk: int = 1024, group=None):
+                 attn_chunk: int = 1024, group=None, attn_impl: str = "tc"):
         assert batch % world == 0 and pool.layout == "hnd"
         self._C = load()
         self.cfg, self.w, self.pool, self.rank, self.world = cfg, weights, pool, rank, world
@@ -68,7 +68,7 @@ class TPDecoder:
         self.max_blocks = (max_ctx + 15) // 16
         self.block_table = torch.zeros((B, self.max_blocks), dtype=torch.int32, device=dev)
         self.inv_freq = ops.rope_inv_freq(cfg.rope_theta, dev, D)
-        self.attn = ops.PagedAttention(dev, B, self.qh, self.kh, max_ctx, attn_chunk)
+        self.attn = ops.PagedAttention(dev, B, self.qh, self.kh, max_ctx, attn_chunk, impl=attn_impl)
         self.step_ctr = torch.zeros(1, dtype=torch.int32, device=dev)
         self.status = new_status(dev)
         self.ws = GemmWorkspace(dev)
@@ -177,7 +177,7 @@ Qwen3Decoder.bytes_per_step = lambda self, ctx: _bytes_per_step(self.cfg, self.w
 
 
 def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world: int, ctx: torch.Tensor, extra_tokens: int,
-                        seed: int = 0, kv_init: str = "normal", attn_chunk: int = 1024):
+                        seed: int = 0, kv_init: str = "normal", attn_chunk: int = 1024, attn_impl: str = "tc"):
     """Weights shard, KV pool sized for ``ctx`` (+ ``extra_tokens`` of growth per sequence), randomly permuted block
     table, and the decode engine for this rank. Every rank passes the same ``ctx`` and ``seed``."""
     batch = ctx.numel()
@@ -201,7 +201,7 @@ def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world
         table[i, :nb] = perm[o:o + nb]
         o += nb
     if world == 1:
-        eng = Qwen3Decoder(cfg, weights, pool, batch, max_ctx, attn_chunk)
+        eng = Qwen3Decoder(cfg, weights, pool, batch, max_ctx, attn_chunk, attn_impl)
     else:
-        eng = TPDecoder(cfg, weights, pool, batch, max_ctx, rank, world, attn_chunk)
+        eng = TPDecoder(cfg, weights, pool, batch, max_ctx, rank, world, attn_chunk, attn_impl=attn_impl)
     return eng, table

@@ -56,8 +56,8 @@ def main():
         table[i, :nb] = perm[o:o + nb]
         o += nb
     ids = torch.randint(0, cfg.vocab, (B,), generator=g).int()
-    full = Qwen3Decoder(cfg, full_w, full_pool, B, max_ctx, attn_chunk=64)
-    tp = TPDecoder(cfg, shard_w, tp_pool, B, max_ctx, rank, world, attn_chunk=64)
+    full = Qwen3Decoder(cfg, full_w, full_pool, B, max_ctx, attn_chunk=64, attn_impl="simt")
+    tp = TPDecoder(cfg, shard_w, tp_pool, B, max_ctx, rank, world, attn_chunk=128)
     full.set_batch(ids.to(dev), ctx.int().to(dev), table.to(dev))
     tp.set_batch(ids.to(dev), ctx.int().to(dev), table.to(dev))
     worst = 0.0

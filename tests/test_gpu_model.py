@@ -5,14 +5,14 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _setup(layers=2, max_batch=4, max_ctx=256):
+def _setup(layers=2, max_batch=4, max_ctx=256, attn_impl="simt", attn_chunk=64):
     from skygdr_b200 import ops
     from skygdr_b200.models import Qwen3Config, Qwen3Decoder, Qwen3Weights
 
     cfg = Qwen3Config.tiny(layers=layers)
     w = Qwen3Weights(cfg, "cuda", seed=1, std=0.05)
     pool = ops.PagedKVPool(cfg.geometry, 64, "hnd")
-    eng = Qwen3Decoder(cfg, w, pool, max_batch=max_batch, max_ctx=max_ctx, attn_chunk=64)
+    eng = Qwen3Decoder(cfg, w, pool, max_batch=max_batch, max_ctx=max_ctx, attn_chunk=attn_chunk, attn_impl=attn_impl)
     return cfg, w, pool, eng
 
 
@@ -28,10 +28,11 @@ def _tables(seq_lens, max_blocks, nblocks=64, seed=0):
     return table.cuda()
 
 
-def test_prefill_and_decode_match_reference():
+@pytest.mark.parametrize("attn_impl,attn_chunk", [("simt", 64), ("tc", 128)])
+def test_prefill_and_decode_match_reference(attn_impl, attn_chunk):
     from skygdr_b200.models import reference_forward
 
-    cfg, w, pool, eng = _setup()
+    cfg, w, pool, eng = _setup(attn_impl=attn_impl, attn_chunk=attn_chunk)
     torch.manual_seed(0)
     seq_lens = [37, 16, 50]
     prompts = [torch.randint(0, cfg.vocab, (n,), device="cuda") for n in seq_lens]
