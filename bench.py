@@ -44,6 +44,7 @@ def parse():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--attn-impl", default="tc", choices=["tc", "simt"])
     ap.add_argument("--attn-chunk", type=int, default=1024)
+    ap.add_argument("--profile-step", action="store_true", help="also print per-kernel-kind times of one eager step (tensor-parallel engine)")
     return ap.parse_args()
 
 
@@ -126,6 +127,11 @@ def main() -> int:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms, e2e_ms = float(t[0]), float(t[1])
     status = eng.check_status()
+    prof = None
+    if args.profile_step and hasattr(eng, "profile_step"):
+        eng.profile_step(max_ctx)
+        prof = eng.profile_step(max_ctx)
+        eng._advance(batch)
 
     if rank == 0:
         tok_s = batch * args.steps / (dev_ms * 1e-3)
@@ -148,6 +154,8 @@ def main() -> int:
                          "hbm_frac_of_measured": step_bytes / (dev_ms / args.steps) / 1e6 / hbm},
             "kernel_status": status, "impl": "ours",
         }
+        if prof:
+            out["eager_step_profile_ms"] = prof
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -142,6 +142,50 @@ class TPDecoder:
                           TIMEOUT_NS, self.status)
         self._C.step_increment(self.step_ctr)
 
+    def profile_step(self, max_ctx: int) -> dict:
+        """One eager step with a CUDA event after every kernel; returns milliseconds per kernel kind. Eager launches add
+        host gaps, so read it for shares and for time spent waiting on peers, not for absolutes."""
+        marks = []
+        C = self._C
+        orig = {n: getattr(C, n) for n in ("tp_norm", "gemm_tp", "tp_argmax", "step_increment", "rope_append", "paged_attn_decode", "embedding")}
+
+        def wrap(name, fn):
+            def f(*a, **k):
+                r = fn(*a, **k)
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append((name, e))
+                return r
+            return f
+
+        class Proxy:
+            pass
+
+        proxy = Proxy()
+        for n in dir(C):
+            if not n.startswith("__"):
+                setattr(proxy, n, wrap(n, orig[n]) if n in orig else getattr(C, n))
+        import skygdr_b200.ops.small as small
+        import skygdr_b200.ops.attention as att
+
+        saved = (self._C, small.load, self.attn._C)
+        self._C = proxy
+        small.load = lambda: proxy
+        self.attn._C = proxy
+        try:
+            start = torch.cuda.Event(enable_timing=True)
+            start.record()
+            self._step(self.batch, max_ctx)
+            torch.cuda.synchronize(self.device)
+        finally:
+            self._C, small.load, self.attn._C = saved
+        out, prev = {}, start
+        for name, e in marks:
+            out[name] = out.get(name, 0.0) + prev.elapsed_time(e)
+            prev = e
+        out["total"] = start.elapsed_time(marks[-1][1])
+        return out
+
     _advance = Qwen3Decoder._advance
     step = Qwen3Decoder.step
     capture = Qwen3Decoder.capture
