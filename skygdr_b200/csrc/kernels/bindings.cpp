@@ -276,7 +276,7 @@ static void argmax(torch::Tensor logits, torch::Tensor out) {
 
 // ---- GEMM ----
 static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, bool gated, c10::optional<torch::Tensor> workspace,
-                 c10::optional<torch::Tensor> counters, torch::Tensor status) {
+                 c10::optional<torch::Tensor> counters, torch::Tensor status, int ntok) {
     c10::cuda::CUDAGuard g(x.device());
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1, "row-major 2-D tensors");
     GemmParams p;
@@ -286,11 +286,11 @@ static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, 
     p.N = gated ? (int)w.size(0) / 2 : (int)w.size(0);
     TORCH_CHECK(w.size(1) == p.K && y.size(0) == p.M && y.size(1) == p.N, "shape mismatch");
     p.ldx = x.stride(0); p.ldw = w.stride(0); p.ldy = y.stride(0);
-    p.splits = splits; p.gated = gated;
+    p.splits = splits; p.gated = gated; p.ntok = ntok;
     if (splits > 1) {
         TORCH_CHECK(workspace.has_value() && counters.has_value(), "split-K needs workspace and counters");
-        TORCH_CHECK((size_t)workspace->numel() >= gemm_workspace_floats(p.M, p.N, splits, gated), "workspace too small");
-        TORCH_CHECK((size_t)counters->numel() >= gemm_counter_count(p.M, p.N, gated), "counters too small");
+        TORCH_CHECK((size_t)workspace->numel() >= gemm_workspace_floats(p.M, p.N, splits, gated, ntok), "workspace too small");
+        TORCH_CHECK((size_t)counters->numel() >= gemm_counter_count(p.M, p.N, gated, ntok), "counters too small");
         p.workspace = workspace->data_ptr<float>();
         p.counters = reinterpret_cast<unsigned int*>(counters->data_ptr());
     }
@@ -308,7 +308,7 @@ static TpSeq make_seq(uint64_t step_ptr, unsigned uses_per_step, unsigned use_in
 // ag = (n_src, counters_ptr, step_ptr, uses_per_step, use_index, arrivals_per_use, timeout_ns) or empty
 // rs = (world, src_rank, rows_per_rank, [dst ptrs], [counter ptrs]) or empty
 static void gemm_tp(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, bool gated, c10::optional<torch::Tensor> workspace,
-                    c10::optional<torch::Tensor> counters, torch::Tensor status, py::tuple ag, py::tuple rs) {
+                    c10::optional<torch::Tensor> counters, torch::Tensor status, py::tuple ag, py::tuple rs, int ntok) {
     c10::cuda::CUDAGuard g(x.device());
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "row-major 2-D tensors");
     GemmParams p;
@@ -322,11 +322,11 @@ static void gemm_tp(torch::Tensor x, torch::Tensor w, torch::Tensor y, int split
         TORCH_CHECK(y.dim() == 2 && y.size(0) == p.M && y.size(1) == p.N && y.stride(1) == 1, "y shape");
         p.y = bf16_mut(y); p.ldy = y.stride(0);
     }
-    p.splits = splits; p.gated = gated;
+    p.splits = splits; p.gated = gated; p.ntok = ntok;
     if (splits > 1) {
         TORCH_CHECK(workspace.has_value() && counters.has_value(), "split-K needs workspace and counters");
-        TORCH_CHECK((size_t)workspace->numel() >= gemm_workspace_floats(p.M, p.N, splits, gated), "workspace too small");
-        TORCH_CHECK((size_t)counters->numel() >= gemm_counter_count(p.M, p.N, gated), "counters too small");
+        TORCH_CHECK((size_t)workspace->numel() >= gemm_workspace_floats(p.M, p.N, splits, gated, ntok), "workspace too small");
+        TORCH_CHECK((size_t)counters->numel() >= gemm_counter_count(p.M, p.N, gated, ntok), "counters too small");
         p.workspace = workspace->data_ptr<float>();
         p.counters = reinterpret_cast<unsigned int*>(counters->data_ptr());
     }
@@ -417,8 +417,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("tp_norm", &tp_norm);
     m.def("tp_argmax", &tp_argmax);
     m.def("step_increment", &step_increment);
-    m.def("gemm_workspace_floats", &gemm_workspace_floats);
-    m.def("gemm_counter_count", &gemm_counter_count);
+    m.def("gemm_workspace_floats", &gemm_workspace_floats, py::arg("M"), py::arg("N"), py::arg("splits"), py::arg("gated"), py::arg("ntok") = 0);
+    m.def("gemm_counter_count", &gemm_counter_count, py::arg("M"), py::arg("N"), py::arg("gated"), py::arg("ntok") = 0);
     m.def("gemm_pick_ntok", &gemm_pick_ntok);
     m.attr("STATUS_BYTES") = py::int_(sizeof(LaunchStatus));
 

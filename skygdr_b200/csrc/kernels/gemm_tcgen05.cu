@@ -306,21 +306,22 @@ int gemm_pick_ntok(int M, bool gated) {
     return 256;
 }
 
-size_t gemm_workspace_floats(int M, int N, int splits, bool gated) {
+size_t gemm_workspace_floats(int M, int N, int splits, bool gated, int ntok) {
     if (splits <= 1) return 0;
-    const int ntok = gemm_pick_ntok(M, gated);
+    if (ntok <= 0) ntok = gemm_pick_ntok(M, gated);
     const long long tiles = (long long)((N + BM - 1) / BM) * ((M + ntok - 1) / ntok);
     return (size_t)(tiles * splits * ntok * (gated ? 2 : 1) * BM);
 }
-size_t gemm_counter_count(int M, int N, bool gated) {
-    const int ntok = gemm_pick_ntok(M, gated);
+size_t gemm_counter_count(int M, int N, bool gated, int ntok) {
+    if (ntok <= 0) ntok = gemm_pick_ntok(M, gated);
     return (size_t)((N + BM - 1) / BM) * ((M + ntok - 1) / ntok);
 }
 
 cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream) {
     if (p.K % BK || p.M <= 0 || p.N <= 0 || p.splits < 1 || p.splits > p.K / BK) return cudaErrorInvalidValue;
     if (p.splits > 1 && (!p.workspace || !p.counters)) return cudaErrorInvalidValue;
-    const int ntok = gemm_pick_ntok(p.M, p.gated != 0);
+    const int ntok = p.ntok > 0 ? p.ntok : gemm_pick_ntok(p.M, p.gated != 0);
+    if (ntok != 16 && ntok != 32 && ntok != 64 && ntok != 128 && ntok != 256) return cudaErrorInvalidValue;
     CUtensorMap tw, tx;
     const long long w_rows = p.gated ? 2LL * p.N : p.N;
     if (!make_tmap_bf16_2d(&tw, p.w, w_rows, p.K, p.ldw, BM)) return cudaErrorInvalidValue;

@@ -46,6 +46,7 @@ struct GemmParams {
     int M, N, K;
     long long ldx, ldw, ldy;
     int splits;               // split-K factor (1 = none)
+    int ntok;                 // token-tile width (16/32/64/128/256); 0 = smallest that covers M
     int gated;                // 1: y = silu(x*w_gate^T) * (x*w_up^T)
     float* workspace;         // split-K partials, gemm_workspace_floats() floats
     unsigned int* counters;   // split-K tile counters, gemm_counter_count() entries, zero before first use
@@ -55,7 +56,7 @@ struct GemmParams {
 };
 
 int gemm_pick_ntok(int M, bool gated);
-size_t gemm_workspace_floats(int M, int N, int splits, bool gated);
-size_t gemm_counter_count(int M, int N, bool gated);
+size_t gemm_workspace_floats(int M, int N, int splits, bool gated, int ntok = 0);
+size_t gemm_counter_count(int M, int N, bool gated, int ntok = 0);
 cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream);
 }  // namespace sky

@@ -19,31 +19,38 @@ def _sms(device) -> int:
 
 
 def pick_splits(M: int, N: int, K: int, sms: int, gated: bool = False) -> int:
-    """Split-K factor for weight-streaming GEMMs: one CTA occupies one SM, so the CTA count should fill
-    whole waves of ``sms``. Picks the factor (each split keeps at least 4 k-blocks of 64) whose last wave is
-    fullest; ties go to the smaller factor."""
-    C = load()
-    ntok = C.gemm_pick_ntok(M, gated)
-    tiles = ((N + 127) // 128) * ((M + ntok - 1) // ntok)
+    """Split-K factor for the default token tile (kept for callers that do not choose the tile)."""
+    return pick_config(M, N, K, sms, gated, fixed_ntok=load().gemm_pick_ntok(M, gated))[1]
+
+
+def pick_config(M: int, N: int, K: int, sms: int, gated: bool = False, fixed_ntok: int = 0) -> Tuple[int, int]:
+    """(token tile, split-K factor) for y[M][N] = x[M][K] w[N][K]^T with small M.
+
+    One CTA holds one SM (its pipeline takes ~200 KB of shared memory), so the time is about
+    waves x (fixed cost + bytes per CTA / per-SM stream rate), bounded below by total bytes over HBM rate.
+    Constants are measured on B200: ~6 us of prologue + epilogue per CTA, ~55 GB/s per SM, 5.5 TB/s per GPU; a split
+    adds its fp32 partial (written, then re-read by the last CTA of the tile)."""
+    wrows = 2 if gated else 1
     kb = K // 64
-    # Measured on B200: with more than half a wave of tiles, the prologue/epilogue each extra CTA pays
-    # (barrier and TMEM set-up, pipeline fill, partial write + reduce) costs more than the idle SMs.
-    if 2 * tiles > sms or M > 128:
-        return 1
-    best, best_eff = 1, 0.0
-    for s in range(1, 17):
-        if s > 1 and kb // s < 4:
-            break
-        per = (kb + s - 1) // s
-        s_eff = (kb + per - 1) // per          # splits that actually get work
-        ctas = tiles * s_eff
-        waves = (ctas + sms - 1) // sms
-        # time ~ waves * per (k-blocks streamed back to back by the busiest SM)
-        eff = (tiles * kb) / (waves * per * sms)
-        if s > 1:
-            eff /= 1.0 + s_eff * ntok * 4.0 / K      # fp32 partials written and re-read, relative to the weight bytes
-        if eff > best_eff + 0.03:
-            best, best_eff = s, eff
+    cands = [fixed_ntok] if fixed_ntok else [n for n in (16, 32, 64, 128, 256) if n >= 16 and (n < 2 * M or n == 16) and not (gated and n > 128)]
+    best, best_t = (cands[-1], 1), float("inf")
+    tiles_n = (N + 127) // 128
+    for ntok in cands:
+        tiles_m = (M + ntok - 1) // ntok
+        for s in range(1, 17):
+            if s > 1 and kb // s < 4:
+                break
+            per = (kb + s - 1) // s
+            s_eff = (kb + per - 1) // per
+            ctas = tiles_n * tiles_m * s_eff
+            waves = (ctas + sms - 1) // sms
+            bytes_cta = per * (128 * 64 * 2 * wrows + ntok * 64 * 2)
+            part = ntok * 128 * 4 * wrows
+            t_cta = 6.0 + bytes_cta / 55e3 + (part / 100e3 + 1.0 + s_eff * part / 200e3 if s_eff > 1 else 0.0)
+            hbm = (tiles_n * 128 * K * 2 * wrows + M * K * 2) / 5.5e6
+            t = max(waves * t_cta, hbm)
+            if t < best_t * 0.92:                 # simpler shapes come first; a rival must be clearly better
+                best, best_t = (ntok, s_eff), t
     return best
 
 
@@ -74,7 +81,7 @@ def workspace_for(device) -> GemmWorkspace:
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, gated: bool = False,
-         splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None) -> torch.Tensor:
+         splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, ntok: int = 0) -> torch.Tensor:
     """y = x @ w.T (w is [N][K]); gated: w is [2N][K] and y = silu(x @ w[:N].T) * (x @ w[N:].T)."""
     C = load()
     M, K = x.shape
@@ -82,11 +89,14 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, g
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     if splits is None:
-        splits = pick_splits(M, N, K, _sms(x.device), gated)
+        if ntok == 0 and M <= 256:
+            ntok, splits = pick_config(M, N, K, _sms(x.device), gated)
+        else:
+            splits = 1 if M > 256 else pick_config(M, N, K, _sms(x.device), gated, fixed_ntok=ntok)[1]
     ws = ws or workspace_for(x.device)
     if splits > 1:
-        ws.ensure(C.gemm_workspace_floats(M, N, splits, gated), C.gemm_counter_count(M, N, gated))
-        C.gemm(x, w, out, splits, gated, ws.ws, ws.counters, ws.status)
+        ws.ensure(C.gemm_workspace_floats(M, N, splits, gated, ntok), C.gemm_counter_count(M, N, gated, ntok))
+        C.gemm(x, w, out, splits, gated, ws.ws, ws.counters, ws.status, ntok)
     else:
-        C.gemm(x, w, out, 1, gated, None, None, ws.status)
+        C.gemm(x, w, out, 1, gated, None, None, ws.status, ntok)
     return out

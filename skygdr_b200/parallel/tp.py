@@ -22,7 +22,7 @@ from .. import ops
 from .._ext import load
 from ..models.qwen3 import Qwen3Config, Qwen3Decoder, Qwen3Weights
 from ..ops.flow import new_status, read_status
-from ..ops.gemm import GemmWorkspace, pick_splits
+from ..ops.gemm import GemmWorkspace, pick_config
 from ..ops.kv_cache import KVGeometry, PagedKVPool
 from .symm import SymmetricHeap
 
@@ -97,7 +97,8 @@ class TPDecoder:
         else:
             name, off = ("rs0", self.c_rs0) if rs_which == 0 else ("rs1", self.c_rs1)
             rs_buf, rs_ctr = self.heap.ptr(name, self.rank), self.heap.ptr("counters", self.rank, off)
-            seq = (self.step_ctr.data_ptr(), L, rs_use, self.world * self.tiles_h)
+            k_in = (self.cfg.q_heads // self.world) * self.cfg.head_dim if rs_which == 0 else self.cfg.ffn // self.world
+            seq = (self.step_ctr.data_ptr(), L, rs_use, self._rs_arrivals(k_in))
         ag_name, ag_off = ("agA", self.c_agA) if ag_which == "A" else ("agB", self.c_agB)
         self._C.tp_norm(rs_buf, rs_ctr, seq, self.resid, w, self.heap.all_ptrs(ag_name),
                         self.heap.all_ptrs("counters", ag_off + 4 * self.rank), self.rank, self.cfg.eps, TIMEOUT_NS, self.status)
@@ -105,12 +106,17 @@ class TPDecoder:
     def _gemm(self, x, w, y, gated=False, ag=(), rs=()):
         M, K = x.shape
         N = w.shape[0] // 2 if gated else w.shape[0]
-        splits = pick_splits(M, N, K, 148, gated)
+        ntok, splits = pick_config(M, N, K, 148, gated)
         if splits > 1:
-            self.ws.ensure(self._C.gemm_workspace_floats(M, N, splits, gated), self._C.gemm_counter_count(M, N, gated))
-            self._C.gemm_tp(x, w, y, splits, gated, self.ws.ws, self.ws.counters, self.status, ag, rs)
+            self.ws.ensure(self._C.gemm_workspace_floats(M, N, splits, gated, ntok), self._C.gemm_counter_count(M, N, gated, ntok))
+            self._C.gemm_tp(x, w, y, splits, gated, self.ws.ws, self.ws.counters, self.status, ag, rs, ntok)
         else:
-            self._C.gemm_tp(x, w, y, 1, gated, None, None, self.status, ag, rs)
+            self._C.gemm_tp(x, w, y, 1, gated, None, None, self.status, ag, rs, ntok)
+
+    def _rs_arrivals(self, K: int) -> int:
+        """Arrivals one reduce-scatter adds to a rank's counter: every output tile of every rank's GEMM."""
+        ntok, _ = pick_config(self.batch, self.cfg.hidden, K, 148, False)
+        return self.world * self.tiles_h * ((self.batch + ntok - 1) // ntok)
 
     def set_batch(self, ids: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor) -> None:
         b = ids.numel()
