@@ -1,0 +1,188 @@
+"""TP decode under contention: Qwen3-8B tensor-parallel decode while every GPU also receives KV bursts over NVLink
+and offloads KV to pinned host memory.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        benchmarks/config5_tp_contention.py [--seconds 3] [--burst-gb 2 --burst-every-ms 500] [--offload-gbps 16]
+        [--baseline nccl] [--out gpurun_out/config5.json]
+
+Phases per run: clean decode; contended, unscheduled (bursts and offload unpaced); contended, scheduled (the offload is
+held to its offered rate by its credit page, the bursts are paced to `--burst-budget-gbps`). Each rank r receives bursts
+from rank (r+1) % N through the paged transfer kernel and runs one offload task (chunked async copies, low-priority
+streams). Decode tokens/s is device-timed (CUDA events around graph replays), max over ranks.
+`--baseline nccl` adds the comparison arm the fused collectives are measured against: the same decoder with
+torch.distributed all-gather / reduce-scatter (NCCL) and torch.matmul (cuBLAS) in place of the fused kernels.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from skygdr_b200 import ops  # noqa: E402
+from skygdr_b200._ext import load  # noqa: E402
+from skygdr_b200.cli.common import env_info  # noqa: E402
+from skygdr_b200.models import Qwen3Config  # noqa: E402
+from skygdr_b200.parallel.nccl_baseline import NcclTPDecoder  # noqa: E402
+from skygdr_b200.parallel.symm import SymmetricHeap  # noqa: E402
+from skygdr_b200.parallel.tp import build_decode_engine  # noqa: E402
+
+
+def timed_decode(eng, seconds, world, dev):
+    for _ in range(3):
+        eng.replay()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    steps, ms = 0, 0.0
+    n = torch.zeros(1, device=dev)
+    t0 = time.perf_counter()
+    while True:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(8):
+            eng.replay()
+        e1.record()
+        e1.synchronize()
+        ms += e0.elapsed_time(e1)
+        steps += 8
+        # all ranks must stop after the same number of steps: rank 0 decides
+        n[0] = 1.0 if time.perf_counter() - t0 >= seconds else 0.0
+        if world > 1:
+            dist.broadcast(n, 0)
+        if float(n[0]) > 0:
+            break
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return steps, float(t[0])
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--seconds", type=float, default=3.0)
+    ap.add_argument("--burst-gb", type=float, default=2.0)
+    ap.add_argument("--burst-every-ms", type=float, default=500.0)
+    ap.add_argument("--burst-budget-gbps", type=float, default=200.0)
+    ap.add_argument("--offload-gbps", type=float, default=16.0)
+    ap.add_argument("--batch-per-gpu", type=int, default=16)
+    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--baseline", default="", choices=["", "nccl"])
+    ap.add_argument("--out", default="gpurun_out/config5.json")
+    a = ap.parse_args()
+    C = load()
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = Qwen3Config(layers=a.layers)
+    batch = a.batch_per_gpu * world
+    g = torch.Generator().manual_seed(0)
+    ctx = torch.randint(2048, 16384 + 1, (batch,), generator=g)
+    steps_cap = int(a.seconds * 400) + 64
+    eng, table = build_decode_engine(cfg, dev, rank, world, ctx, steps_cap * (3 if not a.baseline else 4), seed=0)
+    max_ctx = int(ctx.max()) + steps_cap * 4 + 1
+    ids0 = torch.randint(0, cfg.vocab, (batch,), generator=g).int()
+    eng.set_batch(ids0.to(dev), ctx.int().to(dev), table.to(dev))
+    eng.capture(batch, eng.max_ctx)
+    res = {"env": env_info(), "config": vars(a), "world": world, "phases": {}}
+
+    # ---- clean ----
+    steps, ms = timed_decode(eng, a.seconds, world, dev)
+    clean = batch * steps / (ms * 1e-3)
+    res["phases"]["clean"] = {"tok_s": clean, "ms_per_step": ms / steps}
+
+    # ---- background flows ----
+    geom = ops.KVGeometry()
+    nb = int(a.burst_gb * 1e9 / (geom.block_elems * 2))
+    heap = SymmetricHeap(nb * geom.block_elems * 2 + 4096, rank, world, dev)
+    heap.alloc("inbound", nb * geom.block_elems * 2)
+    if world > 1:
+        dist.barrier()
+    src = ops.PagedKVPool(geom, nb, "nhd", device=dev)
+    for i in range(0, nb, 256):
+        src.data[i:i + 256].normal_()
+    dst_rank = (rank - 1) % world                       # this rank SENDS to rank-1, i.e. receives from rank+1
+    inbound_local = ops.PagedKVPool(geom, nb, "hnd", device=dev, data=heap.local_tensor("inbound", (nb * geom.block_elems,), torch.bfloat16))
+    remote = ops.RemotePool(heap.ptr("inbound", dst_rank), inbound_local.strides, geom.kv_heads)
+    sp, dp = torch.randperm(nb).int().to(dev), torch.randperm(nb).int().to(dev)
+    t_page = ops.CreditPage(flow_id=1, unlimited=True)
+    t_flow = ops.KvTransferFlow(dev, page=t_page, max_wait_ms=20.0)
+    xfer_stream = torch.cuda.Stream(dev)
+    o_page = ops.CreditPage(flow_id=2, unlimited=True)
+
+    def contended(scheduled: bool):
+        stop = threading.Event()
+        xfer_ms = []
+        pacers = []
+        if scheduled:
+            t_page.grant(t_flow.consumed, unlimited=False)
+            pacers.append(ops.LocalPacer(t_page, a.burst_budget_gbps, window_ms=1.0).start(base=t_flow.consumed))
+            base = o_page.read()["consumed_bytes"]
+            pacers.append(ops.LocalPacer(o_page, a.offload_gbps, window_ms=2.0).start(base=base))
+        else:
+            t_page.set_unlimited()
+            o_page.set_unlimited()
+        pc = C.PcieTaskConfig()
+        pc.device, pc.h2d, pc.chunk_bytes, pc.streams, pc.batch, pc.inflight = local, False, 32 << 20, 4, 2, 4
+        pc.seconds, pc.progress_ms = a.seconds + 2.0, 100
+        pc.consumed_base = o_page.read()["consumed_bytes"]
+        pc.set_credit_page(o_page.host_ptr)
+        task = C.PcieTask(pc)
+        task.setup()                       # pinned allocations stall the device: do them before anyone is timed
+        if world > 1:
+            dist.barrier()
+        task.start()
+
+        def bursts():
+            while not stop.is_set():
+                with torch.cuda.stream(xfer_stream):
+                    st = t_flow.transfer_to_completion(src, [remote], sp, dp)
+                xfer_ms.append(st["device_time_ms"])
+                stop.wait(a.burst_every_ms / 1e3)
+
+        th = threading.Thread(target=bursts, daemon=True)
+        th.start()
+        steps, ms = timed_decode(eng, a.seconds, world, dev)
+        stop.set()
+        th.join()
+        task.stop()
+        task.join()
+        for p in pacers:
+            p.stop()
+        pr = task.progress()
+        return {"tok_s": batch * steps / (ms * 1e-3), "vs_clean": batch * steps / (ms * 1e-3) / clean, "ms_per_step": ms / steps,
+                "burst_ms_mean": sum(xfer_ms) / max(1, len(xfer_ms)), "bursts": len(xfer_ms),
+                "burst_gbs": nb * geom.block_elems * 2 / 1e6 / (sum(xfer_ms) / max(1, len(xfer_ms))) if xfer_ms else None,
+                "offload_gb_s": pr.avg_bw_gib_s * 1.073741824}
+
+    res["phases"]["contended_unscheduled"] = contended(False)
+    if world > 1:
+        dist.barrier()
+    res["phases"]["contended_scheduled"] = contended(True)
+    res["kernel_status"] = eng.check_status()
+
+    if a.baseline == "nccl" and world > 1:
+        base = NcclTPDecoder.from_engine(eng)
+        base.capture(batch, eng.max_ctx)
+        steps, ms = timed_decode(base, a.seconds, world, dev)
+        res["phases"]["nccl_cublas_baseline_clean"] = {"tok_s": batch * steps / (ms * 1e-3), "ms_per_step": ms / steps,
+                                                       "fused_speedup": clean / (batch * steps / (ms * 1e-3))}
+    if rank == 0:
+        os.makedirs(os.path.dirname(os.path.abspath(a.out)), exist_ok=True)
+        json.dump(res, open(a.out, "w"), indent=1)
+        print(json.dumps(res["phases"], indent=1))
+    if world > 1:
+        dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)        # peer mappings and helper threads are torn down with the process
+
+
+if __name__ == "__main__":
+    main()

@@ -459,6 +459,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("csv", [](const PcieProgress& p) { return PcieTask::csv_row(p); });
     py::class_<PcieTask>(m, "PcieTask")
         .def(py::init<const PcieTaskConfig&>())
+        .def("setup", &PcieTask::setup, py::call_guard<py::gil_scoped_release>())
         .def("start", &PcieTask::start, py::call_guard<py::gil_scoped_release>())
         .def("stop", &PcieTask::stop)
         .def("join", &PcieTask::join, py::call_guard<py::gil_scoped_release>())

@@ -82,6 +82,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
+    // With an all-gather in front, the producer may wait for peers up to its own deadline; the consumers of its
+    // barriers must outlast that, or a late peer would look like a broken pipeline.
+    const unsigned long long bar_timeout = p.ag.n_src > 0 ? p.ag.timeout_ns + 1000000000ull : 200000000ull;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -132,7 +135,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             bool ok = true;
             for (int i = 0; i < nkb && ok; ++i) {
                 const int s = i % S::STAGES;
-                if (!mbar_wait(&full_bar[s], (i / S::STAGES) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 2); ok = false; break; }
+                if (!mbar_wait(&full_bar[s], (i / S::STAGES) & 1, bar_timeout)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 2); ok = false; break; }
                 tc_fence_after();
                 const uint32_t st = smem_u32(smem + s * S::STAGE_BYTES);
                 const uint64_t a0 = umma_desc_k_sw128(st);
@@ -155,7 +158,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const int n = n0 + r;
         bool ok = true;
         pdl_wait();     // nothing is written before the previous kernel has finished reading its inputs
-        if (nkb > 0) ok = mbar_wait(&acc_bar, 0);
+        if (nkb > 0) ok = mbar_wait(&acc_bar, 0, bar_timeout);
         if (!ok && lane == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 3);
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(slice * 32) << 16);

@@ -202,6 +202,7 @@ void PcieTask::run() {
                     if (e != cudaSuccess) { fail("cudaMemcpyAsync"); stop_.store(true); break; }
                     batch_bytes += n;
                     issued_ += n;
+                    if (page) __atomic_store_n(&page->consumed_bytes, base + issued_, __ATOMIC_RELAXED);   // the pacer's view of use
                 }
                 if (batch_bytes) {
                     cudaEvent_t ev;
