@@ -33,7 +33,9 @@ from skygdr_b200.parallel.symm import SymmetricHeap  # noqa: E402
 from skygdr_b200.parallel.tp import build_decode_engine  # noqa: E402
 
 
-def timed_decode(eng, seconds, world, dev):
+def timed_decode(eng, seconds, world, dev, state=None):
+    if state is not None:                       # every phase starts from the same context lengths
+        eng.ids.copy_(state[0]); eng.positions.copy_(state[1]); eng.ctx_lens.copy_(state[2])
     for _ in range(3):
         eng.replay()
     if world > 1:
@@ -73,6 +75,7 @@ def main():
     ap.add_argument("--batch-per-gpu", type=int, default=16)
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--baseline", default="", choices=["", "nccl"])
+    ap.add_argument("--diagnose", action="store_true", help="also run each background flow alone, paced and unpaced")
     ap.add_argument("--out", default="gpurun_out/config5.json")
     a = ap.parse_args()
     C = load()
@@ -86,15 +89,15 @@ def main():
     g = torch.Generator().manual_seed(0)
     ctx = torch.randint(2048, 16384 + 1, (batch,), generator=g)
     steps_cap = int(a.seconds * 400) + 64
-    eng, table = build_decode_engine(cfg, dev, rank, world, ctx, steps_cap * (3 if not a.baseline else 4), seed=0)
-    max_ctx = int(ctx.max()) + steps_cap * 4 + 1
+    eng, table = build_decode_engine(cfg, dev, rank, world, ctx, steps_cap, seed=0)
     ids0 = torch.randint(0, cfg.vocab, (batch,), generator=g).int()
     eng.set_batch(ids0.to(dev), ctx.int().to(dev), table.to(dev))
     eng.capture(batch, eng.max_ctx)
     res = {"env": env_info(), "config": vars(a), "world": world, "phases": {}}
 
+    state0 = (eng.ids.clone(), eng.positions.clone(), eng.ctx_lens.clone())
     # ---- clean ----
-    steps, ms = timed_decode(eng, a.seconds, world, dev)
+    steps, ms = timed_decode(eng, a.seconds, world, dev, state0)
     clean = batch * steps / (ms * 1e-3)
     res["phases"]["clean"] = {"tok_s": clean, "ms_per_step": ms / steps}
 
@@ -117,11 +120,14 @@ def main():
     xfer_stream = torch.cuda.Stream(dev)
     o_page = ops.CreditPage(flow_id=2, unlimited=True)
 
-    def contended(scheduled: bool):
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    quota = max(8, int(2 * sms * min(1.0, a.burst_budget_gbps / 700.0)))
+
+    def contended(scheduled: bool, do_bursts: bool = True, do_offload: bool = True, do_pacers: bool = True):
         stop = threading.Event()
         xfer_ms = []
         pacers = []
-        if scheduled:
+        if scheduled and do_pacers:
             t_page.grant(t_flow.consumed, unlimited=False)
             pacers.append(ops.LocalPacer(t_page, a.burst_budget_gbps, window_ms=1.0).start(base=t_flow.consumed))
             base = o_page.read()["consumed_bytes"]
@@ -135,21 +141,24 @@ def main():
         pc.consumed_base = o_page.read()["consumed_bytes"]
         pc.set_credit_page(o_page.host_ptr)
         task = C.PcieTask(pc)
-        task.setup()                       # pinned allocations stall the device: do them before anyone is timed
+        if do_offload:
+            task.setup()                       # pinned allocations stall the device: do them before anyone is timed
         if world > 1:
             dist.barrier()
-        task.start()
+        if do_offload:
+            task.start()
 
         def bursts():
             while not stop.is_set():
                 with torch.cuda.stream(xfer_stream):
-                    st = t_flow.transfer_to_completion(src, [remote], sp, dp)
+                    # scheduled: the paced flow also gets an SM quota in proportion to its budget
+                    st = t_flow.transfer_to_completion(src, [remote], sp, dp, ctas=quota if scheduled else None)
                 xfer_ms.append(st["device_time_ms"])
                 stop.wait(a.burst_every_ms / 1e3)
 
-        th = threading.Thread(target=bursts, daemon=True)
+        th = threading.Thread(target=bursts if do_bursts else (lambda: None), daemon=True)
         th.start()
-        steps, ms = timed_decode(eng, a.seconds, world, dev)
+        steps, ms = timed_decode(eng, a.seconds, world, dev, state0)
         stop.set()
         th.join()
         task.stop()
@@ -162,6 +171,12 @@ def main():
                 "burst_gbs": nb * geom.block_elems * 2 / 1e6 / (sum(xfer_ms) / max(1, len(xfer_ms))) if xfer_ms else None,
                 "offload_gb_s": pr.avg_bw_gib_s * 1.073741824}
 
+    if a.diagnose:
+        for name, kw in (("only_pacer_threads", dict(do_bursts=False, do_offload=False)), ("only_offload_unpaced", dict(do_bursts=False)),
+                         ("only_bursts_unpaced", dict(do_offload=False))):
+            res["phases"][name] = contended(name == "only_pacer_threads", **kw)
+        res["phases"]["only_offload_paced"] = contended(True, do_bursts=False)
+        res["phases"]["only_bursts_paced"] = contended(True, do_offload=False)
     res["phases"]["contended_unscheduled"] = contended(False)
     if world > 1:
         dist.barrier()
@@ -171,7 +186,7 @@ def main():
     if a.baseline == "nccl" and world > 1:
         base = NcclTPDecoder.from_engine(eng)
         base.capture(batch, eng.max_ctx)
-        steps, ms = timed_decode(base, a.seconds, world, dev)
+        steps, ms = timed_decode(base, a.seconds, world, dev, state0)
         res["phases"]["nccl_cublas_baseline_clean"] = {"tok_s": batch * steps / (ms * 1e-3), "ms_per_step": ms / steps,
                                                        "fused_speedup": clean / (batch * steps / (ms * 1e-3))}
     if rank == 0:

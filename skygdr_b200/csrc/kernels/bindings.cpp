@@ -440,6 +440,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readwrite("duty_on_ms", &PcieTaskConfig::duty_on_ms)
         .def_readwrite("duty_off_ms", &PcieTaskConfig::duty_off_ms)
         .def_readwrite("consumed_base", &PcieTaskConfig::consumed_base)
+        .def_readwrite("min_issue_bytes", &PcieTaskConfig::min_issue_bytes)
         .def_readwrite("external_bytes", &PcieTaskConfig::external_bytes)
         .def("set_credit_page", [](PcieTaskConfig& c, uint64_t host_ptr) { c.credit_page = (SkyCreditPage*)host_ptr; })
         .def("set_external", [](PcieTaskConfig& c, uint64_t host_ptr, uint64_t dev_ptr, uint64_t bytes) {

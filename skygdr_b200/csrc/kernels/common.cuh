@@ -112,7 +112,7 @@ __device__ __forceinline__ bool credit_acquire(const SkyCreditPage* page, unsign
         if (need <= g) break;
         if (globaltimer_ns() - t0 > max_wait_ns) { *stall_ns += globaltimer_ns() - t0; return false; }
         __nanosleep(ns);
-        if (ns < 2048) ns <<= 1;
+        if (ns < 8192) ns <<= 1;      // the page is in host memory: poll it gently
     }
     *stall_ns += globaltimer_ns() - t0;
     return true;

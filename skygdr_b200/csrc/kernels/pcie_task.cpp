@@ -186,6 +186,9 @@ void PcieTask::run() {
                         uint64_t granted = __atomic_load_n(&page->granted_bytes, __ATOMIC_ACQUIRE);
                         uint64_t used = base + issued_;
                         if (granted <= used) break;
+                        // Do not shred the flow into tiny copies when credit trickles in: wait for a worthwhile piece.
+                        const uint64_t piece = std::min<uint64_t>(n, cfg_.min_issue_bytes);
+                        if (granted - used < piece) break;
                         n = std::min<uint64_t>(n, granted - used);
                     }
                     if (n == 0) break;

@@ -28,6 +28,7 @@ struct PcieTaskConfig {
     int duty_on_ms = 0, duty_off_ms = 0;
     SkyCreditPage* credit_page = nullptr;  // host address of the flow's page; nullptr = ungated
     uint64_t consumed_base = 0;
+    uint64_t min_issue_bytes = 8ull << 20; // under a credit gate, smallest copy worth issuing (except a final tail)
     // Optional caller-owned buffers walked through in chunk steps (kv_offload of a real pool).
     void* external_host = nullptr;
     void* external_dev = nullptr;

@@ -53,8 +53,9 @@ class KvTransferFlow:
 
     def transfer(self, src: PagedKVPool, dsts: Sequence[RemotePool], src_blocks: torch.Tensor, dst_blocks: torch.Tensor,
                  replicate: bool = False, fp8: bool = False, keep_layout: bool = False, first_chunk: int = 0,
-                 signal: bool = True) -> None:
-        """Enqueues one transfer on the current stream of the source device."""
+                 signal: bool = True, ctas: Optional[int] = None) -> None:
+        """Enqueues one transfer on the current stream of the source device. ``ctas`` overrides the flow's CTA count
+        for this launch: a paced flow should also hold fewer SMs (its SM quota), or its waiting CTAs crowd out co-runners."""
         assert src.layout == "nhd"
         g = src.geom
         heads_per_dst = g.kv_heads if replicate else g.kv_heads // len(dsts)
@@ -65,9 +66,9 @@ class KvTransferFlow:
         self._C.kv_transfer(
             src.data, [d.ptr for d in dsts], [d.scale_ptr for d in dsts], [d.done_flag_ptr if signal else 0 for d in dsts],
             src_blocks, dst_blocks, g.layers, g.kv_heads, g.block_tokens, g.head_dim, list(src.strides), list(dsts[0].strides),
-            heads_per_dst, replicate, fp8, keep_layout, self.pages_per_chunk, self.ctas,
+            heads_per_dst, replicate, fp8, keep_layout, self.pages_per_chunk, ctas or self.ctas,
             self.page.dev_ptr if self.page else 0, self.consumed, self.max_wait_ns, first_chunk, self.seq, self.status)
-        self._last = (src, dsts, src_blocks, dst_blocks, replicate, fp8, keep_layout)
+        self._last = (src, dsts, src_blocks, dst_blocks, replicate, fp8, keep_layout, ctas)
 
     def result(self) -> Dict[str, int]:
         """Synchronises and returns the status block; accounts the bytes that were moved."""
@@ -80,8 +81,8 @@ class KvTransferFlow:
     def resume(self, st: Dict[str, int]) -> None:
         """Relaunches the last transfer from the cursor a yielded launch left behind."""
         assert st["status"] in (1, 2)
-        src, dsts, sb, db, rep, fp8, keep = self._last
-        self.transfer(src, dsts, sb, db, rep, fp8, keep, first_chunk=st["cursor"])
+        src, dsts, sb, db, rep, fp8, keep, ctas = self._last
+        self.transfer(src, dsts, sb, db, rep, fp8, keep, first_chunk=st["cursor"], ctas=ctas)
 
     def transfer_to_completion(self, *args, max_launches: int = 10000, **kw) -> Dict[str, int]:
         """Transfers, relaunching after every credit yield; sums bytes and stall time."""
