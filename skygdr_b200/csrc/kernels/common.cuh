@@ -46,6 +46,11 @@ __device__ __forceinline__ void st_sys_u64(unsigned long long* p, unsigned long 
 __device__ __forceinline__ void red_release_sys_add_u32(unsigned int* p, unsigned int v) {
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Arrival without its own fence. Use after ONE __threadfence_system() when several peers are notified: a release
+// per peer would serialise one system-scope fence (a round trip over NVLink) per arrival.
+__device__ __forceinline__ void red_relaxed_sys_add_u32(unsigned int* p, unsigned int v) {
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 // 16-byte streaming load that does not pollute L1, and plain 16-byte store.
 __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
@@ -63,14 +68,15 @@ __device__ __forceinline__ void st_cs_v4(void* p, uint4 v) {
 
 // Waits until *flag >= want (acquire, system scope) or `timeout_ns` passes.
 __device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned int want, unsigned long long timeout_ns) {
-    if ((int)(ld_acquire_sys_u32(flag) - want) >= 0) return true;
+    // poll relaxed, then one acquire fence: an acquire per poll would fence every iteration
+    if ((int)(ld_sys_u32(flag) - want) >= 0) { __threadfence_system(); return true; }
     unsigned long long t0 = globaltimer_ns();
     unsigned ns = 32;
     for (;;) {
-        if ((int)(ld_acquire_sys_u32(flag) - want) >= 0) return true;
+        if ((int)(ld_sys_u32(flag) - want) >= 0) { __threadfence_system(); return true; }
         if (globaltimer_ns() - t0 > timeout_ns) return false;
         __nanosleep(ns);
-        if (ns < 1024) ns <<= 1;
+        if (ns < 256) ns <<= 1;
     }
 }
 

@@ -28,14 +28,33 @@ bool pdl_enabled() {
     return on == 1;
 }
 
-// Where output element (token t, column n) goes: the local y, or a peer's reduce-scatter slot.
-__device__ __forceinline__ void gemm_store(const GemmParams& p, int t, int n, float v) {
-    if (p.rs.world == 0) {
-        p.y[(long long)t * p.ldy + n] = __float2bfloat16(v);
-    } else {
-        const int j = t / p.rs.rows_per_rank, lr = t - j * p.rs.rows_per_rank;
-        p.rs.dst[j][((long long)(p.rs.src_rank * p.rs.rows_per_rank + lr)) * p.N + n] = __float2bfloat16(v);
+// Writes a chunk of 16 token rows x 128 columns. Thread r (0..127 of the epilogue warps) holds column n0+r of the 16
+// rows. The values are staged through shared memory so that each row leaves as 16-byte pieces, 256 contiguous bytes
+// per row, instead of one 2-byte store per element: that matters most when the destination is a peer over NVLink.
+__device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16* stage, int t_base, int n0, int r, const float* vals) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) stage[j * 128 + r] = __float2bfloat16(vals[j]);
+    asm volatile("bar.sync 3, 128;" ::: "memory");
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int idx = r + 128 * k, j = idx >> 4, ch = idx & 15;
+        const int t = t_base + j, n = n0 + ch * 8;
+        if (t < p.M && n < p.N) {
+            __nv_bfloat16* dst;
+            if (p.rs.world == 0) dst = p.y + (long long)t * p.ldy + n;
+            else {
+                const int d = t / p.rs.rows_per_rank, lr = t - d * p.rs.rows_per_rank;
+                dst = p.rs.dst[d] + ((long long)(p.rs.src_rank * p.rs.rows_per_rank + lr)) * p.N + n;
+            }
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + j * 128 + ch * 8);
+            if (n + 8 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) st_v4(dst, v);
+            else {
+                const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+                for (int q = 0; q < 8 && n + q < p.N; ++q) dst[q] = e[q];
+            }
+        }
     }
+    asm volatile("bar.sync 3, 128;" ::: "memory");
 }
 
 constexpr int GEMM_THREADS = 192;
@@ -61,6 +80,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     __shared__ uint64_t full_bar[8], empty_bar[8], acc_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int s_last;
+    __shared__ __align__(16) __nv_bfloat16 stage[16 * 128];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     pdl_trigger();     // the next kernel may start its own prologue while this one streams
@@ -155,7 +175,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         // ---- epilogue warps: TMEM lanes 32*(warp%4) .. +31 ----
         const int slice = warp & 3;
         const int r = slice * 32 + lane;           // weight row inside the tile
-        const int n = n0 + r;
         bool ok = true;
         pdl_wait();     // nothing is written before the previous kernel has finished reading its inputs
         if (nkb > 0) ok = mbar_wait(&acc_bar, 0, bar_timeout);
@@ -180,15 +199,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 for (int i = 0; i < 16; ++i) { v[i] = 0; u[i] = 0; }
             }
             if (direct) {
+                float vals[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const int t = t0 + c + i;
-                    if (t < p.M && n < p.N) {
-                        float val = __uint_as_float(v[i]);
-                        if (GATED) { const float up = __uint_as_float(u[i]); val = val / (1.0f + __expf(-val)) * up; }
-                        gemm_store(p, t, n, val);
-                    }
+                    float val = __uint_as_float(v[i]);
+                    if (GATED) { const float up = __uint_as_float(u[i]); val = val / (1.0f + __expf(-val)) * up; }
+                    vals[i] = val;
                 }
+                store_chunk16(p, stage, t0 + c, n0, r, vals);
             } else {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -212,30 +230,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 __threadfence();
                 const long long tile_id = (long long)tile_m * gridDim.x + tile_n;
                 const float* base = p.workspace + (tile_id * p.splits) * S::ACC_COLS * BM;
-                // 8 token columns at a time: all their partial loads are in flight together
+                // 16 token columns at a time: all their partial loads are in flight together
 #pragma unroll 1
-                for (int c0 = 0; c0 < NTOK; c0 += 8) {
-                    if (t0 + c0 >= p.M) break;
-                    float g[8], up[8];
+                for (int c0 = 0; c0 < NTOK; c0 += 16) {
+                    float g[16], up[16];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) { g[j] = 0.f; up[j] = 0.f; }
-                    for (int s2 = 0; s2 < p.splits; ++s2) {
-                        float a[8], b[8];
+                    for (int j = 0; j < 16; ++j) { g[j] = 0.f; up[j] = 0.f; }
+                    if (t0 + c0 < p.M) {
+                        for (int s2 = 0; s2 < p.splits; ++s2) {
+                            float a[16], b[16];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            a[j] = __ldcg(base + ((long long)s2 * S::ACC_COLS + c0 + j) * BM + r);
-                            if (GATED) b[j] = __ldcg(base + ((long long)s2 * S::ACC_COLS + NTOK + c0 + j) * BM + r);
+                            for (int j = 0; j < 16; ++j) {
+                                a[j] = __ldcg(base + ((long long)s2 * S::ACC_COLS + c0 + j) * BM + r);
+                                if (GATED) b[j] = __ldcg(base + ((long long)s2 * S::ACC_COLS + NTOK + c0 + j) * BM + r);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) { g[j] += a[j]; if (GATED) up[j] += b[j]; }
                         }
+                        if (GATED) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) { g[j] += a[j]; if (GATED) up[j] += b[j]; }
+                            for (int j = 0; j < 16; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * up[j];
+                        }
                     }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int t = t0 + c0 + j;
-                        float val = g[j];
-                        if (GATED) val = val / (1.0f + __expf(-val)) * up[j];
-                        if (t < p.M && n < p.N) gemm_store(p, t, n, val);
-                    }
+                    store_chunk16(p, stage, t0 + c0, n0, r, g);     // rows past M are skipped inside
                 }
             }
         }
@@ -246,7 +263,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (wrote && threadIdx.x == 64) {
             __threadfence_system();
-            for (int j = 0; j < p.rs.world; ++j) red_release_sys_add_u32(p.rs.counters[j], 1u);
+            for (int j = 0; j < p.rs.world; ++j) red_relaxed_sys_add_u32(p.rs.counters[j], 1u);
         }
     }
     tc_fence_before();

@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(256) tp_norm_kernel(const TpNormParams p) {
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence_system();
-        for (int j = 0; j < p.world; ++j) red_release_sys_add_u32(p.ag_counter[j], 1u);
+        for (int j = 0; j < p.world; ++j) red_relaxed_sys_add_u32(p.ag_counter[j], 1u);
     }
 }
 
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(256) tp_argmax_kernel(const TpArgmaxParams p) 
         for (int w = 1; w < 8; ++w) best = best_s[w] > best ? best_s[w] : best;
         for (int j = 0; j < p.world; ++j) p.slots[j][(long long)p.rank * p.rows + row] = best;
         __threadfence_system();
-        for (int j = 0; j < p.world; ++j) red_release_sys_add_u32(p.counters[j], 1u);
+        for (int j = 0; j < p.world; ++j) red_relaxed_sys_add_u32(p.counters[j], 1u);
         int ok = 1;
         if (*(volatile unsigned int*)&p.status->status == SKY_STATUS_OK) {
             const unsigned want = tp_seq(p.seq) * p.seq.arrivals_per_use;

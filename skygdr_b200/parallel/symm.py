@@ -29,10 +29,11 @@ class SymmetricHeap:
         self._offsets: Dict[str, Tuple[int, int]] = {}
         self._top = 0
 
-    def alloc(self, name: str, nbytes: int, align: int = 256) -> int:
-        """Reserves a named range; every rank must make the same calls in the same order."""
+    def alloc(self, name: str, nbytes: int, align: int = 256, local: bool = True) -> int:
+        """Reserves a named range; every rank must make the same calls in the same order. ``local=False`` records a
+        range that exists only on peers with a larger heap (ranks with different roles may size their heaps differently)."""
         off = (self._top + align - 1) // align * align
-        assert off + nbytes <= self.nbytes, f"symmetric heap exhausted at {name}"
+        assert not local or off + nbytes <= self.nbytes, f"symmetric heap exhausted at {name}"
         self._offsets[name] = (off, nbytes)
         self._top = off + nbytes
         return off
