@@ -129,23 +129,27 @@ def main():
             core.handle_line("REGISTER kv_offload besteffort 0 kv_offload", 0)
 
             def control():
-                granted_base = 0
+                # The daemon core decides (unlimited / a byte grant for the offload); this loop turns "unlimited" into the
+                # offload's offered rate, since the emulated offload never has more than that to send.
+                granted, t_prev = 0.0, time.perf_counter()
                 while not stop.is_set():
+                    now = time.perf_counter()
+                    dt, t_prev = now - t_prev, now
                     tu, ou = t_page.read(), o_page.read()
                     core.report_usage(1, tu["consumed_bytes"], tu["completed_bytes"], in_flight["bytes"])
                     core.report_usage(2, ou["consumed_bytes"], ou["completed_bytes"], 1 << 40)
                     core.step_window(time.perf_counter_ns())
                     f = core.page_fields(2)
-                    if f["unlimited"]:
-                        # nothing to protect: the offload runs at its offered rate
-                        granted_base = max(granted_base, ou["consumed_bytes"]) + int(a.offload_gbps * 1e9 * 0.002)
-                        o_page.grant(granted_base, unlimited=False)
-                    else:
-                        granted_base = max(granted_base, int(f["granted_bytes"]))
-                        o_page.grant(min(granted_base, ou["consumed_bytes"] + int(a.offload_gbps * 1e9 * 0.004)), unlimited=False)
+                    rate = a.offload_gbps if f["unlimited"] else min(a.offload_gbps, f["budget_per_window"] / 0.002 / 1e9)
+                    granted = min(max(granted, float(ou["consumed_bytes"])) + rate * 1e9 * dt, ou["consumed_bytes"] + rate * 1e9 * 0.006 + (8 << 20))
+                    o_page.grant(int(granted), unlimited=False)
                     time.sleep(0.002)
 
             threading.Thread(target=control, daemon=True).start()
+        # one small prompt before the clock starts: library initialisation and allocator growth are not part of TTFT
+        wn = 4096
+        eng.prefill(torch.randint(0, cfg.vocab, (wn,), device=dev), [wn], torch.arange(1, geom.blocks_for(wn) + 1, dtype=torch.int32, device=dev).view(1, -1), pool=pool)
+        torch.cuda.synchronize(dev)
         dist.barrier()
         t0 = time.perf_counter()
         task.start()
@@ -190,6 +194,10 @@ def main():
         pool = ops.PagedKVPool(geom, a.slots * slot_blocks, "hnd", device=dev, data=heap.local_tensor("pool", (pool_bytes // 2,), torch.bfloat16))
         flags = heap.local_tensor("flags", (4096,), torch.int32)
         eng = Qwen3Decoder(cfg, weights, pool, max_batch=a.slots, max_ctx=a.max_in + 1024 + 16, attn_chunk=1024)
+        eng.set_batch(torch.zeros(1, dtype=torch.int32, device=dev), torch.full((1,), 8, dtype=torch.int32, device=dev),
+                      torch.zeros((1, 1), dtype=torch.int32, device=dev))
+        eng.step(b=1, max_ctx=64, advance=False)            # warm-up step on block 0
+        torch.cuda.synchronize(dev)
         dist.barrier()
         t0 = time.perf_counter()
         pending = {r["id"]: r for r in mine}

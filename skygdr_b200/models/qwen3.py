@@ -209,6 +209,23 @@ class Qwen3Decoder:
         self.graph.replay()
         return self.next_ids[:self.graph_batch]
 
+    def check_status(self) -> str:
+        """"OK", or the first non-OK status a kernel of this engine left behind (bounded waits that gave up)."""
+        from ..ops.flow import read_status
+        from ..ops.gemm import workspace_for
+
+        torch.cuda.synchronize(self.device)
+        for st in (read_status(self.attn.status), read_status(workspace_for(self.device).status)):
+            if st["status"] != 0:
+                return f"{st['status_name']}:{st['detail']}"
+        return "OK"
+
+    def bytes_per_step(self, ctx: torch.Tensor) -> int:
+        """HBM bytes one decode step must read on this GPU: the weights (the embedding table only by row) and the KV of ``ctx``."""
+        weights = self.w.nbytes() - self.w.embed.numel() * 2 + self.max_batch * self.cfg.hidden * 2
+        kv = int(ctx.sum()) * self.cfg.layers * 2 * self.pool.geom.kv_heads * self.cfg.head_dim * 2
+        return weights + kv
+
     # ---- prefill: whole prompts, token-major or head-major pool, returns last-position logits ----
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor, seq_lens: List[int], block_table: torch.Tensor, pool: Optional[PagedKVPool] = None,

@@ -212,20 +212,6 @@ def _bytes_per_step(cfg: Qwen3Config, w: Qwen3Weights, ctx: torch.Tensor, kv_hea
     return weights + kv
 
 
-def _single_check_status(self) -> str:
-    torch.cuda.synchronize(self.device)
-    from ..ops.gemm import workspace_for
-
-    for st in (read_status(self.attn.status), read_status(workspace_for(self.device).status)):
-        if st["status"] != 0:
-            return f"{st['status_name']}:{st['detail']}"
-    return "OK"
-
-
-Qwen3Decoder.check_status = _single_check_status
-Qwen3Decoder.bytes_per_step = lambda self, ctx: _bytes_per_step(self.cfg, self.w, ctx, self.cfg.kv_heads, self.max_batch)
-
-
 def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world: int, ctx: torch.Tensor, extra_tokens: int,
                         seed: int = 0, kv_init: str = "normal", attn_chunk: int = 1024, attn_impl: str = "tc"):
     """Weights shard, KV pool sized for ``ctx`` (+ ``extra_tokens`` of growth per sequence), randomly permuted block
