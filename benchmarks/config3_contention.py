@@ -57,7 +57,7 @@ class DecodeLoop:
             o += nb
         self.q = torch.randn((batch, 32, 128), dtype=torch.bfloat16, device=dev)
         self.out = torch.empty_like(self.q)
-        self.attn = ops.PagedAttention(dev, batch, 32, 8, max_ctx=max(ctx), chunk_tokens=1024)
+        self.attn = ops.PagedAttention(dev, batch, 32, 8, max_ctx=max(ctx), chunk_tokens=1024, impl="tc")
         self.bytes_per_step = sum(ctx) * 8 * 128 * 2 * 2 * layers
         self.stream = torch.cuda.Stream(dev, priority=-1)
         self.max_ctx = max(ctx)
@@ -157,12 +157,13 @@ def main():
         if scheduled:
             cfg = ctl.DaemonConfig()
             cfg.page_dir, cfg.capacity_gbps, cfg.window_ns, cfg.policy = "", 6400.0, 2_000_000, "target_track"
+            cfg.lease_ns = 3600 * 10**9
             cfg.pcfg.enter_ratio, cfg.pcfg.exit_ratio, cfg.pcfg.util_threshold_pct = 0.97, 0.99, 0.0
             cfg.pcfg.min_be_fraction = 0.01
             core = ctl.DaemonCore(cfg)
-            core.handle_line(f"REGISTER decode high {base_kv_gbs * 0.98:.1f} other", 0)
-            core.handle_line(f"REGISTER kv_transfer normal {a.transfer_target_gbps} kv_transfer", 0)
-            core.handle_line("REGISTER memhog besteffort 0 best_effort", 0)
+            core.handle_line(f"REGISTER decode high {base_kv_gbs * 0.98:.1f} other", time.perf_counter_ns())
+            core.handle_line(f"REGISTER kv_transfer normal {a.transfer_target_gbps} kv_transfer", time.perf_counter_ns())
+            core.handle_line("REGISTER memhog besteffort 0 best_effort", time.perf_counter_ns())
 
             def control_loop():
                 # mirror the daemon's pages <-> the device-visible pages of the two kernels, every window

@@ -123,10 +123,11 @@ def main():
             pacer = None
             dc = ctl.DaemonConfig()
             dc.page_dir, dc.capacity_gbps, dc.window_ns, dc.policy = "", a.offload_gbps + 40.0, 2_000_000, "target_track"
+            dc.lease_ns = 3600 * 10**9          # in-process flows: no lease renewals needed for the length of a run
             dc.pcfg.util_threshold_pct = 0.0
             core = ctl.DaemonCore(dc)
-            core.handle_line("REGISTER kv_transfer high 40 kv_transfer", 0)
-            core.handle_line("REGISTER kv_offload besteffort 0 kv_offload", 0)
+            core.handle_line("REGISTER kv_transfer high 40 kv_transfer", time.perf_counter_ns())
+            core.handle_line("REGISTER kv_offload besteffort 0 kv_offload", time.perf_counter_ns())
 
             def control():
                 # The daemon core decides (unlimited / a byte grant for the offload); this loop turns "unlimited" into the

@@ -294,3 +294,82 @@ def test_silu_embedding_argmax(ops):
     got = ops.argmax(logits)
     assert torch.equal(got.long(), logits.float().argmax(-1)) or int(got[3]) == 77
     assert int(got[3]) == 77
+
+
+def test_peer_wait_runs_out_and_returns_a_status(ops):
+    """A wait on a peer's arrival counter that nothing will ever advance must give up at its deadline, leave
+    TIMEOUT_FLAG in the status block and return normally: the context stays usable afterwards."""
+    from skygdr_b200._ext import load
+
+    C = load()
+    rows, hidden = 4, 1024
+    resid = torch.randn((rows, hidden), dtype=torch.bfloat16, device="cuda")
+    w = torch.ones(hidden, dtype=torch.bfloat16, device="cuda")
+    rs_buf = torch.zeros((1, rows, hidden), dtype=torch.bfloat16, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")          # stays 0: the "peer" never arrives
+    step = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ag = torch.zeros((rows, hidden), dtype=torch.bfloat16, device="cuda")
+    ag_ctr = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = ops.new_status("cuda")
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    C.tp_norm(rs_buf.data_ptr(), counter.data_ptr(), (step.data_ptr(), 1, 0, 5), resid, w, [ag.data_ptr()], [ag_ctr.data_ptr()], 0, 1e-6,
+              20_000_000, status)                                          # 20 ms deadline
+    t1.record()
+    torch.cuda.synchronize()
+    st = ops.read_status(status)
+    assert st["status_name"] == "TIMEOUT_FLAG" and 100 <= st["detail"] < 100 + rows
+    assert 15.0 < t0.elapsed_time(t1) < 500.0
+    assert int(ag_ctr.item()) == rows                                      # it still finished its own work and signalled
+    # the context is alive: an ordinary kernel runs and gives the right answer
+    x = torch.randn((8, 512), dtype=torch.bfloat16, device="cuda")
+    y = ops.rmsnorm(x, torch.ones(512, dtype=torch.bfloat16, device="cuda"), 1e-6)
+    xf = x.float()
+    assert torch.allclose(y.float(), xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6), atol=2e-2, rtol=2e-2)
+    # once a status is set, later waits of the same engine are skipped instead of each burning a deadline
+    t0.record()
+    C.tp_norm(rs_buf.data_ptr(), counter.data_ptr(), (step.data_ptr(), 1, 0, 5), resid, w, [ag.data_ptr()], [ag_ctr.data_ptr()], 0, 1e-6,
+              20_000_000, status)
+    t1.record()
+    torch.cuda.synchronize()
+    assert t0.elapsed_time(t1) < 10.0
+
+
+def test_gemm_tile_and_split_choices_agree_with_reference(ops):
+    """Every (token tile, split) the cost model may choose gives the same product."""
+    torch.manual_seed(9)
+    M, N, K = 128, 768, 4096
+    x = torch.randn((M, K), dtype=torch.bfloat16, device="cuda")
+    w = (torch.randn((N, K), dtype=torch.bfloat16, device="cuda") / 64).contiguous()
+    ref = x.float() @ w.float().t()
+    for ntok, splits in [(16, 1), (32, 5), (64, 2), (128, 1), (128, 3), (32, 1)]:
+        y = ops.gemm(x, w, splits=splits, ntok=ntok)
+        assert (y.float() - ref).abs().max() < 2e-2 * float(ref.abs().max()), (ntok, splits)
+    nt, sp = ops.pick_config(M, N, K, 148)
+    assert nt in (16, 32, 64, 128) and 1 <= sp <= 16
+
+
+def test_cli_programs_run(ops):
+    """The command-line programs print the reference's summary lines."""
+    import re
+    import subprocess
+    import sys
+
+    def run(mod, *args):
+        r = subprocess.run([sys.executable, "-m", f"skygdr_b200.cli.{mod}", *args], capture_output=True, text=True, timeout=180)
+        assert r.returncode == 0, r.stdout + r.stderr
+        return r.stdout
+
+    out = run("gpu_memhog", "--gb=1", "--op=copy", "--seconds=0", "--iters=3")
+    assert re.search(r"\[memhog\] bytes=\d+ kernel_s=[0-9.]+ bw_gib_s=[0-9.]+", out)
+    out = run("decode_hbm_stress", "0", "1024", "5")
+    assert re.search(r"HBM stress done: approx [0-9.]+ GiB in [0-9.]+ s = [0-9.]+ GiB/s", out)
+    out = run("gpu_pcie_memcpy", "--seconds=0", "--total_bytes=256M", "--chunk_mb=16", "--streams=2", "--batch=1", "--inflight=2", "--dir=h2d",
+              "--report_ms=50")
+    assert "[pcie] t=" in out and re.search(r"\[pcie\] done dir=h2d completed_bytes=268435456", out)
+    out = run("kv_nvlink_transfer", "0", "0", "256", "3", "--layers", "4")
+    assert re.search(r"KV transfer done: [0-9.]+ GiB in [0-9.]+ s = [0-9.]+ GiB/s", out)
+    out = run("kv_nvlink_transfer_trace", "--src", "0", "--dst", "0", "--iters", "5", "--dist", "computed", "--layers", "4", "--max-tokens", "4096")
+    assert "Trace-shaped KV transfer done:" in out and "transfers: 5" in out
+    out = run("decode_kvcache_stress", "--layers", "2", "--context", "2048", "--gen", "4", "--batch", "4")
+    assert "seq-tokens/s:" in out and "KV bandwidth:" in out
