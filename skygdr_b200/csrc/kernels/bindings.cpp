@@ -153,7 +153,8 @@ static void kv_transfer(torch::Tensor src_pool, std::vector<uint64_t> dst_ptrs, 
                         std::vector<uint64_t> done_flag_ptrs, torch::Tensor src_blocks, torch::Tensor dst_blocks, int layers, int heads,
                         int block_tokens, int head_dim, std::vector<int64_t> src_strides, std::vector<int64_t> dst_strides,
                         int heads_per_dst, bool replicate, bool fp8, bool keep_layout, int pages_per_chunk, int ctas, uint64_t credit_dev_ptr,
-                        uint64_t consumed_base, uint64_t max_wait_ns, uint64_t first_chunk, uint32_t done_value, torch::Tensor status) {
+                        uint64_t consumed_base, uint64_t max_wait_ns, uint64_t first_chunk, uint32_t done_value, torch::Tensor status,
+                        bool use_tma) {
     TORCH_CHECK(dst_ptrs.size() >= 1 && dst_ptrs.size() <= (size_t)KV_MAX_DST, "1..8 destinations");
     TORCH_CHECK(src_strides.size() == 3 && dst_strides.size() == 3, "strides are (block, layer, kv)");
     TORCH_CHECK(src_blocks.numel() == dst_blocks.numel(), "block lists differ in length");
@@ -181,7 +182,8 @@ static void kv_transfer(torch::Tensor src_pool, std::vector<uint64_t> dst_ptrs, 
     p.consumed_base = consumed_base; p.max_wait_ns = max_wait_ns; p.first_chunk = first_chunk;
     p.status = status_ptr(status);
     if (p.n_pairs == 0) return;
-    SKY_CUDA_CHECK(launch_kv_transfer(p, ctas, cur_stream()));
+    if (use_tma) SKY_CUDA_CHECK(launch_kv_transfer_tma(p, src_pool.numel(), ctas, cur_stream()));
+    else SKY_CUDA_CHECK(launch_kv_transfer(p, ctas, cur_stream()));
 }
 
 // ---- memhog ----

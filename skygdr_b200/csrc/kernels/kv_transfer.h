@@ -34,5 +34,7 @@ struct KvTransferParams {
 };
 
 cudaError_t launch_kv_transfer(const KvTransferParams& p, int ctas, cudaStream_t stream);
+// All-TMA variant for bf16 pages (kv_transfer_tma.cu). pool_elems: elements of the whole source pool allocation.
+cudaError_t launch_kv_transfer_tma(const KvTransferParams& p, long long pool_elems, int ctas, cudaStream_t stream);
 
 }  // namespace sky

@@ -39,13 +39,19 @@ class RemotePool:
 
 class KvTransferFlow:
     def __init__(self, device, page: Optional[CreditPage] = None, ctas: Optional[int] = None, pages_per_chunk: int = 8,
-                 max_wait_ms: float = 2.0):
+                 max_wait_ms: float = 2.0, method: str = "auto"):
+        """method: "tma" (copy hardware does gather, layout change and peer write; bf16 only), "simt" (register path; also
+        fp8 packing and same-layout copies), or "auto" (tma whenever it applies)."""
+        assert method in ("auto", "tma", "simt")
+        self.method = method
+        self._ctas_given = ctas is not None
         self._C = load()
         self.device = torch.device(device)
         self.page = page
         self.status = new_status(self.device)
         self.consumed = 0
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.sms = sms
         self.ctas = ctas or 2 * sms
         self.pages_per_chunk = pages_per_chunk
         self.max_wait_ns = int(max_wait_ms * 1e6)
@@ -61,13 +67,17 @@ class KvTransferFlow:
         heads_per_dst = g.kv_heads if replicate else g.kv_heads // len(dsts)
         for d in dsts:
             assert replicate or keep_layout or d.kv_heads == heads_per_dst, "destination head count does not match the scatter"
+        use_tma = self.method != "simt" and not fp8 and not keep_layout and g.kv_heads <= 8 and g.head_dim == 128 and src.data.is_contiguous()
+        assert use_tma or self.method != "tma", "the TMA variant moves contiguous bf16 pools of <= 8 heads without fp8 packing"
+        if use_tma and ctas is None and not self._ctas_given:
+            ctas = self.sms                      # one driving thread and a 192 KB ring per SM
         self.seq += 1
         self._C.reset_status(self.status)
         self._C.kv_transfer(
             src.data, [d.ptr for d in dsts], [d.scale_ptr for d in dsts], [d.done_flag_ptr if signal else 0 for d in dsts],
             src_blocks, dst_blocks, g.layers, g.kv_heads, g.block_tokens, g.head_dim, list(src.strides), list(dsts[0].strides),
             heads_per_dst, replicate, fp8, keep_layout, self.pages_per_chunk, ctas or self.ctas,
-            self.page.dev_ptr if self.page else 0, self.consumed, self.max_wait_ns, first_chunk, self.seq, self.status)
+            self.page.dev_ptr if self.page else 0, self.consumed, self.max_wait_ns, first_chunk, self.seq, self.status, use_tma)
         self._last = (src, dsts, src_blocks, dst_blocks, replicate, fp8, keep_layout, ctas)
 
     def result(self) -> Dict[str, int]:

@@ -26,13 +26,14 @@ def _pools(ops, n_src=40, n_dst=48, layers=3, heads=8, seed=0):
     return g, src, dst
 
 
-def test_kv_transfer_exact(ops):
+@pytest.mark.parametrize("method", ["simt", "tma"])
+def test_kv_transfer_exact(ops, method):
     g, src, dst = _pools(ops)
     n = 23
     sb = torch.randperm(src.num_blocks, device="cuda")[:n].int()
     db = torch.randperm(dst.num_blocks, device="cuda")[:n].int()
     flag = torch.zeros(1, dtype=torch.int32, device="cuda")
-    flow = ops.KvTransferFlow("cuda", pages_per_chunk=4)
+    flow = ops.KvTransferFlow("cuda", pages_per_chunk=4, method=method)
     flow.transfer(src, [ops.RemotePool.of(dst, flag)], sb, db)
     st = flow.result()
     assert st["status"] == 0 and st["cursor"] == 2**64 - 1
@@ -44,13 +45,14 @@ def test_kv_transfer_exact(ops):
     assert float(dst.data[untouched].abs().sum()) == 0.0
 
 
-def test_kv_transfer_scatter_and_replicate(ops):
+@pytest.mark.parametrize("method", ["simt", "tma"])
+def test_kv_transfer_scatter_and_replicate(ops, method):
     g, src, _ = _pools(ops, layers=2)
     gd = ops.KVGeometry(layers=2, kv_heads=2)
     parts = [ops.PagedKVPool(gd, 16, "hnd") for _ in range(4)]
     sb = torch.arange(5, 14, device="cuda").int()
     db = torch.arange(0, 9, device="cuda").int()
-    flow = ops.KvTransferFlow("cuda")
+    flow = ops.KvTransferFlow("cuda", method=method)
     flow.transfer(src, [ops.RemotePool.of(p) for p in parts], sb, db)
     assert flow.result()["status"] == 0
     for i, p in enumerate(parts):
@@ -85,7 +87,8 @@ def test_kv_transfer_fp8_pack(ops):
     assert (q != want_q).float().mean() < 1e-3
 
 
-def test_kv_transfer_credit_yield_and_resume(ops):
+@pytest.mark.parametrize("method", ["simt", "tma"])
+def test_kv_transfer_credit_yield_and_resume(ops, method):
     g, src, dst = _pools(ops, layers=2)
     n = 20
     sb = torch.arange(n, device="cuda").int()
@@ -93,7 +96,7 @@ def test_kv_transfer_credit_yield_and_resume(ops):
     page = ops.CreditPage(flow_id=7, unlimited=False)
     total = ops.link_bytes(g, n)
     page.grant(total // 2)                       # nothing will ever add to this: a host-made stall
-    flow = ops.KvTransferFlow("cuda", page=page, pages_per_chunk=2, max_wait_ms=1.0)
+    flow = ops.KvTransferFlow("cuda", page=page, pages_per_chunk=2, max_wait_ms=1.0, method=method)
     flow.transfer(src, [ops.RemotePool.of(dst)], sb, db)
     st = flow.result()
     assert st["status_name"] == "YIELD_CREDIT"
