@@ -84,6 +84,20 @@ def build_bin(force: bool = False) -> Path:
     return BIN
 
 
+def build_sanitized(kind: str = "address") -> Path:
+    """fabricd with a sanitizer: ``address`` = ASan + UBSan, ``thread`` = TSan. Used by the CPU tests to run a
+    daemon session (connections, window timer, lease expiry) under the sanitizer; the reference has no such runs."""
+    assert kind in ("address", "thread")
+    BIN.mkdir(exist_ok=True)
+    out = BIN / f"fabricd_{'asan' if kind == 'address' else 'tsan'}"
+    srcs = [CTL / "fabricd.cc"]
+    hdrs = sorted(CTL.glob("*.hpp")) + sorted(CTL.glob("*.h"))
+    if _newer(out, srcs + hdrs):
+        flags = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer"] if kind == "address" else ["-fsanitize=thread"]
+        _run(["g++", "-std=c++17", "-O1", "-g", *flags, f"-I{CTL}", str(srcs[0]), "-o", str(out), "-ldl", "-pthread"])
+    return out
+
+
 def cuda_path() -> Path:
     return PKG / ("_C" + _ext_suffix())
 
@@ -112,7 +126,6 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
         extra_cuda_cflags=["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xptxas", "-v", *NVCC_ARCH,
                            "--expt-relaxed-constexpr"],
         extra_include_paths=[str(KERNELS), str(CTL)],
-        extra_ldflags=["-lcuda"] if False else [],
         build_directory=str(build_dir),
         verbose=verbose,
         is_python_module=False,

@@ -1,0 +1,35 @@
+import pytest
+
+from skygdr_b200.utils.config import RuntimeConfig
+
+
+def test_round_trip_overrides_and_env():
+    c = RuntimeConfig()
+    c2 = RuntimeConfig.from_json(c.to_json())
+    assert c2 == c and c2.flows[1].name == "kv_offload"
+    c2.override("window_us=1000", "policy.enter_ratio=0.7", "policy.name=ladder", "control.port=9000")
+    assert c2.window_us == 1000 and c2.policy.enter_ratio == 0.7 and c2.policy.name == "ladder" and c2.control.port == 9000
+    with pytest.raises(KeyError):
+        c2.override("nope=1")
+    with pytest.raises(KeyError):
+        c2.override("policy=1")
+    with pytest.raises(KeyError):
+        RuntimeConfig.from_dict({"bogus": 1})
+    c3 = RuntimeConfig().from_env({"SKYGDR_CTRL_PORT": "7001", "SKYGDR_CTRL_LOW_SLEEP_US": "250", "SKYGDR_DAEMON": "10.0.0.1:7171"})
+    assert c3.control.port == 7001 and c3.control.low_sleep_us == 250 and (c3.daemon_host, c3.daemon_port) == ("10.0.0.1", 7171)
+    args = c2.daemon_args()
+    assert args[args.index("--policy") + 1] == "ladder" and args[args.index("--window_us") + 1] == "1000"
+
+
+def test_daemon_accepts_the_generated_arguments(tmp_path):
+    from skygdr_b200.control import FabricClient, FabricDaemon
+    from skygdr_b200.control.daemon import free_port
+
+    c = RuntimeConfig().override("policy.name=ladder", "window_us=2000")
+    c.daemon_port = free_port()
+    extra = c.daemon_args()[2:]          # the launcher passes --port itself
+    # the launcher sets policy/window/capacity/lease too; later flags win
+    with FabricDaemon(port=c.daemon_port, extra=extra) as d:
+        with FabricClient(port=d.port) as cl:
+            assert cl.request("POLICY") == "OK policy=ladder"
+            assert cl.request("WINDOW") == "OK window_us=2000"
