@@ -66,14 +66,18 @@ struct GemmSmem {
     static constexpr int W_BYTES = BM * BK * 2;
     static constexpr int X_BYTES = NTOK * BK * 2;
     static constexpr int STAGE_BYTES = W_BYTES * (GATED ? 2 : 1) + X_BYTES;
-    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    // Two CTAs per SM where three stages fit in half an SM's shared memory: while one CTA is in its prologue or
+    // epilogue the other keeps the SM's share of the weight stream going.
+    static constexpr bool TWO_PER_SM = 3 * STAGE_BYTES <= 104 * 1024;
+    static constexpr int BUDGET = TWO_PER_SM ? 104 * 1024 : 200 * 1024;
+    static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024;  // + alignment slack
     static constexpr int ACC_COLS = NTOK * (GATED ? 2 : 1);
     static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;
 };
 
 template <int NTOK, bool GATED>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, (GemmSmem<NTOK, GATED>::TWO_PER_SM ? 2 : 1))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     using S = GemmSmem<NTOK, GATED>;
     extern __shared__ unsigned char smem_raw[];

@@ -26,10 +26,11 @@ def pick_splits(M: int, N: int, K: int, sms: int, gated: bool = False) -> int:
 def pick_config(M: int, N: int, K: int, sms: int, gated: bool = False, fixed_ntok: int = 0) -> Tuple[int, int]:
     """(token tile, split-K factor) for y[M][N] = x[M][K] w[N][K]^T with small M.
 
-    One CTA holds one SM (its pipeline takes ~200 KB of shared memory), so the time is about
-    waves x (fixed cost + bytes per CTA / per-SM stream rate), bounded below by total bytes over HBM rate.
-    Constants are measured on B200: ~6 us of prologue + epilogue per CTA, ~55 GB/s per SM, 5.5 TB/s per GPU; a split
-    adds its fp32 partial (written, then re-read by the last CTA of the tile)."""
+    The time is about waves x (fixed cost per CTA + bytes per CTA / stream rate of a CTA), bounded below by total bytes
+    over the HBM rate; a split adds its fp32 partial (written, then re-read by the last CTA of the tile). A pipeline of
+    small stages fits two CTAs on an SM, which then share the SM's stream rate. The constants minimise the regret
+    against a measured sweep of the decoder's shapes at 1, 2 and 8 tensor-parallel ranks on B200 (token tiles 16-128,
+    1-16 splits): 2-3 us fixed per CTA, 55 GB/s for a CTA alone on its SM, 45 GB/s each for two, 5.5 TB/s per GPU."""
     wrows = 2 if gated else 1
     kb = K // 64
     cands = [fixed_ntok] if fixed_ntok else [n for n in (16, 32, 64, 128, 256) if n >= 16 and (n < 2 * M or n == 16) and not (gated and n > 128)]
@@ -42,14 +43,19 @@ def pick_config(M: int, N: int, K: int, sms: int, gated: bool = False, fixed_nto
                 break
             per = (kb + s - 1) // s
             s_eff = (kb + per - 1) // per
+            if s_eff != s:
+                continue                               # the same partition as a smaller s
             ctas = tiles_n * tiles_m * s_eff
-            waves = (ctas + sms - 1) // sms
-            bytes_cta = per * (128 * 64 * 2 * wrows + ntok * 64 * 2)
+            stage = 128 * 64 * 2 * wrows + ntok * 64 * 2
+            two = 3 * stage <= 104 * 1024              # the kernel fits two CTAs per SM for small stages
+            slots = sms * (2 if two else 1)
+            waves = (ctas + slots - 1) // slots
+            shared = two and ctas > sms                # two co-resident CTAs share the SM's stream rate
             part = ntok * 128 * 4 * wrows
-            t_cta = 6.0 + bytes_cta / 55e3 + (part / 100e3 + 1.0 + s_eff * part / 200e3 if s_eff > 1 else 0.0)
+            t_cta = (2.0 if shared else 3.0) + per * stage / (45e3 if shared else 55e3) + (1.0 + s_eff * part / 50e3 if s_eff > 1 else 0.0)
             hbm = (tiles_n * 128 * K * 2 * wrows + M * K * 2) / 5.5e6
             t = max(waves * t_cta, hbm)
-            if t < best_t * 0.92:                 # simpler shapes come first; a rival must be clearly better
+            if t < best_t * 0.92:                      # simpler shapes come first; a rival must be clearly better
                 best, best_t = (ntok, s_eff), t
     return best
 

@@ -1,0 +1,93 @@
+"""Host-side helpers of the ops layer, on CPU tensors: pool geometry, reference gathers, fp8 packing oracle, the GEMM
+shape chooser (with a stubbed extension), the attention oracle."""
+import math
+import types
+
+import pytest
+import torch
+
+
+def test_geometry_and_pool_views():
+    from skygdr_b200.ops.kv_cache import KVGeometry, PagedKVPool
+
+    g = KVGeometry()
+    assert g.bytes_per_token() == 147456 and g.page_elems == 16 * 8 * 128 and g.block_elems == 36 * 2 * g.page_elems
+    assert g.blocks_for(1) == 1 and g.blocks_for(16) == 1 and g.blocks_for(17) == 2
+    small = KVGeometry(layers=2, kv_heads=2)
+    nhd = PagedKVPool(small, 5, "nhd", device="cpu", dtype=torch.float32)
+    hnd = PagedKVPool(small, 5, "hnd", device="cpu", dtype=torch.float32)
+    assert nhd.data.shape == (5, 2, 2, 16, 2, 128) and hnd.data.shape == (5, 2, 2, 2, 16, 128)
+    assert nhd.strides == (small.block_elems, 2 * small.page_elems, small.page_elems) and hnd.head_stride == 16 * 128
+    nhd.data.normal_()
+    hnd.data.copy_(nhd.data.permute(0, 1, 2, 4, 3, 5))
+    blocks = torch.tensor([3, 0, 4])
+    assert torch.equal(nhd.gather_reference(blocks), hnd.gather_reference(blocks))
+
+
+def test_reference_transfer_and_link_bytes():
+    from skygdr_b200.ops.kv_cache import KVGeometry, PagedKVPool
+    from skygdr_b200.ops.kv_transfer import link_bytes, reference_transfer
+
+    g = KVGeometry(layers=1, kv_heads=4)
+    src = PagedKVPool(g, 3, "nhd", device="cpu", dtype=torch.float32)
+    src.data.copy_(torch.arange(src.data.numel(), dtype=torch.float32).view_as(src.data))
+    out = reference_transfer(src, torch.tensor([2, 0]), slice(1, 3))
+    assert out.shape == (2, 1, 2, 2, 16, 128)
+    assert torch.equal(out[0, 0, 1, 0, 5], src.data[2, 0, 1, 5, 1])          # head 1 of the slice = source head 1
+    assert link_bytes(g, 10) == 10 * g.block_elems * 2
+    assert link_bytes(g, 10, n_dst=3, replicate=True) == 3 * link_bytes(g, 10)
+    assert link_bytes(g, 10, fp8=True) == 10 * (g.block_elems + g.block_elems // 32)
+
+
+def test_fp8_mx_oracle_properties():
+    from skygdr_b200.ops.kv_transfer import fp8_mx_reference
+
+    torch.manual_seed(0)
+    x = torch.randn(4, 64) * torch.tensor([1e-3, 1.0, 50.0, 1e4])[:, None]
+    x[0, :32] = 0
+    q, s = fp8_mx_reference(x.bfloat16())
+    assert q.shape == (4, 64) and s.shape == (4, 2) and q.dtype == torch.uint8
+    back = q.view(torch.float8_e4m3fn).float() * torch.exp2(s.float() - 127).repeat_interleave(32, -1)
+    assert int(s[0, 0]) == 0 and float(back[0, :32].abs().max()) == 0.0        # all-zero group: smallest scale, zeros
+    rel = (back - x.bfloat16().float()).abs().max(-1).values / x.abs().max(-1).values
+    assert float(rel.max()) < 0.07                                              # e4m3 keeps 3 mantissa bits
+    scaled = x.bfloat16().float().view(4, 2, 32) * torch.exp2(127 - s.float())[..., None]
+    assert float(scaled.abs().max()) <= 448.0                                   # nothing saturates under the chosen scale
+    assert float(scaled.view(4, 2, 32)[1:].abs().amax(-1).min()) > 224.0        # ... and the scale is the smallest such power of two
+
+
+def test_pick_config_rules(monkeypatch):
+    import importlib
+
+    g = importlib.import_module("skygdr_b200.ops.gemm")           # the package re-exports a function of the same name
+
+    monkeypatch.setattr(g, "load", lambda: types.SimpleNamespace(
+        gemm_pick_ntok=lambda M, gated: 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128))
+    for M, N, K, gated in [(16, 6144, 4096, False), (16, 12288, 4096, True), (128, 768, 4096, False), (128, 4096, 512, False),
+                           (16, 151936, 4096, False), (1, 128, 64, False), (300, 1024, 2048, False)]:
+        ntok, s = g.pick_config(M, N, K, 148, gated)
+        assert ntok in (16, 32, 64, 128, 256) and 1 <= s <= 16
+        assert s == 1 or (K // 64) // s >= 4                                    # a split keeps at least 4 k-blocks
+        assert not (gated and ntok > 128)
+    assert g.pick_config(16, 151936, 4096, 148)[1] == 1                          # many tiles: never split
+    assert g.pick_config(128, 768, 4096, 148)[1] > 1                             # six tiles: must split
+    assert g.pick_config(16, 6144, 4096, 148, fixed_ntok=16)[0] == 16
+
+
+def test_attention_oracle_matches_dense_softmax():
+    from skygdr_b200.ops.attention import paged_attn_reference
+    from skygdr_b200.ops.kv_cache import KVGeometry, PagedKVPool
+
+    torch.manual_seed(1)
+    g = KVGeometry(layers=1, kv_heads=2)
+    pool = PagedKVPool(g, 6, "hnd", device="cpu", dtype=torch.float32)
+    pool.data.normal_()
+    table = torch.tensor([[4, 1, 0], [2, 5, 3]], dtype=torch.int32)
+    ctx = torch.tensor([20, 48], dtype=torch.int32)
+    q = torch.randn(2, 4, 128)
+    out = paged_attn_reference(q, pool, 0, table, ctx)
+    b, h = 0, 3
+    k = torch.cat([pool.data[4, 0, 0, 1], pool.data[1, 0, 0, 1]])[:20]          # query head 3 reads kv head 1
+    v = torch.cat([pool.data[4, 0, 1, 1], pool.data[1, 0, 1, 1]])[:20]
+    p = torch.softmax(q[b, h] @ k.t() / math.sqrt(128), -1)
+    assert torch.allclose(out[b, h], p @ v, atol=1e-5)
