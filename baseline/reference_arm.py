@@ -39,7 +39,7 @@ def run(args, rank: int) -> dict:
                "--report-every", str(max(1, args.steps))]
         r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
         text = r.stdout + r.stderr
-        m = re.search(r"seq-tokens/s[^0-9]*([0-9.]+)", text) or re.search(r"tokens/s[^0-9]*([0-9.]+)", text)
+        m = re.search(r"sequence-throughput:\s*([0-9.]+)", text)
         out["nearest"] = {
             "program": "llm_problem_analysis/decode_vllm_kvcache_hbm_stress.cu (built unmodified, sm_100)",
             "what": "batched KV scan only: fp32 KV, fixed context, no block table, no weights, no sampling",

@@ -213,3 +213,74 @@ def test_bandwidth_join_and_clock_offset_units():
     ctrl = [{"ts_unix_ms": "1000", "mode": "HIGH"}, {"ts_unix_ms": "2000", "mode": "LOW1"}, {"ts_unix_ms": "3000", "mode": "LOW2"}]
     bg = [{"ts_unix_ms": "6000", "control_mode": "HIGH"}, {"ts_unix_ms": "7010", "control_mode": "LOW1"}, {"ts_unix_ms": "8020", "control_mode": "LOW2"}]
     assert estimate_clock_offset_ms(ctrl, bg) == pytest.approx(5015, abs=6)
+
+
+def _fake_ref_bin(tmp_path):
+    """Stand-ins for the four reference programs: print the reference's own summary lines (text taken from the
+    published result files' formats) after a short sleep, so that the harness has something to overlap and scrape."""
+    d = tmp_path / "refbin"
+    d.mkdir()
+    bodies = {
+        "decode_hbm_stress": 'echo "gpu=$1 name=FAKE working_set=$2 MiB iters=$3"; sleep 0.3; echo "HBM stress done: approx 48.00 GiB in 0.300 s = 160.00 GiB/s"',
+        "kv_nvlink_transfer": 'echo "src_gpu=$1 dst_gpu=$2 size=$3 MiB iters=$4"; sleep 0.1; echo "KV transfer done: 4.00 GiB in 0.100 s = 40.00 GiB/s"',
+        "kv_nvlink_transfer_trace": 'echo "src_gpu=0 dst_gpu=1"; echo "Trace-shaped KV transfer done:"; echo "  transfers: 8"; echo "  total:     1.00 GiB"; echo "  time:      0.010 s"; echo "  bw:        100.00 GiB/s"',
+        "decode_vllm_kvcache_hbm_stress": 'echo "GPU: 1 FAKE"; sleep 0.2; echo "Time: 0.200 s"; echo "Throughput: 5.00 tokens/s"; echo "Effective sequence-throughput: 80.00 seq-tokens/s"; echo "Approx bandwidth:             123.00 GiB/s"',
+    }
+    bodies["decode_transformer_kvcache_stress"] = bodies["decode_vllm_kvcache_hbm_stress"]
+    for name, body in bodies.items():
+        p = d / name
+        p.write_text("#!/bin/sh\n" + body + "\n")
+        p.chmod(0o755)
+    return d
+
+
+def test_colocation_harness_phases_and_summaries(tmp_path, monkeypatch):
+    """The harness runs workload alone, competitor alone, both overlapped, and writes the reference's result
+    layout (llm_problem_analysis/final_run_vllm_decode_kv_colocation_bench.sh:251-419)."""
+    from skygdr_b200.cli import colocation_bench as cb
+
+    monkeypatch.setenv("SKYGDR_REF_BIN", str(_fake_ref_bin(tmp_path)))
+    monkeypatch.setenv("ENABLE_DMON", "0")
+    monkeypatch.setenv("START_DELAY_SEC", "0.05")
+    monkeypatch.setenv("KV_DISTS", "computed input")
+    monkeypatch.setenv("REPEATS", "2")
+    out = tmp_path / "res"
+    assert cb.main(["vllm_decode", "--impl", "reference", "--out-dir", str(out)]) == 0
+    names = sorted(p.name for p in out.iterdir())
+    for want in ("env_info.txt", "summary.txt", "compact_summary.txt", "warmup_decode.log", "decode_vllm_alone_r1.log", "kv_input_alone_r2.log",
+                 "decode_vllm_overlap_computed_r2.log", "kv_computed_overlap_r1.log"):
+        assert want in names, (want, names)
+    s = (out / "summary.txt").read_text()
+    assert "Optimized vLLM-like decode + trace-shaped KV transfer benchmark" in s and "Repeat 2" in s
+    assert "================ decode_vllm overlap, dist=input, repeat=1 ================" in s
+    assert s.count("Effective sequence-throughput: 80.00 seq-tokens/s") == 2 * (1 + 2)      # alone + one per dist, per repeat
+    c = (out / "compact_summary.txt").read_text()
+    assert "Compact KV transfer summary" in c and "kv_computed_alone_r1.log:  bw:        100.00 GiB/s" in c
+    assert "REPEATS=2" in (out / "env_info.txt").read_text()
+
+    out2 = tmp_path / "res2"
+    monkeypatch.delenv("KV_DISTS")
+    assert cb.main(["hbm_kv", "--impl", "reference", "--preset", "stress", "--out-dir", str(out2)]) == 0
+    s = (out2 / "summary.txt").read_text()
+    assert "KV_ITERS=3000" in s and "HBM_WORKING_SET_MIB=32768" in s                       # the preset's values
+    assert s.index("decode_hbm_stress alone") < s.index("kv_nvlink_transfer alone") < s.index("decode_hbm_stress overlap")
+    assert "working_set=32768 MiB" in s and "= 40.00 GiB/s" in s
+
+    out3 = tmp_path / "res3"
+    assert cb.main(["multi_kv", "--impl", "reference", "--out-dir", str(out3)]) == 0
+    assert sorted(p.name for p in out3.glob("kv_*.log")) == [f"kv_{i}.log" for i in range(4)]
+
+
+def test_colocation_harness_plans_our_programs(tmp_path, monkeypatch):
+    from skygdr_b200.cli import colocation_bench as cb
+
+    monkeypatch.setenv("LAYERS", "12")                                                      # the environment beats the preset
+    cfg = cb.resolve_config("trace_decode", "real_trace")
+    assert cfg["LAYERS"] == "12" and cfg["FFN_DIM"] == "16384" and cfg["KV_ITERS_CACHED"] == "2000"
+    h = cb.Harness("trace_decode", cfg, str(tmp_path / "plan"), "ours", dry_run=True)
+    assert h.main() == 0
+    flat = [" ".join(c) for c in h.commands]
+    assert any("skygdr_b200.cli.decode_kvcache_stress" in c and "--mode model --batch 1" in c and "--layers 12" in c for c in flat)
+    assert any("skygdr_b200.cli.kv_nvlink_transfer_trace" in c and "--dist cached" in c and "--iters 2000" in c for c in flat)
+    with pytest.raises(SystemExit):
+        cb.resolve_config("hbm_kv", "no_such_preset")

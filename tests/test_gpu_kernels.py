@@ -375,4 +375,4 @@ def test_cli_programs_run(ops):
     out = run("kv_nvlink_transfer_trace", "--src", "0", "--dst", "0", "--iters", "5", "--dist", "computed", "--layers", "4", "--max-tokens", "4096")
     assert "Trace-shaped KV transfer done:" in out and "transfers: 5" in out
     out = run("decode_kvcache_stress", "--layers", "2", "--context", "2048", "--gen", "4", "--batch", "4")
-    assert "seq-tokens/s:" in out and "KV bandwidth:" in out
+    assert "Effective sequence-throughput:" in out and "Approx bandwidth:" in out
