@@ -9,7 +9,8 @@ One process drives all GPUs (peer access). Arms:
   memcpy_peer   the reference's mechanism: one contiguous cudaMemcpyPeerAsync per request (no block table, no layout change)
   per_page      one peer copy per block: what a copy-engine design pays for a paged cache
   pairs         GPU 2i -> 2i+1 for all pairs at once (aggregate GB/s)
-  fanout        GPU0 -> k destinations in one launch (replicated stores)
+  fanout        GPU0 -> k destinations in one launch (replicated stores), and the same through an NVLink multicast
+                address (multimem.st: the payload leaves GPU0 once)
   --ref         also runs the reference's own kv_nvlink_transfer_trace binary (baseline/_ref/bin) with the same geometry
 Every time is a device time: CUDA events on the source stream, and the kernel's own globaltimer stamps.
 Roofline: payload bytes over NVLink at 900 GB/s per direction (nominal) and 770 GB/s (measured peer copy).
@@ -166,6 +167,28 @@ def main():
         st = fl.result()
         ok = all(torch.equal(d.data[dp[:nb].long().to(d.data.device)], ops.reference_transfer(src, sp[:nb]).to(d.data.device)) for d in dsts)
         res["arms"][f"fanout_x{k}"] = {"egress_gbs": st["bytes_done"] / (st["device_time_ms"] * 1e-3) / 1e9, "frac_of_900": st["bytes_done"] / (st["device_time_ms"] * 1e-3) / 1e9 / 900.0, "exact": bool(ok)}
+        # the same fan-out through an NVLink multicast address: the payload leaves GPU0 once, NVSwitch replicates it
+        try:
+            team = [0] + list(range(1, k + 1))
+            with ops.MulticastPools(geom, min(max_blocks, 1024), team) as mc:
+                for pool in mc.pools:
+                    pool.data.zero_()
+                for d in team:
+                    torch.cuda.synchronize(d)
+                flags = [ops.RemotePool(0, mc.pools[0].strides, geom.kv_heads) for _ in range(k)]   # no done flags; k destinations
+                fl2 = ops.KvTransferFlow("cuda:0", method="simt")
+                fl2.transfer(src, flags, sp[:nb], dp[:nb], replicate=True, multicast_ptr=mc.multicast_ptr); fl2.result()
+                fl2.transfer(src, flags, sp[:nb], dp[:nb], replicate=True, multicast_ptr=mc.multicast_ptr)
+                st = fl2.result()
+                want = ops.reference_transfer(src, sp[:nb])
+                ok = st["status"] == 0 and all(torch.equal(pl.data[dp[:nb].long().to(pl.data.device)], want.to(pl.data.device)) for pl in mc.pools[1:])
+                sec = st["device_time_ms"] * 1e-3
+                res["arms"][f"fanout_multimem_x{k}"] = {"egress_gbs": st["bytes_done"] / sec / 1e9, "delivered_gbs": k * st["bytes_done"] / sec / 1e9,
+                                                        "frac_of_900_per_destination": st["bytes_done"] / sec / 1e9 / 900.0, "exact": bool(ok),
+                                                        "granularity": int(mc.region.granularity)}
+                del want
+        except Exception as exc:                                             # no multicast support on this machine: say so, keep the unicast arm
+            res["arms"][f"fanout_multimem_x{k}"] = {"unavailable": repr(exc)[:300]}
         del src, dsts
         torch.cuda.empty_cache()
     if a.ref:

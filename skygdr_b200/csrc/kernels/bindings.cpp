@@ -13,6 +13,7 @@
 #include "gemm_tcgen05.h"
 #include "kv_transfer.h"
 #include "memhog.h"
+#include "multicast.h"
 #include "paged_attn.h"
 #include "pcie_task.h"
 #include "tp_fused.h"
@@ -154,7 +155,8 @@ static void kv_transfer(torch::Tensor src_pool, std::vector<uint64_t> dst_ptrs, 
                         int block_tokens, int head_dim, std::vector<int64_t> src_strides, std::vector<int64_t> dst_strides,
                         int heads_per_dst, bool replicate, bool fp8, bool keep_layout, int pages_per_chunk, int ctas, uint64_t credit_dev_ptr,
                         uint64_t consumed_base, uint64_t max_wait_ns, uint64_t first_chunk, uint32_t done_value, torch::Tensor status,
-                        bool use_tma) {
+                        bool use_tma, uint64_t multicast_ptr) {
+    TORCH_CHECK(!(multicast_ptr && (use_tma || fp8 || !replicate)), "a multicast destination takes replicated bf16 pages from the register path");
     TORCH_CHECK(dst_ptrs.size() >= 1 && dst_ptrs.size() <= (size_t)KV_MAX_DST, "1..8 destinations");
     TORCH_CHECK(src_strides.size() == 3 && dst_strides.size() == 3, "strides are (block, layer, kv)");
     TORCH_CHECK(src_blocks.numel() == dst_blocks.numel(), "block lists differ in length");
@@ -167,6 +169,7 @@ static void kv_transfer(torch::Tensor src_pool, std::vector<uint64_t> dst_ptrs, 
         p.dst_scales[i] = i < dst_scale_ptrs.size() ? (void*)dst_scale_ptrs[i] : nullptr;
         p.done_flag[i] = i < done_flag_ptrs.size() ? (unsigned int*)done_flag_ptrs[i] : nullptr;
     }
+    p.mc_dst = (void*)multicast_ptr;
     p.src_blocks = i32_ptr(src_blocks);
     p.dst_blocks = i32_ptr(dst_blocks);
     p.n_pairs = (int)src_blocks.numel();
@@ -406,7 +409,29 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("ipc_free", &ipc_free);
     m.def("tensor_from_ptr", &tensor_from_ptr);
     m.def("enable_peer_access", &enable_peer_access);
-    m.def("kv_transfer", &kv_transfer, py::call_guard<py::gil_scoped_release>());
+    m.def("kv_transfer", &kv_transfer, py::call_guard<py::gil_scoped_release>(), py::arg("src_pool"), py::arg("dst_ptrs"),
+          py::arg("dst_scale_ptrs"), py::arg("done_flag_ptrs"), py::arg("src_blocks"), py::arg("dst_blocks"), py::arg("layers"),
+          py::arg("heads"), py::arg("block_tokens"), py::arg("head_dim"), py::arg("src_strides"), py::arg("dst_strides"),
+          py::arg("heads_per_dst"), py::arg("replicate"), py::arg("fp8"), py::arg("keep_layout"), py::arg("pages_per_chunk"),
+          py::arg("ctas"), py::arg("credit_dev_ptr"), py::arg("consumed_base"), py::arg("max_wait_ns"), py::arg("first_chunk"),
+          py::arg("done_value"), py::arg("status"), py::arg("use_tma"), py::arg("multicast_ptr") = 0);
+    m.def("multicast_supported", [](int device) {
+        std::string why;
+        bool ok = multicast_supported(device, &why);
+        return std::make_pair(ok, why);
+    });
+    py::class_<MulticastRegion>(m, "MulticastRegion")
+        .def_readonly("devices", &MulticastRegion::devices)
+        .def_readonly("bytes", &MulticastRegion::bytes)
+        .def_readonly("granularity", &MulticastRegion::granularity)
+        .def_readonly("unicast", &MulticastRegion::unicast)
+        .def_readonly("multicast", &MulticastRegion::multicast);
+    m.def("multicast_create", [](std::vector<int> devices, uint64_t bytes) {
+        try {
+            return multicast_create(devices, (size_t)bytes);
+        } catch (const std::exception& e) { TORCH_CHECK(false, e.what()); }
+    }, py::return_value_policy::reference);
+    m.def("multicast_destroy", [](MulticastRegion* r) { multicast_destroy(r); });
     m.def("memhog", &memhog, py::call_guard<py::gil_scoped_release>());
     m.def("paged_attn_decode", &paged_attn_decode);
     m.def("rmsnorm", &rmsnorm);

@@ -15,7 +15,10 @@
 //                                       power-of-two scale byte per 32 elements
 // With n_dst > 1 the heads are either scattered (destination g receives heads
 // [g*Hd, (g+1)*Hd): tensor-parallel decode ranks) or replicated (every
-// destination receives all heads: fan-out).
+// destination receives all heads: fan-out). A fan-out can also go through an
+// NVLink multicast address (`mc_dst`): one `multimem.st` per 16 bytes leaves
+// this GPU and NVSwitch writes it into every destination, so the source's
+// link carries the payload once instead of once per destination.
 #include <cuda_fp8.h>
 
 #include "common.cuh"
@@ -65,7 +68,7 @@ __global__ void __launch_bounds__(256) kv_transfer_kernel(const KvTransferParams
     const long long n_chunks = (n_pages + p.pages_per_chunk - 1) / p.pages_per_chunk;
     const unsigned long long page_link_bytes =
         (p.fp8 ? (unsigned long long)n_vec * 8ull + (unsigned long long)n_vec / 4ull : (unsigned long long)n_vec * 16ull) *
-        (p.replicate ? p.n_dst : 1);
+        (p.replicate && !p.mc_dst ? p.n_dst : 1);     // a multicast store leaves this GPU once
 
     unsigned long long grant_cache = 0, stall_ns = 0, my_bytes = 0, my_chunks = 0, last_need = 0;
     if (tid == 0) {
@@ -139,7 +142,9 @@ __global__ void __launch_bounds__(256) kv_transfer_kernel(const KvTransferParams
                                                       : dst_off + ((long long)hl * p.block_tokens + t) * p.head_dim + c * 8;
                     if (!p.fp8) {
                         if (valid) {
-                            if (p.replicate) {
+                            if (p.mc_dst) {
+                                multimem_st_v4((__nv_bfloat16*)p.mc_dst + e, v[u]);
+                            } else if (p.replicate) {
                                 for (int g = 0; g < p.n_dst; ++g) st_v4((__nv_bfloat16*)p.dst[g] + e, v[u]);
                             } else {
                                 st_v4((__nv_bfloat16*)p.dst[g0] + e, v[u]);
@@ -200,6 +205,7 @@ cudaError_t launch_kv_transfer(const KvTransferParams& p, int ctas, cudaStream_t
     if (p.head_dim % 8 != 0 || p.n_dst < 1 || p.n_dst > KV_MAX_DST || p.pages_per_chunk < 1) return cudaErrorInvalidValue;
     if (!p.replicate && p.heads_per_dst * p.n_dst != p.heads) return cudaErrorInvalidValue;
     if (p.fp8 && (p.head_dim % 32 != 0)) return cudaErrorInvalidValue;
+    if (p.mc_dst && (p.fp8 || !p.replicate)) return cudaErrorInvalidValue;   // multicast stores carry whole bf16 pages to every member
     kv_transfer_kernel<8><<<ctas, 256, 0, stream>>>(p);
     return cudaGetLastError();
 }

@@ -14,6 +14,8 @@ constexpr int KV_MAX_DST = 8;
 struct KvTransferParams {
     const __nv_bfloat16* src_pool;        // token-major pages on the source GPU
     void* dst[KV_MAX_DST];                // head-major pools (local or peer-mapped)
+    void* mc_dst;                         // fan-out through NVSwitch: multicast address of the destinations' pools (bf16,
+                                          // replicate only); stores go out once and land in every team member's copy
     void* dst_scales[KV_MAX_DST];         // fp8 mode: one byte per 32 elements, same indexing / 32
     unsigned int* done_flag[KV_MAX_DST];  // optional: set to done_value (release, system scope) when all pages landed
     const int* src_blocks;                // [n_pairs] block ids in the source pool

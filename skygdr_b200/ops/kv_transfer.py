@@ -37,6 +37,45 @@ class RemotePool:
                    done_flag.data_ptr() if done_flag is not None else 0)
 
 
+class MulticastPools:
+    """Head-major pools of the same shape on every GPU of a team, all bound to one NVLink multicast object.
+
+    ``pools[i]`` is GPU ``devices[i]``'s own copy (an ordinary ``PagedKVPool`` over that GPU's memory);
+    ``multicast_ptr`` is the address whose stores NVSwitch delivers into every copy. The GPU that issues the
+    stores has to be a member, so the team is the source GPU followed by the destinations and the source holds a
+    copy too (the price of the fan-out: pool-sized memory on the source). One process drives all members; close()
+    before the process ends so that nothing stays bound."""
+
+    def __init__(self, geom: KVGeometry, n_blocks: int, devices: Sequence[int]):
+        C = load()
+        self._C = C
+        self.geom, self.n_blocks, self.devices = geom, n_blocks, [int(d) for d in devices]
+        for d in self.devices:
+            ok, why = C.multicast_supported(d)
+            if not ok:
+                raise RuntimeError(f"NVLink multicast is not available on device {d}: {why}")
+        elems = n_blocks * geom.block_elems
+        self.region = C.multicast_create(self.devices, elems * 2)
+        self.multicast_ptr = int(self.region.multicast)
+        self.pools: List[PagedKVPool] = []
+        shape = [n_blocks, geom.layers, 2, geom.kv_heads, geom.block_tokens, geom.head_dim]
+        for i, d in enumerate(self.devices):
+            data = C.tensor_from_ptr(int(self.region.unicast[i]), shape, torch.bfloat16, d)
+            self.pools.append(PagedKVPool(geom, n_blocks, "hnd", data=data))
+
+    def close(self) -> None:
+        if self.region is not None:
+            self.pools = []
+            self._C.multicast_destroy(self.region)
+            self.region = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
 class KvTransferFlow:
     def __init__(self, device, page: Optional[CreditPage] = None, ctas: Optional[int] = None, pages_per_chunk: int = 8,
                  max_wait_ms: float = 2.0, method: str = "auto"):
@@ -59,15 +98,18 @@ class KvTransferFlow:
 
     def transfer(self, src: PagedKVPool, dsts: Sequence[RemotePool], src_blocks: torch.Tensor, dst_blocks: torch.Tensor,
                  replicate: bool = False, fp8: bool = False, keep_layout: bool = False, first_chunk: int = 0,
-                 signal: bool = True, ctas: Optional[int] = None) -> None:
+                 signal: bool = True, ctas: Optional[int] = None, multicast_ptr: int = 0) -> None:
         """Enqueues one transfer on the current stream of the source device. ``ctas`` overrides the flow's CTA count
-        for this launch: a paced flow should also hold fewer SMs (its SM quota), or its waiting CTAs crowd out co-runners."""
+        for this launch: a paced flow should also hold fewer SMs (its SM quota), or its waiting CTAs crowd out co-runners.
+        ``multicast_ptr`` (with ``replicate``): the pages go out once through that NVLink multicast address and land in
+        every team member's pool (``MulticastPools``); ``dsts`` then only names the done flags to raise."""
         assert src.layout == "nhd"
         g = src.geom
         heads_per_dst = g.kv_heads if replicate else g.kv_heads // len(dsts)
         for d in dsts:
             assert replicate or keep_layout or d.kv_heads == heads_per_dst, "destination head count does not match the scatter"
-        use_tma = self.method != "simt" and not fp8 and not keep_layout and g.kv_heads <= 8 and g.head_dim == 128 and src.data.is_contiguous()
+        assert not multicast_ptr or (replicate and not fp8 and not keep_layout), "multicast fan-out carries replicated bf16 pages"
+        use_tma = self.method != "simt" and not multicast_ptr and not fp8 and not keep_layout and g.kv_heads <= 8 and g.head_dim == 128 and src.data.is_contiguous()
         assert use_tma or self.method != "tma", "the TMA variant moves contiguous bf16 pools of <= 8 heads without fp8 packing"
         if use_tma and ctas is None and not self._ctas_given:
             ctas = self.sms                      # one driving thread and a 192 KB ring per SM
@@ -77,8 +119,9 @@ class KvTransferFlow:
             src.data, [d.ptr for d in dsts], [d.scale_ptr for d in dsts], [d.done_flag_ptr if signal else 0 for d in dsts],
             src_blocks, dst_blocks, g.layers, g.kv_heads, g.block_tokens, g.head_dim, list(src.strides), list(dsts[0].strides),
             heads_per_dst, replicate, fp8, keep_layout, self.pages_per_chunk, ctas or self.ctas,
-            self.page.dev_ptr if self.page else 0, self.consumed, self.max_wait_ns, first_chunk, self.seq, self.status, use_tma)
-        self._last = (src, dsts, src_blocks, dst_blocks, replicate, fp8, keep_layout, ctas)
+            self.page.dev_ptr if self.page else 0, self.consumed, self.max_wait_ns, first_chunk, self.seq, self.status, use_tma,
+            **({"multicast_ptr": multicast_ptr} if multicast_ptr else {}))
+        self._last = (src, dsts, src_blocks, dst_blocks, replicate, fp8, keep_layout, ctas, multicast_ptr)
 
     def result(self) -> Dict[str, int]:
         """Synchronises and returns the status block; accounts the bytes that were moved."""
@@ -91,8 +134,8 @@ class KvTransferFlow:
     def resume(self, st: Dict[str, int]) -> None:
         """Relaunches the last transfer from the cursor a yielded launch left behind."""
         assert st["status"] in (1, 2)
-        src, dsts, sb, db, rep, fp8, keep, ctas = self._last
-        self.transfer(src, dsts, sb, db, rep, fp8, keep, first_chunk=st["cursor"], ctas=ctas)
+        src, dsts, sb, db, rep, fp8, keep, ctas, mc = self._last
+        self.transfer(src, dsts, sb, db, rep, fp8, keep, first_chunk=st["cursor"], ctas=ctas, multicast_ptr=mc)
 
     def transfer_to_completion(self, *args, max_launches: int = 10000, **kw) -> Dict[str, int]:
         """Transfers, relaunching after every credit yield; sums bytes and stall time."""
@@ -113,6 +156,7 @@ class KvTransferFlow:
 
 
 def link_bytes(geom: KVGeometry, n_blocks: int, n_dst: int = 1, replicate: bool = False, fp8: bool = False) -> int:
+    """Bytes that leave the source GPU (unicast fan-out sends every page once per destination; a multicast one, n_dst=1)."""
     per_page = geom.page_elems * (2 if not fp8 else 1) + (geom.page_elems // 32 if fp8 else 0)
     return n_blocks * geom.layers * 2 * per_page * (n_dst if replicate else 1)
 

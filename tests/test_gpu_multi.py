@@ -28,3 +28,40 @@ def _run(world, script, timeout=240):
 def test_tensor_parallel_decode_and_peer_kv_transfer_2gpu():
     r = _run(2, "tp_worker.py")
     assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 3, reason="needs 3 GPUs (source + 2 destinations)")
+def test_multicast_fanout_lands_in_every_destination():
+    """GPU0's pages go out once through the NVLink multicast address and must equal, in both destinations' pools, what
+    the unicast fan-out writes (a PyTorch permute of the source pages). One process drives the three GPUs."""
+    from skygdr_b200 import ops
+    from skygdr_b200._ext import load
+
+    C = load()
+    ok, why = C.multicast_supported(0)
+    if not ok:
+        pytest.skip(f"no NVLink multicast here: {why}")
+    geom = ops.KVGeometry(layers=3, kv_heads=8)
+    nb = 40
+    src = ops.PagedKVPool(geom, nb, "nhd", device="cuda:0")
+    src.data.normal_()
+    g = torch.Generator().manual_seed(5)
+    sp = torch.randperm(nb, generator=g).int().cuda(0)
+    dp = torch.randperm(nb, generator=g).int().cuda(0)
+    with ops.MulticastPools(geom, nb, [0, 1, 2]) as mc:
+        for pool in mc.pools:
+            pool.data.fill_(-1.0)
+        for d in range(3):
+            torch.cuda.synchronize(d)
+        flow = ops.KvTransferFlow("cuda:0", method="simt")
+        none = [ops.RemotePool(0, mc.pools[0].strides, geom.kv_heads) for _ in range(2)]
+        with torch.cuda.device(0):
+            flow.transfer(src, none, sp[:32], dp[:32], replicate=True, multicast_ptr=mc.multicast_ptr)
+            st = flow.result()
+        assert st["status"] == 0 and st["bytes_done"] == ops.link_bytes(geom, 32)        # egress counts the payload once
+        want = ops.reference_transfer(src, sp[:32])
+        for pool in mc.pools:                                                              # the source's own copy receives it too
+            dev = pool.data.device
+            assert torch.equal(pool.data[dp[:32].long().to(dev)], want.to(dev))
+            untouched = dp[32:].long().to(dev)
+            assert bool((pool.data[untouched] == -1.0).all())
