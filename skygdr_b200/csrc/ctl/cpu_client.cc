@@ -216,14 +216,14 @@ int main(int argc, char** argv) {
 
     // ---- data loop: one message in flight (the reference's write-with-ack path, src/cpu_client.cc:1088-1249) ----
     int rc = 0;
+    SkyHeartbeatWatch heartbeat = {0, 0, 0};
     for (uint64_t i = 0; i < iters && !ctl.stop_requested(); ++i) {
         uint64_t off;
         if (pattern == "seq") { off = seq_off; seq_off += msg; if (seq_off + msg > span) seq_off = 0; }
         else off = span > msg ? (uint64_t)(rng.uniform() * double(span - msg)) : 0;
         off &= ~(align - 1);
         if (page) {                                      // byte grant of the flow, if it has one
-            while (!page->unlimited && consumed + msg > __atomic_load_n(&page->granted_bytes, __ATOMIC_ACQUIRE) &&
-                   !page->stop && !ctl.stop_requested())
+            while (consumed + msg > sky_host_allowance(page, &heartbeat, mono_ns()) && !page->stop && !ctl.stop_requested())
                 std::this_thread::sleep_for(std::chrono::microseconds(50));
             if (page->stop) break;
             consumed += msg;

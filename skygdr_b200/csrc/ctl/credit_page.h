@@ -43,6 +43,15 @@ enum SkyStatus {
     SKY_STATUS_TIMEOUT_FLAG = 3,   // a bounded wait on a peer flag gave up
     SKY_STATUS_BAD_INDEX = 4,      // a bounds check rejected an index (debug builds)
     SKY_STATUS_TIMEOUT_MBAR = 5,   // a bounded wait on an mbarrier gave up
+    SKY_STATUS_CONTROL_LOST = 6,   // the control side's heartbeat went stale and the page says to stall then
+};
+
+// What a data path does once the control side's epoch has not moved for `dead_after_windows` windows
+// (a daemon that died or hung): the reference has no heartbeat at all.
+enum SkyDeadPolicy {
+    SKY_DEAD_STALL = 0,            // keep the last grant; give up with SKY_STATUS_CONTROL_LOST when it runs out
+    SKY_DEAD_UNPACED = 1,          // carry on without a gate
+    SKY_DEAD_STATIC = 2,           // grant itself `fallback_per_window` bytes per window from the moment of detection
 };
 
 typedef struct SkyCreditPage {
@@ -59,7 +68,10 @@ typedef struct SkyCreditPage {
     uint32_t flow_id;
     uint32_t priority;
     double   target_gbps;      // goal of the flow (0 = best effort)
-    uint64_t _pad_grant[7];
+    uint32_t dead_after_windows;   // heartbeat: epoch unchanged for this many windows = control side gone (0 = never)
+    uint32_t dead_policy;          // SkyDeadPolicy
+    uint64_t fallback_per_window;  // SKY_DEAD_STATIC: bytes per window
+    uint64_t _pad_grant[5];
     // ---- usage half: written by the data path only (offset 128) ----
     uint64_t consumed_bytes;   // tickets taken so far (cumulative)
     uint64_t completed_bytes;  // bytes known to be delivered (cumulative)
@@ -69,8 +81,46 @@ typedef struct SkyCreditPage {
     uint64_t chunks;           // chunks moved
     uint64_t yields;           // times the data path gave up and returned early
     uint64_t backlog_bytes;    // bytes requested of the flow and not yet delivered
-    uint64_t _pad_usage[8];
+    uint64_t heartbeat_lost;   // 0, or 1 + the epoch at which the data path last found the heartbeat stale
+    uint64_t heartbeat_lost_ns;// data-path clock at that moment
+    uint64_t _pad_usage[6];
 } SkyCreditPage;
+
+// Host-side data paths (copy workers, the compat client) follow the same heartbeat rule as the kernels: the bytes
+// a flow may have consumed by `now_ns`, given the page and a watch that the caller keeps between calls.
+typedef struct SkyHeartbeatWatch {
+    uint64_t epoch;        // last epoch seen
+    uint64_t t_change_ns;  // when it last changed (caller's clock); 0 = not started
+    uint64_t t_dead_ns;    // when the control side was taken for dead; 0 = alive
+} SkyHeartbeatWatch;
+
+#if !defined(__CUDA_ARCH__)
+static inline uint64_t sky_host_allowance(SkyCreditPage* p, SkyHeartbeatWatch* w, uint64_t now_ns) {
+    if (__atomic_load_n(&p->unlimited, __ATOMIC_RELAXED)) return ~0ull;
+    const uint64_t granted = __atomic_load_n(&p->granted_bytes, __ATOMIC_ACQUIRE);
+    const uint32_t n = __atomic_load_n(&p->dead_after_windows, __ATOMIC_RELAXED);
+    if (n == 0) return granted;
+    const uint64_t e = __atomic_load_n(&p->epoch, __ATOMIC_ACQUIRE);
+    if (w->t_change_ns == 0 || e != w->epoch) {
+        w->epoch = e;
+        w->t_change_ns = now_ns;
+        w->t_dead_ns = 0;
+        return granted;
+    }
+    if (w->t_dead_ns == 0) {
+        if (now_ns - w->t_change_ns <= (uint64_t)n * p->window_ns) return granted;
+        w->t_dead_ns = now_ns;
+        p->heartbeat_lost_ns = now_ns;
+        __atomic_store_n(&p->heartbeat_lost, e + 1, __ATOMIC_RELEASE);
+    }
+    if (p->dead_policy == SKY_DEAD_UNPACED) return ~0ull;
+    if (p->dead_policy == SKY_DEAD_STATIC) {
+        const uint64_t win = p->window_ns ? p->window_ns : 1;
+        return granted + (now_ns - w->t_dead_ns) / win * p->fallback_per_window;
+    }
+    return granted;        // SKY_DEAD_STALL: what was granted is all there is
+}
+#endif
 
 #ifdef __cplusplus
 }

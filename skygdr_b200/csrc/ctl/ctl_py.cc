@@ -188,7 +188,10 @@ PYBIND11_MODULE(_ctl, m) {
         .def_readwrite("tag", &DaemonConfig::tag)
         .def_readwrite("smooth_windows", &DaemonConfig::smooth_windows)
         .def_readwrite("burst_windows", &DaemonConfig::burst_windows)
-        .def_readwrite("external_util", &DaemonConfig::external_util);
+        .def_readwrite("external_util", &DaemonConfig::external_util)
+        .def_readwrite("dead_after_windows", &DaemonConfig::dead_after_windows)
+        .def_readwrite("dead_policy", &DaemonConfig::dead_policy)
+        .def_readwrite("dead_fallback_gbps", &DaemonConfig::dead_fallback_gbps);
     py::class_<DaemonCore::WindowLog>(m, "WindowLog")
         .def_readonly("window_id", &DaemonCore::WindowLog::window_id)
         .def_readonly("flow_id", &DaemonCore::WindowLog::flow_id)
@@ -230,7 +233,20 @@ PYBIND11_MODULE(_ctl, m) {
             o["budget_per_window"] = p->budget_per_window; o["consumed_bytes"] = p->consumed_bytes;
             o["completed_bytes"] = p->completed_bytes; o["backlog_bytes"] = p->backlog_bytes;
             o["window_ns"] = p->window_ns; o["target_gbps"] = p->target_gbps;
+            o["dead_after_windows"] = p->dead_after_windows; o["dead_policy"] = p->dead_policy;
+            o["fallback_per_window"] = p->fallback_per_window; o["heartbeat_lost"] = p->heartbeat_lost;
             return o;
+        });
+
+    // The heartbeat rule of host-side data paths, callable on a core's page (tests, in-process flows).
+    py::class_<SkyHeartbeatWatch>(m, "HeartbeatWatch")
+        .def(py::init([]() { return SkyHeartbeatWatch{0, 0, 0}; }))
+        .def_readonly("epoch", &SkyHeartbeatWatch::epoch)
+        .def_readonly("t_dead_ns", &SkyHeartbeatWatch::t_dead_ns)
+        .def("allowance", [](SkyHeartbeatWatch& w, DaemonCore& d, uint32_t id, uint64_t now_ns) {
+            SkyCreditPage* p = d.page(id);
+            if (!p) throw py::key_error("unknown flow");
+            return sky_host_allowance(p, &w, now_ns);
         });
 
     // ---- signals, with an injectable NVML ----

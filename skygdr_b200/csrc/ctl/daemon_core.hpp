@@ -51,6 +51,11 @@ struct DaemonConfig {
     int smooth_windows = 5;
     double burst_windows = 2.0;
     bool external_util = false;           // link utilisation is supplied (NVML) instead of summed from flows
+    // Heartbeat contract written into every page: a data path that sees `epoch` unchanged for this many windows while it
+    // waits for credit takes the daemon for dead and follows dead_policy (SkyDeadPolicy). 0 = no heartbeat check.
+    uint32_t dead_after_windows = 0;
+    uint32_t dead_policy = SKY_DEAD_STALL;
+    double dead_fallback_gbps = 1.0;      // SKY_DEAD_STATIC: the rate a flow grants itself
 };
 
 class DaemonCore {
@@ -358,6 +363,9 @@ private:
         st.page->mode = SKY_MODE_HIGH;
         st.page->unlimited = 1;
         st.page->window_ns = cfg_.window_ns;
+        st.page->dead_policy = cfg_.dead_policy;
+        st.page->fallback_per_window = (uint64_t)(cfg_.dead_fallback_gbps * 1e9 * double(cfg_.window_ns) * 1e-9);
+        st.page->dead_after_windows = cfg_.dead_after_windows;
         st.ctl.configure(0, 100);
         st.ctl.enable();
         __atomic_store_n(&st.page->magic, SKYGDR_CREDIT_MAGIC, __ATOMIC_RELEASE);

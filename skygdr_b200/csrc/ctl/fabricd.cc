@@ -77,6 +77,14 @@ int main(int argc, char** argv) {
         else if (k == "--enter_windows") cfg.pcfg.enter_windows = atoi(v.c_str());
         else if (k == "--exit_windows") cfg.pcfg.exit_windows = atoi(v.c_str());
         else if (k == "--low1_fraction") cfg.pcfg.low1_fraction = atof(v.c_str());
+        else if (k == "--dead_after_windows") cfg.dead_after_windows = (uint32_t)strtoul(v.c_str(), nullptr, 10);
+        else if (k == "--dead_policy") {
+            if (v == "stall") cfg.dead_policy = SKY_DEAD_STALL;
+            else if (v == "unpaced") cfg.dead_policy = SKY_DEAD_UNPACED;
+            else if (v == "static") cfg.dead_policy = SKY_DEAD_STATIC;
+            else { fprintf(stderr, "fabricd: --dead_policy is stall, unpaced or static\n"); return 2; }
+        }
+        else if (k == "--dead_fallback_gbps") cfg.dead_fallback_gbps = atof(v.c_str());
         else { fprintf(stderr, "fabricd: unknown flag %s\n", k.c_str()); return 2; }
     }
     if (cfg.window_ns < 100000) { fprintf(stderr, "fabricd: window below 100 us\n"); return 2; }

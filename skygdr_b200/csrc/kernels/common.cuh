@@ -108,19 +108,53 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 // page's stop flag is set (then *stopped tells which).
 __device__ __forceinline__ bool credit_acquire(const SkyCreditPage* page, unsigned long long need,
                                                unsigned long long* cache, unsigned long long max_wait_ns,
-                                               unsigned long long* stall_ns, bool* stopped) {
+                                               unsigned long long* stall_ns, bool* stopped, bool* control_lost = nullptr) {
     *stopped = false;
+    if (control_lost) *control_lost = false;
     if (page == nullptr) return true;
     if (need <= *cache) return true;
     unsigned long long t0 = globaltimer_ns();
     unsigned ns = 64;
+    // Heartbeat: the control side bumps `epoch` every window. If it stays put for dead_after_windows windows while this
+    // thread is waiting for credit, the control side is taken for dead and the page's dead_policy applies.
+    const unsigned dead_windows = ld_sys_u32(&page->dead_after_windows);
+    const unsigned long long dead_ns = dead_windows ? (unsigned long long)dead_windows * ld_sys_u64((const unsigned long long*)&page->window_ns) : 0ull;
+    unsigned long long epoch0 = dead_ns ? ld_sys_u64((const unsigned long long*)&page->epoch) : 0ull, t_epoch = t0, t_dead = 0;
+    // An earlier wait (this CTA's or another's) may have found the heartbeat stale at this very epoch already.
+    bool dead = dead_ns && ld_sys_u64((const unsigned long long*)&page->heartbeat_lost) == epoch0 + 1;
+    if (dead) t_dead = ld_sys_u64((const unsigned long long*)&page->heartbeat_lost_ns);
     for (;;) {
         if (ld_sys_u32(&page->stop)) { *stopped = true; *stall_ns += globaltimer_ns() - t0; return false; }
         if (ld_sys_u32(&page->unlimited)) { *cache = ~0ull; break; }
         unsigned long long g = ld_sys_u64((const unsigned long long*)&page->granted_bytes);
         *cache = g;
         if (need <= g) break;
-        if (globaltimer_ns() - t0 > max_wait_ns) { *stall_ns += globaltimer_ns() - t0; return false; }
+        const unsigned long long now = globaltimer_ns();
+        if (dead_ns) {
+            const unsigned long long e = ld_sys_u64((const unsigned long long*)&page->epoch);
+            if (e != epoch0) { epoch0 = e; t_epoch = now; dead = false; }
+            else if (!dead && now - t_epoch > dead_ns) {
+                dead = true;
+                t_dead = now;
+                SkyCreditPage* w = const_cast<SkyCreditPage*>(page);
+                st_sys_u64((unsigned long long*)&w->heartbeat_lost_ns, now);
+                st_sys_u64((unsigned long long*)&w->heartbeat_lost, e + 1);
+            }
+            if (dead) {
+                if (control_lost) *control_lost = true;
+                const unsigned policy = ld_sys_u32(&page->dead_policy);
+                if (policy == SKY_DEAD_UNPACED) { *cache = ~0ull; break; }
+                if (policy == SKY_DEAD_STATIC) {
+                    const unsigned long long w = max(1ull, ld_sys_u64((const unsigned long long*)&page->window_ns));
+                    const unsigned long long self = g + (now > t_dead ? (now - t_dead) / w : 0ull) * ld_sys_u64((const unsigned long long*)&page->fallback_per_window);
+                    if (need <= self) break;         // not cached: the next chunk asks again
+                } else {
+                    *stall_ns += now - t0;
+                    return false;                    // SKY_DEAD_STALL
+                }
+            }
+        }
+        if (now - t0 > max_wait_ns) { *stall_ns += now - t0; return false; }
         __nanosleep(ns);
         if (ns < 8192) ns <<= 1;      // the page is in host memory: poll it gently
     }

@@ -86,8 +86,8 @@ __global__ void __launch_bounds__(256) kv_transfer_kernel(const KvTransferParams
                     long long last_page = min((long long)(k + 1) * p.pages_per_chunk, n_pages);
                     unsigned long long need = p.consumed_base +
                         (unsigned long long)(last_page - (long long)p.first_chunk * p.pages_per_chunk) * page_link_bytes;
-                    bool stopped;
-                    if (credit_acquire(p.page, need, &grant_cache, p.max_wait_ns, &stall_ns, &stopped)) {
+                    bool stopped, lost;
+                    if (credit_acquire(p.page, need, &grant_cache, p.max_wait_ns, &stall_ns, &stopped, &lost)) {
                         go = 1;
                         // Publish progress chunk by chunk (posted writes to the mapped page), so the control
                         // side sees rates inside a long transfer. Chunks are ticketed in order, so `need` is
@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(256) kv_transfer_kernel(const KvTransferParams
                         last_need = need;
                     } else {
                         atomicMin(&p.status->cursor, k);
-                        set_status(p.status, stopped ? SKY_STATUS_STOPPED : SKY_STATUS_YIELD_CREDIT, (unsigned)k);
+                        set_status(p.status, stopped ? SKY_STATUS_STOPPED : lost ? SKY_STATUS_CONTROL_LOST : SKY_STATUS_YIELD_CREDIT, (unsigned)k);
                     }
                 }
             }
@@ -119,6 +119,10 @@ __global__ void __launch_bounds__(256) kv_transfer_kernel(const KvTransferParams
             const int rem = (int)(pg - (long long)pair * pages_per_pair);
             const int layer = rem >> 1, kv = rem & 1;
             const int sb = __ldg(p.src_blocks + pair), db = __ldg(p.dst_blocks + pair);
+            if ((p.src_num_blocks && (unsigned)sb >= (unsigned)p.src_num_blocks) || (p.dst_num_blocks && (unsigned)db >= (unsigned)p.dst_num_blocks)) {
+                if (tid == 0) set_status(p.status, SKY_STATUS_BAD_INDEX, (unsigned)pair);    // same verdict in every thread
+                continue;
+            }
             const __nv_bfloat16* src = p.src_pool + (long long)sb * p.src_block_stride + (long long)layer * p.src_layer_stride +
                                        (long long)kv * p.src_kv_stride;
             const long long dst_off = (long long)db * p.dst_block_stride + (long long)layer * p.dst_layer_stride +

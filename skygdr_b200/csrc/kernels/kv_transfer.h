@@ -21,6 +21,8 @@ struct KvTransferParams {
     const int* src_blocks;                // [n_pairs] block ids in the source pool
     const int* dst_blocks;                // [n_pairs] block ids in the destination pool(s)
     int n_pairs, layers, heads, block_tokens, head_dim;
+    int src_num_blocks, dst_num_blocks;   // pool sizes for the index check (0 = unchecked): a block id outside its pool
+                                          // is skipped and reported as SKY_STATUS_BAD_INDEX with the pair's position
     long long src_block_stride, src_layer_stride, src_kv_stride;  // in source elements
     long long dst_block_stride, dst_layer_stride, dst_kv_stride;  // in destination elements
     int n_dst, heads_per_dst, replicate, fp8;

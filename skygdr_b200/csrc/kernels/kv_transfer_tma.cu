@@ -75,10 +75,10 @@ __global__ void __launch_bounds__(TMA_THREADS) kv_transfer_tma_kernel(const __gr
         if ((long long)k >= n_chunks) break;
         const long long page0 = (long long)k * p.pages_per_chunk, page1 = min(page0 + p.pages_per_chunk, n_pages);
         const unsigned long long need = p.consumed_base + (unsigned long long)(page1 - (long long)p.first_chunk * p.pages_per_chunk) * page_link_bytes;
-        bool stopped;
-        if (!credit_acquire(p.page, need, &grant_cache, p.max_wait_ns, &stall_ns, &stopped)) {
+        bool stopped, lost;
+        if (!credit_acquire(p.page, need, &grant_cache, p.max_wait_ns, &stall_ns, &stopped, &lost)) {
             atomicMin(&p.status->cursor, k);
-            set_status(p.status, stopped ? SKY_STATUS_STOPPED : SKY_STATUS_YIELD_CREDIT, (unsigned)k);
+            set_status(p.status, stopped ? SKY_STATUS_STOPPED : lost ? SKY_STATUS_CONTROL_LOST : SKY_STATUS_YIELD_CREDIT, (unsigned)k);
             break;
         }
         if (p.usage) {
@@ -91,6 +91,10 @@ __global__ void __launch_bounds__(TMA_THREADS) kv_transfer_tma_kernel(const __gr
             const int rem = (int)(pg - (long long)pair * pages_per_pair);
             const int layer = rem >> 1, kv = rem & 1;
             const int sb = __ldg(p.src_blocks + pair), db = __ldg(p.dst_blocks + pair);
+            if ((p.src_num_blocks && (unsigned)sb >= (unsigned)p.src_num_blocks) || (p.dst_num_blocks && (unsigned)db >= (unsigned)p.dst_num_blocks)) {
+                set_status(p.status, SKY_STATUS_BAD_INDEX, (unsigned)pair);    // nothing is loaded or stored for this page
+                continue;
+            }
             // the slot about to be loaded was last read by the store of page (issued - SLOTS)
             bulk_wait_read<SLOTS - LOOKAHEAD - 1>();
             const int s = (int)(issued % SLOTS);

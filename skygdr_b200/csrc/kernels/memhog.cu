@@ -85,10 +85,10 @@ __global__ void __launch_bounds__(512) memhog_kernel(const MemhogParams p) {
                 if (go && p.page) {
                     // all CTAs advance together, so the flow has consumed about seq*grid+block chunks
                     unsigned long long need = p.consumed_base + ((seq * gridDim.x) + blockIdx.x + 1) * p.chunk_vec * bytes_per_vec;
-                    bool stopped;
-                    if (!credit_acquire(p.page, need, &grant_cache, p.max_wait_ns, &stall_ns, &stopped)) {
+                    bool stopped, lost;
+                    if (!credit_acquire(p.page, need, &grant_cache, p.max_wait_ns, &stall_ns, &stopped, &lost)) {
                         go = 0;
-                        set_status(p.status, stopped ? SKY_STATUS_STOPPED : SKY_STATUS_YIELD_CREDIT, (unsigned)seq);
+                        set_status(p.status, stopped ? SKY_STATUS_STOPPED : lost ? SKY_STATUS_CONTROL_LOST : SKY_STATUS_YIELD_CREDIT, (unsigned)seq);
                     }
                 }
                 s_go = go;

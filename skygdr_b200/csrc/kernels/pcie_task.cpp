@@ -151,6 +151,7 @@ void PcieTask::run() {
         last_bytes = completed_;
     };
 
+    SkyHeartbeatWatch heartbeat = {0, 0, 0};
     while (!stop_.load()) {
         for (auto& ln : lanes_) settle(ln, false);
         uint64_t now = now_ns();
@@ -183,7 +184,8 @@ void PcieTask::run() {
                     if (outstanding >= cfg_.max_outstanding_bytes) break;
                     n = std::min<uint64_t>(n, cfg_.max_outstanding_bytes - outstanding);
                     if (page && !__atomic_load_n(&page->unlimited, __ATOMIC_RELAXED)) {
-                        uint64_t granted = __atomic_load_n(&page->granted_bytes, __ATOMIC_ACQUIRE);
+                        uint64_t granted = sky_host_allowance(page, &heartbeat, now);      // the grant, or the page's dead-control rule
+                        if (granted == ~0ull) granted = base + issued_ + n;
                         uint64_t used = base + issued_;
                         if (granted <= used) break;
                         // Do not shred the flow into tiny copies when credit trickles in: wait for a worthwhile piece.

@@ -10,7 +10,8 @@ import torch
 
 from .._ext import load
 
-STATUS_NAMES = {0: "OK", 1: "YIELD_CREDIT", 2: "STOPPED", 3: "TIMEOUT_FLAG", 4: "BAD_INDEX", 5: "TIMEOUT_MBAR"}
+STATUS_NAMES = {0: "OK", 1: "YIELD_CREDIT", 2: "STOPPED", 3: "TIMEOUT_FLAG", 4: "BAD_INDEX", 5: "TIMEOUT_MBAR", 6: "CONTROL_LOST"}
+DEAD_POLICIES = {"stall": 0, "unpaced": 1, "static": 2}
 
 
 class CreditPage:
@@ -49,6 +50,14 @@ class CreditPage:
     def grant(self, granted_bytes: int, unlimited: bool = False, stop: bool = False) -> None:
         self.granted = granted_bytes
         self._C.credit_page_grant(self.host_ptr, granted_bytes, unlimited, stop)
+
+    def set_heartbeat(self, window_ms: float, dead_after_windows: int, policy: str = "stall", fallback_gbps: float = 1.0) -> None:
+        """The heartbeat contract of this page: a data path that waits for credit and sees ``epoch`` (bumped by every
+        ``grant``) stand still for ``dead_after_windows`` windows takes the control side for dead and follows ``policy``:
+        "stall" (give up with CONTROL_LOST once the last grant is used), "unpaced", or "static" (``fallback_gbps``)."""
+        window_ns = int(window_ms * 1e6)
+        self._C.credit_page_heartbeat(self.host_ptr, window_ns, dead_after_windows, DEAD_POLICIES[policy],
+                                      int(fallback_gbps * 1e9 * window_ms * 1e-3))
 
     def set_unlimited(self) -> None:
         self._C.credit_page_grant(self.host_ptr, self.granted, True, False)

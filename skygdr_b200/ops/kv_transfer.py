@@ -29,12 +29,13 @@ class RemotePool:
     kv_heads: int           # heads stored in this pool
     scale_ptr: int = 0      # fp8: scale bytes, same indexing / 32
     done_flag_ptr: int = 0  # optional u32 set when a transfer has fully landed
+    num_blocks: int = 0     # pool size for the kernel's block-id check (0 = unchecked)
 
     @classmethod
     def of(cls, pool: PagedKVPool, done_flag: Optional[torch.Tensor] = None) -> "RemotePool":
         assert pool.layout == "hnd"
         return cls(pool.data.data_ptr(), pool.strides, pool.geom.kv_heads, 0,
-                   done_flag.data_ptr() if done_flag is not None else 0)
+                   done_flag.data_ptr() if done_flag is not None else 0, pool.num_blocks)
 
 
 class MulticastPools:
@@ -120,7 +121,7 @@ class KvTransferFlow:
             src_blocks, dst_blocks, g.layers, g.kv_heads, g.block_tokens, g.head_dim, list(src.strides), list(dsts[0].strides),
             heads_per_dst, replicate, fp8, keep_layout, self.pages_per_chunk, ctas or self.ctas,
             self.page.dev_ptr if self.page else 0, self.consumed, self.max_wait_ns, first_chunk, self.seq, self.status, use_tma,
-            **({"multicast_ptr": multicast_ptr} if multicast_ptr else {}))
+            multicast_ptr=multicast_ptr, src_num_blocks=src.num_blocks, dst_num_blocks=min(d.num_blocks for d in dsts))
         self._last = (src, dsts, src_blocks, dst_blocks, replicate, fp8, keep_layout, ctas, multicast_ptr)
 
     def result(self) -> Dict[str, int]:
@@ -133,7 +134,7 @@ class KvTransferFlow:
 
     def resume(self, st: Dict[str, int]) -> None:
         """Relaunches the last transfer from the cursor a yielded launch left behind."""
-        assert st["status"] in (1, 2)
+        assert st["status"] in (1, 2, 6)
         src, dsts, sb, db, rep, fp8, keep, ctas, mc = self._last
         self.transfer(src, dsts, sb, db, rep, fp8, keep, first_chunk=st["cursor"], ctas=ctas, multicast_ptr=mc)
 

@@ -284,3 +284,27 @@ def test_colocation_harness_plans_our_programs(tmp_path, monkeypatch):
     assert any("skygdr_b200.cli.kv_nvlink_transfer_trace" in c and "--dist cached" in c and "--iters 2000" in c for c in flat)
     with pytest.raises(SystemExit):
         cb.resolve_config("hbm_kv", "no_such_preset")
+
+
+def test_flow_outlives_a_killed_daemon_under_the_unpaced_dead_policy():
+    """The daemon is killed (no snapshot, no goodbye) while a paced flow runs. With `--dead_policy unpaced` the flow notices
+    the stale heartbeat in its page and finishes on its own; the failure is made on the host."""
+    d = FabricDaemon(window_us=2000, capacity_gbps=0.05, lease_ms=3000, extra=["--dead_after_windows", "10", "--dead_policy", "unpaced"])
+    env = dict(ENV, SKYGDR_DAEMON=f"127.0.0.1:{d.port}", SKYGDR_FLOW_NAME="kv_offload", SKYGDR_FLOW_PRIORITY="besteffort")
+    p = subprocess.Popen([f"{BIN}/cpu_client", "-", "0", "sim:4", "3000", "64K", "write", "1", "0"], stdout=subprocess.PIPE,
+                         stderr=subprocess.PIPE, text=True, env=env)
+    try:
+        with FabricClient(port=d.port) as c:
+            t0 = time.time()
+            while "kv_offload" not in c.request("FLOWS") and time.time() - t0 < 5:
+                time.sleep(0.02)
+            c.request("FLOW 1 LOW4")                    # 0.05 GB/s / 2.75: 3000 x 64 KiB would take about 10 s
+        time.sleep(0.3)
+        assert p.poll() is None                         # still crawling under its grant
+        d.kill()
+        out, err = p.communicate(timeout=20)            # 20 ms of silence, then unpaced: done in well under a second
+    finally:
+        d.kill()
+        if p.poll() is None:
+            p.kill()
+    assert "samples=3000" in out, out + err

@@ -168,3 +168,36 @@ def test_token_bucket(ctl):
     assert b.refill(-1.0, w, 0) == 200_000_000            # unlimited leaves the counter alone
     g = b.refill(1.0, w, 200_000_000)
     assert g == 205_000_000 and b.refill(0.0, w, 205_000_000) == 205_000_000
+
+
+def test_heartbeat_rule_of_host_data_paths(ctl):
+    """A page carries the daemon's heartbeat contract; a host data path that sees the epoch stand still for
+    dead_after_windows windows follows dead_policy: stall on the last grant, run unpaced, or grant itself a static rate."""
+    win = 1_000_000
+    for policy, name in ((0, "stall"), (1, "unpaced"), (2, "static")):
+        d = _core(ctl, window_ns=win, dead_after_windows=4, dead_policy=policy, dead_fallback_gbps=2.0, policy="static")
+        d.handle_line("REGISTER kv_offload besteffort 0 kv_offload", 0)
+        d.handle_line("FLOW 1 LOW1", 0)
+        d.report_usage(1, 0, 0, 1 << 30)
+        d.step_window(win)
+        d.step_window(2 * win)
+        f = d.page_fields(1)
+        assert f["dead_after_windows"] == 4 and f["dead_policy"] == policy and f["fallback_per_window"] == 2_000_000
+        granted = f["granted_bytes"]
+        assert f["unlimited"] == 0 and granted > 0
+        w = ctl.HeartbeatWatch()
+        assert w.allowance(d, 1, 10 * win) == granted                     # first look starts the watch
+        d.step_window(11 * win)
+        g2 = d.page_fields(1)["granted_bytes"]
+        assert w.allowance(d, 1, 12 * win) == g2 and w.t_dead_ns == 0     # the epoch moved: alive
+        assert w.allowance(d, 1, 16 * win) == g2                          # 4 windows of silence: not yet over the line
+        got = w.allowance(d, 1, 17 * win)                                 # now it is
+        assert w.t_dead_ns == 17 * win and d.page_fields(1)["heartbeat_lost"] == d.page_fields(1)["epoch"] + 1, name
+        if name == "stall":
+            assert got == g2 and w.allowance(d, 1, 100 * win) == g2
+        elif name == "unpaced":
+            assert got == 2**64 - 1
+        else:
+            assert got == g2 and w.allowance(d, 1, 27 * win) == g2 + 10 * 2_000_000
+        d.step_window(30 * win)                                           # the daemon is back: grants rule again
+        assert w.allowance(d, 1, 31 * win) == d.page_fields(1)["granted_bytes"] and w.t_dead_ns == 0
