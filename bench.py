@@ -42,7 +42,7 @@ def parse():
     ap.add_argument("--ctx-hi", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=36, help="for smoke runs only; the benchmark uses 36")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--attn-impl", default="tc", choices=["tc", "simt"])
+    ap.add_argument("--attn-impl", default="tc", choices=["tc", "tcp", "simt"])
     ap.add_argument("--attn-chunk", type=int, default=1024)
     ap.add_argument("--profile-step", action="store_true", help="also print per-kernel-kind times of one eager step (tensor-parallel engine)")
     return ap.parse_args()

@@ -70,7 +70,7 @@ def main():
     ap.add_argument("--op", default="axpy")
     ap.add_argument("--rows", type=int, default=16)
     ap.add_argument("--no-flush", action="store_true")
-    ap.add_argument("--impl", default="simt", choices=["simt", "tc"])
+    ap.add_argument("--impl", default="simt", choices=["simt", "tc", "tcp"])
     a = ap.parse_args()
     dev = "cuda"
     hbm, tf, src = peaks()

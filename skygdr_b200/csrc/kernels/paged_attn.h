@@ -30,6 +30,7 @@ struct PagedAttnParams {
 
 cudaError_t launch_paged_attn_decode(const PagedAttnParams& p, cudaStream_t stream);
 // Tensor-core version (paged_attn_tc.cu). pool_rows: 128-element rows from p.kv to the end of the pool allocation;
-// chunk_tokens must be a multiple of 128.
-cudaError_t launch_paged_attn_decode_tc(const PagedAttnParams& p, long long pool_rows, cudaStream_t stream);
+// chunk_tokens must be a multiple of 128. persistent_ctas > 0 selects the persistent variant with that many CTAs (two per
+// SM is the intended number; batch <= 256 and chunk_tokens <= 1024 there).
+cudaError_t launch_paged_attn_decode_tc(const PagedAttnParams& p, long long pool_rows, cudaStream_t stream, int persistent_ctas = 0);
 }  // namespace sky

@@ -15,8 +15,12 @@ class PagedAttention:
     """Holds the split-KV scratch (partials, statistics, counters) for a maximum batch and context."""
 
     def __init__(self, device, max_batch: int, q_heads: int, kv_heads: int, max_ctx: int, chunk_tokens: int = 512, impl: str = "simt"):
-        """impl: "simt" (CUDA cores, paged_attn.cu) or "tc" (tcgen05 tensor cores, paged_attn_tc.cu; chunk_tokens % 128 == 0)."""
-        assert impl in ("simt", "tc") and (impl == "simt" or chunk_tokens % 128 == 0)
+        """impl: "simt" (CUDA cores, paged_attn.cu), "tc" (tcgen05 tensor cores, one CTA per (sequence, split, KV head);
+        chunk_tokens % 128 == 0) or "tcp" (the same engine as a persistent kernel of two CTAs per SM that walk the work items;
+        chunk_tokens <= 1024, batch <= 256; meant for small batches, where it can use 512-token items without paying a CTA
+        start-up per item)."""
+        assert impl in ("simt", "tc", "tcp") and (impl == "simt" or chunk_tokens % 128 == 0)
+        assert impl != "tcp" or (chunk_tokens <= 1024 and max_batch <= 256)
         self.impl = impl
         self._C = load()
         self.device = torch.device(device)
@@ -28,6 +32,7 @@ class PagedAttention:
         self.counters = torch.zeros((max_batch * kv_heads,), dtype=torch.int32, device=self.device)
         self.status = new_status(self.device)
         self.max_batch = max_batch
+        self._persistent = 2 * torch.cuda.get_device_properties(self.device).multi_processor_count if impl == "tcp" else 0
 
     def __call__(self, q: torch.Tensor, pool: PagedKVPool, layer: int, block_table: torch.Tensor, ctx_lens: torch.Tensor,
                  max_ctx: Optional[int] = None, out: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
@@ -39,7 +44,8 @@ class PagedAttention:
                                   min(max_ctx or self.max_ctx, self.max_ctx), self.chunk_tokens,
                                   scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]),
                                   self.part_o, self.part_m, self.part_l, self.counters, self.status,
-                                  (pool.data.numel() - layer * ls) // 128 if self.impl == "tc" else 0)
+                                  (pool.data.numel() - layer * ls) // 128 if self.impl != "simt" else 0,
+                                  **({"persistent_ctas": self._persistent} if self._persistent else {}))
         return out
 
 
