@@ -82,7 +82,9 @@ def main():
     ap.add_argument("--ref", action="store_true")
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--pages-per-chunk", type=int, default=8)
+    ap.add_argument("--skip", default="", help="comma list of arm groups to leave out: paced, copy_engine, pairs, fanout, multimem")
     a = ap.parse_args()
+    skip = set(filter(None, a.skip.split(",")))
     assert a.gpus >= 2, "needs at least two GPUs"
     geom = ops.KVGeometry()
     g = torch.Generator().manual_seed(a.seed)
@@ -104,7 +106,7 @@ def main():
     ok = torch.equal(dsts[0].data[dp[:nb].long().to(dsts[0].data.device)], ops.reference_transfer(src, sp[:nb]).to(dsts[0].data.device))
     res["arms"]["kernel"]["exact"] = bool(ok)
     # paced arms
-    for pct in (75, 50, 25):
+    for pct in (() if "paced" in skip else (75, 50, 25)):
         page = ops.CreditPage(flow_id=pct, unlimited=False)
         pf = ops.KvTransferFlow("cuda:0", page=page, ctas=a.ctas or None, pages_per_chunk=a.pages_per_chunk, max_wait_ms=20.0)
         budget = unpaced * pct / 100.0
@@ -117,7 +119,7 @@ def main():
                                          "stall_ms_per_cta_sum": stall * 1e-6, "wall_s": wall}
     # baselines through the copy engine
     sdev, ddev = src.data.device, dsts[0].data.device
-    for name in ("memcpy_peer", "per_page"):
+    for name in (() if "copy_engine" in skip else ("memcpy_peer", "per_page")):
         tot_b, tot_s = 0, 0.0
         for i, nb in enumerate(blocks):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -138,7 +140,7 @@ def main():
     del src, dsts
     torch.cuda.empty_cache()
     # all pairs at once
-    if a.gpus >= 4:
+    if a.gpus >= 4 and "pairs" not in skip:
         pairs = [(2 * i, 2 * i + 1) for i in range(a.gpus // 2)]
         sets = [make_pair(s, [d], geom, max_blocks, a.seed + s) for s, d in pairs]
         flows = [ops.KvTransferFlow(f"cuda:{s}") for s, _ in pairs]
@@ -156,7 +158,7 @@ def main():
         torch.cuda.empty_cache()
     # fan-out from GPU0
     for k in sorted({min(a.gpus - 1, x) for x in (2, 4, 7)}):
-        if k < 2:
+        if k < 2 or "fanout" in skip:
             continue
         src, dsts, sp, dp = make_pair(0, list(range(1, k + 1)), geom, min(max_blocks, 1024), a.seed)
         fl = ops.KvTransferFlow("cuda:0")
@@ -169,6 +171,8 @@ def main():
         res["arms"][f"fanout_x{k}"] = {"egress_gbs": st["bytes_done"] / (st["device_time_ms"] * 1e-3) / 1e9, "frac_of_900": st["bytes_done"] / (st["device_time_ms"] * 1e-3) / 1e9 / 900.0, "exact": bool(ok)}
         # the same fan-out through an NVLink multicast address: the payload leaves GPU0 once, NVSwitch replicates it
         try:
+            if "multimem" in skip:
+                raise RuntimeError("left out by --skip multimem")
             team = [0] + list(range(1, k + 1))
             with ops.MulticastPools(geom, min(max_blocks, 1024), team) as mc:
                 for pool in mc.pools:

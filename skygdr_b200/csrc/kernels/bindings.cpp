@@ -105,6 +105,14 @@ static void credit_page_grant(uint64_t host_ptr, uint64_t granted, bool unlimite
     __atomic_store_n(&p->granted_bytes, granted, __ATOMIC_RELEASE);
     __atomic_store_n(&p->epoch, p->epoch + 1, __ATOMIC_RELEASE);
 }
+static void credit_page_heartbeat(uint64_t host_ptr, uint64_t window_ns, uint32_t dead_after_windows, uint32_t dead_policy,
+                                  uint64_t fallback_per_window) {
+    auto* p = (SkyCreditPage*)host_ptr;
+    p->window_ns = window_ns;
+    p->dead_policy = dead_policy;
+    p->fallback_per_window = fallback_per_window;
+    __atomic_store_n(&p->dead_after_windows, dead_after_windows, __ATOMIC_RELEASE);
+}
 static py::dict credit_page_read(uint64_t host_ptr) {
     auto* p = (SkyCreditPage*)host_ptr;
     py::dict d;
@@ -112,6 +120,8 @@ static py::dict credit_page_read(uint64_t host_ptr) {
     d["mode"] = p->mode; d["consumed_bytes"] = p->consumed_bytes; d["completed_bytes"] = p->completed_bytes;
     d["stall_ns"] = p->stall_ns; d["busy_ns"] = p->busy_ns; d["chunks"] = p->chunks; d["yields"] = p->yields;
     d["backlog_bytes"] = p->backlog_bytes; d["last_ts_ns"] = p->last_ts_ns;
+    d["heartbeat_lost"] = p->heartbeat_lost; d["heartbeat_lost_ns"] = p->heartbeat_lost_ns; d["window_ns"] = p->window_ns;
+    d["dead_after_windows"] = p->dead_after_windows; d["dead_policy"] = p->dead_policy;
     return d;
 }
 
@@ -155,7 +165,7 @@ static void kv_transfer(torch::Tensor src_pool, std::vector<uint64_t> dst_ptrs, 
                         int block_tokens, int head_dim, std::vector<int64_t> src_strides, std::vector<int64_t> dst_strides,
                         int heads_per_dst, bool replicate, bool fp8, bool keep_layout, int pages_per_chunk, int ctas, uint64_t credit_dev_ptr,
                         uint64_t consumed_base, uint64_t max_wait_ns, uint64_t first_chunk, uint32_t done_value, torch::Tensor status,
-                        bool use_tma, uint64_t multicast_ptr) {
+                        bool use_tma, uint64_t multicast_ptr, int src_num_blocks, int dst_num_blocks) {
     TORCH_CHECK(!(multicast_ptr && (use_tma || fp8 || !replicate)), "a multicast destination takes replicated bf16 pages from the register path");
     TORCH_CHECK(dst_ptrs.size() >= 1 && dst_ptrs.size() <= (size_t)KV_MAX_DST, "1..8 destinations");
     TORCH_CHECK(src_strides.size() == 3 && dst_strides.size() == 3, "strides are (block, layer, kv)");
@@ -170,6 +180,7 @@ static void kv_transfer(torch::Tensor src_pool, std::vector<uint64_t> dst_ptrs, 
         p.done_flag[i] = i < done_flag_ptrs.size() ? (unsigned int*)done_flag_ptrs[i] : nullptr;
     }
     p.mc_dst = (void*)multicast_ptr;
+    p.src_num_blocks = src_num_blocks; p.dst_num_blocks = dst_num_blocks;
     p.src_blocks = i32_ptr(src_blocks);
     p.dst_blocks = i32_ptr(dst_blocks);
     p.n_pairs = (int)src_blocks.numel();
@@ -214,7 +225,7 @@ static void memhog(torch::Tensor a, torch::Tensor b, int op, int iters, uint64_t
 static void paged_attn_decode(torch::Tensor q, torch::Tensor kv_layer, torch::Tensor out, torch::Tensor block_table, torch::Tensor ctx_lens,
                               int64_t block_stride, int64_t kv_stride, int64_t head_stride, int kv_heads, int max_ctx, int chunk_tokens,
                               double scale, torch::Tensor part_o, torch::Tensor part_m, torch::Tensor part_l, torch::Tensor counters,
-                              torch::Tensor status, int64_t pool_rows) {
+                              torch::Tensor status, int64_t pool_rows, int persistent_ctas) {
     c10::cuda::CUDAGuard g(q.device());
     TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && out.is_contiguous(), "q/out: contiguous [batch][heads][128]");
     PagedAttnParams p;
@@ -231,7 +242,8 @@ static void paged_attn_decode(torch::Tensor q, torch::Tensor kv_layer, torch::Te
     p.part_o = part_o.data_ptr<float>(); p.part_m = part_m.data_ptr<float>(); p.part_l = part_l.data_ptr<float>();
     p.counters = reinterpret_cast<unsigned int*>(counters.data_ptr());
     p.status = status_ptr(status);
-    if (pool_rows > 0) SKY_CUDA_CHECK(launch_paged_attn_decode_tc(p, pool_rows, cur_stream()));
+    TORCH_CHECK(persistent_ctas == 0 || pool_rows > 0, "the persistent variant is the tensor-core kernel: give pool_rows");
+    if (pool_rows > 0) SKY_CUDA_CHECK(launch_paged_attn_decode_tc(p, pool_rows, cur_stream(), persistent_ctas));
     else SKY_CUDA_CHECK(launch_paged_attn_decode(p, cur_stream()));
 }
 
@@ -403,6 +415,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("credit_page_init", &credit_page_init);
     m.def("credit_page_grant", &credit_page_grant);
     m.def("credit_page_read", &credit_page_read);
+    m.def("credit_page_heartbeat", &credit_page_heartbeat);
     m.def("ipc_alloc", &ipc_alloc);
     m.def("ipc_open", &ipc_open);
     m.def("ipc_close", &ipc_close);
@@ -414,7 +427,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("heads"), py::arg("block_tokens"), py::arg("head_dim"), py::arg("src_strides"), py::arg("dst_strides"),
           py::arg("heads_per_dst"), py::arg("replicate"), py::arg("fp8"), py::arg("keep_layout"), py::arg("pages_per_chunk"),
           py::arg("ctas"), py::arg("credit_dev_ptr"), py::arg("consumed_base"), py::arg("max_wait_ns"), py::arg("first_chunk"),
-          py::arg("done_value"), py::arg("status"), py::arg("use_tma"), py::arg("multicast_ptr") = 0);
+          py::arg("done_value"), py::arg("status"), py::arg("use_tma"), py::arg("multicast_ptr") = 0,
+          py::arg("src_num_blocks") = 0, py::arg("dst_num_blocks") = 0);
     m.def("multicast_supported", [](int device) {
         std::string why;
         bool ok = multicast_supported(device, &why);
@@ -433,7 +447,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     }, py::return_value_policy::reference);
     m.def("multicast_destroy", [](MulticastRegion* r) { multicast_destroy(r); });
     m.def("memhog", &memhog, py::call_guard<py::gil_scoped_release>());
-    m.def("paged_attn_decode", &paged_attn_decode);
+    m.def("paged_attn_decode", &paged_attn_decode, py::arg("q"), py::arg("kv_layer"), py::arg("out"), py::arg("block_table"), py::arg("ctx_lens"),
+          py::arg("block_stride"), py::arg("kv_stride"), py::arg("head_stride"), py::arg("kv_heads"), py::arg("max_ctx"), py::arg("chunk_tokens"),
+          py::arg("scale"), py::arg("part_o"), py::arg("part_m"), py::arg("part_l"), py::arg("counters"), py::arg("status"), py::arg("pool_rows"),
+          py::arg("persistent_ctas") = 0);
     m.def("rmsnorm", &rmsnorm);
     m.def("rope_append", &rope_append);
     m.def("silu_mul", &silu_mul);

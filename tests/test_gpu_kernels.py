@@ -1,5 +1,6 @@
 """Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
 import math
+import time
 
 import pytest
 import torch
@@ -116,6 +117,59 @@ def test_kv_transfer_credit_yield_and_resume(ops, method):
     assert flow.result()["status_name"] == "STOPPED"
 
 
+@pytest.mark.parametrize("method", ["simt", "tma"])
+def test_kv_transfer_rejects_block_ids_outside_the_pools(ops, method):
+    """A corrupted block list (made on the host) never becomes an out-of-range access: the kernel checks every block id
+    against the pool sizes, skips the page, and reports BAD_INDEX with the position of the offending pair."""
+    g, src, dst = _pools(ops, layers=2)
+    dst.data.fill_(-2.0)
+    sb = torch.tensor([3, 5, 7, 9], device="cuda").int()
+    db = torch.tensor([0, 1, 2, 3], device="cuda").int()
+    for bad_src, bad_dst, where in ((1000, 1, 1), (5, 48, 1), (-1, 2, 2)):
+        sb2, db2 = sb.clone(), db.clone()
+        sb2[where], db2[where] = bad_src, bad_dst
+        flow = ops.KvTransferFlow("cuda", pages_per_chunk=4, method=method)
+        flow.transfer(src, [ops.RemotePool.of(dst)], sb2, db2)
+        st = flow.result()
+        assert st["status_name"] == "BAD_INDEX" and st["detail"] == where, st
+    assert bool((dst.data[4:] == -2.0).all())                     # nothing beyond the named destination blocks was written
+    flow = ops.KvTransferFlow("cuda", method=method)              # and a clean list still goes through
+    flow.transfer(src, [ops.RemotePool.of(dst)], sb, db)
+    assert flow.result()["status"] == 0
+    assert torch.equal(dst.data[db.long()], ops.reference_transfer(src, sb))
+
+
+@pytest.mark.parametrize("policy", ["stall", "unpaced", "static"])
+def test_kv_transfer_follows_the_page_when_the_control_side_goes_silent(ops, policy):
+    """Nothing renews the grant (a control side that died: made on the host by simply not granting). The kernel waits
+    for credit, sees the epoch stand still for 5 windows of 1 ms, and follows the page's dead policy; every wait is bounded."""
+    g, src, dst = _pools(ops, layers=2)
+    n = 20
+    sb = torch.arange(n, device="cuda").int()
+    db = torch.arange(n, device="cuda").int()
+    total = ops.link_bytes(g, n)
+    page = ops.CreditPage(flow_id=9, unlimited=False)
+    page.set_heartbeat(window_ms=1.0, dead_after_windows=5, policy=policy, fallback_gbps=total / 1e9 / 0.004)   # static: all of it in 4 windows
+    page.grant(total // 4)
+    flow = ops.KvTransferFlow("cuda", page=page, pages_per_chunk=2, max_wait_ms=200.0, method="simt")
+    t0 = time.perf_counter()
+    flow.transfer(src, [ops.RemotePool.of(dst)], sb, db)
+    st = flow.result()
+    wall = time.perf_counter() - t0
+    rd = page.read()
+    assert rd["heartbeat_lost"] == rd["epoch"] + 1                # the data path flagged the silence in the page
+    assert wall < 0.15                                            # decided after ~5 ms, far below the 200 ms credit wait
+    if policy == "stall":
+        assert st["status_name"] == "CONTROL_LOST" and 0 < st["bytes_done"] <= total // 4
+        page.grant(total)                                         # the control side is back: resume from the cursor
+        flow.resume(st)
+        st2 = flow.result()
+        assert st2["status"] == 0 and st["bytes_done"] + st2["bytes_done"] == total
+    else:
+        assert st["status"] == 0 and st["bytes_done"] == total
+    assert torch.equal(dst.data[db.long()], ops.reference_transfer(src, sb))
+
+
 def test_kv_offload_to_mapped_host(ops):
     from skygdr_b200._ext import load
     from skygdr_b200.ops.kv_transfer import RemotePool
@@ -169,7 +223,7 @@ def test_memhog_duty_cycle_and_time_limit(ops):
     assert 0.3 < half["bytes_done"] / full["bytes_done"] < 0.75
 
 
-@pytest.mark.parametrize("impl", ["simt", "tc"])
+@pytest.mark.parametrize("impl", ["simt", "tc", "tcp"])
 @pytest.mark.parametrize("kv_heads,q_heads", [(8, 32), (1, 4), (2, 4), (4, 4), (1, 8)])
 def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
     torch.manual_seed(1)
@@ -196,6 +250,37 @@ def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
         assert ops.read_status(attn.status)["status"] == 0
         assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
     # counters are left at zero for the next launch
+    assert int(attn.counters.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("chunk", [512, 1024])
+def test_persistent_attention_walks_many_items_per_cta(ops, chunk):
+    """More work items than CTAs (48 sequences x up to 5 splits x 8 KV heads against 296 CTAs): every CTA runs several items
+    back to back, so barrier phases, the K/V ring and the Q tile carry over item boundaries. Two launches in a row."""
+    torch.manual_seed(3)
+    g = ops.KVGeometry(layers=1, kv_heads=8)
+    ctx = torch.randint(1, 2400, (48,), dtype=torch.int32, device="cuda")
+    ctx[:4] = torch.tensor([1, 128, 129, 2399], dtype=torch.int32)
+    B = ctx.numel()
+    max_blocks = (2400 + 15) // 16 + 8
+    nblk = int(((ctx + 15) // 16).sum()) + 4
+    pool = ops.PagedKVPool(g, nblk, "hnd")
+    pool.data.normal_()
+    perm = torch.randperm(nblk, device="cuda").int()
+    table = torch.zeros((B, max_blocks), dtype=torch.int32, device="cuda")
+    o = 0
+    for b in range(B):
+        nb = (int(ctx[b]) + 15) // 16
+        table[b, :nb] = perm[o:o + nb]
+        o += nb
+    q = torch.randn((B, 32, 128), dtype=torch.bfloat16, device="cuda")
+    attn = ops.PagedAttention("cuda", B, 32, 8, max_ctx=2400, chunk_tokens=chunk, impl="tcp")
+    ref = ops.paged_attn_reference(q, pool, 0, table, ctx)
+    for _ in range(2):
+        out = attn(q, pool, 0, table, ctx)
+        torch.cuda.synchronize()
+        assert ops.read_status(attn.status)["status"] == 0
+        assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
     assert int(attn.counters.abs().sum()) == 0
 
 
