@@ -112,6 +112,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--log_dir", required=True)
     ap.add_argument("--tag", default="case_study")
     ap.add_argument("--policy", default="ladder", choices=["ladder", "target_track", "none", "static"])
+    ap.add_argument("--pcie_bin", default="", help="program of the protected flow (reference flag); default: this package's gpu_pcie_memcpy")
+    ap.add_argument("--gpu_metrics_script", default="", help="signal logger script (reference flag); default: this package's gpu_metrics_logger")
     ap.add_argument("--restore_cmd", default="", help="override the protected-flow command (must write the progress CSV given by {progress})")
     ap.add_argument("--metrics_cmd", default="", help="override the signal command (must write the metrics CSV given by {metrics})")
     ap.add_argument("--min_poll_ms", type=int, default=5)
@@ -140,11 +142,13 @@ def main(argv=None) -> int:
         return 2
     response = send_control(a.cpu_control_host, a.cpu_control_port, "HIGH")
     run_start = int(time.time() * 1000)
+    metrics_head = [a.python_bin, a.gpu_metrics_script] if a.gpu_metrics_script else [a.python_bin, "-m", "skygdr_b200.cli.gpu_metrics_logger"]
+    restore_head = [a.pcie_bin] if a.pcie_bin else [a.python_bin, "-m", "skygdr_b200.cli.gpu_pcie_memcpy"]
     metrics_cmd = (a.metrics_cmd.format(metrics=metrics_csv).split() if a.metrics_cmd else
-                   [a.python_bin, "-m", "skygdr_b200.cli.gpu_metrics_logger", "--gpu", str(a.gpu), "--interval_ms",
+                   [*metrics_head, "--gpu", str(a.gpu), "--interval_ms",
                     str(a.gpu_metrics_interval_ms), "--out", metrics_csv])
     restore_cmd = (a.restore_cmd.format(progress=progress_csv).split() if a.restore_cmd else
-                   [a.python_bin, "-m", "skygdr_b200.cli.gpu_pcie_memcpy", f"--device={a.device}", "--seconds=0", f"--dir={a.dir}",
+                   [*restore_head, f"--device={a.device}", "--seconds=0", f"--dir={a.dir}",
                     f"--chunk_mb={a.chunk_mb}", f"--streams={a.streams}", f"--batch={a.batch}", f"--inflight={a.inflight}",
                     f"--pinned={a.pinned}", f"--total_bytes={total_bytes}", f"--max_outstanding_bytes={a.restore_max_outstanding_bytes}",
                     f"--progress_ms={a.progress_ms}", f"--progress_smooth_windows={a.progress_smooth_windows}",

@@ -28,6 +28,7 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--tile-tokens", type=int, default=1024)
     ap.add_argument("--ffn-dim", type=int, default=12288)
+    ap.add_argument("--ffn-blocks", type=int, default=512, help="accepted for compatibility with the transformer-style stressor; unused")
     ap.add_argument("--threads", type=int, default=128)
     ap.add_argument("--report-every", type=int, default=16)
     ap.add_argument("--mode", default="attention", choices=["attention", "model"])

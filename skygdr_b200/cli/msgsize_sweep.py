@@ -41,8 +41,11 @@ def client_cmd(a, msg: int, iters: int):
 
     exe = os.path.join(build.build_bin(), "cpu_client")
     # positional tail in the reference's order: qd span pattern align mtu sample max_samples ts_ms ts_out write_ack read_min_qd rd_atomic qps
-    return [exe, a.server_ip, str(a.tcp_port), a.fabric, str(iters), str(msg), a.op, "1", "0", str(a.qd), str(a.span), a.pattern,
-            str(a.align), "1024", str(a.sample), "0", "0", "", str(a.write_ack), "16", "0", str(a.qps)]
+    fabric = a.ib_dev or a.fabric                 # the reference's --ib_dev names the device; here it names the fabric (sim:<GB/s>, tcp)
+    write_ack = 1 if a.write_ack is None else a.write_ack
+    return [exe, a.server_ip, str(a.tcp_port), fabric, str(iters), str(msg), a.op, str(a.port), str(a.gid_idx), str(a.qd), str(a.span),
+            a.pattern, str(a.align), str(a.mtu), str(a.sample), str(a.max_samples), str(a.ts_ms), a.ts_out, str(write_ack),
+            str(16 if a.read_min_qd is None else a.read_min_qd), str(a.rd_atomic or 0), str(a.qps)]
 
 
 def main(argv=None) -> int:
@@ -58,7 +61,19 @@ def main(argv=None) -> int:
     ap.add_argument("--pattern", default="random")
     ap.add_argument("--align", type=int, default=256)
     ap.add_argument("--sample", type=int, default=1)
-    ap.add_argument("--write_ack", type=int, default=1)
+    ap.add_argument("--write_ack", type=int, choices=[0, 1], default=None)
+    # the rest of the reference's flag set (src/tools/rdma_msgsize_sweep.py:101-127), passed through to the client's positional tail
+    ap.add_argument("--cpu_client", default="", help="accepted for compatibility; the in-tree client is used")
+    ap.add_argument("--ib_dev", default="", help="fabric name: sim:<GB/s> or tcp (takes the place of the verbs device)")
+    ap.add_argument("--port", type=int, default=1)
+    ap.add_argument("--gid_idx", type=int, default=0)
+    ap.add_argument("--mtu", type=int, default=1024)
+    ap.add_argument("--max_samples", type=int, default=0)
+    ap.add_argument("--ts_ms", type=int, default=0)
+    ap.add_argument("--ts_out", default="")
+    ap.add_argument("--write_ack_batch", type=int, default=None, help="deprecated in the reference too; ignored")
+    ap.add_argument("--read_min_qd", type=int, default=None)
+    ap.add_argument("--rd_atomic", type=int, default=None)
     ap.add_argument("--msg_sizes", default="64,4K,64K,1M")
     ap.add_argument("--warmup_iters", type=int, default=200)
     ap.add_argument("--warmup_runs", type=int, default=1)

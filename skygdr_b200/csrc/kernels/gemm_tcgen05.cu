@@ -312,14 +312,14 @@ template <int NTOK, bool GATED>
 static cudaError_t launch_t(const GemmParams& p, const CUtensorMap& tw, const CUtensorMap& tx, cudaStream_t stream) {
     using S = GemmSmem<NTOK, GATED>;
     auto kern = gemm_tcgen05_kernel<NTOK, GATED>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
+    // SKYGDR_GEMM_ONE_PER_SM=1 pads the request of the small-stage kernels so that only one CTA fits on an SM (a switch for
+    // measuring what co-residency is worth; the kernel itself does not change).
+    static const bool one_per_sm = [] { const char* v = getenv("SKYGDR_GEMM_ONE_PER_SM"); return v && v[0] == '1'; }();
+    const int dyn = (S::TWO_PER_SM && one_per_sm) ? (S::TOTAL > 120 * 1024 ? S::TOTAL : 120 * 1024) : S::TOTAL;
+    static unsigned long long attr_mask = 0;
+    if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), dyn, &attr_mask); e != cudaSuccess) return e;
     dim3 grid((p.N + BM - 1) / BM, (p.M + NTOK - 1) / NTOK, p.splits);
-    return launch_pdl(kern, grid, dim3(GEMM_THREADS), (size_t)S::TOTAL, stream, tw, tx, p);
+    return launch_pdl(kern, grid, dim3(GEMM_THREADS), (size_t)dyn, stream, tw, tx, p);
 }
 
 int gemm_pick_ntok(int M, bool gated) {

@@ -177,12 +177,8 @@ cudaError_t launch_kv_transfer_tma(const KvTransferParams& p, long long pool_ele
            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
     constexpr int smem_bytes = SLOTS * SLOT_BYTES + 128;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(kv_transfer_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
+    static unsigned long long attr_mask = 0;
+    if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kv_transfer_tma_kernel), smem_bytes, &attr_mask); e != cudaSuccess) return e;
     kv_transfer_tma_kernel<<<ctas, TMA_THREADS, smem_bytes, stream>>>(tm, p);
     return cudaGetLastError();
 }

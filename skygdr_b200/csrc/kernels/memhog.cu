@@ -81,7 +81,9 @@ __global__ void __launch_bounds__(512) memhog_kernel(const MemhogParams p) {
                         now = globaltimer_ns();
                     }
                 }
-                if (p.duration_ns && now - t0 >= p.duration_ns) go = 0;
+                // The time limit counts from the first CTA's start, not this one's: with more CTAs than fit on the GPU at
+                // once, the late ones must not each run a full period of their own.
+                if (p.duration_ns && now - *(volatile unsigned long long*)&p.status->t_start_ns >= p.duration_ns) go = 0;
                 if (go && p.page) {
                     // all CTAs advance together, so the flow has consumed about seq*grid+block chunks
                     unsigned long long need = p.consumed_base + ((seq * gridDim.x) + blockIdx.x + 1) * p.chunk_vec * bytes_per_vec;

@@ -286,12 +286,8 @@ static cudaError_t launch_g(const PagedAttnParams& p, cudaStream_t stream) {
     constexpr int smem_bytes = ATT_WARPS * STAGES * 2 * T * ATT_D * 2;
     static_assert(smem_bytes >= (int)((2 * ATT_WARPS * G + ATT_WARPS * G * ATT_D) * sizeof(float)), "merge area must fit in the ring");
     auto kern = paged_attn_decode_kernel<G, T, STAGES>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
+    static unsigned long long attr_mask = 0;
+    if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), smem_bytes, &attr_mask); e != cudaSuccess) return e;
     dim3 grid((p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens, p.kv_heads, p.batch);
     return launch_pdl(kern, grid, dim3(ATT_WARPS * 32), (size_t)smem_bytes, stream, p);
 }

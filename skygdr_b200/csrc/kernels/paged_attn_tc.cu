@@ -656,24 +656,16 @@ __global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tcp_kernel(const __g
 template <int G>
 cudaError_t launch_tcp_g(const PagedAttnParams& p, const CUtensorMap& tm, int ctas, cudaStream_t stream) {
     auto kern = paged_attn_tcp_kernel<G>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
+    static unsigned long long attr_mask = 0;
+    if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), TC_SMEM, &attr_mask); e != cudaSuccess) return e;
     return launch_pdl(kern, dim3(ctas), dim3(TC_THREADS), (size_t)TC_SMEM, stream, tm, p);
 }
 
 template <int G>
 cudaError_t launch_tc_g(const PagedAttnParams& p, const CUtensorMap& tm, cudaStream_t stream) {
     auto kern = paged_attn_tc_kernel<G>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
+    static unsigned long long attr_mask = 0;
+    if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), TC_SMEM, &attr_mask); e != cudaSuccess) return e;
     dim3 grid((p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens, p.kv_heads, p.batch);
     return launch_pdl(kern, grid, dim3(TC_THREADS), (size_t)TC_SMEM, stream, tm, p);
 }

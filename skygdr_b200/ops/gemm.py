@@ -1,6 +1,7 @@
 """bf16 GEMM on tcgen05 tensor cores (skygdr_b200/csrc/kernels/gemm_tcgen05.cu)."""
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -23,14 +24,34 @@ def pick_splits(M: int, N: int, K: int, sms: int, gated: bool = False) -> int:
     return pick_config(M, N, K, sms, gated, fixed_ntok=load().gemm_pick_ntok(M, gated))[1]
 
 
-def pick_config(M: int, N: int, K: int, sms: int, gated: bool = False, fixed_ntok: int = 0) -> Tuple[int, int]:
+@dataclass(frozen=True)
+class GemmCostModel:
+    """Constants of the tile/split chooser (microseconds, bytes per microsecond)."""
+    fixed_alone: float          # prologue + epilogue of a CTA that has its SM to itself
+    fixed_shared: float         # ... of a CTA that shares the SM with another
+    rate_alone: float           # stream rate of a CTA alone on its SM
+    rate_shared: float          # ... of each of two co-resident CTAs
+    two_per_sm: bool            # count two CTA slots per SM for small pipeline stages
+    part_write_rate: float      # a split writes its fp32 partial at this rate (inf = free)
+    part_read_rate: float       # the last CTA of a tile re-reads all partials at this rate
+    hbm_rate: float = 5.5e6
+
+
+# Fitted to a measured sweep of the decoder's GEMM shapes run alone on B200 (token tiles 16-128, 1-16 splits, L2 flushed).
+STANDALONE = GemmCostModel(3.0, 2.0, 55e3, 45e3, True, float("inf"), 50e3)
+# The fused tensor-parallel GEMMs wait for all-gather arrivals and raise reduce-scatter arrivals per token tile and finish a split
+# tile with one more dependent step before the push, so fewer, larger CTAs win there. These are the constants under which the
+# tensor-parallel decode step was tuned end to end (TP 2 / 4 / 8); the stand-alone fit costs it 3 % at TP 2 and 15 % at TP 8.
+FUSED_TP = GemmCostModel(6.0, 6.0, 55e3, 55e3, False, 100e3, 200e3)
+
+
+def pick_config(M: int, N: int, K: int, sms: int, gated: bool = False, fixed_ntok: int = 0,
+                model: GemmCostModel = STANDALONE) -> Tuple[int, int]:
     """(token tile, split-K factor) for y[M][N] = x[M][K] w[N][K]^T with small M.
 
     The time is about waves x (fixed cost per CTA + bytes per CTA / stream rate of a CTA), bounded below by total bytes
     over the HBM rate; a split adds its fp32 partial (written, then re-read by the last CTA of the tile). A pipeline of
-    small stages fits two CTAs on an SM, which then share the SM's stream rate. The constants minimise the regret
-    against a measured sweep of the decoder's shapes at 1, 2 and 8 tensor-parallel ranks on B200 (token tiles 16-128,
-    1-16 splits): 2-3 us fixed per CTA, 55 GB/s for a CTA alone on its SM, 45 GB/s each for two, 5.5 TB/s per GPU."""
+    small stages fits two CTAs on an SM, which then share the SM's stream rate."""
     wrows = 2 if gated else 1
     kb = K // 64
     cands = [fixed_ntok] if fixed_ntok else [n for n in (16, 32, 64, 128, 256) if n >= 16 and (n < 2 * M or n == 16) and not (gated and n > 128)]
@@ -43,17 +64,18 @@ def pick_config(M: int, N: int, K: int, sms: int, gated: bool = False, fixed_nto
                 break
             per = (kb + s - 1) // s
             s_eff = (kb + per - 1) // per
-            if s_eff != s:
+            if s_eff != s and model.two_per_sm:
                 continue                               # the same partition as a smaller s
             ctas = tiles_n * tiles_m * s_eff
             stage = 128 * 64 * 2 * wrows + ntok * 64 * 2
-            two = 3 * stage <= 104 * 1024              # the kernel fits two CTAs per SM for small stages
+            two = model.two_per_sm and 3 * stage <= 104 * 1024     # the kernel fits two CTAs per SM for small stages
             slots = sms * (2 if two else 1)
             waves = (ctas + slots - 1) // slots
             shared = two and ctas > sms                # two co-resident CTAs share the SM's stream rate
             part = ntok * 128 * 4 * wrows
-            t_cta = (2.0 if shared else 3.0) + per * stage / (45e3 if shared else 55e3) + (1.0 + s_eff * part / 50e3 if s_eff > 1 else 0.0)
-            hbm = (tiles_n * 128 * K * 2 * wrows + M * K * 2) / 5.5e6
+            split_cost = part / model.part_write_rate + 1.0 + s_eff * part / model.part_read_rate if s_eff > 1 else 0.0
+            t_cta = (model.fixed_shared if shared else model.fixed_alone) + per * stage / (model.rate_shared if shared else model.rate_alone) + split_cost
+            hbm = (tiles_n * 128 * K * 2 * wrows + M * K * 2) / model.hbm_rate
             t = max(waves * t_cta, hbm)
             if t < best_t * 0.92:                      # simpler shapes come first; a rival must be clearly better
                 best, best_t = (ntok, s_eff), t

@@ -22,7 +22,7 @@ from .. import ops
 from .._ext import load
 from ..models.qwen3 import Qwen3Config, Qwen3Decoder, Qwen3Weights
 from ..ops.flow import new_status, read_status
-from ..ops.gemm import GemmWorkspace, pick_config
+from ..ops.gemm import FUSED_TP, GemmWorkspace, pick_config
 from ..ops.kv_cache import KVGeometry, PagedKVPool
 from .symm import SymmetricHeap
 
@@ -106,7 +106,7 @@ class TPDecoder:
     def _gemm(self, x, w, y, gated=False, ag=(), rs=()):
         M, K = x.shape
         N = w.shape[0] // 2 if gated else w.shape[0]
-        ntok, splits = pick_config(M, N, K, 148, gated)
+        ntok, splits = pick_config(M, N, K, 148, gated, model=FUSED_TP)
         if splits > 1:
             self.ws.ensure(self._C.gemm_workspace_floats(M, N, splits, gated, ntok), self._C.gemm_counter_count(M, N, gated, ntok))
             self._C.gemm_tp(x, w, y, splits, gated, self.ws.ws, self.ws.counters, self.status, ag, rs, ntok)
@@ -115,7 +115,7 @@ class TPDecoder:
 
     def _rs_arrivals(self, K: int) -> int:
         """Arrivals one reduce-scatter adds to a rank's counter: every output tile of every rank's GEMM."""
-        ntok, _ = pick_config(self.batch, self.cfg.hidden, K, 148, False)
+        ntok, _ = pick_config(self.batch, self.cfg.hidden, K, 148, False, model=FUSED_TP)
         return self.world * self.tiles_h * ((self.batch + ntok - 1) // ntok)
 
     def set_batch(self, ids: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor) -> None:
