@@ -61,14 +61,17 @@ constexpr int GEMM_THREADS = 192;
 constexpr int BM = 128;   // weight rows per tile (MMA M)
 constexpr int BK = 64;    // K per stage: 64 bf16 = 128 bytes = one swizzle row
 
-template <int NTOK, bool GATED>
+// DEEP: one CTA per SM with the deepest pipeline that fits (up to 8 stages). The fused tensor-parallel GEMMs use it: their
+// producer streams weight tiles while the CTA waits for its all-gather arrivals, so every extra stage is weight traffic hidden
+// behind the wait (measured: TP 2 decode 8.82 ms per step with 8 stages, 9.13-9.16 ms with the 5 stages of the shared layout).
+template <int NTOK, bool GATED, bool DEEP = false>
 struct GemmSmem {
     static constexpr int W_BYTES = BM * BK * 2;
     static constexpr int X_BYTES = NTOK * BK * 2;
     static constexpr int STAGE_BYTES = W_BYTES * (GATED ? 2 : 1) + X_BYTES;
     // Two CTAs per SM where three stages fit in half an SM's shared memory: while one CTA is in its prologue or
     // epilogue the other keeps the SM's share of the weight stream going.
-    static constexpr bool TWO_PER_SM = 3 * STAGE_BYTES <= 104 * 1024;
+    static constexpr bool TWO_PER_SM = !DEEP && 3 * STAGE_BYTES <= 104 * 1024;
     static constexpr int BUDGET = TWO_PER_SM ? 104 * 1024 : 200 * 1024;
     static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024;  // + alignment slack
@@ -76,10 +79,10 @@ struct GemmSmem {
     static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;
 };
 
-template <int NTOK, bool GATED>
-__global__ void __launch_bounds__(GEMM_THREADS, (GemmSmem<NTOK, GATED>::TWO_PER_SM ? 2 : 1))
+template <int NTOK, bool GATED, bool DEEP>
+__global__ void __launch_bounds__(GEMM_THREADS, (GemmSmem<NTOK, GATED, DEEP>::TWO_PER_SM ? 2 : 1))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
-    using S = GemmSmem<NTOK, GATED>;
+    using S = GemmSmem<NTOK, GATED, DEEP>;
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint64_t full_bar[8], empty_bar[8], acc_bar;
     __shared__ uint32_t tmem_slot;
@@ -308,10 +311,10 @@ bool make_tmap_bf16_2d(CUtensorMap* m, const void* base, long long rows, long lo
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int NTOK, bool GATED>
+template <int NTOK, bool GATED, bool DEEP>
 static cudaError_t launch_t(const GemmParams& p, const CUtensorMap& tw, const CUtensorMap& tx, cudaStream_t stream) {
-    using S = GemmSmem<NTOK, GATED>;
-    auto kern = gemm_tcgen05_kernel<NTOK, GATED>;
+    using S = GemmSmem<NTOK, GATED, DEEP>;
+    auto kern = gemm_tcgen05_kernel<NTOK, GATED, DEEP>;
     // SKYGDR_GEMM_ONE_PER_SM=1 pads the request of the small-stage kernels so that only one CTA fits on an SM (a switch for
     // measuring what co-residency is worth; the kernel itself does not change).
     static const bool one_per_sm = [] { const char* v = getenv("SKYGDR_GEMM_ONE_PER_SM"); return v && v[0] == '1'; }();
@@ -350,14 +353,16 @@ cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream) {
     const long long w_rows = p.gated ? 2LL * p.N : p.N;
     if (!make_tmap_bf16_2d(&tw, p.w, w_rows, p.K, p.ldw, BM)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16_2d(&tx, p.x, p.M, p.K, p.ldx, ntok)) return cudaErrorInvalidValue;
+    const bool deep = p.ag.n_src > 0 || p.rs.world > 0;     // fused tensor-parallel GEMM: one CTA per SM, deepest pipeline
 #define SKY_GEMM_CASE(NT)                                                                   \
-    case NT: return p.gated ? launch_t<NT, true>(p, tw, tx, stream) : launch_t<NT, false>(p, tw, tx, stream);
+    case NT: return deep ? (p.gated ? launch_t<NT, true, true>(p, tw, tx, stream) : launch_t<NT, false, true>(p, tw, tx, stream))   \
+                         : (p.gated ? launch_t<NT, true, false>(p, tw, tx, stream) : launch_t<NT, false, false>(p, tw, tx, stream));
     switch (ntok) {
         SKY_GEMM_CASE(16)
         SKY_GEMM_CASE(32)
         SKY_GEMM_CASE(64)
         SKY_GEMM_CASE(128)
-        default: return p.gated ? cudaErrorInvalidValue : launch_t<256, false>(p, tw, tx, stream);
+        default: return p.gated ? cudaErrorInvalidValue : launch_t<256, false, false>(p, tw, tx, stream);
     }
 #undef SKY_GEMM_CASE
 }

@@ -72,6 +72,12 @@ def test_pick_config_rules(monkeypatch):
     assert g.pick_config(16, 151936, 4096, 148)[1] == 1                          # many tiles: never split
     assert g.pick_config(128, 768, 4096, 148)[1] > 1                             # six tiles: must split
     assert g.pick_config(16, 6144, 4096, 148, fixed_ntok=16)[0] == 16
+    # the fused tensor-parallel GEMMs keep the tile/split choices under which the TP step was tuned end to end
+    tuned = {(128, 768, 4096, False): (32, 5), (128, 4096, 512, False): (32, 1), (128, 1536, 4096, True): (64, 5), (128, 4096, 1536, False): (64, 2),
+             (32, 3072, 4096, False): (32, 5), (32, 4096, 2048, False): (32, 4), (32, 6144, 4096, True): (32, 3), (32, 4096, 6144, False): (32, 4)}
+    for (M, N, K, gated), want in tuned.items():
+        assert g.pick_config(M, N, K, 148, gated, model=g.FUSED_TP) == want
+    assert g.pick_config(128, 768, 4096, 148)[0] == 16                           # alone, small token tiles win
 
 
 def test_attention_oracle_matches_dense_softmax():
