@@ -16,6 +16,7 @@
 #include "multicast.h"
 #include "paged_attn.h"
 #include "pcie_task.h"
+#include "prefill_attn.h"
 #include "tp_fused.h"
 
 namespace py = pybind11;
@@ -198,6 +199,24 @@ static void kv_transfer(torch::Tensor src_pool, std::vector<uint64_t> dst_ptrs, 
     if (p.n_pairs == 0) return;
     if (use_tma) SKY_CUDA_CHECK(launch_kv_transfer_tma(p, src_pool.numel(), ctas, cur_stream()));
     else SKY_CUDA_CHECK(launch_kv_transfer(p, ctas, cur_stream()));
+}
+
+// ---- causal prefill attention over the paged pool ----
+static void prefill_attn(torch::Tensor q, torch::Tensor kv_layer, torch::Tensor out, torch::Tensor block_table, torch::Tensor seq_start,
+                         int64_t block_stride, int64_t kv_stride, int64_t head_stride, int64_t tok_stride, int kv_heads, int max_len, double scale,
+                         torch::Tensor status, int64_t pool_rows) {
+    c10::cuda::CUDAGuard g(q.device());
+    TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous() && out.is_contiguous() && out.sizes() == q.sizes(), "q/out: contiguous [tokens][heads][128]");
+    TORCH_CHECK(block_table.dim() == 2 && seq_start.numel() == block_table.size(0) + 1, "seq_start holds n_seqs + 1 offsets");
+    PrefillAttnParams p;
+    memset(&p, 0, sizeof p);
+    p.q = bf16_ptr(q); p.kv = bf16_ptr(kv_layer); p.out = bf16_mut(out);
+    p.block_table = i32_ptr(block_table); p.seq_start = i32_ptr(seq_start);
+    p.block_stride = block_stride; p.kv_stride = kv_stride; p.head_stride = head_stride; p.tok_stride = tok_stride;
+    p.n_seqs = (int)block_table.size(0); p.q_heads = (int)q.size(1); p.kv_heads = kv_heads; p.max_blocks = (int)block_table.size(1);
+    p.max_len = max_len; p.total_tokens = (int)q.size(0); p.scale = (float)scale;
+    p.status = status_ptr(status);
+    SKY_CUDA_CHECK(launch_prefill_attn_tc(p, pool_rows, cur_stream()));
 }
 
 // ---- memhog ----
@@ -451,6 +470,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("block_stride"), py::arg("kv_stride"), py::arg("head_stride"), py::arg("kv_heads"), py::arg("max_ctx"), py::arg("chunk_tokens"),
           py::arg("scale"), py::arg("part_o"), py::arg("part_m"), py::arg("part_l"), py::arg("counters"), py::arg("status"), py::arg("pool_rows"),
           py::arg("persistent_ctas") = 0);
+    m.def("prefill_attn", &prefill_attn);
     m.def("rmsnorm", &rmsnorm);
     m.def("rope_append", &rope_append);
     m.def("silu_mul", &silu_mul);

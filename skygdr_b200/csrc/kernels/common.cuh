@@ -282,7 +282,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 
-}  // namespace sky// Raises a kernel's dynamic shared memory limit once per device: the attribute belongs to the (function, device) pair, and one
+// Raises a kernel's dynamic shared memory limit once per device: the attribute belongs to the (function, device) pair, and one
 // process may drive several GPUs. `done_mask` is a per-kernel static, one bit per device ordinal.
 inline cudaError_t set_max_dynamic_smem_once(const void* func, int bytes, unsigned long long* done_mask) {
     int dev = 0;
@@ -295,4 +295,4 @@ inline cudaError_t set_max_dynamic_smem_once(const void* func, int bytes, unsign
     return e;
 }
 
-
+}  // namespace sky

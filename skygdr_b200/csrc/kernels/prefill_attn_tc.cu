@@ -1,0 +1,322 @@
+// Causal prefill attention on the 5th-generation tensor cores, reading K and V straight from the paged pool.
+//
+// One CTA per (query tile of 128 tokens, query head, prompt). Query rows are the MMA's M, so TMEM lane t holds query
+// row t and the softmax of a row lives in one thread: no shuffles, no exchange through shared memory.
+//
+//   warp 4   : TMA producer. Q tile once (two boxes of [128 tokens] x [64 dims]); then per key tile of 128 tokens
+//              K and V, each as 8 pages x 2 dim halves of [16 tokens] x [64 dims], 128-byte swizzle, into a ring of
+//              three 32 KB units (K0, V0, K1, ...). The pool is addressed through one 3-D tensor map
+//              {128 dims, rows between tokens, token rows}, which covers head-major and token-major pages alike.
+//   warp 5   : MMA issuer and TMEM owner (512 columns: two score buffers of 128 and the output accumulator of 128).
+//                S[128 q x 128 keys]  = Q[128 x 128] . K_tile^T          (A, B K-major)
+//                O[128 q x 128 dims] += P[128 x 128] . V_tile             (A = P K-major, B = V as stored, MN-major)
+//              The next tile's scores are issued before this tile's P.V, so the softmax of tile j+1 can start while the
+//              tensor core works on tile j.
+//   warps 0-3: softmax. Thread t reads its score row (two passes over TMEM: maximum, then exponentials), masks the
+//              diagonal tile, writes P as bf16 into the swizzled operand layout, keeps the running sum; the running
+//              maximum is raised lazily (only when a tile exceeds it by 8 in log2 units) and then the accumulator row
+//              is rescaled in TMEM. The epilogue divides by the row sum and writes bf16 rows.
+// Causality skips key tiles above the diagonal, so a query tile at position qt does qt + 1 key tiles; CTAs are
+// launched heaviest first. The four query heads of a KV head run next to one another (head is the fastest grid
+// dimension) and find each other's K/V tiles in L2.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "prefill_attn.h"
+
+namespace sky {
+namespace {
+
+constexpr int PF_THREADS = 192;
+constexpr int PF_TILE = 128;
+constexpr int PF_UNITS = 3;
+constexpr int PF_HALF = PF_TILE * 64 * 2;          // [128 rows][64 cols] bf16, swizzled: 16 KB
+constexpr int PF_TILE_BYTES = 2 * PF_HALF;         // 32 KB: Q tile, K tile, V tile, P tile
+constexpr int PF_SMEM = PF_TILE_BYTES * (1 + PF_UNITS + 2) + 1024;
+constexpr float PF_RESCALE = 8.0f;
+
+__device__ __forceinline__ uint32_t pf_sw128(int row, int col) {        // byte offset of (row, col) in a [rows][64] swizzled half
+    return (uint32_t)(row * 128 + (((col >> 3) ^ (row & 7)) << 4) + (col & 7) * 2);
+}
+__device__ __forceinline__ uint64_t pf_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(lbo >> 4) << 16;
+    d |= (uint64_t)(sbo >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void pf_tmem_st_x16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void pf_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                                                                         const __grid_constant__ CUtensorMap tmap_kv, const PrefillAttnParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ uint64_t full_bar[PF_UNITS], empty_bar[PF_UNITS], q_full, s_ready[2], p_ready[2], o_done[2];
+    __shared__ uint32_t tmem_slot;
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* q_sm = smem;
+    unsigned char* ring = smem + PF_TILE_BYTES;
+    unsigned char* p_sm = ring + PF_UNITS * PF_TILE_BYTES;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.x, seq = blockIdx.z;
+    const int tok_base = p.seq_start[seq];
+    const int n = p.seq_start[seq + 1] - tok_base;                       // prompt length
+    const int q_tiles = (n + PF_TILE - 1) / PF_TILE;
+    const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;                 // heaviest query tiles first
+    if (qt >= q_tiles) return;                                           // whole CTA leaves together, before any barrier
+    const int n_kt = qt + 1;                                             // key tiles 0..qt (causal)
+    const int kvh = head / (p.q_heads / p.kv_heads);
+    const int* table = p.block_table + (long long)seq * p.max_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PF_UNITS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&q_full, 1);
+        mbar_init(&s_ready[0], 1); mbar_init(&s_ready[1], 1);
+        mbar_init(&p_ready[0], 128); mbar_init(&p_ready[1], 128);
+        mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
+        fence_barrier_init();
+    }
+    if (warp == 5) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    const uint32_t tm_s[2] = {tmem_base, tmem_base + 128};
+    const uint32_t tm_o = tmem_base + 256;
+
+    if (warp == 4) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_q);
+            tma_prefetch_desc(&tmap_kv);
+            mbar_expect_tx(&q_full, PF_TILE_BYTES);
+            tma_load_3d(q_sm, &tmap_q, 0, head, tok_base + qt * PF_TILE, &q_full);
+            tma_load_3d(q_sm + PF_HALF, &tmap_q, 64, head, tok_base + qt * PF_TILE, &q_full);
+        }
+        const int ts_rows = (int)(p.tok_stride >> 7);                    // 128-element rows between two tokens of a page
+        const long long head_row = (long long)kvh * (p.head_stride >> 7);
+        const int pg = lane >> 1, half = lane & 1;                       // lanes 0-15: page pg, dim half
+        for (int u = 0; u < 2 * n_kt; ++u) {
+            const int s = u % PF_UNITS;
+            if (u >= PF_UNITS && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], (uint32_t)((u / PF_UNITS) - 1) & 1))) {
+                if (lane == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 41);
+                break;
+            }
+            unsigned char* st = ring + s * PF_TILE_BYTES;
+            if (lane == 0) mbar_expect_tx(&full_bar[s], PF_TILE_BYTES);
+            __syncwarp();
+            if (lane < 16) {
+                const int e = (u >> 1) * 8 + pg;
+                const int blk = e < p.max_blocks ? __ldg(table + e) : 0;
+                const long long row0 = ((long long)blk * p.block_stride >> 7) + ((u & 1) ? (p.kv_stride >> 7) : 0) + head_row;
+                tma_load_3d(st + half * PF_HALF + pg * 2048, &tmap_kv, half * 64, (int)(row0 % ts_rows), (int)(row0 / ts_rows), &full_bar[s]);
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128);                     // Q K-major x K K-major
+            constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128) | (1u << 16);        // P K-major x V MN-major
+            const uint32_t q_addr = smem_u32(q_sm), p_addr = smem_u32(p_sm);
+            bool good = mbar_wait(&q_full, 0);
+            if (!good) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 42);
+            auto issue_s = [&](int j) -> bool {
+                const int u = 2 * j, s = u % PF_UNITS;
+                if (!mbar_wait(&full_bar[s], (uint32_t)(u / PF_UNITS) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 43); return false; }
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(ring + s * PF_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {                                        // 8 steps of 16 dims
+                    const uint64_t a = umma_desc_k_sw128(q_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
+                    const uint64_t b = umma_desc_k_sw128(k_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
+                    tc_mma_f16(tm_s[j & 1], a, b, idesc_s, k ? 1u : 0u);
+                }
+                tc_commit(&empty_bar[s]);        // the K tile is free once the scores are done
+                tc_commit(&s_ready[j & 1]);
+                return true;
+            };
+            if (good) good = issue_s(0);
+            for (int j = 0; j < n_kt && good; ++j) {
+                if (j + 1 < n_kt) good = issue_s(j + 1);
+                if (!good) break;
+                if (!mbar_wait(&p_ready[j & 1], (uint32_t)(j >> 1) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 44); break; }
+                const int u = 2 * j + 1, s = u % PF_UNITS;
+                if (!mbar_wait(&full_bar[s], (uint32_t)(u / PF_UNITS) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 45); break; }
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(ring + s * PF_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {                                        // 8 steps of 16 keys
+                    const uint64_t a = umma_desc_k_sw128(p_addr + (j & 1) * PF_TILE_BYTES + (k >> 2) * PF_HALF + (k & 3) * 32);
+                    const uint64_t b = pf_desc_mn_sw128(v_addr + k * 2048, PF_HALF, 1024);
+                    tc_mma_f16(tm_o, a, b, idesc_o, (j | k) ? 1u : 0u);
+                }
+                tc_commit(&empty_bar[s]);        // the V tile is free again
+                tc_commit(&o_done[j & 1]);       // this tile's P buffer is free; the accumulator may be touched
+            }
+        }
+    } else {
+        // ---------------- softmax warps: thread t <-> query row t ----------------
+        const int t = threadIdx.x;
+        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+        const float qs = p.scale * 1.4426950408889634f;
+        const int qpos_raw = qt * PF_TILE + t;
+        const bool row_valid = qpos_raw < n;
+        const int qpos = row_valid ? qpos_raw : n - 1;                   // rows past the prompt compute something finite, unused
+        float m_ref = -INFINITY, l_sum = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kt; ++j) {
+            const int par = j & 1;
+            if (!mbar_wait(&s_ready[par], (uint32_t)(j >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 46); ok = false; break; }
+            tc_fence_after();
+            const bool diag = j == qt;
+            const int kbase = j * PF_TILE;
+            // pass 1: row maximum
+            float tmax = -INFINITY;
+#pragma unroll 1
+            for (int c0 = 0; c0 < PF_TILE; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld_x16(tm_s[par] + lane_off + c0, r);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int kpos = kbase + c0 + i;
+                    const bool masked = diag && (kpos > qpos || kpos >= n);
+                    if (!masked) tmax = fmaxf(tmax, __uint_as_float(r[i]) * qs);
+                }
+            }
+            float alpha = 1.0f;
+            bool raise = tmax > m_ref + PF_RESCALE || m_ref == -INFINITY;
+            if (raise) {
+                alpha = m_ref == -INFINITY ? 0.f : exp2f(m_ref - tmax);
+                m_ref = tmax;
+            }
+            const bool any_raise = __any_sync(0xffffffffu, raise) && j > 0;      // tcgen05.ld/st are warp-wide: decide per warp
+            // P buffer `par` was last read by the P.V of tile j-2; a rescale waits for tile j-1 (in-order completion covers j-2).
+            if (any_raise) {
+                if (!mbar_wait(&o_done[(j - 1) & 1], (uint32_t)((j - 1) >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 47); ok = false; break; }
+                tc_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < 128; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld_x16(tm_o + lane_off + c0, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    pf_tmem_st_x16(tm_o + lane_off + c0, r);
+                }
+                pf_wait_st();
+            } else if (j > 1) {
+                if (!mbar_wait(&o_done[par], (uint32_t)((j - 2) >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 47); ok = false; break; }
+            }
+            l_sum *= alpha;
+            // pass 2: exponentials -> P (bf16, swizzled operand layout), row sum
+            unsigned char* prow = p_sm + par * PF_TILE_BYTES;
+#pragma unroll 1
+            for (int c0 = 0; c0 < PF_TILE; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld_x16(tm_s[par] + lane_off + c0, r);
+                tc_wait_ld();
+                uint32_t packed[8];
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    float e0, e1;
+                    {
+                        const int kpos = kbase + c0 + i;
+                        const bool masked = diag && (kpos > qpos || kpos >= n);
+                        e0 = masked ? 0.f : exp2f(__uint_as_float(r[i]) * qs - m_ref);
+                    }
+                    {
+                        const int kpos = kbase + c0 + i + 1;
+                        const bool masked = diag && (kpos > qpos || kpos >= n);
+                        e1 = masked ? 0.f : exp2f(__uint_as_float(r[i + 1]) * qs - m_ref);
+                    }
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+                    // the sum uses the rounded values, so that P.V and the normaliser agree
+                    l_sum += __bfloat162float(b2.x) + __bfloat162float(b2.y);
+                    packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+                }
+                const int hf = c0 >> 6, col = c0 & 63;                  // 16 keys = two 16-byte chunks of this row
+                *reinterpret_cast<uint4*>(prow + hf * PF_HALF + pf_sw128(t, col)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(prow + hf * PF_HALF + pf_sw128(t, col + 8)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            }
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(&p_ready[par]);
+        }
+        if (ok && !mbar_wait(&o_done[(n_kt - 1) & 1], (uint32_t)((n_kt - 1) >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 48); ok = false; }
+        tc_fence_after();
+        // ---------------- epilogue: row t of the output ----------------
+        const float inv = (ok && l_sum > 0.f) ? 1.0f / l_sum : 0.f;
+        __nv_bfloat16* orow = p.out + ((long long)(tok_base + qpos_raw) * p.q_heads + head) * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld_x16(tm_o + lane_off + c0, r);
+            tc_wait_ld();
+            uint32_t packed[8];
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+                const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+            }
+            if (row_valid) {
+                *reinterpret_cast<uint4*>(orow + c0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(orow + c0 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem_base, 512);
+}
+
+typedef CUresult (*PfEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 3-D bf16 map {128, mid, outer} with box {64, 1, box_outer}, 128-byte swizzle, zero fill outside.
+bool pf_make_tmap(CUtensorMap* m, const void* base, long long mid, long long outer, int box_outer) {
+    static PfEncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) return false;
+        fn = reinterpret_cast<PfEncodeFn>(ptr);
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || mid < 1 || outer < 1) return false;
+    const cuuint64_t dims[3] = {128, (cuuint64_t)mid, (cuuint64_t)outer};
+    const cuuint64_t strides[2] = {256, (cuuint64_t)mid * 256};
+    const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_outer};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+cudaError_t launch_prefill_attn_tc(const PrefillAttnParams& p, long long pool_rows, cudaStream_t stream) {
+    if (p.n_seqs < 1 || p.q_heads < 1 || p.kv_heads < 1 || p.q_heads % p.kv_heads || p.max_len < 1 || p.total_tokens < 1) return cudaErrorInvalidValue;
+    if ((p.block_stride | p.kv_stride | p.head_stride | p.tok_stride) & 127) return cudaErrorInvalidValue;        // whole rows of 128 elements
+    const long long ts_rows = p.tok_stride >> 7;
+    if (ts_rows < 1 || pool_rows < ts_rows || pool_rows / ts_rows > 0x7fffffffLL) return cudaErrorInvalidValue;
+    // a page's 16 tokens must sit on one middle coordinate: its first row and the head offset may not cross a token row group
+    if ((p.block_stride >> 7) % ts_rows || (p.kv_stride >> 7) % ts_rows) return cudaErrorInvalidValue;
+    if ((long long)p.kv_heads * (p.head_stride >> 7) > ts_rows && ts_rows != 1) return cudaErrorInvalidValue;
+    CUtensorMap tq, tkv;
+    if (!pf_make_tmap(&tq, p.q, p.q_heads, p.total_tokens, PF_TILE)) return cudaErrorInvalidValue;
+    if (!pf_make_tmap(&tkv, p.kv, ts_rows, pool_rows / ts_rows, 16)) return cudaErrorInvalidValue;
+    static unsigned long long attr_mask = 0;
+    if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(prefill_attn_tc_kernel), PF_SMEM, &attr_mask); e != cudaSuccess) return e;
+    dim3 grid(p.q_heads, (p.max_len + PF_TILE - 1) / PF_TILE, p.n_seqs);
+    prefill_attn_tc_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(tq, tkv, p);
+    return cudaGetLastError();
+}
+
+}  // namespace sky

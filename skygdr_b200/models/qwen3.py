@@ -229,12 +229,15 @@ class Qwen3Decoder:
     # ---- prefill: whole prompts, token-major or head-major pool, returns last-position logits ----
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor, seq_lens: List[int], block_table: torch.Tensor, pool: Optional[PagedKVPool] = None,
-                chunk: int = 2048) -> torch.Tensor:
+                chunk: int = 2048, attn: Optional[str] = None) -> torch.Tensor:
         """Runs the prompts through the stack, writing K/V into ``pool`` (default: the decode pool).
 
-        GEMMs and K/V append use this package's kernels. The causal attention over the prompt uses
-        torch's scaled_dot_product_attention (a library kernel): prefill attention is not one of the
-        contended paths this runtime schedules."""
+        GEMMs and K/V append use this package's kernels. The causal attention over the prompt is this package's tcgen05
+        kernel reading the pages in place (``attn="tc"``, csrc/kernels/prefill_attn_tc.cu) or torch's
+        scaled_dot_product_attention over gathered copies of K and V (``attn="sdpa"``, a library kernel, kept as the
+        comparison arm). Default: ``self.prefill_attn``."""
+        attn = attn or self.prefill_attn
+        assert attn in ("tc", "sdpa")
         cfg, w = self.cfg, self.w
         pool = pool or self.pool
         dev = ids.device
@@ -252,6 +255,17 @@ class Qwen3Decoder:
             q = ops.rope_append(qkv, lw.q_norm, lw.k_norm, pool, li, self.inv_freq, block_table, positions, cfg.q_heads, cfg.eps,
                                 seq_ids=seq_ids)
             ao = torch.empty_like(q)
+            if attn == "tc":
+                if li == 0:
+                    if self._prefill_attn is None:
+                        self._prefill_attn = ops.PrefillAttention(dev)
+                    seq_start = torch.tensor([0] + list(torch.tensor(seq_lens).cumsum(0).tolist()), dtype=torch.int32, device=dev)
+                self._prefill_attn(q, pool, li, block_table, seq_start, max(seq_lens), out=ao)
+                h = ops.gemm(ao.view(T, -1), lw.o)
+                xn = ops.rmsnorm(h, lw.ln2, cfg.eps, residual=resid)
+                act = ops.gemm(xn, lw.gate_up, gated=True)
+                h = ops.gemm(act, lw.down)
+                continue
             o = 0
             for si, n in enumerate(seq_lens):
                 nb = (n + 15) // 16

@@ -1,5 +1,5 @@
 """Python face of the sm_100a kernels."""
-from .attention import PagedAttention, paged_attn_reference
+from .attention import PagedAttention, PrefillAttention, paged_attn_reference, prefill_attn_reference
 from .flow import CreditPage, LocalPacer, new_status, read_status
 from .gemm import gemm, pick_config, pick_splits
 from .kv_cache import BLOCK_TOKENS, KVGeometry, PagedKVPool
@@ -8,7 +8,7 @@ from .memhog import Memhog
 from .small import argmax, embedding, rmsnorm, rope_append, rope_inv_freq, silu_mul
 
 __all__ = [
-    "PagedAttention", "paged_attn_reference", "CreditPage", "LocalPacer", "new_status", "read_status", "gemm", "pick_config", "pick_splits",
+    "PagedAttention", "PrefillAttention", "paged_attn_reference", "prefill_attn_reference", "CreditPage", "LocalPacer", "new_status", "read_status", "gemm", "pick_config", "pick_splits",
     "BLOCK_TOKENS", "KVGeometry", "PagedKVPool", "KvTransferFlow", "MulticastPools", "RemotePool", "link_bytes", "reference_transfer",
     "Memhog", "argmax", "embedding", "rmsnorm", "rope_append", "rope_inv_freq", "silu_mul",
 ]

@@ -49,6 +49,60 @@ class PagedAttention:
         return out
 
 
+class PrefillAttention:
+    """Causal attention of whole prompts against their own K/V in the paged pool (prefill_attn_tc.cu): tcgen05 MMAs with the
+    accumulators in TMEM, K/V pages fetched by TMA straight from the pool in either layout, one CTA per 128-token query tile.
+    Pages must hold finite values past a prompt's last token (a fresh pool is zeroed); block-table entries past a prompt's
+    pages must name valid blocks."""
+
+    def __init__(self, device):
+        self._C = load()
+        self.device = torch.device(device)
+        self.status = new_status(self.device)
+
+    def __call__(self, q: torch.Tensor, pool: PagedKVPool, layer: int, block_table: torch.Tensor, seq_start: torch.Tensor, max_len: int,
+                 out: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
+        """q: [tokens][q_heads][128] with the prompts packed back to back; seq_start: int32 [n_seqs + 1] token offsets."""
+        if out is None:
+            out = torch.empty_like(q)
+        bs, ls, ks = pool.strides
+        g = pool.geom
+        if pool.layout == "hnd":
+            head_stride, tok_stride = g.block_tokens * g.head_dim, g.head_dim
+        else:
+            head_stride, tok_stride = g.head_dim, g.kv_heads * g.head_dim
+        self._C.prefill_attn(q, pool.layer_base(layer), out, block_table, seq_start, bs, ks, head_stride, tok_stride, g.kv_heads, int(max_len),
+                             scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]), self.status,
+                             (pool.data.numel() - layer * ls) // 128)
+        return out
+
+
+def prefill_attn_reference(q: torch.Tensor, pool: PagedKVPool, layer: int, block_table: torch.Tensor, seq_lens, scale: Optional[float] = None) -> torch.Tensor:
+    """Plain fp32 causal softmax attention of packed prompts over the gathered pages (test oracle)."""
+    T, Hq, D = q.shape
+    Hkv = pool.geom.kv_heads
+    G = Hq // Hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    out = torch.empty((T, Hq, D), dtype=torch.float32, device=q.device)
+    o = 0
+    for s, n in enumerate(seq_lens):
+        n = int(n)
+        nb = (n + 15) // 16
+        kv = pool.data[block_table[s, :nb].long(), layer]
+        if pool.layout == "nhd":
+            kv = kv.permute(0, 1, 3, 2, 4)                 # -> [nb][2][H][16][D]
+        k = kv[:, 0].permute(1, 0, 2, 3).reshape(Hkv, nb * 16, D)[:, :n].float()
+        v = kv[:, 1].permute(1, 0, 2, 3).reshape(Hkv, nb * 16, D)[:, :n].float()
+        qs = q[o:o + n].float().view(n, Hkv, G, D).permute(1, 2, 0, 3)          # [Hkv][G][n][D]
+        sc = torch.einsum("hgqd,hkd->hgqk", qs, k) * scale
+        mask = torch.ones((n, n), dtype=torch.bool, device=q.device).tril()
+        sc = sc.masked_fill(~mask, float("-inf"))
+        pr = torch.softmax(sc, dim=-1)
+        out[o:o + n] = torch.einsum("hgqk,hkd->hgqd", pr, v).permute(2, 0, 1, 3).reshape(n, Hq, D)
+        o += n
+    return out
+
+
 def paged_attn_reference(q: torch.Tensor, pool: PagedKVPool, layer: int, block_table: torch.Tensor, ctx_lens: torch.Tensor,
                          scale: Optional[float] = None) -> torch.Tensor:
     """Plain fp32 softmax attention over the gathered pages (test oracle)."""
