@@ -1,6 +1,7 @@
 """Small, self-contained cases of each kernel, for timing and for profiler captures.
 
     python benchmarks/kernel_cases.py attn   [--batch 16 --ctx 8192 --kv-heads 8 --q-heads 32 --chunk 1024]
+    python benchmarks/kernel_cases.py pattn  [--ctx 16384 --batch 1 --impl tc|sdpa]     (causal prefill attention over the paged pool)
     python benchmarks/kernel_cases.py gemm   [--m 16 --n 12288 --k 4096 --gated --splits 0]
     python benchmarks/kernel_cases.py kvt    [--blocks 256]         (same-GPU destination)
     python benchmarks/kernel_cases.py memhog [--gb 2 --op axpy]
@@ -51,7 +52,7 @@ def timed(fn, warm, iters, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["attn", "gemm", "kvt", "memhog", "norm"])
+    ap.add_argument("case", choices=["attn", "pattn", "gemm", "kvt", "memhog", "norm"])
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warm", type=int, default=2)
     ap.add_argument("--batch", type=int, default=16)
@@ -70,13 +71,41 @@ def main():
     ap.add_argument("--op", default="axpy")
     ap.add_argument("--rows", type=int, default=16)
     ap.add_argument("--no-flush", action="store_true")
-    ap.add_argument("--impl", default="simt", choices=["simt", "tc", "tcp"])
+    ap.add_argument("--impl", default="simt", choices=["simt", "tc", "tcp", "sdpa"])
     a = ap.parse_args()
     dev = "cuda"
     hbm, tf, src = peaks()
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     out = {"case": a.case, "peaks": src}
-    if a.case == "attn":
+    if a.case == "pattn":
+        # `--batch` prompts of `--ctx` tokens each; impl tc = this package's kernel on the pages in place,
+        # sdpa = torch's scaled_dot_product_attention on contiguous K/V (the gather that feeds it is not timed)
+        g = ops.KVGeometry(layers=1, kv_heads=a.kv_heads)
+        n, B = a.ctx, a.batch
+        nb = (n + 15) // 16
+        pool = ops.PagedKVPool(g, B * nb + 1, "hnd")
+        pool.data.normal_()
+        table = (torch.randperm(B * nb, device=dev) + 1).int().view(B, nb)
+        table = torch.cat([table, torch.zeros((B, 8), dtype=torch.int32, device=dev)], 1).contiguous()
+        q = torch.randn((B * n, a.q_heads, 128), dtype=torch.bfloat16, device=dev)
+        seq_start = (torch.arange(B + 1, device=dev) * n).int()
+        flops = B * 2.0 * n * n * 128 * a.q_heads                  # causal: half of 4 n^2 d per head
+        if a.impl == "sdpa":
+            kv = pool.data[table[:, :nb].long().view(-1), 0].view(B, nb, 2, a.kv_heads, 16, 128)
+            k = kv[:, :, 0].permute(0, 2, 1, 3, 4).reshape(B, a.kv_heads, nb * 16, 128)[:, :, :n].contiguous()
+            v = kv[:, :, 1].permute(0, 2, 1, 3, 4).reshape(B, a.kv_heads, nb * 16, 128)[:, :, :n].contiguous()
+            qs = q.view(B, n, a.q_heads, 128).transpose(1, 2).contiguous()
+            fn = lambda: torch.nn.functional.scaled_dot_product_attention(qs, k, v, is_causal=True, enable_gqa=True)
+            status = "library"
+        else:
+            attn = ops.PrefillAttention(dev)
+            o_ = torch.empty_like(q)
+            fn = lambda: attn(q, pool, 0, table, seq_start, n, out=o_)
+        ms, best = timed(fn, a.warm, a.iters, flush)
+        if a.impl != "sdpa":
+            status = ops.read_status(attn.status)["status_name"]
+        out.update(ms=ms, best_ms=best, flops=flops, tflops=flops / ms / 1e9, frac_bf16=flops / ms / 1e9 / tf, tokens=B * n, impl=a.impl, status=status)
+    elif a.case == "attn":
         g = ops.KVGeometry(layers=1, kv_heads=a.kv_heads)
         gen = torch.Generator().manual_seed(0)
         ctx = torch.randint(a.ctx // 2, a.ctx + 1, (a.batch,), generator=gen).int().to(dev)

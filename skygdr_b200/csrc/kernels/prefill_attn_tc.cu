@@ -3,19 +3,22 @@
 // One CTA per (query tile of 128 tokens, query head, prompt). Query rows are the MMA's M, so TMEM lane t holds query
 // row t and the softmax of a row lives in one thread: no shuffles, no exchange through shared memory.
 //
-//   warp 4   : TMA producer. Q tile once (two boxes of [128 tokens] x [64 dims]); then per key tile of 128 tokens
+//   warp 8   : TMA producer. Q tile once (two boxes of [128 tokens] x [64 dims]); then per key tile of 128 tokens
 //              K and V, each as 8 pages x 2 dim halves of [16 tokens] x [64 dims], 128-byte swizzle, into a ring of
 //              three 32 KB units (K0, V0, K1, ...). The pool is addressed through one 3-D tensor map
 //              {128 dims, rows between tokens, token rows}, which covers head-major and token-major pages alike.
-//   warp 5   : MMA issuer and TMEM owner (512 columns: two score buffers of 128 and the output accumulator of 128).
+//   warp 9   : MMA issuer and TMEM owner (512 columns: two score buffers of 128 and the output accumulator of 128).
 //                S[128 q x 128 keys]  = Q[128 x 128] . K_tile^T          (A, B K-major)
 //                O[128 q x 128 dims] += P[128 x 128] . V_tile             (A = P K-major, B = V as stored, MN-major)
 //              The next tile's scores are issued before this tile's P.V, so the softmax of tile j+1 can start while the
 //              tensor core works on tile j.
-//   warps 0-3: softmax. Thread t reads its score row (two passes over TMEM: maximum, then exponentials), masks the
-//              diagonal tile, writes P as bf16 into the swizzled operand layout, keeps the running sum; the running
-//              maximum is raised lazily (only when a tile exceeds it by 8 in log2 units) and then the accumulator row
-//              is rescaled in TMEM. The epilogue divides by the row sum and writes bf16 rows.
+//   warps 0-7: softmax, two warpgroups. Query row r belongs to thread r of each warpgroup; warpgroup 0 owns key columns
+//              0-63 of the tile (and output dims 0-63), warpgroup 1 columns 64-127. A thread reads its 64 scores from
+//              TMEM in one go, the two halves of a row exchange their maxima through shared memory, then each thread
+//              masks (diagonal tile only), exponentiates, writes its half of the P row as bf16 into the swizzled operand
+//              layout and keeps a partial row sum. The running maximum is raised lazily (only when a tile exceeds it by 8
+//              in log2 units) and then the accumulator row is rescaled in TMEM. The epilogue divides by the row sum and
+//              writes bf16 rows.
 // Causality skips key tiles above the diagonal, so a query tile at position qt does qt + 1 key tiles; CTAs are
 // launched heaviest first. The four query heads of a KV head run next to one another (head is the fastest grid
 // dimension) and find each other's K/V tiles in L2.
@@ -27,12 +30,13 @@
 namespace sky {
 namespace {
 
-constexpr int PF_THREADS = 192;
+constexpr int PF_THREADS = 320;
 constexpr int PF_TILE = 128;
-constexpr int PF_UNITS = 3;
+constexpr int PF_UNITS = 4;                        // K(j), V(j), K(j+1), V(j+1): the next tile loads while this one is computed
 constexpr int PF_HALF = PF_TILE * 64 * 2;          // [128 rows][64 cols] bf16, swizzled: 16 KB
 constexpr int PF_TILE_BYTES = 2 * PF_HALF;         // 32 KB: Q tile, K tile, V tile, P tile
-constexpr int PF_SMEM = PF_TILE_BYTES * (1 + PF_UNITS + 2) + 1024;
+constexpr int PF_TILES_BYTES = PF_TILE_BYTES * (1 + PF_UNITS + 2);       // Q, the ring, two P buffers: 224 KB
+constexpr int PF_SMEM = PF_TILES_BYTES + 2 * 2 * PF_TILE * 4 + 256;       // + maxima exchange + barriers; no static shared memory
 constexpr float PF_RESCALE = 8.0f;
 
 __device__ __forceinline__ uint32_t pf_sw128(int row, int col) {        // byte offset of (row, col) in a [rows][64] swizzled half
@@ -53,17 +57,39 @@ __device__ __forceinline__ void pf_tmem_st_x16(uint32_t taddr, const uint32_t* r
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
+__device__ __forceinline__ void pf_tmem_ld_x32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void pf_softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ void pf_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                                          const __grid_constant__ CUtensorMap tmap_kv, const PrefillAttnParams p) {
-    extern __shared__ unsigned char smem_raw[];
-    __shared__ uint64_t full_bar[PF_UNITS], empty_bar[PF_UNITS], q_full, s_ready[2], p_ready[2], o_done[2];
-    __shared__ uint32_t tmem_slot;
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // Everything lives in dynamic shared memory (224 KB of tiles leave no room for a static part and an alignment slack): the
+    // tiles first, since the 128-byte swizzle wants them on 1024-byte boundaries, then the exchange array and the barriers.
+    extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char* q_sm = smem;
     unsigned char* ring = smem + PF_TILE_BYTES;
     unsigned char* p_sm = ring + PF_UNITS * PF_TILE_BYTES;
+    float (*xch)[2][PF_TILE] = reinterpret_cast<float (*)[2][PF_TILE]>(smem + PF_TILES_BYTES);      // [tile parity][warpgroup][row]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PF_TILES_BYTES + 2 * 2 * PF_TILE * 4);
+    uint64_t* full_bar = bars;                        // [PF_UNITS]
+    uint64_t* empty_bar = bars + PF_UNITS;            // [PF_UNITS]
+    uint64_t* s_ready = bars + 2 * PF_UNITS;          // [2]
+    uint64_t* p_ready = s_ready + 2;                  // [2]
+    uint64_t* o_done = p_ready + 2;                   // [2]
+    uint64_t& q_full = *(o_done + 2);
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(o_done + 3);
+    if (smem_u32(smem) & 1023) {                      // the swizzled tiles would be misread: report instead of computing garbage
+        if (threadIdx.x == 0) set_status(p.status, SKY_STATUS_BAD_INDEX, 49);
+        return;
+    }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.x, seq = blockIdx.z;
@@ -80,11 +106,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
         for (int s = 0; s < PF_UNITS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&q_full, 1);
         mbar_init(&s_ready[0], 1); mbar_init(&s_ready[1], 1);
-        mbar_init(&p_ready[0], 128); mbar_init(&p_ready[1], 128);
+        mbar_init(&p_ready[0], 256); mbar_init(&p_ready[1], 256);
         mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
         fence_barrier_init();
     }
-    if (warp == 5) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+    if (warp == 9) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -92,7 +118,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
     const uint32_t tm_s[2] = {tmem_base, tmem_base + 128};
     const uint32_t tm_o = tmem_base + 256;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             tma_prefetch_desc(&tmap_q);
@@ -120,7 +146,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
                 tma_load_3d(st + half * PF_HALF + pg * 2048, &tmap_kv, half * 64, (int)(row0 % ts_rows), (int)(row0 / ts_rows), &full_bar[s]);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128);                     // Q K-major x K K-major
@@ -163,37 +189,55 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
             }
         }
     } else {
-        // ---------------- softmax warps: thread t <-> query row t ----------------
-        const int t = threadIdx.x;
-        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+        // ---------------- softmax warpgroups: thread (wg, r) <-> half of query row r ----------------
+        const int wg = warp >> 2;                                        // 0: key columns / output dims 0-63, 1: 64-127
+        const int r = threadIdx.x & 127;                                 // query row of the tile = TMEM lane
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;     // a warp reaches the TMEM lanes of its rank in the warpgroup
+        const int col0 = wg * 64;
         const float qs = p.scale * 1.4426950408889634f;
-        const int qpos_raw = qt * PF_TILE + t;
+        const int qpos_raw = qt * PF_TILE + r;
         const bool row_valid = qpos_raw < n;
         const int qpos = row_valid ? qpos_raw : n - 1;                   // rows past the prompt compute something finite, unused
         float m_ref = -INFINITY, l_sum = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kt; ++j) {
             const int par = j & 1;
-            if (!mbar_wait(&s_ready[par], (uint32_t)(j >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 46); ok = false; break; }
+            // A wait that runs out does not leave the loop: the thread keeps taking part in the named barrier and the P
+            // arrivals (so that nobody waits for it without a bound) and only stops waiting itself.
+            if (ok && !mbar_wait(&s_ready[par], (uint32_t)(j >> 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 46); ok = false; }
             tc_fence_after();
+            uint32_t sc[64];
+            pf_tmem_ld_x32(tm_s[par] + lane_off + col0, sc);
+            pf_tmem_ld_x32(tm_s[par] + lane_off + col0 + 32, sc + 32);
+            tc_wait_ld();
             const bool diag = j == qt;
-            const int kbase = j * PF_TILE;
-            // pass 1: row maximum
+            const int kbase = j * PF_TILE + col0;
+            // Maximum of the raw scores (the scale is positive, so it commutes); masked entries of the diagonal tile become -inf.
             float tmax = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < PF_TILE; c0 += 16) {
-                uint32_t r[16];
-                tmem_ld_x16(tm_s[par] + lane_off + c0, r);
-                tc_wait_ld();
+            if (diag) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int kpos = kbase + c0 + i;
-                    const bool masked = diag && (kpos > qpos || kpos >= n);
-                    if (!masked) tmax = fmaxf(tmax, __uint_as_float(r[i]) * qs);
+                for (int i = 0; i < 64; ++i) {
+                    const int kpos = kbase + i;
+                    if (kpos > qpos || kpos >= n) sc[i] = 0xff800000u;      // -inf
+                    tmax = fmaxf(tmax, __uint_as_float(sc[i]));
                 }
+            } else {
+                float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 64; i += 4) {
+                    t0 = fmaxf(t0, __uint_as_float(sc[i]));
+                    t1 = fmaxf(t1, __uint_as_float(sc[i + 1]));
+                    t2 = fmaxf(t2, __uint_as_float(sc[i + 2]));
+                    t3 = fmaxf(t3, __uint_as_float(sc[i + 3]));
+                }
+                tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
             }
+            tmax *= qs;
+            xch[par][wg][r] = tmax;
+            pf_softmax_bar();                                            // both halves of every row have posted their maxima
+            tmax = fmaxf(tmax, xch[par][wg ^ 1][r]);
             float alpha = 1.0f;
-            bool raise = tmax > m_ref + PF_RESCALE || m_ref == -INFINITY;
+            const bool raise = tmax > m_ref + PF_RESCALE || m_ref == -INFINITY;        // same verdict in both threads of a row
             if (raise) {
                 alpha = m_ref == -INFINITY ? 0.f : exp2f(m_ref - tmax);
                 m_ref = tmax;
@@ -201,70 +245,63 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
             const bool any_raise = __any_sync(0xffffffffu, raise) && j > 0;      // tcgen05.ld/st are warp-wide: decide per warp
             // P buffer `par` was last read by the P.V of tile j-2; a rescale waits for tile j-1 (in-order completion covers j-2).
             if (any_raise) {
-                if (!mbar_wait(&o_done[(j - 1) & 1], (uint32_t)((j - 1) >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 47); ok = false; break; }
+                if (ok && !mbar_wait(&o_done[(j - 1) & 1], (uint32_t)((j - 1) >> 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 47); ok = false; }
                 tc_fence_after();
 #pragma unroll 1
-                for (int c0 = 0; c0 < 128; c0 += 16) {
-                    uint32_t r[16];
-                    tmem_ld_x16(tm_o + lane_off + c0, r);
+                for (int c0 = 0; c0 < 64; c0 += 16) {                   // this thread's half of the accumulator row
+                    uint32_t o[16];
+                    tmem_ld_x16(tm_o + lane_off + col0 + c0, o);
                     tc_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    pf_tmem_st_x16(tm_o + lane_off + c0, r);
+                    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    pf_tmem_st_x16(tm_o + lane_off + col0 + c0, o);
                 }
                 pf_wait_st();
             } else if (j > 1) {
-                if (!mbar_wait(&o_done[par], (uint32_t)((j - 2) >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 47); ok = false; break; }
+                if (ok && !mbar_wait(&o_done[par], (uint32_t)((j - 2) >> 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 47); ok = false; }
             }
             l_sum *= alpha;
-            // pass 2: exponentials -> P (bf16, swizzled operand layout), row sum
-            unsigned char* prow = p_sm + par * PF_TILE_BYTES;
-#pragma unroll 1
-            for (int c0 = 0; c0 < PF_TILE; c0 += 16) {
-                uint32_t r[16];
-                tmem_ld_x16(tm_s[par] + lane_off + c0, r);
-                tc_wait_ld();
-                uint32_t packed[8];
+            // exponentials -> this thread's 64 keys of the P row (bf16, swizzled operand layout), partial row sum
+            unsigned char* prow = p_sm + par * PF_TILE_BYTES + wg * PF_HALF;
+            const float neg_m = -m_ref;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    float e0, e1;
-                    {
-                        const int kpos = kbase + c0 + i;
-                        const bool masked = diag && (kpos > qpos || kpos >= n);
-                        e0 = masked ? 0.f : exp2f(__uint_as_float(r[i]) * qs - m_ref);
-                    }
-                    {
-                        const int kpos = kbase + c0 + i + 1;
-                        const bool masked = diag && (kpos > qpos || kpos >= n);
-                        e1 = masked ? 0.f : exp2f(__uint_as_float(r[i + 1]) * qs - m_ref);
-                    }
-                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
-                    // the sum uses the rounded values, so that P.V and the normaliser agree
-                    l_sum += __bfloat162float(b2.x) + __bfloat162float(b2.y);
+            for (int c = 0; c < 64; c += 8) {
+                float e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) e[i] = exp2f(fmaf(__uint_as_float(sc[c + i]), qs, neg_m));      // masked scores are -inf: 0
+                s0 += e[0] + e[4]; s1 += e[1] + e[5]; s2 += e[2] + e[6]; s3 += e[3] + e[7];
+                uint32_t packed[4];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(e[i], e[i + 1]);
                     packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
                 }
-                const int hf = c0 >> 6, col = c0 & 63;                  // 16 keys = two 16-byte chunks of this row
-                *reinterpret_cast<uint4*>(prow + hf * PF_HALF + pf_sw128(t, col)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                *reinterpret_cast<uint4*>(prow + hf * PF_HALF + pf_sw128(t, col + 8)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                *reinterpret_cast<uint4*>(prow + pf_sw128(r, c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
+            l_sum += (s0 + s1) + (s2 + s3);
             fence_proxy_async();
             tc_fence_before();
             mbar_arrive(&p_ready[par]);
         }
-        if (ok && !mbar_wait(&o_done[(n_kt - 1) & 1], (uint32_t)((n_kt - 1) >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 48); ok = false; }
+        if (ok && !mbar_wait(&o_done[(n_kt - 1) & 1], (uint32_t)((n_kt - 1) >> 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 48); ok = false; }
         tc_fence_after();
-        // ---------------- epilogue: row t of the output ----------------
-        const float inv = (ok && l_sum > 0.f) ? 1.0f / l_sum : 0.f;
-        __nv_bfloat16* orow = p.out + ((long long)(tok_base + qpos_raw) * p.q_heads + head) * 128;
+        // ---------------- epilogue: this thread's 64 dims of output row r ----------------
+        pf_softmax_bar();                                                // every thread is past its last read of xch
+        xch[0][wg][r] = l_sum;
+        pf_softmax_bar();
+        const float l_row = l_sum + xch[0][wg ^ 1][r];
+        const float inv = (ok && l_row > 0.f) ? 1.0f / l_row : 0.f;
+        __nv_bfloat16* orow = p.out + ((long long)(tok_base + qpos_raw) * p.q_heads + head) * 128 + col0;
 #pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld_x16(tm_o + lane_off + c0, r);
+        for (int c0 = 0; c0 < 64; c0 += 16) {
+            uint32_t o[16];
+            tmem_ld_x16(tm_o + lane_off + col0 + c0, o);
             tc_wait_ld();
             uint32_t packed[8];
 #pragma unroll
             for (int i = 0; i < 16; i += 2) {
-                const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
                 packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
             }
             if (row_valid) {
@@ -275,7 +312,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem_base, 512);
+    if (warp == 9) tmem_dealloc(tmem_base, 512);
 }
 
 typedef CUresult (*PfEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,

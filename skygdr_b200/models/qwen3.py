@@ -114,9 +114,11 @@ class Qwen3Decoder:
     """Single-GPU decode engine: fixed-capacity batch, preallocated activations, optional CUDA graph."""
 
     def __init__(self, cfg: Qwen3Config, weights: Qwen3Weights, pool: PagedKVPool, max_batch: int, max_ctx: int,
-                 attn_chunk: int = 1024, attn_impl: str = "tc"):
-        assert pool.layout == "hnd"
+                 attn_chunk: int = 1024, attn_impl: str = "tc", prefill_attn: str = "tc"):
+        assert pool.layout == "hnd" and prefill_attn in ("tc", "sdpa")
         self.cfg, self.w, self.pool = cfg, weights, pool
+        self.prefill_attn = prefill_attn              # default of prefill(): this package's kernel or the library arm
+        self._prefill_attn = None
         dev = pool.data.device
         self.device = dev
         self.max_batch, self.max_ctx = max_batch, max_ctx

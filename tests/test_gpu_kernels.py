@@ -253,6 +253,38 @@ def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
     assert int(attn.counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("layout", ["hnd", "nhd"])
+@pytest.mark.parametrize("kv_heads,q_heads", [(8, 32), (2, 4), (1, 1)])
+def test_prefill_attention_matches_reference(ops, layout, kv_heads, q_heads):
+    """Causal attention of packed prompts read in place from the paged pool, against fp32 softmax attention in PyTorch.
+    Lengths straddle the 128-token tile (1, 127, 128, 129), the page (16) and several key tiles (700)."""
+    torch.manual_seed(4)
+    g = ops.KVGeometry(layers=2, kv_heads=kv_heads)
+    lens = [1, 127, 128, 129, 300, 700, 16, 17]
+    nblk = sum((n + 15) // 16 for n in lens) + 3
+    pool = ops.PagedKVPool(g, nblk, layout)
+    pool.data.normal_()
+    max_blocks = ((max(lens) + 127) // 128) * 8 + 8
+    perm = (torch.randperm(nblk - 1, device="cuda") + 1).int()
+    table = torch.zeros((len(lens), max_blocks), dtype=torch.int32, device="cuda")
+    o = 0
+    for s, n in enumerate(lens):
+        nb = (n + 15) // 16
+        table[s, :nb] = perm[o:o + nb]
+        o += nb
+    T = sum(lens)
+    q = torch.randn((T, q_heads, 128), dtype=torch.bfloat16, device="cuda")
+    seq_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32, device="cuda")
+    attn = ops.PrefillAttention("cuda")
+    for layer in (0, 1):
+        out = attn(q, pool, layer, table, seq_start, max(lens))
+        torch.cuda.synchronize()
+        assert ops.read_status(attn.status)["status"] == 0, ops.read_status(attn.status)
+        ref = ops.prefill_attn_reference(q, pool, layer, table, lens)
+        err = (out.float() - ref).abs().max()
+        assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float(err)
+
+
 @pytest.mark.parametrize("chunk", [512, 1024])
 def test_persistent_attention_walks_many_items_per_cta(ops, chunk):
     """More work items than CTAs (48 sequences x up to 5 splits x 8 KV heads against 296 CTAs): every CTA runs several items
