@@ -23,6 +23,7 @@ struct PrefillAttnParams {
     int max_len;                 // longest prompt (sizes the grid)
     int total_tokens;
     float scale;
+    int two_tiles;               // 1: two query tiles per CTA working in alternation (prefill_attn_tc2_kernel); 0: one tile per CTA
     LaunchStatus* status;
 };
 

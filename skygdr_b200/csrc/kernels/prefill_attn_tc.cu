@@ -315,6 +315,253 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
     if (warp == 9) tmem_dealloc(tmem_base, 512);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Two query tiles per CTA. Tiles A = 2c and B = 2c + 1 of a prompt (256 consecutive queries) share every K/V tile that
+// the CTA loads, and their softmax warpgroups work in alternation with the tensor core: while warpgroup A turns its
+// scores of key tile j into P, the tensor core runs P.V of tile B and the next scores of B, and the other way round.
+// One warpgroup per query tile, one thread per query row (all 128 scores of a row in registers, no exchange between
+// threads). TMEM: scores of A and B (single-buffered, 128 columns each) and the two accumulators: 512 columns.
+// Shared memory: Q_A, Q_B, a ring of three K/V units, P_A, P_B (single-buffered): 224 KB.
+constexpr int PF2_UNITS = 3;
+constexpr int PF2_TILES_BYTES = PF_TILE_BYTES * (2 + PF2_UNITS + 2);
+constexpr int PF2_SMEM = PF2_TILES_BYTES + 256;
+
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                                                                          const __grid_constant__ CUtensorMap tmap_kv, const PrefillAttnParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    unsigned char* q_sm = smem;                                        // Q_A, Q_B
+    unsigned char* ring = smem + 2 * PF_TILE_BYTES;
+    unsigned char* p_sm = ring + PF2_UNITS * PF_TILE_BYTES;            // P_A, P_B
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PF2_TILES_BYTES);
+    uint64_t* full_bar = bars;                        // [PF2_UNITS]
+    uint64_t* empty_bar = bars + PF2_UNITS;           // [PF2_UNITS]
+    uint64_t* s_ready = bars + 2 * PF2_UNITS;         // [2]: per query tile, one completion per key tile
+    uint64_t* p_ready = s_ready + 2;                  // [2]
+    uint64_t* o_done = p_ready + 2;                   // [2]
+    uint64_t& q_full = *(o_done + 2);
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(o_done + 3);
+    if (smem_u32(smem) & 1023) {
+        if (threadIdx.x == 0) set_status(p.status, SKY_STATUS_BAD_INDEX, 59);
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.x, seq = blockIdx.z;
+    const int tok_base = p.seq_start[seq];
+    const int n = p.seq_start[seq + 1] - tok_base;
+    const int q_tiles = (n + PF_TILE - 1) / PF_TILE;
+    const int pair = (int)gridDim.y - 1 - (int)blockIdx.y;               // heaviest pairs first
+    if (2 * pair >= q_tiles) return;
+    const int qt_x[2] = {2 * pair, 2 * pair + 1};
+    const int nkt_x[2] = {qt_x[0] + 1, qt_x[1] < q_tiles ? qt_x[1] + 1 : 0};      // key tiles each query tile needs (0: tile B is past the prompt)
+    const int n_kt = max(nkt_x[0], nkt_x[1]);
+    const int kvh = head / (p.q_heads / p.kv_heads);
+    const int* table = p.block_table + (long long)seq * p.max_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PF2_UNITS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&q_full, 1);
+        for (int x = 0; x < 2; ++x) { mbar_init(&s_ready[x], 1); mbar_init(&p_ready[x], 128); mbar_init(&o_done[x], 1); }
+        fence_barrier_init();
+    }
+    if (warp == 9) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 8) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_q);
+            tma_prefetch_desc(&tmap_kv);
+            mbar_expect_tx(&q_full, 2 * PF_TILE_BYTES);                  // tile B is fetched even when it is past the prompt (zero fill or unused rows)
+            for (int x = 0; x < 2; ++x) {
+                tma_load_3d(q_sm + x * PF_TILE_BYTES, &tmap_q, 0, head, tok_base + qt_x[x] * PF_TILE, &q_full);
+                tma_load_3d(q_sm + x * PF_TILE_BYTES + PF_HALF, &tmap_q, 64, head, tok_base + qt_x[x] * PF_TILE, &q_full);
+            }
+        }
+        const int ts_rows = (int)(p.tok_stride >> 7);
+        const long long head_row = (long long)kvh * (p.head_stride >> 7);
+        const int pg = lane >> 1, half = lane & 1;
+        for (int u = 0; u < 2 * n_kt; ++u) {
+            const int s = u % PF2_UNITS;
+            if (u >= PF2_UNITS && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], (uint32_t)((u / PF2_UNITS) - 1) & 1))) {
+                if (lane == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 51);
+                break;
+            }
+            unsigned char* st = ring + s * PF_TILE_BYTES;
+            if (lane == 0) mbar_expect_tx(&full_bar[s], PF_TILE_BYTES);
+            __syncwarp();
+            if (lane < 16) {
+                const int e = (u >> 1) * 8 + pg;
+                const int blk = e < p.max_blocks ? __ldg(table + e) : 0;
+                const long long row0 = ((long long)blk * p.block_stride >> 7) + ((u & 1) ? (p.kv_stride >> 7) : 0) + head_row;
+                tma_load_3d(st + half * PF_HALF + pg * 2048, &tmap_kv, half * 64, (int)(row0 % ts_rows), (int)(row0 / ts_rows), &full_bar[s]);
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128);
+            constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128) | (1u << 16);
+            bool good = mbar_wait(&q_full, 0);
+            if (!good) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 52);
+            // scores of query tile x against key tile j; the K unit is released after the last tile that uses it
+            auto issue_s = [&](int x, int j) -> bool {
+                const int u = 2 * j, s = u % PF2_UNITS;
+                if (!mbar_wait(&full_bar[s], (uint32_t)(u / PF2_UNITS) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 53); return false; }
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(ring + s * PF_TILE_BYTES), q_addr = smem_u32(q_sm + x * PF_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint64_t a = umma_desc_k_sw128(q_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
+                    const uint64_t b = umma_desc_k_sw128(k_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
+                    tc_mma_f16(tmem_base + x * 128, a, b, idesc_s, k ? 1u : 0u);
+                }
+                const bool last_user = x == 1 || j >= nkt_x[1];
+                if (last_user) tc_commit(&empty_bar[s]);
+                tc_commit(&s_ready[x]);
+                return true;
+            };
+            auto issue_pv = [&](int x, int j) -> bool {
+                if (!mbar_wait(&p_ready[x], (uint32_t)j & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 54); return false; }
+                const int u = 2 * j + 1, s = u % PF2_UNITS;
+                if (!mbar_wait(&full_bar[s], (uint32_t)(u / PF2_UNITS) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 55); return false; }
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(ring + s * PF_TILE_BYTES), p_addr = smem_u32(p_sm + x * PF_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint64_t a = umma_desc_k_sw128(p_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
+                    const uint64_t b = pf_desc_mn_sw128(v_addr + k * 2048, PF_HALF, 1024);
+                    tc_mma_f16(tmem_base + 256 + x * 128, a, b, idesc_o, (j | k) ? 1u : 0u);
+                }
+                const bool last_user = x == 1 || j >= nkt_x[1];
+                if (last_user) tc_commit(&empty_bar[s]);
+                tc_commit(&o_done[x]);
+                return true;
+            };
+            if (good) good = issue_s(0, 0);
+            if (good && nkt_x[1] > 0) good = issue_s(1, 0);
+            for (int j = 0; j < n_kt && good; ++j) {
+                for (int x = 0; x < 2 && good; ++x) {
+                    if (j >= nkt_x[x]) continue;
+                    good = issue_pv(x, j);
+                    if (good && j + 1 < nkt_x[x]) good = issue_s(x, j + 1);     // its score buffer is free: the P of tile j has been written
+                }
+            }
+        }
+    } else {
+        // ---------------- softmax warpgroups: warpgroup x <-> query tile x, thread r <-> query row r ----------------
+        const int x = warp >> 2;
+        const int r = threadIdx.x & 127;
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tm_s = tmem_base + x * 128, tm_o = tmem_base + 256 + x * 128;
+        const int qt = qt_x[x], my_kt = nkt_x[x];
+        const float qs = p.scale * 1.4426950408889634f;
+        const int qpos_raw = qt * PF_TILE + r;
+        const bool row_valid = my_kt > 0 && qpos_raw < n;
+        const int qpos = qpos_raw < n ? qpos_raw : n - 1;
+        unsigned char* prow = p_sm + x * PF_TILE_BYTES;
+        float m_ref = -INFINITY, l_sum = 0.f;
+        bool ok = true;
+        for (int j = 0; j < my_kt; ++j) {
+            // A wait that runs out does not leave the loop: the thread keeps arriving, so that nobody waits for it without a bound.
+            if (ok && !mbar_wait(&s_ready[x], (uint32_t)j & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 56); ok = false; }
+            tc_fence_after();
+            uint32_t sc[128];
+            pf_tmem_ld_x32(tm_s + lane_off, sc);
+            pf_tmem_ld_x32(tm_s + lane_off + 32, sc + 32);
+            pf_tmem_ld_x32(tm_s + lane_off + 64, sc + 64);
+            pf_tmem_ld_x32(tm_s + lane_off + 96, sc + 96);
+            tc_wait_ld();
+            const int kbase = j * PF_TILE;
+            float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
+            if (j == qt) {                                                 // the diagonal tile: causal mask and the prompt's end
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    const int kpos = kbase + i;
+                    if (kpos > qpos || kpos >= n) sc[i] = 0xff800000u;     // -inf
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 128; i += 4) {
+                t0 = fmaxf(t0, __uint_as_float(sc[i]));
+                t1 = fmaxf(t1, __uint_as_float(sc[i + 1]));
+                t2 = fmaxf(t2, __uint_as_float(sc[i + 2]));
+                t3 = fmaxf(t3, __uint_as_float(sc[i + 3]));
+            }
+            const float tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)) * qs;
+            float alpha = 1.0f;
+            const bool raise = tmax > m_ref + PF_RESCALE || m_ref == -INFINITY;
+            if (raise) {
+                alpha = m_ref == -INFINITY ? 0.f : exp2f(m_ref - tmax);
+                m_ref = tmax;
+            }
+            // P_x is single-buffered and the accumulator may only be touched between two P.V: wait for the P.V of tile j-1.
+            if (j > 0 && ok && !mbar_wait(&o_done[x], (uint32_t)(j - 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 57); ok = false; }
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {                 // tcgen05.ld/st are warp-wide: decide per warp
+                tc_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < 128; c0 += 16) {
+                    uint32_t o[16];
+                    tmem_ld_x16(tm_o + lane_off + c0, o);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    pf_tmem_st_x16(tm_o + lane_off + c0, o);
+                }
+                pf_wait_st();
+            }
+            l_sum *= alpha;
+            const float neg_m = -m_ref;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+            for (int c = 0; c < 128; c += 8) {
+                float e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) e[i] = exp2f(fmaf(__uint_as_float(sc[c + i]), qs, neg_m));
+                s0 += e[0] + e[4]; s1 += e[1] + e[5]; s2 += e[2] + e[6]; s3 += e[3] + e[7];
+                uint32_t packed[4];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(e[i], e[i + 1]);
+                    packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+                }
+                *reinterpret_cast<uint4*>(prow + (c >> 6) * PF_HALF + pf_sw128(r, c & 63)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            l_sum += (s0 + s1) + (s2 + s3);
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(&p_ready[x]);
+        }
+        if (my_kt > 0) {
+            if (ok && !mbar_wait(&o_done[x], (uint32_t)(my_kt - 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 58); ok = false; }
+            tc_fence_after();
+            const float inv = (ok && l_sum > 0.f) ? 1.0f / l_sum : 0.f;
+            __nv_bfloat16* orow = p.out + ((long long)(tok_base + qpos_raw) * p.q_heads + head) * 128;
+#pragma unroll 1
+            for (int c0 = 0; c0 < 128; c0 += 16) {
+                uint32_t o[16];
+                tmem_ld_x16(tm_o + lane_off + c0, o);
+                tc_wait_ld();
+                uint32_t packed[8];
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                    packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+                }
+                if (row_valid) {
+                    *reinterpret_cast<uint4*>(orow + c0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    *reinterpret_cast<uint4*>(orow + c0 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) tmem_dealloc(tmem_base, 512);
+}
+
 typedef CUresult (*PfEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -349,6 +596,14 @@ cudaError_t launch_prefill_attn_tc(const PrefillAttnParams& p, long long pool_ro
     CUtensorMap tq, tkv;
     if (!pf_make_tmap(&tq, p.q, p.q_heads, p.total_tokens, PF_TILE)) return cudaErrorInvalidValue;
     if (!pf_make_tmap(&tkv, p.kv, ts_rows, pool_rows / ts_rows, 16)) return cudaErrorInvalidValue;
+    if (p.two_tiles) {
+        static unsigned long long attr_mask2 = 0;
+        if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(prefill_attn_tc2_kernel), PF2_SMEM, &attr_mask2); e != cudaSuccess) return e;
+        const int q_tiles = (p.max_len + PF_TILE - 1) / PF_TILE;
+        dim3 grid(p.q_heads, (q_tiles + 1) / 2, p.n_seqs);
+        prefill_attn_tc2_kernel<<<grid, PF_THREADS, PF2_SMEM, stream>>>(tq, tkv, p);
+        return cudaGetLastError();
+    }
     static unsigned long long attr_mask = 0;
     if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(prefill_attn_tc_kernel), PF_SMEM, &attr_mask); e != cudaSuccess) return e;
     dim3 grid(p.q_heads, (p.max_len + PF_TILE - 1) / PF_TILE, p.n_seqs);

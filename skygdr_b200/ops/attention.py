@@ -55,10 +55,13 @@ class PrefillAttention:
     Pages must hold finite values past a prompt's last token (a fresh pool is zeroed); block-table entries past a prompt's
     pages must name valid blocks."""
 
-    def __init__(self, device):
+    def __init__(self, device, two_tiles: bool = True):
+        """two_tiles: two query tiles per CTA working in alternation with the tensor core (the faster variant); False: one
+        query tile per CTA with two softmax warpgroups per tile."""
         self._C = load()
         self.device = torch.device(device)
         self.status = new_status(self.device)
+        self.two_tiles = two_tiles
 
     def __call__(self, q: torch.Tensor, pool: PagedKVPool, layer: int, block_table: torch.Tensor, seq_start: torch.Tensor, max_len: int,
                  out: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
@@ -73,7 +76,7 @@ class PrefillAttention:
             head_stride, tok_stride = g.head_dim, g.kv_heads * g.head_dim
         self._C.prefill_attn(q, pool.layer_base(layer), out, block_table, seq_start, bs, ks, head_stride, tok_stride, g.kv_heads, int(max_len),
                              scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]), self.status,
-                             (pool.data.numel() - layer * ls) // 128)
+                             (pool.data.numel() - layer * ls) // 128, self.two_tiles)
         return out
 
 

@@ -253,14 +253,15 @@ def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
     assert int(attn.counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("two_tiles", [True, False])
 @pytest.mark.parametrize("layout", ["hnd", "nhd"])
 @pytest.mark.parametrize("kv_heads,q_heads", [(8, 32), (2, 4), (1, 1)])
-def test_prefill_attention_matches_reference(ops, layout, kv_heads, q_heads):
+def test_prefill_attention_matches_reference(ops, layout, kv_heads, q_heads, two_tiles):
     """Causal attention of packed prompts read in place from the paged pool, against fp32 softmax attention in PyTorch.
     Lengths straddle the 128-token tile (1, 127, 128, 129), the page (16) and several key tiles (700)."""
     torch.manual_seed(4)
     g = ops.KVGeometry(layers=2, kv_heads=kv_heads)
-    lens = [1, 127, 128, 129, 300, 700, 16, 17]
+    lens = [1, 127, 128, 129, 300, 700, 16, 17, 256, 257, 385]
     nblk = sum((n + 15) // 16 for n in lens) + 3
     pool = ops.PagedKVPool(g, nblk, layout)
     pool.data.normal_()
@@ -275,7 +276,7 @@ def test_prefill_attention_matches_reference(ops, layout, kv_heads, q_heads):
     T = sum(lens)
     q = torch.randn((T, q_heads, 128), dtype=torch.bfloat16, device="cuda")
     seq_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32, device="cuda")
-    attn = ops.PrefillAttention("cuda")
+    attn = ops.PrefillAttention("cuda", two_tiles=two_tiles)
     for layer in (0, 1):
         out = attn(q, pool, layer, table, seq_start, max(lens))
         torch.cuda.synchronize()
