@@ -4,7 +4,8 @@
 # the HBM stressor, the decode KV-scan stressors, memhog and the PCIe memcpy worker.
 # cpu_client.cc / gpu_server.cu need <infiniband/verbs.h> and are skipped when it is missing.
 set -u
-REF="${1:-/root/reference}"
+REF="${1:-${SKYGDR_REFERENCE_DIR:-}}"
+if [ -z "$REF" ] || [ ! -d "$REF" ]; then echo "usage: build_ref.sh <path to the reference checkout> (or set SKYGDR_REFERENCE_DIR)" >&2; exit 2; fi
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref/bin"
 mkdir -p "$OUT"

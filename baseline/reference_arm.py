@@ -1,6 +1,6 @@
 """`bench.py --impl reference`: what can be run of the unmodified reference for the headline metric.
 
-The reference is not a Python package (no setup.py / pyproject.toml: `pip install /root/reference` ends
+The reference is not a Python package (no setup.py / pyproject.toml: `pip install <reference checkout>` ends
 with "neither 'setup.py' nor 'pyproject.toml' found"), has no decoder model, no GEMM and no tensor
 parallelism, and its scheduled data path needs libibverbs and an RNIC. So the headline configuration
 (Qwen3-8B tensor-parallel decode) cannot be produced by it. What does exist is its decode KV-scan

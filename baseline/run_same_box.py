@@ -1,7 +1,7 @@
 """Same-box comparison: the reference's own CUDA programs (built unmodified for sm_100 by baseline/build_ref.sh)
 next to this runtime's equivalents, on the GPU(s) of this machine.
 
-    python baseline/run_same_box.py [--gpus 1|2] [--out gpurun_out/same_box.json]
+    python baseline/run_same_box.py [--gpus 1|2] [--out results/same_box.json]
 
 One GPU: HBM stressor, memhog (rw), PCIe copy task (d2h, h2d), decode KV-cache stressor. Two GPUs add the NVLink
 transfers (fixed size and trace-shaped). Every reference number is scraped from the program's own summary line.
@@ -35,7 +35,7 @@ def grab(pattern, text, scale=1.0):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--out", default="gpurun_out/same_box.json")
+    ap.add_argument("--out", default="results/same_box.json")
     a = ap.parse_args()
     py = [sys.executable, "-m"]
     G = 1.073741824

@@ -1,7 +1,7 @@
 """Point-to-point KV transfer between GPUs: Qwen3-8B-shaped paged KV (36 layers x 8 KV heads x 128, bf16, 16-token
 blocks, randomly permuted block tables, N(0,1) values), sequence lengths uniform 1k-64k.
 
-    python benchmarks/config2_kv_transfer.py [--gpus 2] [--requests 12] [--out gpurun_out/config2.json] [--ref]
+    python benchmarks/config2_kv_transfer.py [--gpus 2] [--requests 12] [--out results/config2.json] [--ref]
 
 One process drives all GPUs (peer access). Arms:
   kernel        this runtime's paged gather + layout + peer-store kernel, unpaced
@@ -78,7 +78,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=min(2, torch.cuda.device_count()))
     ap.add_argument("--requests", type=int, default=12)
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--out", default="gpurun_out/config2.json")
+    ap.add_argument("--out", default="results/config2.json")
     ap.add_argument("--ref", action="store_true")
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--pages-per-chunk", type=int, default=8)

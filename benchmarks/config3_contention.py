@@ -1,6 +1,6 @@
 """Decode / NVLink / HBM contention on one GPU, with and without scheduling.
 
-    python benchmarks/config3_contention.py [--decode-gpu 1 --src-gpu 0] [--out gpurun_out/config3.json] [--ref]
+    python benchmarks/config3_contention.py [--decode-gpu 1 --src-gpu 0] [--out results/config3.json] [--ref]
 
 On the decode GPU: paged GQA decode attention (32 query / 8 KV heads, head_dim 128, bf16, batch 64, context lengths
 log-normal with median 8k clipped to 1k-32k, 36 layers per step). Against it: an inbound 4 GB KV transfer from the
@@ -95,7 +95,7 @@ def main():
     ap.add_argument("--transfer-gb", type=float, default=4.0)
     ap.add_argument("--memhog-gb", type=float, default=8.0)
     ap.add_argument("--transfer-target-gbps", type=float, default=200.0)
-    ap.add_argument("--out", default="gpurun_out/config3.json")
+    ap.add_argument("--out", default="results/config3.json")
     a = ap.parse_args()
     C = load()
     ddev, sdev = torch.device("cuda", a.decode_gpu), torch.device("cuda", a.src_gpu)

@@ -3,7 +3,7 @@ NVLink with the credit-gated transfer kernel, while a background kv_offload stre
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
         benchmarks/config4_pd_disagg.py --prefill-gpus 4 --decode-gpus 4 [--arm controlled|always_high|always_low]
-        [--rate 4 --duration 20] [--offload-gbps 24] [--layers 36] [--out gpurun_out/config4.json]
+        [--rate 4 --duration 20] [--offload-gbps 24] [--layers 36] [--out results/config4.json]
 
 Requests (same seed on every rank): Poisson arrivals, input lengths log-normal (median 16k, clipped to 64k), output
 lengths uniform 128-1024 (scaled by --out-scale). Request i is prefilled on prefill rank i % P and decoded on decode
@@ -71,7 +71,7 @@ def main():
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--slots", type=int, default=8)
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--out", default="gpurun_out/config4.json")
+    ap.add_argument("--out", default="results/config4.json")
     a = ap.parse_args()
     C = load()
     world, rank, local = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])

@@ -3,7 +3,7 @@ and offloads KV to pinned host memory.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         benchmarks/config5_tp_contention.py [--seconds 3] [--burst-gb 2 --burst-every-ms 500] [--offload-gbps 16]
-        [--baseline nccl] [--out gpurun_out/config5.json]
+        [--baseline nccl] [--out results/config5.json]
 
 Phases per run: clean decode; contended, unscheduled (bursts and offload unpaced); contended, scheduled (the offload is
 held to its offered rate by its credit page, the bursts are paced to `--burst-budget-gbps`). Each rank r receives bursts
@@ -76,7 +76,7 @@ def main():
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--baseline", default="", choices=["", "nccl"])
     ap.add_argument("--diagnose", action="store_true", help="also run each background flow alone, paced and unpaced")
-    ap.add_argument("--out", default="gpurun_out/config5.json")
+    ap.add_argument("--out", default="results/config5.json")
     a = ap.parse_args()
     C = load()
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
