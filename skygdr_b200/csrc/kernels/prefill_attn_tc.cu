@@ -39,35 +39,7 @@ constexpr int PF_TILES_BYTES = PF_TILE_BYTES * (1 + PF_UNITS + 2);       // Q, t
 constexpr int PF_SMEM = PF_TILES_BYTES + 2 * 2 * PF_TILE * 4 + 256;       // + maxima exchange + barriers; no static shared memory
 constexpr float PF_RESCALE = 8.0f;
 
-__device__ __forceinline__ uint32_t pf_sw128(int row, int col) {        // byte offset of (row, col) in a [rows][64] swizzled half
-    return (uint32_t)(row * 128 + (((col >> 3) ^ (row & 7)) << 4) + (col & 7) * 2);
-}
-__device__ __forceinline__ uint64_t pf_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)(lbo >> 4) << 16;
-    d |= (uint64_t)(sbo >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-__device__ __forceinline__ void pf_tmem_st_x16(uint32_t taddr, const uint32_t* r) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
-}
-__device__ __forceinline__ void pf_tmem_ld_x32(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-          "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
 __device__ __forceinline__ void pf_softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-__device__ __forceinline__ void pf_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                                          const __grid_constant__ CUtensorMap tmap_kv, const PrefillAttnParams p) {
@@ -181,7 +153,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {                                        // 8 steps of 16 keys
                     const uint64_t a = umma_desc_k_sw128(p_addr + (j & 1) * PF_TILE_BYTES + (k >> 2) * PF_HALF + (k & 3) * 32);
-                    const uint64_t b = pf_desc_mn_sw128(v_addr + k * 2048, PF_HALF, 1024);
+                    const uint64_t b = umma_desc_mn_sw128(v_addr + k * 2048, PF_HALF, 1024);
                     tc_mma_f16(tm_o, a, b, idesc_o, (j | k) ? 1u : 0u);
                 }
                 tc_commit(&empty_bar[s]);        // the V tile is free again
@@ -207,8 +179,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
             if (ok && !mbar_wait(&s_ready[par], (uint32_t)(j >> 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 46); ok = false; }
             tc_fence_after();
             uint32_t sc[64];
-            pf_tmem_ld_x32(tm_s[par] + lane_off + col0, sc);
-            pf_tmem_ld_x32(tm_s[par] + lane_off + col0 + 32, sc + 32);
+            tmem_ld_x32(tm_s[par] + lane_off + col0, sc);
+            tmem_ld_x32(tm_s[par] + lane_off + col0 + 32, sc + 32);
             tc_wait_ld();
             const bool diag = j == qt;
             const int kbase = j * PF_TILE + col0;
@@ -254,9 +226,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
                     tc_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    pf_tmem_st_x16(tm_o + lane_off + col0 + c0, o);
+                    tmem_st_x16(tm_o + lane_off + col0 + c0, o);
                 }
-                pf_wait_st();
+                tc_wait_st();
             } else if (j > 1) {
                 if (ok && !mbar_wait(&o_done[par], (uint32_t)((j - 2) >> 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 47); ok = false; }
             }
@@ -277,7 +249,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
                     const __nv_bfloat162 b2 = __floats2bfloat162_rn(e[i], e[i + 1]);
                     packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
                 }
-                *reinterpret_cast<uint4*>(prow + pf_sw128(r, c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(prow + sw128_off(r, c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
             l_sum += (s0 + s1) + (s2 + s3);
             fence_proxy_async();
@@ -432,7 +404,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc2_kernel(const _
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const uint64_t a = umma_desc_k_sw128(p_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
-                    const uint64_t b = pf_desc_mn_sw128(v_addr + k * 2048, PF_HALF, 1024);
+                    const uint64_t b = umma_desc_mn_sw128(v_addr + k * 2048, PF_HALF, 1024);
                     tc_mma_f16(tmem_base + 256 + x * 128, a, b, idesc_o, (j | k) ? 1u : 0u);
                 }
                 const bool last_user = x == 1 || j >= nkt_x[1];
@@ -469,10 +441,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc2_kernel(const _
             if (ok && !mbar_wait(&s_ready[x], (uint32_t)j & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 56); ok = false; }
             tc_fence_after();
             uint32_t sc[128];
-            pf_tmem_ld_x32(tm_s + lane_off, sc);
-            pf_tmem_ld_x32(tm_s + lane_off + 32, sc + 32);
-            pf_tmem_ld_x32(tm_s + lane_off + 64, sc + 64);
-            pf_tmem_ld_x32(tm_s + lane_off + 96, sc + 96);
+            tmem_ld_x32(tm_s + lane_off, sc);
+            tmem_ld_x32(tm_s + lane_off + 32, sc + 32);
+            tmem_ld_x32(tm_s + lane_off + 64, sc + 64);
+            tmem_ld_x32(tm_s + lane_off + 96, sc + 96);
             tc_wait_ld();
             const int kbase = j * PF_TILE;
             float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
@@ -508,9 +480,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc2_kernel(const _
                     tc_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    pf_tmem_st_x16(tm_o + lane_off + c0, o);
+                    tmem_st_x16(tm_o + lane_off + c0, o);
                 }
-                pf_wait_st();
+                tc_wait_st();
             }
             l_sum *= alpha;
             const float neg_m = -m_ref;
@@ -527,7 +499,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc2_kernel(const _
                     const __nv_bfloat162 b2 = __floats2bfloat162_rn(e[i], e[i + 1]);
                     packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
                 }
-                *reinterpret_cast<uint4*>(prow + (c >> 6) * PF_HALF + pf_sw128(r, c & 63)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(prow + (c >> 6) * PF_HALF + sw128_off(r, c & 63)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
             l_sum += (s0 + s1) + (s2 + s3);
             fence_proxy_async();
