@@ -311,6 +311,38 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* r) {
         : "r"(taddr) : "memory");
 }
 
+// Split-KV combine of one output element: log-sum-exp merge of `n` partial results (running maximum m, sum l, value o),
+// eight partials at a time so that their loads are in flight together (one L2 round trip per eight splits instead of
+// one per split and array). part_o points at this thread's column of the first partial; partials are `o_pitch` floats apart.
+__device__ __forceinline__ float combine_splits(const float* part_m, const float* part_l, const float* part_o, long long o_pitch, int n) {
+    float mm = -INFINITY, ll = 0.f, oo = 0.f;
+    for (int s0 = 0; s0 < n; s0 += 8) {
+        float m8[8], l8[8], o8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const bool in = s0 + i < n;
+            m8[i] = in ? __ldcg(part_m + s0 + i) : -INFINITY;
+            l8[i] = in ? __ldcg(part_l + s0 + i) : 0.f;
+            o8[i] = in ? __ldcg(part_o + (long long)(s0 + i) * o_pitch) : 0.f;
+        }
+        float cm = m8[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) cm = fmaxf(cm, m8[i]);
+        const float nm = fmaxf(mm, cm);
+        const float keep = mm == -INFINITY ? 0.f : exp2f(mm - nm);
+        ll *= keep;
+        oo *= keep;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float r = m8[i] == -INFINITY ? 0.f : exp2f(m8[i] - nm);
+            ll += l8[i] * r;
+            oo += o8[i] * r;
+        }
+        mm = nm;
+    }
+    return ll > 0.f ? oo / ll : 0.f;
+}
+
 // Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, tile M x N.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);

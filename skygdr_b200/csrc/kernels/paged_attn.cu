@@ -268,15 +268,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         const long long row = row0 + (long long)g * p.max_splits;
-        float mm = -INFINITY;
-        for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, __ldcg(p.part_m + row + s));
-        float ll = 0.f, oo = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float r = exp2f(__ldcg(p.part_m + row + s) - mm);
-            ll += __ldcg(p.part_l + row + s) * r;
-            oo += __ldcg(p.part_o + (row + s) * ATT_D + d) * r;
-        }
-        p.out[((long long)b * p.q_heads + kvh * G + g) * ATT_D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+        p.out[((long long)b * p.q_heads + kvh * G + g) * ATT_D + d] =
+            __float2bfloat16(combine_splits(p.part_m + row, p.part_l + row, p.part_o + row * ATT_D + d, ATT_D, n_splits));
     }
 }
 

@@ -286,15 +286,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tc_kernel(const __gr
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     const long long row = row0 + (long long)g * p.max_splits;
-                    float mm = -INFINITY;
-                    for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, __ldcg(p.part_m + row + s));
-                    float ll = 0.f, oo = 0.f;
-                    for (int s = 0; s < n_splits; ++s) {
-                        const float r = exp2f(__ldcg(p.part_m + row + s) - mm);
-                        ll += __ldcg(p.part_l + row + s) * r;
-                        oo += __ldcg(p.part_o + (row + s) * 128 + d) * r;
-                    }
-                    p.out[((long long)b * p.q_heads + kvh * G + g) * 128 + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+                    p.out[((long long)b * p.q_heads + kvh * G + g) * 128 + d] =
+                        __float2bfloat16(combine_splits(p.part_m + row, p.part_l + row, p.part_o + row * 128 + d, 128, n_splits));
                 }
             }
         }
@@ -602,15 +595,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tcp_kernel(const __g
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
                         const long long row = row0 + (long long)g * p.max_splits;
-                        float mm = -INFINITY;
-                        for (int s = 0; s < it.n_splits; ++s) mm = fmaxf(mm, __ldcg(p.part_m + row + s));
-                        float ll = 0.f, oo = 0.f;
-                        for (int s = 0; s < it.n_splits; ++s) {
-                            const float r = exp2f(__ldcg(p.part_m + row + s) - mm);
-                            ll += __ldcg(p.part_l + row + s) * r;
-                            oo += __ldcg(p.part_o + (row + s) * 128 + d) * r;
-                        }
-                        p.out[((long long)it.b * p.q_heads + it.kvh * G + g) * 128 + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+                        p.out[((long long)it.b * p.q_heads + it.kvh * G + g) * 128 + d] =
+                            __float2bfloat16(combine_splits(p.part_m + row, p.part_l + row, p.part_o + row * 128 + d, 128, it.n_splits));
                     }
                 }
                 softmax_bar();                                 // s_last and lsum are rewritten by the next item

@@ -56,12 +56,19 @@ __global__ void __launch_bounds__(256) tp_norm_kernel(const TpNormParams p) {
         if (v < nvec) {
             unpack8f(*reinterpret_cast<const uint4*>(p.resid + (long long)row * p.hidden + v * 8), vals[k]);
             if (p.rs_buf) {
-                for (int s = 0; s < p.world; ++s) {
-                    float part[8];
-                    const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(p.rs_buf + ((long long)(s * p.rows + row)) * p.hidden + v * 8));
-                    unpack8f(raw, part);
+                // all partials of this piece are requested before the first one is used: one L2 round trip, not `world` of them
+                uint4 raw[TP_MAX_RANKS];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) vals[k][i] += part[i];
+                for (int s = 0; s < TP_MAX_RANKS; ++s)
+                    if (s < p.world) raw[s] = __ldcg(reinterpret_cast<const uint4*>(p.rs_buf + ((long long)(s * p.rows + row)) * p.hidden + v * 8));
+#pragma unroll
+                for (int s = 0; s < TP_MAX_RANKS; ++s) {
+                    if (s < p.world) {
+                        float part[8];
+                        unpack8f(raw[s], part);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) vals[k][i] += part[i];
+                    }
                 }
                 const uint4 packed = pack8f(vals[k]);
                 *reinterpret_cast<uint4*>(p.resid + (long long)row * p.hidden + v * 8) = packed;
