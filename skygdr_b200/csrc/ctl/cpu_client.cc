@@ -22,6 +22,7 @@
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
+#include <deque>
 #include <thread>
 #include <vector>
 
@@ -214,10 +215,43 @@ int main(int argc, char** argv) {
         win_completed0 = completed;
     };
 
-    // ---- data loop: one message in flight (the reference's write-with-ack path, src/cpu_client.cc:1088-1249) ----
+    // ---- data loop ----
+    // Two shapes, as in the reference: acknowledged writes keep one message in flight and wait for its ACK tag
+    // (src/cpu_client.cc:1088-1249); reads and unacknowledged writes keep `qd` messages in flight per queue pair and
+    // repost as completions come back (the steady-queue-depth loop, src/cpu_client.cc:943-1087). On the simulated
+    // fabric the link serves one message at a time at its rate, so latency grows with the depth while throughput
+    // stays at the link rate; over TCP the requests are pipelined on the connection.
     int rc = 0;
     SkyHeartbeatWatch heartbeat = {0, 0, 0};
-    for (uint64_t i = 0; i < iters && !ctl.stop_requested(); ++i) {
+    struct InFlight { uint64_t t_post, t_link_done; uint32_t tag; };
+    std::deque<InFlight> in_flight;
+    const size_t depth = write_ack ? 1 : (size_t)std::max(1, qd) * (size_t)qps;
+    uint64_t link_free = mono_ns();
+    auto account = [&](uint64_t t_post, uint64_t t_done) {
+        ++completed;
+        if (page) { page->completed_bytes += msg; page->last_ts_ns = t_done; }
+        if ((seen++ % sample) == 0) {
+            double us = (t_done - t_post) * 1e-3;
+            if (max_samples == 0 || lat_us.size() < max_samples) lat_us.push_back(us);
+            lat_win.push_back(us);
+        }
+    };
+    auto complete_oldest = [&]() -> bool {
+        InFlight f = in_flight.front();
+        in_flight.pop_front();
+        if (s >= 0) {
+            if (is_read && !sim) { if (!recv_all(s, buf.data(), msg)) { rc = 4; return false; } }
+            else if (is_read || write_ack) {
+                uint32_t tag = 0;
+                if (!recv_all(s, &tag, 4)) { rc = 4; return false; }
+                if (write_ack && tag != f.tag) { fprintf(stderr, "[client] unexpected ACK tag %u (want %u)\n", tag, f.tag); rc = 4; return false; }
+            }
+        }
+        if (sim) while (mono_ns() < f.t_link_done) { /* the link is still busy with this message */ }
+        account(f.t_post, mono_ns());
+        return true;
+    };
+    for (uint64_t i = 0; i < iters && !ctl.stop_requested() && rc == 0; ++i) {
         uint64_t off;
         if (pattern == "seq") { off = seq_off; seq_off += msg; if (seq_off + msg > span) seq_off = 0; }
         else off = span > msg ? (uint64_t)(rng.uniform() * double(span - msg)) : 0;
@@ -229,46 +263,33 @@ int main(int argc, char** argv) {
             consumed += msg;
             page->consumed_bytes = consumed;
         }
-        uint64_t t0 = mono_ns();
+        while (in_flight.size() >= depth && rc == 0) complete_oldest();
+        if (rc) break;
+        InFlight f{mono_ns(), 0, (uint32_t)i};
         if (sim) {
-            uint64_t service_ns = (uint64_t)(double(msg) / (sim_gbps * 1e9) * 1e9);
-            if (s >= 0) {                                // server in the loop, payload not moved
-                MsgHeader h{off, (uint32_t)msg, (uint32_t)i, is_read ? 1u : 0u, 0};
-                uint32_t tag = 0;
-                if (!send_all(s, &h, sizeof h) || ((write_ack || is_read) && !recv_all(s, &tag, 4))) { rc = 4; break; }
-            }
-            while (mono_ns() - t0 < service_ns) { /* the link is busy with this message */ }
-        } else {
+            const uint64_t service_ns = (uint64_t)(double(msg) / (sim_gbps * 1e9) * 1e9);
+            f.t_link_done = std::max(f.t_post, link_free) + service_ns;
+            link_free = f.t_link_done;
+        }
+        if (s >= 0) {
             MsgHeader h{off, (uint32_t)msg, (uint32_t)i, is_read ? 1u : 0u, 0};
             if (!send_all(s, &h, sizeof h)) { rc = 3; break; }
-            if (is_read) { if (!recv_all(s, buf.data(), msg)) { rc = 4; break; } }
-            else {
-                if (!send_all(s, buf.data(), msg)) { rc = 3; break; }
-                if (write_ack) {
-                    uint32_t tag = 0;
-                    if (!recv_all(s, &tag, 4)) { rc = 4; break; }
-                    if (tag != (uint32_t)i) { fprintf(stderr, "[client] unexpected ACK tag %u (want %u)\n", tag, (uint32_t)i); rc = 4; break; }
-                }
-            }
+            if (!sim && !is_read && !send_all(s, buf.data(), msg)) { rc = 3; break; }     // the payload of a write travels with it
         }
-        uint64_t t1 = mono_ns();
-        ++completed;
-        if (page) { page->completed_bytes = consumed; page->last_ts_ns = t1; }
-        if ((seen++ % sample) == 0) {
-            double us = (t1 - t0) * 1e-3;
-            if (max_samples == 0 || lat_us.size() < max_samples) lat_us.push_back(us);
-            lat_win.push_back(us);
-        }
-        uint32_t pace = ctl.sleep_us();                 // legacy pacing: sleep after each post
+        in_flight.push_back(f);
+        if (write_ack && !complete_oldest()) break;      // acknowledged writes: wait for this one before the next
+        uint32_t pace = ctl.sleep_us();                  // legacy pacing: sleep after each post
         if (pace) std::this_thread::sleep_for(std::chrono::microseconds(pace));
         flush_window(false);
-        if (dsock >= 0 && t1 - renew_at > 500000000ull) {
+        const uint64_t now = mono_ns();
+        if (dsock >= 0 && now - renew_at > 500000000ull) {
             char line[64], rep[64];
             int n = snprintf(line, sizeof line, "RENEW %u\n", flow_id);
             if (send_all(dsock, line, (size_t)n)) { ssize_t k = recv(dsock, rep, sizeof rep, 0); (void)k; }
-            renew_at = t1;
+            renew_at = now;
         }
     }
+    while (!in_flight.empty() && rc == 0) complete_oldest();       // drain what is still in flight
     double sec = (mono_ns() - t_start) * 1e-9;
     flush_window(true);
     if (ts_fp && ts_fp != stdout) fclose(ts_fp);

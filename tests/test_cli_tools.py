@@ -308,3 +308,24 @@ def test_flow_outlives_a_killed_daemon_under_the_unpaced_dead_policy():
         if p.poll() is None:
             p.kill()
     assert "samples=3000" in out, out + err
+
+
+def test_steady_queue_depth_trades_latency_for_nothing_on_a_saturated_link():
+    """Reads and unacknowledged writes keep `qd` messages in flight (the reference's steady-queue-depth loop,
+    src/cpu_client.cc:943-1087): on the simulated 1 GB/s link the throughput stays at the link rate while the latency of a
+    64 KiB message is depth x 65.5 us. Reads never run below read_min_qd (16); acknowledged writes keep one in flight."""
+    def run(*tail):
+        out = subprocess.run([f"{BIN}/cpu_client", "-", "0", "sim:1", "300", "64K", *tail], capture_output=True, text=True, env=ENV, timeout=60).stdout
+        return float(out.split("throughput=")[1].split()[0]), float(out.split("p50=")[1].split()[0])
+
+    positional = ["0", "random", "256", "1024", "1", "0", "0", ""]          # span pattern align mtu sample max_samples ts_ms ts_out
+    thr, p50 = run("write", "1", "0", "8", *positional, "0")                # write_ack=0, qd=8
+    assert 0.85 < thr < 0.97 and 480 < p50 < 600
+    thr, p50 = run("write", "1", "0", "2", *positional, "0")                # qd=2
+    assert 0.85 < thr < 0.97 and 110 < p50 < 170
+    thr, p50 = run("write", "1", "0", "8", *positional, "1")                # acknowledged: one in flight whatever qd says
+    assert 0.85 < thr < 0.97 and 60 < p50 < 90
+    thr, p50 = run("read", "1", "0", "4")                                   # raised to read_min_qd = 16
+    assert 0.85 < thr < 0.97 and 950 < p50 < 1150
+    thr, p50 = run("read", "1", "0", "4", *positional, "0", "2")            # read_min_qd=2 -> qd 4
+    assert 0.85 < thr < 0.97 and 230 < p50 < 300
