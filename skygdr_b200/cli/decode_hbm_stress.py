@@ -19,6 +19,7 @@ def main(argv=None) -> int:
     from skygdr_b200.ops import Memhog
 
     torch.cuda.set_device(gpu)
+    print(f"gpu={gpu} name={torch.cuda.get_device_name(gpu)} working_set={ws_mib} MiB iters={iters}", flush=True)
     hog = Memhog(f"cuda:{gpu}", gb=ws_mib / 1024.0, op="axpy")
     hog.a.fill_(1.0)
     hog.launch(iters=1)

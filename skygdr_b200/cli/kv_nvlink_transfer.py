@@ -123,9 +123,24 @@ def main(argv=None) -> int:
 
     assert a.elem_bytes == 2 and a.head_dim == 128, "the transfer kernel moves bf16 pages of head_dim 128"
     geom = KVGeometry(a.layers, a.kv_heads, a.head_dim)
+    def pct(v, q):                                        # the reference's index rule (kv_nvlink_transfer_trace.cu:255-266)
+        v = sorted(v)
+        return v[int(q * (len(v) - 1))] if v else 0
+
     if a.trace:
         iters = a.iters or 10000
         tokens = ctl.sample_trace_tokens(a.dist, a.seed, iters, a.max_tokens)
+        dist = ctl.trace_dist(a.dist, a.max_tokens)
+        nbytes = [geom.blocks_for(t) * geom.block_elems * 2 for t in tokens]
+        # header block with the reference's labels (kv_nvlink_transfer_trace.cu:291-325), which its harnesses grep for
+        print(f"src_gpu={a.src} dst_gpu={a.dst} iters={iters} dist={a.dist}")
+        print("peer_access src->dst=1 dst->src=1")
+        print(f"KV geometry: layers={a.layers} kv_heads={a.kv_heads} head_dim={a.head_dim} elem_bytes={a.elem_bytes}")
+        print(f"Trace quantiles: p50={round(dist.inverse_cdf(0.5))} p90={round(dist.inverse_cdf(0.9))} p99={round(dist.inverse_cdf(0.99))} "
+              f"max={round(dist.inverse_cdf(1.0))} tokens")
+        print(f"sampled tokens: p50={pct(tokens, 0.5)} p90={pct(tokens, 0.9)} p99={pct(tokens, 0.99)} max={max(tokens)}")
+        print(f"sampled bytes: p50={pct(nbytes, 0.5)} p90={pct(nbytes, 0.9)} p99={pct(nbytes, 0.99)} max={max(nbytes)}")
+        print(f"max transfer allocation: {max(nbytes) / GIB:.2f} GiB (paged: whole 16-token blocks)", flush=True)
         total, dev_s, per_ms, wall = run_transfers(a.src, a.dst, tokens, geom, a.method, a.budget_gbps, seed=a.seed)
         gib = total / GIB
         print("Trace-shaped KV transfer done:")
@@ -141,6 +156,7 @@ def main(argv=None) -> int:
     size_mib = int(a.pos[2]) if len(a.pos) > 2 else 1024
     iters = int(a.pos[3]) if len(a.pos) > 3 else (a.iters or 100)
     tokens_per = max(16, (size_mib << 20) // geom.bytes_per_token())
+    print(f"src_gpu={src_gpu} dst_gpu={dst_gpu} size={size_mib} MiB iters={iters}", flush=True)
     total, dev_s, per_ms, wall = run_transfers(src_gpu, dst_gpu, [tokens_per] * iters, geom, a.method, a.budget_gbps, seed=a.seed)
     print(f"KV transfer done: {total / GIB:.2f} GiB in {dev_s:.3f} s = {total / GIB / dev_s:.2f} GiB/s ({total / dev_s / 1e9:.2f} GB/s) "
           f"method={a.method}")
