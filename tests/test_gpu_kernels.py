@@ -485,12 +485,16 @@ def test_cli_programs_run(ops):
     assert re.search(r"\[memhog\] bytes=\d+ kernel_s=[0-9.]+ bw_gib_s=[0-9.]+", out)
     out = run("decode_hbm_stress", "0", "1024", "5")
     assert re.search(r"HBM stress done: approx [0-9.]+ GiB in [0-9.]+ s = [0-9.]+ GiB/s", out)
+    assert re.search(r"gpu=0 name=.+ working_set=1024 MiB iters=5", out)
     out = run("gpu_pcie_memcpy", "--seconds=0", "--total_bytes=256M", "--chunk_mb=16", "--streams=2", "--batch=1", "--inflight=2", "--dir=h2d",
               "--report_ms=50")
     assert "[pcie] t=" in out and re.search(r"\[pcie\] done dir=h2d completed_bytes=268435456", out)
     out = run("kv_nvlink_transfer", "0", "0", "256", "3", "--layers", "4")
-    assert re.search(r"KV transfer done: [0-9.]+ GiB in [0-9.]+ s = [0-9.]+ GiB/s", out)
+    assert re.search(r"KV transfer done: [0-9.]+ GiB in [0-9.]+ s = [0-9.]+ GiB/s", out) and "src_gpu=0 dst_gpu=0 size=256 MiB iters=3" in out
     out = run("kv_nvlink_transfer_trace", "--src", "0", "--dst", "0", "--iters", "5", "--dist", "computed", "--layers", "4", "--max-tokens", "4096")
     assert "Trace-shaped KV transfer done:" in out and "transfers: 5" in out
+    for label in ("src_gpu=0 dst_gpu=0 iters=5 dist=computed", "KV geometry: layers=4 kv_heads=8 head_dim=128 elem_bytes=2", "Trace quantiles: p50=758",
+                  "sampled tokens: p50=", "sampled bytes: p50=", "max transfer allocation:"):
+        assert label in out, label
     out = run("decode_kvcache_stress", "--layers", "2", "--context", "2048", "--gen", "4", "--batch", "4")
     assert "Effective sequence-throughput:" in out and "Approx bandwidth:" in out
