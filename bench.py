@@ -43,6 +43,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=36, help="for smoke runs only; the benchmark uses 36")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--attn-impl", default="tc", choices=["tc", "tcp", "simt"])
+    ap.add_argument("--tp-collective", default="rs_ag", choices=["rs_ag", "oneshot"],
+                    help="tensor-parallel form: reduce-scatter + all-gather (default) or the one-shot all-reduce")
     ap.add_argument("--attn-chunk", type=int, default=1024)
     ap.add_argument("--profile-step", action="store_true", help="also print per-kernel-kind times of one eager step (tensor-parallel engine)")
     return ap.parse_args()
@@ -87,7 +89,7 @@ def main() -> int:
     total_steps = 2 * (args.steps + args.warmup) + 8
     max_ctx = int(ctx.max()) + total_steps + 1
     eng, table = build_decode_engine(cfg, dev, rank, world, ctx, total_steps, seed=args.seed, kv_init="normal",
-                                     attn_chunk=args.attn_chunk, attn_impl=args.attn_impl)
+                                     attn_chunk=args.attn_chunk, attn_impl=args.attn_impl, collective=args.tp_collective)
 
     ids0 = torch.randint(0, cfg.vocab, (batch,), generator=g).int()
     eng.set_batch(ids0.to(dev), ctx.int().to(dev), table.to(dev))

@@ -376,10 +376,11 @@ static void gemm_tp(torch::Tensor x, torch::Tensor w, torch::Tensor y, int split
     }
     if (rs.size() > 0) {
         p.rs.world = rs[0].cast<int>(); p.rs.src_rank = rs[1].cast<int>(); p.rs.rows_per_rank = rs[2].cast<int>();
+        p.rs.all = rs.size() > 5 && rs[5].cast<bool>() ? 1 : 0;
         auto dst = rs[3].cast<std::vector<uint64_t>>();
         auto ctr = rs[4].cast<std::vector<uint64_t>>();
         TORCH_CHECK((int)dst.size() == p.rs.world && (int)ctr.size() == p.rs.world && p.rs.world <= TP_MAX_RANKS, "rs pointer lists");
-        TORCH_CHECK(p.M <= p.rs.world * p.rs.rows_per_rank, "more token rows than the ranks own");
+        TORCH_CHECK(p.M <= (p.rs.all ? 1 : p.rs.world) * p.rs.rows_per_rank, "more token rows than the receive buffers hold");
         for (int i = 0; i < p.rs.world; ++i) { p.rs.dst[i] = (__nv_bfloat16*)dst[i]; p.rs.counters[i] = (unsigned int*)ctr[i]; }
     }
     SKY_CUDA_CHECK(launch_gemm(p, cur_stream()));
@@ -387,7 +388,7 @@ static void gemm_tp(torch::Tensor x, torch::Tensor w, torch::Tensor y, int split
 
 static void tp_norm(uint64_t rs_buf, uint64_t rs_counter, py::tuple rs_seq, torch::Tensor resid, torch::Tensor w,
                     std::vector<uint64_t> ag_dst, std::vector<uint64_t> ag_counter, int rank, double eps, uint64_t timeout_ns,
-                    torch::Tensor status) {
+                    torch::Tensor status, int rs_world) {
     c10::cuda::CUDAGuard g(resid.device());
     TpNormParams p;
     memset(&p, 0, sizeof p);
@@ -395,9 +396,14 @@ static void tp_norm(uint64_t rs_buf, uint64_t rs_counter, py::tuple rs_seq, torc
     p.rs_counter = (const unsigned int*)rs_counter;
     if (rs_buf) p.rs_seq = make_seq(rs_seq[0].cast<uint64_t>(), rs_seq[1].cast<unsigned>(), rs_seq[2].cast<unsigned>(), rs_seq[3].cast<unsigned>());
     p.resid = bf16_mut(resid); p.w = bf16_ptr(w);
-    p.world = (int)ag_dst.size(); p.rank = rank; p.rows = (int)resid.size(0); p.hidden = (int)resid.size(1);
-    TORCH_CHECK(p.world >= 1 && p.world <= TP_MAX_RANKS && ag_counter.size() == ag_dst.size(), "peer lists");
-    for (int i = 0; i < p.world; ++i) { p.ag_dst[i] = (__nv_bfloat16*)ag_dst[i]; p.ag_counter[i] = (unsigned int*)ag_counter[i]; }
+    // rs_world = 0: reduce-scatter / all-gather form (as many partials as all-gather destinations, rows offset by the rank);
+    // rs_world > 0: one-shot all-reduce form (rs_world full-size partials, the normed rows go to ag_dst as they are).
+    p.ag_n = (int)ag_dst.size();
+    p.world = rs_world > 0 ? rs_world : p.ag_n;
+    p.rank = rank; p.rows = (int)resid.size(0); p.hidden = (int)resid.size(1);
+    p.ag_row0 = rs_world > 0 ? 0 : rank * p.rows;
+    TORCH_CHECK(p.world >= 1 && p.world <= TP_MAX_RANKS && p.ag_n >= 1 && p.ag_n <= TP_MAX_RANKS && ag_counter.size() == ag_dst.size(), "peer lists");
+    for (int i = 0; i < p.ag_n; ++i) { p.ag_dst[i] = (__nv_bfloat16*)ag_dst[i]; p.ag_counter[i] = (unsigned int*)ag_counter[i]; }
     p.eps = (float)eps; p.timeout_ns = timeout_ns; p.status = status_ptr(status);
     SKY_CUDA_CHECK(launch_tp_norm(p, cur_stream()));
 }
@@ -479,7 +485,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("argmax", &argmax);
     m.def("gemm", &gemm);
     m.def("gemm_tp", &gemm_tp);
-    m.def("tp_norm", &tp_norm);
+    m.def("tp_norm", &tp_norm, py::arg("rs_buf"), py::arg("rs_counter"), py::arg("rs_seq"), py::arg("resid"), py::arg("w"), py::arg("ag_dst"),
+          py::arg("ag_counter"), py::arg("rank"), py::arg("eps"), py::arg("timeout_ns"), py::arg("status"), py::arg("rs_world") = 0);
     m.def("tp_argmax", &tp_argmax);
     m.def("step_increment", &step_increment);
     m.def("gemm_workspace_floats", &gemm_workspace_floats, py::arg("M"), py::arg("N"), py::arg("splits"), py::arg("gated"), py::arg("ntok") = 0);

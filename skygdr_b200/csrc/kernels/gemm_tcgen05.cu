@@ -41,12 +41,23 @@ __device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16
         const int t = t_base + j, n = n0 + ch * 8;
         if (t < p.M && n < p.N) {
             __nv_bfloat16* dst;
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + j * 128 + ch * 8);
+            if (p.rs.world > 0 && p.rs.all) {                       // one-shot all-reduce: the same row to every rank
+                const long long off = ((long long)p.rs.src_rank * p.rs.rows_per_rank + t) * p.N + n;
+                if (n + 8 <= p.N) {
+                    for (int d = 0; d < p.rs.world; ++d) st_v4(p.rs.dst[d] + off, v);
+                } else {
+                    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+                    for (int d = 0; d < p.rs.world; ++d)
+                        for (int q = 0; q < 8 && n + q < p.N; ++q) p.rs.dst[d][off + q] = e[q];
+                }
+                continue;
+            }
             if (p.rs.world == 0) dst = p.y + (long long)t * p.ldy + n;
             else {
                 const int d = t / p.rs.rows_per_rank, lr = t - d * p.rs.rows_per_rank;
                 dst = p.rs.dst[d] + ((long long)(p.rs.src_rank * p.rs.rows_per_rank + lr)) * p.N + n;
             }
-            const uint4 v = *reinterpret_cast<const uint4*>(stage + j * 128 + ch * 8);
             if (n + 8 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) st_v4(dst, v);
             else {
                 const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);

@@ -32,9 +32,13 @@ struct TpAgWait {
 
 // GEMM -> reduce-scatter: instead of y, token row t goes to rank t / rows_per_rank, into that rank's
 // receive buffer slot [src_rank][t % rows_per_rank][N] (bf16), followed by one arrival on its counter.
+// With `all` set the push is the first half of a one-shot all-reduce instead: every token row of the tile goes to EVERY rank,
+// into slot [src_rank][t][N] of its buffer (rows_per_rank then holds the full number of token rows), and the consumer sums
+// `world` partials per row. More bytes on the links, half as many hops per layer.
 struct TpRsPush {
     int world;                                    // 0: off
     int src_rank, rows_per_rank;
+    int all;
     __nv_bfloat16* dst[TP_MAX_RANKS];             // peers' receive buffers (peer-mapped)
     unsigned int* counters[TP_MAX_RANKS];         // peers' arrival counters (peer-mapped)
 };

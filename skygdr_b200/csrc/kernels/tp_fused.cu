@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(256) tp_norm_kernel(const TpNormParams p) {
     float tot = 0.f;
     for (int i = 0; i < 8; ++i) tot += red[i];
     const float inv = rsqrtf(tot / p.hidden + p.eps);
-    const long long grow = (long long)(p.rank * p.rows + row) * p.hidden;
+    const long long grow = (long long)(p.ag_row0 + row) * p.hidden;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const int v = threadIdx.x + k * 256;
@@ -94,18 +94,19 @@ __global__ void __launch_bounds__(256) tp_norm_kernel(const TpNormParams p) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = vals[k][i] * inv * g[i];
             const uint4 packed = pack8f(o);
-            for (int j = 0; j < p.world; ++j) st_v4(p.ag_dst[j] + grow + v * 8, packed);
+            for (int j = 0; j < p.ag_n; ++j) st_v4(p.ag_dst[j] + grow + v * 8, packed);
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && p.ag_counter[0] != nullptr) {            // a purely local destination needs no arrival
         __threadfence_system();
-        for (int j = 0; j < p.world; ++j) red_relaxed_sys_add_u32(p.ag_counter[j], 1u);
+        for (int j = 0; j < p.ag_n; ++j) red_relaxed_sys_add_u32(p.ag_counter[j], 1u);
     }
 }
 
 cudaError_t launch_tp_norm(const TpNormParams& p, cudaStream_t stream) {
     if (p.hidden % 8 || p.hidden > 8192 || p.rows <= 0 || p.world < 1 || p.world > TP_MAX_RANKS) return cudaErrorInvalidValue;
+    if (p.ag_n < 1 || p.ag_n > TP_MAX_RANKS) return cudaErrorInvalidValue;
     return launch_pdl(tp_norm_kernel, dim3(p.rows), dim3(256), 0, stream, p);
 }
 

@@ -17,6 +17,10 @@ struct TpNormParams {
     __nv_bfloat16* ag_dst[TP_MAX_RANKS];    // every rank's gather buffer [world*rows][hidden] (peer-mapped; own included)
     unsigned int* ag_counter[TP_MAX_RANKS]; // on rank j: its counter for source = this rank
     int world, rank, rows, hidden;
+    // One-shot all-reduce form: `rows` is the whole batch, rs_buf holds [world][rows][hidden] full-size partials, the residual is
+    // replicated, and the normed rows go to ag_n = 1 destination (a local buffer, ag_counter[0] == nullptr) at row ag_row0 = 0.
+    // The reduce-scatter / all-gather form has ag_n = world and ag_row0 = rank * rows.
+    int ag_n, ag_row0;
     float eps;
     unsigned long long timeout_ns;
     LaunchStatus* status;

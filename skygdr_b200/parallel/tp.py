@@ -22,7 +22,7 @@ from .. import ops
 from .._ext import load
 from ..models.qwen3 import Qwen3Config, Qwen3Decoder, Qwen3Weights
 from ..ops.flow import new_status, read_status
-from ..ops.gemm import FUSED_TP, GemmWorkspace, pick_config
+from ..ops.gemm import FUSED_TP, STANDALONE, GemmWorkspace, pick_config
 from ..ops.kv_cache import KVGeometry, PagedKVPool
 from .symm import SymmetricHeap
 
@@ -31,8 +31,13 @@ TIMEOUT_NS = 2_000_000_000
 
 class TPDecoder:
     def __init__(self, cfg: Qwen3Config, weights: Qwen3Weights, pool: PagedKVPool, batch: int, max_ctx: int, rank: int, world: int,
-                 attn_chunk: int = 1024, group=None, attn_impl: str = "tc"):
-        assert batch % world == 0 and pool.layout == "hnd"
+                 attn_chunk: int = 1024, group=None, attn_impl: str = "tc", collective: str = "rs_ag"):
+        """collective: "rs_ag" = GEMM -> reduce-scatter and all-gather -> GEMM with a token-sharded residual stream (4 hops per
+        layer); "oneshot" = every rank pushes its full partial tile to every peer and the norm kernel sums `world` partials, with
+        the residual stream and the normed activations replicated (2 hops per layer, world-1 times the bytes; built for
+        latency-bound decode sizes, not yet run on GPUs)."""
+        assert batch % world == 0 and pool.layout == "hnd" and collective in ("rs_ag", "oneshot")
+        self.collective = collective
         self._C = load()
         self.cfg, self.w, self.pool, self.rank, self.world = cfg, weights, pool, rank, world
         dev = pool.data.device
@@ -43,17 +48,21 @@ class TPDecoder:
         H, D, L = cfg.hidden, cfg.head_dim, cfg.layers
         self.qh, self.kh = cfg.q_heads // world, cfg.kv_heads // world
         B = batch
-        heap_bytes = 4 * B * H * 2 + world * B * 8 + 8192 + 4096
+        oneshot = collective == "oneshot"
+        heap_bytes = 4 * B * H * 2 + world * B * 8 + 8192 + 4096 + (2 * world * B * H * 2 + 4096 if oneshot else 0)
         self.heap = SymmetricHeap(heap_bytes, rank, world, dev, group)
         hp = self.heap
         for name in ("agA", "agB", "rs0", "rs1"):
             hp.alloc(name, B * H * 2)
+        if oneshot:
+            for name in ("ar0", "ar1"):                  # [world][B][H] partials of the O and the down projection
+                hp.alloc(name, world * B * H * 2)
         hp.alloc("am_slots", world * B * 8)
         hp.alloc("counters", 4096)
         # counter words: agA[world] | agB[world] | rs0 | rs1 | am[world]
         self.c_agA, self.c_agB, self.c_rs0, self.c_rs1, self.c_am = 0, 4 * world, 8 * world, 8 * world + 4, 8 * world + 8
         bf = dict(dtype=torch.bfloat16, device=dev)
-        self.resid = torch.zeros((self.rows, H), **bf)
+        self.resid = torch.zeros((B if oneshot else self.rows, H), **bf)      # replicated in the one-shot form
         self.xA = hp.local_tensor("agA", (B, H), torch.bfloat16)
         self.xB = hp.local_tensor("agB", (B, H), torch.bfloat16)
         self.qkv = torch.empty((B, (self.qh + 2 * self.kh) * D), **bf)
@@ -106,7 +115,7 @@ class TPDecoder:
     def _gemm(self, x, w, y, gated=False, ag=(), rs=()):
         M, K = x.shape
         N = w.shape[0] // 2 if gated else w.shape[0]
-        ntok, splits = pick_config(M, N, K, 148, gated, model=FUSED_TP)
+        ntok, splits = pick_config(M, N, K, 148, gated, model=FUSED_TP if (ag or rs) else STANDALONE)
         if splits > 1:
             self.ws.ensure(self._C.gemm_workspace_floats(M, N, splits, gated, ntok), self._C.gemm_counter_count(M, N, gated, ntok))
             self._C.gemm_tp(x, w, y, splits, gated, self.ws.ws, self.ws.counters, self.status, ag, rs, ntok)
@@ -125,8 +134,51 @@ class TPDecoder:
         self.ctx_lens[:b].copy_(positions + 1)
         self.block_table[:b, :block_table.shape[1]].copy_(block_table)
 
+    # ---- one-shot all-reduce form ----
+    def _ar(self, which: int) -> tuple:
+        """Push descriptor of a GEMM whose partial tile goes to every rank's `ar<which>` buffer, slot [this rank][row]."""
+        name = "ar0" if which == 0 else "ar1"
+        off = self.c_rs0 if which == 0 else self.c_rs1
+        return (self.world, self.rank, self.batch, self.heap.all_ptrs(name), self.heap.all_ptrs("counters", off), True)
+
+    def _norm_ar(self, ar_which: Optional[int], use: int, w: torch.Tensor, x_out: torch.Tensor) -> None:
+        """Sum of `world` partials + residual (replicated, updated in place) -> RMSNorm -> x_out, all local."""
+        L = self.cfg.layers
+        if ar_which is None:
+            buf, ctr, seq = 0, 0, ()
+        else:
+            name, off = ("ar0", self.c_rs0) if ar_which == 0 else ("ar1", self.c_rs1)
+            buf, ctr = self.heap.ptr(name, self.rank), self.heap.ptr("counters", self.rank, off)
+            k_in = (self.cfg.q_heads // self.world) * self.cfg.head_dim if ar_which == 0 else self.cfg.ffn // self.world
+            seq = (self.step_ctr.data_ptr(), L, use, self._rs_arrivals(k_in))
+        self._C.tp_norm(buf, ctr, seq, self.resid, w, [x_out.data_ptr()], [0], self.rank, self.cfg.eps, TIMEOUT_NS, self.status,
+                        rs_world=self.world)
+
+    def _step_oneshot(self, b: int, max_ctx: int) -> None:
+        cfg, w, L = self.cfg, self.w, self.cfg.layers
+        ops.embedding(self.ids, w.embed, out=self.resid)                      # every rank embeds the whole batch
+        for li, lw in enumerate(w.layers):
+            self._norm_ar(None if li == 0 else 1, li - 1, lw.ln1, self.xA)
+            self._gemm(self.xA, lw.qkv, self.qkv)
+            ops.rope_append(self.qkv, lw.q_norm, lw.k_norm, self.pool, li, self.inv_freq, self.block_table, self.positions, self.qh,
+                            cfg.eps, q_out=self.q)
+            self.attn(self.q, self.pool, li, self.block_table, self.ctx_lens, max_ctx=max_ctx, out=self.attn_out)
+            self._gemm(self.attn_out.view(b, -1), lw.o, self.dummy, rs=self._ar(0))
+            self._norm_ar(0, li, lw.ln2, self.xB)
+            self._gemm(self.xB, lw.gate_up, self.act, gated=True)
+            self._gemm(self.act, lw.down, self.dummy, rs=self._ar(1))
+        self._norm_ar(1, L - 1, w.final_norm, self.xA)
+        self._gemm(self.xA, w.lm_head, self.logits)
+        self._C.tp_argmax(self.logits, w.vocab_lo, self.rank, self.heap.all_ptrs("am_slots"),
+                          self.heap.all_ptrs("counters", self.c_am + 4 * self.rank), self.heap.ptr("am_slots", self.rank),
+                          self.heap.ptr("counters", self.rank, self.c_am), (self.step_ctr.data_ptr(), 1, 0, b), self.next_ids,
+                          TIMEOUT_NS, self.status)
+        self._C.step_increment(self.step_ctr)
+
     def _step(self, b: int, max_ctx: int) -> None:
         assert b == self.batch, "a tensor-parallel step always runs the full batch"
+        if self.collective == "oneshot":
+            return self._step_oneshot(b, max_ctx)
         cfg, w, L = self.cfg, self.w, self.cfg.layers
         r0 = self.rank * self.rows
         ops.embedding(self.ids[r0:r0 + self.rows], w.embed, out=self.resid)
@@ -213,7 +265,8 @@ def _bytes_per_step(cfg: Qwen3Config, w: Qwen3Weights, ctx: torch.Tensor, kv_hea
 
 
 def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world: int, ctx: torch.Tensor, extra_tokens: int,
-                        seed: int = 0, kv_init: str = "normal", attn_chunk: int = 1024, attn_impl: str = "tc"):
+                        seed: int = 0, kv_init: str = "normal", attn_chunk: int = 1024, attn_impl: str = "tc",
+                        collective: str = "rs_ag"):
     """Weights shard, KV pool sized for ``ctx`` (+ ``extra_tokens`` of growth per sequence), randomly permuted block
     table, and the decode engine for this rank. Every rank passes the same ``ctx`` and ``seed``."""
     batch = ctx.numel()
@@ -239,5 +292,5 @@ def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world
     if world == 1:
         eng = Qwen3Decoder(cfg, weights, pool, batch, max_ctx, attn_chunk, attn_impl)
     else:
-        eng = TPDecoder(cfg, weights, pool, batch, max_ctx, rank, world, attn_chunk, attn_impl=attn_impl)
+        eng = TPDecoder(cfg, weights, pool, batch, max_ctx, rank, world, attn_chunk, attn_impl=attn_impl, collective=collective)
     return eng, table

@@ -57,7 +57,8 @@ def main():
         o += nb
     ids = torch.randint(0, cfg.vocab, (B,), generator=g).int()
     full = Qwen3Decoder(cfg, full_w, full_pool, B, max_ctx, attn_chunk=64, attn_impl="simt")
-    tp = TPDecoder(cfg, shard_w, tp_pool, B, max_ctx, rank, world, attn_chunk=128)
+    collective = os.environ.get("SKYGDR_TP_COLLECTIVE", "rs_ag")          # "oneshot": the one-shot all-reduce form
+    tp = TPDecoder(cfg, shard_w, tp_pool, B, max_ctx, rank, world, attn_chunk=128, collective=collective)
     full.set_batch(ids.to(dev), ctx.int().to(dev), table.to(dev))
     tp.set_batch(ids.to(dev), ctx.int().to(dev), table.to(dev))
     worst = 0.0

@@ -17,8 +17,8 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(world, script, timeout=240):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def _run(world, script, timeout=240, **extra_env):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), os.path.join(HERE, "multi", script)]
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
@@ -27,6 +27,14 @@ def _run(world, script, timeout=240):
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_tensor_parallel_decode_and_peer_kv_transfer_2gpu():
     r = _run(2, "tp_worker.py")
+    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.skipif(os.environ.get("SKYGDR_TEST_ONESHOT") != "1", reason="the one-shot all-reduce form is opt-in until it has been run on GPUs once")
+def test_tensor_parallel_decode_oneshot_allreduce_2gpu():
+    """The same step-by-step comparison against the single-GPU decoder, with the one-shot all-reduce collective."""
+    r = _run(2, "tp_worker.py", SKYGDR_TP_COLLECTIVE="oneshot")
     assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
