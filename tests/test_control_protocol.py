@@ -201,3 +201,64 @@ def test_heartbeat_rule_of_host_data_paths(ctl):
             assert got == g2 and w.allowance(d, 1, 27 * win) == g2 + 10 * 2_000_000
         d.step_window(30 * win)                                           # the daemon is back: grants rule again
         assert w.allowance(d, 1, 31 * win) == d.page_fields(1)["granted_bytes"] and w.t_dead_ns == 0
+
+
+def test_protocol_survives_arbitrary_lines(ctl):
+    """Property test: whatever line arrives (control characters, huge numbers, half commands, many tokens), the daemon core
+    answers with exactly one line that starts with OK or ERR, stays consistent (flow count bounded by the registrations it
+    accepted, grants never decrease) and keeps answering afterwards. The reference's end point gets its robustness from reading
+    at most 255 bytes and knowing eight words (src/cpu_client.cc:176-236,299-300); this one has a grammar, so it is fuzzed."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    words = st.sampled_from(["REGISTER", "RENEW", "UNREGISTER", "BUDGET", "FLOWS", "FLOW", "POLICY", "WINDOW", "CAPACITY", "PING", "STATUS", "HIGH",
+                             "LOW", "LOW1", "LOW2", "LOW3", "LOW4", "SLEEP", "STOP", "kv_transfer", "kv_offload", "high", "low", "besteffort",
+                             "nan", "inf", "-1", "0", "1", "2", "40", "1e308", "99999999999999999999", "target_track", "ladder", "static", "none", "x"])
+    junk = st.text(alphabet=st.characters(blacklist_categories=("Cs",), blacklist_characters="\n"), max_size=40)
+    line = st.one_of(st.lists(st.one_of(words, junk), max_size=8).map(" ".join), junk)
+
+    d = _core(ctl, window_ns=1_000_000)
+    state = {"now": 0, "granted": {}}
+
+    @settings(max_examples=400, deadline=None)
+    @given(line)
+    def check(text):
+        state["now"] += 1_000_000
+        reply = d.handle_line(text, state["now"])
+        assert reply.endswith("\n") and reply.count("\n") == 1 and (reply.startswith("OK") or reply.startswith("ERR")), (text, reply)
+        d.step_window(state["now"])
+        assert 0 <= d.n_flows <= 4096
+        flows = d.handle_line("FLOWS", state["now"])
+        assert flows.startswith("OK n=")
+        for tok in flows.split()[2:]:
+            fid = int(tok.split(":")[0])
+            g = d.page_fields(fid)["granted_bytes"]
+            assert g >= state["granted"].get(fid, 0), (text, fid)
+            state["granted"][fid] = g
+        assert d.handle_line("PING", state["now"]).startswith("OK")
+
+    check()
+
+
+def test_window_step_cost_leaves_room_in_a_one_millisecond_window(ctl):
+    """256 registered flows, all with traffic: one policy + grant pass must take a small part of the shortest window (1 ms).
+    The reference's loop polls every 100 ms from Python (src/tools/pcie_case_study_controller.py:148)."""
+    import time
+
+    d = _core(ctl, window_ns=1_000_000, policy="target_track")
+    for i in range(256):
+        prio, target = ("high", 1.0) if i % 8 == 0 else ("besteffort", 0.0)
+        assert d.handle_line(f"REGISTER f{i} {prio} {target} kind{i % 4}", 0).startswith("OK")
+    now = 0
+    for w in range(50):                                              # settle
+        now += 1_000_000
+        for i in range(1, 257):
+            d.report_usage(i, w * 100_000, w * 100_000, 1 << 20)
+        d.step_window(now)
+    t0 = time.perf_counter()
+    n = 400
+    for w in range(n):
+        now += 1_000_000
+        d.step_window(now)
+    per_window_us = (time.perf_counter() - t0) / n * 1e6
+    assert per_window_us < 250.0, per_window_us                     # a quarter of the shortest window, with 256 flows
