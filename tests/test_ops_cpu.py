@@ -97,3 +97,30 @@ def test_attention_oracle_matches_dense_softmax():
     v = torch.cat([pool.data[4, 0, 1, 1], pool.data[1, 0, 1, 1]])[:20]
     p = torch.softmax(q[b, h] @ k.t() / math.sqrt(128), -1)
     assert torch.allclose(out[b, h], p @ v, atol=1e-5)
+
+
+@pytest.mark.parametrize("layout", ["hnd", "nhd"])
+def test_prefill_oracle_matches_torch_sdpa(layout):
+    """The oracle of the prefill attention kernel (gather pages, causal softmax in fp32) against torch's own attention."""
+    from skygdr_b200.ops.attention import prefill_attn_reference
+    from skygdr_b200.ops.kv_cache import KVGeometry, PagedKVPool
+
+    torch.manual_seed(2)
+    g = KVGeometry(layers=2, kv_heads=2)
+    lens = [5, 33, 16]
+    pool = PagedKVPool(g, 12, layout, device="cpu", dtype=torch.float32)
+    pool.data.normal_()
+    table = torch.tensor([[3, 0, 0], [7, 1, 9], [4, 0, 0]], dtype=torch.int32)
+    q = torch.randn(sum(lens), 4, 128)
+    out = prefill_attn_reference(q, pool, 1, table, lens)
+    o = 0
+    for s, n in enumerate(lens):
+        nb = (n + 15) // 16
+        kv = pool.data[table[s, :nb].long(), 1]
+        if layout == "nhd":
+            kv = kv.permute(0, 1, 3, 2, 4)
+        k = kv[:, 0].permute(1, 0, 2, 3).reshape(2, nb * 16, 128)[:, :n]
+        v = kv[:, 1].permute(1, 0, 2, 3).reshape(2, nb * 16, 128)[:, :n]
+        want = torch.nn.functional.scaled_dot_product_attention(q[o:o + n].transpose(0, 1)[None], k[None], v[None], is_causal=True, enable_gqa=True)
+        assert torch.allclose(out[o:o + n], want[0].transpose(0, 1), atol=1e-5)
+        o += n
