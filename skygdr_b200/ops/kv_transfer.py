@@ -77,6 +77,53 @@ class MulticastPools:
         self.close()
 
 
+class FanoutTarget:
+    """Destination pools of a 1 -> k fan-out, through the NVLink multicast address where the machine has one and as a loop of
+    unicast peer stores where it has not (no NVSwitch, an old driver, a GPU outside the fabric): the caller sends the same way
+    either way. ``mode`` says which was set up ("multimem" or "unicast"), ``why`` why multicast was not used."""
+
+    def __init__(self, geom: KVGeometry, n_blocks: int, src_gpu: int, dst_gpus: Sequence[int], prefer_multicast: bool = True):
+        self.geom, self.src_gpu, self.dst_gpus = geom, int(src_gpu), [int(d) for d in dst_gpus]
+        self.why = ""
+        self._mc: Optional[MulticastPools] = None
+        if prefer_multicast and len(self.dst_gpus) >= 1:
+            try:
+                self._mc = MulticastPools(geom, n_blocks, [self.src_gpu] + self.dst_gpus)
+            except Exception as exc:                 # capability probe or creation failed on the host: nothing ran on a GPU
+                self.why = str(exc)
+        if self._mc is not None:
+            self.mode = "multimem"
+            self.pools = self._mc.pools[1:]          # the source's own copy is not a destination
+        else:
+            self.mode = "unicast"
+            C = load()
+            for d in self.dst_gpus:
+                if d != self.src_gpu and not (C.enable_peer_access(self.src_gpu, d) and C.enable_peer_access(d, self.src_gpu)):
+                    raise RuntimeError(f"no peer access between GPU {self.src_gpu} and GPU {d}")
+            self.pools = [PagedKVPool(geom, n_blocks, "hnd", device=torch.device("cuda", d)) for d in self.dst_gpus]
+        self._remotes = [RemotePool.of(p) for p in self.pools]
+
+    def send(self, flow: "KvTransferFlow", src: PagedKVPool, src_blocks: torch.Tensor, dst_blocks: torch.Tensor, **kw) -> None:
+        """Enqueues the fan-out of ``src_blocks`` into the same ``dst_blocks`` of every destination pool."""
+        if self._mc is not None:
+            placeholders = [RemotePool(0, self.pools[0].strides, self.geom.kv_heads) for _ in self.pools]
+            flow.transfer(src, placeholders, src_blocks, dst_blocks, replicate=True, multicast_ptr=self._mc.multicast_ptr, **kw)
+        else:
+            flow.transfer(src, self._remotes, src_blocks, dst_blocks, replicate=True, **kw)
+
+    def close(self) -> None:
+        self.pools, self._remotes = [], []
+        if self._mc is not None:
+            self._mc.close()
+            self._mc = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
 class KvTransferFlow:
     def __init__(self, device, page: Optional[CreditPage] = None, ctas: Optional[int] = None, pages_per_chunk: int = 8,
                  max_wait_ms: float = 2.0, method: str = "auto"):

@@ -73,3 +73,28 @@ def test_multicast_fanout_lands_in_every_destination():
             assert torch.equal(pool.data[dp[:32].long().to(dev)], want.to(dev))
             untouched = dp[32:].long().to(dev)
             assert bool((pool.data[untouched] == -1.0).all())
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 3, reason="needs 3 GPUs (source + 2 destinations)")
+@pytest.mark.parametrize("prefer_multicast", [True, False])
+def test_fanout_target_sends_the_same_way_with_and_without_multicast(prefer_multicast):
+    """FanoutTarget picks the NVLink multicast address where it exists and unicast peer stores otherwise; the destinations
+    end up with the same pages either way."""
+    from skygdr_b200 import ops
+
+    geom = ops.KVGeometry(layers=2, kv_heads=8)
+    src = ops.PagedKVPool(geom, 24, "nhd", device="cuda:0")
+    src.data.normal_()
+    sb = torch.arange(16, device="cuda:0").int()
+    db = (torch.arange(16, device="cuda:0") + 4).int()
+    with ops.FanoutTarget(geom, 24, 0, [1, 2], prefer_multicast=prefer_multicast) as tgt:
+        assert tgt.mode in ("multimem", "unicast") and (prefer_multicast or tgt.mode == "unicast")
+        flow = ops.KvTransferFlow("cuda:0", method="simt")
+        with torch.cuda.device(0):
+            tgt.send(flow, src, sb, db)
+            st = flow.result()
+        assert st["status"] == 0
+        want = ops.reference_transfer(src, sb)
+        for pool in tgt.pools:
+            dev = pool.data.device
+            assert torch.equal(pool.data[db.long().to(dev)], want.to(dev))
