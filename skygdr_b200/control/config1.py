@@ -92,7 +92,93 @@ def controller_csv(res) -> str:
     return "\n".join(lines) + "\n"
 
 
+def run_live(cfg: Config1 | None = None, policy: str = "target_track", time_scale: float = 1.0) -> Dict[str, float]:
+    """The same experiment against the real daemon process, in real time.
+
+    ``fabricd`` runs as its own process with its own window timer; this process registers the two flows over TCP the way
+    a client does (REGISTER, lease renewals), maps their credit pages, and plays the data paths and the shared link: every
+    ~0.25 ms of wall time it shares the elapsed link capacity max-min between the flows, never moving a flow beyond its grant,
+    and publishes consumed / completed / backlog bytes in the pages, which is all the daemon ever sees. Nothing here calls
+    into the daemon's code: what is measured is the deployed control loop (socket, timer thread, shared pages, policy).
+    ``time_scale`` < 1 shortens the run (duration and request sizes shrink together) for tests."""
+    import time
+
+    from . import FabricClient, FabricDaemon, ctl
+
+    cfg = cfg or Config1()
+    dur = cfg.duration_s * time_scale
+    arrivals = [(t * time_scale, int(b * time_scale)) for t, b in ctl.poisson_uniform(cfg.seed, cfg.rate_per_s / time_scale, cfg.duration_s * time_scale,
+                                                                                 cfg.size_lo_mb * 1e6 / time_scale, cfg.size_hi_mb * 1e6 / time_scale)] \
+        if time_scale != 1.0 else list(ctl.poisson_uniform(cfg.seed, cfg.rate_per_s, cfg.duration_s, cfg.size_lo_mb * 1e6, cfg.size_hi_mb * 1e6))
+    cap = cfg.capacity_gbps * 1e9
+    with FabricDaemon(policy=policy, window_us=int(cfg.window_ms * 1000), capacity_gbps=cfg.capacity_gbps, lease_ms=2000) as d, \
+            FabricClient(port=d.port) as c:
+        kv = c.register("kv_transfer", "high", cfg.target_gbps)
+        off = c.register("kv_offload", "besteffort", 0.0)
+        flows = [kv, off]
+        consumed = [0, 0]
+        queue: List[List[float]] = []            # [remaining bytes, arrival time]
+        done_ms: List[float] = []
+        next_arrival = 0
+        t0 = time.perf_counter()
+        t_prev, t_renew = 0.0, 0.0
+        while True:
+            time.sleep(cfg.tick_ms * 1e-3)
+            now = time.perf_counter() - t0
+            dt, t_prev = now - t_prev, now
+            while next_arrival < len(arrivals) and arrivals[next_arrival][0] <= now:
+                queue.append([float(arrivals[next_arrival][1]), arrivals[next_arrival][0]])
+                next_arrival += 1
+            if now > dur and not queue:
+                break
+            if now > dur + 5.0:
+                break                                # a stuck run ends with unfinished requests instead of hanging
+            # what each flow may move in this tick: its demand, capped by its grant
+            grants = [f.grant() for f in flows]
+            demand = [sum(q[0] for q in queue), float("inf") if now <= dur else 0.0]
+            room = [float("inf") if g["unlimited"] else max(0.0, g["granted_bytes"] - consumed[i]) for i, g in enumerate(grants)]
+            want = [min(demand[i], room[i]) for i in range(2)]
+            budget = cap * dt
+            fair = budget / 2
+            move = [min(want[0], fair), min(want[1], fair)]
+            spare = budget - move[0] - move[1]
+            for i in range(2):                       # max-min: what one flow leaves goes to the other
+                extra = min(spare, want[i] - move[i])
+                move[i] += extra
+                spare -= extra
+            left = move[0]
+            while queue and left > 0:                # kv_transfer serves its requests in arrival order
+                take = min(left, queue[0][0])
+                queue[0][0] -= take
+                left -= take
+                if queue[0][0] <= 0:
+                    done_ms.append((now - queue[0][1]) * 1e3)
+                    queue.pop(0)
+            consumed[0] += int(move[0])
+            consumed[1] += int(move[1])
+            kv.report(consumed[0], consumed[0], int(sum(q[0] for q in queue)))
+            off.report(consumed[1], consumed[1], 1 << 40 if now <= dur else 0)
+            if now - t_renew > 0.5:
+                c.renew(kv)
+                c.renew(off)
+                t_renew = now
+        elapsed = time.perf_counter() - t0
+        c.unregister(kv)
+        c.unregister(off)
+    return {
+        "policy": policy, "requests": len(arrivals), "unfinished": len(queue),
+        "flow_time_p50_ms": ctl.percentile(done_ms, 0.5) if done_ms else float("nan"),
+        "flow_time_p99_ms": ctl.percentile(done_ms, 0.99) if done_ms else float("nan"),
+        "flow_time_mean_ms": sum(done_ms) / len(done_ms) if done_ms else float("nan"),
+        "kv_transfer_gb": consumed[0] / 1e9, "offload_goodput_gbps": consumed[1] / 1e9 / min(elapsed, dur), "wall_s": elapsed,
+    }
+
+
 if __name__ == "__main__":
     import json
+    import sys
 
-    print(json.dumps(run_config1(), indent=1))
+    if "--live" in sys.argv:
+        print(json.dumps({p: run_live(policy=p) for p in ("none", "target_track")}, indent=1))
+    else:
+        print(json.dumps(run_config1(), indent=1))

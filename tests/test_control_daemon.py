@@ -151,3 +151,18 @@ def test_signals_with_fake_nvml(ctl):
     assert not failing.sample_pcie().valid          # an NVML error gives an invalid sample, not an exception
     assert ctl.hbm_peak_gbs("NVIDIA H200") == 4800 and ctl.hbm_peak_gbs("unknown") == 0
     assert ctl.pcie_lane_gbs(4) == pytest.approx(1.969)
+
+
+def test_live_control_loop_against_the_daemon_process():
+    """Config 1 in real time against the deployed pieces: fabricd as a process with its own window timer, two flows registered
+    over TCP, grants read from the shared pages, a link model in this process. With target_track the kv_transfer requests
+    finish sooner than without scheduling and the offload keeps most of its goodput. Kept short and lenient: it runs in real
+    time on whatever the test machine is doing."""
+    from skygdr_b200.control.config1 import Config1, run_live
+
+    cfg = Config1(duration_s=2.5)
+    none = run_live(cfg, policy="none")
+    tt = run_live(cfg, policy="target_track")
+    assert none["unfinished"] == 0 and tt["unfinished"] == 0 and none["requests"] == tt["requests"] > 20
+    assert tt["flow_time_mean_ms"] < none["flow_time_mean_ms"], (tt, none)
+    assert tt["offload_goodput_gbps"] > 0.85 * none["offload_goodput_gbps"], (tt, none)
