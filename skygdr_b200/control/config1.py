@@ -174,11 +174,59 @@ def run_live(cfg: Config1 | None = None, policy: str = "target_track", time_scal
     }
 
 
+def run_processes(cfg: Config1 | None = None, policy: str = "target_track", msg: str = "8M") -> Dict[str, float]:
+    """The experiment with the compatibility programs as the flows: `fabricd`, one `gpu_server link:<GB/s>` (a link that its
+    clients share, first come first served) and two `cpu_client` processes that register themselves with the daemon
+    (SKYGDR_DAEMON): kv_transfer as a Poisson request stream (SKYGDR_REQUESTS), kv_offload backlogged and stopped over its
+    control port when the requests are through. Both keep two reads in flight so that the link never idles on a round trip.
+    Flow times and rates are scraped from the clients' own summary lines."""
+    import os
+    import re
+    import subprocess
+    import time
+
+    from . import FabricDaemon, send_control, wait_for_control
+    from .. import build
+    from .daemon import free_port
+
+    cfg = cfg or Config1()
+    bin_dir = str(build.build_bin())
+    link_port, ctrl_port = free_port(), free_port()
+    with FabricDaemon(policy=policy, window_us=int(cfg.window_ms * 1000), capacity_gbps=cfg.capacity_gbps, lease_ms=3000) as d:
+        server = subprocess.Popen([f"{bin_dir}/gpu_server", f"link:{cfg.capacity_gbps}", "1G", str(link_port), "1", "0"], stdout=subprocess.PIPE, text=True)
+        try:
+            server.stdout.readline()                                            # "[server] ... listening"
+            env = dict(os.environ, SKYGDR_DAEMON=f"127.0.0.1:{d.port}", SKYGDR_READ_MIN_QD="2")
+            tail = ["read", "1", "0", "2"]                                      # op port gid_idx qd
+            off_iters = int(cfg.capacity_gbps * 1e9 * (cfg.duration_s + 30) / (8 << 20))
+            off = subprocess.Popen([f"{bin_dir}/cpu_client", "127.0.0.1", str(link_port), "link", str(off_iters), msg, *tail], stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                                   text=True, env=dict(env, SKYGDR_FLOW_NAME="kv_offload", SKYGDR_FLOW_PRIORITY="besteffort", SKYGDR_CTRL_PORT=str(ctrl_port)))
+            wait_for_control("127.0.0.1", ctrl_port, 10.0)
+            time.sleep(0.2)                                                     # the offload is up to speed before the requests start
+            req = f"{cfg.rate_per_s}:{cfg.size_lo_mb * 1e6}:{cfg.size_hi_mb * 1e6}:{cfg.seed}:{cfg.duration_s}"
+            kv = subprocess.run([f"{bin_dir}/cpu_client", "127.0.0.1", str(link_port), "link", "1", msg, *tail], capture_output=True, text=True, timeout=cfg.duration_s + 60,
+                                env=dict(env, SKYGDR_FLOW_NAME="kv_transfer", SKYGDR_FLOW_PRIORITY="high", SKYGDR_FLOW_TARGET_GBPS=str(cfg.target_gbps), SKYGDR_REQUESTS=req))
+            send_control("127.0.0.1", ctrl_port, "STOP")
+            off_out, _ = off.communicate(timeout=30)
+        finally:
+            server.terminate()
+            server.wait(timeout=5)
+    m = re.search(r"requests=(\d+) finished=(\d+) unfinished=(\d+) flow_time_ms p50=([0-9.]+) p99=([0-9.]+) mean=([0-9.]+)", kv.stdout)
+    if not m:
+        raise RuntimeError("kv_transfer client gave no request summary:\n" + kv.stdout + kv.stderr)
+    thr = re.search(r"throughput=([0-9.]+) GiB/s", off_out)
+    return {"policy": policy, "requests": int(m.group(1)), "unfinished": int(m.group(3)), "flow_time_p50_ms": float(m.group(4)),
+            "flow_time_p99_ms": float(m.group(5)), "flow_time_mean_ms": float(m.group(6)),
+            "offload_goodput_gbps": float(thr.group(1)) * 1.073741824 if thr else float("nan")}
+
+
 if __name__ == "__main__":
     import json
     import sys
 
-    if "--live" in sys.argv:
+    if "--processes" in sys.argv:
+        print(json.dumps({p: run_processes(policy=p) for p in ("none", "target_track")}, indent=1))
+    elif "--live" in sys.argv:
         print(json.dumps({p: run_live(policy=p) for p in ("none", "target_track")}, indent=1))
     else:
         print(json.dumps(run_config1(), indent=1))

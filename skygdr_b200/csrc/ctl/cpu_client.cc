@@ -99,9 +99,12 @@ int main(int argc, char** argv) {
     if (write_ack && qps > 1) qps = 1;                   // the ack path is single-connection
     if (is_read && qd < read_min_qd) qd = read_min_qd;
 
-    const bool sim = fabric.rfind("sim", 0) == 0;
+    // `sim[:GB/s]`: this process models the link itself (one client, no payload); `link`: the server models a link that all its
+    // clients share (gpu_server link:<GB/s>), so this side only exchanges headers and tags; `tcp`: payload over the socket.
+    const bool link = fabric.rfind("link", 0) == 0;
+    const bool sim = link || fabric.rfind("sim", 0) == 0;
     double sim_gbps = 64.0;
-    if (sim && fabric.size() > 4) sim_gbps = atof(fabric.c_str() + 4);
+    if (sim && !link && fabric.size() > 4) sim_gbps = atof(fabric.c_str() + 4);
     if (sim_gbps <= 0) sim_gbps = 64.0;
 
     // ---- control state ----
@@ -223,15 +226,16 @@ int main(int argc, char** argv) {
     // stays at the link rate; over TCP the requests are pipelined on the connection.
     int rc = 0;
     SkyHeartbeatWatch heartbeat = {0, 0, 0};
-    struct InFlight { uint64_t t_post, t_link_done; uint32_t tag; };
+    struct InFlight { uint64_t t_post, t_link_done, len; uint32_t tag; };
     std::deque<InFlight> in_flight;
     const size_t depth = write_ack ? 1 : (size_t)std::max(1, qd) * (size_t)qps;
-    uint64_t link_free = mono_ns();
-    auto account = [&](uint64_t t_post, uint64_t t_done) {
+    uint64_t link_free = mono_ns(), bytes_done = 0;
+    auto account = [&](const InFlight& f, uint64_t t_done) {
         ++completed;
-        if (page) { page->completed_bytes += msg; page->last_ts_ns = t_done; }
+        bytes_done += f.len;
+        if (page) { page->completed_bytes += f.len; page->last_ts_ns = t_done; }
         if ((seen++ % sample) == 0) {
-            double us = (t_done - t_post) * 1e-3;
+            double us = (t_done - f.t_post) * 1e-3;
             if (max_samples == 0 || lat_us.size() < max_samples) lat_us.push_back(us);
             lat_win.push_back(us);
         }
@@ -240,44 +244,45 @@ int main(int argc, char** argv) {
         InFlight f = in_flight.front();
         in_flight.pop_front();
         if (s >= 0) {
-            if (is_read && !sim) { if (!recv_all(s, buf.data(), msg)) { rc = 4; return false; } }
+            if (is_read && !sim) { if (!recv_all(s, buf.data(), f.len)) { rc = 4; return false; } }
             else if (is_read || write_ack) {
                 uint32_t tag = 0;
                 if (!recv_all(s, &tag, 4)) { rc = 4; return false; }
                 if (write_ack && tag != f.tag) { fprintf(stderr, "[client] unexpected ACK tag %u (want %u)\n", tag, f.tag); rc = 4; return false; }
             }
         }
-        if (sim) while (mono_ns() < f.t_link_done) { /* the link is still busy with this message */ }
-        account(f.t_post, mono_ns());
+        if (sim && !link) while (mono_ns() < f.t_link_done) { /* the link is still busy with this message */ }
+        account(f, mono_ns());
         return true;
     };
-    for (uint64_t i = 0; i < iters && !ctl.stop_requested() && rc == 0; ++i) {
+    // One message of `len` bytes: credit gate, queue depth, post, (ACK), legacy pacing, window flush, lease renewal.
+    auto issue = [&](uint64_t i, uint64_t len) -> bool {
         uint64_t off;
-        if (pattern == "seq") { off = seq_off; seq_off += msg; if (seq_off + msg > span) seq_off = 0; }
-        else off = span > msg ? (uint64_t)(rng.uniform() * double(span - msg)) : 0;
+        if (pattern == "seq") { off = seq_off; seq_off += len; if (seq_off + len > span) seq_off = 0; }
+        else off = span > len ? (uint64_t)(rng.uniform() * double(span - len)) : 0;
         off &= ~(align - 1);
         if (page) {                                      // byte grant of the flow, if it has one
-            while (consumed + msg > sky_host_allowance(page, &heartbeat, mono_ns()) && !page->stop && !ctl.stop_requested())
+            while (consumed + len > sky_host_allowance(page, &heartbeat, mono_ns()) && !page->stop && !ctl.stop_requested())
                 std::this_thread::sleep_for(std::chrono::microseconds(50));
-            if (page->stop) break;
-            consumed += msg;
+            if (page->stop) return false;
+            consumed += len;
             page->consumed_bytes = consumed;
         }
         while (in_flight.size() >= depth && rc == 0) complete_oldest();
-        if (rc) break;
-        InFlight f{mono_ns(), 0, (uint32_t)i};
-        if (sim) {
-            const uint64_t service_ns = (uint64_t)(double(msg) / (sim_gbps * 1e9) * 1e9);
+        if (rc) return false;
+        InFlight f{mono_ns(), 0, len, (uint32_t)i};
+        if (sim && !link) {
+            const uint64_t service_ns = (uint64_t)(double(len) / (sim_gbps * 1e9) * 1e9);
             f.t_link_done = std::max(f.t_post, link_free) + service_ns;
             link_free = f.t_link_done;
         }
         if (s >= 0) {
-            MsgHeader h{off, (uint32_t)msg, (uint32_t)i, is_read ? 1u : 0u, 0};
-            if (!send_all(s, &h, sizeof h)) { rc = 3; break; }
-            if (!sim && !is_read && !send_all(s, buf.data(), msg)) { rc = 3; break; }     // the payload of a write travels with it
+            MsgHeader h{off, (uint32_t)len, (uint32_t)i, is_read ? 1u : 0u, 0};
+            if (!send_all(s, &h, sizeof h)) { rc = 3; return false; }
+            if (!sim && !is_read && !send_all(s, buf.data(), len)) { rc = 3; return false; }   // the payload of a write travels with it
         }
         in_flight.push_back(f);
-        if (write_ack && !complete_oldest()) break;      // acknowledged writes: wait for this one before the next
+        if (write_ack && !complete_oldest()) return false;   // acknowledged writes: wait for this one before the next
         uint32_t pace = ctl.sleep_us();                  // legacy pacing: sleep after each post
         if (pace) std::this_thread::sleep_for(std::chrono::microseconds(pace));
         flush_window(false);
@@ -288,6 +293,61 @@ int main(int argc, char** argv) {
             if (send_all(dsock, line, (size_t)n)) { ssize_t k = recv(dsock, rep, sizeof rep, 0); (void)k; }
             renew_at = now;
         }
+        return true;
+    };
+
+    // SKYGDR_REQUESTS=rate_per_s:lo_bytes:hi_bytes:seed:duration_s turns the flow into a request stream: Poisson arrivals of
+    // requests with uniform sizes, each sent as messages of at most msg_bytes in arrival order; the flow time of a request
+    // runs from its arrival to its last completion. Without it the flow is backlogged for `iters` messages, as in the reference.
+    std::vector<double> flow_ms;
+    size_t n_requests = 0, unfinished = 0;
+    const char* req_env = getenv("SKYGDR_REQUESTS");
+    if (req_env && *req_env) {
+        double rate = 20, lo = 50e6, hi = 500e6, dur = 10;
+        unsigned long long seed = 0;
+        if (sscanf(req_env, "%lf:%lf:%lf:%llu:%lf", &rate, &lo, &hi, &seed, &dur) < 5 || rate <= 0 || hi < lo || dur <= 0) {
+            fprintf(stderr, "[client] SKYGDR_REQUESTS wants rate:lo_bytes:hi_bytes:seed:duration_s\n");
+            return finish(2);
+        }
+        const std::vector<Arrival> arr = poisson_uniform(seed, rate, dur, lo, hi);
+        n_requests = arr.size();
+        struct Req { uint64_t remaining, t_arrival; };
+        std::deque<Req> q;
+        size_t next = 0;
+        uint64_t i = 0, backlog = 0;
+        const uint64_t t_base = mono_ns();
+        while (!ctl.stop_requested() && rc == 0) {
+            const uint64_t now = mono_ns();
+            while (next < arr.size() && t_base + (uint64_t)(arr[next].t_s * 1e9) <= now) {
+                q.push_back({arr[next].bytes, t_base + (uint64_t)(arr[next].t_s * 1e9)});
+                backlog += arr[next].bytes;
+                ++next;
+            }
+            if (page) page->backlog_bytes = backlog;
+            if (q.empty()) {
+                if (next >= arr.size()) break;
+                const uint64_t wait_ns = t_base + (uint64_t)(arr[next].t_s * 1e9) - now;
+                std::this_thread::sleep_for(std::chrono::nanoseconds(std::min<uint64_t>(wait_ns, 200000)));
+                continue;
+            }
+            const uint64_t len = std::min<uint64_t>(msg, q.front().remaining);
+            if (!issue(i++, len)) break;
+            while (!in_flight.empty() && rc == 0 && q.front().remaining <= len) complete_oldest();   // the request ends with this message
+            q.front().remaining -= len;
+            backlog -= len;
+            if (q.front().remaining == 0) {
+                flow_ms.push_back((mono_ns() - q.front().t_arrival) * 1e-6);
+                q.pop_front();
+            }
+        }
+        unfinished = q.size() + (arr.size() - next);
+        if (page) page->backlog_bytes = 0;
+    } else {
+        for (uint64_t i = 0; i < iters && !ctl.stop_requested() && rc == 0; ++i) {
+            if (page) page->backlog_bytes = (iters - i) * msg;
+            if (!issue(i, msg)) break;
+        }
+        if (page) page->backlog_bytes = 0;
     }
     while (!in_flight.empty() && rc == 0) complete_oldest();       // drain what is still in flight
     double sec = (mono_ns() - t_start) * 1e-9;
@@ -296,7 +356,14 @@ int main(int argc, char** argv) {
     printf("[client] done: iters=%llu msg=%llu qd=%d qps=%d span=%llu pattern=%s\n", (unsigned long long)iters, (unsigned long long)msg, qd,
            qps, (unsigned long long)span, pattern.c_str());
     printf("[client] elapsed=%.3f s  ops=%.0f ops/s  throughput=%.2f GiB/s\n", sec, sec > 0 ? completed / sec : 0.0,
-           sec > 0 ? double(msg) * double(completed) / kGiB / sec : 0.0);
+           sec > 0 ? double(bytes_done) / kGiB / sec : 0.0);
+    if (n_requests) {
+        std::sort(flow_ms.begin(), flow_ms.end());
+        double mean = 0;
+        for (double v : flow_ms) mean += v;
+        printf("[client] requests=%zu finished=%zu unfinished=%zu flow_time_ms p50=%.3f p99=%.3f mean=%.3f\n", n_requests, flow_ms.size(),
+               unfinished, percentile_sorted(flow_ms, 0.5), percentile_sorted(flow_ms, 0.99), flow_ms.empty() ? 0.0 : mean / flow_ms.size());
+    }
     if (ctl.stop_requested()) printf("[client] control_stop=1 mode=%s pace_sleep_us=%u\n", mode_name(ctl.mode()), ctl.sleep_us());
     if (!lat_us.empty()) {
         std::sort(lat_us.begin(), lat_us.end());

@@ -1,7 +1,7 @@
 // gpu_server: the target end of a flow. Exposes a memory region, serves clients one after another,
 // and acknowledges a write only after its bytes are in place.
 //
-//   gpu_server <fabric:tcp|sim> <mr_size> <tcp_port> <port> <gid_idx> [mtu=1024]
+//   gpu_server <fabric:tcp|sim|link:GB/s> <mr_size> <tcp_port> <port> <gid_idx> [mtu=1024]
 //
 // Same command line and session order as the reference's server (src/gpu_server.cu:8,215-530:
 // handshake, region info, client parameters, ready byte, then either idle until "done" or the
@@ -9,11 +9,18 @@
 // an RNIC and must flush GPUDirect writes before the ACK (:54-80,426-436); here the first argument
 // names the fabric instead of an InfiniBand device: `tcp` receives the payload on the session socket
 // into the region (the ACK follows the last byte, so it has the same meaning), `sim` moves no payload.
+// `link:<GB/s>` is the shared-link form used by the CPU-only control-loop experiment: clients are served at the same
+// time (a thread each) and every message occupies one simulated link of that rate for len / rate, first come first
+// served, before its tag goes back, so concurrent flows really take bandwidth from one another.
 // GPU-resident pools between processes are exposed by skygdr_b200.parallel.symm (CUDA IPC) instead.
 #include <signal.h>
 
+#include <atomic>
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
+#include <thread>
 #include <vector>
 
 #include "util.hpp"
@@ -26,14 +33,14 @@ static void on_sig(int) { g_stop = 1; }
 
 int main(int argc, char** argv) {
     if (argc < 6) {
-        fprintf(stderr, "usage: %s <fabric:tcp|sim> <mr_size> <tcp_port> <port> <gid_idx> [mtu=1024]\n", argv[0]);
+        fprintf(stderr, "usage: %s <fabric:tcp|sim|link:GB/s> <mr_size> <tcp_port> <port> <gid_idx> [mtu=1024]\n", argv[0]);
         return 1;
     }
     std::string fabric = argv[1];
     uint64_t mr_size = 0;
     if (!parse_size(argv[2], &mr_size) || mr_size == 0) { fprintf(stderr, "[server] bad mr_size\n"); return 2; }
     int tcp_port = atoi(argv[3]);
-    bool sim = fabric.rfind("sim", 0) == 0;
+    bool sim = fabric.rfind("sim", 0) == 0 || fabric.rfind("link", 0) == 0;
     std::vector<unsigned char> region;
     if (!sim) region.resize(mr_size);
     struct sigaction sa{};
@@ -45,10 +52,28 @@ int main(int argc, char** argv) {
     if (ls < 0) { perror("[server] listen"); return 1; }
     printf("[server] fabric=%s mr_size=%llu listening on %d\n", fabric.c_str(), (unsigned long long)mr_size, tcp_port);
     fflush(stdout);
-    uint32_t serial = 1;
-    while (!g_stop) {
-        int c = accept(ls, nullptr, nullptr);
-        if (c < 0) { if (g_stop) break; continue; }
+    std::atomic<uint32_t> serial{1};
+    std::mutex link_mu;
+    uint64_t link_free_ns = 0;
+    const bool link = fabric.rfind("link", 0) == 0;
+    double link_gbps = 64.0;
+    if (link && fabric.size() > 5) link_gbps = atof(fabric.c_str() + 5);
+    if (link_gbps <= 0) link_gbps = 64.0;
+    auto occupy_link = [&](uint32_t len) {               // first come first served; returns when the message has left the link
+        uint64_t t_done;
+        {
+            std::lock_guard<std::mutex> g(link_mu);
+            const uint64_t now = mono_ns();
+            t_done = std::max(now, link_free_ns) + (uint64_t)(double(len) / (link_gbps * 1e9) * 1e9);
+            link_free_ns = t_done;
+        }
+        for (;;) {
+            const uint64_t now = mono_ns();
+            if (now >= t_done) break;
+            if (t_done - now > 200000) std::this_thread::sleep_for(std::chrono::nanoseconds(t_done - now - 100000));
+        }
+    };
+    auto serve = [&](int c) {
         int yes = 1;
         setsockopt(c, IPPROTO_TCP, TCP_NODELAY, &yes, sizeof yes);
         ConnInfo peer{}, mine{};
@@ -61,12 +86,12 @@ int main(int argc, char** argv) {
         for (uint32_t q = 1; ok && q < cp.qps; ++q) ok = recv_all(c, &peer, sizeof peer) && send_all(c, &mine, sizeof mine);
         ok = ok && send_all(c, &ready, 1);
         uint64_t msgs = 0, bytes = 0;
-        std::vector<unsigned char> scratch;
         while (ok && !g_stop) {
             MsgHeader h;
             if (!recv_all(c, &h, sizeof h)) break;
             if (h.kind == 2) break;                                  // client is done
             if (h.offset + h.len > mr_size) { fprintf(stderr, "[server] access outside the region\n"); break; }
+            if (link) occupy_link(h.len);
             if (h.kind == 0) {                                       // write (+ optional ack)
                 if (!sim) { if (!recv_all(c, region.data() + h.offset, h.len)) break; }
                 ++msgs; bytes += h.len;
@@ -81,6 +106,12 @@ int main(int argc, char** argv) {
                (unsigned long long)bytes, cp.op ? "write" : "read", cp.write_ack, cp.qd, cp.qps);
         fflush(stdout);
         close(c);
+    };
+    while (!g_stop) {
+        int c = accept(ls, nullptr, nullptr);
+        if (c < 0) { if (g_stop) break; continue; }
+        if (link) std::thread(serve, c).detach();        // shared link: clients at the same time
+        else serve(c);                                   // the reference's order: one client after the other
     }
     close(ls);
     return 0;

@@ -329,3 +329,17 @@ def test_steady_queue_depth_trades_latency_for_nothing_on_a_saturated_link():
     assert 0.85 < thr < 0.97 and 950 < p50 < 1150
     thr, p50 = run("read", "1", "0", "4", *positional, "0", "2")            # read_min_qd=2 -> qd 4
     assert 0.85 < thr < 0.97 and 230 < p50 < 300
+
+
+def test_config1_with_the_compat_programs_as_flows():
+    """fabricd + gpu_server link:<GB/s> + two cpu_client processes that register themselves (one request stream, one backlogged
+    flow stopped over its control port): with target_track the requests finish sooner than without scheduling. Short and
+    lenient: it runs in real time."""
+    from skygdr_b200.control.config1 import Config1, run_processes
+
+    cfg = Config1(duration_s=2.5)
+    none = run_processes(cfg, policy="none")
+    tt = run_processes(cfg, policy="target_track")
+    assert none["unfinished"] == 0 and tt["unfinished"] == 0 and none["requests"] == tt["requests"] > 20
+    assert tt["flow_time_mean_ms"] < none["flow_time_mean_ms"], (tt, none)
+    assert tt["offload_goodput_gbps"] > 0.8 * none["offload_goodput_gbps"], (tt, none)
