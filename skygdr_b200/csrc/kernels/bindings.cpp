@@ -204,7 +204,7 @@ static void kv_transfer(torch::Tensor src_pool, std::vector<uint64_t> dst_ptrs, 
 // ---- causal prefill attention over the paged pool ----
 static void prefill_attn(torch::Tensor q, torch::Tensor kv_layer, torch::Tensor out, torch::Tensor block_table, torch::Tensor seq_start,
                          int64_t block_stride, int64_t kv_stride, int64_t head_stride, int64_t tok_stride, int kv_heads, int max_len, double scale,
-                         torch::Tensor status, int64_t pool_rows, bool two_tiles) {
+                         torch::Tensor status, int64_t pool_rows, int two_tiles) {
     c10::cuda::CUDAGuard g(q.device());
     TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous() && out.is_contiguous() && out.sizes() == q.sizes(), "q/out: contiguous [tokens][heads][128]");
     TORCH_CHECK(block_table.dim() == 2 && seq_start.numel() == block_table.size(0) + 1, "seq_start holds n_seqs + 1 offsets");
@@ -215,7 +215,8 @@ static void prefill_attn(torch::Tensor q, torch::Tensor kv_layer, torch::Tensor 
     p.block_stride = block_stride; p.kv_stride = kv_stride; p.head_stride = head_stride; p.tok_stride = tok_stride;
     p.n_seqs = (int)block_table.size(0); p.q_heads = (int)q.size(1); p.kv_heads = kv_heads; p.max_blocks = (int)block_table.size(1);
     p.max_len = max_len; p.total_tokens = (int)q.size(0); p.scale = (float)scale;
-    p.two_tiles = two_tiles ? 1 : 0;
+    TORCH_CHECK(two_tiles >= 0 && two_tiles <= 2, "variant: 0 one query tile per CTA, 1 two tiles, 2 two tiles with 64-key steps");
+    p.two_tiles = two_tiles;
     p.status = status_ptr(status);
     SKY_CUDA_CHECK(launch_prefill_attn_tc(p, pool_rows, cur_stream()));
 }

@@ -23,7 +23,8 @@ struct PrefillAttnParams {
     int max_len;                 // longest prompt (sizes the grid)
     int total_tokens;
     float scale;
-    int two_tiles;               // 1: two query tiles per CTA working in alternation (prefill_attn_tc2_kernel); 0: one tile per CTA
+    int two_tiles;               // 1: two query tiles per CTA working in alternation (prefill_attn_tc2_kernel); 0: one tile per CTA;
+                                 // 2: two tiles with key steps of 64 and double-buffered scores (prefill_attn_tc3_kernel)
     LaunchStatus* status;
 };
 

@@ -534,6 +534,256 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc2_kernel(const _
     if (warp == 9) tmem_dealloc(tmem_base, 512);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Two query tiles per CTA with key steps of 64. Same roles, rings and tiles as the kernel above, but every 128-token
+// K/V tile is consumed as two steps of 64 keys, so that each query tile can keep TWO score buffers in TMEM
+// (2 tiles x 2 buffers x 64 columns + 2 accumulators x 128 columns = 512 columns): the scores of step t+1 are computed
+// while the warpgroup still works on step t, and a softmax warpgroup never waits for its own score MMA. P is
+// double-buffered the same way (2 x 16 KB per query tile, the space of one 32 KB buffer).
+// Barriers per query tile x: s_ready[x][t&1], p_ready[x][t&1], o_done[x][t&1], one completion each per step of that parity.
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                                                                          const __grid_constant__ CUtensorMap tmap_kv, const PrefillAttnParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    unsigned char* q_sm = smem;                                        // Q_A, Q_B
+    unsigned char* ring = smem + 2 * PF_TILE_BYTES;
+    unsigned char* p_sm = ring + PF2_UNITS * PF_TILE_BYTES;            // P_A[2], P_B[2]: four [128 q][64 keys] halves
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PF2_TILES_BYTES);
+    uint64_t* full_bar = bars;                        // [PF2_UNITS]
+    uint64_t* empty_bar = bars + PF2_UNITS;           // [PF2_UNITS]
+    uint64_t* s_ready = bars + 2 * PF2_UNITS;         // [2 tiles][2 parities]
+    uint64_t* p_ready = s_ready + 4;                  // [2][2]
+    uint64_t* o_done = p_ready + 4;                   // [2][2]
+    uint64_t& q_full = *(o_done + 4);
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(o_done + 5);
+    if (smem_u32(smem) & 1023) {
+        if (threadIdx.x == 0) set_status(p.status, SKY_STATUS_BAD_INDEX, 69);
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.x, seq = blockIdx.z;
+    const int tok_base = p.seq_start[seq];
+    const int n = p.seq_start[seq + 1] - tok_base;
+    const int q_tiles = (n + PF_TILE - 1) / PF_TILE;
+    const int pair = (int)gridDim.y - 1 - (int)blockIdx.y;
+    if (2 * pair >= q_tiles) return;
+    const int qt_x[2] = {2 * pair, 2 * pair + 1};
+    const int nkt_x[2] = {qt_x[0] + 1, qt_x[1] < q_tiles ? qt_x[1] + 1 : 0};      // 128-token key tiles per query tile
+    const int n_kt = max(nkt_x[0], nkt_x[1]);
+    const int kvh = head / (p.q_heads / p.kv_heads);
+    const int* table = p.block_table + (long long)seq * p.max_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PF2_UNITS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&q_full, 1);
+        for (int i = 0; i < 4; ++i) { mbar_init(&s_ready[i], 1); mbar_init(&p_ready[i], 128); mbar_init(&o_done[i], 1); }
+        fence_barrier_init();
+    }
+    if (warp == 9) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;                               // scores: x * 128 + buffer * 64; accumulators: 256 + x * 128
+
+    if (warp == 8) {
+        // ---------------- TMA producer (as in the kernel above) ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_q);
+            tma_prefetch_desc(&tmap_kv);
+            mbar_expect_tx(&q_full, 2 * PF_TILE_BYTES);
+            for (int x = 0; x < 2; ++x) {
+                tma_load_3d(q_sm + x * PF_TILE_BYTES, &tmap_q, 0, head, tok_base + qt_x[x] * PF_TILE, &q_full);
+                tma_load_3d(q_sm + x * PF_TILE_BYTES + PF_HALF, &tmap_q, 64, head, tok_base + qt_x[x] * PF_TILE, &q_full);
+            }
+        }
+        const int ts_rows = (int)(p.tok_stride >> 7);
+        const long long head_row = (long long)kvh * (p.head_stride >> 7);
+        const int pg = lane >> 1, half = lane & 1;
+        for (int u = 0; u < 2 * n_kt; ++u) {
+            const int s = u % PF2_UNITS;
+            if (u >= PF2_UNITS && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], (uint32_t)((u / PF2_UNITS) - 1) & 1))) {
+                if (lane == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 61);
+                break;
+            }
+            unsigned char* st = ring + s * PF_TILE_BYTES;
+            if (lane == 0) mbar_expect_tx(&full_bar[s], PF_TILE_BYTES);
+            __syncwarp();
+            if (lane < 16) {
+                const int e = (u >> 1) * 8 + pg;
+                const int blk = e < p.max_blocks ? __ldg(table + e) : 0;
+                const long long row0 = ((long long)blk * p.block_stride >> 7) + ((u & 1) ? (p.kv_stride >> 7) : 0) + head_row;
+                tma_load_3d(st + half * PF_HALF + pg * 2048, &tmap_kv, half * 64, (int)(row0 % ts_rows), (int)(row0 / ts_rows), &full_bar[s]);
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer: steps of 64 keys; step t of a query tile uses key tile t >> 1, half t & 1 ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64);
+            constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128) | (1u << 16);
+            bool good = mbar_wait(&q_full, 0);
+            if (!good) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 62);
+            auto issue_s = [&](int x, int t) -> bool {
+                const int j = t >> 1, hb = t & 1, u = 2 * j, s = u % PF2_UNITS;
+                if (!mbar_wait(&full_bar[s], (uint32_t)(u / PF2_UNITS) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 63); return false; }
+                tc_fence_after();
+                // rows hb * 64 .. + 63 of the K tile: 64 rows x 128 bytes further into each dim half
+                const uint32_t k_addr = smem_u32(ring + s * PF_TILE_BYTES) + hb * 64 * 128, q_addr = smem_u32(q_sm + x * PF_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint64_t a = umma_desc_k_sw128(q_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
+                    const uint64_t b = umma_desc_k_sw128(k_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
+                    tc_mma_f16(tmem_base + x * 128 + (t & 1) * 64, a, b, idesc_s, k ? 1u : 0u);
+                }
+                const bool last_user = hb == 1 && (x == 1 || j >= nkt_x[1]);
+                if (last_user) tc_commit(&empty_bar[s]);
+                tc_commit(&s_ready[x * 2 + (t & 1)]);
+                return true;
+            };
+            auto issue_pv = [&](int x, int t) -> bool {
+                const int j = t >> 1, hb = t & 1;
+                if (!mbar_wait(&p_ready[x * 2 + (t & 1)], (uint32_t)(t >> 1) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 64); return false; }
+                const int u = 2 * j + 1, s = u % PF2_UNITS;
+                if (!mbar_wait(&full_bar[s], (uint32_t)(u / PF2_UNITS) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 65); return false; }
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(ring + s * PF_TILE_BYTES) + hb * 64 * 128;
+                const uint32_t p_addr = smem_u32(p_sm + x * PF_TILE_BYTES + (t & 1) * PF_HALF);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {                          // 4 steps of 16 keys
+                    const uint64_t a = umma_desc_k_sw128(p_addr + k * 32);
+                    const uint64_t b = umma_desc_mn_sw128(v_addr + k * 2048, PF_HALF, 1024);
+                    tc_mma_f16(tmem_base + 256 + x * 128, a, b, idesc_o, (t | k) ? 1u : 0u);
+                }
+                const bool last_user = hb == 1 && (x == 1 || j >= nkt_x[1]);
+                if (last_user) tc_commit(&empty_bar[s]);
+                tc_commit(&o_done[x * 2 + (t & 1)]);
+                return true;
+            };
+            const int steps_x[2] = {2 * nkt_x[0], 2 * nkt_x[1]};
+            const int steps = max(steps_x[0], steps_x[1]);
+            for (int t = 0; t < 2 && good; ++t)                        // both score buffers of both tiles
+                for (int x = 0; x < 2 && good; ++x)
+                    if (t < steps_x[x]) good = issue_s(x, t);
+            for (int t = 0; t < steps && good; ++t) {
+                for (int x = 0; x < 2 && good; ++x) {
+                    if (t >= steps_x[x]) continue;
+                    good = issue_pv(x, t);
+                    if (good && t + 2 < steps_x[x]) good = issue_s(x, t + 2);      // its buffer is free: the P of step t has been written
+                }
+            }
+        }
+    } else {
+        // ---------------- softmax warpgroups: warpgroup x <-> query tile x, thread r <-> query row r ----------------
+        const int x = warp >> 2;
+        const int r = threadIdx.x & 127;
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tm_o = tmem_base + 256 + x * 128;
+        const int qt = qt_x[x], my_steps = 2 * nkt_x[x];
+        const float qs = p.scale * 1.4426950408889634f;
+        const int qpos_raw = qt * PF_TILE + r;
+        const bool row_valid = my_steps > 0 && qpos_raw < n;
+        const int qpos = qpos_raw < n ? qpos_raw : n - 1;
+        float m_ref = -INFINITY, l_sum = 0.f;
+        bool ok = true;
+        for (int t = 0; t < my_steps; ++t) {
+            const int par = t & 1, bi = x * 2 + par;
+            if (ok && !mbar_wait(&s_ready[bi], (uint32_t)(t >> 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 66); ok = false; }
+            tc_fence_after();
+            uint32_t sc[64];
+            tmem_ld_x32(tmem_base + x * 128 + par * 64 + lane_off, sc);
+            tmem_ld_x32(tmem_base + x * 128 + par * 64 + lane_off + 32, sc + 32);
+            tc_wait_ld();
+            const int kbase = t * 64;                                    // first key of this step
+            if ((t >> 1) == qt) {                                        // the diagonal key tile: causal mask and the prompt's end
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const int kpos = kbase + i;
+                    if (kpos > qpos || kpos >= n) sc[i] = 0xff800000u;     // -inf
+                }
+            }
+            float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 64; i += 4) {
+                t0 = fmaxf(t0, __uint_as_float(sc[i]));
+                t1 = fmaxf(t1, __uint_as_float(sc[i + 1]));
+                t2 = fmaxf(t2, __uint_as_float(sc[i + 2]));
+                t3 = fmaxf(t3, __uint_as_float(sc[i + 3]));
+            }
+            const float tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)) * qs;      // -inf when the whole step is masked (upper half of a diagonal tile)
+            float alpha = 1.0f;
+            const bool raise = tmax > m_ref + PF_RESCALE || (m_ref == -INFINITY && tmax > -INFINITY);
+            if (raise) {
+                alpha = m_ref == -INFINITY ? 0.f : exp2f(m_ref - tmax);
+                m_ref = tmax;
+            }
+            const bool any_raise = __any_sync(0xffffffffu, raise) && t > 0;
+            // P buffer `par` was last read by the P.V of step t-2; a rescale of the accumulator waits for step t-1 as well.
+            if (any_raise) {
+                if (ok && !mbar_wait(&o_done[x * 2 + ((t - 1) & 1)], (uint32_t)((t - 1) >> 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 67); ok = false; }
+                tc_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < 128; c0 += 16) {
+                    uint32_t o[16];
+                    tmem_ld_x16(tm_o + lane_off + c0, o);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st_x16(tm_o + lane_off + c0, o);
+                }
+                tc_wait_st();
+            } else if (t > 1) {
+                if (ok && !mbar_wait(&o_done[bi], (uint32_t)((t - 2) >> 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 67); ok = false; }
+            }
+            l_sum *= alpha;
+            unsigned char* prow = p_sm + x * PF_TILE_BYTES + par * PF_HALF;
+            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;       // nothing seen yet: every score of this step is -inf, exp2 gives 0
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+            for (int c = 0; c < 64; c += 8) {
+                float e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) e[i] = exp2f(fmaf(__uint_as_float(sc[c + i]), qs, neg_m));
+                s0 += e[0] + e[4]; s1 += e[1] + e[5]; s2 += e[2] + e[6]; s3 += e[3] + e[7];
+                uint32_t packed[4];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(e[i], e[i + 1]);
+                    packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+                }
+                *reinterpret_cast<uint4*>(prow + sw128_off(r, c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            l_sum += (s0 + s1) + (s2 + s3);
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(&p_ready[bi]);
+        }
+        if (my_steps > 0) {
+            const int tl = my_steps - 1;
+            if (ok && !mbar_wait(&o_done[x * 2 + (tl & 1)], (uint32_t)(tl >> 1) & 1)) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 68); ok = false; }
+            tc_fence_after();
+            const float inv = (ok && l_sum > 0.f) ? 1.0f / l_sum : 0.f;
+            __nv_bfloat16* orow = p.out + ((long long)(tok_base + qpos_raw) * p.q_heads + head) * 128;
+#pragma unroll 1
+            for (int c0 = 0; c0 < 128; c0 += 16) {
+                uint32_t o[16];
+                tmem_ld_x16(tm_o + lane_off + c0, o);
+                tc_wait_ld();
+                uint32_t packed[8];
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                    packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+                }
+                if (row_valid) {
+                    *reinterpret_cast<uint4*>(orow + c0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    *reinterpret_cast<uint4*>(orow + c0 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) tmem_dealloc(tmem_base, 512);
+}
+
 typedef CUresult (*PfEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -568,6 +818,14 @@ cudaError_t launch_prefill_attn_tc(const PrefillAttnParams& p, long long pool_ro
     CUtensorMap tq, tkv;
     if (!pf_make_tmap(&tq, p.q, p.q_heads, p.total_tokens, PF_TILE)) return cudaErrorInvalidValue;
     if (!pf_make_tmap(&tkv, p.kv, ts_rows, pool_rows / ts_rows, 16)) return cudaErrorInvalidValue;
+    if (p.two_tiles == 2) {                              // key steps of 64, double-buffered scores (not yet run on a GPU)
+        static unsigned long long attr_mask3 = 0;
+        if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(prefill_attn_tc3_kernel), PF2_SMEM, &attr_mask3); e != cudaSuccess) return e;
+        const int q_tiles = (p.max_len + PF_TILE - 1) / PF_TILE;
+        dim3 grid(p.q_heads, (q_tiles + 1) / 2, p.n_seqs);
+        prefill_attn_tc3_kernel<<<grid, PF_THREADS, PF2_SMEM, stream>>>(tq, tkv, p);
+        return cudaGetLastError();
+    }
     if (p.two_tiles) {
         static unsigned long long attr_mask2 = 0;
         if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(prefill_attn_tc2_kernel), PF2_SMEM, &attr_mask2); e != cudaSuccess) return e;

@@ -55,9 +55,10 @@ class PrefillAttention:
     Pages must hold finite values past a prompt's last token (a fresh pool is zeroed); block-table entries past a prompt's
     pages must name valid blocks."""
 
-    def __init__(self, device, two_tiles: bool = True):
-        """two_tiles: two query tiles per CTA working in alternation with the tensor core (the faster variant); False: one
-        query tile per CTA with two softmax warpgroups per tile."""
+    def __init__(self, device, two_tiles=True):
+        """two_tiles: True = two query tiles per CTA working in alternation with the tensor core (the faster variant); False = one
+        query tile per CTA with two softmax warpgroups per tile; 2 = two tiles with key steps of 64 and double-buffered scores
+        (built for the next measurement round: compiled, not yet run on a GPU)."""
         self._C = load()
         self.device = torch.device(device)
         self.status = new_status(self.device)
@@ -76,7 +77,7 @@ class PrefillAttention:
             head_stride, tok_stride = g.head_dim, g.kv_heads * g.head_dim
         self._C.prefill_attn(q, pool.layer_base(layer), out, block_table, seq_start, bs, ks, head_stride, tok_stride, g.kv_heads, int(max_len),
                              scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]), self.status,
-                             (pool.data.numel() - layer * ls) // 128, self.two_tiles)
+                             (pool.data.numel() - layer * ls) // 128, int(self.two_tiles))
         return out
 
 

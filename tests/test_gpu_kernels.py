@@ -1,5 +1,6 @@
 """Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
 import math
+import os
 import time
 
 import pytest
@@ -253,7 +254,7 @@ def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
     assert int(attn.counters.abs().sum()) == 0
 
 
-@pytest.mark.parametrize("two_tiles", [True, False])
+@pytest.mark.parametrize("two_tiles", [True, False] + ([2] if os.environ.get("SKYGDR_TEST_PREFILL_64") == "1" else []))   # 2: not yet run on a GPU
 @pytest.mark.parametrize("layout", ["hnd", "nhd"])
 @pytest.mark.parametrize("kv_heads,q_heads", [(8, 32), (2, 4), (1, 1)])
 def test_prefill_attention_matches_reference(ops, layout, kv_heads, q_heads, two_tiles):
