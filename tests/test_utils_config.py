@@ -33,3 +33,21 @@ def test_daemon_accepts_the_generated_arguments(tmp_path):
         with FabricClient(port=d.port) as cl:
             assert cl.request("POLICY") == "OK policy=ladder"
             assert cl.request("WINDOW") == "OK window_us=2000"
+
+
+def test_bench_reference_arm_prints_one_json_line():
+    """`bench.py --impl reference` must always end with exit code 0 and one JSON line that either carries the metric or says
+    why the reference cannot produce it (it has no decoder model; see baseline/reference_arm.py)."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3"],
+                       capture_output=True, text=True, timeout=300, cwd=root)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and ("unavailable" in d or "value" in d)
