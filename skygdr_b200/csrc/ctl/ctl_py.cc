@@ -238,6 +238,15 @@ PYBIND11_MODULE(_ctl, m) {
             return o;
         });
 
+    // Native pacer thread for one page given by address (a page of the daemon core, of pinned host memory, of a mapped file).
+    py::class_<PagePacer>(m, "PagePacer")
+        .def(py::init([](uint64_t page_addr, double rate_gbps, uint64_t window_ns, double burst_windows) {
+            return new PagePacer(reinterpret_cast<SkyCreditPage*>(page_addr), rate_gbps, window_ns, burst_windows);
+        }), py::arg("page_addr"), py::arg("rate_gbps"), py::arg("window_ns") = 1000000, py::arg("burst_windows") = 2.0)
+        .def("start", &PagePacer::start, py::arg("base") = 0)
+        .def("stop", &PagePacer::stop, py::call_guard<py::gil_scoped_release>())
+        .def_property_readonly("windows", &PagePacer::windows);
+
     // The heartbeat rule of host-side data paths, callable on a core's page (tests, in-process flows).
     py::class_<SkyHeartbeatWatch>(m, "HeartbeatWatch")
         .def(py::init([]() { return SkyHeartbeatWatch{0, 0, 0}; }))

@@ -9,6 +9,9 @@
 // optional NVML link counters), and the action is a store of a byte grant into
 // each page, which a kernel or copy worker reads directly.
 #pragma once
+#include <chrono>
+#include <thread>
+#include <atomic>
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -39,6 +42,54 @@ inline SkyCreditPage* map_credit_page(const std::string& path, bool create) {
     return reinterpret_cast<SkyCreditPage*>(p);
 }
 inline void unmap_credit_page(SkyCreditPage* p) { if (p) munmap(p, 4096); }
+
+// A control side for ONE page without a daemon: a native thread that adds `rate` worth of bytes to the page's grant every
+// window (with a burst allowance of a few windows for a flow that fell behind) and bumps the epoch, so that an in-process
+// flow is paced without a Python thread (and its interpreter lock) in the loop.
+class PagePacer {
+public:
+    PagePacer(SkyCreditPage* page, double rate_gbps, uint64_t window_ns, double burst_windows)
+        : page_(page), rate_(rate_gbps), window_ns_(window_ns ? window_ns : 1000000), burst_(burst_windows) {}
+    ~PagePacer() { stop(); }
+    void start(uint64_t base) {
+        stop();
+        stop_.store(false);
+        page_->unlimited = 0;
+        page_->window_ns = window_ns_;
+        page_->budget_per_window = (uint64_t)(rate_ * 1e9 * double(window_ns_) * 1e-9);
+        __atomic_store_n(&page_->granted_bytes, base, __ATOMIC_RELEASE);
+        __atomic_store_n(&page_->epoch, page_->epoch + 1, __ATOMIC_RELEASE);
+        thread_ = std::thread([this, base] {
+            double granted = double(base);
+            uint64_t t_prev = mono_ns();
+            while (!stop_.load(std::memory_order_relaxed)) {
+                std::this_thread::sleep_for(std::chrono::nanoseconds(window_ns_));
+                const uint64_t now = mono_ns();
+                const double add = rate_ * double(now - t_prev);           // GB/s x ns = bytes
+                t_prev = now;
+                const double used = double(__atomic_load_n(&page_->consumed_bytes, __ATOMIC_RELAXED));
+                granted = used < granted ? std::min(granted + add, std::max(granted, used + add * burst_)) : granted + add;
+                __atomic_store_n(&page_->granted_bytes, (uint64_t)granted, __ATOMIC_RELEASE);
+                __atomic_store_n(&page_->epoch, page_->epoch + 1, __ATOMIC_RELEASE);
+                windows_.fetch_add(1, std::memory_order_relaxed);
+            }
+        });
+    }
+    void stop() {
+        stop_.store(true);
+        if (thread_.joinable()) thread_.join();
+    }
+    uint64_t windows() const { return windows_.load(); }
+
+private:
+    SkyCreditPage* page_;
+    double rate_;
+    uint64_t window_ns_;
+    double burst_;
+    std::atomic<bool> stop_{true};
+    std::atomic<uint64_t> windows_{0};
+    std::thread thread_;
+};
 
 struct DaemonConfig {
     double capacity_gbps = 64.0;          // capacity of the shared domain

@@ -2,8 +2,6 @@
 launch status block, shared by the transfer, offload and memhog kernels."""
 from __future__ import annotations
 
-import threading
-import time
 from typing import Dict, Optional
 
 import torch
@@ -82,37 +80,24 @@ class CreditPage:
 
 
 class LocalPacer:
-    """In-process control side for one page: a thread that adds ``rate_gbps`` worth of bytes to the
-    grant every ``window_ms`` (what fabricd does for registered flows, without the daemon)."""
+    """In-process control side for one page: adds ``rate_gbps`` worth of bytes to the grant every ``window_ms`` (what fabricd
+    does for registered flows, without the daemon). The loop is a native thread (csrc/ctl/daemon_core.hpp, PagePacer), so a
+    paced flow does not depend on the interpreter lock of the process that also launches the kernels."""
 
     def __init__(self, page: CreditPage, rate_gbps: float, window_ms: float = 1.0, burst_windows: float = 2.0):
-        self.page, self.rate, self.window_s, self.burst = page, rate_gbps, window_ms * 1e-3, burst_windows
-        self._stop = threading.Event()
-        self._thr: Optional[threading.Thread] = None
+        from ..control import ctl
+
+        self.page = page
+        self._native = ctl.PagePacer(page.host_ptr, rate_gbps, int(window_ms * 1e6), burst_windows)
 
     def start(self, base: int = 0):
-        self.page.grant(base, unlimited=False)
-
-        def run():
-            granted = float(base)
-            t_prev = time.perf_counter()
-            while not self._stop.is_set():
-                time.sleep(self.window_s)
-                now = time.perf_counter()
-                add = self.rate * 1e9 * (now - t_prev)
-                t_prev = now
-                used = self.page.read()["consumed_bytes"]
-                granted = min(granted + add, max(granted, used + add * self.burst)) if used < granted else granted + add
-                self.page.grant(int(granted), unlimited=False)
-
-        self._thr = threading.Thread(target=run, daemon=True)
-        self._thr.start()
+        self.page.granted = base
+        self._native.start(base)
         return self
 
     def stop(self):
-        self._stop.set()
-        if self._thr:
-            self._thr.join()
+        self._native.stop()
+        self.page.granted = self.page.read()["granted_bytes"]
 
 
 def new_status(device) -> torch.Tensor:

@@ -262,3 +262,27 @@ def test_window_step_cost_leaves_room_in_a_one_millisecond_window(ctl):
         d.step_window(now)
     per_window_us = (time.perf_counter() - t0) / n * 1e6
     assert per_window_us < 250.0, per_window_us                     # a quarter of the shortest window, with 256 flows
+
+
+def test_native_page_pacer_grants_at_its_rate_and_lets_a_flow_catch_up(ctl):
+    """The in-process pacer is a native thread on a page given by address: it grants rate x time while the flow keeps up, holds
+    the grant a couple of windows ahead of a flow that does not, and bumps the epoch every window (the heartbeat)."""
+    import ctypes
+    import time
+
+    page = (ctypes.c_uint64 * 32)()                  # 256 bytes; [1] granted, [2] epoch, [16] consumed
+    pacer = ctl.PagePacer(ctypes.addressof(page), 1.0, 1_000_000, 2.0)        # 1 GB/s, 1 ms windows
+    pacer.start(0)
+    time.sleep(0.05)
+    idle = page[1]
+    assert 0 < idle < 6_000_000                      # nothing consumed: the grant stays about two windows ahead
+    t0 = time.perf_counter()
+    g0 = page[1]
+    for _ in range(60):                              # a flow that uses every byte it is given
+        page[16] = page[1]
+        time.sleep(0.001)
+    dt = time.perf_counter() - t0
+    pacer.stop()
+    rate = (page[1] - g0) / dt / 1e9
+    assert 0.7 < rate < 1.3, rate
+    assert page[2] >= pacer.windows > 50 and page[5] & 0xffffffff00000000 == 0      # epoch per window; `unlimited` (high half of word 5) off
