@@ -27,6 +27,7 @@
 #include <vector>
 
 #include "daemon_core.hpp"
+#include "flow_client.hpp"
 #include "protocol.hpp"
 #include "util.hpp"
 #include "wire.hpp"
@@ -154,28 +155,19 @@ int main(int argc, char** argv) {
     if (span < msg) span = msg;
 
     // ---- optional registration with the daemon ----
-    int dsock = -1;
+    FlowClient fabric_client;
     SkyCreditPage* page = nullptr;
-    uint32_t flow_id = 0;
     if (const char* d = getenv("SKYGDR_DAEMON")) {
-        std::string hp = d;
-        size_t colon = hp.rfind(':');
-        if (colon != std::string::npos) dsock = tcp_connect(hp.substr(0, colon), atoi(hp.c_str() + colon + 1));
-        if (dsock >= 0) {
+        if (fabric_client.connect(d)) {
             const char* nm = getenv("SKYGDR_FLOW_NAME");
             const char* pr = getenv("SKYGDR_FLOW_PRIORITY");
             const char* tg = getenv("SKYGDR_FLOW_TARGET_GBPS");
-            std::string line = std::string("REGISTER ") + (nm ? nm : "kv_offload") + " " + (pr ? pr : "besteffort") + " " + (tg ? tg : "0") + "\n";
-            char buf[512] = {0};
-            if (send_all(dsock, line.data(), line.size()) && recv(dsock, buf, sizeof buf - 1, 0) > 0) {
-                std::string rep = buf;
-                size_t p1 = rep.find("flow_id="), p2 = rep.find("page=");
-                if (p1 != std::string::npos) flow_id = (uint32_t)strtoul(rep.c_str() + p1 + 8, nullptr, 10);
-                if (p2 != std::string::npos) {
-                    std::string path = rep.substr(p2 + 5, rep.find(' ', p2) - p2 - 5);
-                    if (path != "-") page = map_credit_page(path, false);
-                }
-                fprintf(stderr, "[client] registered with fabricd: %s", buf);
+            std::string reply;
+            if (fabric_client.register_flow(nm ? nm : "kv_offload", pr ? pr : "besteffort", tg ? atof(tg) : 0.0, "", &reply)) {
+                page = fabric_client.page();
+                fprintf(stderr, "[client] registered with fabricd: %s", reply.c_str());
+            } else {
+                fprintf(stderr, "[client] registration refused: %s", reply.empty() ? "no answer\n" : reply.c_str());
             }
         } else {
             fprintf(stderr, "[client] SKYGDR_DAEMON=%s not reachable; running unregistered\n", d);
@@ -194,7 +186,7 @@ int main(int argc, char** argv) {
             fflush(ts_fp);
         } else fprintf(stderr, "[client] failed to open ts_out=%s\n", ts_out.c_str());
     }
-    uint64_t completed = 0, win_completed0 = 0, seen = 0, seq_off = 0, consumed = 0, renew_at = mono_ns();
+    uint64_t completed = 0, win_completed0 = 0, seen = 0, seq_off = 0, consumed = 0;
     Rng rng(mono_ns() ^ (uint64_t)getpid());
     uint64_t t_start = mono_ns(), win_start = t_start;
     auto flush_window = [&](bool force) {
@@ -286,13 +278,7 @@ int main(int argc, char** argv) {
         uint32_t pace = ctl.sleep_us();                  // legacy pacing: sleep after each post
         if (pace) std::this_thread::sleep_for(std::chrono::microseconds(pace));
         flush_window(false);
-        const uint64_t now = mono_ns();
-        if (dsock >= 0 && now - renew_at > 500000000ull) {
-            char line[64], rep[64];
-            int n = snprintf(line, sizeof line, "RENEW %u\n", flow_id);
-            if (send_all(dsock, line, (size_t)n)) { ssize_t k = recv(dsock, rep, sizeof rep, 0); (void)k; }
-            renew_at = now;
-        }
+        fabric_client.renew_if_due(mono_ns());
         return true;
     };
 
@@ -373,11 +359,8 @@ int main(int argc, char** argv) {
     } else printf("[client] latency_us samples=0\n");
     fflush(stdout);
     if (s >= 0) { MsgHeader h{0, 0, 0, 2, 0}; send_all(s, &h, sizeof h); close(s); }
-    if (dsock >= 0) {
-        char line[64];
-        int n = snprintf(line, sizeof line, "UNREGISTER %u\nQUIT\n", flow_id);
-        send_all(dsock, line, (size_t)n);
-        close(dsock);
-    }
+    fabric_client.unregister();
+    page = nullptr;
+    fabric_client.close();
     return finish(rc);
 }
