@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(256) kv_transfer_kernel(const KvTransferParams
             const int layer = rem >> 1, kv = rem & 1;
             const int sb = __ldg(p.src_blocks + pair), db = __ldg(p.dst_blocks + pair);
             if ((p.src_num_blocks && (unsigned)sb >= (unsigned)p.src_num_blocks) || (p.dst_num_blocks && (unsigned)db >= (unsigned)p.dst_num_blocks)) {
-                if (tid == 0) set_status(p.status, SKY_STATUS_BAD_INDEX, (unsigned)pair);    // same verdict in every thread
+                if (tid == 0) set_status(p.status, SKY_STATUS_BAD_INDEX, (unsigned)pair);    // same decision in every thread
                 continue;
             }
             const __nv_bfloat16* src = p.src_pool + (long long)sb * p.src_block_stride + (long long)layer * p.src_layer_stride +

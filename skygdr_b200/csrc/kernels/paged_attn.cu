@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
     bool failed = false;
     for (int j = 0; j < my_n; ++j) {
         const int s = j % STAGES;
-        // warp-uniform verdict: the shuffles below need every lane on the same path
+        // warp-uniform decision: the shuffles below need every lane on the same path
         if (!__all_sync(0xffffffffu, mbar_wait(bar + s, (j / STAGES) & 1))) { failed = true; break; }
         const unsigned char* kpage = ring + s * SLOT_BYTES;
         const unsigned char* vpage = kpage + PAGE_BYTES;

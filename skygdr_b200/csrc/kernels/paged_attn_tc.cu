@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tc_kernel(const __gr
             for (int g = 0; g < G; ++g) {
                 const float tm = fmaxf(fmaxf(xch[i & 1][0][g], xch[i & 1][1][g]), fmaxf(xch[i & 1][2][g], xch[i & 1][3][g]));
                 alpha[g] = 1.0f;
-                if (tm > m_ref[g] + RESCALE_THRESHOLD || m_ref[g] == -INFINITY) {      // same verdict in every thread
+                if (tm > m_ref[g] + RESCALE_THRESHOLD || m_ref[g] == -INFINITY) {      // same decision in every thread
                     alpha[g] = m_ref[g] == -INFINITY ? 0.f : exp2f(m_ref[g] - tm);
                     m_ref[g] = tm;
                     rescale = true;

@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
             pf_softmax_bar();                                            // both halves of every row have posted their maxima
             tmax = fmaxf(tmax, xch[par][wg ^ 1][r]);
             float alpha = 1.0f;
-            const bool raise = tmax > m_ref + PF_RESCALE || m_ref == -INFINITY;        // same verdict in both threads of a row
+            const bool raise = tmax > m_ref + PF_RESCALE || m_ref == -INFINITY;        // same decision in both threads of a row
             if (raise) {
                 alpha = m_ref == -INFINITY ? 0.f : exp2f(m_ref - tmax);
                 m_ref = tmax;
