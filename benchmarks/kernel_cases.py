@@ -71,7 +71,7 @@ def main():
     ap.add_argument("--op", default="axpy")
     ap.add_argument("--rows", type=int, default=16)
     ap.add_argument("--no-flush", action="store_true")
-    ap.add_argument("--impl", default="simt", choices=["simt", "tc", "tc1", "tc3", "tcp", "sdpa"])
+    ap.add_argument("--impl", default="simt", choices=["simt", "tc", "tc1", "tc3", "tc2v3", "tc2v4", "tc2v5", "tc2v6", "tcp", "sdpa"])
     a = ap.parse_args()
     dev = "cuda"
     hbm, tf, src = peaks()
@@ -98,7 +98,7 @@ def main():
             fn = lambda: torch.nn.functional.scaled_dot_product_attention(qs, k, v, is_causal=True, enable_gqa=True)
             status = "library"
         else:
-            attn = ops.PrefillAttention(dev, two_tiles={"tc1": False, "tc3": 2}.get(a.impl, True))   # tc1: one query tile per CTA; tc3: 64-key steps
+            attn = ops.PrefillAttention(dev, two_tiles={"tc1": False, "tc3": 2, "tc2v3": 3, "tc2v4": 4, "tc2v5": 5, "tc2v6": 6}.get(a.impl, True))   # tc1: one query tile per CTA; tc3: 64-key steps; tc2vN: variants 3-6 of the two-tile kernel
             o_ = torch.empty_like(q)
             fn = lambda: attn(q, pool, 0, table, seq_start, n, out=o_)
         ms, best = timed(fn, a.warm, a.iters, flush)

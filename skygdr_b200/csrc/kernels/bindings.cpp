@@ -215,7 +215,7 @@ static void prefill_attn(torch::Tensor q, torch::Tensor kv_layer, torch::Tensor 
     p.block_stride = block_stride; p.kv_stride = kv_stride; p.head_stride = head_stride; p.tok_stride = tok_stride;
     p.n_seqs = (int)block_table.size(0); p.q_heads = (int)q.size(1); p.kv_heads = kv_heads; p.max_blocks = (int)block_table.size(1);
     p.max_len = max_len; p.total_tokens = (int)q.size(0); p.scale = (float)scale;
-    TORCH_CHECK(two_tiles >= 0 && two_tiles <= 2, "variant: 0 one query tile per CTA, 1 two tiles, 2 two tiles with 64-key steps");
+    TORCH_CHECK(two_tiles >= 0 && two_tiles <= 6, "variant: 0 one query tile per CTA, 1 two tiles, 2 two tiles with 64-key steps, 3-6 two tiles with exp2 on the FMA pipe and/or P in TMEM");
     p.two_tiles = two_tiles;
     p.status = status_ptr(status);
     SKY_CUDA_CHECK(launch_prefill_attn_tc(p, pool_rows, cur_stream()));

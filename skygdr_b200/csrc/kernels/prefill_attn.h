@@ -24,7 +24,9 @@ struct PrefillAttnParams {
     int total_tokens;
     float scale;
     int two_tiles;               // 1: two query tiles per CTA working in alternation (prefill_attn_tc2_kernel); 0: one tile per CTA;
-                                 // 2: two tiles with key steps of 64 and double-buffered scores (prefill_attn_tc3_kernel)
+                                 // 2: two tiles with key steps of 64 and double-buffered scores (prefill_attn_tc3_kernel);
+                                 // 3-6: the two-tile kernel with part of the exponentials on the FMA pipe and/or P kept in TMEM
+                                 // (3: 1 of 4 exponentials; 4: P in TMEM; 5: both; 6: 2 of 4 exponentials and P in TMEM)
     LaunchStatus* status;
 };
 

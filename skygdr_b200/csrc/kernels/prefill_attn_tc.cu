@@ -294,16 +294,33 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
 // One warpgroup per query tile, one thread per query row (all 128 scores of a row in registers, no exchange between
 // threads). TMEM: scores of A and B (single-buffered, 128 columns each) and the two accumulators: 512 columns.
 // Shared memory: Q_A, Q_B, a ring of three K/V units, P_A, P_B (single-buffered): 224 KB.
-constexpr int PF2_UNITS = 3;
-constexpr int PF2_TILES_BYTES = PF_TILE_BYTES * (2 + PF2_UNITS + 2);
+constexpr int PF2_TILES_BYTES = PF_TILE_BYTES * 7;
 constexpr int PF2_SMEM = PF2_TILES_BYTES + 256;
 
+// exp2 on the FMA and integer pipes instead of the special-function unit: floor by a round-down add of 1.5 * 2^23, a cubic
+// for 2^frac (largest relative error 1.0e-4, far below bf16's 3.9e-3), the integer part added to the exponent field.
+// Arguments below -126 return 2^-126 (about 1e-38) instead of 0, which vanishes in a bf16 P and in the row sum.
+__device__ __forceinline__ float pf_exp2_poly(float x) {
+    x = fmaxf(x, -126.0f);
+    float t;
+    asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(t) : "f"(x), "f"(12582912.0f));
+    const float f = x - (t - 12582912.0f);
+    const float pl = fmaf(fmaf(fmaf(0.07826747000217438f, f, 0.22630836069583893f), f, 0.6954241991043091f), f, 1.0f);
+    return __uint_as_float(__float_as_uint(pl) + (__float_as_uint(t) << 23));
+}
+
+// POLY: how many of every four exponentials take pf_exp2_poly (0 = all on the special-function unit, as measured).
+// PTMEM: P is written as packed bf16 over the first 64 columns of its own score buffer in TMEM (lane = query row, two
+// keys per column) and the P.V MMA takes its A operand from there; the 64 KB of P tiles in shared memory become two more
+// ring units. Neither option has run on a GPU yet; <0, false> is the measured kernel.
+template <int POLY, bool PTMEM>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc2_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                                           const __grid_constant__ CUtensorMap tmap_kv, const PrefillAttnParams p) {
+    constexpr int PF2_UNITS = PTMEM ? 5 : 3;
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char* q_sm = smem;                                        // Q_A, Q_B
     unsigned char* ring = smem + 2 * PF_TILE_BYTES;
-    unsigned char* p_sm = ring + PF2_UNITS * PF_TILE_BYTES;            // P_A, P_B
+    unsigned char* p_sm = ring + PF2_UNITS * PF_TILE_BYTES;            // P_A, P_B (not used with PTMEM: the ring ends where the barriers start)
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PF2_TILES_BYTES);
     uint64_t* full_bar = bars;                        // [PF2_UNITS]
     uint64_t* empty_bar = bars + PF2_UNITS;           // [PF2_UNITS]
@@ -403,9 +420,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc2_kernel(const _
                 const uint32_t v_addr = smem_u32(ring + s * PF_TILE_BYTES), p_addr = smem_u32(p_sm + x * PF_TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    const uint64_t a = umma_desc_k_sw128(p_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
                     const uint64_t b = umma_desc_mn_sw128(v_addr + k * 2048, PF_HALF, 1024);
-                    tc_mma_f16(tmem_base + 256 + x * 128, a, b, idesc_o, (j | k) ? 1u : 0u);
+                    if constexpr (PTMEM) {                              // 16 keys of P = 8 columns of packed bf16 in the score buffer
+                        tc_mma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + k * 8, b, idesc_o, (j | k) ? 1u : 0u);
+                    } else {
+                        const uint64_t a = umma_desc_k_sw128(p_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
+                        tc_mma_f16(tmem_base + 256 + x * 128, a, b, idesc_o, (j | k) ? 1u : 0u);
+                    }
                 }
                 const bool last_user = x == 1 || j >= nkt_x[1];
                 if (last_user) tc_commit(&empty_bar[s]);
@@ -487,22 +508,50 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc2_kernel(const _
             l_sum *= alpha;
             const float neg_m = -m_ref;
             float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+            if constexpr (!PTMEM) {
 #pragma unroll
-            for (int c = 0; c < 128; c += 8) {
-                float e[8];
+                for (int c = 0; c < 128; c += 8) {
+                    float e[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) e[i] = exp2f(fmaf(__uint_as_float(sc[c + i]), qs, neg_m));
-                s0 += e[0] + e[4]; s1 += e[1] + e[5]; s2 += e[2] + e[6]; s3 += e[3] + e[7];
-                uint32_t packed[4];
+                    for (int i = 0; i < 8; ++i) {
+                        const float a = fmaf(__uint_as_float(sc[c + i]), qs, neg_m);
+                        e[i] = (i & 3) < POLY ? pf_exp2_poly(a) : exp2f(a);
+                    }
+                    s0 += e[0] + e[4]; s1 += e[1] + e[5]; s2 += e[2] + e[6]; s3 += e[3] + e[7];
+                    uint32_t packed[4];
 #pragma unroll
-                for (int i = 0; i < 8; i += 2) {
-                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(e[i], e[i + 1]);
-                    packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+                    for (int i = 0; i < 8; i += 2) {
+                        const __nv_bfloat162 b2 = __floats2bfloat162_rn(e[i], e[i + 1]);
+                        packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+                    }
+                    *reinterpret_cast<uint4*>(prow + (c >> 6) * PF_HALF + sw128_off(r, c & 63)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 }
-                *reinterpret_cast<uint4*>(prow + (c >> 6) * PF_HALF + sw128_off(r, c & 63)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                l_sum += (s0 + s1) + (s2 + s3);
+                fence_proxy_async();
+            } else {
+                // every lane of the warp has its 128 scores in registers (the load above was warp-wide and waited for), and the
+                // next score MMA of this tile is issued only after the P.V that reads these columns: the buffer is ours
+#pragma unroll
+                for (int c0 = 0; c0 < 128; c0 += 32) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        float e[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float a = fmaf(__uint_as_float(sc[c0 + c + i]), qs, neg_m);
+                            e[i] = i < POLY ? pf_exp2_poly(a) : exp2f(a);
+                        }
+                        s0 += e[0]; s1 += e[1]; s2 += e[2]; s3 += e[3];
+                        const __nv_bfloat162 lo = __floats2bfloat162_rn(e[0], e[1]), hi = __floats2bfloat162_rn(e[2], e[3]);
+                        pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&lo);
+                        pk[(c >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+                    }
+                    tmem_st_x16(tm_s + lane_off + (c0 >> 1), pk);
+                }
+                l_sum += (s0 + s1) + (s2 + s3);
+                tc_wait_st();
             }
-            l_sum += (s0 + s1) + (s2 + s3);
-            fence_proxy_async();
             tc_fence_before();
             mbar_arrive(&p_ready[x]);
         }
@@ -543,6 +592,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc2_kernel(const _
 // Barriers per query tile x: s_ready[x][t&1], p_ready[x][t&1], o_done[x][t&1], one completion each per step of that parity.
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc3_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                                           const __grid_constant__ CUtensorMap tmap_kv, const PrefillAttnParams p) {
+    constexpr int PF2_UNITS = 3;
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char* q_sm = smem;                                        // Q_A, Q_B
     unsigned char* ring = smem + 2 * PF_TILE_BYTES;
@@ -805,6 +855,14 @@ bool pf_make_tmap(CUtensorMap* m, const void* base, long long mid, long long out
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+template <int POLY, bool PTMEM>
+cudaError_t pf_launch_tc2(dim3 grid, const CUtensorMap& tq, const CUtensorMap& tkv, const PrefillAttnParams& p, cudaStream_t stream) {
+    static unsigned long long attr_mask = 0;             // one per instantiation
+    if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(prefill_attn_tc2_kernel<POLY, PTMEM>), PF2_SMEM, &attr_mask); e != cudaSuccess) return e;
+    prefill_attn_tc2_kernel<POLY, PTMEM><<<grid, PF_THREADS, PF2_SMEM, stream>>>(tq, tkv, p);
+    return cudaGetLastError();
+}
+
 }  // namespace
 
 cudaError_t launch_prefill_attn_tc(const PrefillAttnParams& p, long long pool_rows, cudaStream_t stream) {
@@ -827,12 +885,16 @@ cudaError_t launch_prefill_attn_tc(const PrefillAttnParams& p, long long pool_ro
         return cudaGetLastError();
     }
     if (p.two_tiles) {
-        static unsigned long long attr_mask2 = 0;
-        if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(prefill_attn_tc2_kernel), PF2_SMEM, &attr_mask2); e != cudaSuccess) return e;
         const int q_tiles = (p.max_len + PF_TILE - 1) / PF_TILE;
-        dim3 grid(p.q_heads, (q_tiles + 1) / 2, p.n_seqs);
-        prefill_attn_tc2_kernel<<<grid, PF_THREADS, PF2_SMEM, stream>>>(tq, tkv, p);
-        return cudaGetLastError();
+        const dim3 grid(p.q_heads, (q_tiles + 1) / 2, p.n_seqs);
+        switch (p.two_tiles) {                           // 1 is the measured kernel; 3-6 have not run on a GPU yet
+            case 1: return pf_launch_tc2<0, false>(grid, tq, tkv, p, stream);
+            case 3: return pf_launch_tc2<1, false>(grid, tq, tkv, p, stream);
+            case 4: return pf_launch_tc2<0, true>(grid, tq, tkv, p, stream);
+            case 5: return pf_launch_tc2<1, true>(grid, tq, tkv, p, stream);
+            case 6: return pf_launch_tc2<2, true>(grid, tq, tkv, p, stream);
+            default: return cudaErrorInvalidValue;
+        }
     }
     static unsigned long long attr_mask = 0;
     if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(prefill_attn_tc_kernel), PF_SMEM, &attr_mask); e != cudaSuccess) return e;

@@ -58,7 +58,9 @@ class PrefillAttention:
     def __init__(self, device, two_tiles=True):
         """two_tiles: True = two query tiles per CTA working in alternation with the tensor core (the faster variant); False = one
         query tile per CTA with two softmax warpgroups per tile; 2 = two tiles with key steps of 64 and double-buffered scores
-        (built for the next measurement round: compiled, not yet run on a GPU)."""
+        (compiled, not yet run on a GPU); 3-6 = the two-tile kernel with one of every four exponentials computed by a cubic on
+        the FMA pipe (3), with P written to TMEM over its own scores and taken from there by the P.V MMA (4), both (5), or two
+        of every four exponentials and P in TMEM (6). 3-6 are compiled, not yet run on a GPU."""
         self._C = load()
         self.device = torch.device(device)
         self.status = new_status(self.device)

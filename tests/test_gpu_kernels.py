@@ -254,7 +254,12 @@ def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
     assert int(attn.counters.abs().sum()) == 0
 
 
-@pytest.mark.parametrize("two_tiles", [True, False] + ([2] if os.environ.get("SKYGDR_TEST_PREFILL_64") == "1" else []))   # 2: not yet run on a GPU
+# variants 2 (64-key steps) and 3-6 (exp2 on the FMA pipe, P in TMEM) have not run on a GPU yet: opt in one at a time
+_PREFILL_EXTRA = ([2] if os.environ.get("SKYGDR_TEST_PREFILL_64") == "1" else []) + \
+    [int(v) for v in os.environ.get("SKYGDR_TEST_PREFILL_VARIANTS", "").split(",") if v]
+
+
+@pytest.mark.parametrize("two_tiles", [True, False] + _PREFILL_EXTRA)
 @pytest.mark.parametrize("layout", ["hnd", "nhd"])
 @pytest.mark.parametrize("kv_heads,q_heads", [(8, 32), (2, 4), (1, 1)])
 def test_prefill_attention_matches_reference(ops, layout, kv_heads, q_heads, two_tiles):

@@ -124,3 +124,26 @@ def test_prefill_oracle_matches_torch_sdpa(layout):
         want = torch.nn.functional.scaled_dot_product_attention(q[o:o + n].transpose(0, 1)[None], k[None], v[None], is_causal=True, enable_gqa=True)
         assert torch.allclose(out[o:o + n], want[0].transpose(0, 1), atol=1e-5)
         o += n
+
+
+def test_exp2_cubic_of_the_prefill_kernel_is_accurate_enough_for_bf16():
+    """The prefill kernel's opt-in exp2 on the FMA pipe (pf_exp2_poly in prefill_attn_tc.cu): the same arithmetic in fp32 on the
+    CPU, with the coefficients read from the kernel source, stays within 2e-4 of 2^x over the range the softmax feeds it."""
+    import pathlib
+    import re
+
+    src = (pathlib.Path(__file__).resolve().parent.parent / "skygdr_b200" / "csrc" / "kernels" / "prefill_attn_tc.cu").read_text()
+    body = src[src.index("float pf_exp2_poly(float x)"):]
+    body = body[:body.index("\n}\n")]
+    c3, c2, c1 = (float(v) for v in re.search(r"fmaf\(fmaf\(fmaf\(([0-9.]+)f, f, ([0-9.]+)f\), f, ([0-9.]+)f\), f, 1\.0f\)", body).groups())
+    assert "12582912.0f" in body and "<< 23" in body and "-126.0f" in body
+    x = torch.cat([torch.linspace(-126.0, 8.0, 200001), torch.tensor([-1e30, -float("inf"), 0.0, -0.0, 1.0, -1.0])]).float()
+    xc = x.clamp(min=-126.0)
+    fl = torch.floor(xc)                               # add.rm of 1.5 * 2^23, minus the same constant
+    f = xc - fl
+    pl = ((c3 * f + c2) * f + c1) * f + 1.0
+    got = (pl.view(torch.int32) + (fl.to(torch.int32) << 23)).view(torch.float32)
+    want = torch.exp2(xc.double())
+    rel = ((got.double() - want) / want).abs().max().item()
+    assert rel < 2e-4, rel
+    assert got[-6].item() == got[-5].item() == 2.0 ** -126      # masked scores: 1e-38, nothing in a bf16 row
