@@ -46,6 +46,8 @@ def parse():
     ap.add_argument("--tp-collective", default="rs_ag", choices=["rs_ag", "oneshot"],
                     help="tensor-parallel form: reduce-scatter + all-gather (default) or the one-shot all-reduce")
     ap.add_argument("--attn-chunk", type=int, default=1024)
+    ap.add_argument("--fuse-norm", action="store_true",
+                    help="1 GPU: RMSNorms folded into the GEMM epilogues, 6 kernels per layer instead of 8 (not yet run on a GPU)")
     ap.add_argument("--profile-step", action="store_true", help="also print per-kernel-kind times of one eager step (tensor-parallel engine)")
     return ap.parse_args()
 
@@ -89,7 +91,8 @@ def main() -> int:
     total_steps = 2 * (args.steps + args.warmup) + 8
     max_ctx = int(ctx.max()) + total_steps + 1
     eng, table = build_decode_engine(cfg, dev, rank, world, ctx, total_steps, seed=args.seed, kv_init="normal",
-                                     attn_chunk=args.attn_chunk, attn_impl=args.attn_impl, collective=args.tp_collective)
+                                     attn_chunk=args.attn_chunk, attn_impl=args.attn_impl, collective=args.tp_collective,
+                                     fuse_norm=args.fuse_norm)
 
     ids0 = torch.randint(0, cfg.vocab, (batch,), generator=g).int()
     eng.set_batch(ids0.to(dev), ctx.int().to(dev), table.to(dev))
@@ -147,6 +150,7 @@ def main() -> int:
             "config": {"model": cfg.name if args.layers == 36 else f"{cfg.name}-{args.layers}L", "global_batch": batch,
                        "seq_len": f"context uniform {args.ctx_lo}-{args.ctx_hi}, 1 new token per step",
                        "parallelism": f"tp{world}", "kv_block_tokens": 16, "sampling": "greedy", "attention": f"{args.attn_impl}, {args.attn_chunk}-token splits",
+                       "norms": "folded into the GEMM epilogues" if args.fuse_norm else "norm kernels",
                        "l2": "inputs larger than L2: each step streams %.1f GB of weights and KV per GPU" % (step_bytes / 1e9)},
             "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": sess.h2d_bytes_per_step, "d2h_bytes_per_step": sess.d2h_bytes_per_step},

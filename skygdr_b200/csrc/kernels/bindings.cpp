@@ -302,9 +302,17 @@ static void silu_mul(torch::Tensor gate_up, torch::Tensor out) {
     const int ffn = (int)out.size(-1), rows = (int)(out.numel() / ffn);
     SKY_CUDA_CHECK(launch_silu_mul(bf16_ptr(gate_up), bf16_mut(out), rows, ffn, cur_stream()));
 }
-static void embedding(torch::Tensor ids, torch::Tensor table, torch::Tensor out) {
+static void embedding(torch::Tensor ids, torch::Tensor table, torch::Tensor out, c10::optional<torch::Tensor> row_ss) {
     c10::cuda::CUDAGuard g(table.device());
-    SKY_CUDA_CHECK(launch_embedding(i32_ptr(ids), bf16_ptr(table), bf16_mut(out), (int)ids.numel(), (int)table.size(1), (int)table.size(0), cur_stream()));
+    float* ss = nullptr;
+    int slots = 0, pitch = 0;
+    if (row_ss.has_value()) {
+        TORCH_CHECK(row_ss->dim() == 2 && row_ss->is_contiguous() && row_ss->scalar_type() == torch::kFloat32 && row_ss->size(1) >= ids.numel(),
+                    "row_ss: fp32 [slots][>= tokens]");
+        ss = row_ss->data_ptr<float>(); slots = (int)row_ss->size(0); pitch = (int)row_ss->size(1);
+    }
+    SKY_CUDA_CHECK(launch_embedding(i32_ptr(ids), bf16_ptr(table), bf16_mut(out), (int)ids.numel(), (int)table.size(1), (int)table.size(0), cur_stream(),
+                                    ss, slots, pitch));
 }
 static void argmax(torch::Tensor logits, torch::Tensor out) {
     c10::cuda::CUDAGuard g(logits.device());
@@ -313,8 +321,10 @@ static void argmax(torch::Tensor logits, torch::Tensor out) {
 }
 
 // ---- GEMM ----
+// ss_in / ss_out: fp32 vectors of at least M entries (see GemmNormFuse); residual: y is the residual stream, updated in place.
 static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, bool gated, c10::optional<torch::Tensor> workspace,
-                 c10::optional<torch::Tensor> counters, torch::Tensor status, int ntok) {
+                 c10::optional<torch::Tensor> counters, torch::Tensor status, int ntok, c10::optional<torch::Tensor> ss_in, double eps,
+                 bool residual, c10::optional<torch::Tensor> ss_out) {
     c10::cuda::CUDAGuard g(x.device());
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1, "row-major 2-D tensors");
     GemmParams p;
@@ -333,6 +343,17 @@ static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, 
         p.counters = reinterpret_cast<unsigned int*>(counters->data_ptr());
     }
     p.status = status_ptr(status);
+    if (ss_in.has_value()) {
+        TORCH_CHECK(ss_in->scalar_type() == torch::kFloat32 && ss_in->is_contiguous() && ss_in->numel() >= p.M, "ss_in: fp32, one entry per row of x");
+        p.nf.row_ss_in = ss_in->data_ptr<float>(); p.nf.eps = (float)eps;
+    }
+    if (ss_out.has_value()) {
+        TORCH_CHECK(residual && ss_out->scalar_type() == torch::kFloat32 && ss_out->is_contiguous() && ss_out->numel() >= p.M,
+                    "ss_out: fp32, one entry per row, only with residual");
+        p.nf.row_ss_out = ss_out->data_ptr<float>();
+    }
+    TORCH_CHECK(!residual || !gated, "the residual add follows a plain projection");
+    p.nf.residual = residual ? 1 : 0;
     SKY_CUDA_CHECK(launch_gemm(p, cur_stream()));
 }
 
@@ -482,9 +503,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("rmsnorm", &rmsnorm);
     m.def("rope_append", &rope_append);
     m.def("silu_mul", &silu_mul);
-    m.def("embedding", &embedding);
+    m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("out"), py::arg("row_ss") = py::none());
     m.def("argmax", &argmax);
-    m.def("gemm", &gemm);
+    m.def("gemm", &gemm, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("splits"), py::arg("gated"), py::arg("workspace"), py::arg("counters"),
+          py::arg("status"), py::arg("ntok"), py::arg("ss_in") = py::none(), py::arg("eps") = 1e-6, py::arg("residual") = false,
+          py::arg("ss_out") = py::none());
     m.def("gemm_tp", &gemm_tp);
     m.def("tp_norm", &tp_norm, py::arg("rs_buf"), py::arg("rs_counter"), py::arg("rs_seq"), py::arg("resid"), py::arg("w"), py::arg("ag_dst"),
           py::arg("ag_counter"), py::arg("rank"), py::arg("eps"), py::arg("timeout_ns"), py::arg("status"), py::arg("rs_world") = 0);

@@ -31,7 +31,26 @@ bool pdl_enabled() {
 // Writes a chunk of 16 token rows x 128 columns. Thread r (0..127 of the epilogue warps) holds column n0+r of the 16
 // rows. The values are staged through shared memory so that each row leaves as 16-byte pieces, 256 contiguous bytes
 // per row, instead of one 2-byte store per element: that matters most when the destination is a peer over NVLink.
-__device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16* stage, int t_base, int n0, int r, const float* vals) {
+__device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16* stage, int t_base, int n0, int r, float* vals) {
+    if (p.nf.residual) {
+        // y is the residual stream: add it (column n0+r of 16 rows; the 128 threads read 256 contiguous bytes per row) and
+        // hand the sum of squares of the rounded results to the next norm
+        const int n = n0 + r;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = t_base + j;
+            float sq = 0.f;
+            if (t < p.M && n < p.N) {
+                vals[j] += __bfloat162float(p.y[(long long)t * p.ldy + n]);
+                const float q = __bfloat162float(__float2bfloat16(vals[j]));
+                sq = q * q;
+            }
+            if (p.nf.row_ss_out) {                                   // uniform over the warp
+                for (int o = 16; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if ((r & 31) == 0 && t < p.M) atomicAdd(p.nf.row_ss_out + t, sq);
+            }
+        }
+    }
 #pragma unroll
     for (int j = 0; j < 16; ++j) stage[j * 128 + r] = __float2bfloat16(vals[j]);
     asm volatile("bar.sync 3, 128;" ::: "memory");
@@ -66,6 +85,15 @@ __device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16
         }
     }
     asm volatile("bar.sync 3, 128;" ::: "memory");
+}
+
+// Factors of the folded RMSNorm for 16 token rows starting at t_base (1 when the GEMM has no norm in front of it).
+__device__ __forceinline__ void row_scales16(const GemmParams& p, int t_base, float* inv) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int t = t_base + j;
+        inv[j] = (p.nf.row_ss_in && t < p.M) ? rsqrtf(__ldcg(p.nf.row_ss_in + t) / (float)p.K + p.nf.eps) : 1.0f;
+    }
 }
 
 constexpr int GEMM_THREADS = 192;
@@ -217,11 +245,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 for (int i = 0; i < 16; ++i) { v[i] = 0; u[i] = 0; }
             }
             if (direct) {
-                float vals[16];
+                float vals[16], inv[16];
+                row_scales16(p, t0 + c, inv);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    float val = __uint_as_float(v[i]);
-                    if (GATED) { const float up = __uint_as_float(u[i]); val = val / (1.0f + __expf(-val)) * up; }
+                    float val = __uint_as_float(v[i]) * inv[i];
+                    if (GATED) { const float up = __uint_as_float(u[i]) * inv[i]; val = val / (1.0f + __expf(-val)) * up; }
                     vals[i] = val;
                 }
                 store_chunk16(p, stage, t0 + c, n0, r, vals);
@@ -265,6 +294,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 #pragma unroll
                             for (int j = 0; j < 16; ++j) { g[j] += a[j]; if (GATED) up[j] += b[j]; }
                         }
+                        float inv[16];
+                        row_scales16(p, t0 + c0, inv);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) { g[j] *= inv[j]; if (GATED) up[j] *= inv[j]; }
                         if (GATED) {
 #pragma unroll
                             for (int j = 0; j < 16; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * up[j];
@@ -358,6 +391,8 @@ size_t gemm_counter_count(int M, int N, bool gated, int ntok) {
 cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream) {
     if (p.K % BK || p.M <= 0 || p.N <= 0 || p.splits < 1 || p.splits > p.K / BK) return cudaErrorInvalidValue;
     if (p.splits > 1 && (!p.workspace || !p.counters)) return cudaErrorInvalidValue;
+    if (p.nf.residual && (p.gated || p.rs.world > 0)) return cudaErrorInvalidValue;      // the in-place add follows a plain, local projection
+    if (p.nf.row_ss_out && !p.nf.residual) return cudaErrorInvalidValue;
     const int ntok = p.ntok > 0 ? p.ntok : gemm_pick_ntok(p.M, p.gated != 0);
     if (ntok != 16 && ntok != 32 && ntok != 64 && ntok != 128 && ntok != 256) return cudaErrorInvalidValue;
     CUtensorMap tw, tx;

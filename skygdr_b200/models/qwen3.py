@@ -103,6 +103,23 @@ class Qwen3Weights:
         gen.manual_seed(seed * 1000003 + 900003)
         self.final_norm = (1.0 + 0.1 * torch.randn(H, generator=gen, device=device)).to(torch.bfloat16)
 
+    def fold_norms(self) -> "Qwen3Weights":
+        """Multiplies the gains of the three RMSNorms that feed a projection (ln1 -> qkv, ln2 -> gate_up, final norm -> lm_head)
+        into that projection's columns, in place, and sets the gains to one. The model is the same function of its inputs up
+        to bf16 rounding of the products; what is left of each norm is one factor per token, which the GEMM epilogues can apply
+        (``Qwen3Decoder(fuse_norm=True)``). Every other path keeps working on the folded weights, with gains of one."""
+        if getattr(self, "norms_folded", False):
+            return self
+        for w in self.layers:
+            w.qkv.mul_(w.ln1[None, :])
+            w.gate_up.mul_(w.ln2[None, :])
+            w.ln1.fill_(1.0)
+            w.ln2.fill_(1.0)
+        self.lm_head.mul_(self.final_norm[None, :])
+        self.final_norm.fill_(1.0)
+        self.norms_folded = True
+        return self
+
     def nbytes(self) -> int:
         n = self.embed.numel() + self.lm_head.numel() + self.final_norm.numel()
         for w in self.layers:
@@ -114,8 +131,16 @@ class Qwen3Decoder:
     """Single-GPU decode engine: fixed-capacity batch, preallocated activations, optional CUDA graph."""
 
     def __init__(self, cfg: Qwen3Config, weights: Qwen3Weights, pool: PagedKVPool, max_batch: int, max_ctx: int,
-                 attn_chunk: int = 1024, attn_impl: str = "tc", prefill_attn: str = "tc"):
+                 attn_chunk: int = 1024, attn_impl: str = "tc", prefill_attn: str = "tc", fuse_norm: bool = False):
+        """fuse_norm: no norm kernels in the decode step. The O and down projections add their result to the residual stream in
+        their epilogue and leave each row's sum of squares behind; the QKV, gate/up and lm_head GEMMs read the residual stream
+        as it is and scale their output rows by rsqrt(mean square + eps). Needs ``weights.fold_norms()`` (done here if it has
+        not been). 6 kernels per layer instead of 8. Compiled and checked against the model's arithmetic on the CPU; not yet
+        run on a GPU, so it is off by default."""
         assert pool.layout == "hnd" and prefill_attn in ("tc", "sdpa")
+        self.fuse_norm = fuse_norm
+        if fuse_norm:
+            weights.fold_norms()
         self.cfg, self.w, self.pool = cfg, weights, pool
         self.prefill_attn = prefill_attn              # default of prefill(): this package's kernel or the library arm
         self._prefill_attn = None
@@ -143,6 +168,10 @@ class Qwen3Decoder:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.graph_batch = 0
         self.kernels_per_step = 1 + 8 * cfg.layers + 3   # embedding, 8 per layer, final norm, lm_head, argmax
+        if fuse_norm:
+            # one slot per norm of the step: ln1 and ln2 of every layer, then the final norm
+            self.row_ss = torch.zeros((2 * cfg.layers + 1, B), dtype=torch.float32, device=dev)
+            self.kernels_per_step = 1 + 6 * cfg.layers + 2
 
     # ---- state ----
     def set_batch(self, ids: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor) -> None:
@@ -155,7 +184,25 @@ class Qwen3Decoder:
         self.block_table[:b, :block_table.shape[1]].copy_(block_table)
 
     # ---- one decode step for the first `b` slots ----
+    def _step_fused_norm(self, b: int, max_ctx: int) -> None:
+        cfg, w, ss = self.cfg, self.w, self.row_ss
+        resid = self.resid[:b]
+        qkv, q, ao, act = self.qkv[:b], self.q[:b], self.attn_out[:b], self.act[:b]
+        pos, ctx, table = self.positions[:b], self.ctx_lens[:b], self.block_table[:b]
+        ops.embedding(self.ids[:b], w.embed, out=resid, row_ss=ss)           # slot 0 filled, the others zeroed
+        for li, lw in enumerate(w.layers):
+            ops.gemm(resid, lw.qkv, out=qkv, ss_in=ss[2 * li], eps=cfg.eps)
+            ops.rope_append(qkv, lw.q_norm, lw.k_norm, self.pool, li, self.inv_freq, table, pos, cfg.q_heads, cfg.eps, q_out=q)
+            self.attn(q, self.pool, li, table, ctx, max_ctx=max_ctx, out=ao)
+            ops.gemm(ao.view(b, -1), lw.o, out=resid, residual=True, ss_out=ss[2 * li + 1])
+            ops.gemm(resid, lw.gate_up, out=act, gated=True, ss_in=ss[2 * li + 1], eps=cfg.eps)
+            ops.gemm(act, lw.down, out=resid, residual=True, ss_out=ss[2 * li + 2])
+        ops.gemm(resid, w.lm_head, out=self.logits[:b], ss_in=ss[2 * cfg.layers], eps=cfg.eps)
+        ops.argmax(self.logits[:b], out=self.next_ids[:b])
+
     def _step(self, b: int, max_ctx: int) -> None:
+        if self.fuse_norm:
+            return self._step_fused_norm(b, max_ctx)
         cfg, w = self.cfg, self.w
         resid, xn, h = self.resid[:b], self.xn[:b], self.h[:b]
         qkv, q, ao, act = self.qkv[:b], self.q[:b], self.attn_out[:b], self.act[:b]

@@ -109,8 +109,14 @@ def workspace_for(device) -> GemmWorkspace:
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, gated: bool = False,
-         splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, ntok: int = 0) -> torch.Tensor:
-    """y = x @ w.T (w is [N][K]); gated: w is [2N][K] and y = silu(x @ w[:N].T) * (x @ w[N:].T)."""
+         splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, ntok: int = 0, ss_in: Optional[torch.Tensor] = None,
+         eps: float = 1e-6, residual: bool = False, ss_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ w.T (w is [N][K]); gated: w is [2N][K] and y = silu(x @ w[:N].T) * (x @ w[N:].T).
+
+    RMSNorm folded into the epilogues (the gain is expected inside ``w`` already, see ``Qwen3Weights.fold_norms``):
+    ``ss_in`` (fp32, one sum of squares per row of x) scales output row t by rsqrt(ss_in[t] / K + eps); ``residual`` makes ``out``
+    the residual stream, updated in place (out += x @ w.T), and ``ss_out`` then receives the sums of squares of the new rows
+    (added to what it holds: zero it first)."""
     C = load()
     M, K = x.shape
     N = w.shape[0] // 2 if gated else w.shape[0]
@@ -124,7 +130,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, g
     ws = ws or workspace_for(x.device)
     if splits > 1:
         ws.ensure(C.gemm_workspace_floats(M, N, splits, gated, ntok), C.gemm_counter_count(M, N, gated, ntok))
-        C.gemm(x, w, out, splits, gated, ws.ws, ws.counters, ws.status, ntok)
+        C.gemm(x, w, out, splits, gated, ws.ws, ws.counters, ws.status, ntok, ss_in, eps, residual, ss_out)
     else:
-        C.gemm(x, w, out, 1, gated, None, None, ws.status, ntok)
+        C.gemm(x, w, out, 1, gated, None, None, ws.status, ntok, ss_in, eps, residual, ss_out)
     return out

@@ -46,10 +46,12 @@ def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch
     return out
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, row_ss: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gathers table rows. ``row_ss`` (fp32 [slots][>= tokens]): slot 0 receives every gathered row's sum of squares and the other
+    slots are zeroed, ready for the GEMM epilogues that accumulate into them."""
     if out is None:
         out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
-    load().embedding(ids, table, out)
+    load().embedding(ids, table, out, row_ss)
     return out
 
 

@@ -266,7 +266,7 @@ def _bytes_per_step(cfg: Qwen3Config, w: Qwen3Weights, ctx: torch.Tensor, kv_hea
 
 def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world: int, ctx: torch.Tensor, extra_tokens: int,
                         seed: int = 0, kv_init: str = "normal", attn_chunk: int = 1024, attn_impl: str = "tc",
-                        collective: str = "rs_ag"):
+                        collective: str = "rs_ag", fuse_norm: bool = False):
     """Weights shard, KV pool sized for ``ctx`` (+ ``extra_tokens`` of growth per sequence), randomly permuted block
     table, and the decode engine for this rank. Every rank passes the same ``ctx`` and ``seed``."""
     batch = ctx.numel()
@@ -290,7 +290,8 @@ def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world
         table[i, :nb] = perm[o:o + nb]
         o += nb
     if world == 1:
-        eng = Qwen3Decoder(cfg, weights, pool, batch, max_ctx, attn_chunk, attn_impl)
+        eng = Qwen3Decoder(cfg, weights, pool, batch, max_ctx, attn_chunk, attn_impl, fuse_norm=fuse_norm)
     else:
+        assert not fuse_norm, "the norm-free step exists for the single-GPU engine (the tensor-parallel norm kernel is also the collective)"
         eng = TPDecoder(cfg, weights, pool, batch, max_ctx, rank, world, attn_chunk, attn_impl=attn_impl, collective=collective)
     return eng, table

@@ -1,18 +1,20 @@
 """Qwen3 decoder on the package's kernels against a plain PyTorch forward of the same weights."""
+import os
+
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
 
 
-def _setup(layers=2, max_batch=4, max_ctx=256, attn_impl="simt", attn_chunk=64):
+def _setup(layers=2, max_batch=4, max_ctx=256, attn_impl="simt", attn_chunk=64, fuse_norm=False):
     from skygdr_b200 import ops
     from skygdr_b200.models import Qwen3Config, Qwen3Decoder, Qwen3Weights
 
     cfg = Qwen3Config.tiny(layers=layers)
     w = Qwen3Weights(cfg, "cuda", seed=1, std=0.05)
     pool = ops.PagedKVPool(cfg.geometry, 64, "hnd")
-    eng = Qwen3Decoder(cfg, w, pool, max_batch=max_batch, max_ctx=max_ctx, attn_chunk=attn_chunk, attn_impl=attn_impl)
+    eng = Qwen3Decoder(cfg, w, pool, max_batch=max_batch, max_ctx=max_ctx, attn_chunk=attn_chunk, attn_impl=attn_impl, fuse_norm=fuse_norm)
     return cfg, w, pool, eng
 
 
@@ -76,6 +78,40 @@ def test_prefill_with_the_native_attention_kernel_matches_reference():
         ref_last = reference_forward(cfg, w, pr)[-1]
         err = (logits[i].float() - ref_last).abs().max() / ref_last.abs().max()
         assert err < 0.05, (i, float(err))
+
+
+@pytest.mark.skipif(os.environ.get("SKYGDR_TEST_FUSED_NORM") != "1", reason="the norm-free decode step has not run on a GPU yet: opt in")
+def test_decode_without_norm_kernels_matches_reference():
+    """fuse_norm: the RMSNorms live in the GEMM epilogues (row factors, residual add, sums of squares). Same checks as the
+    default engine, against the PyTorch forward of the folded weights, eager and as a graph."""
+    from skygdr_b200.models import reference_forward
+
+    cfg, w, pool, eng = _setup(attn_impl="tc", attn_chunk=128, fuse_norm=True)
+    assert w.norms_folded and float(w.layers[0].ln1.float().min()) == 1.0
+    torch.manual_seed(0)
+    seq_lens = [37, 16, 50]
+    prompts = [torch.randint(0, cfg.vocab, (n,), device="cuda") for n in seq_lens]
+    table = _tables(seq_lens, eng.max_blocks)
+    eng.prefill(torch.cat(prompts), seq_lens, table)
+    refs = [reference_forward(cfg, w, p) for p in prompts]
+    ids = torch.stack([r[-1].argmax() for r in refs]).int()
+    seqs = [p.clone() for p in prompts]
+    for step in range(3):
+        pos = torch.tensor([s.numel() for s in seqs], dtype=torch.int32, device="cuda")
+        eng.set_batch(ids, pos, table)
+        eng.step(b=3, max_ctx=128, advance=False)
+        seqs = [torch.cat([s, i.view(1).long()]) for s, i in zip(seqs, ids)]
+        new_ids = []
+        for i in range(3):
+            ref = reference_forward(cfg, w, seqs[i])[-1]
+            err = (eng.logits[i].float() - ref).abs().max() / ref.abs().max()
+            assert err < 0.05, (step, i, float(err))
+            new_ids.append(ref.argmax())
+        ids = torch.stack(new_ids).int()
+    assert eng.check_status() == "OK"
+    # the sums of squares the epilogues left behind are those of the residual stream after the last layer
+    want = eng.resid[:3].float().pow(2).sum(-1)
+    assert torch.allclose(eng.row_ss[2 * cfg.layers, :3], want, rtol=1e-3)
 
 
 def test_graph_replay_equals_eager():

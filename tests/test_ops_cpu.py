@@ -147,3 +147,42 @@ def test_exp2_cubic_of_the_prefill_kernel_is_accurate_enough_for_bf16():
     rel = ((got.double() - want) / want).abs().max().item()
     assert rel < 2e-4, rel
     assert got[-6].item() == got[-5].item() == 2.0 ** -126      # masked scores: 1e-38, nothing in a bf16 row
+
+
+def test_folding_the_norm_gain_into_the_next_projection_keeps_the_function():
+    """What `Qwen3Weights.fold_norms` and the GEMM epilogue options rely on: rmsnorm(x) * g @ W.T equals
+    (x @ (W * g).T) * rsqrt(mean(x^2) + eps) row by row, up to bf16 rounding of the folded weight."""
+    torch.manual_seed(0)
+    M, K, N, eps = 16, 512, 256, 1e-6
+    x = torch.randn(M, K).bfloat16()
+    g = (1.0 + 0.1 * torch.randn(K)).bfloat16()
+    W = (0.02 * torch.randn(N, K)).bfloat16()
+    xf = x.float()
+    inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    ref = ((xf * inv * g.float()).bfloat16().float() @ W.float().T)
+    Wf = (W * g[None, :])                                   # what fold_norms does, in place and in bf16
+    fused = (xf @ Wf.float().T) * inv
+    err = (fused - ref).abs().max() / ref.abs().max()
+    assert err < 0.02, float(err)
+    # the gated form scales gate and up before the SiLU
+    Wg, Wu = (0.02 * torch.randn(N, K)).bfloat16(), (0.02 * torch.randn(N, K)).bfloat16()
+    xn = (xf * inv * g.float()).bfloat16().float()
+    ref_g = torch.nn.functional.silu(xn @ Wg.float().T) * (xn @ Wu.float().T)
+    a, b = (xf @ (Wg * g[None, :]).float().T) * inv, (xf @ (Wu * g[None, :]).float().T) * inv
+    err = (torch.nn.functional.silu(a) * b - ref_g).abs().max() / ref_g.abs().max()
+    assert err < 0.02, float(err)
+
+
+def test_fold_norms_on_cpu_weights_keeps_the_reference_logits():
+    from skygdr_b200.models import Qwen3Config, Qwen3Weights, reference_forward
+
+    cfg = Qwen3Config.tiny(layers=2)
+    w = Qwen3Weights(cfg, "cpu", seed=3, std=0.05)
+    ids = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(1))
+    before = reference_forward(cfg, w, ids)
+    w.fold_norms()
+    assert w.norms_folded and bool((w.layers[1].ln2 == 1).all()) and bool((w.final_norm == 1).all())
+    after = reference_forward(cfg, w, ids)
+    err = (after - before).abs().max() / before.abs().max()
+    assert err < 0.03, float(err)
+    assert w.fold_norms() is w                              # idempotent
