@@ -63,7 +63,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tc_kernel(const __gr
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    // Default order: splits fastest, then KV heads, then sequences. tail_order: KV heads fastest, then sequences, then a slot
+    // index z: slot z < n_splits - 1 is full chunk z, the last slot of the grid is the sequence's last chunk (the partial one,
+    // half a chunk on average), the slots between are empty. The CTAs that run last, alone on their SMs, are then the short ones.
+    const int kvh = p.tail_order ? blockIdx.x : blockIdx.y, b = p.tail_order ? blockIdx.y : blockIdx.z;
+    int split = blockIdx.x;
     // Everything up to pdl_wait() touches only this CTA's shared memory, so it may overlap the previous kernel's tail.
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_UNITS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -75,11 +79,17 @@ __global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tc_kernel(const __gr
     for (int i = threadIdx.x; i < 3 * QP_BYTES / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_sm)[i] = make_uint4(0, 0, 0, 0);
     pdl_wait();
     const int ctx = p.ctx_lens[b];
+    const int n_splits = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
+    if (p.tail_order) {
+        const int z = blockIdx.z;
+        if (z < n_splits - 1) split = z;
+        else if (z == (int)gridDim.z - 1) split = n_splits - 1;
+        else return;
+    }
     const int tok0 = split * p.chunk_tokens;
-    if (tok0 >= ctx) return;
+    if (tok0 >= ctx || ctx <= 0) return;
     const int tok1 = min(ctx, tok0 + p.chunk_tokens);
     const int n_tiles = (tok1 - tok0 + TILE_TOK - 1) / TILE_TOK;
-    const int n_splits = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
     const int* table = p.block_table + (long long)b * p.max_blocks;
 
     if (warp == 5) { tmem_alloc(&tmem_slot, 64); tmem_relinquish(); }
@@ -621,7 +631,9 @@ cudaError_t launch_tc_g(const PagedAttnParams& p, const CUtensorMap& tm, cudaStr
     auto kern = paged_attn_tc_kernel<G>;
     static unsigned long long attr_mask = 0;
     if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), TC_SMEM, &attr_mask); e != cudaSuccess) return e;
-    dim3 grid((p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens, p.kv_heads, p.batch);
+    const int slots = (p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens;
+    if (p.tail_order && (p.batch > 65535 || slots > 65535)) return cudaErrorInvalidValue;
+    const dim3 grid = p.tail_order ? dim3(p.kv_heads, p.batch, slots) : dim3(slots, p.kv_heads, p.batch);
     return launch_pdl(kern, grid, dim3(TC_THREADS), (size_t)TC_SMEM, stream, tm, p);
 }
 

@@ -131,7 +131,8 @@ class Qwen3Decoder:
     """Single-GPU decode engine: fixed-capacity batch, preallocated activations, optional CUDA graph."""
 
     def __init__(self, cfg: Qwen3Config, weights: Qwen3Weights, pool: PagedKVPool, max_batch: int, max_ctx: int,
-                 attn_chunk: int = 1024, attn_impl: str = "tc", prefill_attn: str = "tc", fuse_norm: bool = False):
+                 attn_chunk: int = 1024, attn_impl: str = "tc", prefill_attn: str = "tc", fuse_norm: bool = False,
+                 attn_tail_order: bool = False):
         """fuse_norm: no norm kernels in the decode step. The O and down projections add their result to the residual stream in
         their epilogue and leave each row's sum of squares behind; the QKV, gate/up and lm_head GEMMs read the residual stream
         as it is and scale their output rows by rsqrt(mean square + eps). Needs ``weights.fold_norms()`` (done here if it has
@@ -164,7 +165,7 @@ class Qwen3Decoder:
         self.max_blocks = (max_ctx + 15) // 16
         self.block_table = torch.zeros((B, self.max_blocks), dtype=torch.int32, device=dev)
         self.inv_freq = ops.rope_inv_freq(cfg.rope_theta, dev, cfg.head_dim)
-        self.attn = ops.PagedAttention(dev, B, cfg.q_heads, cfg.kv_heads, max_ctx, attn_chunk, impl=attn_impl)
+        self.attn = ops.PagedAttention(dev, B, cfg.q_heads, cfg.kv_heads, max_ctx, attn_chunk, impl=attn_impl, tail_order=attn_tail_order)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.graph_batch = 0
         self.kernels_per_step = 1 + 8 * cfg.layers + 3   # embedding, 8 per layer, final norm, lm_head, argmax

@@ -14,11 +14,15 @@ from .kv_cache import PagedKVPool
 class PagedAttention:
     """Holds the split-KV scratch (partials, statistics, counters) for a maximum batch and context."""
 
-    def __init__(self, device, max_batch: int, q_heads: int, kv_heads: int, max_ctx: int, chunk_tokens: int = 512, impl: str = "simt"):
+    def __init__(self, device, max_batch: int, q_heads: int, kv_heads: int, max_ctx: int, chunk_tokens: int = 512, impl: str = "simt",
+                 tail_order: bool = False):
         """impl: "simt" (CUDA cores, paged_attn.cu), "tc" (tcgen05 tensor cores, one CTA per (sequence, split, KV head);
         chunk_tokens % 128 == 0) or "tcp" (the same engine as a persistent kernel of two CTAs per SM that walk the work items;
         chunk_tokens <= 1024, batch <= 256; meant for small batches, where it can use 512-token items without paying a CTA
-        start-up per item)."""
+        start-up per item). tail_order ("tc" only): every sequence's last, partial chunk is scheduled after all full chunks, so
+        the CTAs that finish the launch alone on their SMs are short ones (not yet run on a GPU)."""
+        assert not tail_order or impl == "tc"
+        self.tail_order = tail_order
         assert impl in ("simt", "tc", "tcp") and (impl == "simt" or chunk_tokens % 128 == 0)
         assert impl != "tcp" or (chunk_tokens <= 1024 and max_batch <= 256)
         self.impl = impl
@@ -45,7 +49,8 @@ class PagedAttention:
                                   scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]),
                                   self.part_o, self.part_m, self.part_l, self.counters, self.status,
                                   (pool.data.numel() - layer * ls) // 128 if self.impl != "simt" else 0,
-                                  **({"persistent_ctas": self._persistent} if self._persistent else {}))
+                                  **({"persistent_ctas": self._persistent} if self._persistent else {}),
+                                  **({"tail_order": True} if self.tail_order else {}))
         return out
 
 

@@ -31,7 +31,8 @@ TIMEOUT_NS = 2_000_000_000
 
 class TPDecoder:
     def __init__(self, cfg: Qwen3Config, weights: Qwen3Weights, pool: PagedKVPool, batch: int, max_ctx: int, rank: int, world: int,
-                 attn_chunk: int = 1024, group=None, attn_impl: str = "tc", collective: str = "rs_ag"):
+                 attn_chunk: int = 1024, group=None, attn_impl: str = "tc", collective: str = "rs_ag",
+                 attn_tail_order: bool = False):
         """collective: "rs_ag" = GEMM -> reduce-scatter and all-gather -> GEMM with a token-sharded residual stream (4 hops per
         layer); "oneshot" = every rank pushes its full partial tile to every peer and the norm kernel sums `world` partials, with
         the residual stream and the normed activations replicated (2 hops per layer, world-1 times the bytes; built for
@@ -77,7 +78,7 @@ class TPDecoder:
         self.max_blocks = (max_ctx + 15) // 16
         self.block_table = torch.zeros((B, self.max_blocks), dtype=torch.int32, device=dev)
         self.inv_freq = ops.rope_inv_freq(cfg.rope_theta, dev, D)
-        self.attn = ops.PagedAttention(dev, B, self.qh, self.kh, max_ctx, attn_chunk, impl=attn_impl)
+        self.attn = ops.PagedAttention(dev, B, self.qh, self.kh, max_ctx, attn_chunk, impl=attn_impl, tail_order=attn_tail_order)
         self.step_ctr = torch.zeros(1, dtype=torch.int32, device=dev)
         self.status = new_status(dev)
         self.ws = GemmWorkspace(dev)
@@ -266,7 +267,7 @@ def _bytes_per_step(cfg: Qwen3Config, w: Qwen3Weights, ctx: torch.Tensor, kv_hea
 
 def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world: int, ctx: torch.Tensor, extra_tokens: int,
                         seed: int = 0, kv_init: str = "normal", attn_chunk: int = 1024, attn_impl: str = "tc",
-                        collective: str = "rs_ag", fuse_norm: bool = False):
+                        collective: str = "rs_ag", fuse_norm: bool = False, attn_tail_order: bool = False):
     """Weights shard, KV pool sized for ``ctx`` (+ ``extra_tokens`` of growth per sequence), randomly permuted block
     table, and the decode engine for this rank. Every rank passes the same ``ctx`` and ``seed``."""
     batch = ctx.numel()
@@ -290,8 +291,9 @@ def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world
         table[i, :nb] = perm[o:o + nb]
         o += nb
     if world == 1:
-        eng = Qwen3Decoder(cfg, weights, pool, batch, max_ctx, attn_chunk, attn_impl, fuse_norm=fuse_norm)
+        eng = Qwen3Decoder(cfg, weights, pool, batch, max_ctx, attn_chunk, attn_impl, fuse_norm=fuse_norm, attn_tail_order=attn_tail_order)
     else:
         assert not fuse_norm, "the norm-free step exists for the single-GPU engine (the tensor-parallel norm kernel is also the collective)"
-        eng = TPDecoder(cfg, weights, pool, batch, max_ctx, rank, world, attn_chunk, attn_impl=attn_impl, collective=collective)
+        eng = TPDecoder(cfg, weights, pool, batch, max_ctx, rank, world, attn_chunk, attn_impl=attn_impl, collective=collective,
+                        attn_tail_order=attn_tail_order)
     return eng, table
