@@ -68,6 +68,7 @@ def test_read_and_argument_rules(server):
     assert "span=4096" in r.stdout                                                                  # span raised to the message size
 
 
+@pytest.mark.realtime
 def test_control_port_paces_and_stops_a_flow():
     cport = free_port()
     env = dict(ENV, SKYGDR_CTRL_PORT=str(cport), SKYGDR_CTRL_LOW_SLEEP_US="2000", SKYGDR_CTRL_BIND_IP="127.0.0.1")
@@ -87,6 +88,7 @@ def test_control_port_paces_and_stops_a_flow():
     assert 20 <= done < 1000000                                     # it ran, paced, and stopped early
 
 
+@pytest.mark.realtime
 def test_flow_registers_with_the_daemon_and_obeys_its_grant():
     with FabricDaemon(window_us=2000, capacity_gbps=1.0, lease_ms=3000) as d:
         env = dict(ENV, SKYGDR_DAEMON=f"127.0.0.1:{d.port}", SKYGDR_FLOW_NAME="kv_offload", SKYGDR_FLOW_PRIORITY="besteffort")
@@ -106,8 +108,10 @@ def test_flow_registers_with_the_daemon_and_obeys_its_grant():
             assert c.request("FLOWS").startswith("OK n=0")          # it unregistered on exit
 
 
+@pytest.mark.realtime
 def test_msgsize_sweep_writes_one_row_per_size(tmp_path):
     out = tmp_path / "sweep.csv"
+    out.unlink(missing_ok=True)                                     # the sweep appends; a retried attempt starts clean
     r = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.msgsize_sweep", "--fabric", "sim:8", "--iters", "200", "--warmup_iters", "20",
                         "--msg_sizes", "4K,64K,1M", "--out", str(out)], capture_output=True, text=True, env=ENV, timeout=120)
     assert r.returncode == 0, r.stderr
@@ -116,9 +120,11 @@ def test_msgsize_sweep_writes_one_row_per_size(tmp_path):
     rows = list(csv.DictReader(open(out)))
     assert [int(x["msg_bytes"]) for x in rows] == [4096, 65536, 1 << 20]
     assert all(x["rc"] == "0" and float(x["p50_us"]) > 0 for x in rows)
-    assert float(rows[2]["throughput_gib_s"]) == pytest.approx(8 / 1.0737, rel=0.15)          # large messages reach the link rate
+    link = 8 / 1.0737                                               # the simulated 8 GB/s link in GiB/s
+    assert 0.7 * link < float(rows[2]["throughput_gib_s"]) < 1.05 * link                      # large messages reach the link rate, never pass it
 
 
+@pytest.mark.realtime
 def test_policy_loop_program_end_to_end(tmp_path):
     """Background flow = cpu_client with a control port; protected flow and PCIe signal = stand-in scripts that write
     the same CSVs the real tools write. The loop must escalate, release when the restore is done, then STOP."""
@@ -286,6 +292,7 @@ def test_colocation_harness_plans_our_programs(tmp_path, monkeypatch):
         cb.resolve_config("hbm_kv", "no_such_preset")
 
 
+@pytest.mark.realtime
 def test_flow_outlives_a_killed_daemon_under_the_unpaced_dead_policy():
     """The daemon is killed (no snapshot, no goodbye) while a paced flow runs. With `--dead_policy unpaced` the flow notices
     the stale heartbeat in its page and finishes on its own; the failure is made on the host."""
@@ -310,6 +317,7 @@ def test_flow_outlives_a_killed_daemon_under_the_unpaced_dead_policy():
     assert "samples=3000" in out, out + err
 
 
+@pytest.mark.realtime
 def test_steady_queue_depth_trades_latency_for_nothing_on_a_saturated_link():
     """Reads and unacknowledged writes keep `qd` messages in flight (the reference's steady-queue-depth loop,
     src/cpu_client.cc:943-1087): on the simulated 1 GB/s link the throughput stays at the link rate while the latency of a

@@ -79,6 +79,7 @@ def test_lease_expiry_collects_a_silent_flow(daemon):
         assert c.request(f"RENEW {a.flow_id}") == "ERR unknown_flow"
 
 
+@pytest.mark.realtime
 def test_daemon_crash_leaves_last_grant_and_restart_restores_flows(tmp_path):
     snap = str(tmp_path / "snap.json")
     d = FabricDaemon(window_us=2000, lease_ms=5000, snapshot=snap)
@@ -106,6 +107,7 @@ def test_daemon_crash_leaves_last_grant_and_restart_restores_flows(tmp_path):
         d2.stop()
 
 
+@pytest.mark.realtime
 def test_killed_daemon_is_detected_by_clients(tmp_path):
     d = FabricDaemon(window_us=2000)
     c = FabricClient(port=d.port)
