@@ -186,3 +186,28 @@ def test_fold_norms_on_cpu_weights_keeps_the_reference_logits():
     err = (after - before).abs().max() / before.abs().max()
     assert err < 0.03, float(err)
     assert w.fold_norms() is w                              # idempotent
+
+
+def test_library_send_recv_handoff_moves_paged_kv_between_two_ranks(tmp_path):
+    """The comparison arm for the transfer kernel (gather + layout change, library send / recv, scatter) as two gloo
+    ranks: the receiver must end up with head-major copies of exactly the sender's blocks, in its own block order."""
+    import json
+    import os
+    import socket
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = tmp_path / "lib.json"
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", str(port), os.path.join(root, "benchmarks", "config2_library_sendrecv.py"), "--device", "cpu",
+                        "--requests", "2", "--min-tokens", "64", "--max-tokens", "1024", "--layers", "2", "--blocks-per-message", "7",
+                        "--out", str(out)], capture_output=True, text=True, timeout=300, cwd=root)
+    assert r.returncode == 0, r.stderr[-2000:]
+    d = json.load(open(out))
+    assert d["arms"]["send_recv_paged"]["exact"] is True
+    assert d["arms"]["send_recv_paged"]["gb"] == d["arms"]["send_recv_contiguous"]["gb"] > 0       # same payload in both arms
+    assert d["config"]["backend"] == "gloo"
