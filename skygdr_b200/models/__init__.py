@@ -1,3 +1,3 @@
-from .qwen3 import DecodeSession, Qwen3Config, Qwen3Decoder, Qwen3Weights, reference_forward
+from .qwen3 import DecodeSession, Qwen3Config, Qwen3Decoder, Qwen3Weights, reference_forward, reference_forward_tp
 
-__all__ = ["DecodeSession", "Qwen3Config", "Qwen3Decoder", "Qwen3Weights", "reference_forward"]
+__all__ = ["DecodeSession", "Qwen3Config", "Qwen3Decoder", "Qwen3Weights", "reference_forward", "reference_forward_tp"]

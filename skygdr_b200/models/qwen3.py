@@ -390,6 +390,63 @@ def reference_forward(cfg: Qwen3Config, w: Qwen3Weights, ids: torch.Tensor) -> t
     return xn @ w.lm_head.float().t()
 
 
+def reference_forward_tp(cfg: Qwen3Config, w: Qwen3Weights, ids: torch.Tensor, group=None) -> torch.Tensor:
+    """The same forward on a tensor-parallel shard of the weights (``Qwen3Weights(..., tp_rank, tp_world)``), in plain PyTorch
+    with ``torch.distributed`` collectives, so it runs on CPU ranks over gloo: column-parallel QKV and gate/up (this rank's
+    heads and FFN columns), row-parallel O and down whose bf16 partial products are summed over the ranks, and a
+    vocabulary-parallel lm_head. Returns this rank's logits columns [tokens][vocab_hi - vocab_lo] in fp32. It states what
+    ``parallel.TPDecoder`` must compute and checks the shard layout without a GPU."""
+    import torch.distributed as dist
+
+    world = w.tp_world
+    T = ids.numel()
+    D, Hq, Hkv, F = cfg.head_dim, cfg.q_heads // world, cfg.kv_heads // world, cfg.ffn // world
+
+    def norm(x, g):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.eps) * g.float()
+
+    def bf(x):
+        return x.to(torch.bfloat16).float()
+
+    def allsum(partial):
+        x = bf(partial).contiguous()                 # each rank's partial tile travels as bf16
+        if world > 1:
+            dist.all_reduce(x, group=group)
+        return bf(x)
+
+    inv = ops.rope_inv_freq(cfg.rope_theta, ids.device, D)
+    ang = torch.arange(T, device=ids.device).float()[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rope(x):
+        x1, x2 = x[..., :D // 2], x[..., D // 2:]
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
+
+    resid = w.embed[ids.long()].float()
+    h = None
+    mask = torch.triu(torch.ones(T, T, dtype=torch.bool, device=ids.device), 1)[None]
+    for lw in w.layers:
+        if h is not None:
+            resid = bf(resid + h)
+        xn = bf(norm(resid, lw.ln1))
+        qkv = bf(xn @ lw.qkv.float().t()).view(T, Hq + 2 * Hkv, D)
+        q = bf(rope(bf(norm(qkv[:, :Hq], lw.q_norm))))
+        k = bf(rope(bf(norm(qkv[:, Hq:Hq + Hkv], lw.k_norm))))
+        v = qkv[:, Hq + Hkv:]
+        kr, vr = k.repeat_interleave(Hq // Hkv, 1), v.repeat_interleave(Hq // Hkv, 1)
+        s = (torch.einsum("thd,shd->hts", q, kr) / math.sqrt(D)).masked_fill(mask, float("-inf"))
+        ao = bf(torch.einsum("hts,shd->thd", torch.softmax(s, -1), vr)).reshape(T, Hq * D)
+        h = allsum(ao @ lw.o.float().t())
+        resid = bf(resid + h)
+        xn = bf(norm(resid, lw.ln2))
+        gu = xn @ lw.gate_up.float().t()
+        act = bf(torch.nn.functional.silu(gu[:, :F]) * gu[:, F:])
+        h = allsum(act @ lw.down.float().t())
+    resid = bf(resid + h)
+    xn = bf(norm(resid, w.final_norm))
+    return xn @ w.lm_head.float().t()
+
+
 class DecodeSession:
     """The call a user makes to decode: host token ids in, host token ids out, one step at a time.
 

@@ -211,3 +211,26 @@ def test_library_send_recv_handoff_moves_paged_kv_between_two_ranks(tmp_path):
     assert d["arms"]["send_recv_paged"]["exact"] is True
     assert d["arms"]["send_recv_paged"]["gb"] == d["arms"]["send_recv_contiguous"]["gb"] > 0       # same payload in both arms
     assert d["config"]["backend"] == "gloo"
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_shards_reproduce_the_unsharded_forward_on_cpu_ranks(world):
+    """Shard layout of the weights (heads, FFN columns, O / down input slices, vocabulary ranges) checked by gloo ranks:
+    the plain-PyTorch tensor-parallel forward on the shards must give the unsharded logits."""
+    import json
+    import os
+    import socket
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr", "127.0.0.1",
+                        "--master-port", str(port), os.path.join(root, "tests", "multi", "tp_oracle_worker.py")],
+                       capture_output=True, text=True, timeout=300, cwd=root)
+    assert r.returncode == 0, r.stderr[-3000:]
+    d = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert d["world"] == world and d["covered"] and d["argmax_agrees"] and d["clear_rows"] > 0
+    assert d["rel_err_max"] < 0.03, d             # bf16 rounding of per-rank partial sums is the only difference
