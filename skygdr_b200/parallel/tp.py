@@ -246,9 +246,24 @@ class TPDecoder:
         return out
 
     _advance = Qwen3Decoder._advance
-    step = Qwen3Decoder.step
     capture = Qwen3Decoder.capture
-    replay = Qwen3Decoder.replay
+
+    # A step's kernels wait (bounded) for every peer, so a step launched after a peer has gone only burns its time-outs.
+    # With a ``liveness.RankWatch`` attached, the host checks the peers before every launch and raises ``PeerLost`` instead.
+    watch = None
+
+    def attach_watch(self, watch) -> None:
+        self.watch = watch
+
+    def step(self, *args, **kwargs) -> torch.Tensor:
+        if self.watch is not None:
+            self.watch.guard()
+        return Qwen3Decoder.step(self, *args, **kwargs)
+
+    def replay(self) -> torch.Tensor:
+        if self.watch is not None:
+            self.watch.guard()
+        return Qwen3Decoder.replay(self)
 
     def check_status(self) -> str:
         torch.cuda.synchronize(self.device)

@@ -38,6 +38,15 @@ def test_tensor_parallel_decode_oneshot_allreduce_2gpu():
     assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.skipif(os.environ.get("SKYGDR_TEST_TP_LEAVE") != "1", reason="opt-in until it has been run on GPUs once")
+def test_a_rank_leaving_between_steps_is_learnt_on_the_host_before_the_next_launch():
+    """Rank world-1 leaves a tensor-parallel job between steps (nothing in flight); the others must get PeerLost from the
+    liveness store instead of launching a step that would wait for it, and keep a usable context."""
+    r = _run(2, "tp_leave_worker.py")
+    assert "TP_LEAVE_LEFT" in r.stdout and "TP_LEAVE_DETECTED rank=0" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 3, reason="needs 3 GPUs (source + 2 destinations)")
 def test_multicast_fanout_lands_in_every_destination():
     """GPU0's pages go out once through the NVLink multicast address and must equal, in both destinations' pools, what
