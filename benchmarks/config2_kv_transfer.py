@@ -29,7 +29,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 from skygdr_b200 import ops  # noqa: E402
 from skygdr_b200._ext import load  # noqa: E402
-from skygdr_b200.cli.common import env_info  # noqa: E402
+from skygdr_b200.cli.common import ResultFile, env_info  # noqa: E402
 
 NVLINK_NOMINAL, NVLINK_MEASURED = 900.0, 770.0
 
@@ -83,6 +83,7 @@ def main():
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--pages-per-chunk", type=int, default=8)
     ap.add_argument("--skip", default="", help="comma list of arm groups to leave out: paced, copy_engine, pairs, fanout, multimem")
+    ap.add_argument("--resume", action="store_true", help="keep the arms that --out already holds and measure only the missing ones")
     a = ap.parse_args()
     skip = set(filter(None, a.skip.split(",")))
     assert a.gpus >= 2, "needs at least two GPUs"
@@ -91,8 +92,9 @@ def main():
     seq = torch.randint(1024, 65536 + 1, (a.requests,), generator=g).tolist()
     blocks = [geom.blocks_for(t) for t in seq]
     max_blocks = max(blocks)
-    res = {"config": {"geometry": "36 layers x 8 kv heads x 128, bf16, 16-token blocks", "seq_lens": seq, "total_gb": sum(blocks) * geom.block_elems * 2 / 1e9,
-                      "gpus": a.gpus}, "env": env_info(), "arms": {}}
+    rf = ResultFile(a.out, {"config": {"geometry": "36 layers x 8 kv heads x 128, bf16, 16-token blocks", "seq_lens": seq,
+                                       "total_gb": sum(blocks) * geom.block_elems * 2 / 1e9, "gpus": a.gpus}, "env": env_info()}, resume=a.resume)
+    res = rf.data                                  # every finished arm is written to --out at once (rf.save / rf.put)
     src, dsts, sp, dp = make_pair(0, [1], geom, max_blocks, a.seed)
     remotes = [ops.RemotePool.of(dsts[0])]
     flow = ops.KvTransferFlow("cuda:0", ctas=a.ctas or None, pages_per_chunk=a.pages_per_chunk)
@@ -105,8 +107,11 @@ def main():
     nb = blocks[-1]
     ok = torch.equal(dsts[0].data[dp[:nb].long().to(dsts[0].data.device)], ops.reference_transfer(src, sp[:nb]).to(dsts[0].data.device))
     res["arms"]["kernel"]["exact"] = bool(ok)
+    rf.save()
     # paced arms
     for pct in (() if "paced" in skip else (75, 50, 25)):
+        if rf.done(f"kernel@{pct}%"):
+            continue
         page = ops.CreditPage(flow_id=pct, unlimited=False)
         pf = ops.KvTransferFlow("cuda:0", page=page, ctas=a.ctas or None, pages_per_chunk=a.pages_per_chunk, max_wait_ms=20.0)
         budget = unpaced * pct / 100.0
@@ -115,11 +120,13 @@ def main():
         b, ev, k, stall = time_kernel(pf, src, remotes, sp, dp, blocks[: max(4, a.requests // 2)], paced=True)
         wall = time.perf_counter() - t0
         pacer.stop()
-        res["arms"][f"kernel@{pct}%"] = {"budget_gbs": budget, "achieved_gbs": b / ev / 1e9, "achieved_over_budget": b / ev / 1e9 / budget,
-                                         "stall_ms_per_cta_sum": stall * 1e-6, "wall_s": wall}
+        rf.put(f"kernel@{pct}%", {"budget_gbs": budget, "achieved_gbs": b / ev / 1e9, "achieved_over_budget": b / ev / 1e9 / budget,
+                                  "stall_ms_per_cta_sum": stall * 1e-6, "wall_s": wall})
     # baselines through the copy engine
     sdev, ddev = src.data.device, dsts[0].data.device
     for name in (() if "copy_engine" in skip else ("memcpy_peer", "per_page")):
+        if rf.done(name):
+            continue
         tot_b, tot_s = 0, 0.0
         for i, nb in enumerate(blocks):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -136,11 +143,11 @@ def main():
             if i >= 1:                                                       # first one warms up
                 tot_b += nb * geom.block_elems * 2
                 tot_s += e0.elapsed_time(e1) * 1e-3
-        res["arms"][name] = {"gbs": tot_b / tot_s / 1e9, "frac_of_900": tot_b / tot_s / 1e9 / NVLINK_NOMINAL}
+        rf.put(name, {"gbs": tot_b / tot_s / 1e9, "frac_of_900": tot_b / tot_s / 1e9 / NVLINK_NOMINAL})
     del src, dsts
     torch.cuda.empty_cache()
     # all pairs at once
-    if a.gpus >= 4 and "pairs" not in skip:
+    if a.gpus >= 4 and "pairs" not in skip and not rf.done(f"pairs_x{a.gpus // 2}"):
         pairs = [(2 * i, 2 * i + 1) for i in range(a.gpus // 2)]
         sets = [make_pair(s, [d], geom, max_blocks, a.seed + s) for s, d in pairs]
         flows = [ops.KvTransferFlow(f"cuda:{s}") for s, _ in pairs]
@@ -152,13 +159,13 @@ def main():
             sts = [fl.result() for fl in flows]
         t_max = max(st["device_time_ms"] for st in sts) * 1e-3
         t0 = min(st["t_start_ns"] for st in sts)
-        res["arms"][f"pairs_x{len(pairs)}"] = {"aggregate_gbs_max_over_pairs": sum(st["bytes_done"] for st in sts) / t_max / 1e9,
-                                               "per_pair_gbs": [st["bytes_done"] / (st["device_time_ms"] * 1e-3) / 1e9 for st in sts]}
+        rf.put(f"pairs_x{len(pairs)}", {"aggregate_gbs_max_over_pairs": sum(st["bytes_done"] for st in sts) / t_max / 1e9,
+                                        "per_pair_gbs": [st["bytes_done"] / (st["device_time_ms"] * 1e-3) / 1e9 for st in sts]})
         del sets
         torch.cuda.empty_cache()
     # fan-out from GPU0
     for k in sorted({min(a.gpus - 1, x) for x in (2, 4, 7)}):
-        if k < 2 or "fanout" in skip:
+        if k < 2 or "fanout" in skip or (rf.done(f"fanout_x{k}") and rf.done(f"fanout_multimem_x{k}")):
             continue
         src, dsts, sp, dp = make_pair(0, list(range(1, k + 1)), geom, min(max_blocks, 1024), a.seed)
         fl = ops.KvTransferFlow("cuda:0")
@@ -193,6 +200,7 @@ def main():
                 del want
         except Exception as exc:                                             # no multicast support on this machine: say so, keep the unicast arm
             res["arms"][f"fanout_multimem_x{k}"] = {"unavailable": repr(exc)[:300]}
+        rf.save()
         del src, dsts
         torch.cuda.empty_cache()
     if a.ref:
@@ -209,8 +217,7 @@ def main():
             res["arms"]["reference_binary_fixed_4GiB"] = {"gib_s": float(m.group(1)) if m else None, "gbs": float(m.group(1)) * 1.073741824 if m else None, "rc": r.returncode}
         else:
             res["arms"]["reference_binary_trace"] = {"unavailable": "baseline/_ref/bin not built (run baseline/build_ref.sh)"}
-    os.makedirs(os.path.dirname(os.path.abspath(a.out)), exist_ok=True)
-    json.dump(res, open(a.out, "w"), indent=1)
+    rf.save()
     print(json.dumps(res["arms"], indent=1))
 
 

@@ -50,3 +50,40 @@ def dump_json(path: str, obj) -> None:
     os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
     with open(path, "w") as f:
         json.dump(obj, f, indent=1)
+
+
+class ResultFile:
+    """A benchmark's result JSON that is written after every arm, so that a run that is cut short keeps what it measured,
+    and that a later run can continue (``resume=True``): arms already in the file are skipped, not measured again. The
+    reference's tools continue result files in the same spirit (``gpu_metrics_logger.py --append``, the sweep's
+    append-with-header logic, src/tools/rdma_msgsize_sweep.py:174-187)."""
+
+    def __init__(self, path: str, head: Dict, section: str = "arms", resume: bool = False):
+        self.path, self.section = path, section
+        self.data = dict(head)
+        self.data.setdefault(section, {})
+        self.kept: Dict = {}
+        if resume and os.path.exists(path):
+            try:
+                with open(path) as f:
+                    self.kept = dict(json.load(f).get(section, {}))
+            except (OSError, ValueError):
+                self.kept = {}                  # an unreadable file is not a reason to refuse the run
+            self.data[section].update(self.kept)
+
+    def done(self, name: str) -> bool:
+        return name in self.kept
+
+    def get(self, name: str):
+        return self.data[self.section].get(name)
+
+    def put(self, name: str, value) -> None:
+        self.data[self.section][name] = value
+        self.save()
+
+    def save(self) -> None:
+        os.makedirs(os.path.dirname(os.path.abspath(self.path)), exist_ok=True)
+        tmp = self.path + ".tmp"
+        with open(tmp, "w") as f:
+            json.dump(self.data, f, indent=1)
+        os.replace(tmp, self.path)              # never leaves a half-written file behind

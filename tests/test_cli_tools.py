@@ -355,3 +355,25 @@ def test_config1_with_the_compat_programs_as_flows():
         if ok:
             break
     assert ok, (tt, none)
+
+
+def test_result_file_keeps_finished_arms_and_skips_them_on_resume(tmp_path):
+    from skygdr_b200.cli.common import ResultFile
+
+    path = str(tmp_path / "r" / "res.json")
+    rf = ResultFile(path, {"config": {"gpus": 2}})
+    assert not rf.done("kernel")
+    rf.put("kernel", {"gbs": 700.0})
+    rf.put("memcpy_peer", {"gbs": 770.0})                      # the run is cut here: both arms are already on disk
+    import json
+
+    assert set(json.load(open(path))["arms"]) == {"kernel", "memcpy_peer"} and not os.path.exists(path + ".tmp")
+    again = ResultFile(path, {"config": {"gpus": 2}}, resume=True)
+    assert again.done("kernel") and again.done("memcpy_peer") and not again.done("per_page")
+    assert again.get("kernel") == {"gbs": 700.0}
+    again.put("per_page", {"gbs": 97.0})
+    assert set(json.load(open(path))["arms"]) == {"kernel", "memcpy_peer", "per_page"}
+    fresh = ResultFile(path, {"config": {}}, resume=False)      # without resume everything is measured again
+    assert not fresh.done("kernel")
+    open(path, "w").write("{ not json")
+    assert not ResultFile(path, {}, resume=True).done("kernel")
