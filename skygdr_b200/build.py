@@ -71,6 +71,15 @@ HOST_BINARIES = {
 }
 
 
+def _nvtx_flags() -> list:
+    """NVTX v3 is header-only; the control plane's timeline ranges (csrc/ctl/trace.hpp) are compiled in where the CUDA
+    toolkit's headers are present and are empty otherwise."""
+    for root in (os.environ.get("CUDA_HOME"), os.environ.get("CUDA_PATH"), "/usr/local/cuda"):
+        if root and (Path(root) / "include" / "nvtx3" / "nvToolsExt.h").exists():
+            return ["-DSKYGDR_WITH_NVTX", f"-isystem{Path(root) / 'include'}"]
+    return []
+
+
 def build_bin(force: bool = False) -> Path:
     BIN.mkdir(exist_ok=True)
     hdrs = sorted(CTL.glob("*.hpp")) + sorted(CTL.glob("*.h"))
@@ -80,7 +89,7 @@ def build_bin(force: bool = False) -> Path:
             continue
         out = BIN / name
         if force or _newer(out, srcs + hdrs):
-            _run(["g++", "-std=c++17", "-O2", "-Wall", f"-I{CTL}", *map(str, srcs), "-o", str(out), "-ldl", "-pthread"])
+            _run(["g++", "-std=c++17", "-O2", "-Wall", f"-I{CTL}", *_nvtx_flags(), *map(str, srcs), "-o", str(out), "-ldl", "-pthread"])
     return BIN
 
 

@@ -28,6 +28,7 @@
 #include <thread>
 
 #include "daemon_core.hpp"
+#include "trace.hpp"
 #include "signals.hpp"
 
 using namespace skygdr;
@@ -112,6 +113,7 @@ int main(int argc, char** argv) {
     if (ls < 0) { perror("fabricd: listen"); return 1; }
     fprintf(stderr, "fabricd: listening on %s:%d policy=%s window_us=%llu capacity_gbps=%.1f\n", bind_ip.c_str(), port,
             core.policy_name(), (unsigned long long)(cfg.window_ns / 1000), cfg.capacity_gbps);
+    if (trace_enabled()) fprintf(stderr, "fabricd: nvtx ranges %s\n", trace_compiled_in() ? "on" : "requested but not compiled in");
 
     std::mutex mu;
     FILE* log = log_path.empty() ? nullptr : fopen(log_path.c_str(), "w");
@@ -123,8 +125,10 @@ int main(int argc, char** argv) {
         while (!g_stop.load()) {
             uint64_t now = mono_ns();
             if (now < next) { std::this_thread::sleep_for(std::chrono::nanoseconds(std::min<uint64_t>(next - now, 2'000'000))); continue; }
+            TraceRange window_range("fabricd.window");
             double util = 0;
             if (sigs && cfg.external_util) {
+                TraceRange r("fabricd.signals");
                 PcieSample s = sigs->sample_pcie();
                 util = util_source == "pcie_tx" ? s.tx_util_pct : s.rx_util_pct;
             }
@@ -132,6 +136,7 @@ int main(int argc, char** argv) {
             uint64_t win_ns;
             {
                 std::lock_guard<std::mutex> g(mu);
+                TraceRange r("fabricd.policy_and_grants");
                 logs = core.step_window(now, util);
                 win_ns = core.config().window_ns;
             }
@@ -174,7 +179,11 @@ int main(int argc, char** argv) {
                 if (trim(line) == "QUIT") { quit = true; break; }
                 if (trim(line) == "SHUTDOWN") { g_stop.store(1); quit = true; send(c, "OK\n", 3, MSG_NOSIGNAL); break; }
                 std::string rep;
-                { std::lock_guard<std::mutex> g(mu); rep = core.handle_line(line, mono_ns()); }
+                {
+                    TraceRange r("fabricd.request");
+                    std::lock_guard<std::mutex> g(mu);
+                    rep = core.handle_line(line, mono_ns());
+                }
                 if (send(c, rep.data(), rep.size(), MSG_NOSIGNAL) < 0) { quit = true; break; }
             }
             if (quit) break;

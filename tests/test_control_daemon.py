@@ -171,3 +171,71 @@ def test_live_control_loop_against_the_daemon_process():
         if ok:
             break
     assert ok, (tt, none)
+
+
+_FAKE_PROFILER = r"""
+// A stand-in for a profiler: an NVTX injection library that writes every range it is told about to a file.
+#include <nvtx3/nvToolsExt.h>
+#include <cstdio>
+#include <cstdlib>
+#include <mutex>
+static FILE* g_log;
+static std::mutex g_mu;
+static int NVTX_API my_push(const char* name) { std::lock_guard<std::mutex> g(g_mu); if (g_log) { fprintf(g_log, "push %s\n", name); fflush(g_log); } return 0; }
+static int NVTX_API my_pop(void) { std::lock_guard<std::mutex> g(g_mu); if (g_log) { fprintf(g_log, "pop\n"); fflush(g_log); } return 0; }
+extern "C" __attribute__((visibility("default"))) int InitializeInjectionNvtx2(NvtxGetExportTableFunc_t get) {
+    const char* path = getenv("FAKE_NVTX_LOG");
+    g_log = path ? fopen(path, "w") : nullptr;
+    auto* cb = (const NvtxExportTableCallbacks*)get(NVTX_ETID_CALLBACKS);
+    if (!cb) return 0;
+    NvtxFunctionTable table = nullptr;
+    unsigned int size = 0;
+    if (!cb->GetModuleFunctionTable(NVTX_CB_MODULE_CORE, &table, &size) || size <= NVTX_CBID_CORE_RangePop) return 0;
+    *table[NVTX_CBID_CORE_RangePushA] = (NvtxFunctionPointer)my_push;
+    *table[NVTX_CBID_CORE_RangePop] = (NvtxFunctionPointer)my_pop;
+    return 1;
+}
+"""
+
+
+def test_daemon_emits_timeline_ranges_to_an_attached_profiler(tmp_path):
+    """SKYGDR_NVTX=1 makes fabricd wrap every control window, its policy pass and every request in an NVTX range. A small
+    injection library stands in for the profiler and records what it is told."""
+    import subprocess
+
+    from skygdr_b200 import build
+
+    if not build._nvtx_flags():
+        pytest.skip("no NVTX headers on this machine: the ranges are compiled out")
+    src, lib, log = tmp_path / "fake_profiler.cc", tmp_path / "libfake_profiler.so", tmp_path / "ranges.log"
+    src.write_text(_FAKE_PROFILER)
+    subprocess.run(["g++", "-std=c++17", "-shared", "-fPIC", build._nvtx_flags()[1], str(src), "-o", str(lib), "-ldl"], check=True)
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, SKYGDR_NVTX="1", NVTX_INJECTION64_PATH=str(lib), FAKE_NVTX_LOG=str(log))
+    p = subprocess.Popen([str(build.build_bin() / "fabricd"), "--port", str(port), "--window_us", "2000"], stderr=subprocess.PIPE, text=True, env=env)
+    try:
+        assert _wait(lambda: _try(lambda: send_control("127.0.0.1", port, "STATUS")) is not None, 5.0)
+        time.sleep(0.1)
+        with FabricClient(port=port) as c:
+            c.request("SHUTDOWN")
+        _, err = p.communicate(timeout=10)
+    finally:
+        if p.poll() is None:
+            p.kill()
+    assert "nvtx ranges on" in err
+    lines = log.read_text().splitlines()
+    names = {l.split(" ", 1)[1] for l in lines if l.startswith("push ")}
+    assert {"fabricd.window", "fabricd.policy_and_grants", "fabricd.request"} <= names, names
+    pushes, pops = sum(l.startswith("push") for l in lines), sum(l == "pop" for l in lines)
+    assert pushes >= 40 and abs(pushes - pops) <= 2            # 2 ms windows for 0.1 s and more; every range is closed
+
+
+def _try(fn):
+    try:
+        return fn()
+    except OSError:
+        return None
