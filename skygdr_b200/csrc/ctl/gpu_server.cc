@@ -1,7 +1,7 @@
 // gpu_server: the target end of a flow. Exposes a memory region, serves clients one after another,
 // and acknowledges a write only after its bytes are in place.
 //
-//   gpu_server <fabric:tcp|sim|link:GB/s> <mr_size> <tcp_port> <port> <gid_idx> [mtu=1024]
+//   gpu_server <fabric:tcp|gpu[:device]|sim|link:GB/s> <mr_size> <tcp_port> <port> <gid_idx> [mtu=1024]
 //
 // Same command line and session order as the reference's server (src/gpu_server.cu:8,215-530:
 // handshake, region info, client parameters, ready byte, then either idle until "done" or the
@@ -9,6 +9,11 @@
 // an RNIC and must flush GPUDirect writes before the ACK (:54-80,426-436); here the first argument
 // names the fabric instead of an InfiniBand device: `tcp` receives the payload on the session socket
 // into the region (the ACK follows the last byte, so it has the same meaning), `sim` moves no payload.
+// `gpu[:device]` is `tcp` with the region in that GPU's memory, as in the reference: the payload arrives in pinned staging
+// buffers and goes on with asynchronous copies (one chunk in flight while the next is received), and the ACK is sent only
+// after the stream has drained, that is, once the bytes are visible in device memory: the counterpart of the reference's
+// cudaDeviceFlushGPUDirectRDMAWrites before its ACK. Reads come back the same way. The CUDA runtime is bound at run time
+// (cuda_rt.hpp), so the program still builds and runs its other fabrics without one.
 // `link:<GB/s>` is the shared-link form used by the CPU-only control-loop experiment: clients are served at the same
 // time (a thread each) and every message occupies one simulated link of that rate for len / rate, first come first
 // served, before its tag goes back, so concurrent flows really take bandwidth from one another.
@@ -23,6 +28,7 @@
 #include <thread>
 #include <vector>
 
+#include "cuda_rt.hpp"
 #include "util.hpp"
 #include "wire.hpp"
 
@@ -33,7 +39,7 @@ static void on_sig(int) { g_stop = 1; }
 
 int main(int argc, char** argv) {
     if (argc < 6) {
-        fprintf(stderr, "usage: %s <fabric:tcp|sim|link:GB/s> <mr_size> <tcp_port> <port> <gid_idx> [mtu=1024]\n", argv[0]);
+        fprintf(stderr, "usage: %s <fabric:tcp|gpu[:device]|sim|link:GB/s> <mr_size> <tcp_port> <port> <gid_idx> [mtu=1024]\n", argv[0]);
         return 1;
     }
     std::string fabric = argv[1];
@@ -41,8 +47,47 @@ int main(int argc, char** argv) {
     if (!parse_size(argv[2], &mr_size) || mr_size == 0) { fprintf(stderr, "[server] bad mr_size\n"); return 2; }
     int tcp_port = atoi(argv[3]);
     bool sim = fabric.rfind("sim", 0) == 0 || fabric.rfind("link", 0) == 0;
+    const bool gpu = fabric.rfind("gpu", 0) == 0;
     std::vector<unsigned char> region;
-    if (!sim) region.resize(mr_size);
+    if (!sim && !gpu) region.resize(mr_size);
+    // gpu fabric: device region, two pinned staging buffers, one stream
+    CudaRt rt;
+    unsigned char* d_region = nullptr;
+    unsigned char* stage[2] = {nullptr, nullptr};
+    void* stream = nullptr;
+    const size_t kStage = 4u << 20;
+    if (gpu) {
+        const int device = fabric.size() > 4 ? atoi(fabric.c_str() + 4) : 0;
+        const std::string why = rt.load();
+        if (!why.empty()) { fprintf(stderr, "[server] gpu fabric unavailable: %s\n", why.c_str()); return 1; }
+        int e = rt.SetDevice(device);
+        if (!e) e = rt.Malloc((void**)&d_region, mr_size);
+        for (int i = 0; i < 2 && !e; ++i) e = rt.HostAlloc((void**)&stage[i], kStage, 0);
+        if (!e) e = rt.StreamCreateWithFlags(&stream, 1 /* non-blocking */);
+        if (e) { fprintf(stderr, "[server] gpu fabric set-up failed on device %d: %s\n", device, rt.err(e).c_str()); return 1; }
+    }
+    // Both return false on a socket or CUDA error. A staging buffer is reused every other chunk, so the stream is drained
+    // before a buffer's second use; the final drain is what the ACK waits for.
+    auto recv_to_device = [&](int c, uint64_t off, uint32_t len) {
+        int k = 0;
+        for (uint32_t done = 0; done < len; ++k) {
+            const uint32_t n = (uint32_t)std::min<uint64_t>(kStage, len - done);
+            if (k >= 2 && rt.StreamSynchronize(stream)) return false;
+            if (!recv_all(c, stage[k & 1], n)) return false;
+            if (rt.MemcpyAsync(d_region + off + done, stage[k & 1], n, CudaRt::kHostToDevice, stream)) return false;
+            done += n;
+        }
+        return rt.StreamSynchronize(stream) == 0;
+    };
+    auto send_from_device = [&](int c, uint64_t off, uint32_t len) {
+        for (uint32_t done = 0; done < len;) {
+            const uint32_t n = (uint32_t)std::min<uint64_t>(kStage, len - done);
+            if (rt.MemcpyAsync(stage[0], d_region + off + done, n, CudaRt::kDeviceToHost, stream) || rt.StreamSynchronize(stream)) return false;
+            if (!send_all(c, stage[0], n)) return false;
+            done += n;
+        }
+        return true;
+    };
     struct sigaction sa{};
     sa.sa_handler = on_sig;
     sigaction(SIGINT, &sa, nullptr);
@@ -93,11 +138,13 @@ int main(int argc, char** argv) {
             if (h.offset + h.len > mr_size) { fprintf(stderr, "[server] access outside the region\n"); break; }
             if (link) occupy_link(h.len);
             if (h.kind == 0) {                                       // write (+ optional ack)
-                if (!sim) { if (!recv_all(c, region.data() + h.offset, h.len)) break; }
+                if (gpu) { if (!recv_to_device(c, h.offset, h.len)) break; }
+                else if (!sim) { if (!recv_all(c, region.data() + h.offset, h.len)) break; }
                 ++msgs; bytes += h.len;
                 if (cp.write_ack) { uint32_t tag = h.tag; if (!send_all(c, &tag, 4)) break; }
             } else if (h.kind == 1) {                                // read: send the bytes back
-                if (!sim) { if (!send_all(c, region.data() + h.offset, h.len)) break; }
+                if (gpu) { if (!send_from_device(c, h.offset, h.len)) break; }
+                else if (!sim) { if (!send_all(c, region.data() + h.offset, h.len)) break; }
                 else { uint32_t tag = h.tag; if (!send_all(c, &tag, 4)) break; }
                 ++msgs; bytes += h.len;
             }
@@ -114,5 +161,11 @@ int main(int argc, char** argv) {
         else serve(c);                                   // the reference's order: one client after the other
     }
     close(ls);
+    if (gpu) {
+        rt.StreamDestroy(stream);
+        rt.FreeHost(stage[0]);
+        rt.FreeHost(stage[1]);
+        rt.Free(d_region);
+    }
     return 0;
 }

@@ -377,3 +377,121 @@ def test_result_file_keeps_finished_arms_and_skips_them_on_resume(tmp_path):
     assert not fresh.done("kernel")
     open(path, "w").write("{ not json")
     assert not ResultFile(path, {}, resume=True).done("kernel")
+
+
+_FAKE_CUDART = r"""
+// A stand-in CUDA runtime on host memory that logs what it is asked to do, for the server's gpu fabric on a machine without a GPU.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+static FILE* lg() { static FILE* f = fopen(getenv("FAKE_CUDART_LOG"), "a"); return f; }
+#define LOG(...) do { fprintf(lg(), __VA_ARGS__); fflush(lg()); } while (0)
+extern "C" {
+int cudaSetDevice(int d) { LOG("set_device %d\n", d); return 0; }
+int cudaMalloc(void** p, size_t n) { *p = calloc(1, n); LOG("malloc %zu\n", n); return *p ? 0 : 2; }
+int cudaFree(void* p) { free(p); return 0; }
+int cudaHostAlloc(void** p, size_t n, unsigned) { *p = malloc(n); LOG("host_alloc %zu\n", n); return *p ? 0 : 2; }
+int cudaFreeHost(void* p) { free(p); return 0; }
+int cudaMemcpyAsync(void* d, const void* s, size_t n, int kind, void*) { memcpy(d, s, n); LOG("%s %zu\n", kind == 1 ? "h2d" : "d2h", n); return 0; }
+int cudaStreamCreateWithFlags(void** s, unsigned) { *s = (void*)0x1; return 0; }
+int cudaStreamSynchronize(void*) { LOG("sync\n"); return 0; }
+int cudaStreamDestroy(void*) { return 0; }
+const char* cudaGetErrorString(int) { return "fake error"; }
+}
+"""
+
+
+def test_server_gpu_fabric_acks_after_the_bytes_are_in_device_memory(tmp_path):
+    """`gpu_server gpu:0 ...` keeps its region in device memory: payload goes through pinned staging and asynchronous copies and
+    the ACK follows the stream's drain. Run against a stand-in CUDA runtime (host memory, call log); the client side is
+    spoken here byte by byte (the structs of csrc/ctl/wire.hpp), then once more by the real cpu_client."""
+    import struct
+
+    src, lib, log = tmp_path / "fake_cudart.cc", tmp_path / "libfake_cudart.so", tmp_path / "cudart.log"
+    src.write_text(_FAKE_CUDART)
+    subprocess.run(["g++", "-shared", "-fPIC", str(src), "-o", str(lib)], check=True)
+    port = free_port()
+    env = dict(ENV, SKYGDR_CUDART=str(lib), FAKE_CUDART_LOG=str(log))
+    p = subprocess.Popen([f"{BIN}/gpu_server", "gpu:0", "16M", str(port), "1", "0"], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
+    try:
+        assert "fabric=gpu:0" in p.stdout.readline()
+        entries = lambda: log.read_text().split("\n")[:-1]
+        assert entries()[:2] == ["set_device 0", f"malloc {16 << 20}"] and entries().count(f"host_alloc {4 << 20}") == 2
+
+        def recv_all(s, n):
+            buf = b""
+            while len(buf) < n:
+                part = s.recv(n - len(buf))
+                assert part
+                buf += part
+            return buf
+
+        with socket.create_connection(("127.0.0.1", port), timeout=10) as s:
+            s.sendall(struct.pack("<I16sBBH", 7, b"\0" * 16, 1, 0, 0))                     # ConnInfo
+            recv_all(s, 24)
+            rkey, addr, length = struct.unpack("<I4xQQ", recv_all(s, 24))                  # RemoteInfo
+            assert length == 16 << 20
+            s.sendall(struct.pack("<BBHII", 1, 1, 0, 4, 1))                                # ClientParams: write, write_ack, qd 4, qps 1
+            assert recv_all(s, 1) == b"\x01"
+            big = os.urandom(10 * (1 << 20) + 123)                                         # three staging chunks, odd tail
+            small = os.urandom(4096)
+            for tag, off, data in ((11, 4096, big), (12, 0, small)):
+                before = len(entries())
+                s.sendall(struct.pack("<QIIII", off, len(data), tag, 0, 0) + data)
+                assert struct.unpack("<I", recv_all(s, 4))[0] == tag                       # the ACK carries the tag
+                new = entries()[before:]
+                assert sum(int(e.split()[1]) for e in new if e.startswith("h2d")) == len(data)
+                assert new[-1] == "sync"                                                   # by the time the ACK is out, the stream has drained
+                assert [e for e in new if e.startswith("h2d")][0] == f"h2d {min(len(data), 4 << 20)}"
+            for off, data in ((4096, big), (0, small)):                                    # read back what the device region holds
+                s.sendall(struct.pack("<QIIII", off, len(data), 99, 1, 0))
+                assert recv_all(s, len(data)) == data
+            s.sendall(struct.pack("<QIIII", 0, 0, 0, 2, 0))                                # done
+        assert "session closed: msgs=4" in p.stdout.readline()
+        r = client(["127.0.0.1", port, "tcp", 40, "256K", "write", 1, 0])                  # the compat client needs no change
+        assert r.returncode == 0 and "[client] done: iters=40" in r.stdout, r.stdout + r.stderr
+    finally:
+        p.terminate()
+        p.wait(timeout=5)
+    # without a runtime the gpu fabric is refused with a reason; the other fabrics do not need one
+    r = subprocess.run([f"{BIN}/gpu_server", "gpu", "1M", str(free_port()), "1", "0"], capture_output=True, text=True,
+                       env=dict(ENV, SKYGDR_CUDART=str(tmp_path / "missing.so")), timeout=10)
+    assert r.returncode == 1 and "gpu fabric unavailable" in r.stderr
+
+
+@pytest.mark.gpu
+def test_server_gpu_fabric_on_a_real_device(tmp_path):
+    """The same server mode against the real CUDA runtime: bytes written through the session come back unchanged from device memory."""
+    import struct
+
+    port = free_port()
+    p = subprocess.Popen([f"{BIN}/gpu_server", "gpu:0", "8M", str(port), "1", "0"], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=ENV)
+    try:
+        line = p.stdout.readline()
+        if "fabric=gpu:0" not in line:
+            pytest.skip("no loadable CUDA runtime library for the server: " + p.stderr.read()[-300:])
+
+        def recv_all(s, n):
+            buf = b""
+            while len(buf) < n:
+                part = s.recv(n - len(buf))
+                assert part
+                buf += part
+            return buf
+
+        with socket.create_connection(("127.0.0.1", port), timeout=10) as s:
+            s.sendall(struct.pack("<I16sBBH", 7, b"\0" * 16, 1, 0, 0))
+            recv_all(s, 48)
+            s.sendall(struct.pack("<BBHII", 1, 1, 0, 4, 1))
+            assert recv_all(s, 1) == b"\x01"
+            data = os.urandom(5 * (1 << 20) + 77)
+            s.sendall(struct.pack("<QIIII", 512, len(data), 5, 0, 0) + data)
+            assert struct.unpack("<I", recv_all(s, 4))[0] == 5
+            s.sendall(struct.pack("<QIIII", 512, len(data), 6, 1, 0))
+            assert recv_all(s, len(data)) == data
+            s.sendall(struct.pack("<QIIII", 0, 0, 0, 2, 0))
+        r = client(["127.0.0.1", port, "tcp", 40, "256K", "write", 1, 0])
+        assert r.returncode == 0 and "[client] done: iters=40" in r.stdout, r.stdout + r.stderr
+    finally:
+        p.terminate()
+        p.wait(timeout=5)
