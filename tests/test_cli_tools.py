@@ -495,3 +495,31 @@ def test_server_gpu_fabric_on_a_real_device(tmp_path):
     finally:
         p.terminate()
         p.wait(timeout=5)
+
+
+_REFERENCE_FLAGS = {
+    # tool -> the flags of the reference program it stands for (its argparse / argv parsing, read from the sources)
+    "controller": "--cpu_control_host --cpu_control_port --control_timeout_s --python_bin --pcie_bin --gpu_metrics_script --gpu "
+                  "--gpu_metrics_interval_ms --device --dir --chunk_mb --streams --batch --inflight --pinned --baseline_restore_gib_s "
+                  "--restore_total_bytes --restore_max_outstanding_bytes --progress_ms --progress_smooth_windows --poll_ms --warmup_ms "
+                  "--post_restore_ms --enter_ratio --exit_ratio --rx_threshold_pct --enter_windows --exit_windows --log_dir --tag",
+    "gpu_metrics_logger": "--gpu --interval_ms --out --append --live --plot --plot_in --plot_out --plot_show --plot_title --plot_on_exit",
+    "bandwidth_usage": "--gpu --interval_ms --duration_s --csv --out --quiet",
+    "cpu_client_control": "--host --port --timeout_s",
+    "msgsize_sweep": "--msg_sizes --warmup_iters --warmup_runs --warmup_sleep_ms --out",
+    "case_study_analyze": "--controller_csv --bg_ts_csv --out_csv --out_png --paper_out_pdf --plot_start_s --plot_end_s --rx_threshold_pct "
+                          "--pcie_peak_gib_s --always_high_restore_csv --always_low_restore_csv --controlled_restore_csv",
+    "gpu_pcie_memcpy": "--device --seconds --dir --bytes --chunk_mb --streams --batch --inflight --pinned --report_ms --total_bytes "
+                       "--max_outstanding_bytes --progress_ms --progress_smooth_windows --progress_out --duty_on_ms --duty_off_ms",
+    "gpu_memhog": "--device --gb --blocks --threads --iters --seconds --op --streams --vec",
+    "kv_nvlink_transfer_trace": "--src --dst --iters --dist --layers --kv-heads --head-dim --elem-bytes --max-tokens --sync-every --seed",
+    "decode_kvcache_stress": "--gpu --layers --kv-heads --head-dim --context --gen --batch --tile-tokens --threads --report-every --ffn-dim --ffn-blocks",
+}
+
+
+@pytest.mark.parametrize("tool", sorted(_REFERENCE_FLAGS))
+def test_tools_accept_every_flag_of_the_reference_program(tool):
+    r = subprocess.run([sys.executable, "-m", f"skygdr_b200.cli.{tool}", "--help"], capture_output=True, text=True, env=ENV, timeout=60)
+    assert r.returncode == 0, r.stderr[-500:]
+    missing = [f for f in _REFERENCE_FLAGS[tool].split() if f not in r.stdout]
+    assert not missing, (tool, missing)
