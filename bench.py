@@ -70,6 +70,7 @@ def main() -> int:
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    args.warmup = max(3, args.warmup)          # fewer than three warm-up steps would time first-use effects; the line reports what was done
     import torch
     import torch.distributed as dist
 
