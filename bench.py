@@ -46,8 +46,9 @@ def parse():
     ap.add_argument("--tp-collective", default="rs_ag", choices=["rs_ag", "oneshot"],
                     help="tensor-parallel form: reduce-scatter + all-gather (default) or the one-shot all-reduce")
     ap.add_argument("--attn-chunk", type=int, default=1024)
-    ap.add_argument("--attn-order", default="seq", choices=["seq", "tail"],
-                    help="tail: every sequence's partial last chunk is scheduled after all full chunks (not yet run on a GPU)")
+    ap.add_argument("--attn-order", default="seq", choices=["seq", "tail", "fine"],
+                    help="tail: every sequence's partial last chunk is scheduled after all full chunks; fine: that part is also cut into "
+                         "quarter chunks (neither has run on a GPU yet)")
     ap.add_argument("--fuse-norm", action="store_true",
                     help="1 GPU: RMSNorms folded into the GEMM epilogues, 6 kernels per layer instead of 8 (not yet run on a GPU)")
     ap.add_argument("--profile-step", action="store_true", help="also print per-kernel-kind times of one eager step (tensor-parallel engine)")
@@ -95,7 +96,7 @@ def main() -> int:
     max_ctx = int(ctx.max()) + total_steps + 1
     eng, table = build_decode_engine(cfg, dev, rank, world, ctx, total_steps, seed=args.seed, kv_init="normal",
                                      attn_chunk=args.attn_chunk, attn_impl=args.attn_impl, collective=args.tp_collective,
-                                     fuse_norm=args.fuse_norm, attn_tail_order=args.attn_order == "tail")
+                                     fuse_norm=args.fuse_norm, attn_tail_order={"seq": False, "tail": True, "fine": "fine"}[args.attn_order])
 
     ids0 = torch.randint(0, cfg.vocab, (batch,), generator=g).int()
     eng.set_batch(ids0.to(dev), ctx.int().to(dev), table.to(dev))
@@ -152,7 +153,7 @@ def main() -> int:
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random-init weights, N(0,1) KV, uniform context lengths)",
             "config": {"model": cfg.name if args.layers == 36 else f"{cfg.name}-{args.layers}L", "global_batch": batch,
                        "seq_len": f"context uniform {args.ctx_lo}-{args.ctx_hi}, 1 new token per step",
-                       "parallelism": f"tp{world}", "kv_block_tokens": 16, "sampling": "greedy", "attention": f"{args.attn_impl}, {args.attn_chunk}-token splits" + (", partial chunks last" if args.attn_order == "tail" else ""),
+                       "parallelism": f"tp{world}", "kv_block_tokens": 16, "sampling": "greedy", "attention": f"{args.attn_impl}, {args.attn_chunk}-token splits" + ({"seq": "", "tail": ", partial chunks last", "fine": ", partial chunks last in quarter-chunk pieces"}[args.attn_order]),
                        "norms": "folded into the GEMM epilogues" if args.fuse_norm else "norm kernels",
                        "l2": "inputs larger than L2: each step streams %.1f GB of weights and KV per GPU" % (step_bytes / 1e9)},
             "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,

@@ -73,6 +73,7 @@ def main():
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--impl", default="simt", choices=["simt", "tc", "tc1", "tc3", "tc2v3", "tc2v4", "tc2v5", "tc2v6", "tcp", "sdpa"])
     ap.add_argument("--tail-order", action="store_true", help="attn, impl tc: partial chunks scheduled last")
+    ap.add_argument("--fine-tail", action="store_true", help="attn, impl tc: partial chunks cut into quarter chunks and scheduled last")
     a = ap.parse_args()
     dev = "cuda"
     hbm, tf, src = peaks()
@@ -122,7 +123,7 @@ def main():
             table[b, :nb] = perm[o:o + nb]
             o += nb
         q = torch.randn((a.batch, a.q_heads, 128), dtype=torch.bfloat16, device=dev)
-        attn = ops.PagedAttention(dev, a.batch, a.q_heads, a.kv_heads, max_ctx=a.ctx, chunk_tokens=a.chunk, impl=a.impl, tail_order=a.tail_order)
+        attn = ops.PagedAttention(dev, a.batch, a.q_heads, a.kv_heads, max_ctx=a.ctx, chunk_tokens=a.chunk, impl=a.impl, tail_order="fine" if a.fine_tail else a.tail_order)
         o_ = torch.empty_like(q)
         ms, best = timed(lambda: attn(q, pool, 0, table, ctx, max_ctx=int(ctx.max()), out=o_), a.warm, a.iters, flush)
         byt = int(ctx.sum()) * a.kv_heads * 128 * 2 * 2

@@ -246,9 +246,10 @@ static void memhog(torch::Tensor a, torch::Tensor b, int op, int iters, uint64_t
 static void paged_attn_decode(torch::Tensor q, torch::Tensor kv_layer, torch::Tensor out, torch::Tensor block_table, torch::Tensor ctx_lens,
                               int64_t block_stride, int64_t kv_stride, int64_t head_stride, int kv_heads, int max_ctx, int chunk_tokens,
                               double scale, torch::Tensor part_o, torch::Tensor part_m, torch::Tensor part_l, torch::Tensor counters,
-                              torch::Tensor status, int64_t pool_rows, int persistent_ctas, bool tail_order) {
+                              torch::Tensor status, int64_t pool_rows, int persistent_ctas, int tail_order) {
     c10::cuda::CUDAGuard g(q.device());
     TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && out.is_contiguous(), "q/out: contiguous [batch][heads][128]");
+    TORCH_CHECK(tail_order >= 0 && tail_order <= 2, "tail_order: 0 off, 1 partial chunks last, 2 quarter-chunk pieces last");
     TORCH_CHECK(!tail_order || (pool_rows > 0 && persistent_ctas == 0), "tail_order belongs to the one-CTA-per-item tensor-core kernel");
     PagedAttnParams p;
     memset(&p, 0, sizeof p);
@@ -264,7 +265,7 @@ static void paged_attn_decode(torch::Tensor q, torch::Tensor kv_layer, torch::Te
     p.part_o = part_o.data_ptr<float>(); p.part_m = part_m.data_ptr<float>(); p.part_l = part_l.data_ptr<float>();
     p.counters = reinterpret_cast<unsigned int*>(counters.data_ptr());
     p.status = status_ptr(status);
-    p.tail_order = tail_order ? 1 : 0;
+    p.tail_order = tail_order;
     TORCH_CHECK(persistent_ctas == 0 || pool_rows > 0, "the persistent variant is the tensor-core kernel: give pool_rows");
     if (pool_rows > 0) SKY_CUDA_CHECK(launch_paged_attn_decode_tc(p, pool_rows, cur_stream(), persistent_ctas));
     else SKY_CUDA_CHECK(launch_paged_attn_decode(p, cur_stream()));
@@ -500,7 +501,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("paged_attn_decode", &paged_attn_decode, py::arg("q"), py::arg("kv_layer"), py::arg("out"), py::arg("block_table"), py::arg("ctx_lens"),
           py::arg("block_stride"), py::arg("kv_stride"), py::arg("head_stride"), py::arg("kv_heads"), py::arg("max_ctx"), py::arg("chunk_tokens"),
           py::arg("scale"), py::arg("part_o"), py::arg("part_m"), py::arg("part_l"), py::arg("counters"), py::arg("status"), py::arg("pool_rows"),
-          py::arg("persistent_ctas") = 0, py::arg("tail_order") = false);
+          py::arg("persistent_ctas") = 0, py::arg("tail_order") = 0);
     m.def("prefill_attn", &prefill_attn);
     m.def("rmsnorm", &rmsnorm);
     m.def("rope_append", &rope_append);

@@ -26,7 +26,9 @@ struct PagedAttnParams {
     float* part_l;                // [batch][q_heads][max_splits]
     unsigned int* counters;       // [batch][kv_heads], zero before the first launch; the kernel re-zeroes them
     LaunchStatus* status;
-    int tail_order;               // tensor-core kernel: 1 = every sequence's last (partial) chunk is scheduled after all full chunks
+    int tail_order;               // tensor-core kernel: 1 = every sequence's last (partial) chunk is scheduled after all full chunks;
+                                  // 2 = that last part is cut into quarter chunks, scheduled last (needs chunk_tokens % 512 == 0 and
+                                  // max_splits >= max_ctx / chunk_tokens + 4)
 };
 
 cudaError_t launch_paged_attn_decode(const PagedAttnParams& p, cudaStream_t stream);

@@ -79,16 +79,32 @@ __global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tc_kernel(const __gr
     for (int i = threadIdx.x; i < 3 * QP_BYTES / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_sm)[i] = make_uint4(0, 0, 0, 0);
     pdl_wait();
     const int ctx = p.ctx_lens[b];
-    const int n_splits = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
-    if (p.tail_order) {
-        const int z = blockIdx.z;
-        if (z < n_splits - 1) split = z;
-        else if (z == (int)gridDim.z - 1) split = n_splits - 1;
+    int n_splits = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
+    int tok0, tok1;
+    if (p.tail_order == 2) {
+        // Fine tail: full chunks first, then what is left of every sequence (less than a chunk) in pieces of a quarter chunk,
+        // which occupy the last four slots of the grid. The CTAs that finish the launch alone on their SMs then hold at most a
+        // quarter chunk, so the idle tail shrinks accordingly; a sequence has up to three partials more.
+        const int small = p.chunk_tokens >> 2;                          // a multiple of 128: the launcher checks chunk % 512
+        const int n_full = ctx / p.chunk_tokens;
+        const int rem = ctx - n_full * p.chunk_tokens;
+        const int n_small = (rem + small - 1) / small;
+        n_splits = n_full + n_small;
+        const int z = blockIdx.z, j = z - ((int)gridDim.z - 4);
+        if (j < 0 && z < n_full) { split = z; tok0 = z * p.chunk_tokens; tok1 = tok0 + p.chunk_tokens; }
+        else if (j >= 0 && j < n_small) { split = n_full + j; tok0 = n_full * p.chunk_tokens + j * small; tok1 = min(ctx, tok0 + small); }
         else return;
+    } else {
+        if (p.tail_order) {
+            const int z = blockIdx.z;
+            if (z < n_splits - 1) split = z;
+            else if (z == (int)gridDim.z - 1) split = n_splits - 1;
+            else return;
+        }
+        tok0 = split * p.chunk_tokens;
+        tok1 = min(ctx, tok0 + p.chunk_tokens);
     }
-    const int tok0 = split * p.chunk_tokens;
     if (tok0 >= ctx || ctx <= 0) return;
-    const int tok1 = min(ctx, tok0 + p.chunk_tokens);
     const int n_tiles = (tok1 - tok0 + TILE_TOK - 1) / TILE_TOK;
     const int* table = p.block_table + (long long)b * p.max_blocks;
 
@@ -631,8 +647,10 @@ cudaError_t launch_tc_g(const PagedAttnParams& p, const CUtensorMap& tm, cudaStr
     auto kern = paged_attn_tc_kernel<G>;
     static unsigned long long attr_mask = 0;
     if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), TC_SMEM, &attr_mask); e != cudaSuccess) return e;
-    const int slots = (p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens;
+    // fine tail (tail_order 2): one slot per possible full chunk, then four for the quarter-chunk pieces
+    const int slots = p.tail_order == 2 ? p.max_ctx / p.chunk_tokens + 4 : (p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens;
     if (p.tail_order && (p.batch > 65535 || slots > 65535)) return cudaErrorInvalidValue;
+    if (p.tail_order == 2 && (p.chunk_tokens % 512 != 0 || slots > p.max_splits)) return cudaErrorInvalidValue;
     const dim3 grid = p.tail_order ? dim3(p.kv_heads, p.batch, slots) : dim3(slots, p.kv_heads, p.batch);
     return launch_pdl(kern, grid, dim3(TC_THREADS), (size_t)TC_SMEM, stream, tm, p);
 }

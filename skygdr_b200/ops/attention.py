@@ -15,21 +15,24 @@ class PagedAttention:
     """Holds the split-KV scratch (partials, statistics, counters) for a maximum batch and context."""
 
     def __init__(self, device, max_batch: int, q_heads: int, kv_heads: int, max_ctx: int, chunk_tokens: int = 512, impl: str = "simt",
-                 tail_order: bool = False):
+                 tail_order=False):
         """impl: "simt" (CUDA cores, paged_attn.cu), "tc" (tcgen05 tensor cores, one CTA per (sequence, split, KV head);
         chunk_tokens % 128 == 0) or "tcp" (the same engine as a persistent kernel of two CTAs per SM that walk the work items;
         chunk_tokens <= 1024, batch <= 256; meant for small batches, where it can use 512-token items without paying a CTA
-        start-up per item). tail_order ("tc" only): every sequence's last, partial chunk is scheduled after all full chunks, so
-        the CTAs that finish the launch alone on their SMs are short ones (not yet run on a GPU)."""
-        assert not tail_order or impl == "tc"
-        self.tail_order = tail_order
+        start-up per item). tail_order ("tc" only): True = every sequence's last, partial chunk is scheduled after all full
+        chunks, so the CTAs that finish the launch alone on their SMs are short ones; "fine" = that last part is also cut into
+        quarter chunks (chunk_tokens % 512 == 0; up to three partials more per sequence), so they are shorter still. Neither has
+        run on a GPU yet."""
+        assert tail_order in (False, True, "fine") and (not tail_order or impl == "tc")
+        assert tail_order != "fine" or chunk_tokens % 512 == 0
+        self.tail_order = 2 if tail_order == "fine" else int(bool(tail_order))
         assert impl in ("simt", "tc", "tcp") and (impl == "simt" or chunk_tokens % 128 == 0)
         assert impl != "tcp" or (chunk_tokens <= 1024 and max_batch <= 256)
         self.impl = impl
         self._C = load()
         self.device = torch.device(device)
         self.q_heads, self.kv_heads, self.chunk_tokens, self.max_ctx = q_heads, kv_heads, chunk_tokens, max_ctx
-        self.max_splits = (max_ctx + chunk_tokens - 1) // chunk_tokens
+        self.max_splits = max_ctx // chunk_tokens + 4 if self.tail_order == 2 else (max_ctx + chunk_tokens - 1) // chunk_tokens
         self.part_o = torch.empty((max_batch, q_heads, self.max_splits, 128), dtype=torch.float32, device=self.device)
         self.part_m = torch.empty((max_batch, q_heads, self.max_splits), dtype=torch.float32, device=self.device)
         self.part_l = torch.empty_like(self.part_m)
@@ -50,7 +53,7 @@ class PagedAttention:
                                   self.part_o, self.part_m, self.part_l, self.counters, self.status,
                                   (pool.data.numel() - layer * ls) // 128 if self.impl != "simt" else 0,
                                   **({"persistent_ctas": self._persistent} if self._persistent else {}),
-                                  **({"tail_order": True} if self.tail_order else {}))
+                                  **({"tail_order": self.tail_order} if self.tail_order else {}))
         return out
 
 

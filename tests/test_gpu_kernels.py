@@ -224,8 +224,8 @@ def test_memhog_duty_cycle_and_time_limit(ops):
     assert 0.3 < half["bytes_done"] / full["bytes_done"] < 0.75
 
 
-# "tc-tail" (partial chunks scheduled last) has not run on a GPU yet: opt in
-@pytest.mark.parametrize("impl", ["simt", "tc", "tcp"] + (["tc-tail"] if os.environ.get("SKYGDR_TEST_ATTN_TAIL") == "1" else []))
+# "tc-tail" (partial chunks scheduled last) and "tc-fine" (in quarter-chunk pieces) have not run on a GPU yet: opt in
+@pytest.mark.parametrize("impl", ["simt", "tc", "tcp"] + (["tc-tail", "tc-fine"] if os.environ.get("SKYGDR_TEST_ATTN_TAIL") == "1" else []))
 @pytest.mark.parametrize("kv_heads,q_heads", [(8, 32), (1, 4), (2, 4), (4, 4), (1, 8)])
 def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
     torch.manual_seed(1)
@@ -244,7 +244,8 @@ def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
         table[b, :nb] = perm[o:o + nb]
         o += nb
     q = torch.randn((B, q_heads, 128), dtype=torch.bfloat16, device="cuda")
-    attn = ops.PagedAttention("cuda", B, q_heads, kv_heads, max_ctx=4096, chunk_tokens=512, impl=impl.split("-")[0], tail_order=impl == "tc-tail")
+    attn = ops.PagedAttention("cuda", B, q_heads, kv_heads, max_ctx=4096, chunk_tokens=512, impl=impl.split("-")[0],
+                              tail_order={"tc-tail": True, "tc-fine": "fine"}.get(impl, False))
     for layer in (0, 1):
         out = attn(q, pool, layer, table, ctx, max_ctx=int(ctx.max()))
         ref = ops.paged_attn_reference(q, pool, layer, table, ctx)

@@ -234,3 +234,54 @@ def test_tensor_parallel_shards_reproduce_the_unsharded_forward_on_cpu_ranks(wor
     d = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
     assert d["world"] == world and d["covered"] and d["argmax_agrees"] and d["clear_rows"] > 0
     assert d["rel_err_max"] < 0.03, d             # bf16 rounding of per-rank partial sums is the only difference
+
+
+def _decode_attention_items(ctx, chunk, grid_z, mode):
+    """The (split, tok0, tok1) of every grid slot z of one sequence, as paged_attn_tc_kernel computes them
+    (skygdr_b200/csrc/kernels/paged_attn_tc.cu), and the number of partials the combine waits for."""
+    items, n_splits = [], (ctx + chunk - 1) // chunk
+    if mode == 2:
+        small, n_full = chunk // 4, ctx // chunk
+        n_small = (ctx - n_full * chunk + small - 1) // small
+        n_splits = n_full + n_small
+        for z in range(grid_z):
+            j = z - (grid_z - 4)
+            if j < 0 and z < n_full:
+                items.append((z, z * chunk, z * chunk + chunk))
+            elif 0 <= j < n_small:
+                items.append((n_full + j, n_full * chunk + j * small, min(ctx, n_full * chunk + (j + 1) * small)))
+    else:
+        for z in range(grid_z):
+            if mode == 1:
+                if z < n_splits - 1:
+                    split = z
+                elif z == grid_z - 1:
+                    split = n_splits - 1
+                else:
+                    continue
+            else:
+                split = z
+            if split * chunk < ctx:
+                items.append((split, split * chunk, min(ctx, (split + 1) * chunk)))
+    return items, n_splits
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_decode_attention_grid_orders_cover_every_token_once(mode):
+    """Default order, partial-chunk-last and quarter-chunk-pieces-last must all cut a sequence into the number of partials the
+    combine waits for, with distinct split indices below the scratch's max_splits and every token in exactly one piece."""
+    chunk, max_ctx = 1024, 16384 + 100
+    grid_z = max_ctx // chunk + 4 if mode == 2 else (max_ctx + chunk - 1) // chunk
+    max_splits = grid_z
+    longest_late = 0
+    for ctx in [1, 15, 127, 128, 129, 255, 256, 257, 1023, 1024, 1025, 1280, 1281, 2048, 2049, 3000, 5000, 16384, max_ctx]:
+        items, n_splits = _decode_attention_items(ctx, chunk, grid_z, mode)
+        assert len(items) == n_splits and sorted(i[0] for i in items) == list(range(n_splits)) and n_splits <= max_splits
+        covered = sorted((t0, t1) for _, t0, t1 in items)
+        assert covered[0][0] == 0 and covered[-1][1] == ctx and all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+        assert all(t0 % 128 == 0 and 0 < t1 - t0 <= chunk for _, t0, t1 in items)        # whole key tiles, whole pages
+        if mode == 2:
+            late = [t1 - t0 for s, t0, t1 in items if s >= ctx // chunk]
+            longest_late = max([longest_late] + late)
+    if mode == 2:
+        assert longest_late == chunk // 4                                                # what runs last is at most a quarter chunk
