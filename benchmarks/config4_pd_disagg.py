@@ -9,7 +9,7 @@ Requests (same seed on every rank): Poisson arrivals, input lengths log-normal (
 lengths uniform 128-1024 (scaled by --out-scale). Request i is prefilled on prefill rank i % P and decoded on decode
 rank i % D, in one of that rank's KV slots. Per request:
 
-  arrival -> (queue) -> prefill (this package's GEMMs / norm / RoPE+append; prompt attention through torch SDPA)
+  arrival -> (queue) -> prefill (this package's GEMMs / norm / RoPE+append and its tcgen05 prefill attention over the paged pool)
           -> kv_transfer: paged gather + token-major -> head-major + peer stores into the decode rank's pool; the
              kernel's last CTA publishes `first_token + 1` in the request's ready flag (release, system scope)
           -> decode rank sees the flag (acquire) and adds the sequence to its running batch -> first decode step = TTFT
