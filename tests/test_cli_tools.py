@@ -523,3 +523,37 @@ def test_tools_accept_every_flag_of_the_reference_program(tool):
     assert r.returncode == 0, r.stderr[-500:]
     missing = [f for f in _REFERENCE_FLAGS[tool].split() if f not in r.stdout]
     assert not missing, (tool, missing)
+
+
+def test_decode_variants_driver_isolates_failures_and_resumes(tmp_path):
+    """benchmarks/decode_variants.py runs every variant as its own process; here bench.py is replaced by a stand-in that
+    succeeds for the default engine, crashes for one option and is never started for an option that does not apply."""
+    import json
+
+    fake = tmp_path / "fake_bench.py"
+    fake.write_text(textwrap.dedent("""
+        import json, sys
+        a = sys.argv[1:]
+        if "--attn-order" in a and a[a.index("--attn-order") + 1] == "tail":
+            sys.exit(3)                                   # this variant dies
+        v = 2100.0 if "--fuse-norm" in a else 2000.0
+        print("noise before the line")
+        print(json.dumps({"value": v, "ms_per_step": 16000 / v, "e2e": {"value": v - 10}, "kernel_status": "OK", "gpu_launches": 330,
+                          "roofline": {"hbm_frac_of_measured": 0.7}, "clocks": {"sm_mhz": 1965}}))
+    """))
+    out = tmp_path / "variants.json"
+    cmd = [sys.executable, os.path.join(ROOT, "benchmarks", "decode_variants.py"), "--variants", "default,fuse_norm,tail,oneshot",
+           "--bench-cmd", f"{sys.executable} {fake}", "--out", str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=ENV, timeout=120)
+    assert r.returncode == 0, r.stderr
+    rows = json.load(open(out))["variants"]
+    assert rows["default"]["tok_s"] == 2000.0 and rows["fuse_norm"]["tok_s"] == 2100.0
+    assert rows["tail"]["error"] == "exit code 3" and rows["oneshot"]["skipped"] == "needs two or more GPUs"
+    assert "fuse_norm" in r.stdout and "1.050" in r.stdout                         # the table gives the ratio to the default engine
+    # resume: finished variants are kept, the failed one is tried again
+    fake.write_text(fake.read_text().replace("sys.exit(3)", "pass").replace("2000.0", "1.0"))
+    r = subprocess.run(cmd + ["--resume"], capture_output=True, text=True, env=ENV, timeout=120)
+    rows = json.load(open(out))["variants"]
+    assert rows["default"]["tok_s"] == 2000.0 and rows["tail"]["tok_s"] == 1.0
+    bad = subprocess.run(cmd[:3] + ["nonsense"], capture_output=True, text=True, env=ENV, timeout=60)
+    assert bad.returncode != 0 and "unknown variant" in bad.stderr
