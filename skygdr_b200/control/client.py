@@ -119,8 +119,17 @@ class FabricClient:
         reply, self._buf = self._buf.split(b"\n", 1)
         return reply.decode()
 
-    def register(self, name: str, priority: str | int, target_gbps: float, kind: Optional[str] = None) -> FlowHandle:
-        rep = parse_reply(self.request(f"REGISTER {name} {priority} {target_gbps} {kind or name}"))
+    def link(self, name: str, capacity_gbps: Optional[float] = None) -> Dict[str, str]:
+        """Defines a link (one shared capacity with its own policy pass, e.g. ``nvlink:gpu0`` at 700 GB/s), changes its
+        capacity, or just reports it. Flows name their link when they register; the default link always exists."""
+        rep = parse_reply(self.request(f"LINK {name}" + ("" if capacity_gbps is None else f" {capacity_gbps}")))
+        if rep.get("status") != "OK":
+            raise RuntimeError(f"LINK failed: {rep}")
+        return rep
+
+    def register(self, name: str, priority: str | int, target_gbps: float, kind: Optional[str] = None,
+                 link: Optional[str] = None) -> FlowHandle:
+        rep = parse_reply(self.request(f"REGISTER {name} {priority} {target_gbps} {kind or name}" + (f" link={link}" if link else "")))
         if rep.get("status") != "OK":
             raise RuntimeError(f"REGISTER failed: {rep}")
         path = rep.get("page")

@@ -13,7 +13,7 @@
 // What differs: the third argument names a fabric instead of an InfiniBand device. `tcp` moves the payload
 // to gpu_server over the session socket; `sim[:gbps]` charges each message its service time on a simulated
 // link (server_ip "-" then needs no server at all). And the flow can register with fabricd
-// (SKYGDR_DAEMON=host:port, SKYGDR_FLOW_NAME/PRIORITY/TARGET_GBPS): it then obeys the byte grants of its
+// (SKYGDR_DAEMON=host:port, SKYGDR_FLOW_NAME/PRIORITY/TARGET_GBPS/LINK): it then obeys the byte grants of its
 // credit page in addition to the legacy sleep pacing, and publishes its progress there.
 #include <signal.h>
 #include <sys/select.h>
@@ -163,7 +163,8 @@ int main(int argc, char** argv) {
             const char* pr = getenv("SKYGDR_FLOW_PRIORITY");
             const char* tg = getenv("SKYGDR_FLOW_TARGET_GBPS");
             std::string reply;
-            if (fabric_client.register_flow(nm ? nm : "kv_offload", pr ? pr : "besteffort", tg ? atof(tg) : 0.0, "", &reply)) {
+            const char* lk = getenv("SKYGDR_FLOW_LINK");
+            if (fabric_client.register_flow(nm ? nm : "kv_offload", pr ? pr : "besteffort", tg ? atof(tg) : 0.0, "", &reply, lk ? lk : "")) {
                 page = fabric_client.page();
                 fprintf(stderr, "[client] registered with fabricd: %s", reply.c_str());
             } else {

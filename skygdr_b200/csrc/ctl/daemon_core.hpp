@@ -111,8 +111,9 @@ struct DaemonConfig {
 
 class DaemonCore {
 public:
-    explicit DaemonCore(const DaemonConfig& cfg) : cfg_(cfg), reg_(cfg.lease_ns), policy_(make_policy(cfg.policy, cfg.pcfg)) {
-        if (!policy_) policy_ = make_policy("none", cfg.pcfg);
+    explicit DaemonCore(const DaemonConfig& cfg) : cfg_(cfg), reg_(cfg.lease_ns) {
+        if (!make_policy(cfg_.policy, cfg_.pcfg)) cfg_.policy = "none";
+        links_.push_back(Link{"default", cfg_.capacity_gbps, make_policy(cfg_.policy, cfg_.pcfg)});
     }
     ~DaemonCore() {
         for (auto& kv : state_) release_page(kv.second, /*at_exit=*/true);
@@ -131,21 +132,29 @@ public:
         const std::string& cmd = tok[0];
         char buf[512];
         if (cmd == "REGISTER") {
-            if (tok.size() < 4) return "ERR usage REGISTER <name> <priority> <target_gbps> [kind]\n";
+            if (tok.size() < 4) return "ERR usage REGISTER <name> <priority> <target_gbps> [kind] [link=<name>]\n";
             int prio;
             if (!parse_priority(tok[2], &prio)) return "ERR bad_priority\n";
             char* end = nullptr;
             double target = strtod(tok[3].c_str(), &end);
             if (end == tok[3].c_str() || *end || !(target >= 0) || !std::isfinite(target)) return "ERR bad_target\n";
-            int kind = tok.size() > 4 ? kind_from_name(tok[4]) : kind_from_name(tok[1]);
+            // optional tail, in either order: the flow's kind and the link whose capacity it shares (default: the first link)
+            int kind = kind_from_name(tok[1]), link = 0;
+            for (size_t i = 4; i < tok.size(); ++i) {
+                if (tok[i].compare(0, 5, "link=") == 0) {
+                    link = find_link(tok[i].substr(5));
+                    if (link < 0) return "ERR unknown_link\n";
+                } else kind = kind_from_name(tok[i]);
+            }
             uint32_t id = reg_.add(tok[1], prio, target, kind, now_ns);
             FlowState& st = state_[id];
+            st.link = link;
             st.smooth = WindowSmoother(cfg_.smooth_windows);
             st.bucket.burst_windows = cfg_.burst_windows;
             if (!attach_page(id, st)) { reg_.remove(id); state_.erase(id); return "ERR page_alloc\n"; }
             init_page(id, st, prio, target);
-            snprintf(buf, sizeof buf, "OK flow_id=%u page=%s lease_ms=%" PRIu64 " window_us=%" PRIu64 "\n", id,
-                     st.path.empty() ? "-" : st.path.c_str(), cfg_.lease_ns / 1000000, cfg_.window_ns / 1000);
+            snprintf(buf, sizeof buf, "OK flow_id=%u page=%s lease_ms=%" PRIu64 " window_us=%" PRIu64 " link=%s\n", id,
+                     st.path.empty() ? "-" : st.path.c_str(), cfg_.lease_ns / 1000000, cfg_.window_ns / 1000, links_[link].name.c_str());
             return buf;
         }
         if (cmd == "RENEW" || cmd == "UNREGISTER" || cmd == "BUDGET") {
@@ -169,19 +178,21 @@ public:
             std::ostringstream os;
             auto flows = reg_.snapshot();
             os << "OK n=" << flows.size();
-            for (auto& f : flows)
+            for (auto& f : flows) {
                 os << " " << f.id << ":" << f.name << ":" << f.priority << ":" << f.target_gbps << ":" << kind_name(f.kind)
                    << ":" << mode_name(f.mode);
+                auto it = state_.find(f.id);
+                if (it != state_.end() && it->second.link != 0) os << ":" << links_[it->second.link].name;   // only when not the default
+            }
             os << "\n";
             return os.str();
         }
         if (cmd == "POLICY") {
-            if (tok.size() < 2) { return std::string("OK policy=") + policy_->name() + "\n"; }
-            auto p = make_policy(tok[1], cfg_.pcfg);
-            if (!p) return "ERR unknown_policy\n";
-            policy_ = std::move(p);
+            if (tok.size() < 2) { return std::string("OK policy=") + links_[0].policy->name() + "\n"; }
+            if (!make_policy(tok[1], cfg_.pcfg)) return "ERR unknown_policy\n";
             cfg_.policy = tok[1];
-            return std::string("OK policy=") + policy_->name() + "\n";
+            for (auto& l : links_) l.policy = make_policy(cfg_.policy, cfg_.pcfg);     // every link runs its own instance
+            return std::string("OK policy=") + links_[0].policy->name() + "\n";
         }
         if (cmd == "WINDOW") {
             if (tok.size() < 2) { snprintf(buf, sizeof buf, "OK window_us=%" PRIu64 "\n", cfg_.window_ns / 1000); return buf; }
@@ -192,9 +203,40 @@ public:
             return buf;
         }
         if (cmd == "CAPACITY") {
-            if (tok.size() >= 2) { double c = atof(tok[1].c_str()); if (c > 0) cfg_.capacity_gbps = c; }
+            if (tok.size() >= 2) { double c = atof(tok[1].c_str()); if (c > 0) { cfg_.capacity_gbps = c; links_[0].capacity_gbps = c; } }
             snprintf(buf, sizeof buf, "OK capacity_gbps=%.3f\n", cfg_.capacity_gbps);
             return buf;
+        }
+        if (cmd == "LINK") {
+            // LINK <name> [capacity_gbps]: defines a link (or changes its capacity); without a capacity, reports it.
+            if (tok.size() < 2) return "ERR usage LINK <name> [capacity_gbps]\n";
+            int li = find_link(tok[1]);
+            if (tok.size() >= 3) {
+                char* end = nullptr;
+                const double c = strtod(tok[2].c_str(), &end);
+                if (end == tok[2].c_str() || *end || !(c > 0) || !std::isfinite(c)) return "ERR bad_capacity\n";
+                if (li < 0) {
+                    if (!valid_link_name(tok[1])) return "ERR bad_link_name\n";
+                    if (links_.size() >= 64) return "ERR too_many_links\n";
+                    links_.push_back(Link{tok[1], c, make_policy(cfg_.policy, cfg_.pcfg)});
+                    li = (int)links_.size() - 1;
+                } else {
+                    links_[li].capacity_gbps = c;
+                    if (li == 0) cfg_.capacity_gbps = c;
+                }
+            }
+            if (li < 0) return "ERR unknown_link\n";
+            size_t n = 0;
+            for (auto& kv : state_) n += kv.second.link == li;
+            snprintf(buf, sizeof buf, "OK link=%s capacity_gbps=%.3f flows=%zu\n", links_[li].name.c_str(), links_[li].capacity_gbps, n);
+            return buf;
+        }
+        if (cmd == "LINKS") {
+            std::ostringstream os;
+            os << "OK n=" << links_.size();
+            for (auto& l : links_) os << " " << l.name << ":" << l.capacity_gbps;
+            os << "\n";
+            return os.str();
         }
         if (cmd == "FLOW") {
             // FLOW <id> <legacy command>: manual override of one flow, same reply line as an end-point.
@@ -227,7 +269,8 @@ public:
         std::vector<FlowSignal> sig;
         double dt = last_step_ns_ ? double(now_ns - last_step_ns_) * 1e-9 : double(cfg_.window_ns) * 1e-9;
         if (dt <= 0) dt = double(cfg_.window_ns) * 1e-9;
-        double sum_gbps = 0;
+        std::vector<double> sum_gbps(links_.size(), 0.0);
+        std::vector<std::vector<size_t>> members(links_.size());       // flows of every link, in registry order
         for (auto& f : flows) {
             FlowState& st = state_[f.id];
             uint64_t done = st.page->completed_bytes;
@@ -241,47 +284,57 @@ public:
             s.backlog_bytes = st.page->backlog_bytes;
             s.active = s.backlog_bytes > 0 || delta > 0;
             if (!s.active) st.smooth.clear();
-            sum_gbps += s.inst_gbps;
+            const size_t li = (size_t)st.link < links_.size() ? (size_t)st.link : 0;
+            sum_gbps[li] += s.inst_gbps;
+            members[li].push_back(sig.size());
             sig.push_back(s);
         }
-        LinkSignal link;
-        link.capacity_gbps = cfg_.capacity_gbps;
-        link.util_pct = cfg_.external_util ? external_util_pct : 100.0 * sum_gbps / std::max(1e-9, cfg_.capacity_gbps);
-        auto dec = policy_->step(sig, link);
         std::vector<WindowLog> logs;
         uint64_t ts = unix_ms();
-        for (size_t i = 0; i < dec.size() && i < flows.size(); ++i) {
-            const FlowDecision& d = dec[i];
-            FlowState& st = state_[d.id];
-            int mode = d.mode;
-            double budget = d.budget_gbps;
-            std::string label = d.decision;
-            if (st.manual) {  // an operator pinned this flow with FLOW <id> LOWn / SLEEP
-                mode = st.ctl.mode();
-                budget = mode == SKY_MODE_HIGH ? -1.0
-                       : mode == SKY_MODE_CUSTOM ? sleep_to_budget(st.ctl.sleep_us())
-                       : cfg_.capacity_gbps * ladder_fraction(mode, cfg_.pcfg.low1_fraction);
-                label = "MANUAL";
+        // One policy pass per link: flows only compete with the flows that share their link's capacity.
+        for (size_t li = 0; li < links_.size(); ++li) {
+            if (members[li].empty()) continue;
+            std::vector<FlowSignal> lsig;
+            for (size_t i : members[li]) lsig.push_back(sig[i]);
+            LinkSignal link;
+            link.capacity_gbps = links_[li].capacity_gbps;
+            // a supplied utilisation (NVML) describes the first link; the others are summed from their flows
+            link.util_pct = (cfg_.external_util && li == 0) ? external_util_pct : 100.0 * sum_gbps[li] / std::max(1e-9, link.capacity_gbps);
+            auto dec = links_[li].policy->step(lsig, link);
+            for (size_t k = 0; k < dec.size() && k < members[li].size(); ++k) {
+                const size_t i = members[li][k];
+                const FlowDecision& d = dec[k];
+                FlowState& st = state_[d.id];
+                int mode = d.mode;
+                double budget = d.budget_gbps;
+                std::string label = d.decision;
+                if (st.manual) {  // an operator pinned this flow with FLOW <id> LOWn / SLEEP
+                    mode = st.ctl.mode();
+                    budget = mode == SKY_MODE_HIGH ? -1.0
+                           : mode == SKY_MODE_CUSTOM ? sleep_to_budget(st.ctl.sleep_us(), link.capacity_gbps)
+                           : link.capacity_gbps * ladder_fraction(mode, cfg_.pcfg.low1_fraction);
+                    label = "MANUAL";
+                }
+                SkyCreditPage* pg = st.page;
+                if (budget < 0) {
+                    pg->unlimited = 1;
+                    pg->budget_per_window = 0;
+                } else {
+                    // Leaving the unlimited state: bytes taken while ungated were never counted against a grant.
+                    if (pg->unlimited && pg->consumed_bytes > st.bucket.granted) st.bucket.granted = pg->consumed_bytes;
+                    uint64_t g = st.bucket.refill(budget, (uint64_t)(dt * 1e9), pg->consumed_bytes);
+                    pg->budget_per_window = (uint64_t)(budget * 1e9 * double(cfg_.window_ns) * 1e-9);
+                    __atomic_store_n(&pg->granted_bytes, g, __ATOMIC_RELEASE);
+                    pg->unlimited = 0;
+                }
+                pg->mode = (uint32_t)mode;
+                pg->window_ns = cfg_.window_ns;
+                __atomic_store_n(&pg->epoch, pg->epoch + 1, __ATOMIC_RELEASE);
+                reg_.update(d.id, [&](FlowInfo& f) { f.mode = mode; f.budget_gbps = budget; });
+                logs.push_back({window_id_, ts, d.id, flows[i].name, mode, label,
+                                budget < 0 ? -1.0 : budget * 1e9 * double(cfg_.window_ns) * 1e-9, sig[i].inst_gbps,
+                                sig[i].smooth_gbps, sig[i].backlog_bytes, link.util_pct, pg->granted_bytes});
             }
-            SkyCreditPage* pg = st.page;
-            if (budget < 0) {
-                pg->unlimited = 1;
-                pg->budget_per_window = 0;
-            } else {
-                // Leaving the unlimited state: bytes taken while ungated were never counted against a grant.
-                if (pg->unlimited && pg->consumed_bytes > st.bucket.granted) st.bucket.granted = pg->consumed_bytes;
-                uint64_t g = st.bucket.refill(budget, (uint64_t)(dt * 1e9), pg->consumed_bytes);
-                pg->budget_per_window = (uint64_t)(budget * 1e9 * double(cfg_.window_ns) * 1e-9);
-                __atomic_store_n(&pg->granted_bytes, g, __ATOMIC_RELEASE);
-                pg->unlimited = 0;
-            }
-            pg->mode = (uint32_t)mode;
-            pg->window_ns = cfg_.window_ns;
-            __atomic_store_n(&pg->epoch, pg->epoch + 1, __ATOMIC_RELEASE);
-            reg_.update(d.id, [&](FlowInfo& f) { f.mode = mode; f.budget_gbps = budget; });
-            logs.push_back({window_id_, ts, d.id, flows[i].name, mode, label,
-                            budget < 0 ? -1.0 : budget * 1e9 * double(cfg_.window_ns) * 1e-9, sig[i].inst_gbps,
-                            sig[i].smooth_gbps, sig[i].backlog_bytes, link.util_pct, pg->granted_bytes});
         }
         last_step_ns_ = now_ns;
         ++window_id_;
@@ -289,9 +342,9 @@ public:
     }
 
     // `SLEEP <us>` as a budget: a chunk of the window's worth of bytes every (service + sleep).
-    double sleep_to_budget(uint32_t sleep_us) const {
+    double sleep_to_budget(uint32_t sleep_us, double capacity_gbps) const {
         double win_s = double(cfg_.window_ns) * 1e-9;
-        double chunk = cfg_.capacity_gbps * 1e9 * win_s;  // bytes the link moves in one window
+        double chunk = capacity_gbps * 1e9 * win_s;  // bytes the link moves in one window
         double service = win_s;
         return chunk / (service + sleep_us * 1e-6) / 1e9;
     }
@@ -310,8 +363,11 @@ public:
     // ---- snapshot / restore (JSON, one flow per array element) ----
     std::string snapshot_json() const {
         std::ostringstream os;
-        os << "{\"policy\":\"" << policy_->name() << "\",\"window_ns\":" << cfg_.window_ns << ",\"capacity_gbps\":"
-           << cfg_.capacity_gbps << ",\"window_id\":" << window_id_ << ",\"flows\":[";
+        os << "{\"policy\":\"" << links_[0].policy->name() << "\",\"window_ns\":" << cfg_.window_ns << ",\"capacity_gbps\":"
+           << cfg_.capacity_gbps << ",\"window_id\":" << window_id_ << ",\"links\":[";
+        for (size_t i = 0; i < links_.size(); ++i)
+            os << (i ? "," : "") << "{\"link_name\":\"" << links_[i].name << "\",\"link_capacity_gbps\":" << links_[i].capacity_gbps << "}";
+        os << "],\"flows\":[";
         bool first = true;
         for (auto& f : reg_.snapshot()) {
             auto it = state_.find(f.id);
@@ -320,7 +376,8 @@ public:
             os << "{\"id\":" << f.id << ",\"name\":\"" << f.name << "\",\"priority\":" << f.priority << ",\"target_gbps\":"
                << f.target_gbps << ",\"kind\":\"" << kind_name(f.kind) << "\",\"mode\":\"" << mode_name(f.mode)
                << "\",\"budget_gbps\":" << f.budget_gbps << ",\"page\":\"" << (it != state_.end() ? it->second.path : "")
-               << "\",\"granted\":" << (it != state_.end() ? it->second.page->granted_bytes : 0) << "}";
+               << "\",\"granted\":" << (it != state_.end() ? it->second.page->granted_bytes : 0) << ",\"link\":\""
+               << links_[it != state_.end() ? it->second.link : 0].name << "\"}";
         }
         os << "]}";
         return os.str();
@@ -340,7 +397,30 @@ public:
             return obj.substr(p, e - p);
         };
         std::string pol = field(js, "policy");
-        if (!pol.empty()) { auto p = make_policy(pol, cfg_.pcfg); if (p) { policy_ = std::move(p); cfg_.policy = pol; } }
+        if (!pol.empty() && make_policy(pol, cfg_.pcfg)) {
+            cfg_.policy = pol;
+            for (auto& l : links_) l.policy = make_policy(pol, cfg_.pcfg);
+        }
+        // links first (the array sits before the flows in the snapshot), so that the flows find theirs
+        size_t lk = js.find("\"links\":[");
+        if (lk != std::string::npos && lk < arr) {
+            size_t q = lk + 9;
+            while (true) {
+                size_t b = js.find('{', q), close = js.find(']', q);
+                if (b == std::string::npos || close < b) break;
+                size_t e = js.find('}', b);
+                if (e == std::string::npos) return false;
+                std::string obj = js.substr(b, e - b + 1);
+                const std::string name = field(obj, "link_name");
+                const double cap = atof(field(obj, "link_capacity_gbps").c_str());
+                if (valid_link_name(name) && cap > 0) {
+                    int li = find_link(name);
+                    if (li < 0 && links_.size() < 64) links_.push_back(Link{name, cap, make_policy(cfg_.policy, cfg_.pcfg)});
+                    else if (li >= 0) { links_[li].capacity_gbps = cap; if (li == 0) cfg_.capacity_gbps = cap; }
+                }
+                q = e + 1;
+            }
+        }
         size_t p = arr + 9;
         while (true) {
             size_t b = js.find('{', p);
@@ -364,6 +444,7 @@ public:
             FlowState& st = state_[f.id];
             st.smooth = WindowSmoother(cfg_.smooth_windows);
             st.bucket.burst_windows = cfg_.burst_windows;
+            st.link = std::max(0, find_link(field(obj, "link")));       // snapshots from before links existed: the first link
             if (!attach_page(f.id, st)) return false;
             if (st.page->magic != SKYGDR_CREDIT_MAGIC) init_page(f.id, st, f.priority, f.target_gbps);
             st.bucket.granted = st.page->granted_bytes;
@@ -379,7 +460,8 @@ public:
     const DaemonConfig& config() const { return cfg_; }
     uint64_t windows() const { return window_id_; }
     uint64_t expired() const { return expired_; }
-    const char* policy_name() const { return policy_->name(); }
+    const char* policy_name() const { return links_[0].policy->name(); }
+    size_t link_count() const { return links_.size(); }
 
 private:
     struct FlowState {
@@ -391,7 +473,26 @@ private:
         TokenBucket bucket;
         ControlState ctl;
         bool manual = false;
+        int link = 0;              // index into links_: the capacity this flow shares
     };
+    // A link is one shared capacity (a GPU's NVLink egress, its PCIe link, ...) with its own policy state. Link 0, "default",
+    // always exists and carries the configured capacity; more are defined with `LINK <name> <capacity_gbps>`.
+    struct Link {
+        std::string name;
+        double capacity_gbps;
+        std::unique_ptr<Policy> policy;
+    };
+    int find_link(const std::string& name) const {
+        for (size_t i = 0; i < links_.size(); ++i)
+            if (links_[i].name == name) return (int)i;
+        return -1;
+    }
+    static bool valid_link_name(const std::string& n) {
+        if (n.empty() || n.size() > 32) return false;
+        for (char c : n)
+            if (!(isalnum((unsigned char)c) || c == '_' || c == '-' || c == '.' || c == ':' || c == '>')) return false;
+        return true;
+    }
 
     bool attach_page(uint32_t id, FlowState& st) {
         if (cfg_.page_dir.empty()) {
@@ -443,7 +544,7 @@ public:
 private:
     DaemonConfig cfg_;
     FlowRegistry reg_;
-    std::unique_ptr<Policy> policy_;
+    std::vector<Link> links_;
     std::map<uint32_t, FlowState> state_;
     uint64_t window_id_ = 0, last_step_ns_ = 0, expired_ = 0;
     bool keep_pages_ = false;

@@ -3,6 +3,7 @@
 //   fabricd --port 7070 [--bind 127.0.0.1] [--policy target_track|ladder|static|none]
 //           [--window_us 5000] [--capacity_gbps 64] [--lease_ms 5000] [--log PATH.csv]
 //           [--snapshot PATH.json] [--restore PATH.json] [--gpu N --util_source pcie_rx|pcie_tx|sum]
+//           [--link NAME=GBPS ...]   more links beside the default one (each a shared capacity with its own policy pass)
 //           [--enter_ratio 0.65 --exit_ratio 0.80 --util_threshold_pct 85 --enter_windows 1 --exit_windows 2]
 //
 // A TCP line server (one or more commands per connection, each answered by one
@@ -53,6 +54,7 @@ int main(int argc, char** argv) {
     DaemonConfig cfg;
     int port = 7070, gpu = -1;
     std::string bind_ip = "127.0.0.1", log_path, snap_path, restore_path, util_source = "sum";
+    std::vector<std::pair<std::string, std::string>> link_defs;
     for (int i = 1; i < argc; ++i) {
         std::string k = argv[i];
         std::string v;
@@ -86,6 +88,11 @@ int main(int argc, char** argv) {
             else { fprintf(stderr, "fabricd: --dead_policy is stall, unpaced or static\n"); return 2; }
         }
         else if (k == "--dead_fallback_gbps") cfg.dead_fallback_gbps = atof(v.c_str());
+        else if (k == "--link") {
+            const size_t e = v.rfind('=');
+            if (e == std::string::npos || e == 0) { fprintf(stderr, "fabricd: --link NAME=GBPS\n"); return 2; }
+            link_defs.emplace_back(v.substr(0, e), v.substr(e + 1));
+        }
         else { fprintf(stderr, "fabricd: unknown flag %s\n", k.c_str()); return 2; }
     }
     if (cfg.window_ns < 100000) { fprintf(stderr, "fabricd: window below 100 us\n"); return 2; }
@@ -93,6 +100,10 @@ int main(int argc, char** argv) {
     cfg.external_util = gpu >= 0 && util_source != "sum";
     DaemonCore core(cfg);
     core.keep_pages_on_exit(!snap_path.empty());
+    for (auto& ld : link_defs) {
+        const std::string rep = core.handle_line("LINK " + ld.first + " " + ld.second, mono_ns());
+        if (rep.compare(0, 2, "OK") != 0) { fprintf(stderr, "fabricd: --link %s=%s: %s", ld.first.c_str(), ld.second.c_str(), rep.c_str()); return 2; }
+    }
     if (!restore_path.empty()) {
         std::ifstream in(restore_path);
         std::stringstream ss;

@@ -33,10 +33,12 @@ public:
 
     // Registers the flow; on success flow_id() is set and page() is the mapped credit page (nullptr when the daemon keeps
     // its pages on the heap). `reply` receives the daemon's answer line either way.
-    bool register_flow(const std::string& name, const std::string& priority, double target_gbps, const std::string& kind, std::string* reply) {
-        char line[256];
-        const int n = snprintf(line, sizeof line, "REGISTER %s %s %g %s\n", name.c_str(), priority.c_str(), target_gbps,
-                               kind.empty() ? name.c_str() : kind.c_str());
+    // `link` names the shared capacity the flow competes on (a link defined at the daemon); empty = the default link.
+    bool register_flow(const std::string& name, const std::string& priority, double target_gbps, const std::string& kind, std::string* reply,
+                       const std::string& link = "") {
+        char line[320];
+        const int n = snprintf(line, sizeof line, "REGISTER %s %s %g %s%s%s\n", name.c_str(), priority.c_str(), target_gbps,
+                               kind.empty() ? name.c_str() : kind.c_str(), link.empty() ? "" : " link=", link.c_str());
         std::string rep;
         if (!request(std::string(line, (size_t)n), &rep)) return false;
         if (reply) *reply = rep;

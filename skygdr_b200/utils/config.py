@@ -31,6 +31,7 @@ class FlowSettings:
     priority: str = "high"
     target_gbps: float = 40.0
     kind: str = "kv_transfer"
+    link: str = ""                 # the shared capacity the flow competes on; "" = the daemon's default link
 
 
 @dataclass
@@ -54,6 +55,7 @@ class RuntimeConfig:
     policy: PolicySettings = field(default_factory=PolicySettings)
     control: ControlPortSettings = field(default_factory=ControlPortSettings)
     flows: List[FlowSettings] = field(default_factory=lambda: [FlowSettings(), FlowSettings("kv_offload", "besteffort", 0.0, "kv_offload")])
+    links: Dict[str, float] = field(default_factory=dict)     # more links beside the default one: name -> capacity in GB/s
 
     # ---- JSON ----
     def to_json(self) -> str:
@@ -111,4 +113,5 @@ class RuntimeConfig:
         return ["--port", str(self.daemon_port), "--policy", p.name, "--window_us", str(self.window_us), "--capacity_gbps",
                 str(self.capacity_gbps), "--lease_ms", str(self.lease_ms), "--enter_ratio", str(p.enter_ratio), "--exit_ratio",
                 str(p.exit_ratio), "--util_threshold_pct", str(p.util_threshold_pct), "--enter_windows", str(p.enter_windows),
-                "--exit_windows", str(p.exit_windows), "--low1_fraction", str(p.low1_fraction)]
+                "--exit_windows", str(p.exit_windows), "--low1_fraction", str(p.low1_fraction)] + \
+            [x for name, cap in self.links.items() for x in ("--link", f"{name}={cap}")]

@@ -557,3 +557,23 @@ def test_decode_variants_driver_isolates_failures_and_resumes(tmp_path):
     assert rows["default"]["tok_s"] == 2000.0 and rows["tail"]["tok_s"] == 1.0
     bad = subprocess.run(cmd[:3] + ["nonsense"], capture_output=True, text=True, env=ENV, timeout=60)
     assert bad.returncode != 0 and "unknown variant" in bad.stderr
+
+
+@pytest.mark.realtime
+def test_compat_client_registers_on_the_link_named_in_its_environment():
+    with FabricDaemon(window_us=2000, capacity_gbps=64.0, lease_ms=3000, extra=["--link", "roce0=12.5"]) as d:
+        env = dict(ENV, SKYGDR_DAEMON=f"127.0.0.1:{d.port}", SKYGDR_FLOW_NAME="kv_offload", SKYGDR_FLOW_LINK="roce0")
+        p = subprocess.Popen([f"{BIN}/cpu_client", "-", "0", "sim:1", "3000", "64K", "write", "1", "0"], stdout=subprocess.PIPE,
+                             stderr=subprocess.PIPE, text=True, env=env)
+        try:
+            with FabricClient(port=d.port) as c:
+                t0 = time.time()
+                while "kv_offload" not in c.request("FLOWS") and time.time() - t0 < 5:
+                    time.sleep(0.02)
+                assert "1:kv_offload:0:0:kv_offload:HIGH:roce0" in c.request("FLOWS")
+                assert c.link("roce0")["flows"] == "1"
+            out, err = p.communicate(timeout=60)
+        finally:
+            if p.poll() is None:
+                p.kill()
+        assert p.returncode == 0 and "link=roce0" in err

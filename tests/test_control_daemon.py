@@ -239,3 +239,36 @@ def _try(fn):
         return fn()
     except OSError:
         return None
+
+
+def test_daemon_process_with_two_links(tmp_path):
+    """fabricd --link: flows registered over TCP on different links are paced independently, and the snapshot written at
+    SIGTERM restores links and membership in a new daemon."""
+    snap = str(tmp_path / "snap.json")
+    with FabricDaemon(policy="target_track", window_us=2000, capacity_gbps=64.0, snapshot=snap,
+                      extra=["--link", "nvlink:gpu0=700", "--link=pcie:gpu1=55"]) as d:
+        with FabricClient(port=d.port) as c:
+            assert c.request("LINKS") == "OK n=3 default:64 nvlink:gpu0:700 pcie:gpu1:55"
+            hi = c.register("kv_transfer", "high", 600.0, link="nvlink:gpu0")
+            be = c.register("kv_bursts", "besteffort", 0.0, kind="kv_transfer", link="nvlink:gpu0")
+            off = c.register("kv_offload", "besteffort", 0.0)
+            with pytest.raises(RuntimeError):
+                c.register("x", "high", 1.0, link="missing")
+            assert c.link("nvlink:gpu0")["flows"] == "2" and c.link("pcie:gpu1", 60.0)["capacity_gbps"] == "60.000"
+            # the protected flow has backlog; the best-effort flows report steady progress on their own links
+            done = 0
+            t_end = time.time() + 0.25
+            while time.time() < t_end:
+                done += 6_000_000                                    # about 6 MB per millisecond on the default link
+                hi.report(0, 0, 4_000_000_000)
+                be.report(done * 100, done * 100, 1 << 40)           # ~600 GB/s on the 700 GB/s link
+                off.report(done, done, 1 << 40)
+                time.sleep(0.001)
+            assert be.grant()["unlimited"] == 0 and be.grant()["budget_per_window"] > 0     # held to what the link has left
+            assert off.grant()["unlimited"] == 1                                             # other link: never touched
+    assert d.proc.returncode == 0 and os.path.exists(snap)
+    with FabricDaemon(window_us=2000, restore=snap) as d2:
+        with FabricClient(port=d2.port) as c:
+            assert c.request("LINKS") == "OK n=3 default:64 nvlink:gpu0:700 pcie:gpu1:60"
+            flows = c.request("FLOWS")
+            assert "kv_transfer:100:600:kv_transfer" in flows and flows.count(":nvlink:gpu0") == 2

@@ -286,3 +286,42 @@ def test_native_page_pacer_grants_at_its_rate_and_lets_a_flow_catch_up(ctl):
     rate = (page[1] - g0) / dt / 1e9
     assert 0.7 < rate < 1.3, rate
     assert page[2] >= pacer.windows > 50 and page[5] & 0xffffffff00000000 == 0      # epoch per window; `unlimited` (high half of word 5) off
+
+
+def test_flows_on_different_links_do_not_take_bandwidth_from_one_another(ctl):
+    """Links: each is one shared capacity with its own policy pass. A protected NVLink flow must throttle the best-effort
+    flow that shares its link and leave alone the one on the PCIe link, whatever that one is doing."""
+    d = _core(ctl, capacity_gbps=64.0)
+    assert d.handle_line("LINKS", 0) == "OK n=1 default:64\n"
+    assert d.handle_line("LINK nvlink:gpu0 700", 0) == "OK link=nvlink:gpu0 capacity_gbps=700.000 flows=0\n"
+    assert d.handle_line("LINK bad/name 10", 0) == "ERR bad_link_name\n"
+    assert d.handle_line("LINK nvlink:gpu0 -5", 0) == "ERR bad_capacity\n"
+    assert d.handle_line("LINK nope", 0) == "ERR unknown_link\n"
+    assert d.handle_line("REGISTER x high 1 link=nope", 0) == "ERR unknown_link\n" and d.n_flows == 0
+    assert d.handle_line("REGISTER kv_transfer high 600 link=nvlink:gpu0", 0).rstrip().endswith("link=nvlink:gpu0")
+    assert d.handle_line("REGISTER kv_bursts besteffort 0 kv_transfer link=nvlink:gpu0", 0).startswith("OK flow_id=2")
+    assert d.handle_line("REGISTER kv_offload besteffort 0", 0).rstrip().endswith("link=default")       # PCIe: the default link
+    assert d.handle_line("LINK nvlink:gpu0", 0) == "OK link=nvlink:gpu0 capacity_gbps=700.000 flows=2\n"
+    assert d.handle_line("FLOWS", 0).split()[2:] == ["1:kv_transfer:100:600:kv_transfer:HIGH:nvlink:gpu0",
+                                                     "2:kv_bursts:0:0:kv_transfer:HIGH:nvlink:gpu0", "3:kv_offload:0:0:kv_offload:HIGH"]
+    win = 5_000_000
+    d.step_window(win)
+    # the protected flow has backlog; both best-effort flows run flat out on their own links
+    d.report_usage(1, 0, 0, 4_000_000_000)
+    d.report_usage(2, 3_400_000_000, 3_400_000_000, 1 << 40)          # 680 GB/s on the NVLink link
+    d.report_usage(3, 300_000_000, 300_000_000, 1 << 40)              # 60 GB/s on the 64 GB/s default link
+    logs = {l.flow: l for l in d.step_window(2 * win)}
+    assert logs["kv_bursts"].decision in ("RESERVE", "DECREASE")
+    assert logs["kv_bursts"].budget_bytes == pytest.approx((700 - 600) * 1e9 * 0.005, rel=0.6)           # what the link has left
+    assert logs["kv_offload"].budget_bytes == -1.0 and d.page_fields(3)["unlimited"] == 1               # other link: untouched
+    assert logs["kv_bursts"].link_util_pct == pytest.approx(100 * 680 / 700, rel=0.02)
+    assert logs["kv_offload"].link_util_pct == pytest.approx(100 * 60 / 64, rel=0.02)
+    # capacity of a link can be changed while flows run; the default link follows CAPACITY as before
+    assert d.handle_line("LINK nvlink:gpu0 900", 0).startswith("OK link=nvlink:gpu0 capacity_gbps=900.000 flows=2")
+    assert d.handle_line("CAPACITY 32", 0) == "OK capacity_gbps=32.000\n" and d.handle_line("LINKS", 0) == "OK n=2 default:32 nvlink:gpu0:900\n"
+    # snapshot and restore keep links and membership
+    d2 = _core(ctl)
+    assert d2.restore_json(d.snapshot_json(), 0)
+    assert d2.handle_line("LINKS", 0) == "OK n=2 default:32 nvlink:gpu0:900\n"
+    assert d2.handle_line("LINK nvlink:gpu0", 0).endswith("flows=2\n")
+    assert "3:kv_offload:0:0:kv_offload:HIGH" in d2.handle_line("FLOWS", 0) and "2:kv_bursts:0:0:kv_transfer:CUSTOM:nvlink:gpu0" in d2.handle_line("FLOWS", 0)   # throttled when the snapshot was taken

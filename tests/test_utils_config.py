@@ -19,6 +19,9 @@ def test_round_trip_overrides_and_env():
     assert c3.control.port == 7001 and c3.control.low_sleep_us == 250 and (c3.daemon_host, c3.daemon_port) == ("10.0.0.1", 7171)
     args = c2.daemon_args()
     assert args[args.index("--policy") + 1] == "ladder" and args[args.index("--window_us") + 1] == "1000"
+    c4 = RuntimeConfig.from_dict({"links": {"nvlink:gpu0": 700.0}, "flows": [{"name": "kv_transfer", "link": "nvlink:gpu0"}]})
+    assert c4.daemon_args()[-2:] == ["--link", "nvlink:gpu0=700.0"] and c4.flows[0].link == "nvlink:gpu0"
+    assert RuntimeConfig.from_json(c4.to_json()) == c4
 
 
 def test_daemon_accepts_the_generated_arguments(tmp_path):
