@@ -215,6 +215,7 @@ PYBIND11_MODULE(_ctl, m) {
         .def_property_readonly("windows", &DaemonCore::windows)
         .def_property_readonly("expired", &DaemonCore::expired)
         .def_property_readonly("policy_name", [](const DaemonCore& d) { return std::string(d.policy_name()); })
+        .def_property_readonly("link_count", &DaemonCore::link_count)
         .def_property_readonly("n_flows", [](DaemonCore& d) { return d.registry().size(); })
         .def_static("csv_header", [] { return std::string(DaemonCore::window_csv_header()); })
         // Usage half of a flow's page, as the data path would write it (tests, in-process flows).
