@@ -131,6 +131,7 @@ PYBIND11_MODULE(_ctl, m) {
         .def_readwrite("kind", &SimFlowSpec::kind)
         .def_readwrite("backlogged", &SimFlowSpec::backlogged)
         .def_readwrite("offered_gbps", &SimFlowSpec::offered_gbps)
+        .def_readwrite("contended_efficiency", &SimFlowSpec::contended_efficiency)
         .def("set_arrivals", [](SimFlowSpec& s, const std::vector<std::pair<double, uint64_t>>& a) {
             s.arrivals.clear();
             for (auto& p : a) s.arrivals.push_back({p.first, p.second});

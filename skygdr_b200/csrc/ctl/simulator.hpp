@@ -29,6 +29,11 @@ struct SimFlowSpec {
     int kind = FLOW_OTHER;
     bool backlogged = false;          // always has bytes to send
     double offered_gbps = -1;         // cap on what the source can offer (<0: none)
+    // Useful fraction of the flow's link share while at least one other flow is moving bytes in the same tick (1 = the
+    // flow does not suffer from company). Models measured asymmetries such as the reference's: a copy-engine transfer keeps
+    // its rate next to an HBM-bound decoder, the decoder loses about 10 %
+    // (llm_problem_analysis/bench_results_20260515_092702/summary.txt:13-25). The link time is used up either way.
+    double contended_efficiency = 1.0;
     std::vector<Arrival> arrivals;    // finite requests, FIFO, one transfer at a time
 };
 
@@ -176,13 +181,16 @@ inline SimResult run_simulation(const SimConfig& cfg, const std::vector<SimFlowS
                 demand[i] = std::min(want, cap_Bps * tick_s);
             }
             std::vector<double> alloc = maxmin_fair(demand, cap_Bps * tick_s);
+            int movers = 0;
+            for (size_t i = 0; i < n; ++i) movers += alloc[i] > 0;
             for (size_t i = 0; i < n; ++i) {
                 Live& l = live[i];
                 double b = alloc[i];
                 if (b <= 0) continue;
+                window_link_bytes += b;                              // the share of the link is spent in full
+                if (movers > 1) b *= std::min(1.0, std::max(0.0, specs[i].contended_efficiency));
                 l.window_bytes += b;
                 res.bytes_moved[i] += b;
-                window_link_bytes += b;
                 if (l.window_budget_left >= 0) l.window_budget_left -= b;
                 if (!specs[i].backlogged) {
                     l.front_left -= b;

@@ -164,3 +164,23 @@ def test_kv_bytes_and_poisson(ctl):
     vals = [rng.lognormal(8192, 0.8, 1024, 32768) for _ in range(20000)]
     assert min(vals) >= 1024 and max(vals) <= 32768
     assert sorted(vals)[10000] == pytest.approx(8192, rel=0.05)
+
+
+def test_contended_efficiency_costs_goodput_only_in_company(ctl):
+    """A flow with contended_efficiency 0.9 (the reference's HBM-bound decoder next to an inbound copy) delivers 90 % of its
+    link share while another flow is moving bytes and all of it when alone; the link time is spent either way."""
+    def run(flows):
+        cfg = ctl.SimConfig()
+        cfg.capacity_gbps, cfg.duration_s, cfg.drain_s, cfg.policy = 64.0, 1.0, 0.0, "none"
+        specs = []
+        for name, eff in flows:
+            s = ctl.SimFlowSpec()
+            s.name, s.backlogged, s.contended_efficiency = name, True, eff
+            specs.append(s)
+        return ctl.run_simulation(cfg, specs)
+
+    both = run([("copy", 1.0), ("decode", 0.9)])
+    assert both.bytes_moved[0] == pytest.approx(32e9, rel=0.01) and both.bytes_moved[1] == pytest.approx(0.9 * 32e9, rel=0.01)
+    assert both.link_bytes == pytest.approx(64e9, rel=0.01)                       # the link was busy all the time
+    alone = run([("decode", 0.9)])
+    assert alone.bytes_moved[0] == pytest.approx(64e9, rel=0.01)
