@@ -132,6 +132,7 @@ PYBIND11_MODULE(_ctl, m) {
         .def_readwrite("backlogged", &SimFlowSpec::backlogged)
         .def_readwrite("offered_gbps", &SimFlowSpec::offered_gbps)
         .def_readwrite("contended_efficiency", &SimFlowSpec::contended_efficiency)
+        .def_readwrite("link", &SimFlowSpec::link)
         .def("set_arrivals", [](SimFlowSpec& s, const std::vector<std::pair<double, uint64_t>>& a) {
             s.arrivals.clear();
             for (auto& p : a) s.arrivals.push_back({p.first, p.second});
@@ -140,6 +141,7 @@ PYBIND11_MODULE(_ctl, m) {
     py::class_<SimConfig>(m, "SimConfig")
         .def(py::init<>())
         .def_readwrite("capacity_gbps", &SimConfig::capacity_gbps)
+        .def_readwrite("more_links_gbps", &SimConfig::more_links_gbps)
         .def_readwrite("window_ms", &SimConfig::window_ms)
         .def_readwrite("tick_ms", &SimConfig::tick_ms)
         .def_readwrite("duration_s", &SimConfig::duration_s)

@@ -1,4 +1,4 @@
-// CPU fabric simulator: a shared link, registered flows, and the
+// CPU fabric simulator: one or more shared links, registered flows, and the
 // signal -> policy -> action loop running on simulated time.
 //
 // The reference has no simulator; its loop needs two hosts and a RoCE NIC
@@ -13,6 +13,7 @@
 #include <algorithm>
 #include <cmath>
 #include <deque>
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -34,11 +35,13 @@ struct SimFlowSpec {
     // its rate next to an HBM-bound decoder, the decoder loses about 10 %
     // (llm_problem_analysis/bench_results_20260515_092702/summary.txt:13-25). The link time is used up either way.
     double contended_efficiency = 1.0;
+    int link = 0;                     // which of the simulated links the flow uses (0 = SimConfig::capacity_gbps)
     std::vector<Arrival> arrivals;    // finite requests, FIFO, one transfer at a time
 };
 
 struct SimConfig {
     double capacity_gbps = 64.0;
+    std::vector<double> more_links_gbps;   // capacities of links 1, 2, ...: each is shared only by the flows that name it
     double window_ms = 5.0;
     double tick_ms = 0.25;
     double duration_s = 10.0;
@@ -107,8 +110,19 @@ inline std::vector<double> maxmin_fair(const std::vector<double>& demand, double
 inline SimResult run_simulation(const SimConfig& cfg, const std::vector<SimFlowSpec>& specs) {
     SimResult res;
     const size_t n = specs.size();
-    auto policy = make_policy(cfg.policy, cfg.pcfg);
-    if (!policy) policy = make_policy("none", cfg.pcfg);
+    // links: capacity, member flows, one policy instance each (as in the daemon)
+    std::vector<double> link_cap{cfg.capacity_gbps};
+    for (double c : cfg.more_links_gbps) link_cap.push_back(c > 0 ? c : cfg.capacity_gbps);
+    const size_t n_links = link_cap.size();
+    std::vector<std::vector<size_t>> members(n_links);
+    for (size_t i = 0; i < n; ++i) members[(specs[i].link >= 0 && (size_t)specs[i].link < n_links) ? (size_t)specs[i].link : 0].push_back(i);
+    std::vector<std::unique_ptr<Policy>> policies;
+    for (size_t l = 0; l < n_links; ++l) {
+        auto pol = make_policy(cfg.policy, cfg.pcfg);
+        if (!pol) pol = make_policy("none", cfg.pcfg);
+        policies.push_back(std::move(pol));
+    }
+    auto link_of = [&](size_t i) { return (specs[i].link >= 0 && (size_t)specs[i].link < n_links) ? (size_t)specs[i].link : (size_t)0; };
 
     struct Live {
         std::deque<SimRequestRecord> queue;  // arrived, unfinished (front = in flight)
@@ -130,11 +144,10 @@ inline SimResult run_simulation(const SimConfig& cfg, const std::vector<SimFlowS
 
     const double tick_s = cfg.tick_ms * 1e-3, win_s = cfg.window_ms * 1e-3;
     const int ticks_per_window = std::max(1, (int)std::llround(cfg.window_ms / cfg.tick_ms));
-    const double cap_Bps = cfg.capacity_gbps * 1e9;
     double t = 0;
     uint64_t window_id = 0;
-    double window_link_bytes = 0;
-    std::vector<FlowDecision> last_dec;
+    std::vector<double> window_link_bytes(n_links, 0.0);
+    std::vector<std::vector<FlowDecision>> last_dec(n_links);
 
     auto all_done = [&]() {
         for (size_t i = 0; i < n; ++i) {
@@ -156,7 +169,7 @@ inline SimResult run_simulation(const SimConfig& cfg, const std::vector<SimFlowS
             }
             l.window_bytes = 0;
         }
-        window_link_bytes = 0;
+        std::fill(window_link_bytes.begin(), window_link_bytes.end(), 0.0);
         // ---- ticks ----
         for (int k = 0; k < ticks_per_window; ++k) {
             // arrivals up to the end of this tick become visible at its start + their offset
@@ -174,21 +187,28 @@ inline SimResult run_simulation(const SimConfig& cfg, const std::vector<SimFlowS
                 Live& l = live[i];
                 double want;
                 bool past_end = t >= cfg.duration_s;
-                if (specs[i].backlogged) want = past_end ? 0.0 : cap_Bps * tick_s;
+                const double link_tick = link_cap[link_of(i)] * 1e9 * tick_s;
+                if (specs[i].backlogged) want = past_end ? 0.0 : link_tick;
                 else want = l.queue.empty() ? 0.0 : l.front_left;
                 if (specs[i].offered_gbps >= 0) want = std::min(want, specs[i].offered_gbps * 1e9 * tick_s);
                 if (l.window_budget_left >= 0) want = std::min(want, l.window_budget_left);
-                demand[i] = std::min(want, cap_Bps * tick_s);
+                demand[i] = std::min(want, link_tick);
             }
-            std::vector<double> alloc = maxmin_fair(demand, cap_Bps * tick_s);
-            int movers = 0;
-            for (size_t i = 0; i < n; ++i) movers += alloc[i] > 0;
+            // every link is split max-min fair among its own flows
+            std::vector<double> alloc(n, 0.0);
+            std::vector<int> movers(n_links, 0);
+            for (size_t lk = 0; lk < n_links; ++lk) {
+                std::vector<double> dl;
+                for (size_t i : members[lk]) dl.push_back(demand[i]);
+                const std::vector<double> al = maxmin_fair(dl, link_cap[lk] * 1e9 * tick_s);
+                for (size_t k = 0; k < members[lk].size(); ++k) { alloc[members[lk][k]] = al[k]; movers[lk] += al[k] > 0; }
+            }
             for (size_t i = 0; i < n; ++i) {
                 Live& l = live[i];
                 double b = alloc[i];
                 if (b <= 0) continue;
-                window_link_bytes += b;                              // the share of the link is spent in full
-                if (movers > 1) b *= std::min(1.0, std::max(0.0, specs[i].contended_efficiency));
+                window_link_bytes[link_of(i)] += b;                  // the share of the link is spent in full
+                if (movers[link_of(i)] > 1) b *= std::min(1.0, std::max(0.0, specs[i].contended_efficiency));
                 l.window_bytes += b;
                 res.bytes_moved[i] += b;
                 if (l.window_budget_left >= 0) l.window_budget_left -= b;
@@ -208,8 +228,11 @@ inline SimResult run_simulation(const SimConfig& cfg, const std::vector<SimFlowS
             t += tick_s;
         }
         // ---- end of window: signals ----
-        res.link_bytes += window_link_bytes;
-        LinkSignal link{cfg.capacity_gbps, 100.0 * window_link_bytes / (cap_Bps * win_s)};
+        std::vector<LinkSignal> links(n_links);
+        for (size_t lk = 0; lk < n_links; ++lk) {
+            res.link_bytes += window_link_bytes[lk];
+            links[lk] = LinkSignal{link_cap[lk], 100.0 * window_link_bytes[lk] / (link_cap[lk] * 1e9 * win_s)};
+        }
         std::vector<FlowSignal> sig(n);
         for (size_t i = 0; i < n; ++i) {
             Live& l = live[i];
@@ -229,22 +252,28 @@ inline SimResult run_simulation(const SimConfig& cfg, const std::vector<SimFlowS
             if (!s.active) l.smooth.clear();
         }
         // ---- policy ----
-        if (window_id % (uint64_t)std::max(1, cfg.policy_every_windows) == 0 || last_dec.empty())
-            last_dec = policy->step(sig, link);
-        else
-            for (auto& d : last_dec) d.decision = "HOLD";
-        for (auto& d : last_dec) {
-            if (d.id == 0 || d.id > n) continue;
-            Live& l = live[d.id - 1];
-            l.budget_gbps = d.budget_gbps;
-            l.mode = d.mode;
-            l.decision = d.decision;
+        for (size_t lk = 0; lk < n_links; ++lk) {
+            if (members[lk].empty()) continue;
+            if (window_id % (uint64_t)std::max(1, cfg.policy_every_windows) == 0 || last_dec[lk].empty()) {
+                std::vector<FlowSignal> lsig;
+                for (size_t i : members[lk]) lsig.push_back(sig[i]);
+                last_dec[lk] = policies[lk]->step(lsig, links[lk]);
+            } else {
+                for (auto& d : last_dec[lk]) d.decision = "HOLD";
+            }
+            for (auto& d : last_dec[lk]) {
+                if (d.id == 0 || d.id > n) continue;
+                Live& l = live[d.id - 1];
+                l.budget_gbps = d.budget_gbps;
+                l.mode = d.mode;
+                l.decision = d.decision;
+            }
         }
         for (size_t i = 0; i < n; ++i) {
             Live& l = live[i];
             res.rows.push_back({window_id, t * 1e3, (uint32_t)(i + 1), specs[i].name, l.mode, l.decision,
                                 l.budget_gbps < 0 ? -1.0 : l.budget_gbps * 1e9 * win_s, sig[i].inst_gbps,
-                                sig[i].smooth_gbps, specs[i].backlogged ? 0 : sig[i].backlog_bytes, link.util_pct});
+                                sig[i].smooth_gbps, specs[i].backlogged ? 0 : sig[i].backlog_bytes, links[link_of(i)].util_pct});
         }
         ++window_id;
     }

@@ -184,3 +184,28 @@ def test_contended_efficiency_costs_goodput_only_in_company(ctl):
     assert both.link_bytes == pytest.approx(64e9, rel=0.01)                       # the link was busy all the time
     alone = run([("decode", 0.9)])
     assert alone.bytes_moved[0] == pytest.approx(64e9, rel=0.01)
+
+
+def test_simulated_links_are_independent(ctl):
+    """Two links in one simulation: the protected NVLink-like flow is shielded from the best-effort flow on its own link,
+    and the best-effort flow on the other link keeps that link's full rate the whole time."""
+    cfg = ctl.SimConfig()
+    cfg.capacity_gbps, cfg.more_links_gbps, cfg.duration_s, cfg.drain_s, cfg.policy = 64.0, [700.0], 2.0, 1.0, "target_track"
+    prot, be_same, be_other = ctl.SimFlowSpec(), ctl.SimFlowSpec(), ctl.SimFlowSpec()
+    prot.name, prot.priority, prot.target_gbps, prot.link = "kv_transfer", 100, 600.0, 1
+    prot.set_arrivals([(0.05 * k, 20_000_000_000) for k in range(1, 30)])      # 20 GB every 50 ms: 400 GB/s offered
+    be_same.name, be_same.backlogged, be_same.link = "kv_bursts", True, 1
+    be_other.name, be_other.backlogged, be_other.link = "kv_offload", True, 0
+    res = ctl.run_simulation(cfg, [prot, be_same, be_other])
+    assert res.bytes_moved[2] == pytest.approx(64e9 * 2.0, rel=0.01)          # the PCIe-like link never noticed
+    ft = sorted(res.flow_times_ms(1))
+    assert len(ft) == 29 and ft[len(ft) // 2] < 45.0                          # 20 GB at >= 600 GB/s is 33 ms; fair sharing would give 57 ms
+    rows_same = [r for r in res.rows if r.flow == "kv_bursts"]
+    assert any(r.budget_bytes >= 0 for r in rows_same)                        # it was throttled at times ...
+    assert all(r.budget_bytes < 0 for r in res.rows if r.flow == "kv_offload")   # ... and the other link's flow never
+    assert max(r.link_util_pct for r in res.rows if r.flow == "kv_offload") <= 100.0 + 1e-6
+    # unscheduled, the same workload shares the fast link half and half while a request is in flight
+    cfg.policy = "none"
+    res0 = ctl.run_simulation(cfg, [prot, be_same, be_other])
+    ft0 = sorted(res0.flow_times_ms(1))
+    assert ft0[len(ft0) // 2] > ft[len(ft) // 2] * 1.2
