@@ -65,6 +65,7 @@ def main():
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--gated", action="store_true")
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--persistent", action="store_true", help="gemm: the persistent form with two accumulators in TMEM (many-token shapes)")
     ap.add_argument("--blocks", type=int, default=256)
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--gb", type=float, default=2.0)
@@ -133,7 +134,15 @@ def main():
         x = torch.randn((a.m, a.k), dtype=torch.bfloat16, device=dev)
         w = torch.randn((a.n * (2 if a.gated else 1), a.k), dtype=torch.bfloat16, device=dev) / 64
         y = torch.empty((a.m, a.n), dtype=torch.bfloat16, device=dev)
-        ms, best = timed(lambda: ops.gemm(x, w, out=y, gated=a.gated, splits=a.splits or None), a.warm, a.iters, flush)
+        ms, best = timed(lambda: ops.gemm(x, w, out=y, gated=a.gated, splits=a.splits or None, persistent=a.persistent), a.warm, a.iters, flush)
+        if a.persistent:                                                       # a new kernel: say how far it is from the library product
+            ref = (x.float() @ w.float().t())
+            if a.gated:
+                ref = torch.nn.functional.silu(ref[:, :a.n]) * ref[:, a.n:]
+            out["max_rel_err"] = float((y.float() - ref).abs().max() / ref.abs().max())
+            from skygdr_b200.ops.gemm import workspace_for
+
+            out["status"] = ops.read_status(workspace_for(dev).status)["status_name"]
         byt = (w.numel() + x.numel() + y.numel()) * 2
         fl = 2.0 * a.m * w.shape[0] * a.k
         out.update(ms=ms, best_ms=best, bytes=byt, gbs=byt / ms / 1e6, frac_hbm=byt / ms / 1e6 / hbm, tflops=fl / ms / 1e9,

@@ -327,7 +327,7 @@ static void argmax(torch::Tensor logits, torch::Tensor out) {
 // ss_in / ss_out: fp32 vectors of at least M entries (see GemmNormFuse); residual: y is the residual stream, updated in place.
 static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, bool gated, c10::optional<torch::Tensor> workspace,
                  c10::optional<torch::Tensor> counters, torch::Tensor status, int ntok, c10::optional<torch::Tensor> ss_in, double eps,
-                 bool residual, c10::optional<torch::Tensor> ss_out) {
+                 bool residual, c10::optional<torch::Tensor> ss_out, bool persistent) {
     c10::cuda::CUDAGuard g(x.device());
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1, "row-major 2-D tensors");
     GemmParams p;
@@ -357,6 +357,8 @@ static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, 
     }
     TORCH_CHECK(!residual || !gated, "the residual add follows a plain projection");
     p.nf.residual = residual ? 1 : 0;
+    TORCH_CHECK(!persistent || (splits == 1 && !residual && !ss_in.has_value()), "the persistent form is the plain projection without split-K");
+    p.persistent = persistent ? 1 : 0;
     SKY_CUDA_CHECK(launch_gemm(p, cur_stream()));
 }
 
@@ -510,7 +512,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("argmax", &argmax);
     m.def("gemm", &gemm, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("splits"), py::arg("gated"), py::arg("workspace"), py::arg("counters"),
           py::arg("status"), py::arg("ntok"), py::arg("ss_in") = py::none(), py::arg("eps") = 1e-6, py::arg("residual") = false,
-          py::arg("ss_out") = py::none());
+          py::arg("ss_out") = py::none(), py::arg("persistent") = false);
     m.def("gemm_tp", &gemm_tp);
     m.def("tp_norm", &tp_norm, py::arg("rs_buf"), py::arg("rs_counter"), py::arg("rs_seq"), py::arg("resid"), py::arg("w"), py::arg("ag_dst"),
           py::arg("ag_counter"), py::arg("rank"), py::arg("eps"), py::arg("timeout_ns"), py::arg("status"), py::arg("rs_world") = 0);

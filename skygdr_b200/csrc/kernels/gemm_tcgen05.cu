@@ -15,6 +15,7 @@
 // (llm_problem_analysis/decode_transformer_kvcache_stress.cu:323-356).
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -323,6 +324,147 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 }
 
 // ---------------------------------------------------------------------------
+// Persistent form for many-token (prefill) shapes: one CTA per SM walks the output tiles, and the accumulator is double
+// buffered in TMEM, so the epilogue of tile i (TMEM -> registers -> shared memory -> global) runs while the tensor core
+// already works on tile i + 1. The shared-memory ring runs across tile boundaries, so the loads of the next tile are in
+// flight during the last MMAs of the current one. Same roles and the same operand layout as the kernel above (weight rows
+// on the MMA's M, tokens on N); no split-K, no tensor-parallel hooks, no folded norm: this is the plain projection of
+// a prefill step. Tiles are numbered token tile fastest, so the CTAs that run side by side share a few weight panels and
+// the x tiles stay in L2. Not yet run on a GPU: opt-in (GemmParams::persistent).
+template <int NTOK, bool GATED>
+struct GemmPersistSmem {
+    static constexpr int W_BYTES = BM * BK * 2;
+    static constexpr int X_BYTES = NTOK * BK * 2;
+    static constexpr int STAGE_BYTES = W_BYTES * (GATED ? 2 : 1) + X_BYTES;
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024;
+    static constexpr int ACC_COLS = NTOK * (GATED ? 2 : 1);     // one accumulator
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;              // two of them
+    static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS >= 32, "two accumulators must fit TMEM");
+};
+
+template <int NTOK, bool GATED>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+    using S = GemmPersistSmem<NTOK, GATED>;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ uint64_t full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ __align__(16) __nv_bfloat16 stage[16 * 128];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (p.M + NTOK - 1) / NTOK, tiles_n = (p.N + BM - 1) / BM;
+    const int n_tiles = tiles_m * tiles_n;
+    const int nkb = p.K / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 1); }
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(&tmem_slot, S::TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_w);
+            tma_prefetch_desc(&tmap_x);
+            pdl_wait();                                    // x is the previous kernel's output
+            long long it = 0;                              // k-blocks issued so far, over all tiles of this CTA
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int n0 = (tile / tiles_m) * BM, t0 = (tile % tiles_m) * NTOK;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % S::STAGES);
+                    if (it >= S::STAGES && !mbar_wait(&empty_bar[s], (uint32_t)((it / S::STAGES) - 1) & 1)) {
+                        set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 61);
+                        ok = false;
+                        break;
+                    }
+                    unsigned char* st = smem + s * S::STAGE_BYTES;
+                    mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+                    tma_load_2d(st, &tmap_w, kb * BK, n0, &full_bar[s]);
+                    if (GATED) tma_load_2d(st + S::W_BYTES, &tmap_w, kb * BK, p.N + n0, &full_bar[s]);
+                    tma_load_2d(st + S::W_BYTES * (GATED ? 2 : 1), &tmap_x, kb * BK, t0, &full_bar[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, NTOK);
+            long long it = 0;
+            int j = 0;                                     // tiles of this CTA so far
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
+                const int buf = j & 1;
+                // the epilogue must have drained this accumulator (used two tiles ago) before it is overwritten
+                if (j >= 2 && !mbar_wait(&acc_empty[buf], (uint32_t)((j >> 1) - 1) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 62); break; }
+                tc_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)(buf * S::ACC_COLS);
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % S::STAGES);
+                    if (!mbar_wait(&full_bar[s], (uint32_t)(it / S::STAGES) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 63); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t st = smem_u32(smem + s * S::STAGE_BYTES);
+                    const uint64_t a0 = umma_desc_k_sw128(st);
+                    const uint64_t a1 = umma_desc_k_sw128(st + S::W_BYTES);
+                    const uint64_t b = umma_desc_k_sw128(st + S::W_BYTES * (GATED ? 2 : 1));
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint32_t accum = (kb | k) ? 1u : 0u;
+                        tc_mma_f16(acc, a0 + 2 * k, b + 2 * k, idesc, accum);
+                        if (GATED) tc_mma_f16(acc + NTOK, a1 + 2 * k, b + 2 * k, idesc, accum);
+                    }
+                    tc_commit(&empty_bar[s]);
+                }
+                if (ok) tc_commit(&acc_full[buf]);         // this tile's accumulator is complete
+            }
+        }
+    } else {
+        // ---- epilogue warps: TMEM lanes 32*(warp%4) .. +31 ----
+        const int slice = warp & 3;
+        const int r = slice * 32 + lane;
+        pdl_wait();
+        int j = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
+            const int buf = j & 1;
+            const int n0 = (tile / tiles_m) * BM, t0 = (tile % tiles_m) * NTOK;
+            if (!mbar_wait(&acc_full[buf], (uint32_t)(j >> 1) & 1)) { if (lane == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 64); break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (uint32_t)(buf * S::ACC_COLS) + ((uint32_t)(slice * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < NTOK; c += 16) {
+                if (t0 + c >= p.M) break;                  // uniform over the 128 threads: rows past M are never stored
+                uint32_t v[16], u[16];
+                tmem_ld_x16(taddr + c, v);
+                if (GATED) tmem_ld_x16(taddr + NTOK + c, u);
+                tc_wait_ld();
+                float vals[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float val = __uint_as_float(v[i]);
+                    if (GATED) { const float up = __uint_as_float(u[i]); val = val / (1.0f + __expf(-val)) * up; }
+                    vals[i] = val;
+                }
+                store_chunk16(p, stage, t0 + c, n0, r, vals);   // ends with a barrier of the 128 epilogue threads
+            }
+            // every thread's TMEM loads are complete (tc_wait_ld above); hand the accumulator back to the MMA warp
+            tc_fence_before();
+            asm volatile("bar.sync 3, 128;" ::: "memory");
+            if (r == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, S::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
 // Host side: tensor maps and dispatch.
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -369,6 +511,20 @@ static cudaError_t launch_t(const GemmParams& p, const CUtensorMap& tw, const CU
     return launch_pdl(kern, grid, dim3(GEMM_THREADS), (size_t)dyn, stream, tw, tx, p);
 }
 
+template <int NTOK, bool GATED>
+static cudaError_t launch_persistent_t(const GemmParams& p, const CUtensorMap& tw, const CUtensorMap& tx, cudaStream_t stream) {
+    using S = GemmPersistSmem<NTOK, GATED>;
+    auto kern = gemm_persistent_kernel<NTOK, GATED>;
+    static unsigned long long attr_mask = 0;
+    if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), S::TOTAL, &attr_mask); e != cudaSuccess) return e;
+    int dev = 0, sms = 0;
+    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
+    if (cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); e != cudaSuccess) return e;
+    const long long tiles = (long long)((p.N + BM - 1) / BM) * ((p.M + NTOK - 1) / NTOK);
+    const int ctas = (int)std::min<long long>(tiles, sms > 0 ? sms : 1);     // one CTA per SM, each walks tiles cta, cta + ctas, ...
+    return launch_pdl(kern, dim3(ctas), dim3(GEMM_THREADS), (size_t)S::TOTAL, stream, tw, tx, p);
+}
+
 int gemm_pick_ntok(int M, bool gated) {
     if (M <= 16) return 16;
     if (M <= 32) return 32;
@@ -399,6 +555,13 @@ cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream) {
     const long long w_rows = p.gated ? 2LL * p.N : p.N;
     if (!make_tmap_bf16_2d(&tw, p.w, w_rows, p.K, p.ldw, BM)) return cudaErrorInvalidValue;
     if (!make_tmap_bf16_2d(&tx, p.x, p.M, p.K, p.ldx, ntok)) return cudaErrorInvalidValue;
+    if (p.persistent) {
+        // the persistent form is the plain projection at many-token shapes: 256-token tiles (128 when gated or asked for)
+        if (p.splits != 1 || p.ag.n_src > 0 || p.rs.world > 0 || p.nf.row_ss_in || p.nf.residual) return cudaErrorInvalidValue;
+        if (ntok == 256 && !p.gated) return launch_persistent_t<256, false>(p, tw, tx, stream);
+        if (ntok == 128) return p.gated ? launch_persistent_t<128, true>(p, tw, tx, stream) : launch_persistent_t<128, false>(p, tw, tx, stream);
+        return cudaErrorInvalidValue;
+    }
     const bool deep = p.ag.n_src > 0 || p.rs.world > 0;     // fused tensor-parallel GEMM: one CTA per SM, deepest pipeline
 #define SKY_GEMM_CASE(NT)                                                                   \
     case NT: return deep ? (p.gated ? launch_t<NT, true, true>(p, tw, tx, stream) : launch_t<NT, false, true>(p, tw, tx, stream))   \

@@ -72,6 +72,8 @@ struct GemmParams {
     TpAgWait ag;
     TpRsPush rs;
     GemmNormFuse nf;
+    int persistent;           // 1: one CTA per SM walks the output tiles with two accumulators in TMEM (many-token shapes; needs
+                              // splits == 1, ntok 256 or 128, none of ag / rs / nf)
 };
 
 int gemm_pick_ntok(int M, bool gated);

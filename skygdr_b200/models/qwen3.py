@@ -144,6 +144,9 @@ class Qwen3Decoder:
             weights.fold_norms()
         self.cfg, self.w, self.pool = cfg, weights, pool
         self.prefill_attn = prefill_attn              # default of prefill(): this package's kernel or the library arm
+        # prefill(): True runs its projections (more than 256 tokens) through the persistent GEMM with two TMEM accumulators
+        # (compiled, not yet run on a GPU, hence off)
+        self.prefill_gemm_persistent = False
         self._prefill_attn = None
         dev = pool.data.device
         self.device = dev
@@ -299,9 +302,14 @@ class Qwen3Decoder:
         resid = ops.embedding(ids.int(), w.embed)
         h = None
         D = cfg.head_dim
+        persistent = self.prefill_gemm_persistent and T > 256
+
+        def proj(x, wt, gated=False):
+            return ops.gemm(x, wt, gated=gated, persistent=True) if persistent else ops.gemm(x, wt, gated=gated)
+
         for li, lw in enumerate(w.layers):
             xn = ops.rmsnorm(resid, lw.ln1, cfg.eps) if h is None else ops.rmsnorm(h, lw.ln1, cfg.eps, residual=resid)
-            qkv = ops.gemm(xn, lw.qkv)
+            qkv = proj(xn, lw.qkv)
             q = ops.rope_append(qkv, lw.q_norm, lw.k_norm, pool, li, self.inv_freq, block_table, positions, cfg.q_heads, cfg.eps,
                                 seq_ids=seq_ids)
             ao = torch.empty_like(q)
@@ -311,10 +319,10 @@ class Qwen3Decoder:
                         self._prefill_attn = ops.PrefillAttention(dev)
                     seq_start = torch.tensor([0] + list(torch.tensor(seq_lens).cumsum(0).tolist()), dtype=torch.int32, device=dev)
                 self._prefill_attn(q, pool, li, block_table, seq_start, max(seq_lens), out=ao)
-                h = ops.gemm(ao.view(T, -1), lw.o)
+                h = proj(ao.view(T, -1), lw.o)
                 xn = ops.rmsnorm(h, lw.ln2, cfg.eps, residual=resid)
-                act = ops.gemm(xn, lw.gate_up, gated=True)
-                h = ops.gemm(act, lw.down)
+                act = proj(xn, lw.gate_up, gated=True)
+                h = proj(act, lw.down)
                 continue
             o = 0
             for si, n in enumerate(seq_lens):
@@ -330,10 +338,10 @@ class Qwen3Decoder:
                 out = torch.nn.functional.scaled_dot_product_attention(qs[None], k[None], v[None], is_causal=True, enable_gqa=True)
                 ao[o:o + n] = out[0].transpose(0, 1)
                 o += n
-            h = ops.gemm(ao.view(T, -1), lw.o)
+            h = proj(ao.view(T, -1), lw.o)
             xn = ops.rmsnorm(h, lw.ln2, cfg.eps, residual=resid)
-            act = ops.gemm(xn, lw.gate_up, gated=True)
-            h = ops.gemm(act, lw.down)
+            act = proj(xn, lw.gate_up, gated=True)
+            h = proj(act, lw.down)
         xn = ops.rmsnorm(h, w.final_norm, cfg.eps, residual=resid)
         last = torch.cumsum(torch.tensor(seq_lens, device=dev), 0) - 1
         return ops.gemm(xn[last].contiguous(), w.lm_head)

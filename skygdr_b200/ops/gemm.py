@@ -110,13 +110,16 @@ def workspace_for(device) -> GemmWorkspace:
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, gated: bool = False,
          splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, ntok: int = 0, ss_in: Optional[torch.Tensor] = None,
-         eps: float = 1e-6, residual: bool = False, ss_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+         eps: float = 1e-6, residual: bool = False, ss_out: Optional[torch.Tensor] = None, persistent: bool = False) -> torch.Tensor:
     """y = x @ w.T (w is [N][K]); gated: w is [2N][K] and y = silu(x @ w[:N].T) * (x @ w[N:].T).
 
     RMSNorm folded into the epilogues (the gain is expected inside ``w`` already, see ``Qwen3Weights.fold_norms``):
     ``ss_in`` (fp32, one sum of squares per row of x) scales output row t by rsqrt(ss_in[t] / K + eps); ``residual`` makes ``out``
     the residual stream, updated in place (out += x @ w.T), and ``ss_out`` then receives the sums of squares of the new rows
-    (added to what it holds: zero it first)."""
+    (added to what it holds: zero it first).
+
+    ``persistent`` (many-token shapes, plain projection): one CTA per SM walks the output tiles with two accumulators in TMEM,
+    so a tile's epilogue overlaps the next tile's MMAs (tiles of 256 tokens, 128 when gated). Compiled, not yet run on a GPU."""
     C = load()
     M, K = x.shape
     N = w.shape[0] // 2 if gated else w.shape[0]
@@ -128,6 +131,10 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, g
         else:
             splits = 1 if M > 256 else pick_config(M, N, K, _sms(x.device), gated, fixed_ntok=ntok)[1]
     ws = ws or workspace_for(x.device)
+    if persistent:
+        assert not residual and ss_in is None, "the persistent form is the plain projection"
+        C.gemm(x, w, out, 1, gated, None, None, ws.status, 128 if (gated or ntok == 128) else 256, None, eps, False, None, True)
+        return out
     if splits > 1:
         ws.ensure(C.gemm_workspace_floats(M, N, splits, gated, ntok), C.gemm_counter_count(M, N, gated, ntok))
         C.gemm(x, w, out, splits, gated, ws.ws, ws.counters, ws.status, ntok, ss_in, eps, residual, ss_out)

@@ -506,3 +506,27 @@ def test_cli_programs_run(ops):
         assert label in out, label
     out = run("decode_kvcache_stress", "--layers", "2", "--context", "2048", "--gen", "4", "--batch", "4")
     assert "Effective sequence-throughput:" in out and "Approx bandwidth:" in out
+
+
+@pytest.mark.skipif(os.environ.get("SKYGDR_TEST_GEMM_PERSISTENT") != "1", reason="the persistent GEMM has not run on a GPU yet: opt in")
+@pytest.mark.parametrize("M,N,K,gated,ntok", [(2048, 1024, 1024, False, 0), (300, 640, 512, False, 0), (1000, 200, 256, False, 128),
+                                              (777, 384, 1024, True, 0), (40000, 256, 128, False, 0)])
+def test_persistent_gemm_matches_reference(ops, M, N, K, gated, ntok):
+    """One CTA per SM walking the output tiles with two TMEM accumulators: full tiles, ragged tokens and features, a gated
+    case, and a case with far more tiles than CTAs (every accumulator and every ring slot is reused many times)."""
+    from skygdr_b200.ops.gemm import workspace_for
+
+    torch.manual_seed(12)
+    x = torch.randn((M, K), dtype=torch.bfloat16, device="cuda")
+    w = (torch.randn((N * (2 if gated else 1), K), dtype=torch.bfloat16, device="cuda") / math.sqrt(K)).contiguous()
+    y = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(x, w, out=y, gated=gated, ntok=ntok, persistent=True)
+    ref = x.float() @ w.float().t()
+    if gated:
+        ref = torch.nn.functional.silu(ref[:, :N]) * ref[:, N:]
+    torch.cuda.synchronize()
+    assert ops.read_status(workspace_for("cuda").status)["status"] == 0
+    err = (y.float() - ref).abs().max()
+    assert err < 2e-2 * max(1.0, float(ref.abs().max())), float(err)
+    y2 = ops.gemm(x, w, gated=gated)                      # the one-tile-per-CTA kernel must agree to rounding
+    assert (y.float() - y2.float()).abs().max() < 2e-2 * max(1.0, float(ref.abs().max()))
