@@ -103,10 +103,16 @@ class FlowHandle:
 class FabricClient:
     """A persistent connection to ``fabricd``: register flows, renew leases, query budgets."""
 
-    def __init__(self, host: str = "127.0.0.1", port: int = 7070, timeout_s: float = 2.0):
+    def __init__(self, host: str = "127.0.0.1", port: int = 7070, timeout_s: float = 2.0, unix: Optional[str] = None):
+        """TCP by default; ``unix`` = path of the daemon's Unix-domain socket (``fabricd --unix PATH``) for clients on its host."""
         self.host, self.port = host, port
-        self.sock = socket.create_connection((host, port), timeout=timeout_s)
-        self.sock.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
+        if unix:
+            self.sock = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            self.sock.settimeout(timeout_s)
+            self.sock.connect(unix)
+        else:
+            self.sock = socket.create_connection((host, port), timeout=timeout_s)
+            self.sock.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
         self._buf = b""
 
     def request(self, line: str) -> str:

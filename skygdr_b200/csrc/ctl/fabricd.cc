@@ -4,6 +4,7 @@
 //           [--window_us 5000] [--capacity_gbps 64] [--lease_ms 5000] [--log PATH.csv]
 //           [--snapshot PATH.json] [--restore PATH.json] [--gpu N --util_source pcie_rx|pcie_tx|sum]
 //           [--link NAME=GBPS ...]   more links beside the default one (each a shared capacity with its own policy pass)
+//           [--unix PATH]            also listen on a Unix-domain socket (same protocol; for clients on the same host)
 //           [--enter_ratio 0.65 --exit_ratio 0.80 --util_threshold_pct 85 --enter_windows 1 --exit_windows 2]
 //
 // A TCP line server (one or more commands per connection, each answered by one
@@ -22,6 +23,7 @@
 #include <signal.h>
 #include <sys/select.h>
 #include <sys/socket.h>
+#include <sys/un.h>
 
 #include <atomic>
 #include <cerrno>
@@ -50,11 +52,24 @@ static int make_listener(const std::string& ip, int port) {
     return ls;
 }
 
+static int make_unix_listener(const std::string& path) {
+    sockaddr_un a{};
+    if (path.empty() || path.size() >= sizeof a.sun_path) return -1;
+    int ls = socket(AF_UNIX, SOCK_STREAM, 0);
+    if (ls < 0) return -1;
+    a.sun_family = AF_UNIX;
+    memcpy(a.sun_path, path.c_str(), path.size() + 1);
+    unlink(path.c_str());                                  // a socket file left by an earlier daemon
+    if (bind(ls, (sockaddr*)&a, sizeof a) != 0 || listen(ls, 64) != 0) { close(ls); return -1; }
+    return ls;
+}
+
 int main(int argc, char** argv) {
     DaemonConfig cfg;
     int port = 7070, gpu = -1;
     std::string bind_ip = "127.0.0.1", log_path, snap_path, restore_path, util_source = "sum";
     std::vector<std::pair<std::string, std::string>> link_defs;
+    std::string unix_path;
     for (int i = 1; i < argc; ++i) {
         std::string k = argv[i];
         std::string v;
@@ -88,6 +103,7 @@ int main(int argc, char** argv) {
             else { fprintf(stderr, "fabricd: --dead_policy is stall, unpaced or static\n"); return 2; }
         }
         else if (k == "--dead_fallback_gbps") cfg.dead_fallback_gbps = atof(v.c_str());
+        else if (k == "--unix") unix_path = v;
         else if (k == "--link") {
             const size_t e = v.rfind('=');
             if (e == std::string::npos || e == 0) { fprintf(stderr, "fabricd: --link NAME=GBPS\n"); return 2; }
@@ -204,20 +220,30 @@ int main(int argc, char** argv) {
     };
     std::vector<std::thread> conns;
 
+    int uls = -1;
+    if (!unix_path.empty()) {
+        uls = make_unix_listener(unix_path);
+        if (uls < 0) { perror("fabricd: unix listen"); g_stop.store(1); }
+        else fprintf(stderr, "fabricd: also listening on unix:%s\n", unix_path.c_str());
+    }
     while (!g_stop.load()) {
         fd_set rf;
         FD_ZERO(&rf);
         FD_SET(ls, &rf);
+        if (uls >= 0) FD_SET(uls, &rf);
         timeval tv{0, 200000};
-        int r = select(ls + 1, &rf, nullptr, nullptr, &tv);
+        int r = select(std::max(ls, uls) + 1, &rf, nullptr, nullptr, &tv);
         if (r <= 0) continue;
-        int c = accept(ls, nullptr, nullptr);
-        if (c < 0) continue;
-        conns.emplace_back(serve, c);
+        for (int l : {ls, uls}) {
+            if (l < 0 || !FD_ISSET(l, &rf)) continue;
+            int c = accept(l, nullptr, nullptr);
+            if (c >= 0) conns.emplace_back(serve, c);
+        }
     }
     for (auto& t : conns) t.join();
     timer.join();
     close(ls);
+    if (uls >= 0) { close(uls); unlink(unix_path.c_str()); }
     if (!snap_path.empty()) {
         std::lock_guard<std::mutex> g(mu);
         std::ofstream out(snap_path);

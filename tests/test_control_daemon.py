@@ -272,3 +272,15 @@ def test_daemon_process_with_two_links(tmp_path):
             assert c.request("LINKS") == "OK n=3 default:64 nvlink:gpu0:700 pcie:gpu1:60"
             flows = c.request("FLOWS")
             assert "kv_transfer:100:600:kv_transfer" in flows and flows.count(":nvlink:gpu0") == 2
+
+
+def test_daemon_serves_the_same_protocol_on_a_unix_socket(tmp_path):
+    path = str(tmp_path / "fabricd.sock")
+    with FabricDaemon(window_us=2000, extra=["--unix", path]) as d:
+        assert _wait(lambda: os.path.exists(path))
+        with FabricClient(unix=path) as local, FabricClient(port=d.port) as remote:
+            h = local.register("kv_transfer", "high", 40.0)
+            assert h.flow_id == 1 and "1:kv_transfer:100:40:kv_transfer" in remote.request("FLOWS")
+            assert local.renew(h) and local.request("PING") == "OK pong"
+            assert remote.unregister(h) and local.request("FLOWS").startswith("OK n=0")
+    assert not os.path.exists(path)                    # the daemon removes its socket file on the way out
