@@ -257,6 +257,16 @@ public:
             }
             return reply;
         }
+        if (cmd == "STATS") {
+            // the daemon about itself: how many windows it has run, what a policy + grant pass costs, how busy every link was
+            std::ostringstream os;
+            os << "OK windows=" << window_id_ << " flows=" << reg_.size() << " expired=" << expired_ << " policy=" << links_[0].policy->name()
+               << " window_us=" << cfg_.window_ns / 1000 << " step_us_last=" << double(step_cost_last_ns_) * 1e-3
+               << " step_us_max=" << double(step_cost_max_ns_) * 1e-3 << " links=" << links_.size();
+            for (auto& l : links_) os << " util_pct:" << l.name << "=" << l.last_util_pct;
+            os << "\n";
+            return os.str();
+        }
         if (cmd == "PING") return "OK pong\n";
         return "ERR unknown_cmd\n";
     }
@@ -264,6 +274,7 @@ public:
     // ---- one control window ----
     // external_util_pct is used when cfg.external_util is set (e.g. NVML PCIe utilisation).
     std::vector<WindowLog> step_window(uint64_t now_ns, double external_util_pct = 0.0) {
+        const auto t_step0 = std::chrono::steady_clock::now();
         for (uint32_t id : reg_.expire(now_ns)) { drop_state(id); ++expired_; }
         auto flows = reg_.snapshot();
         std::vector<FlowSignal> sig;
@@ -300,6 +311,7 @@ public:
             link.capacity_gbps = links_[li].capacity_gbps;
             // a supplied utilisation (NVML) describes the first link; the others are summed from their flows
             link.util_pct = (cfg_.external_util && li == 0) ? external_util_pct : 100.0 * sum_gbps[li] / std::max(1e-9, link.capacity_gbps);
+            links_[li].last_util_pct = link.util_pct;
             auto dec = links_[li].policy->step(lsig, link);
             for (size_t k = 0; k < dec.size() && k < members[li].size(); ++k) {
                 const size_t i = members[li][k];
@@ -338,6 +350,8 @@ public:
         }
         last_step_ns_ = now_ns;
         ++window_id_;
+        step_cost_last_ns_ = (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t_step0).count();
+        step_cost_max_ns_ = std::max(step_cost_max_ns_, step_cost_last_ns_);
         return logs;
     }
 
@@ -481,6 +495,7 @@ private:
         std::string name;
         double capacity_gbps;
         std::unique_ptr<Policy> policy;
+        double last_util_pct = 0;      // utilisation seen in the last window that had flows on this link
     };
     int find_link(const std::string& name) const {
         for (size_t i = 0; i < links_.size(); ++i)
@@ -546,7 +561,7 @@ private:
     FlowRegistry reg_;
     std::vector<Link> links_;
     std::map<uint32_t, FlowState> state_;
-    uint64_t window_id_ = 0, last_step_ns_ = 0, expired_ = 0;
+    uint64_t window_id_ = 0, last_step_ns_ = 0, expired_ = 0, step_cost_last_ns_ = 0, step_cost_max_ns_ = 0;
     bool keep_pages_ = false;
 };
 

@@ -214,7 +214,7 @@ def test_protocol_survives_arbitrary_lines(ctl):
     words = st.sampled_from(["REGISTER", "RENEW", "UNREGISTER", "BUDGET", "FLOWS", "FLOW", "POLICY", "WINDOW", "CAPACITY", "PING", "STATUS", "HIGH",
                              "LOW", "LOW1", "LOW2", "LOW3", "LOW4", "SLEEP", "STOP", "kv_transfer", "kv_offload", "high", "low", "besteffort",
                              "nan", "inf", "-1", "0", "1", "2", "40", "1e308", "99999999999999999999", "target_track", "ladder", "static", "none", "x",
-                             "LINK", "LINKS", "link=default", "link=nv", "link=", "nv", "default", "700"])
+                             "LINK", "LINKS", "STATS", "link=default", "link=nv", "link=", "nv", "default", "700"])
     junk = st.text(alphabet=st.characters(blacklist_categories=("Cs",), blacklist_characters="\n"), max_size=40)
     line = st.one_of(st.lists(st.one_of(words, junk), max_size=8).map(" ".join), junk)
 
@@ -319,6 +319,10 @@ def test_flows_on_different_links_do_not_take_bandwidth_from_one_another(ctl):
     assert logs["kv_offload"].budget_bytes == -1.0 and d.page_fields(3)["unlimited"] == 1               # other link: untouched
     assert logs["kv_bursts"].link_util_pct == pytest.approx(100 * 680 / 700, rel=0.02)
     assert logs["kv_offload"].link_util_pct == pytest.approx(100 * 60 / 64, rel=0.02)
+    stats = dict(kv.split("=", 1) for kv in d.handle_line("STATS", 0).split()[1:])
+    assert stats["windows"] == "2" and stats["flows"] == "3" and stats["links"] == "2" and stats["policy"] == "target_track"
+    assert float(stats["util_pct:nvlink:gpu0"]) == pytest.approx(100 * 680 / 700, rel=0.02) and float(stats["util_pct:default"]) > 90
+    assert 0 < float(stats["step_us_last"]) <= float(stats["step_us_max"]) < 5000
     # capacity of a link can be changed while flows run; the default link follows CAPACITY as before
     assert d.handle_line("LINK nvlink:gpu0 900", 0).startswith("OK link=nvlink:gpu0 capacity_gbps=900.000 flows=2")
     assert d.handle_line("CAPACITY 32", 0) == "OK capacity_gbps=32.000\n" and d.handle_line("LINKS", 0) == "OK n=2 default:32 nvlink:gpu0:900\n"
