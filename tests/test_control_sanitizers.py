@@ -25,17 +25,22 @@ def test_daemon_session_is_clean_under_sanitizer(kind, tmp_path):
     port = _free_port()
     env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0", TSAN_OPTIONS="halt_on_error=0")
     p = subprocess.Popen([str(exe), "--port", str(port), "--window_us", "1000", "--lease_ms", "300", "--page_dir", str(tmp_path),
-                          "--log", str(tmp_path / "w.csv")], stderr=subprocess.PIPE, text=True, env=env)
+                          "--log", str(tmp_path / "w.csv"), "--link", "nvlink=700", "--unix", str(tmp_path / "d.sock"),
+                          "--snapshot", str(tmp_path / "snap.json")], stderr=subprocess.PIPE, text=True, env=env)
     try:
         wait_for_control("127.0.0.1", port, 15.0, command="PING")
 
         def client(i):
-            with FabricClient(port=port) as c:
-                f = c.register(f"flow{i}", "high" if i % 2 else "besteffort", 10.0 * (i % 2))
+            # half of the clients come over the Unix socket, a third of the flows live on the second link
+            with (FabricClient(unix=str(tmp_path / "d.sock")) if i % 2 else FabricClient(port=port)) as c:
+                f = c.register(f"flow{i}", "high" if i % 2 else "besteffort", 10.0 * (i % 2), link="nvlink" if i % 3 == 0 else None)
                 for k in range(20):
                     f.report(k * 1_000_000, k * 1_000_000, 5_000_000 if i % 2 else 1 << 40)
                     c.renew(f)
                     c.budget(f)
+                    c.request("STATS")
+                    if k == 10 and i == 0:
+                        c.link("late_link", 55.0)      # a link appears while windows are running
                     time.sleep(0.005)
                 if i % 3:
                     c.unregister(f)            # the others are left to expire
