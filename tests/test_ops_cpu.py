@@ -285,3 +285,107 @@ def test_decode_attention_grid_orders_cover_every_token_once(mode):
             longest_late = max([longest_late] + late)
     if mode == 2:
         assert longest_late == chunk // 4                                                # what runs last is at most a quarter chunk
+
+
+def _simulate_persistent_gemm_pipeline(n_my_tiles, nkb, stages, seed):
+    """The barrier protocol of gemm_persistent_kernel (skygdr_b200/csrc/kernels/gemm_tcgen05.cu) as three coroutines under a
+    random scheduler: TMA producer, MMA issuer, epilogue. mbarriers are modelled as phase counters: a wait on parity P
+    passes once the barrier's current phase has parity != P. Asynchronous completions (TMA bytes landing, tcgen05.commit
+    arrivals) are events that the scheduler delivers at random later times. Returns the order in which the epilogue saw
+    (tile, checksum) and raises on any hazard: a ring slot overwritten before its MMAs read it, an accumulator overwritten
+    before it was drained, an MMA on a slot whose data has not landed."""
+    import random
+
+    rng = random.Random(seed)
+    phase = {("full", s): 0 for s in range(stages)} | {("empty", s): 0 for s in range(stages)} | \
+            {("acc_full", b): 0 for b in range(2)} | {("acc_empty", b): 0 for b in range(2)}
+    slot = [None] * stages            # (tile, kb) whose data is in the slot, or None while free / in flight
+    slot_busy = [False] * stages      # loaded and not yet read by the tensor core
+    acc = [None, None]                # per accumulator: [tile, number of k-blocks accumulated, drained?]
+    pending = []                      # asynchronous completions not yet delivered: callables
+    seen = []
+
+    def passed(bar, parity):
+        return (phase[bar] & 1) != parity
+
+    def producer():
+        it = 0
+        for j in range(n_my_tiles):
+            for kb in range(nkb):
+                s = it % stages
+                if it >= stages:
+                    while not passed(("empty", s), ((it // stages) - 1) & 1):
+                        yield
+                assert not slot_busy[s], ("slot overwritten before it was read", j, kb)
+                slot[s] = None
+
+                def land(s=s, j=j, kb=kb):
+                    slot[s] = (j, kb)
+                    slot_busy[s] = True
+                    phase[("full", s)] += 1
+                pending.append(land)
+                it += 1
+                yield
+
+    def mma():
+        it = 0
+        for j in range(n_my_tiles):
+            buf = j & 1
+            if j >= 2:
+                while not passed(("acc_empty", buf), ((j >> 1) - 1) & 1):
+                    yield
+            assert acc[buf] is None or acc[buf][2], ("accumulator overwritten before it was drained", j)
+            acc[buf] = [j, 0, False]
+            for kb in range(nkb):
+                s = it % stages
+                while not passed(("full", s), (it // stages) & 1):
+                    yield
+                assert slot[s] == (j, kb), ("MMA on a slot that does not hold its operands", j, kb, slot[s])
+                acc[buf][1] += 1
+
+                def read_done(s=s):                 # tcgen05.commit -> empty barrier, once the MMAs have read the slot
+                    slot_busy[s] = False
+                    phase[("empty", s)] += 1
+                pending.append(read_done)
+                it += 1
+                yield
+            pending.append(lambda buf=buf: phase.__setitem__(("acc_full", buf), phase[("acc_full", buf)] + 1))
+            yield
+
+    def epilogue():
+        for j in range(n_my_tiles):
+            buf = j & 1
+            while not passed(("acc_full", buf), (j >> 1) & 1):
+                yield
+            assert acc[buf][0] == j and acc[buf][1] == nkb, ("epilogue read an incomplete or foreign accumulator", j, acc[buf])
+            seen.append(j)
+            yield                                    # the loads and stores of the tile take a while
+            acc[buf][2] = True
+            phase[("acc_empty", buf)] += 1           # plain arrive: immediate
+
+    live = [producer(), mma(), epilogue()]
+    steps = 0
+    while live:
+        steps += 1
+        assert steps < 200000, "the pipeline stopped making progress"
+        # asynchronous completions are delivered in issue order per kind, at random times
+        if pending and (rng.random() < 0.5 or len(live) == 0):
+            pending.pop(0)()
+            continue
+        g = rng.choice(live)
+        try:
+            next(g)
+        except StopIteration:
+            live.remove(g)
+        if not live:
+            while pending:
+                pending.pop(0)()
+    return seen
+
+
+@pytest.mark.parametrize("n_my_tiles,nkb,stages", [(1, 1, 4), (1, 9, 4), (2, 3, 4), (3, 64, 4), (7, 5, 6), (5, 1, 4), (4, 2, 8), (9, 16, 4)])
+def test_persistent_gemm_pipeline_protocol(n_my_tiles, nkb, stages):
+    """Parities and ordering of the four barrier families of the persistent GEMM, for few and many tiles per CTA, k-loops shorter
+    and longer than the ring: under many random interleavings every tile reaches the epilogue complete and in order."""
+    for seed in range(40):
+        assert _simulate_persistent_gemm_pipeline(n_my_tiles, nkb, stages, seed) == list(range(n_my_tiles))
