@@ -389,3 +389,135 @@ def test_persistent_gemm_pipeline_protocol(n_my_tiles, nkb, stages):
     and longer than the ring: under many random interleavings every tile reaches the epilogue complete and in order."""
     for seed in range(40):
         assert _simulate_persistent_gemm_pipeline(n_my_tiles, nkb, stages, seed) == list(range(n_my_tiles))
+
+
+def _simulate_tp_collectives(collective, world, layers, steps, seed):
+    """The cross-rank protocol of parallel.tp.TPDecoder as a model: every rank runs its kernels in stream order, a kernel
+    runs only when the counters it waits for have reached the value it computes from (step, use), its remote writes land in
+    the peers' buffers and its arrivals bump the peers' counters. Ranks advance under a random scheduler, so any rank can be
+    arbitrarily late. Every buffer slot carries the tag of what was last written and whether its owner has read it:
+    overwriting an unread slot, or reading a slot that holds something else than expected, is a hazard. Counters only grow.
+    Returns the number of kernels run; raises on a hazard or when no rank can make progress."""
+    import random
+
+    rng = random.Random(seed)
+    L, W = layers, world
+    ctr = [dict() for _ in range(W)]                   # per rank: counter name -> value
+    buf = [dict() for _ in range(W)]                   # per rank: (buffer, slot) -> [tag, read?]
+
+    def get(r, name):
+        return ctr[r].get(name, 0)
+
+    def write(dst, name, slot, tag):
+        cur = buf[dst].get((name, slot))
+        assert cur is None or cur[1], ("overwrote unread data", name, "on rank", dst, "slot", slot, "old", cur, "new", tag)
+        buf[dst][(name, slot)] = [tag, False]
+
+    def read(r, name, slot, tag):
+        cur = buf[r].get((name, slot))
+        assert cur is not None and cur[0] == tag, ("read something else than expected", name, r, slot, cur, tag)
+        cur[1] = True
+
+    def program(r):
+        """Yields (wait, action) pairs: wait is a list of (counter, value) that must hold on rank r before action() runs."""
+        for step in range(steps):
+            for li in range(L + 1):                    # li == L: the final norm and lm_head
+                # ---- norm in front of QKV / lm_head: sums the previous layer's down-projection partials ----
+                prev = ("down", step, li - 1)
+                if collective == "oneshot":
+                    waits = [("rs1", (step * L + li) * W)] if li > 0 else []
+
+                    def k_norm1(li=li, prev=prev):
+                        if li > 0:
+                            for src in range(W):
+                                read(r, "ar1", src, prev)
+                    yield waits, k_norm1
+                    yield [], (lambda: None)           # QKV or lm_head GEMM on local, replicated activations
+                else:
+                    waits = [("rs1", (step * L + li) * W)] if li > 0 else []
+
+                    def k_norm1(step=step, li=li, prev=prev):
+                        if li > 0:
+                            for src in range(W):
+                                read(r, "rs1", src, prev)
+                        for d in range(W):             # all-gather push: this rank's rows into everybody's buffer A
+                            write(d, "agA", r, ("A", step, li))
+                            ctr[d][("agA", r)] = get(d, ("agA", r)) + 1
+                    yield waits, k_norm1
+
+                    def k_qkv(step=step, li=li):
+                        for src in range(W):
+                            read(r, "agA", src, ("A", step, li))
+                    yield [(("agA", src), step * (L + 1) + li + 1) for src in range(W)], k_qkv
+                if li == L:
+                    break
+                yield [], (lambda: None)               # RoPE + append, attention: local
+
+                # ---- O projection: partials to the peers ----
+                def k_o(step=step, li=li):
+                    for d in range(W):
+                        write(d, "ar0" if collective == "oneshot" else "rs0", r, ("o", step, li))
+                        ctr[d]["rs0"] = get(d, "rs0") + 1
+                yield [], k_o
+
+                # ---- norm in front of gate/up ----
+                def k_norm2(step=step, li=li):
+                    for src in range(W):
+                        read(r, "ar0" if collective == "oneshot" else "rs0", src, ("o", step, li))
+                    if collective != "oneshot":
+                        for d in range(W):
+                            write(d, "agB", r, ("B", step, li))
+                            ctr[d][("agB", r)] = get(d, ("agB", r)) + 1
+                yield [("rs0", (step * L + li + 1) * W)], k_norm2
+                if collective == "oneshot":
+                    yield [], (lambda: None)           # gate/up on local activations
+                else:
+                    def k_gu(step=step, li=li):
+                        for src in range(W):
+                            read(r, "agB", src, ("B", step, li))
+                    yield [(("agB", src), step * L + li + 1) for src in range(W)], k_gu
+
+                # ---- down projection: partials to the peers ----
+                def k_down(step=step, li=li):
+                    for d in range(W):
+                        write(d, "ar1" if collective == "oneshot" else "rs1", r, ("down", step, li))
+                        ctr[d]["rs1"] = get(d, "rs1") + 1
+                yield [], k_down
+            # ---- vocabulary-parallel argmax: candidates to everybody, then wait for everybody's ----
+            def k_am_push(step=step):
+                for d in range(W):
+                    write(d, "am", r, ("am", step))
+                    ctr[d]["am"] = get(d, "am") + 1
+            yield [], k_am_push
+
+            def k_am_pick(step=step):
+                for src in range(W):
+                    read(r, "am", src, ("am", step))
+            yield [("am", (step + 1) * W)], k_am_pick
+
+    progs = [program(r) for r in range(W)]
+    nxt = [next(p) for p in progs]
+    done, ran = [False] * W, 0
+    while not all(done):
+        ready = [r for r in range(W) if not done[r] and all(get(r, c) >= v for c, v in nxt[r][0])]
+        assert ready, ("no rank can make progress", [(r, nxt[r][0]) for r in range(W) if not done[r]])
+        # a biased pick: now and then one rank races ahead as far as it can, or stalls for a long time
+        r = rng.choice(ready) if rng.random() < 0.7 else ready[0]
+        nxt[r][1]()
+        ran += 1
+        try:
+            nxt[r] = next(progs[r])
+        except StopIteration:
+            done[r] = True
+    return ran
+
+
+@pytest.mark.parametrize("collective", ["rs_ag", "oneshot"])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_counter_protocol_has_no_deadlock_and_no_overwrite(collective, world):
+    """Both collective forms of the tensor-parallel step (reduce-scatter + all-gather with a token-sharded residual stream,
+    and the one-shot all-reduce with replicated activations): counters computed from (step, use) are always reached, and no
+    rank ever overwrites a peer's buffer before the peer has read it, however far ranks drift apart. Three steps, so the
+    reuse of every buffer across steps is covered."""
+    for seed in range(25):
+        assert _simulate_tp_collectives(collective, world, layers=3, steps=3, seed=seed) > 0
