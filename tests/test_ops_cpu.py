@@ -521,3 +521,161 @@ def test_tensor_parallel_counter_protocol_has_no_deadlock_and_no_overwrite(colle
     reuse of every buffer across steps is covered."""
     for seed in range(25):
         assert _simulate_tp_collectives(collective, world, layers=3, steps=3, seed=seed) > 0
+
+
+def _simulate_prefill_64key_pipeline(nkt0, nkt1, seed, units=3):
+    """The barrier protocol of the prefill attention variant with 64-key steps and double-buffered scores
+    (prefill_attn_tc3_kernel in skygdr_b200/csrc/kernels/prefill_attn_tc.cu) as a model: TMA producer over a ring of
+    `units` K/V tiles, one MMA issuer, one softmax warpgroup per query tile. nkt0 / nkt1 = 128-token key tiles of the two
+    query tiles (nkt1 = nkt0 + 1, or 0 when the second tile does not exist). Tensor-core work completes asynchronously and
+    in issue order (a commit covers everything issued before it); TMA loads complete asynchronously. Softmax decides at
+    random whether a step raises the running maximum (the branch that rescales the accumulator). Raises on any hazard:
+    scores or P overwritten before they were consumed, a ring unit reloaded while a pending MMA still needs it, an
+    accumulator rescaled while a P.V is in flight. Returns the number of softmax steps done per query tile."""
+    import random
+
+    rng = random.Random(seed)
+    nkt = [nkt0, nkt1]
+    n_kt = max(nkt)
+    steps_x = [2 * nkt0, 2 * nkt1]
+    names = [("full", s) for s in range(units)] + [("empty", s) for s in range(units)] + \
+            [(k, x, par) for k in ("s_ready", "p_ready", "o_done") for x in range(2) for par in range(2)]
+    phase = {n: 0 for n in names}
+    ring = [None] * units                      # unit index u held by the slot (None while a load is in flight)
+    unit_reads_left = {}                       # u -> MMAs that still have to finish reading it
+    S = [[None, None], [None, None]]           # S[x][par] = step whose scores the buffer holds
+    P = [[None, None], [None, None]]           # P[x][par] = step whose probabilities the buffer holds
+    pv_in_flight = [0, 0]
+    tc_fifo, tma_fifo = [], []                 # asynchronous completions, each in issue order
+    done_steps = [0, 0]
+
+    def passed(bar, parity):
+        return (phase[bar] & 1) != parity
+
+    def users(u):                              # how many MMAs read ring unit u: both 64-key halves for every tile that has key tile j
+        j = u >> 1
+        return 2 * sum(1 for x in range(2) if j < nkt[x])
+
+    def producer():
+        for u in range(2 * n_kt):
+            s = u % units
+            if u >= units:
+                while not passed(("empty", s), ((u // units) - 1) & 1):
+                    yield
+                old = ring[s]
+                assert old is not None and unit_reads_left[old] == 0, ("ring unit reloaded while still needed", old, unit_reads_left.get(old))
+            ring[s] = None
+            unit_reads_left[u] = users(u)
+
+            def land(s=s, u=u):
+                ring[s] = u
+                phase[("full", s)] += 1
+            tma_fifo.append(land)
+            yield
+
+    def mma():
+        def issue_s(x, t):
+            j, hb = t >> 1, t & 1
+            u = 2 * j
+            s = u % units
+            while not passed(("full", s), (u // units) & 1):
+                yield
+            assert ring[s] == u, ("score MMA on a unit that does not hold its K tile", x, t, ring[s])
+            assert S[x][t & 1] is None or S[x][t & 1] < 0, ("scores overwritten before softmax took them", x, t, S[x][t & 1])
+
+            def fin(x=x, t=t, s=s, u=u):
+                assert ring[s] == u, ("K tile replaced while its MMA was in flight", x, t)
+                unit_reads_left[u] -= 1
+                S[x][t & 1] = t
+            tc_fifo.append(fin)
+            if hb == 1 and (x == 1 or j >= nkt[1]):
+                tc_fifo.append(lambda s=s: phase.__setitem__(("empty", s), phase[("empty", s)] + 1))
+            tc_fifo.append(lambda x=x, t=t: phase.__setitem__(("s_ready", x, t & 1), phase[("s_ready", x, t & 1)] + 1))
+
+        def issue_pv(x, t):
+            j, hb = t >> 1, t & 1
+            while not passed(("p_ready", x, t & 1), (t >> 1) & 1):
+                yield
+            u = 2 * j + 1
+            s = u % units
+            while not passed(("full", s), (u // units) & 1):
+                yield
+            assert ring[s] == u and P[x][t & 1] == t, ("P.V without its operands", x, t, ring[s], P[x][t & 1])
+            pv_in_flight[x] += 1
+
+            def fin(x=x, t=t, s=s, u=u):
+                assert ring[s] == u and P[x][t & 1] == t, ("V tile or P replaced while the P.V was in flight", x, t)
+                unit_reads_left[u] -= 1
+                pv_in_flight[x] -= 1
+                P[x][t & 1] = -1 - t               # consumed
+            tc_fifo.append(fin)
+            if hb == 1 and (x == 1 or j >= nkt[1]):
+                tc_fifo.append(lambda s=s: phase.__setitem__(("empty", s), phase[("empty", s)] + 1))
+            tc_fifo.append(lambda x=x, t=t: phase.__setitem__(("o_done", x, t & 1), phase[("o_done", x, t & 1)] + 1))
+
+        for t in range(2):
+            for x in range(2):
+                if t < steps_x[x]:
+                    yield from issue_s(x, t)
+                    yield
+        for t in range(max(steps_x)):
+            for x in range(2):
+                if t >= steps_x[x]:
+                    continue
+                yield from issue_pv(x, t)
+                yield
+                if t + 2 < steps_x[x]:
+                    yield from issue_s(x, t + 2)
+                    yield
+
+    def softmax(x):
+        for t in range(steps_x[x]):
+            par = t & 1
+            while not passed(("s_ready", x, par), (t >> 1) & 1):
+                yield
+            assert S[x][par] == t, ("softmax read other scores than its step's", x, t, S[x][par])
+            S[x][par] = -1 - t                     # taken into registers
+            yield
+            if rng.random() < 0.4 and t > 0:       # the running maximum rises: rescale the accumulator
+                while not passed(("o_done", x, (t - 1) & 1), ((t - 1) >> 1) & 1):
+                    yield
+                assert pv_in_flight[x] == 0, ("accumulator rescaled while a P.V was in flight", x, t)
+            elif t > 1:
+                while not passed(("o_done", x, par), ((t - 2) >> 1) & 1):
+                    yield
+            assert P[x][par] is None or P[x][par] < 0, ("P overwritten before its P.V had read it", x, t, P[x][par])
+            P[x][par] = t
+            phase[("p_ready", x, par)] += 1
+            done_steps[x] += 1
+            yield
+        if steps_x[x] > 0:
+            tl = steps_x[x] - 1
+            while not passed(("o_done", x, tl & 1), (tl >> 1) & 1):
+                yield
+            assert pv_in_flight[x] == 0
+
+    live = [producer(), mma(), softmax(0), softmax(1)]
+    spins = 0
+    while live or tc_fifo or tma_fifo:
+        spins += 1
+        assert spins < 400000, "the pipeline stopped making progress"
+        pick = rng.random()
+        if tc_fifo and (pick < 0.3 or not live):
+            tc_fifo.pop(0)()
+        elif tma_fifo and (pick < 0.5 or not live):
+            tma_fifo.pop(0)()
+        elif live:
+            g = rng.choice(live)
+            try:
+                next(g)
+            except StopIteration:
+                live.remove(g)
+    return done_steps
+
+
+@pytest.mark.parametrize("nkt0,nkt1", [(1, 0), (1, 2), (2, 3), (3, 4), (5, 6), (9, 0), (8, 9)])
+def test_prefill_64key_pipeline_protocol(nkt0, nkt1):
+    """The 64-key-step prefill variant has twelve barriers with per-parity phases and a three-unit ring shared by two query
+    tiles of different length; this runs its protocol under many random interleavings (and random rescale decisions)."""
+    for seed in range(40):
+        assert _simulate_prefill_64key_pipeline(nkt0, nkt1, seed) == [2 * nkt0, 2 * nkt1]
