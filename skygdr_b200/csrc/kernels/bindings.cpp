@@ -323,6 +323,20 @@ static void argmax(torch::Tensor logits, torch::Tensor out) {
     SKY_CUDA_CHECK(launch_argmax(bf16_ptr(logits), out.data_ptr<int>(), (int)logits.size(0), (int)logits.size(1), logits.stride(0), cur_stream()));
 }
 
+static void sample(torch::Tensor logits, torch::Tensor out, double temperature, int64_t seed, c10::optional<torch::Tensor> positions) {
+    c10::cuda::CUDAGuard g(logits.device());
+    TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && logits.scalar_type() == torch::kBFloat16, "logits: bf16 [rows][vocab]");
+    TORCH_CHECK(out.scalar_type() == torch::kInt32 && out.numel() >= logits.size(0), "out: int32, one entry per row");
+    TORCH_CHECK(temperature > 0, "temperature must be positive (use argmax for greedy)");
+    const int* pos = nullptr;
+    if (positions.has_value()) {
+        TORCH_CHECK(positions->scalar_type() == torch::kInt32 && positions->is_contiguous() && positions->numel() >= logits.size(0), "positions: int32, one per row");
+        pos = positions->data_ptr<int>();
+    }
+    SKY_CUDA_CHECK(launch_sample(bf16_ptr(logits), out.data_ptr<int>(), (int)logits.size(0), (int)logits.size(1), logits.stride(0),
+                                 (float)temperature, (unsigned int)seed, pos, cur_stream()));
+}
+
 // ---- GEMM ----
 // ss_in / ss_out: fp32 vectors of at least M entries (see GemmNormFuse); residual: y is the residual stream, updated in place.
 static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, bool gated, c10::optional<torch::Tensor> workspace,
@@ -510,6 +524,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("silu_mul", &silu_mul);
     m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("out"), py::arg("row_ss") = py::none());
     m.def("argmax", &argmax);
+    m.def("sample", &sample, py::arg("logits"), py::arg("out"), py::arg("temperature"), py::arg("seed"), py::arg("positions") = py::none());
     m.def("gemm", &gemm, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("splits"), py::arg("gated"), py::arg("workspace"), py::arg("counters"),
           py::arg("status"), py::arg("ntok"), py::arg("ss_in") = py::none(), py::arg("eps") = 1e-6, py::arg("residual") = false,
           py::arg("ss_out") = py::none(), py::arg("persistent") = false);

@@ -239,6 +239,56 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __res
     }
 }
 
+// Temperature sampling without a normalisation pass (Gumbel-max): argmax_c (logit_c / T + g_c) with g_c = -log(-log(u_c)) and
+// u_c uniform in (0, 1) picks column c with probability softmax(logits / T)_c. u_c comes from a counter-based hash of
+// (seed, position of the row's sequence, row, column), so a replayed CUDA graph draws fresh noise every step (the position
+// advances) and a given (seed, position) always draws the same token. The hash is restated in skygdr_b200/ops/small.py.
+__device__ __forceinline__ unsigned int sample_hash(unsigned int seed, unsigned int pos, unsigned int row, unsigned int col) {
+    unsigned int h = seed * 0x9E3779B1u ^ (pos + 0x7F4A7C15u) * 0x85EBCA77u ^ (row + 0x165667B1u) * 0xC2B2AE3Du ^ (col + 0x27D4EB2Fu) * 0x9E3779B1u;
+    h ^= h >> 16; h *= 0x85EBCA6Bu; h ^= h >> 13; h *= 0xC2B2AE35u; h ^= h >> 16;      // murmur3 finaliser
+    return h;
+}
+
+__global__ void __launch_bounds__(1024) sample_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, int vocab,
+                                                       long long row_stride, float inv_temperature, unsigned int seed,
+                                                       const int* __restrict__ positions) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    pdl_trigger();
+    pdl_wait();
+    const __nv_bfloat16* row = logits + (long long)blockIdx.x * row_stride;
+    const unsigned int pos = positions ? (unsigned int)positions[blockIdx.x] : 0u;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = threadIdx.x; c < vocab; c += 1024) {
+        const float u = ((float)(sample_hash(seed, pos, blockIdx.x, (unsigned int)c) >> 8) + 0.5f) * (1.0f / 16777216.0f);
+        const float v = __bfloat162float(row[c]) * inv_temperature - logf(-logf(u));
+        if (v > best || (v == best && c < bi)) { best = v; bi = c; }
+    }
+    for (int o = 16; o; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = sv[threadIdx.x]; bi = si[threadIdx.x];
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = bi;
+    }
+}
+
+cudaError_t launch_sample(const __nv_bfloat16* logits, int* out, int rows, int vocab, long long row_stride, float temperature,
+                          unsigned int seed, const int* positions, cudaStream_t stream) {
+    if (rows <= 0 || vocab <= 0 || !(temperature > 0.f)) return cudaErrorInvalidValue;
+    return launch_pdl(sample_kernel, dim3(rows), dim3(1024), 0, stream, logits, out, vocab, row_stride, 1.0f / temperature, seed, positions);
+}
+
 cudaError_t launch_argmax(const __nv_bfloat16* logits, int* out, int rows, int vocab, long long row_stride, cudaStream_t stream) {
     if (rows <= 0 || vocab <= 0) return cudaErrorInvalidValue;
     return launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, stream, logits, out, vocab, row_stride);

@@ -34,4 +34,8 @@ cudaError_t launch_embedding(const int* ids, const __nv_bfloat16* table, __nv_bf
                              float* row_ss = nullptr, int ss_slots = 0, int ss_pitch = 0);
 // Greedy sampling: out[r] = argmax_c logits[r][c] (lowest index wins ties).
 cudaError_t launch_argmax(const __nv_bfloat16* logits, int* out, int rows, int vocab, long long row_stride, cudaStream_t stream);
+// Temperature sampling: out[r] is drawn from softmax(logits[r] / temperature) by the Gumbel-max rule, with noise from a hash
+// of (seed, positions[r] or 0, r, column). Deterministic for given arguments; temperature > 0.
+cudaError_t launch_sample(const __nv_bfloat16* logits, int* out, int rows, int vocab, long long row_stride, float temperature,
+                          unsigned int seed, const int* positions, cudaStream_t stream);
 }  // namespace sky

@@ -147,6 +147,9 @@ class Qwen3Decoder:
         # prefill(): True runs its projections (more than 256 tokens) through the persistent GEMM with two TMEM accumulators
         # (compiled, not yet run on a GPU, hence off)
         self.prefill_gemm_persistent = False
+        # decode sampling: 0 = greedy (argmax); > 0 draws from softmax(logits / temperature), noise keyed by (sample_seed, position).
+        # Set before capture(): a captured graph keeps the choice it was captured with. Sampling has not run on a GPU yet.
+        self.temperature, self.sample_seed = 0.0, 0
         self._prefill_attn = None
         dev = pool.data.device
         self.device = dev
@@ -202,7 +205,7 @@ class Qwen3Decoder:
             ops.gemm(resid, lw.gate_up, out=act, gated=True, ss_in=ss[2 * li + 1], eps=cfg.eps)
             ops.gemm(act, lw.down, out=resid, residual=True, ss_out=ss[2 * li + 2])
         ops.gemm(resid, w.lm_head, out=self.logits[:b], ss_in=ss[2 * cfg.layers], eps=cfg.eps)
-        ops.argmax(self.logits[:b], out=self.next_ids[:b])
+        self._pick(b)
 
     def _step(self, b: int, max_ctx: int) -> None:
         if self.fuse_norm:
@@ -226,7 +229,13 @@ class Qwen3Decoder:
             ops.gemm(act, lw.down, out=h)
         ops.rmsnorm(h, w.final_norm, cfg.eps, residual=resid, out=xn)
         ops.gemm(xn, w.lm_head, out=self.logits[:b])
-        ops.argmax(self.logits[:b], out=self.next_ids[:b])
+        self._pick(b)
+
+    def _pick(self, b: int) -> None:
+        if self.temperature > 0:
+            ops.sample(self.logits[:b], self.temperature, self.sample_seed, positions=self.positions[:b], out=self.next_ids[:b])
+        else:
+            ops.argmax(self.logits[:b], out=self.next_ids[:b])
 
     def _advance(self, b: int) -> None:
         self.ids[:b].copy_(self.next_ids[:b])

@@ -60,3 +60,40 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
         out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
     load().argmax(logits, out)
     return out
+
+
+def sample(logits: torch.Tensor, temperature: float, seed: int, positions: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Draws one token per row from softmax(logits / temperature) (Gumbel-max over hashed noise, one pass, no normalisation).
+    Deterministic for a given (seed, positions): ``positions`` (int32, one per row) makes a replayed CUDA graph draw fresh
+    noise every step, since a sequence's position advances. Greedy decoding is ``argmax``. Compiled, not yet run on a GPU."""
+    if out is None:
+        out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    load().sample(logits, out, float(temperature), int(seed) & 0xFFFFFFFF, positions)
+    return out
+
+
+def sample_noise_reference(seed: int, positions: torch.Tensor, rows: int, vocab: int) -> torch.Tensor:
+    """The uniform numbers the sampling kernel hashes out of (seed, position, row, column), restated with integer tensor
+    arithmetic: fp32 [rows][vocab] in (0, 1). ``sample_reference`` builds the kernel's decision from them."""
+    M = 0xFFFFFFFF
+    r = torch.arange(rows, dtype=torch.int64)[:, None]
+    c = torch.arange(vocab, dtype=torch.int64)[None, :]
+    pos = positions.to(torch.int64).cpu()[:rows, None]
+    h = ((seed & M) * 0x9E3779B1 & M) ^ (((pos + 0x7F4A7C15) & M) * 0x85EBCA77 & M) ^ (((r + 0x165667B1) & M) * 0xC2B2AE3D & M) \
+        ^ (((c + 0x27D4EB2F) & M) * 0x9E3779B1 & M)
+    h = h ^ (h >> 16)
+    h = (h * 0x85EBCA6B) & M
+    h = h ^ (h >> 13)
+    h = (h * 0xC2B2AE35) & M
+    h = h ^ (h >> 16)
+    return ((h >> 8).to(torch.float32) + 0.5) * (1.0 / 16777216.0)
+
+
+def sample_reference(logits: torch.Tensor, temperature: float, seed: int, positions: Optional[torch.Tensor] = None):
+    """(token ids, perturbed values) of the Gumbel-max rule on the CPU in fp32: the oracle of ``sample``."""
+    rows, vocab = logits.shape
+    pos = positions if positions is not None else torch.zeros(rows, dtype=torch.int32)
+    u = sample_noise_reference(seed, pos, rows, vocab)
+    v = logits.float().cpu() * (1.0 / temperature) - torch.log(-torch.log(u))
+    return v.argmax(-1).int(), v

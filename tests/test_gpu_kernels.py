@@ -530,3 +530,23 @@ def test_persistent_gemm_matches_reference(ops, M, N, K, gated, ntok):
     assert err < 2e-2 * max(1.0, float(ref.abs().max())), float(err)
     y2 = ops.gemm(x, w, gated=gated)                      # the one-tile-per-CTA kernel must agree to rounding
     assert (y.float() - y2.float()).abs().max() < 2e-2 * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.skipif(os.environ.get("SKYGDR_TEST_SAMPLING") != "1", reason="the sampling kernel has not run on a GPU yet: opt in")
+def test_temperature_sampling_matches_the_cpu_restatement(ops):
+    """Gumbel-max sampling: the kernel's pick must be the CPU oracle's pick (same hash, fp32 arithmetic), except where the two
+    best perturbed values are within rounding of each other; positions change the draw, the seed changes the stream."""
+    torch.manual_seed(21)
+    rows, vocab = 48, 151936
+    logits = (torch.randn((rows, vocab), device="cuda") * 2.0).to(torch.bfloat16)
+    pos = torch.randint(0, 30000, (rows,), dtype=torch.int32, device="cuda")
+    got = ops.sample(logits, 0.7, seed=99, positions=pos).cpu()
+    want, v = ops.sample_reference(logits.cpu(), 0.7, 99, pos.cpu())
+    picked = v.gather(1, got.long()[:, None])[:, 0]
+    assert bool((picked >= v.max(-1).values - 1e-3).all())                 # the maximum, up to the accuracy of the fast logarithm
+    assert float((got == want).float().mean()) > 0.9
+    assert torch.equal(ops.sample(logits, 0.7, seed=99, positions=pos).cpu(), got)         # deterministic
+    assert not torch.equal(ops.sample(logits, 0.7, seed=99, positions=pos + 1).cpu(), got)
+    assert not torch.equal(ops.sample(logits, 0.7, seed=100, positions=pos).cpu(), got)
+    greedy = ops.argmax(logits).cpu()
+    assert float((ops.sample(logits, 1e-3, seed=1, positions=pos).cpu() == greedy).float().mean()) > 0.95

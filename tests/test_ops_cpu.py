@@ -679,3 +679,28 @@ def test_prefill_64key_pipeline_protocol(nkt0, nkt1):
     tiles of different length; this runs its protocol under many random interleavings (and random rescale decisions)."""
     for seed in range(40):
         assert _simulate_prefill_64key_pipeline(nkt0, nkt1, seed) == [2 * nkt0, 2 * nkt1]
+
+
+def test_gumbel_max_reference_samples_the_softmax():
+    """The sampling rule restated on the CPU (hash -> uniform -> Gumbel noise -> argmax): over many positions the picked tokens
+    follow softmax(logits / T), the same (seed, position) always picks the same token, and a low temperature approaches greedy."""
+    from skygdr_b200 import ops
+
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5, -3.0]]).to(torch.bfloat16)
+    T, n = 0.8, 40000
+    rows = logits.repeat(n, 1)
+    pos = torch.arange(n, dtype=torch.int32)
+    ids, _ = ops.sample_reference(rows, T, seed=123, positions=pos)
+    freq = torch.bincount(ids.long(), minlength=6).float() / n
+    want = torch.softmax(logits[0].float() / T, -1)
+    assert float((freq - want).abs().max()) < 0.01, (freq, want)
+    again, _ = ops.sample_reference(rows[:100], T, seed=123, positions=pos[:100])
+    assert torch.equal(again, ids[:100])
+    other, _ = ops.sample_reference(rows[:2000], T, seed=124, positions=pos[:2000])
+    assert float((other != ids[:2000]).float().mean()) > 0.3                     # another seed is another stream
+    cold, _ = ops.sample_reference(rows[:2000], 0.02, seed=5, positions=pos[:2000])
+    assert float((cold == 0).float().mean()) > 0.999
+    from skygdr_b200.ops.small import sample_noise_reference
+
+    u = sample_noise_reference(7, pos[:64], 64, 4096)
+    assert 0.0 < float(u.min()) and float(u.max()) < 1.0 and abs(float(u.mean()) - 0.5) < 0.005
