@@ -198,6 +198,7 @@ extern "C" __attribute__((visibility("default"))) int InitializeInjectionNvtx2(N
 """
 
 
+@pytest.mark.realtime
 def test_daemon_emits_timeline_ranges_to_an_attached_profiler(tmp_path):
     """SKYGDR_NVTX=1 makes fabricd wrap every control window, its policy pass and every request in an NVTX range. A small
     injection library stands in for the profiler and records what it is told."""
@@ -241,6 +242,7 @@ def _try(fn):
         return None
 
 
+@pytest.mark.realtime
 def test_daemon_process_with_two_links(tmp_path):
     """fabricd --link: flows registered over TCP on different links are paced independently, and the snapshot written at
     SIGTERM restores links and membership in a new daemon."""
@@ -274,6 +276,7 @@ def test_daemon_process_with_two_links(tmp_path):
             assert "kv_transfer:100:600:kv_transfer" in flows and flows.count(":nvlink:gpu0") == 2
 
 
+@pytest.mark.realtime
 def test_daemon_serves_the_same_protocol_on_a_unix_socket(tmp_path):
     path = str(tmp_path / "fabricd.sock")
     with FabricDaemon(window_us=2000, extra=["--unix", path]) as d:
