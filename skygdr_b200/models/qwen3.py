@@ -40,6 +40,16 @@ class Qwen3Config:
     def tiny(cls, layers: int = 2, vocab: int = 1024) -> "Qwen3Config":
         return cls(layers=layers, hidden=512, q_heads=8, kv_heads=2, ffn=1024, vocab=vocab, name="qwen3-tiny")
 
+    @classmethod
+    def from_hf(cls, hf) -> "Qwen3Config":
+        """From a Hugging Face ``Qwen3Config`` (or anything with the same attribute names)."""
+        rope = getattr(hf, "rope_theta", None)
+        if rope is None:                                    # newer configs keep it inside rope_parameters
+            rope = (getattr(hf, "rope_parameters", None) or {}).get("rope_theta", 1e6)
+        return cls(layers=hf.num_hidden_layers, hidden=hf.hidden_size, q_heads=hf.num_attention_heads, kv_heads=hf.num_key_value_heads,
+                   head_dim=getattr(hf, "head_dim", None) or hf.hidden_size // hf.num_attention_heads, ffn=hf.intermediate_size,
+                   vocab=hf.vocab_size, rope_theta=float(rope), eps=float(hf.rms_norm_eps), name=getattr(hf, "name_or_path", "") or "qwen3")
+
     @property
     def geometry(self) -> KVGeometry:
         return KVGeometry(self.layers, self.kv_heads, self.head_dim)
@@ -102,6 +112,50 @@ class Qwen3Weights:
         self.lm_head = rows_of(cfg.vocab, 900002, self.vocab_lo, self.vocab_hi, H)
         gen.manual_seed(seed * 1000003 + 900003)
         self.final_norm = (1.0 + 0.1 * torch.randn(H, generator=gen, device=device)).to(torch.bfloat16)
+
+    @classmethod
+    def from_state_dict(cls, cfg: Qwen3Config, sd, device="cuda", tp_rank: int = 0, tp_world: int = 1) -> "Qwen3Weights":
+        """Weights from a checkpoint in the Hugging Face Qwen3 naming (``model.layers.N.self_attn.q_proj.weight`` ...,
+        a ``state_dict()`` or any mapping of name -> tensor), converted to bf16 in the fused layouts the kernels take and cut
+        to the tensor-parallel shard ``tp_rank`` of ``tp_world``: qkv rows = this rank's [q heads | k heads | v heads], gate_up
+        rows = [gate | up] columns of this rank, O and down as the matching input slices, lm_head as a vocabulary slice.
+        With tied embeddings (no ``lm_head.weight``) the embedding table is the output projection."""
+        self = cls.__new__(cls)
+        self.cfg, self.tp_rank, self.tp_world = cfg, tp_rank, tp_world
+        H, D = cfg.hidden, cfg.head_dim
+        assert cfg.q_heads % tp_world == 0 and cfg.kv_heads % tp_world == 0 and cfg.ffn % tp_world == 0
+        qh, kh, ff = cfg.q_heads // tp_world, cfg.kv_heads // tp_world, cfg.ffn // tp_world
+
+        def t(name, shape):
+            x = sd[name]
+            assert tuple(x.shape) == tuple(shape), (name, tuple(x.shape), tuple(shape))
+            return x.detach().to(device=device, dtype=torch.bfloat16)
+
+        self.layers = []
+        for li in range(cfg.layers):
+            pre = f"model.layers.{li}."
+            w = LayerWeights()
+            q = t(pre + "self_attn.q_proj.weight", (cfg.q_heads * D, H))[tp_rank * qh * D:(tp_rank + 1) * qh * D]
+            k = t(pre + "self_attn.k_proj.weight", (cfg.kv_heads * D, H))[tp_rank * kh * D:(tp_rank + 1) * kh * D]
+            v = t(pre + "self_attn.v_proj.weight", (cfg.kv_heads * D, H))[tp_rank * kh * D:(tp_rank + 1) * kh * D]
+            w.qkv = torch.cat([q, k, v], 0).contiguous()
+            w.o = t(pre + "self_attn.o_proj.weight", (H, cfg.q_heads * D))[:, tp_rank * qh * D:(tp_rank + 1) * qh * D].contiguous()
+            gate = t(pre + "mlp.gate_proj.weight", (cfg.ffn, H))[tp_rank * ff:(tp_rank + 1) * ff]
+            up = t(pre + "mlp.up_proj.weight", (cfg.ffn, H))[tp_rank * ff:(tp_rank + 1) * ff]
+            w.gate_up = torch.cat([gate, up], 0).contiguous()
+            w.down = t(pre + "mlp.down_proj.weight", (H, cfg.ffn))[:, tp_rank * ff:(tp_rank + 1) * ff].contiguous()
+            w.ln1 = t(pre + "input_layernorm.weight", (H,)).clone()
+            w.ln2 = t(pre + "post_attention_layernorm.weight", (H,)).clone()
+            w.q_norm = t(pre + "self_attn.q_norm.weight", (D,)).clone()
+            w.k_norm = t(pre + "self_attn.k_norm.weight", (D,)).clone()
+            self.layers.append(w)
+        self.embed = t("model.embed_tokens.weight", (cfg.vocab, H)).contiguous()
+        vs = (cfg.vocab + tp_world - 1) // tp_world
+        self.vocab_lo, self.vocab_hi = tp_rank * vs, min(cfg.vocab, (tp_rank + 1) * vs)
+        head = t("lm_head.weight", (cfg.vocab, H)) if "lm_head.weight" in sd else self.embed
+        self.lm_head = head[self.vocab_lo:self.vocab_hi].clone().contiguous()
+        self.final_norm = t("model.norm.weight", (H,)).clone()
+        return self
 
     def fold_norms(self) -> "Qwen3Weights":
         """Multiplies the gains of the three RMSNorms that feed a projection (ln1 -> qkv, ln2 -> gate_up, final norm -> lm_head)

@@ -704,3 +704,39 @@ def test_gumbel_max_reference_samples_the_softmax():
 
     u = sample_noise_reference(7, pos[:64], 64, 4096)
     assert 0.0 < float(u.min()) and float(u.max()) < 1.0 and abs(float(u.mean()) - 0.5) < 0.005
+
+
+def test_checkpoint_loader_and_reference_forward_match_the_hugging_face_qwen3():
+    """A tiny random Qwen3 built by the transformers library, loaded through Qwen3Weights.from_state_dict: this package's
+    PyTorch forward (the oracle of all its GPU engines) must give the library's logits, which pins the architecture (QK-norm
+    before RoPE, rotate-half RoPE, GQA head order, gated SiLU MLP, norm placement) and the fused / sharded weight layouts."""
+    transformers = pytest.importorskip("transformers")
+    from skygdr_b200.models import Qwen3Config, Qwen3Weights, reference_forward
+
+    hc = transformers.Qwen3Config(vocab_size=300, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                                  num_key_value_heads=2, head_dim=128, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                                  max_position_embeddings=512)
+    torch.manual_seed(0)
+    hf = transformers.Qwen3ForCausalLM(hc).eval().to(torch.bfloat16)
+    with torch.no_grad():                                            # make the norms' gains non-trivial
+        for name, prm in hf.named_parameters():
+            if "norm" in name:
+                prm.copy_(1.0 + 0.2 * torch.randn_like(prm))
+    cfg = Qwen3Config.from_hf(hc)
+    assert (cfg.layers, cfg.hidden, cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab) == (2, 256, 4, 2, 128, 512, 300)
+    sd = hf.state_dict()
+    w = Qwen3Weights.from_state_dict(cfg, sd, device="cpu")
+    ids = torch.randint(0, 300, (23,))
+    with torch.no_grad():
+        want = hf.float()(ids[None]).logits[0]
+    got = reference_forward(cfg, w, ids)
+    err = float((got - want).abs().max() / want.abs().max())
+    assert err < 0.03, err                                           # bf16 rounding of activations between the layers is the only difference
+    assert float((got.argmax(-1) == want.argmax(-1)).float().mean()) > 0.85
+    # the shards of a two-way split are the matching slices of the full tensors
+    s1 = Qwen3Weights.from_state_dict(cfg, sd, device="cpu", tp_rank=1, tp_world=2)
+    D = cfg.head_dim
+    assert torch.equal(s1.layers[0].qkv[:2 * D], w.layers[0].qkv[2 * D:4 * D])                   # q heads 2-3
+    assert torch.equal(s1.layers[0].qkv[2 * D:3 * D], w.layers[0].qkv[4 * D + D:4 * D + 2 * D])  # k head 1
+    assert torch.equal(s1.layers[1].o, w.layers[1].o[:, 2 * D:]) and torch.equal(s1.layers[1].down, w.layers[1].down[:, 256:])
+    assert torch.equal(s1.layers[1].gate_up[:256], w.layers[1].gate_up[256:512]) and torch.equal(s1.lm_head, w.lm_head[150:])
