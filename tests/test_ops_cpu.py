@@ -740,3 +740,41 @@ def test_checkpoint_loader_and_reference_forward_match_the_hugging_face_qwen3():
     assert torch.equal(s1.layers[0].qkv[2 * D:3 * D], w.layers[0].qkv[4 * D + D:4 * D + 2 * D])  # k head 1
     assert torch.equal(s1.layers[1].o, w.layers[1].o[:, 2 * D:]) and torch.equal(s1.layers[1].down, w.layers[1].down[:, 256:])
     assert torch.equal(s1.layers[1].gate_up[:256], w.layers[1].gate_up[256:512]) and torch.equal(s1.lm_head, w.lm_head[150:])
+
+
+def test_block_allocator_never_hands_a_block_to_two_sequences():
+    """Random admit / grow / finish traffic over a small pool: every live block belongs to exactly one slot, block 0 stays out
+    of circulation, rows cover their contexts, a refused request leaves the row untouched, and everything comes back."""
+    import random
+
+    from skygdr_b200 import ops
+
+    rng = random.Random(3)
+    a = ops.BlockAllocator(num_blocks=64, max_seqs=6, max_ctx=400)
+    assert a.capacity == 63 and a.max_blocks == 25
+    ctx = [0] * 6
+    for _ in range(3000):
+        s = rng.randrange(6)
+        op = rng.random()
+        if op < 0.6:
+            want = min(400, ctx[s] + rng.choice([1, 1, 1, 16, 37, 120]))
+            before = (a.n_blocks[s], a.free_blocks)
+            if a.can_fit(s, want):
+                a.ensure(s, want)
+                ctx[s] = want
+            else:
+                with pytest.raises(MemoryError):
+                    a.ensure(s, want)
+                assert (a.n_blocks[s], a.free_blocks) == before
+        elif op < 0.75:
+            a.release(s)
+            ctx[s] = 0
+        owned = [b for k in range(6) for b in a.blocks_of(k).tolist()]
+        assert len(owned) == len(set(owned)) and 0 not in owned and len(owned) + a.free_blocks == a.capacity
+        assert all(a.n_blocks[k] == a.blocks_for(ctx[k]) for k in range(6))
+        assert all(int(a.table[k, a.n_blocks[k]:].abs().sum()) == 0 for k in range(6))
+    with pytest.raises(MemoryError):
+        a.ensure(0, 401)                                             # longer than a table row
+    for k in range(6):
+        a.release(k)
+    assert a.free_blocks == a.capacity and int(a.table.abs().sum()) == 0
