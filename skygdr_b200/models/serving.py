@@ -37,8 +37,11 @@ class Request:
 
 
 class ContinuousBatcher:
-    def __init__(self, engine, allocator: BlockAllocator):
+    def __init__(self, engine, allocator: BlockAllocator, use_graph: bool = True):
+        """use_graph: run the decode step as a replay of the engine's captured CUDA graph when the engine can capture one (the
+        step is launch-bound otherwise); the batch shape never changes, so one capture serves every step."""
         self.eng, self.alloc = engine, allocator
+        self._graph = bool(use_graph and hasattr(engine, "capture") and hasattr(engine, "replay"))
         self.slots: List[Optional[Request]] = [None] * engine.max_batch
         assert allocator.table.shape[0] >= engine.max_batch, "one table row per engine slot"
         self.waiting: Deque[Request] = deque()
@@ -102,7 +105,12 @@ class ContinuousBatcher:
             return out
         dev = self.eng.device
         self.eng.set_batch(self.h_ids.to(dev), self.h_pos.to(dev), self.alloc.table[:self.eng.max_batch].to(dev))
-        nxt = self.eng.step().cpu()
+        if self._graph:
+            if getattr(self.eng, "graph", None) is None or getattr(self.eng, "graph_batch", None) != self.eng.max_batch:
+                self.eng.capture(self.eng.max_batch, self.eng.max_ctx)
+            nxt = self.eng.replay().cpu()
+        else:
+            nxt = self.eng.step().cpu()
         self.steps += 1
         for slot, req in enumerate(self.slots):
             if req is None:

@@ -152,7 +152,8 @@ def test_tensor_parallel_shards_tile_the_full_weights():
 
 
 @pytest.mark.skipif(os.environ.get("SKYGDR_TEST_SERVING") != "1", reason="the continuous batcher has not driven the GPU engine yet: opt in")
-def test_continuous_batching_gives_each_request_the_tokens_it_gets_alone():
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_continuous_batching_gives_each_request_the_tokens_it_gets_alone(use_graph):
     """Requests of different lengths arrive while the batch is running and share engine steps; since every row of a step is
     computed independently of the other rows, a request must get exactly the tokens it gets when it runs alone."""
     from skygdr_b200 import ops
@@ -165,7 +166,7 @@ def test_continuous_batching_gives_each_request_the_tokens_it_gets_alone():
 
     def run(reqs, arrivals):
         alloc = ops.BlockAllocator(64, max_seqs=eng.max_batch, max_ctx=eng.max_ctx)
-        b = ContinuousBatcher(eng, alloc)
+        b = ContinuousBatcher(eng, alloc, use_graph=use_graph)
         out, pending = {}, list(reqs)
         step = 0
         while pending or not b.idle():
