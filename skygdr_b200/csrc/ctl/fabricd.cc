@@ -1,6 +1,6 @@
 // fabricd: the control daemon.
 //
-//   fabricd --port 7070 [--bind 127.0.0.1] [--policy target_track|ladder|static|none]
+//   fabricd --port 7070 [--bind 127.0.0.1] [--policy target_track|weighted_track|ladder|static|none]
 //           [--window_us 5000] [--capacity_gbps 64] [--lease_ms 5000] [--log PATH.csv]
 //           [--snapshot PATH.json] [--restore PATH.json] [--gpu N --util_source pcie_rx|pcie_tx|sum]
 //           [--link NAME=GBPS ...]   more links beside the default one (each a shared capacity with its own policy pass)

@@ -237,7 +237,40 @@ private:
     bool released_ = true;
 };
 
+// target_track with the unprotected share split by priority instead of evenly: while a protected flow is being served, an
+// unprotected flow i that is active gets (priority_i + 1) / sum over the active unprotected flows of what the link has left,
+// and an idle one is offered what it would get if it woke up. Priorities below the protection line thus act as weights among
+// the best-effort traffic (the reference knows two classes only: the protected restore and everything else).
+class WeightedTrackPolicy : public TargetTrackPolicy {
+public:
+    using TargetTrackPolicy::TargetTrackPolicy;
+    const char* name() const override { return "weighted_track"; }
+    std::vector<FlowDecision> step(const std::vector<FlowSignal>& flows, const LinkSignal& link) override {
+        std::vector<FlowDecision> out = TargetTrackPolicy::step(flows, link);
+        double total = 0, weights_active = 0;
+        int n_be = 0;
+        for (size_t i = 0; i < flows.size() && i < out.size(); ++i) {
+            if (is_protected(flows[i]) || out[i].budget_gbps < 0) continue;
+            total += out[i].budget_gbps;                       // the even split adds up to the unprotected share
+            ++n_be;
+            if (flows[i].active) weights_active += weight(flows[i]);
+        }
+        if (n_be < 2) return out;
+        for (size_t i = 0; i < flows.size() && i < out.size(); ++i) {
+            if (is_protected(flows[i]) || out[i].budget_gbps < 0) continue;
+            const double w = weight(flows[i]);
+            const double denom = flows[i].active ? weights_active : weights_active + w;
+            out[i].budget_gbps = std::max(cfg.min_be_fraction * link.capacity_gbps / n_be, total * w / std::max(1e-9, denom));
+        }
+        return out;
+    }
+
+private:
+    static double weight(const FlowSignal& f) { return double(std::max(0, f.priority)) + 1.0; }
+};
+
 inline std::unique_ptr<Policy> make_policy(const std::string& name, const PolicyConfig& cfg) {
+    if (name == "weighted_track") return std::make_unique<WeightedTrackPolicy>(cfg);
     if (name == "none" || name == "always_high") return std::make_unique<NonePolicy>(cfg);
     if (name == "static" || name == "always_low") return std::make_unique<StaticPolicy>(cfg);
     if (name == "ladder") return std::make_unique<LadderPolicy>(cfg);

@@ -209,3 +209,23 @@ def test_simulated_links_are_independent(ctl):
     res0 = ctl.run_simulation(cfg, [prot, be_same, be_other])
     ft0 = sorted(res0.flow_times_ms(1))
     assert ft0[len(ft0) // 2] > ft[len(ft) // 2] * 1.2
+
+
+def test_weighted_track_splits_the_unprotected_share_by_priority(ctl):
+    """Two best-effort flows with priorities 10 and 0 next to a protected flow: while the protected flow is served they share
+    what is left 11 : 1 (target_track gives them halves); alone on the link, priorities do not matter."""
+    def run(policy):
+        cfg = ctl.SimConfig()
+        cfg.capacity_gbps, cfg.duration_s, cfg.drain_s, cfg.policy = 64.0, 2.0, 0.5, policy
+        prot, a, b = ctl.SimFlowSpec(), ctl.SimFlowSpec(), ctl.SimFlowSpec()
+        prot.name, prot.priority, prot.target_gbps, prot.backlogged = "kv_transfer", 100, 40.0, True     # always being served
+        a.name, a.priority, a.backlogged = "offload_important", 10, True
+        b.name, b.priority, b.backlogged = "offload_background", 0, True
+        return ctl.run_simulation(cfg, [prot, a, b])
+
+    w = run("weighted_track")
+    assert w.bytes_moved[0] == pytest.approx(40e9 * 2.0, rel=0.1)                   # the protected flow gets its goal
+    assert w.bytes_moved[1] / w.bytes_moved[2] == pytest.approx(11.0, rel=0.15)
+    assert sum(w.bytes_moved) == pytest.approx(64e9 * 2.0, rel=0.05)                # nothing is wasted
+    t = run("target_track")
+    assert t.bytes_moved[1] / t.bytes_moved[2] == pytest.approx(1.0, rel=0.1)
