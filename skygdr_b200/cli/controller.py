@@ -1,7 +1,7 @@
 """The signal -> policy -> action loop of the PCIe case study, as a command-line program.
 
     python -m skygdr_b200.cli.controller --cpu_control_host H --cpu_control_port P --baseline_restore_gib_s B --log_dir D
-        [--policy ladder|target_track] [--poll_ms 100] [--restore_total_bytes 64G] [--restore_max_outstanding_bytes 4G] ...
+        [--policy ladder|target_track|weighted_track] [--poll_ms 100] [--restore_total_bytes 64G] [--restore_max_outstanding_bytes 4G] ...
 
 Arguments, output files (`<tag>_{restore_progress,gpu_metrics,controller}.csv`), the 18-column controller CSV and
 the decision names (HOLD | SWITCH_LOW1 | ESCALATE_LOWn | RESTORE_DONE_HIGH | STOP) are those of
@@ -111,7 +111,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--exit_windows", type=int, default=2)
     ap.add_argument("--log_dir", required=True)
     ap.add_argument("--tag", default="case_study")
-    ap.add_argument("--policy", default="ladder", choices=["ladder", "target_track", "none", "static"])
+    ap.add_argument("--policy", default="ladder", choices=["ladder", "target_track", "weighted_track", "none", "static"])
     ap.add_argument("--pcie_bin", default="", help="program of the protected flow (reference flag); default: this package's gpu_pcie_memcpy")
     ap.add_argument("--gpu_metrics_script", default="", help="signal logger script (reference flag); default: this package's gpu_metrics_logger")
     ap.add_argument("--restore_cmd", default="", help="override the protected-flow command (must write the progress CSV given by {progress})")

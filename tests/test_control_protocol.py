@@ -213,7 +213,7 @@ def test_protocol_survives_arbitrary_lines(ctl):
 
     words = st.sampled_from(["REGISTER", "RENEW", "UNREGISTER", "BUDGET", "FLOWS", "FLOW", "POLICY", "WINDOW", "CAPACITY", "PING", "STATUS", "HIGH",
                              "LOW", "LOW1", "LOW2", "LOW3", "LOW4", "SLEEP", "STOP", "kv_transfer", "kv_offload", "high", "low", "besteffort",
-                             "nan", "inf", "-1", "0", "1", "2", "40", "1e308", "99999999999999999999", "target_track", "ladder", "static", "none", "x",
+                             "nan", "inf", "-1", "0", "1", "2", "40", "1e308", "99999999999999999999", "target_track", "weighted_track", "ladder", "static", "none", "x",
                              "LINK", "LINKS", "STATS", "link=default", "link=nv", "link=", "nv", "default", "700"])
     junk = st.text(alphabet=st.characters(blacklist_categories=("Cs",), blacklist_characters="\n"), max_size=40)
     line = st.one_of(st.lists(st.one_of(words, junk), max_size=8).map(" ".join), junk)
