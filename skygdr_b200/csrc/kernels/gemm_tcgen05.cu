@@ -434,7 +434,12 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
             const int buf = j & 1;
             const int n0 = (tile / tiles_m) * BM, t0 = (tile % tiles_m) * NTOK;
-            if (!mbar_wait(&acc_full[buf], (uint32_t)(j >> 1) & 1)) { if (lane == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 64); break; }
+            // All 128 epilogue threads take the same way out: they meet at named barriers below, so a wait that gave up in
+            // some of them only (the deadline is per thread) must end the loop for all of them.
+            const uint32_t mine = mbar_wait(&acc_full[buf], (uint32_t)(j >> 1) & 1) ? 1u : 0u;
+            uint32_t n_ok;
+            asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.popc.u32 %0, 3, 128, q;\n\t}" : "=r"(n_ok) : "r"(mine) : "memory");
+            if (n_ok != 128u) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 64); break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + (uint32_t)(buf * S::ACC_COLS) + ((uint32_t)(slice * 32) << 16);
 #pragma unroll 1
