@@ -32,6 +32,7 @@ PYBIND11_MODULE(_ctl, m) {
           py::arg("head_dim"), py::arg("elem_bytes"), py::arg("align") = 256);
     m.def("pcie_lane_gbs", &pcie_lane_gbs);
     m.def("hbm_peak_gbs", &hbm_peak_gbs);
+    m.def("nvlink_peak_gbs", &nvlink_peak_gbs);
     m.attr("CREDIT_MAGIC") = py::int_((uint64_t)SKYGDR_CREDIT_MAGIC);
     m.attr("CREDIT_PAGE_BYTES") = py::int_(SKYGDR_CREDIT_PAGE_BYTES);
 

@@ -107,6 +107,16 @@ inline double hbm_peak_gbs(const std::string& name) {
     return 0;
 }
 
+// Nominal NVLink bandwidth per direction per GPU in GB/s by product name (all links together); 0 when unknown or absent.
+inline double nvlink_peak_gbs(const std::string& name) {
+    struct Row { const char* key; double gbs; };
+    static const Row rows[] = {
+        {"GB200", 900}, {"B200", 900}, {"B100", 900}, {"H200", 450}, {"H100 PCIe", 0}, {"H100", 450}, {"A100-SXM", 300}, {"A100", 300}, {"V100", 150},
+    };
+    for (auto& r : rows) if (name.find(r.key) != std::string::npos) return r.gbs;
+    return 0;
+}
+
 struct PcieSample {
     uint64_t ts_unix_ms = 0;
     double t_ms = 0;

@@ -577,3 +577,20 @@ def test_compat_client_registers_on_the_link_named_in_its_environment():
             if p.poll() is None:
                 p.kill()
         assert p.returncode == 0 and "link=roce0" in err
+
+
+def test_topology_turns_a_gpu_into_link_definitions_the_daemon_accepts():
+    """NVLink, PCIe and HBM capacities of a GPU from (stand-in) NVML, and fabricd started with them."""
+    from skygdr_b200.cli.topology import links_of_gpu
+
+    fake = {"name": "NVIDIA B200", "pcie_gen": 5, "pcie_width": 16, "pcie": lambda c: 0, "util": lambda: (0, 0), "nvlink": lambda: (0, 0)}
+    links = links_of_gpu(3, fake)
+    assert links == {"nvlink:gpu3": 769.5, "pcie:gpu3": pytest.approx(63.0, abs=0.1), "hbm:gpu3": 7700.0}
+    assert "nvlink:gpu0" not in links_of_gpu(0, dict(fake, name="NVIDIA H100 PCIe"))             # no NVLink on that product
+    assert links_of_gpu(0, dict(fake, name="Some Future GPU")) == {"pcie:gpu0": pytest.approx(63.0, abs=0.1)}
+    extra = [x for k, v in links.items() for x in ("--link", f"{k}={v}")]
+    with FabricDaemon(window_us=2000, extra=extra) as d, FabricClient(port=d.port) as c:
+        assert c.request("LINKS").startswith("OK n=4 default:64 nvlink:gpu3:769.5 pcie:gpu3:63")
+        assert c.register("kv_transfer", "high", 600.0, link="nvlink:gpu3").flow_id == 1
+    r = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.topology"], capture_output=True, text=True, env=ENV, timeout=60)
+    assert (r.returncode == 0 and "--link" in r.stdout) or (r.returncode == 1 and "NVML" in r.stderr)     # with or without a GPU
