@@ -43,6 +43,13 @@ def env_info() -> Dict:
             info["nvidia_smi"] = out[0]
     except Exception:
         pass
+    try:       # how the GPUs are wired (NVLink / PCIe matrix), read-only
+        topo = subprocess.run(["nvidia-smi", "topo", "-m"], capture_output=True, text=True, timeout=10).stdout
+        rows = [ln.rstrip() for ln in topo.splitlines() if ln.startswith(("GPU", "\tGPU", " "))][:10]
+        if rows:
+            info["topology"] = rows
+    except Exception:
+        pass
     return info
 
 
