@@ -212,7 +212,11 @@ PYBIND11_MODULE(_ctl, m) {
     py::class_<DaemonCore>(m, "DaemonCore")
         .def(py::init<const DaemonConfig&>())
         .def("handle_line", &DaemonCore::handle_line)
-        .def("step_window", &DaemonCore::step_window, py::arg("now_ns"), py::arg("external_util_pct") = 0.0)
+        .def("step_window", [](DaemonCore& d, uint64_t now_ns, double external_util_pct, py::object link_gbps) {
+            if (link_gbps.is_none()) return d.step_window(now_ns, external_util_pct);
+            const auto m = link_gbps.cast<std::map<std::string, double>>();
+            return d.step_window(now_ns, external_util_pct, &m);
+        }, py::arg("now_ns"), py::arg("external_util_pct") = 0.0, py::arg("link_gbps") = py::none())
         .def("snapshot_json", &DaemonCore::snapshot_json)
         .def("restore_json", &DaemonCore::restore_json)
         .def("keep_pages_on_exit", &DaemonCore::keep_pages_on_exit)

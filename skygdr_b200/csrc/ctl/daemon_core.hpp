@@ -273,7 +273,11 @@ public:
 
     // ---- one control window ----
     // external_util_pct is used when cfg.external_util is set (e.g. NVML PCIe utilisation).
-    std::vector<WindowLog> step_window(uint64_t now_ns, double external_util_pct = 0.0) {
+    // link_gbps (optional): measured traffic per link name in GB/s (NVML counters of the GPU the link belongs to); a link found
+    // there takes its utilisation from it instead of from the sum over its registered flows, which misses traffic that did
+    // not register.
+    std::vector<WindowLog> step_window(uint64_t now_ns, double external_util_pct = 0.0,
+                                       const std::map<std::string, double>* link_gbps = nullptr) {
         const auto t_step0 = std::chrono::steady_clock::now();
         for (uint32_t id : reg_.expire(now_ns)) { drop_state(id); ++expired_; }
         auto flows = reg_.snapshot();
@@ -311,6 +315,11 @@ public:
             link.capacity_gbps = links_[li].capacity_gbps;
             // a supplied utilisation (NVML) describes the first link; the others are summed from their flows
             link.util_pct = (cfg_.external_util && li == 0) ? external_util_pct : 100.0 * sum_gbps[li] / std::max(1e-9, link.capacity_gbps);
+            if (link_gbps) {
+                auto m = link_gbps->find(links_[li].name);
+                if (m != link_gbps->end() && std::isfinite(m->second) && m->second >= 0)
+                    link.util_pct = 100.0 * m->second / std::max(1e-9, link.capacity_gbps);
+            }
             links_[li].last_util_pct = link.util_pct;
             auto dec = links_[li].policy->step(lsig, link);
             for (size_t k = 0; k < dec.size() && k < members[li].size(); ++k) {

@@ -5,6 +5,8 @@
 //           [--snapshot PATH.json] [--restore PATH.json] [--gpu N --util_source pcie_rx|pcie_tx|sum]
 //           [--link NAME=GBPS ...]   more links beside the default one (each a shared capacity with its own policy pass)
 //           [--unix PATH]            also listen on a Unix-domain socket (same protocol; for clients on the same host)
+//           [--link_signal NAME=GPU:pcie_rx|pcie_tx|nvlink_rx|nvlink_tx ...]   a link's utilisation from that GPU's NVML counters
+//                                    (sampled by a thread of its own) instead of the sum over its registered flows
 //           [--enter_ratio 0.65 --exit_ratio 0.80 --util_threshold_pct 85 --enter_windows 1 --exit_windows 2]
 //
 // A TCP line server (one or more commands per connection, each answered by one
@@ -27,6 +29,7 @@
 
 #include <atomic>
 #include <cerrno>
+#include <map>
 #include <mutex>
 #include <thread>
 
@@ -70,6 +73,8 @@ int main(int argc, char** argv) {
     std::string bind_ip = "127.0.0.1", log_path, snap_path, restore_path, util_source = "sum";
     std::vector<std::pair<std::string, std::string>> link_defs;
     std::string unix_path;
+    struct LinkSignalDef { std::string link, source; int gpu = 0; };
+    std::vector<LinkSignalDef> signal_defs;
     for (int i = 1; i < argc; ++i) {
         std::string k = argv[i];
         std::string v;
@@ -104,6 +109,17 @@ int main(int argc, char** argv) {
         }
         else if (k == "--dead_fallback_gbps") cfg.dead_fallback_gbps = atof(v.c_str());
         else if (k == "--unix") unix_path = v;
+        else if (k == "--link_signal") {
+            const size_t e = v.rfind('='), c = v.rfind(':');
+            LinkSignalDef d;
+            if (e == std::string::npos || c == std::string::npos || c < e) { fprintf(stderr, "fabricd: --link_signal NAME=GPU:SOURCE\n"); return 2; }
+            d.link = v.substr(0, e); d.gpu = atoi(v.substr(e + 1, c - e - 1).c_str()); d.source = v.substr(c + 1);
+            if (d.source != "pcie_rx" && d.source != "pcie_tx" && d.source != "nvlink_rx" && d.source != "nvlink_tx") {
+                fprintf(stderr, "fabricd: --link_signal source is pcie_rx, pcie_tx, nvlink_rx or nvlink_tx\n");
+                return 2;
+            }
+            signal_defs.push_back(d);
+        }
         else if (k == "--link") {
             const size_t e = v.rfind('=');
             if (e == std::string::npos || e == 0) { fprintf(stderr, "fabricd: --link NAME=GBPS\n"); return 2; }
@@ -142,6 +158,41 @@ int main(int argc, char** argv) {
             core.policy_name(), (unsigned long long)(cfg.window_ns / 1000), cfg.capacity_gbps);
     if (trace_enabled()) fprintf(stderr, "fabricd: nvtx ranges %s\n", trace_compiled_in() ? "on" : "requested but not compiled in");
 
+    // Measured traffic of the links that have a signal: a sampler thread keeps the latest GB/s per link (the NVML calls
+    // average over tens of milliseconds and may block that long, which a control window cannot afford).
+    for (auto& d : signal_defs) {
+        const std::string rep = core.handle_line("LINK " + d.link, mono_ns());
+        if (rep.compare(0, 2, "OK") != 0) { fprintf(stderr, "fabricd: --link_signal names an unknown link %s\n", d.link.c_str()); return 2; }
+    }
+    std::mutex sig_mu;
+    std::map<std::string, double> measured_gbps;
+    std::thread sampler;
+    if (!signal_defs.empty()) {
+        NvmlApi api = NvmlApi::load();
+        if (!api.ok()) fprintf(stderr, "fabricd: NVML is not available, --link_signal is ignored\n");
+        else sampler = std::thread([&, api] {
+            std::map<int, std::unique_ptr<GpuSignals>> gpus;
+            for (auto& d : signal_defs)
+                if (!gpus.count(d.gpu)) gpus[d.gpu] = std::make_unique<GpuSignals>(api, (unsigned)d.gpu);
+            while (!g_stop.load()) {
+                for (auto& d : signal_defs) {
+                    GpuSignals& gs = *gpus[d.gpu];
+                    double gbps = -1;
+                    if (d.source.compare(0, 4, "pcie") == 0) {
+                        PcieSample s = gs.sample_pcie();
+                        if (s.valid) gbps = (d.source == "pcie_tx" ? s.tx_gib_s : s.rx_gib_s) * 1.073741824;
+                    } else {
+                        NvlinkSample s = gs.sample_nvlink();
+                        if (s.valid) gbps = d.source == "nvlink_tx" ? s.tx_gb_s : s.rx_gb_s;
+                    }
+                    std::lock_guard<std::mutex> g(sig_mu);
+                    if (gbps >= 0) measured_gbps[d.link] = gbps; else measured_gbps.erase(d.link);
+                }
+                std::this_thread::sleep_for(std::chrono::milliseconds(5));
+            }
+        });
+    }
+
     std::mutex mu;
     FILE* log = log_path.empty() ? nullptr : fopen(log_path.c_str(), "w");
     if (log) { fprintf(log, "%s\n", DaemonCore::window_csv_header()); fflush(log); }
@@ -164,7 +215,9 @@ int main(int argc, char** argv) {
             {
                 std::lock_guard<std::mutex> g(mu);
                 TraceRange r("fabricd.policy_and_grants");
-                logs = core.step_window(now, util);
+                std::map<std::string, double> seen;
+                if (sampler.joinable()) { std::lock_guard<std::mutex> sg(sig_mu); seen = measured_gbps; }
+                logs = core.step_window(now, util, seen.empty() ? nullptr : &seen);
                 win_ns = core.config().window_ns;
             }
             if (log) {
@@ -242,6 +295,7 @@ int main(int argc, char** argv) {
     }
     for (auto& t : conns) t.join();
     timer.join();
+    if (sampler.joinable()) sampler.join();
     close(ls);
     if (uls >= 0) { close(uls); unlink(unix_path.c_str()); }
     if (!snap_path.empty()) {

@@ -287,3 +287,25 @@ def test_daemon_serves_the_same_protocol_on_a_unix_socket(tmp_path):
             assert local.renew(h) and local.request("PING") == "OK pong"
             assert remote.unregister(h) and local.request("FLOWS").startswith("OK n=0")
     assert not os.path.exists(path)                    # the daemon removes its socket file on the way out
+
+
+def test_link_signal_flag_is_checked_and_degrades_without_nvml(tmp_path):
+    """--link_signal must name a defined link and a known source; on a machine without NVML the daemon says so and serves on,
+    taking the link's utilisation from its flows as before."""
+    import subprocess
+
+    from skygdr_b200 import build
+    from skygdr_b200.control.daemon import free_port
+
+    exe = str(build.build_bin() / "fabricd")
+    r = subprocess.run([exe, "--port", str(free_port()), "--link_signal", "nope=0:pcie_rx"], capture_output=True, text=True, timeout=20)
+    assert r.returncode == 2 and "unknown link" in r.stderr
+    r = subprocess.run([exe, "--port", str(free_port()), "--link", "pcie:gpu0=55", "--link_signal", "pcie:gpu0=0:bogus"],
+                       capture_output=True, text=True, timeout=20)
+    assert r.returncode == 2 and "source is" in r.stderr
+    with FabricDaemon(window_us=2000, extra=["--link", "pcie:gpu0=55", "--link_signal", "pcie:gpu0=0:pcie_rx"]) as d:
+        with FabricClient(port=d.port) as c:
+            assert c.register("offload", "besteffort", 0.0, link="pcie:gpu0").flow_id == 1
+            time.sleep(0.05)
+            assert c.request("STATS").startswith("OK windows=")
+    assert d.proc.returncode == 0

@@ -332,3 +332,26 @@ def test_flows_on_different_links_do_not_take_bandwidth_from_one_another(ctl):
     assert d2.handle_line("LINKS", 0) == "OK n=2 default:32 nvlink:gpu0:900\n"
     assert d2.handle_line("LINK nvlink:gpu0", 0).endswith("flows=2\n")
     assert "3:kv_offload:0:0:kv_offload:HIGH" in d2.handle_line("FLOWS", 0) and "2:kv_bursts:0:0:kv_transfer:CUSTOM:nvlink:gpu0" in d2.handle_line("FLOWS", 0)   # throttled when the snapshot was taken
+
+
+def test_measured_link_traffic_replaces_the_sum_over_registered_flows(ctl):
+    """Traffic that never registered (another job's copies on the same PCIe link) is invisible in the flows' counters; with a
+    measured figure for the link, the ladder policy sees the link as busy and protects the restore flow."""
+    d = _core(ctl, policy="ladder")
+    d.handle_line("LINK pcie:gpu0 55", 0)
+    d.handle_line("REGISTER restore high 30 link=pcie:gpu0", 0)
+    d.handle_line("REGISTER offload besteffort 0 link=pcie:gpu0", 0)
+    win = 5_000_000
+    d.step_window(win)
+    for k in range(2, 6):                                              # the restore gets 10 GB/s of its 30, the offload 5
+        d.report_usage(1, k * 50_000_000, k * 50_000_000, 1 << 30)
+        d.report_usage(2, k * 25_000_000, k * 25_000_000, 1 << 40)
+        logs = d.step_window(k * win)                                   # by the flows' counters the link is a quarter busy
+    assert all(l.link_util_pct < 40 for l in logs) and [l.decision for l in logs if l.flow == "offload"] == ["HOLD"]
+    for k in range(6, 10):
+        d.report_usage(1, k * 50_000_000, k * 50_000_000, 1 << 30)
+        d.report_usage(2, k * 25_000_000, k * 25_000_000, 1 << 40)
+        logs = d.step_window(k * win, 0.0, {"pcie:gpu0": 52.0})         # NVML says 52 of 55 GB/s are in use
+    off = [l for l in logs if l.flow == "offload"][0]
+    assert off.link_util_pct == pytest.approx(100 * 52 / 55) and off.mode != 1                 # escalated out of HIGH
+    assert d.step_window(10 * win, 0.0, {"other": 1.0})[0].link_util_pct < 40                  # names that match no link are ignored
