@@ -1,6 +1,6 @@
 """The links of this machine's GPUs, as `fabricd --link` arguments.
 
-    python -m skygdr_b200.cli.topology [--gpus 0,1,...] [--nvlink_efficiency 0.855] [--json]
+    python -m skygdr_b200.cli.topology [--gpus 0,1,...] [--nvlink_efficiency 0.855] [--signals] [--json]
     skygdr_b200/bin/fabricd --port 7070 $(python -m skygdr_b200.cli.topology)
 
 Per GPU, three shared capacities that flows can register on (`REGISTER ... link=<name>`):
@@ -42,6 +42,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", default="", help="comma list; default: every GPU that NVML shows")
     ap.add_argument("--nvlink_efficiency", type=float, default=0.855, help="share of nominal NVLink that a peer copy reaches (770 of 900 GB/s measured)")
+    ap.add_argument("--signals", action="store_true", help="also bind every NVLink / PCIe link to its GPU's inbound NVML counter (--link_signal)")
     ap.add_argument("--json", action="store_true")
     a = ap.parse_args(argv)
     ids = [int(x) for x in a.gpus.split(",") if x] if a.gpus else range(64)
@@ -57,7 +58,13 @@ def main(argv=None) -> int:
     if not links:
         print("NVML is not available on this machine", file=sys.stderr)
         return 1
-    print(json.dumps(links, indent=1) if a.json else " ".join(f"--link {k}={v}" for k, v in links.items()))
+    args = [f"--link {k}={v}" for k, v in links.items()]
+    if a.signals:
+        for k in links:
+            kind, _, gpu = k.partition(":gpu")
+            if kind in ("nvlink", "pcie"):
+                args.append(f"--link_signal {k}={gpu}:{kind}_rx")
+    print(json.dumps(links, indent=1) if a.json else " ".join(args))
     return 0
 
 
