@@ -778,3 +778,118 @@ def test_block_allocator_never_hands_a_block_to_two_sequences():
     for k in range(6):
         a.release(k)
     assert a.free_blocks == a.capacity and int(a.table.abs().sum()) == 0
+
+
+def _stub_kernels(monkeypatch, calls):
+    """Replaces this package's kernel entry points with recorders, so that the engines' Python (buffers, call order, options)
+    runs on a machine without a GPU."""
+    import skygdr_b200.ops as ops
+
+    class Attn:
+        def __init__(self, *a, **k):
+            self.status = torch.zeros(4, dtype=torch.int32)
+            self.kw = k
+
+        def __call__(self, q, pool, li, table, ctx, max_ctx=None, out=None):
+            calls.append("attn")
+            return out
+
+    def shaped(name, a, k):
+        """What the real op returns when no output buffer is passed: a tensor of the right shape."""
+        if name == "embedding":
+            return torch.zeros((a[0].numel(), a[1].shape[1]), dtype=torch.bfloat16)
+        if name == "rmsnorm":
+            return torch.zeros_like(a[0])
+        if name == "gemm":
+            return torch.zeros((a[0].shape[0], a[1].shape[0] // (2 if k.get("gated") else 1)), dtype=torch.bfloat16)
+        if name == "rope_append":
+            return torch.zeros((a[0].shape[0], a[8], 128), dtype=torch.bfloat16)      # q: [tokens][q_heads][128]
+        return None
+
+    def rec(name):
+        def f(*a, **k):
+            calls.append((name, {x: (v if isinstance(v, (bool, int, float, str)) else "tensor") for x, v in k.items() if x not in ("out", "q_out") and v is not None}))
+            out = k.get("out", k.get("q_out"))
+            return out if out is not None else shaped(name, a, k)
+        return f
+
+    class Prefill:
+        def __init__(self, dev, *a, **k):
+            pass
+
+        def __call__(self, q, pool, li, table, seq_start, max_len, out=None):
+            calls.append("prefill_attn")
+            return out
+
+    monkeypatch.setattr(ops, "PagedAttention", Attn)
+    monkeypatch.setattr(ops, "PrefillAttention", Prefill)
+    for name in ("embedding", "rmsnorm", "gemm", "rope_append", "argmax", "sample", "silu_mul"):
+        monkeypatch.setattr(ops, name, rec(name))
+    monkeypatch.setattr(ops, "rope_inv_freq", lambda theta, dev, D: torch.ones(D // 2))
+
+
+def test_decode_engine_issues_the_expected_kernel_sequence(monkeypatch):
+    """The decode engine's host side with the kernels stubbed out: the default step is embedding, eight kernels per layer, final
+    norm, lm_head, argmax; the norm-free step has six per layer and passes the row sums from producer to consumer; a positive
+    temperature swaps argmax for the sampling kernel keyed by the positions."""
+    from skygdr_b200 import ops
+    from skygdr_b200.models import Qwen3Config, Qwen3Decoder, Qwen3Weights
+
+    calls = []
+    _stub_kernels(monkeypatch, calls)
+    cfg = Qwen3Config.tiny(layers=2)
+    pool = ops.PagedKVPool(cfg.geometry, 8, "hnd", device="cpu")
+    eng = Qwen3Decoder(cfg, Qwen3Weights(cfg, "cpu", seed=0), pool, max_batch=2, max_ctx=64, attn_chunk=64)
+    eng.set_batch(torch.tensor([1, 2], dtype=torch.int32), torch.tensor([3, 4], dtype=torch.int32), torch.zeros((2, 4), dtype=torch.int32))
+    assert eng.ctx_lens.tolist() == [4, 5]
+    out = eng.step(max_ctx=64)
+    names = [c if isinstance(c, str) else c[0] for c in calls]
+    layer = ["rmsnorm", "gemm", "rope_append", "attn", "gemm", "rmsnorm", "gemm", "gemm"]
+    assert names == ["embedding"] + layer * 2 + ["rmsnorm", "gemm", "argmax"] and len(names) == eng.kernels_per_step
+    assert out.shape == (2,) and eng.positions.tolist() == [4, 5] and eng.ctx_lens.tolist() == [5, 6]      # the step advanced the batch
+    assert [c[1].get("gated", False) for c in calls if not isinstance(c, str) and c[0] == "gemm"] == [False, False, True, False] * 2 + [False]
+    calls.clear()
+    eng.temperature, eng.sample_seed = 0.7, 5
+    eng.step(max_ctx=64)
+    assert calls[-1][0] == "sample" and calls[-1][1] == {"positions": "tensor"}
+
+    calls.clear()
+    fused = Qwen3Decoder(cfg, Qwen3Weights(cfg, "cpu", seed=0), pool, max_batch=2, max_ctx=64, attn_chunk=64, fuse_norm=True)
+    assert fused.w.norms_folded and fused.row_ss.shape == (2 * cfg.layers + 1, 2)
+    fused.set_batch(torch.tensor([1, 2], dtype=torch.int32), torch.tensor([3, 4], dtype=torch.int32), torch.zeros((2, 4), dtype=torch.int32))
+    fused.step(max_ctx=64)
+    names = [c if isinstance(c, str) else c[0] for c in calls]
+    assert names == ["embedding"] + ["gemm", "rope_append", "attn", "gemm", "gemm", "gemm"] * 2 + ["gemm", "argmax"]
+    assert len(names) == fused.kernels_per_step
+    gemms = [c[1] for c in calls if not isinstance(c, str) and c[0] == "gemm"]
+    # consumer, producer, consumer (gated), producer per layer, then the lm_head as a consumer
+    assert ["ss_in" in g for g in gemms] == [True, False, True, False] * 2 + [True]
+    assert [bool(g.get("residual")) and "ss_out" in g for g in gemms] == [False, True, False, True] * 2 + [False]
+
+
+def test_prefill_issues_the_expected_kernel_sequence(monkeypatch):
+    """The prefill path's host side with the kernels stubbed out: per layer norm, QKV, RoPE + append, the prefill attention
+    kernel, O, norm, gate/up, down; logits only for each prompt's last token; the persistent GEMM only when asked for and only
+    above 256 tokens."""
+    from skygdr_b200 import ops
+    from skygdr_b200.models import Qwen3Config, Qwen3Decoder, Qwen3Weights
+
+    calls = []
+    _stub_kernels(monkeypatch, calls)
+    cfg = Qwen3Config.tiny(layers=2)
+    pool = ops.PagedKVPool(cfg.geometry, 64, "hnd", device="cpu")
+    eng = Qwen3Decoder(cfg, Qwen3Weights(cfg, "cpu", seed=0), pool, max_batch=2, max_ctx=512, attn_chunk=128)
+    table = torch.arange(2 * 32, dtype=torch.int32).view(2, 32)
+    seq_lens = [20, 9]
+    logits = eng.prefill(torch.randint(0, cfg.vocab, (sum(seq_lens),)), seq_lens, table)
+    assert logits.shape == (2, cfg.vocab)
+    names = [c if isinstance(c, str) else c[0] for c in calls]
+    layer = ["rmsnorm", "gemm", "rope_append", "prefill_attn", "gemm", "rmsnorm", "gemm", "gemm"]
+    assert names == ["embedding"] + layer * 2 + ["rmsnorm", "gemm"]
+    assert not any(c[1].get("persistent") for c in calls if not isinstance(c, str))
+    for persistent, n_tokens, want in ((True, 300, True), (True, 200, False), (False, 300, False)):
+        calls.clear()
+        eng.prefill_gemm_persistent = persistent
+        eng.prefill(torch.randint(0, cfg.vocab, (n_tokens,)), [n_tokens], table[:1])
+        flags = [bool(c[1].get("persistent")) for c in calls if not isinstance(c, str) and c[0] == "gemm"]
+        assert flags == [want] * 8 + [False], (persistent, n_tokens, flags)       # the lm_head over one row per prompt stays as it is
