@@ -893,3 +893,92 @@ def test_prefill_issues_the_expected_kernel_sequence(monkeypatch):
         eng.prefill(torch.randint(0, cfg.vocab, (n_tokens,)), [n_tokens], table[:1])
         flags = [bool(c[1].get("persistent")) for c in calls if not isinstance(c, str) and c[0] == "gemm"]
         assert flags == [want] * 8 + [False], (persistent, n_tokens, flags)       # the lm_head over one row per prompt stays as it is
+
+
+class _FakeHeap:
+    """Stand-in for the CUDA IPC symmetric heap: local tensors on the CPU, made-up peer addresses (rank in the high bits)."""
+
+    def __init__(self, nbytes, rank, world, device, group=None):
+        self.rank, self.world, self.off, self.names = rank, world, 0, {}
+
+    def alloc(self, name, nbytes, align=256, local=True):
+        self.off = (self.off + align - 1) // align * align
+        self.names[name] = (self.off, nbytes)
+        self.off += nbytes
+        return self.names[name][0]
+
+    def ptr(self, name, rank, byte_offset=0):
+        return (rank + 1 << 40) + self.names[name][0] + byte_offset
+
+    def all_ptrs(self, name, byte_offset=0):
+        return [self.ptr(name, r, byte_offset) for r in range(self.world)]
+
+    def local_tensor(self, name, shape, dtype):
+        return torch.zeros(shape, dtype=dtype)
+
+
+@pytest.mark.parametrize("collective", ["rs_ag", "oneshot"])
+def test_tensor_parallel_engine_issues_the_expected_kernel_sequence(monkeypatch, collective):
+    """The tensor-parallel engine's host side with heap and kernels stubbed out, for both collective forms: kernels per step,
+    which GEMMs wait for an all-gather or push a reduce-scatter / one-shot all-reduce, the (step, use) counters they are given,
+    and that the expected arrival counts match what the pushing GEMMs' tile counts produce."""
+    import skygdr_b200.parallel.tp as tp
+    from skygdr_b200 import ops
+    from skygdr_b200.models import Qwen3Config, Qwen3Weights
+
+    calls = []
+    _stub_kernels(monkeypatch, calls)
+    monkeypatch.setattr(tp, "SymmetricHeap", _FakeHeap)
+    monkeypatch.setattr(tp, "new_status", lambda dev: torch.zeros(16, dtype=torch.int32))
+    import sys
+
+    monkeypatch.setattr(sys.modules["skygdr_b200.ops.gemm"], "new_status", lambda dev: torch.zeros(16, dtype=torch.int32))
+    monkeypatch.setattr(tp.dist, "barrier", lambda group=None: None)
+
+    class Rec:
+        def __getattr__(self, name):
+            def f(*a, **k):
+                if name in ("gemm_workspace_floats", "gemm_counter_count"):      # sizing helpers of split-K, not launches
+                    return 1024
+                calls.append((name, a, k))
+                return 0
+            return f
+
+    world, rank = 2, 1
+    cfg = Qwen3Config.tiny(layers=2)
+    cfg.q_heads, cfg.kv_heads, cfg.ffn, cfg.vocab = 8, 4, 512, 600
+    w = Qwen3Weights(cfg, "cpu", seed=0, tp_rank=rank, tp_world=world)
+    pool = ops.PagedKVPool(ops.KVGeometry(cfg.layers, cfg.kv_heads // world, cfg.head_dim), 8, "hnd", device="cpu")
+    B = 4
+    eng = tp.TPDecoder(cfg, w, pool, B, 64, rank, world, attn_chunk=128, collective=collective)
+    eng._C = Rec()
+    eng.set_batch(torch.arange(B, dtype=torch.int32), torch.full((B,), 5, dtype=torch.int32), torch.zeros((B, 4), dtype=torch.int32))
+    eng.step(max_ctx=64)
+    names = [c if isinstance(c, str) else c[0] for c in calls]
+    layer = ["tp_norm", "gemm_tp", "rope_append", "attn", "gemm_tp", "tp_norm", "gemm_tp", "gemm_tp"]
+    assert names == ["embedding"] + layer * 2 + ["tp_norm", "gemm_tp", "tp_argmax", "step_increment"]
+    assert len(names) == eng.kernels_per_step
+    gemms = [c for c in calls if not isinstance(c, str) and c[0] == "gemm_tp"]
+    # gemm_tp(x, w, y, splits, gated, ws, counters, status, ag, rs, ntok)
+    ag = [bool(g[1][8]) for g in gemms]
+    rs = [bool(g[1][9]) for g in gemms]
+    assert rs == [False, True, False, True] * 2 + [False]                       # O and down push their partial tiles
+    if collective == "rs_ag":
+        assert ag == [True, False, True, False] * 2 + [True]                    # QKV, gate/up and lm_head wait for gathered rows
+        uses = [(g[1][8][3], g[1][8][4]) for g in gemms if g[1][8]]             # (uses per step, use index)
+        assert uses == [(3, 0), (2, 0), (3, 1), (2, 1), (3, 2)]
+        assert all(len(g[1][9]) == 5 for g in gemms if g[1][9])                 # world, src rank, rows per rank, dst ptrs, counter ptrs
+    else:
+        assert not any(ag)                                                       # activations are replicated: nobody waits in a GEMM
+        pushes = [g[1][9] for g in gemms if g[1][9]]
+        assert all(p[0] == world and p[1] == rank and p[2] == B and p[5] is True for p in pushes)      # slot [this rank][row], to everybody
+        assert eng.resid.shape[0] == B                                           # replicated residual stream
+    norms = [c for c in calls if not isinstance(c, str) and c[0] == "tp_norm"]
+    # tp_norm(rs_buf, rs_ctr, seq, resid, w, ag_dst, ag_ctr, rank, eps, timeout, status[, rs_world=])
+    seqs = [n[1][2] for n in norms]
+    assert seqs[0] == () and [s[1:3] for s in seqs[1:]] == [(2, 0), (2, 0), (2, 1), (2, 1)]       # (uses per step, use index) of rs0 / rs1
+    tiles_h = (cfg.hidden + 127) // 128
+    for s in seqs[1:]:
+        assert s[3] % (world * tiles_h) == 0 and s[3] >= world * tiles_h        # arrivals: every output tile of every rank's GEMM
+    if collective == "oneshot":
+        assert all(n[2].get("rs_world") == world for n in norms) and all(n[1][6] == [0] for n in norms)   # local destination, no arrival
