@@ -982,3 +982,84 @@ def test_tensor_parallel_engine_issues_the_expected_kernel_sequence(monkeypatch,
         assert s[3] % (world * tiles_h) == 0 and s[3] >= world * tiles_h        # arrivals: every output tile of every rank's GEMM
     if collective == "oneshot":
         assert all(n[2].get("rs_world") == world for n in norms) and all(n[1][6] == [0] for n in norms)   # local destination, no arrival
+
+
+def test_paged_attention_wrapper_sizes_scratch_and_passes_the_grid_order(monkeypatch):
+    """The Python face of the decode attention with the launch stubbed out: scratch sizes for the three grid orders and exactly
+    which keyword arguments reach the extension (none of the optional ones in the default configuration)."""
+    import sys
+
+    from skygdr_b200 import ops
+
+    att = sys.modules["skygdr_b200.ops.attention"]            # loaded by the import of ops above
+    monkeypatch.setattr(att, "new_status", lambda dev: torch.zeros(16, dtype=torch.int32))
+    seen = {}
+
+    class C:
+        @staticmethod
+        def paged_attn_decode(*a, **k):
+            seen["args"], seen["kw"] = a, k
+
+    pool = ops.PagedKVPool(ops.KVGeometry(layers=2, kv_heads=2), 8, "hnd", device="cpu")
+    q = torch.zeros((3, 4, 128), dtype=torch.bfloat16)
+    table, ctx = torch.zeros((3, 4), dtype=torch.int32), torch.tensor([5, 40, 64], dtype=torch.int32)
+    for order, want_kw, want_splits in ((False, {}, 5), (True, {"tail_order": 1}, 5), ("fine", {"tail_order": 2}, 8)):
+        a = ops.PagedAttention("cpu", 3, 4, 2, max_ctx=2300, chunk_tokens=512, impl="tc", tail_order=order)
+        a._C = C
+        assert a.max_splits == want_splits and a.part_o.shape == (3, 4, want_splits, 128) and a.part_m.shape == (3, 4, want_splits)
+        out = a(q, pool, 1, table, ctx, max_ctx=100)
+        assert out.shape == q.shape and seen["kw"] == want_kw
+        assert seen["args"][9] == 100 and seen["args"][10] == 512                  # max_ctx of this call, chunk size
+        assert seen["args"][-1] == (pool.data.numel() - 1 * pool.strides[1]) // 128     # rows from this layer's first page to the end
+    simt = ops.PagedAttention("cpu", 3, 4, 2, max_ctx=2300, chunk_tokens=500, impl="simt")
+    simt._C = C
+    simt(q, pool, 0, table, ctx)
+    assert seen["kw"] == {} and seen["args"][-1] == 0 and seen["args"][9] == 2300
+    with pytest.raises(AssertionError):
+        ops.PagedAttention("cpu", 3, 4, 2, max_ctx=2300, chunk_tokens=384, impl="tc", tail_order="fine")     # needs chunk % 512 == 0
+    with pytest.raises(AssertionError):
+        ops.PagedAttention("cpu", 3, 4, 2, max_ctx=2300, chunk_tokens=512, impl="simt", tail_order=True)
+
+
+def test_gemm_wrapper_argument_order_matches_the_extension(monkeypatch):
+    """ops.gemm with the launch stubbed out: which positional arguments reach the extension for the plain, split-K, folded-norm
+    and persistent forms. The binding's own signature is read from the built module, so a mismatch in count shows here."""
+    import sys
+
+    import skygdr_b200.ops  # noqa: F401  (makes sure the submodule is loaded; its name in the package is shadowed by the function)
+    from skygdr_b200._ext import load
+
+    g = sys.modules["skygdr_b200.ops.gemm"]
+    monkeypatch.setattr(g, "new_status", lambda dev: torch.zeros(16, dtype=torch.int32))
+    monkeypatch.setattr(g, "_sms", lambda dev: 148)
+    g._WS.clear()
+    sig = load().gemm.__doc__
+    names = ["x", "w", "y", "splits", "gated", "workspace", "counters", "status", "ntok", "ss_in", "eps", "residual", "ss_out", "persistent"]
+    assert all(f"{n}:" in sig for n in names) and [sig.index(f"{a}:") < sig.index(f"{b}:") for a, b in zip(names, names[1:])] == [True] * 13
+    seen = []
+
+    class C:
+        gemm_workspace_floats = staticmethod(lambda *a: 4096)
+        gemm_counter_count = staticmethod(lambda *a: 64)
+        gemm = staticmethod(lambda *a: seen.append(a))
+
+    monkeypatch.setattr(g, "load", lambda: C)
+    x, w = torch.zeros((16, 1024), dtype=torch.bfloat16), torch.zeros((512, 1024), dtype=torch.bfloat16)
+    y = g.gemm(x, w)
+    a = seen[-1]
+    assert y.shape == (16, 512) and len(a) == 13 and a[3] >= 1 and a[4] is False and a[9] is None and a[11] is False
+    g.gemm(x, w, splits=4, ntok=16)
+    a = seen[-1]
+    assert a[3] == 4 and a[5] is not None and a[6] is not None and a[8] == 16
+    ss = torch.zeros(16)
+    g.gemm(x, w, splits=1, ss_in=ss, eps=1e-5)
+    assert seen[-1][9] is ss and seen[-1][10] == 1e-5
+    g.gemm(x, torch.zeros((1024, 1024), dtype=torch.bfloat16), out=torch.zeros((16, 1024), dtype=torch.bfloat16), splits=1, residual=True, ss_out=ss)
+    assert seen[-1][11] is True and seen[-1][12] is ss
+    big = torch.zeros((700, 1024), dtype=torch.bfloat16)
+    g.gemm(big, w, persistent=True)
+    a = seen[-1]
+    assert len(a) == 14 and a[3] == 1 and a[8] == 256 and a[13] is True
+    g.gemm(big, torch.zeros((1024, 1024), dtype=torch.bfloat16), gated=True, persistent=True)
+    assert seen[-1][8] == 128 and seen[-1][4] is True
+    g._WS.clear()
