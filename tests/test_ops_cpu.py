@@ -1063,3 +1063,16 @@ def test_gemm_wrapper_argument_order_matches_the_extension(monkeypatch):
     g.gemm(big, torch.zeros((1024, 1024), dtype=torch.bfloat16), gated=True, persistent=True)
     assert seen[-1][8] == 128 and seen[-1][4] is True
     g._WS.clear()
+
+
+def test_bindings_expose_the_keywords_the_python_side_uses():
+    """Keyword names that the Python wrappers pass must exist in the built extension's signatures (read from its docstrings)."""
+    from skygdr_b200._ext import load
+
+    C = load()
+    for fn, words in {"paged_attn_decode": ["persistent_ctas:", "tail_order:", "pool_rows:"],
+                      "embedding": ["row_ss:"], "sample": ["temperature:", "seed:", "positions:"],
+                      "gemm": ["persistent: bool = False", "ss_in:", "ss_out:", "residual: bool = False"],
+                      "tp_norm": ["rs_world:"]}.items():
+        doc = getattr(C, fn).__doc__
+        assert all(w in doc for w in words), (fn, doc)
