@@ -1076,3 +1076,27 @@ def test_bindings_expose_the_keywords_the_python_side_uses():
                       "tp_norm": ["rs_world:"]}.items():
         doc = getattr(C, fn).__doc__
         assert all(w in doc for w in words), (fn, doc)
+
+
+def test_build_decode_engine_lays_out_pool_and_tables(monkeypatch):
+    """What the benchmark calls to get an engine, with the kernels stubbed out: every sequence gets its own blocks (never block
+    0), enough for its context plus the growth asked for, and the options reach the engine."""
+    from skygdr_b200.models import Qwen3Config
+    from skygdr_b200.parallel.tp import build_decode_engine
+
+    calls = []
+    _stub_kernels(monkeypatch, calls)
+    cfg = Qwen3Config.tiny(layers=2)
+    ctx = torch.tensor([40, 7, 130, 64])
+    eng, table = build_decode_engine(cfg, torch.device("cpu"), 0, 1, ctx, extra_tokens=20, seed=1, attn_chunk=512, attn_tail_order="fine")
+    need = [(int(c) + 20 + 15) // 16 for c in ctx]
+    used = [table[i, :need[i]].tolist() for i in range(4)]
+    flat = [b for row in used for b in row]
+    assert len(flat) == len(set(flat)) and 0 not in flat and max(flat) < eng.pool.num_blocks == sum(need) + 1
+    assert all(int(table[i, need[i]:].abs().sum()) == 0 for i in range(4))
+    assert eng.max_ctx == 130 + 20 + 1 and table.shape == (4, eng.max_blocks) and eng.max_batch == 4
+    assert eng.attn.kw["tail_order"] == "fine" and eng.attn.kw["impl"] == "tc"
+    assert float(eng.pool.data.float().std()) > 0.5                      # N(0, 1) cache contents, as the benchmark states
+    eng.set_batch(torch.zeros(4, dtype=torch.int32), ctx.int(), table)
+    eng.step()
+    assert len(calls) == eng.kernels_per_step
