@@ -105,3 +105,24 @@ def test_admission_waits_for_memory_and_refuses_what_can_never_fit():
     out[1] = [t for _, t in first] + out[1]
     assert set(out) == {1, 2, 3} and [len(out[k]) for k in (1, 2, 3)] == [4, 4, 2]
     assert out[2] == expected([2] * 60, 4, None)
+
+
+def test_batcher_drives_the_real_engine_class_with_stubbed_kernels(monkeypatch):
+    """The batcher against Qwen3Decoder itself (kernels replaced by recorders that return zeros): signatures, devices and
+    shapes fit, every request gets its number of tokens, and idle slots keep running on block 0."""
+    from test_ops_cpu import _stub_kernels
+
+    from skygdr_b200.models import Qwen3Config, Qwen3Decoder, Qwen3Weights
+
+    calls = []
+    _stub_kernels(monkeypatch, calls)
+    cfg = Qwen3Config.tiny(layers=2)
+    pool = ops.PagedKVPool(cfg.geometry, 32, "hnd", device="cpu")
+    eng = Qwen3Decoder(cfg, Qwen3Weights(cfg, "cpu", seed=0), pool, max_batch=3, max_ctx=128, attn_chunk=128)
+    b = ContinuousBatcher(eng, ops.BlockAllocator(32, max_seqs=3, max_ctx=128), use_graph=False)
+    for rid, (n, new) in enumerate([(20, 3), (5, 6), (33, 2), (9, 4)]):
+        b.submit(Request(rid, torch.randint(0, cfg.vocab, (n,)), new))
+    out = b.run_until_idle(max_steps=50)
+    assert {k: len(v) for k, v in out.items()} == {0: 3, 1: 6, 2: 2, 3: 4}
+    assert b.alloc.free_blocks == b.alloc.capacity and b.idle()
+    assert sum(1 for c in calls if c == "prefill_attn") == 4 * cfg.layers   # one prefill per request
