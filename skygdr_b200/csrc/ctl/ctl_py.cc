@@ -178,7 +178,26 @@ PYBIND11_MODULE(_ctl, m) {
         .def_readonly("sim_time_s", &SimResult::sim_time_s)
         .def_readonly("windows", &SimResult::windows)
         .def("flow_times_ms", &SimResult::flow_times_ms);
-    m.def("run_simulation", &run_simulation, py::call_guard<py::gil_scoped_release>());
+    // policy: None = cfg.policy by name; or a callable(flows: list[FlowSignal], link: LinkSignal) -> list of budgets in GB/s
+    // (negative = unlimited), called once per control window and link.
+    m.def("run_simulation", [](const SimConfig& cfg, const std::vector<SimFlowSpec>& specs, py::object policy) {
+        if (policy.is_none()) {
+            py::gil_scoped_release rel;
+            return run_simulation(cfg, specs);
+        }
+        py::function fn = policy.cast<py::function>();      // owns the callable for the whole call
+        // The policy objects live and die inside run_simulation, where the GIL is not held: they keep a non-owning handle and
+        // take the GIL around every call.
+        const py::handle h = fn;
+        auto make = [&cfg, h]() -> std::unique_ptr<Policy> {
+            return std::make_unique<CallbackPolicy>(cfg.pcfg, [h](const std::vector<FlowSignal>& flows, const LinkSignal& link) {
+                py::gil_scoped_acquire gil;
+                return py::reinterpret_borrow<py::function>(h)(flows, link).cast<std::vector<double>>();
+            });
+        };
+        py::gil_scoped_release rel;
+        return run_simulation(cfg, specs, make);
+    }, py::arg("cfg"), py::arg("specs"), py::arg("policy") = py::none());
 
     // ---- daemon core ----
     py::class_<DaemonConfig>(m, "DaemonConfig")

@@ -18,6 +18,8 @@
 #include <string>
 #include <vector>
 
+#include <functional>
+
 #include "credit_page.h"
 #include "protocol.hpp"
 
@@ -267,6 +269,28 @@ public:
 
 private:
     static double weight(const FlowSignal& f) { return double(std::max(0, f.priority)) + 1.0; }
+};
+
+// A policy supplied by the embedding program (the Python binding wraps a callable in it): every window it gets the flows'
+// signals and the link's and returns, per flow, a budget in GB/s (negative = unlimited). For trying a rule out against the
+// simulator before writing it in C++.
+class CallbackPolicy : public Policy {
+public:
+    using Fn = std::function<std::vector<double>(const std::vector<FlowSignal>&, const LinkSignal&)>;
+    CallbackPolicy(const PolicyConfig& c, Fn fn) : Policy(c), fn_(std::move(fn)) {}
+    const char* name() const override { return "callback"; }
+    std::vector<FlowDecision> step(const std::vector<FlowSignal>& flows, const LinkSignal& link) override {
+        const std::vector<double> budgets = fn_(flows, link);
+        std::vector<FlowDecision> out;
+        for (size_t i = 0; i < flows.size(); ++i) {
+            const double b = i < budgets.size() && std::isfinite(budgets[i]) ? budgets[i] : -1.0;    // missing or NaN: leave the flow alone
+            out.push_back({flows[i].id, b < 0 ? SKY_MODE_HIGH : SKY_MODE_CUSTOM, b < 0 ? -1.0 : b, b < 0 ? "HOLD" : "CALLBACK"});
+        }
+        return out;
+    }
+
+private:
+    Fn fn_;
 };
 
 inline std::unique_ptr<Policy> make_policy(const std::string& name, const PolicyConfig& cfg) {

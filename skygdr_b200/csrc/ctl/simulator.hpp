@@ -13,6 +13,7 @@
 #include <algorithm>
 #include <cmath>
 #include <deque>
+#include <functional>
 #include <memory>
 #include <string>
 #include <vector>
@@ -107,7 +108,9 @@ inline std::vector<double> maxmin_fair(const std::vector<double>& demand, double
     return alloc;
 }
 
-inline SimResult run_simulation(const SimConfig& cfg, const std::vector<SimFlowSpec>& specs) {
+// `custom` (optional): makes the policy instance of a link instead of make_policy(cfg.policy); one call per link.
+inline SimResult run_simulation(const SimConfig& cfg, const std::vector<SimFlowSpec>& specs,
+                                const std::function<std::unique_ptr<Policy>()>& custom = nullptr) {
     SimResult res;
     const size_t n = specs.size();
     // links: capacity, member flows, one policy instance each (as in the daemon)
@@ -118,7 +121,7 @@ inline SimResult run_simulation(const SimConfig& cfg, const std::vector<SimFlowS
     for (size_t i = 0; i < n; ++i) members[(specs[i].link >= 0 && (size_t)specs[i].link < n_links) ? (size_t)specs[i].link : 0].push_back(i);
     std::vector<std::unique_ptr<Policy>> policies;
     for (size_t l = 0; l < n_links; ++l) {
-        auto pol = make_policy(cfg.policy, cfg.pcfg);
+        auto pol = custom ? custom() : make_policy(cfg.policy, cfg.pcfg);
         if (!pol) pol = make_policy("none", cfg.pcfg);
         policies.push_back(std::move(pol));
     }
