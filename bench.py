@@ -13,11 +13,18 @@ fixed as N grows ("weak" scaling); a batch-128 cache at 2k-16k context (about 17
 one GPU next to the weights.
 
 One timed step = embedding, 36 decoder layers (RMSNorm, QKV GEMM, QK-norm + RoPE + KV append, paged
-GQA attention, O GEMM, RMSNorm, gated gate/up GEMM, down GEMM, with the tensor-parallel
-all-gather / reduce-scatter fused into those kernels), final norm, lm_head GEMM, argmax.
+GQA attention, O GEMM, RMSNorm, gated gate/up GEMM, down GEMM, with the tensor-parallel all-reduce
+fused into those kernels: partial tiles pushed to the peers from the GEMM epilogue, summed by the
+norm kernel), final norm, lm_head GEMM, argmax.
 `value` times K CUDA-graph replays of that step with CUDA events (max over ranks); `e2e` times the
 same K steps through `DecodeSession.step`, which also copies the step's token ids and positions from
 pinned host memory and reads the sampled ids back.
+
+`baseline` is the same decoder step built from library calls on the same GPUs, same weights and same
+KV cache: torch.matmul (cuBLAS) for every GEMM and torch.distributed (NCCL) for the collectives, in
+its two usual forms (all-reduce; reduce-scatter + all-gather), each captured in a CUDA graph like
+ours; the faster form is the baseline and `vs_baseline` = value / that. `check` compares one step
+of both engines from the same state (logits and sampled ids).
 """
 from __future__ import annotations
 
@@ -42,15 +49,11 @@ def parse():
     ap.add_argument("--ctx-hi", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=36, help="for smoke runs only; the benchmark uses 36")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--attn-impl", default="tc", choices=["tc", "tcp", "simt"])
-    ap.add_argument("--tp-collective", default="rs_ag", choices=["rs_ag", "oneshot"],
-                    help="tensor-parallel form: reduce-scatter + all-gather (default) or the one-shot all-reduce")
+    ap.add_argument("--attn-impl", default="tc", choices=["tc", "simt"])
+    ap.add_argument("--tp-collective", default="oneshot", choices=["oneshot", "rs_ag"],
+                    help="tensor-parallel form: one-shot all-reduce (default) or reduce-scatter + all-gather")
     ap.add_argument("--attn-chunk", type=int, default=1024)
-    ap.add_argument("--attn-order", default="seq", choices=["seq", "tail", "fine"],
-                    help="tail: every sequence's partial last chunk is scheduled after all full chunks; fine: that part is also cut into "
-                         "quarter chunks (neither has run on a GPU yet)")
-    ap.add_argument("--fuse-norm", action="store_true",
-                    help="1 GPU: RMSNorms folded into the GEMM epilogues, 6 kernels per layer instead of 8 (not yet run on a GPU)")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the library (cuBLAS + NCCL) arm and the numeric check")
     ap.add_argument("--profile-step", action="store_true", help="also print per-kernel-kind times of one eager step (tensor-parallel engine)")
     return ap.parse_args()
 
@@ -76,6 +79,7 @@ def main() -> int:
     import torch.distributed as dist
 
     from skygdr_b200.models import DecodeSession, Qwen3Config
+    from skygdr_b200.parallel.nccl_baseline import NcclTPDecoder
     from skygdr_b200.parallel.tp import build_decode_engine
     from skygdr_b200.utils.clocks import ClockSampler
 
@@ -92,11 +96,11 @@ def main() -> int:
     batch = args.batch_per_gpu * world
     g = torch.Generator().manual_seed(args.seed)
     ctx = torch.randint(args.ctx_lo, args.ctx_hi + 1, (batch,), generator=g)
-    total_steps = 2 * (args.steps + args.warmup) + 8
+    n_arms = 1 if args.no_baseline else 3
+    total_steps = (n_arms + 1) * (args.steps + args.warmup) + 16
     max_ctx = int(ctx.max()) + total_steps + 1
     eng, table = build_decode_engine(cfg, dev, rank, world, ctx, total_steps, seed=args.seed, kv_init="normal",
-                                     attn_chunk=args.attn_chunk, attn_impl=args.attn_impl, collective=args.tp_collective,
-                                     fuse_norm=args.fuse_norm, attn_tail_order={"seq": False, "tail": True, "fine": "fine"}[args.attn_order])
+                                     attn_chunk=args.attn_chunk, attn_impl=args.attn_impl, collective=args.tp_collective)
 
     ids0 = torch.randint(0, cfg.vocab, (batch,), generator=g).int()
     eng.set_batch(ids0.to(dev), ctx.int().to(dev), table.to(dev))
@@ -108,18 +112,29 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    # ---- device-timed: K graph replays ----
-    for _ in range(args.warmup):
-        eng.replay()
-    barrier()
-    with ClockSampler(local) as clocks:
+    def max_over_ranks(*vals):
+        if world == 1:
+            return vals
+        t = torch.tensor(vals, dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return tuple(float(v) for v in t)
+
+    def time_replays(engine) -> float:
+        """K graph replays of `engine`, device-timed with CUDA events between two barriers; max over ranks, in ms."""
+        for _ in range(args.warmup):
+            engine.replay()
+        barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
-            eng.replay()
+            engine.replay()
         e1.record()
         barrier()
-        dev_ms = e0.elapsed_time(e1)
+        return max_over_ranks(e0.elapsed_time(e1))[0]
+
+    with ClockSampler(local, period_s=0.01) as clocks:
+        # ---- device-timed: K graph replays ----
+        dev_ms = time_replays(eng)
         # ---- end to end through DecodeSession.step: H2D inputs, step, D2H result, every step ----
         sess.h_pos.copy_(eng.positions[:batch].cpu())
         sess.h_ids.copy_(eng.ids[:batch].cpu())
@@ -130,17 +145,58 @@ def main() -> int:
         for _ in range(args.steps):
             sess.step()
         barrier()
-        e2e_ms = (time.perf_counter() - t0) * 1e3
-    if world > 1:
-        t = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = float(t[0]), float(t[1])
+        e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)[0]
     status = eng.check_status()
+
+    # ---- the library arm on the same GPUs, weights and cache, and the numeric check against it ----
+    baseline, check = None, None
+    if not args.no_baseline:
+        forms, libs = {}, {}
+        for form in (("allreduce", "rs_ag") if world > 1 else ("allreduce",)):
+            libs[form] = NcclTPDecoder.from_engine(eng, collective=form)
+            libs[form].capture(batch, max_ctx)
+            forms[form] = time_replays(libs[form])
+        best = min(forms, key=forms.get)
+        baseline = {"impl": "torch.matmul (cuBLAS) GEMMs" + (" + torch.distributed (NCCL) collectives" if world > 1 else "") +
+                            "; attention, norms, RoPE and sampling are this package's kernels in both arms",
+                    "form": best if world > 1 else "one GPU, no collective", "ms_per_step": forms[best] / args.steps,
+                    "value": batch * args.steps / (forms[best] * 1e-3),
+                    "all_forms_ms_per_step": {k: v / args.steps for k, v in forms.items()}}
+
+        # One eager step of each engine from the same state: this rank's slice of the logits, and the sampled ids. Two correct
+        # bf16 implementations of 36 layers differ by accumulated rounding; with more than one rank the two library forms
+        # against each other give that floor.
+        def logits_of(engine, state):
+            engine.ids.copy_(state[0]); engine.positions.copy_(state[1]); engine.ctx_lens.copy_(state[2])
+            engine.step(batch, max_ctx, advance=False)
+            torch.cuda.synchronize(dev)
+            return engine.logits[:batch].float().clone(), engine.next_ids[:batch].clone()
+
+        def compare(a, b):
+            d = a - b
+            loc = torch.stack([d.pow(2).sum(), b.pow(2).sum()]).double()
+            mx = torch.stack([d.abs().max(), b.abs().max()]).double()
+            if world > 1:
+                dist.all_reduce(loc)
+                dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+            return {"max_rel_err": float(mx[0] / mx[1].clamp_min(1e-30)), "rms_rel_err": float((loc[0] / loc[1].clamp_min(1e-30)).sqrt())}
+
+        state = (eng.ids.clone(), eng.positions.clone(), eng.ctx_lens.clone())
+        ours_logits, ours_ids = logits_of(eng, state)
+        ref_logits, ref_ids = logits_of(libs["allreduce"], state)
+        check = {"against": "library arm (all-reduce form), one eager step of all 36 layers from the same state; errors relative to the largest / rms logit",
+                 **compare(ours_logits, ref_logits), "sampled_ids_equal": float((ours_ids == ref_ids).float().mean())}
+        if "rs_ag" in libs:
+            other_logits, other_ids = logits_of(libs["rs_ag"], state)
+            check["library_forms_against_each_other"] = {**compare(other_logits, ref_logits),
+                                                         "sampled_ids_equal": float((other_ids == ref_ids).float().mean())}
+        check["status_after"] = eng.check_status()
+        del libs
+
     prof = None
     if args.profile_step and hasattr(eng, "profile_step"):
         eng.profile_step(max_ctx)
         prof = eng.profile_step(max_ctx)
-        eng._advance(batch)
 
     if rank == 0:
         tok_s = batch * args.steps / (dev_ms * 1e-3)
@@ -150,11 +206,12 @@ def main() -> int:
         out = {
             "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random-init weights, N(0,1) KV, uniform context lengths)",
+            "vs_baseline": (tok_s / baseline["value"]) if baseline else None,
+            "dtype": "bf16", "data": "synthetic (random-init weights, N(0,1) KV, uniform context lengths)",
             "config": {"model": cfg.name if args.layers == 36 else f"{cfg.name}-{args.layers}L", "global_batch": batch,
                        "seq_len": f"context uniform {args.ctx_lo}-{args.ctx_hi}, 1 new token per step",
-                       "parallelism": f"tp{world}", "kv_block_tokens": 16, "sampling": "greedy", "attention": f"{args.attn_impl}, {args.attn_chunk}-token splits" + ({"seq": "", "tail": ", partial chunks last", "fine": ", partial chunks last in quarter-chunk pieces"}[args.attn_order]),
-                       "norms": "folded into the GEMM epilogues" if args.fuse_norm else "norm kernels",
+                       "parallelism": f"tp{world}" + (f" ({args.tp_collective})" if world > 1 else ""), "kv_block_tokens": 16, "sampling": "greedy",
+                       "attention": f"{args.attn_impl}, {args.attn_chunk}-token splits",
                        "l2": "inputs larger than L2: each step streams %.1f GB of weights and KV per GPU" % (step_bytes / 1e9)},
             "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": sess.h2d_bytes_per_step, "d2h_bytes_per_step": sess.d2h_bytes_per_step},
@@ -164,6 +221,9 @@ def main() -> int:
                          "hbm_frac_of_measured": step_bytes / (dev_ms / args.steps) / 1e6 / hbm},
             "kernel_status": status, "impl": "ours",
         }
+        if baseline:
+            out["baseline"] = baseline
+            out["check"] = check
         if prof:
             out["eager_step_profile_ms"] = prof
         print(json.dumps(out), flush=True)

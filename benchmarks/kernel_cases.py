@@ -65,16 +65,14 @@ def main():
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--gated", action="store_true")
     ap.add_argument("--splits", type=int, default=0)
-    ap.add_argument("--persistent", action="store_true", help="gemm: the persistent form with two accumulators in TMEM (many-token shapes)")
+    ap.add_argument("--one-tile-per-cta", action="store_true", help="gemm with more than 256 tokens: the one-tile-per-CTA kernel instead of the persistent form")
     ap.add_argument("--blocks", type=int, default=256)
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--gb", type=float, default=2.0)
     ap.add_argument("--op", default="axpy")
     ap.add_argument("--rows", type=int, default=16)
     ap.add_argument("--no-flush", action="store_true")
-    ap.add_argument("--impl", default="simt", choices=["simt", "tc", "tc1", "tc3", "tc2v3", "tc2v4", "tc2v5", "tc2v6", "tcp", "sdpa"])
-    ap.add_argument("--tail-order", action="store_true", help="attn, impl tc: partial chunks scheduled last")
-    ap.add_argument("--fine-tail", action="store_true", help="attn, impl tc: partial chunks cut into quarter chunks and scheduled last")
+    ap.add_argument("--impl", default="simt", choices=["simt", "tc", "sdpa"])
     a = ap.parse_args()
     dev = "cuda"
     hbm, tf, src = peaks()
@@ -101,7 +99,7 @@ def main():
             fn = lambda: torch.nn.functional.scaled_dot_product_attention(qs, k, v, is_causal=True, enable_gqa=True)
             status = "library"
         else:
-            attn = ops.PrefillAttention(dev, two_tiles={"tc1": False, "tc3": 2, "tc2v3": 3, "tc2v4": 4, "tc2v5": 5, "tc2v6": 6}.get(a.impl, True))   # tc1: one query tile per CTA; tc3: 64-key steps; tc2vN: variants 3-6 of the two-tile kernel
+            attn = ops.PrefillAttention(dev)
             o_ = torch.empty_like(q)
             fn = lambda: attn(q, pool, 0, table, seq_start, n, out=o_)
         ms, best = timed(fn, a.warm, a.iters, flush)
@@ -124,7 +122,7 @@ def main():
             table[b, :nb] = perm[o:o + nb]
             o += nb
         q = torch.randn((a.batch, a.q_heads, 128), dtype=torch.bfloat16, device=dev)
-        attn = ops.PagedAttention(dev, a.batch, a.q_heads, a.kv_heads, max_ctx=a.ctx, chunk_tokens=a.chunk, impl=a.impl, tail_order="fine" if a.fine_tail else a.tail_order)
+        attn = ops.PagedAttention(dev, a.batch, a.q_heads, a.kv_heads, max_ctx=a.ctx, chunk_tokens=a.chunk, impl=a.impl)
         o_ = torch.empty_like(q)
         ms, best = timed(lambda: attn(q, pool, 0, table, ctx, max_ctx=int(ctx.max()), out=o_), a.warm, a.iters, flush)
         byt = int(ctx.sum()) * a.kv_heads * 128 * 2 * 2
@@ -134,15 +132,12 @@ def main():
         x = torch.randn((a.m, a.k), dtype=torch.bfloat16, device=dev)
         w = torch.randn((a.n * (2 if a.gated else 1), a.k), dtype=torch.bfloat16, device=dev) / 64
         y = torch.empty((a.m, a.n), dtype=torch.bfloat16, device=dev)
-        ms, best = timed(lambda: ops.gemm(x, w, out=y, gated=a.gated, splits=a.splits or None, persistent=a.persistent), a.warm, a.iters, flush)
-        if a.persistent:                                                       # a new kernel: say how far it is from the library product
-            ref = (x.float() @ w.float().t())
-            if a.gated:
-                ref = torch.nn.functional.silu(ref[:, :a.n]) * ref[:, a.n:]
-            out["max_rel_err"] = float((y.float() - ref).abs().max() / ref.abs().max())
-            from skygdr_b200.ops.gemm import workspace_for
+        ms, best = timed(lambda: ops.gemm(x, w, out=y, gated=a.gated, splits=a.splits or None, persistent=False if a.one_tile_per_cta else None),
+                         a.warm, a.iters, flush)
+        from skygdr_b200.ops.gemm import workspace_for
 
-            out["status"] = ops.read_status(workspace_for(dev).status)["status_name"]
+        out["status"] = ops.read_status(workspace_for(dev).status)["status_name"]
+        out["form"] = "one tile per CTA" if (a.one_tile_per_cta or a.m <= 256) else "persistent, two accumulators in TMEM"
         byt = (w.numel() + x.numel() + y.numel()) * 2
         fl = 2.0 * a.m * w.shape[0] * a.k
         out.update(ms=ms, best_ms=best, bytes=byt, gbs=byt / ms / 1e6, frac_hbm=byt / ms / 1e6 / hbm, tflops=fl / ms / 1e9,

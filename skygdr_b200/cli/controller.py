@@ -211,9 +211,24 @@ def main(argv=None) -> int:
                 exited = restore_proc.poll() is not None
                 if stop_sent and exited:
                     break
-                if exited and deadline is None and not row:
-                    rc = 3                           # the protected flow died without a single progress row
-                    break
+                if exited and deadline is None:
+                    # The protected flow has exited and this pass did not see it finish. Its last row may have been written
+                    # just before it exited, after this pass read the file: read once more. If it still is not done, the
+                    # flow died on the way (reference: the loop ends whenever the restore process exits before RESTORE_DONE,
+                    # src/tools/pcie_case_study_controller.py:349); the background flow is not left in a LOW mode.
+                    last = fresh_row(read_last_csv_row(progress_csv), run_start)
+                    finished = bool(last) and (int(float(last.get("done", 0))) != 0 or int(float(last.get("remaining_bytes", 1))) <= 0)
+                    if not finished:
+                        for cmd in ("HIGH", "STOP"):
+                            try:
+                                response = send_control(a.cpu_control_host, a.cpu_control_port, cmd)
+                            except OSError:
+                                break
+                        w.writerow([int(time.time() * 1000), "STOP", "RESTORE_DIED_STOP", 0, g("elapsed_ms"), g("issued_bytes"), g("completed_bytes"),
+                                    remaining, "", "", "", "", "", "", f"{baseline:.6f}", f"{enter_thresh:.6f}", f"{exit_thresh:.6f}", response])
+                        fp.flush()
+                        rc = 3
+                        break
                 time.sleep(max(a.poll_ms, a.min_poll_ms) / 1000.0)
     except KeyboardInterrupt:
         try:

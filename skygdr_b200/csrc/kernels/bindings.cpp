@@ -204,7 +204,7 @@ static void kv_transfer(torch::Tensor src_pool, std::vector<uint64_t> dst_ptrs, 
 // ---- causal prefill attention over the paged pool ----
 static void prefill_attn(torch::Tensor q, torch::Tensor kv_layer, torch::Tensor out, torch::Tensor block_table, torch::Tensor seq_start,
                          int64_t block_stride, int64_t kv_stride, int64_t head_stride, int64_t tok_stride, int kv_heads, int max_len, double scale,
-                         torch::Tensor status, int64_t pool_rows, int two_tiles) {
+                         torch::Tensor status, int64_t pool_rows, c10::optional<torch::Tensor> pos0) {
     c10::cuda::CUDAGuard g(q.device());
     TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous() && out.is_contiguous() && out.sizes() == q.sizes(), "q/out: contiguous [tokens][heads][128]");
     TORCH_CHECK(block_table.dim() == 2 && seq_start.numel() == block_table.size(0) + 1, "seq_start holds n_seqs + 1 offsets");
@@ -215,8 +215,10 @@ static void prefill_attn(torch::Tensor q, torch::Tensor kv_layer, torch::Tensor 
     p.block_stride = block_stride; p.kv_stride = kv_stride; p.head_stride = head_stride; p.tok_stride = tok_stride;
     p.n_seqs = (int)block_table.size(0); p.q_heads = (int)q.size(1); p.kv_heads = kv_heads; p.max_blocks = (int)block_table.size(1);
     p.max_len = max_len; p.total_tokens = (int)q.size(0); p.scale = (float)scale;
-    TORCH_CHECK(two_tiles >= 0 && two_tiles <= 6, "variant: 0 one query tile per CTA, 1 two tiles, 2 two tiles with 64-key steps, 3-6 two tiles with exp2 on the FMA pipe and/or P in TMEM");
-    p.two_tiles = two_tiles;
+    if (pos0.has_value()) {
+        TORCH_CHECK(pos0->scalar_type() == torch::kInt32 && pos0->is_contiguous() && pos0->numel() == block_table.size(0), "pos0: int32, one entry per sequence");
+        p.pos0 = i32_ptr(*pos0);
+    }
     p.status = status_ptr(status);
     SKY_CUDA_CHECK(launch_prefill_attn_tc(p, pool_rows, cur_stream()));
 }
@@ -246,18 +248,19 @@ static void memhog(torch::Tensor a, torch::Tensor b, int op, int iters, uint64_t
 static void paged_attn_decode(torch::Tensor q, torch::Tensor kv_layer, torch::Tensor out, torch::Tensor block_table, torch::Tensor ctx_lens,
                               int64_t block_stride, int64_t kv_stride, int64_t head_stride, int kv_heads, int max_ctx, int chunk_tokens,
                               double scale, torch::Tensor part_o, torch::Tensor part_m, torch::Tensor part_l, torch::Tensor counters,
-                              torch::Tensor status, int64_t pool_rows, int persistent_ctas, int tail_order) {
+                              torch::Tensor status, int64_t pool_rows, int64_t num_blocks) {
     c10::cuda::CUDAGuard g(q.device());
+    TORCH_CHECK(block_table.dim() == 2 && (int64_t)max_ctx <= block_table.size(1) * 16, "max_ctx = ", max_ctx, " but a block-table row covers ",
+                block_table.size(1) * 16, " tokens");
+    TORCH_CHECK(num_blocks >= 0 && num_blocks <= 0x7fffffffLL, "num_blocks out of range");
     TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && out.is_contiguous(), "q/out: contiguous [batch][heads][128]");
-    TORCH_CHECK(tail_order >= 0 && tail_order <= 2, "tail_order: 0 off, 1 partial chunks last, 2 quarter-chunk pieces last");
-    TORCH_CHECK(!tail_order || (pool_rows > 0 && persistent_ctas == 0), "tail_order belongs to the one-CTA-per-item tensor-core kernel");
     PagedAttnParams p;
     memset(&p, 0, sizeof p);
     p.q = bf16_ptr(q); p.kv = bf16_ptr(kv_layer); p.out = bf16_mut(out);
     p.block_table = i32_ptr(block_table); p.ctx_lens = i32_ptr(ctx_lens);
     p.block_stride = block_stride; p.kv_stride = kv_stride; p.head_stride = head_stride;
     p.batch = (int)q.size(0); p.q_heads = (int)q.size(1); p.kv_heads = kv_heads; p.head_dim = (int)q.size(2);
-    p.block_tokens = 16; p.max_blocks = (int)block_table.size(1);
+    p.block_tokens = 16; p.max_blocks = (int)block_table.size(1); p.num_blocks = (int)num_blocks;
     p.max_ctx = max_ctx; p.chunk_tokens = chunk_tokens; p.scale = (float)scale;
     p.max_splits = (int)part_m.size(2);
     TORCH_CHECK(part_o.scalar_type() == torch::kFloat32 && part_o.numel() >= (int64_t)p.batch * p.q_heads * p.max_splits * 128, "part_o too small");
@@ -265,9 +268,7 @@ static void paged_attn_decode(torch::Tensor q, torch::Tensor kv_layer, torch::Te
     p.part_o = part_o.data_ptr<float>(); p.part_m = part_m.data_ptr<float>(); p.part_l = part_l.data_ptr<float>();
     p.counters = reinterpret_cast<unsigned int*>(counters.data_ptr());
     p.status = status_ptr(status);
-    p.tail_order = tail_order;
-    TORCH_CHECK(persistent_ctas == 0 || pool_rows > 0, "the persistent variant is the tensor-core kernel: give pool_rows");
-    if (pool_rows > 0) SKY_CUDA_CHECK(launch_paged_attn_decode_tc(p, pool_rows, cur_stream(), persistent_ctas));
+    if (pool_rows > 0) SKY_CUDA_CHECK(launch_paged_attn_decode_tc(p, pool_rows, cur_stream()));
     else SKY_CUDA_CHECK(launch_paged_attn_decode(p, cur_stream()));
 }
 
@@ -305,17 +306,9 @@ static void silu_mul(torch::Tensor gate_up, torch::Tensor out) {
     const int ffn = (int)out.size(-1), rows = (int)(out.numel() / ffn);
     SKY_CUDA_CHECK(launch_silu_mul(bf16_ptr(gate_up), bf16_mut(out), rows, ffn, cur_stream()));
 }
-static void embedding(torch::Tensor ids, torch::Tensor table, torch::Tensor out, c10::optional<torch::Tensor> row_ss) {
+static void embedding(torch::Tensor ids, torch::Tensor table, torch::Tensor out) {
     c10::cuda::CUDAGuard g(table.device());
-    float* ss = nullptr;
-    int slots = 0, pitch = 0;
-    if (row_ss.has_value()) {
-        TORCH_CHECK(row_ss->dim() == 2 && row_ss->is_contiguous() && row_ss->scalar_type() == torch::kFloat32 && row_ss->size(1) >= ids.numel(),
-                    "row_ss: fp32 [slots][>= tokens]");
-        ss = row_ss->data_ptr<float>(); slots = (int)row_ss->size(0); pitch = (int)row_ss->size(1);
-    }
-    SKY_CUDA_CHECK(launch_embedding(i32_ptr(ids), bf16_ptr(table), bf16_mut(out), (int)ids.numel(), (int)table.size(1), (int)table.size(0), cur_stream(),
-                                    ss, slots, pitch));
+    SKY_CUDA_CHECK(launch_embedding(i32_ptr(ids), bf16_ptr(table), bf16_mut(out), (int)ids.numel(), (int)table.size(1), (int)table.size(0), cur_stream()));
 }
 static void argmax(torch::Tensor logits, torch::Tensor out) {
     c10::cuda::CUDAGuard g(logits.device());
@@ -340,8 +333,7 @@ static void sample(torch::Tensor logits, torch::Tensor out, double temperature, 
 // ---- GEMM ----
 // ss_in / ss_out: fp32 vectors of at least M entries (see GemmNormFuse); residual: y is the residual stream, updated in place.
 static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, bool gated, c10::optional<torch::Tensor> workspace,
-                 c10::optional<torch::Tensor> counters, torch::Tensor status, int ntok, c10::optional<torch::Tensor> ss_in, double eps,
-                 bool residual, c10::optional<torch::Tensor> ss_out, bool persistent) {
+                 c10::optional<torch::Tensor> counters, torch::Tensor status, int ntok, bool persistent) {
     c10::cuda::CUDAGuard g(x.device());
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1, "row-major 2-D tensors");
     GemmParams p;
@@ -360,18 +352,7 @@ static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, 
         p.counters = reinterpret_cast<unsigned int*>(counters->data_ptr());
     }
     p.status = status_ptr(status);
-    if (ss_in.has_value()) {
-        TORCH_CHECK(ss_in->scalar_type() == torch::kFloat32 && ss_in->is_contiguous() && ss_in->numel() >= p.M, "ss_in: fp32, one entry per row of x");
-        p.nf.row_ss_in = ss_in->data_ptr<float>(); p.nf.eps = (float)eps;
-    }
-    if (ss_out.has_value()) {
-        TORCH_CHECK(residual && ss_out->scalar_type() == torch::kFloat32 && ss_out->is_contiguous() && ss_out->numel() >= p.M,
-                    "ss_out: fp32, one entry per row, only with residual");
-        p.nf.row_ss_out = ss_out->data_ptr<float>();
-    }
-    TORCH_CHECK(!residual || !gated, "the residual add follows a plain projection");
-    p.nf.residual = residual ? 1 : 0;
-    TORCH_CHECK(!persistent || (splits == 1 && !residual && !ss_in.has_value()), "the persistent form is the plain projection without split-K");
+    TORCH_CHECK(!persistent || splits == 1, "the persistent form is the plain projection without split-K");
     p.persistent = persistent ? 1 : 0;
     SKY_CUDA_CHECK(launch_gemm(p, cur_stream()));
 }
@@ -517,17 +498,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("paged_attn_decode", &paged_attn_decode, py::arg("q"), py::arg("kv_layer"), py::arg("out"), py::arg("block_table"), py::arg("ctx_lens"),
           py::arg("block_stride"), py::arg("kv_stride"), py::arg("head_stride"), py::arg("kv_heads"), py::arg("max_ctx"), py::arg("chunk_tokens"),
           py::arg("scale"), py::arg("part_o"), py::arg("part_m"), py::arg("part_l"), py::arg("counters"), py::arg("status"), py::arg("pool_rows"),
-          py::arg("persistent_ctas") = 0, py::arg("tail_order") = 0);
-    m.def("prefill_attn", &prefill_attn);
+          py::arg("num_blocks") = 0);
+    m.def("prefill_attn", &prefill_attn, py::arg("q"), py::arg("kv_layer"), py::arg("out"), py::arg("block_table"), py::arg("seq_start"),
+          py::arg("block_stride"), py::arg("kv_stride"), py::arg("head_stride"), py::arg("tok_stride"), py::arg("kv_heads"), py::arg("max_len"),
+          py::arg("scale"), py::arg("status"), py::arg("pool_rows"), py::arg("pos0") = py::none());
     m.def("rmsnorm", &rmsnorm);
     m.def("rope_append", &rope_append);
     m.def("silu_mul", &silu_mul);
-    m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("out"), py::arg("row_ss") = py::none());
+    m.def("embedding", &embedding);
     m.def("argmax", &argmax);
     m.def("sample", &sample, py::arg("logits"), py::arg("out"), py::arg("temperature"), py::arg("seed"), py::arg("positions") = py::none());
     m.def("gemm", &gemm, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("splits"), py::arg("gated"), py::arg("workspace"), py::arg("counters"),
-          py::arg("status"), py::arg("ntok"), py::arg("ss_in") = py::none(), py::arg("eps") = 1e-6, py::arg("residual") = false,
-          py::arg("ss_out") = py::none(), py::arg("persistent") = false);
+          py::arg("status"), py::arg("ntok"), py::arg("persistent") = false);
     m.def("gemm_tp", &gemm_tp);
     m.def("tp_norm", &tp_norm, py::arg("rs_buf"), py::arg("rs_counter"), py::arg("rs_seq"), py::arg("resid"), py::arg("w"), py::arg("ag_dst"),
           py::arg("ag_counter"), py::arg("rank"), py::arg("eps"), py::arg("timeout_ns"), py::arg("status"), py::arg("rs_world") = 0);

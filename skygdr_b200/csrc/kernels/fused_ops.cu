@@ -173,39 +173,20 @@ cudaError_t launch_silu_mul(const __nv_bfloat16* gate_up, __nv_bfloat16* out, in
 }
 
 __global__ void __launch_bounds__(128) embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
-                                                         __nv_bfloat16* __restrict__ out, int hidden, int vocab, float* row_ss,
-                                                         int ss_slots, int ss_pitch) {
-    __shared__ float red[4];
+                                                         __nv_bfloat16* __restrict__ out, int hidden, int vocab) {
     pdl_trigger();
     pdl_wait();
     const int tok = blockIdx.x;
     int id = ids[tok];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
-    float ss = 0.f;
-    for (int v = threadIdx.x; v < hidden / 8; v += 128) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(table + (long long)id * hidden + v * 8);
-        *reinterpret_cast<uint4*>(out + (long long)tok * hidden + v * 8) = raw;
-        if (row_ss) {
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); ss += f.x * f.x + f.y * f.y; }
-        }
-    }
-    if (row_ss) {
-        // slot 0 gets this row's sum of squares; the other slots of the row (filled by the GEMM epilogues of the step
-        // with atomic adds) are set to zero here, so the step needs no separate clear
-        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-        __syncthreads();
-        if (threadIdx.x == 0) row_ss[tok] = red[0] + red[1] + red[2] + red[3];
-        for (int s = 1 + threadIdx.x; s < ss_slots; s += 128) row_ss[(long long)s * ss_pitch + tok] = 0.f;
-    }
+    for (int v = threadIdx.x; v < hidden / 8; v += 128)
+        *reinterpret_cast<uint4*>(out + (long long)tok * hidden + v * 8) = *reinterpret_cast<const uint4*>(table + (long long)id * hidden + v * 8);
 }
 
 cudaError_t launch_embedding(const int* ids, const __nv_bfloat16* table, __nv_bfloat16* out, int tokens, int hidden, int vocab,
-                             cudaStream_t stream, float* row_ss, int ss_slots, int ss_pitch) {
-    if (hidden % 8 || tokens <= 0 || (row_ss && (ss_slots < 1 || ss_pitch < tokens))) return cudaErrorInvalidValue;
-    return launch_pdl(embedding_kernel, dim3(tokens), dim3(128), 0, stream, ids, table, out, hidden, vocab, row_ss, ss_slots, ss_pitch);
+                             cudaStream_t stream) {
+    if (hidden % 8 || tokens <= 0) return cudaErrorInvalidValue;
+    return launch_pdl(embedding_kernel, dim3(tokens), dim3(128), 0, stream, ids, table, out, hidden, vocab);
 }
 
 __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out, int vocab,

@@ -28,10 +28,8 @@ cudaError_t launch_rope_append(const RopeAppendParams& p, cudaStream_t stream);
 
 // out[r][c] = silu(gate_up[r][c]) * gate_up[r][F + c]
 cudaError_t launch_silu_mul(const __nv_bfloat16* gate_up, __nv_bfloat16* out, int rows, int ffn, cudaStream_t stream);
-// row_ss (optional): [ss_slots][ss_pitch] floats. Slot 0 receives the sum of squares of every gathered row, slots 1.. are zeroed
-// (they are the accumulation targets of the GEMM epilogues that fuse the residual add, see GemmNormFuse).
-cudaError_t launch_embedding(const int* ids, const __nv_bfloat16* table, __nv_bfloat16* out, int tokens, int hidden, int vocab, cudaStream_t stream,
-                             float* row_ss = nullptr, int ss_slots = 0, int ss_pitch = 0);
+// out[t] = table[ids[t]] (ids outside the table are clamped to its ends)
+cudaError_t launch_embedding(const int* ids, const __nv_bfloat16* table, __nv_bfloat16* out, int tokens, int hidden, int vocab, cudaStream_t stream);
 // Greedy sampling: out[r] = argmax_c logits[r][c] (lowest index wins ties).
 cudaError_t launch_argmax(const __nv_bfloat16* logits, int* out, int rows, int vocab, long long row_stride, cudaStream_t stream);
 // Temperature sampling: out[r] is drawn from softmax(logits[r] / temperature) by the Gumbel-max rule, with noise from a hash

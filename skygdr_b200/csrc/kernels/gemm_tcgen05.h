@@ -43,20 +43,6 @@ struct TpRsPush {
     unsigned int* counters[TP_MAX_RANKS];         // peers' arrival counters (peer-mapped)
 };
 
-// RMSNorm folded into the GEMMs around it. The norm's gain is multiplied into the columns of the consuming weight beforehand, so
-// what is left of the norm is one factor per token row, rsqrt(mean(x^2) + eps), and a matrix product is linear in it:
-//   consumer (row_ss_in): x is the un-normalised residual stream; every output row t is scaled by rsqrt(row_ss_in[t] / K + eps)
-//                         in the epilogue (before the SiLU of a gated GEMM).
-//   producer (residual):  y is the residual stream; the epilogue adds the product to it in place and, with row_ss_out, adds the
-//                         sum of squares of the new (bf16-rounded) values of its 128 columns to row_ss_out[t] (zero beforehand).
-// With both in place a decoder layer needs no norm kernel at all.
-struct GemmNormFuse {
-    const float* row_ss_in;   // nullptr: off
-    float eps;
-    int residual;
-    float* row_ss_out;        // nullptr: off
-};
-
 struct GemmParams {
     const __nv_bfloat16* x;   // [M][K], row pitch ldx
     const __nv_bfloat16* w;   // [N][K] (gated: [2N][K], gate rows then up rows), row pitch ldw
@@ -71,9 +57,8 @@ struct GemmParams {
     LaunchStatus* status;
     TpAgWait ag;
     TpRsPush rs;
-    GemmNormFuse nf;
     int persistent;           // 1: one CTA per SM walks the output tiles with two accumulators in TMEM (many-token shapes; needs
-                              // splits == 1, ntok 256 or 128, none of ag / rs / nf)
+                              // splits == 1, ntok 256 or 128, neither ag nor rs)
 };
 
 int gemm_pick_ntok(int M, bool gated);

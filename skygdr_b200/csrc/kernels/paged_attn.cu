@@ -66,7 +66,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ts = lane >> 3, dl = lane & 7;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int ctx = p.ctx_lens[b];
+    // Lengths and block ids are device data that this kernel did not produce: a length beyond what the grid and the block
+    // table cover is cut to that bound and reported, so that every split the combine counts on exists and no table entry
+    // past the row is read.
+    const int ctx_raw = p.ctx_lens[b];
+    const int ctx = min(ctx_raw, min(p.max_ctx, p.max_blocks * T));
+    if (ctx_raw > ctx && split == 0 && kvh == 0 && threadIdx.x == 0) set_status(p.status, SKY_STATUS_BAD_INDEX, 0x40000000u | (unsigned)b);
     const int tok0 = split * p.chunk_tokens;
     if (tok0 >= ctx) return;  // nothing for this CTA (uniform over the block)
     const int tok1 = min(ctx, tok0 + p.chunk_tokens);
@@ -103,7 +108,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
     const int my_n = my_first < page1 ? (page1 - my_first + ATT_WARPS - 1) / ATT_WARPS : 0;
     auto issue = [&](int j) {  // lane 0 only: fetch this warp's j-th page into slot j % STAGES
         const int pg = my_first + j * ATT_WARPS;
-        const int blk = __ldg(table + pg);
+        int blk = __ldg(table + pg);                    // pg < page1 <= max_blocks by the clamp above
+        if (p.num_blocks > 0 && (unsigned)blk >= (unsigned)p.num_blocks) {
+            // a block id outside the pool: report it and read block 0 instead, so that nothing outside the pool is touched
+            set_status(p.status, SKY_STATUS_BAD_INDEX, ((unsigned)b << 16) | ((unsigned)pg & 0xffffu));
+            blk = 0;
+        }
         const __nv_bfloat16* kp = p.kv + (long long)blk * p.block_stride + (long long)kvh * p.head_stride;
         unsigned char* slot = ring + (j % STAGES) * SLOT_BYTES;
         mbar_expect_tx(bar + (j % STAGES), SLOT_BYTES);
@@ -273,14 +283,29 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_attn_decode_kernel(const
     }
 }
 
+// Per-device set-up of one instantiation (its dynamic shared memory limit); also loads the kernel's module on that device.
+template <int G>
+static cudaError_t prepare_g() {
+    constexpr int T = 16, STAGES = 3;
+    constexpr int smem_bytes = ATT_WARPS * STAGES * 2 * T * ATT_D * 2;
+    static_assert(smem_bytes >= (int)((2 * ATT_WARPS * G + ATT_WARPS * G * ATT_D) * sizeof(float)), "merge area must fit in the ring");
+    static unsigned long long attr_mask = 0;
+    return set_max_dynamic_smem_once(reinterpret_cast<const void*>(paged_attn_decode_kernel<G, T, STAGES>), smem_bytes, &attr_mask);
+}
+
+cudaError_t prepare_paged_attn_decode() {
+    if (cudaError_t e = prepare_g<1>(); e != cudaSuccess) return e;
+    if (cudaError_t e = prepare_g<2>(); e != cudaSuccess) return e;
+    if (cudaError_t e = prepare_g<4>(); e != cudaSuccess) return e;
+    return prepare_g<8>();
+}
+
 template <int G>
 static cudaError_t launch_g(const PagedAttnParams& p, cudaStream_t stream) {
     constexpr int T = 16, STAGES = 3;
     constexpr int smem_bytes = ATT_WARPS * STAGES * 2 * T * ATT_D * 2;
-    static_assert(smem_bytes >= (int)((2 * ATT_WARPS * G + ATT_WARPS * G * ATT_D) * sizeof(float)), "merge area must fit in the ring");
     auto kern = paged_attn_decode_kernel<G, T, STAGES>;
-    static unsigned long long attr_mask = 0;
-    if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), smem_bytes, &attr_mask); e != cudaSuccess) return e;
+    if (cudaError_t e = prepare_g<G>(); e != cudaSuccess) return e;
     dim3 grid((p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens, p.kv_heads, p.batch);
     return launch_pdl(kern, grid, dim3(ATT_WARPS * 32), (size_t)smem_bytes, stream, p);
 }
@@ -289,6 +314,7 @@ cudaError_t launch_paged_attn_decode(const PagedAttnParams& p, cudaStream_t stre
     if (p.head_dim != ATT_D || p.block_tokens != 16 || p.kv_heads < 1 || p.q_heads % p.kv_heads) return cudaErrorInvalidValue;
     if (p.chunk_tokens % (16 * ATT_WARPS) != 0 || p.chunk_tokens <= 0) return cudaErrorInvalidValue;
     if ((p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens > p.max_splits) return cudaErrorInvalidValue;
+    if (p.max_blocks <= 0 || (long long)p.max_ctx > (long long)p.max_blocks * 16) return cudaErrorInvalidValue;   // the table row must cover max_ctx
     switch (p.q_heads / p.kv_heads) {
         case 1: return launch_g<1>(p, stream);
         case 2: return launch_g<2>(p, stream);

@@ -16,6 +16,7 @@ struct PagedAttnParams {
     long long kv_stride;          // elements from a block's K page to its V page
     long long head_stride;        // elements between kv heads inside a page (= 16*128)
     int batch, q_heads, kv_heads, head_dim, block_tokens, max_blocks;
+    int num_blocks;               // blocks in the pool from `kv` on (0 = unknown: block ids are not checked by the CUDA-core kernel)
     int max_ctx;                  // upper bound of ctx_lens (sizes the grid)
     int chunk_tokens;             // tokens per CTA (multiple of 64)
     int max_splits;               // row pitch of the scratch arrays
@@ -26,14 +27,13 @@ struct PagedAttnParams {
     float* part_l;                // [batch][q_heads][max_splits]
     unsigned int* counters;       // [batch][kv_heads], zero before the first launch; the kernel re-zeroes them
     LaunchStatus* status;
-    int tail_order;               // tensor-core kernel: 1 = every sequence's last (partial) chunk is scheduled after all full chunks;
-                                  // 2 = that last part is cut into quarter chunks, scheduled last (needs chunk_tokens % 512 == 0 and
-                                  // max_splits >= max_ctx / chunk_tokens + 4)
 };
 
 cudaError_t launch_paged_attn_decode(const PagedAttnParams& p, cudaStream_t stream);
+// Per-device set-up that the launcher otherwise does on its first call for each query-group size (1, 2, 4, 8): loads the
+// kernels on the current device and raises their shared-memory limits. For callers that want it done at start-up.
+cudaError_t prepare_paged_attn_decode();
 // Tensor-core version (paged_attn_tc.cu). pool_rows: 128-element rows from p.kv to the end of the pool allocation;
-// chunk_tokens must be a multiple of 128. persistent_ctas > 0 selects the persistent variant with that many CTAs (two per
-// SM is the intended number; batch <= 256 and chunk_tokens <= 1024 there).
-cudaError_t launch_paged_attn_decode_tc(const PagedAttnParams& p, long long pool_rows, cudaStream_t stream, int persistent_ctas = 0);
+// chunk_tokens must be a multiple of 128.
+cudaError_t launch_paged_attn_decode_tc(const PagedAttnParams& p, long long pool_rows, cudaStream_t stream);
 }  // namespace sky

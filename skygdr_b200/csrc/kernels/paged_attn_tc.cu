@@ -63,11 +63,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tc_kernel(const __gr
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Default order: splits fastest, then KV heads, then sequences. tail_order: KV heads fastest, then sequences, then a slot
-    // index z: slot z < n_splits - 1 is full chunk z, the last slot of the grid is the sequence's last chunk (the partial one,
-    // half a chunk on average), the slots between are empty. The CTAs that run last, alone on their SMs, are then the short ones.
-    const int kvh = p.tail_order ? blockIdx.x : blockIdx.y, b = p.tail_order ? blockIdx.y : blockIdx.z;
-    int split = blockIdx.x;
+    // grid order: splits fastest, then KV heads, then sequences
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     // Everything up to pdl_wait() touches only this CTA's shared memory, so it may overlap the previous kernel's tail.
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_UNITS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -78,32 +75,14 @@ __global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tc_kernel(const __gr
     }
     for (int i = threadIdx.x; i < 3 * QP_BYTES / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_sm)[i] = make_uint4(0, 0, 0, 0);
     pdl_wait();
-    const int ctx = p.ctx_lens[b];
-    int n_splits = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
-    int tok0, tok1;
-    if (p.tail_order == 2) {
-        // Fine tail: full chunks first, then what is left of every sequence (less than a chunk) in pieces of a quarter chunk,
-        // which occupy the last four slots of the grid. The CTAs that finish the launch alone on their SMs then hold at most a
-        // quarter chunk, so the idle tail shrinks accordingly; a sequence has up to three partials more.
-        const int small = p.chunk_tokens >> 2;                          // a multiple of 128: the launcher checks chunk % 512
-        const int n_full = ctx / p.chunk_tokens;
-        const int rem = ctx - n_full * p.chunk_tokens;
-        const int n_small = (rem + small - 1) / small;
-        n_splits = n_full + n_small;
-        const int z = blockIdx.z, j = z - ((int)gridDim.z - 4);
-        if (j < 0 && z < n_full) { split = z; tok0 = z * p.chunk_tokens; tok1 = tok0 + p.chunk_tokens; }
-        else if (j >= 0 && j < n_small) { split = n_full + j; tok0 = n_full * p.chunk_tokens + j * small; tok1 = min(ctx, tok0 + small); }
-        else return;
-    } else {
-        if (p.tail_order) {
-            const int z = blockIdx.z;
-            if (z < n_splits - 1) split = z;
-            else if (z == (int)gridDim.z - 1) split = n_splits - 1;
-            else return;
-        }
-        tok0 = split * p.chunk_tokens;
-        tok1 = min(ctx, tok0 + p.chunk_tokens);
-    }
+    // a length beyond what the grid and the table row cover is cut to that bound and reported (see paged_attn.cu)
+    const int ctx_raw = p.ctx_lens[b];
+    const int ctx = min(ctx_raw, min(p.max_ctx, p.max_blocks * 16));
+    if (ctx_raw > ctx && split == 0 && kvh == 0 && threadIdx.x == 0)
+        set_status(p.status, SKY_STATUS_BAD_INDEX, 0x40000000u | (unsigned)b);
+    const int n_splits = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
+    const int tok0 = split * p.chunk_tokens;
+    const int tok1 = min(ctx, tok0 + p.chunk_tokens);
     if (tok0 >= ctx || ctx <= 0) return;
     const int n_tiles = (tok1 - tok0 + TILE_TOK - 1) / TILE_TOK;
     const int* table = p.block_table + (long long)b * p.max_blocks;
@@ -323,361 +302,27 @@ __global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tc_kernel(const __gr
     if (warp == 5) tmem_dealloc(tmem_base, 64);
 }
 
-// ---------------------------------------------------------------------------------------------------------------
-// Persistent variant. The grid is two CTAs per SM; CTA c works through the items c, c + grid, c + 2 grid, ... where an
-// item is one (sequence, split, KV head). Barrier setup, the TMEM allocation and the tensor-map prefetch happen once per
-// CTA, the K/V ring keeps streaming across item boundaries (the producer runs ahead into the next item while the
-// epilogue of this one is written), and items can be small (512 tokens) so that the last items of a launch are short:
-// at batch 16 the one-CTA-per-item kernel above leaves about 15 % of the SM time idle in its tail.
-// Every role (producer warp, MMA thread, softmax warps) walks the same item sequence on its own and tracks barrier
-// phases with counters that run across items: `u` counts ring units, `gt` counts tiles.
-constexpr int TCP_MAX_BATCH = 256;
-
-struct TcItem {
-    int b, kvh, split, n_splits, tok0, tok1, n_tiles;
-};
-
-// s_prefix[b] = number of (sequence, split) pairs of sequences 0..b-1; s_ctx[b] = context length of sequence b.
-__device__ __forceinline__ TcItem tcp_item(long long idx, const int* s_prefix, const int* s_ctx, int batch, int kv_heads, int chunk) {
-    TcItem it;
-    const int pair = (int)(idx / kv_heads);
-    it.kvh = (int)(idx - (long long)pair * kv_heads);
-    int lo = 0, hi = batch;                            // largest b with s_prefix[b] <= pair
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (s_prefix[mid] <= pair) lo = mid; else hi = mid;
-    }
-    it.b = lo;
-    it.split = pair - s_prefix[lo];
-    const int ctx = s_ctx[lo];
-    it.n_splits = (ctx + chunk - 1) / chunk;
-    it.tok0 = it.split * chunk;
-    it.tok1 = min(ctx, it.tok0 + chunk);
-    it.n_tiles = (it.tok1 - it.tok0 + TILE_TOK - 1) / TILE_TOK;
-    return it;
-}
-
-template <int G>
-__global__ void __launch_bounds__(TC_THREADS, 2) paged_attn_tcp_kernel(const __grid_constant__ CUtensorMap tmap, const PagedAttnParams p) {
-    constexpr int GL = G <= 4 ? 4 : 8;
-    extern __shared__ unsigned char smem_raw[];
-    __shared__ uint64_t full_bar[TC_UNITS], empty_bar[TC_UNITS], s_ready[2], p_ready[2], o_done[2], q_ready;
-    __shared__ uint32_t tmem_slot;
-    __shared__ float xch[2][4][8];
-    __shared__ float lsum[4][8];
-    __shared__ int s_last;
-    __shared__ int s_prefix[TCP_MAX_BATCH + 1], s_ctx[TCP_MAX_BATCH];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* q_sm = smem + TC_UNITS * KV_TILE_BYTES;
-    unsigned char* p_sm = q_sm + QP_BYTES;
-
-    pdl_trigger();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_UNITS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(&s_ready[0], 1); mbar_init(&s_ready[1], 1);
-        mbar_init(&p_ready[0], 128); mbar_init(&p_ready[1], 128);
-        mbar_init(&o_done[0], 1); mbar_init(&o_done[1], 1);
-        mbar_init(&q_ready, 128);
-        fence_barrier_init();
-    }
-    for (int i = threadIdx.x; i < 3 * QP_BYTES / 16; i += TC_THREADS) reinterpret_cast<uint4*>(q_sm)[i] = make_uint4(0, 0, 0, 0);
-    if (warp == 5) { tmem_alloc(&tmem_slot, 64); tmem_relinquish(); }
-    pdl_wait();
-    for (int b = threadIdx.x; b < p.batch; b += TC_THREADS) s_ctx[b] = p.ctx_lens[b];
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int acc = 0;
-        for (int b = 0; b < p.batch; ++b) { s_prefix[b] = acc; acc += (s_ctx[b] + p.chunk_tokens - 1) / p.chunk_tokens; }
-        s_prefix[p.batch] = acc;
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const long long n_items = (long long)s_prefix[p.batch] * p.kv_heads;
-    const uint32_t tmem_base = tmem_slot;
-    const uint32_t tm_s[2] = {tmem_base, tmem_base + 16};
-    const uint32_t tm_o = tmem_base + 32;
-
-    if (warp == 4) {
-        // ---------------- TMA producer: one stream of units across all of this CTA's items ----------------
-        if (lane == 0) tma_prefetch_desc(&tmap);
-        const int pg = lane >> 1, half = lane & 1;
-        long long u = 0;                                      // ring units issued so far
-        bool good = true;
-        for (long long idx = blockIdx.x; idx < n_items && good; idx += gridDim.x) {
-            const TcItem it = tcp_item(idx, s_prefix, s_ctx, p.batch, p.kv_heads, p.chunk_tokens);
-            const int* table = p.block_table + (long long)it.b * p.max_blocks;
-            const long long head_rows = (long long)it.kvh * (p.head_stride >> 7);
-            // this item's slice of the block table: lane l holds entries l and 32 + l (chunk_tokens <= 1024)
-            const int e_base = it.tok0 >> 4;
-            const int ea = e_base + lane, eb = e_base + 32 + lane;
-            const int blk_a = (lane < it.n_tiles * 8 && ea < p.max_blocks) ? __ldg(table + ea) : 0;
-            const int blk_b = (32 + lane < it.n_tiles * 8 && eb < p.max_blocks) ? __ldg(table + eb) : 0;
-            for (int lu = 0; lu < 2 * it.n_tiles; ++lu, ++u) {
-                const int s = (int)(u % TC_UNITS);
-                if (u >= TC_UNITS && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], (uint32_t)((u / TC_UNITS) - 1) & 1))) {
-                    if (lane == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 31);
-                    good = false;
-                    break;
-                }
-                unsigned char* st = smem + s * KV_TILE_BYTES;
-                if (lane == 0) mbar_expect_tx(&full_bar[s], KV_TILE_BYTES);
-                const int e = (lu >> 1) * 8 + pg;             // entry of this lane's page within the item (lanes >= 16 idle)
-                const int va = __shfl_sync(0xffffffffu, blk_a, e & 31), vb = __shfl_sync(0xffffffffu, blk_b, e & 31);
-                const int blk = e < 32 ? va : vb;
-                __syncwarp();
-                if (lane < 16) {
-                    const long long row = ((long long)blk * p.block_stride >> 7) + head_rows + ((lu & 1) ? (p.kv_stride >> 7) : 0);
-                    tma_load_2d(st + half * HALF_BYTES + pg * 2048, &tmap, half * 64, (int)row, &full_bar[s]);
-                }
-            }
-        }
-    } else if (warp == 5) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 16);
-            constexpr uint32_t idesc_o = umma_idesc_bf16(128, 16) | (1u << 15);
-            const uint32_t q_addr = smem_u32(q_sm), p_addr = smem_u32(p_sm);
-            long long gt0 = 0;                                // tiles of earlier items
-            long long k_item = 0;
-            bool good = true;
-            for (long long idx = blockIdx.x; idx < n_items && good; idx += gridDim.x, ++k_item) {
-                const TcItem it = tcp_item(idx, s_prefix, s_ctx, p.batch, p.kv_heads, p.chunk_tokens);
-                if (!mbar_wait(&q_ready, (uint32_t)k_item & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 38); break; }
-                tc_fence_after();
-                auto issue_s = [&](int i) -> bool {
-                    const long long gt = gt0 + i, u = 2 * gt;
-                    const int s = (int)(u % TC_UNITS);
-                    if (!mbar_wait(&full_bar[s], (uint32_t)(u / TC_UNITS) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 32); return false; }
-                    tc_fence_after();
-                    const uint32_t k_addr = smem_u32(smem + s * KV_TILE_BYTES);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint64_t a = umma_desc_k_sw128(k_addr + (j >> 2) * HALF_BYTES + (j & 3) * 32);
-                        const uint64_t bq = umma_desc_k_sw128(q_addr + (j >> 2) * 2048 + (j & 3) * 32);
-                        tc_mma_f16(tm_s[gt & 1], a, bq, idesc_s, j ? 1u : 0u);
-                    }
-                    tc_commit(&empty_bar[s]);
-                    tc_commit(&s_ready[gt & 1]);
-                    return true;
-                };
-                good = issue_s(0);
-                for (int i = 0; i < it.n_tiles && good; ++i) {
-                    if (i + 1 < it.n_tiles) good = issue_s(i + 1);
-                    if (!good) break;
-                    const long long gt = gt0 + i, u = 2 * gt + 1;
-                    const int s = (int)(u % TC_UNITS);
-                    if (!mbar_wait(&p_ready[gt & 1], (uint32_t)(gt >> 1) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 33); good = false; break; }
-                    if (!mbar_wait(&full_bar[s], (uint32_t)(u / TC_UNITS) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 37); good = false; break; }
-                    tc_fence_after();
-                    const uint32_t v_addr = smem_u32(smem + s * KV_TILE_BYTES);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint64_t a = umma_desc_mn_sw128(v_addr + j * 2048, HALF_BYTES, 1024);
-                        const uint64_t bp = umma_desc_k_sw128(p_addr + (int)(gt & 1) * QP_BYTES + (j >> 2) * 2048 + (j & 3) * 32);
-                        tc_mma_f16(tm_o, a, bp, idesc_o, (i | j) ? 1u : 0u);
-                    }
-                    tc_commit(&empty_bar[s]);
-                    tc_commit(&o_done[gt & 1]);
-                }
-                gt0 += it.n_tiles;
-            }
-        }
-    } else {
-        // ---------------- softmax warps, epilogue and the next item's Q ----------------
-        const int t = threadIdx.x;
-        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-        const float qs = p.scale * 1.4426950408889634f;
-        long long gt0 = 0;
-        bool ok = true;
-        for (long long idx = blockIdx.x; idx < n_items && ok; idx += gridDim.x) {
-            const TcItem it = tcp_item(idx, s_prefix, s_ctx, p.batch, p.kv_heads, p.chunk_tokens);
-            // Q^T of this item: every score MMA of the previous item has completed (its scores were consumed above)
-            for (int i = t; i < G * 16; i += 128) {
-                const int g = i >> 4, c = i & 15;
-                const uint4 v = *reinterpret_cast<const uint4*>(p.q + ((long long)it.b * p.q_heads + it.kvh * G + g) * 128 + c * 8);
-                *reinterpret_cast<uint4*>(q_sm + (c >> 3) * 2048 + sw128_off(g, (c & 7) * 8)) = v;
-            }
-            fence_proxy_async();
-            tc_fence_before();
-            mbar_arrive(&q_ready);
-            float m_ref[GL], l_part[GL];
-#pragma unroll
-            for (int g = 0; g < GL; ++g) { m_ref[g] = -INFINITY; l_part[g] = 0.f; }
-            for (int i = 0; i < it.n_tiles; ++i) {
-                const long long gt = gt0 + i;
-                const int par = (int)(gt & 1);
-                if (!mbar_wait(&s_ready[par], (uint32_t)(gt >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 34); ok = false; break; }
-                tc_fence_after();
-                uint32_t raw[GL];
-                if (GL == 4) tmem_ld_x4(tm_s[par] + lane_off, raw); else tmem_ld_x8(tm_s[par] + lane_off, raw);
-                tc_wait_ld();
-                const int tok = it.tok0 + i * TILE_TOK + t;
-                const bool valid = tok < it.tok1;
-                float sc[GL], tmax[GL];
-#pragma unroll
-                for (int g = 0; g < GL; ++g) {
-                    sc[g] = (valid && g < G) ? __uint_as_float(raw[g]) * qs : -INFINITY;
-                    tmax[g] = sc[g];
-                }
-#pragma unroll
-                for (int g = 0; g < G; ++g)
-                    for (int o = 16; o; o >>= 1) tmax[g] = fmaxf(tmax[g], __shfl_xor_sync(0xffffffffu, tmax[g], o));
-                if (lane == 0)
-#pragma unroll
-                    for (int g = 0; g < G; ++g) xch[par][warp][g] = tmax[g];
-                softmax_bar();
-                float alpha[GL];
-                bool rescale = false;
-#pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    const float tm = fmaxf(fmaxf(xch[par][0][g], xch[par][1][g]), fmaxf(xch[par][2][g], xch[par][3][g]));
-                    alpha[g] = 1.0f;
-                    if (tm > m_ref[g] + RESCALE_THRESHOLD || m_ref[g] == -INFINITY) {
-                        alpha[g] = m_ref[g] == -INFINITY ? 0.f : exp2f(m_ref[g] - tm);
-                        m_ref[g] = tm;
-                        rescale = true;
-                    }
-                }
-                float pr[GL];
-#pragma unroll
-                for (int g = 0; g < GL; ++g) {
-                    pr[g] = (g < G && valid) ? exp2f(sc[g] - m_ref[g]) : 0.f;
-                    if (g < G) l_part[g] = l_part[g] * alpha[g] + pr[g];
-                }
-                // P^T buffer `par` was last read by the P.V of tile gt-2 (possibly of the previous item); a rescale of the
-                // accumulator waits for tile gt-1 of this item, which covers gt-2 as the MMAs complete in order.
-                if (rescale && i > 0) {
-                    if (!mbar_wait(&o_done[(gt - 1) & 1], (uint32_t)((gt - 1) >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 35); ok = false; break; }
-                } else if (gt > 1) {
-                    if (!mbar_wait(&o_done[par], (uint32_t)((gt - 2) >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 35); ok = false; break; }
-                }
-                if (rescale && i > 0) {
-                    tc_fence_after();
-                    uint32_t o[GL];
-                    if (GL == 4) tmem_ld_x4(tm_o + lane_off, o); else tmem_ld_x8(tm_o + lane_off, o);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int g = 0; g < GL; ++g) o[g] = __float_as_uint(__uint_as_float(o[g]) * (g < G ? alpha[g] : 1.0f));
-                    if (GL == 4) tmem_st_x4(tm_o + lane_off, o); else tmem_st_x8(tm_o + lane_off, o);
-                    tc_wait_st();
-                }
-#pragma unroll
-                for (int g = 0; g < G; ++g)
-                    *reinterpret_cast<__nv_bfloat16*>(p_sm + par * QP_BYTES + (t >> 6) * 2048 + sw128_off(g, t & 63)) = __float2bfloat16(pr[g]);
-                fence_proxy_async();
-                tc_fence_before();
-                mbar_arrive(&p_ready[par]);
-            }
-            if (!ok) break;
-            const long long gl = gt0 + it.n_tiles - 1;       // the item's last P.V
-            if (!mbar_wait(&o_done[gl & 1], (uint32_t)(gl >> 1) & 1)) { if (t == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 36); ok = false; break; }
-            tc_fence_after();
-            gt0 += it.n_tiles;
-
-            // ---- epilogue of the item: thread d owns dimension d ----
-            float og[G], lg[G];
-            uint32_t o[GL];
-            if (GL == 4) tmem_ld_x4(tm_o + lane_off, o); else tmem_ld_x8(tm_o + lane_off, o);
-            tc_wait_ld();
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                og[g] = __uint_as_float(o[g]);
-                float l = l_part[g];
-                for (int of = 16; of; of >>= 1) l += __shfl_xor_sync(0xffffffffu, l, of);
-                if (lane == 0) lsum[warp][g] = l;
-            }
-            softmax_bar();
-#pragma unroll
-            for (int g = 0; g < G; ++g) lg[g] = lsum[0][g] + lsum[1][g] + lsum[2][g] + lsum[3][g];
-            const int d = t;
-            if (it.n_splits == 1) {
-#pragma unroll
-                for (int g = 0; g < G; ++g)
-                    p.out[((long long)it.b * p.q_heads + it.kvh * G + g) * 128 + d] = __float2bfloat16(lg[g] > 0.f ? og[g] / lg[g] : 0.f);
-                softmax_bar();                                 // lsum is rewritten by the next item
-            } else {
-                const long long row0 = ((long long)it.b * p.q_heads + it.kvh * G) * p.max_splits;
-#pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    const long long row = row0 + (long long)g * p.max_splits + it.split;
-                    p.part_o[row * 128 + d] = og[g];
-                    if (d == 0) { p.part_m[row] = m_ref[g]; p.part_l[row] = lg[g]; }
-                }
-                __threadfence();
-                softmax_bar();
-                if (t == 0) {
-                    unsigned* ctr = p.counters + it.b * p.kv_heads + it.kvh;
-                    const unsigned prev = atomicAdd(ctr, 1u);
-                    s_last = (prev == (unsigned)it.n_splits - 1);
-                    if (s_last) *ctr = 0;
-                }
-                softmax_bar();
-                const bool last = s_last != 0;
-                if (last) {
-                    __threadfence();
-#pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        const long long row = row0 + (long long)g * p.max_splits;
-                        p.out[((long long)it.b * p.q_heads + it.kvh * G + g) * 128 + d] =
-                            __float2bfloat16(combine_splits(p.part_m + row, p.part_l + row, p.part_o + row * 128 + d, 128, it.n_splits));
-                    }
-                }
-                softmax_bar();                                 // s_last and lsum are rewritten by the next item
-            }
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem_base, 64);
-}
-
-template <int G>
-cudaError_t launch_tcp_g(const PagedAttnParams& p, const CUtensorMap& tm, int ctas, cudaStream_t stream) {
-    auto kern = paged_attn_tcp_kernel<G>;
-    static unsigned long long attr_mask = 0;
-    if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), TC_SMEM, &attr_mask); e != cudaSuccess) return e;
-    return launch_pdl(kern, dim3(ctas), dim3(TC_THREADS), (size_t)TC_SMEM, stream, tm, p);
-}
-
 template <int G>
 cudaError_t launch_tc_g(const PagedAttnParams& p, const CUtensorMap& tm, cudaStream_t stream) {
     auto kern = paged_attn_tc_kernel<G>;
     static unsigned long long attr_mask = 0;
     if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), TC_SMEM, &attr_mask); e != cudaSuccess) return e;
-    // fine tail (tail_order 2): one slot per possible full chunk, then four for the quarter-chunk pieces
-    const int slots = p.tail_order == 2 ? p.max_ctx / p.chunk_tokens + 4 : (p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens;
-    if (p.tail_order && (p.batch > 65535 || slots > 65535)) return cudaErrorInvalidValue;
-    if (p.tail_order == 2 && (p.chunk_tokens % 512 != 0 || slots > p.max_splits)) return cudaErrorInvalidValue;
-    const dim3 grid = p.tail_order ? dim3(p.kv_heads, p.batch, slots) : dim3(slots, p.kv_heads, p.batch);
+    const dim3 grid((p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens, p.kv_heads, p.batch);
     return launch_pdl(kern, grid, dim3(TC_THREADS), (size_t)TC_SMEM, stream, tm, p);
 }
 
 }  // namespace
 
 // `pool_rows`: number of 128-element rows from p.kv (the layer's first page) to the end of the pool allocation.
-cudaError_t launch_paged_attn_decode_tc(const PagedAttnParams& p, long long pool_rows, cudaStream_t stream, int persistent_ctas) {
+cudaError_t launch_paged_attn_decode_tc(const PagedAttnParams& p, long long pool_rows, cudaStream_t stream) {
     if (p.head_dim != 128 || p.block_tokens != 16 || p.kv_heads < 1 || p.q_heads % p.kv_heads) return cudaErrorInvalidValue;
     if (p.chunk_tokens % TILE_TOK != 0 || p.chunk_tokens <= 0) return cudaErrorInvalidValue;
     if ((p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens > p.max_splits) return cudaErrorInvalidValue;
+    if (p.max_blocks <= 0 || (long long)p.max_ctx > (long long)p.max_blocks * 16) return cudaErrorInvalidValue;   // the table row must cover max_ctx
     if ((p.block_stride | p.kv_stride | p.head_stride) & 127) return cudaErrorInvalidValue;   // rows of 128 elements
     if (pool_rows <= 0 || pool_rows > 0x7fffffffLL) return cudaErrorInvalidValue;
     CUtensorMap tm;
     if (!make_tmap_bf16_2d(&tm, p.kv, pool_rows, 128, 128, 16)) return cudaErrorInvalidValue;
-    if (persistent_ctas > 0) {
-        if (p.batch > TCP_MAX_BATCH || p.chunk_tokens > 1024) return cudaErrorInvalidValue;
-        const long long most = (long long)p.batch * p.kv_heads * ((p.max_ctx + p.chunk_tokens - 1) / p.chunk_tokens);
-        const int ctas = (int)std::min<long long>(persistent_ctas, most);
-        switch (p.q_heads / p.kv_heads) {
-            case 1: return launch_tcp_g<1>(p, tm, ctas, stream);
-            case 2: return launch_tcp_g<2>(p, tm, ctas, stream);
-            case 4: return launch_tcp_g<4>(p, tm, ctas, stream);
-            case 8: return launch_tcp_g<8>(p, tm, ctas, stream);
-            default: return cudaErrorInvalidValue;
-        }
-    }
     switch (p.q_heads / p.kv_heads) {
         case 1: return launch_tc_g<1>(p, tm, stream);
         case 2: return launch_tc_g<2>(p, tm, stream);

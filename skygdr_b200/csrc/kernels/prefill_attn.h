@@ -14,19 +14,17 @@ struct PrefillAttnParams {
     const __nv_bfloat16* kv;     // base of this layer's pages inside the pool (K and V already appended)
     __nv_bfloat16* out;          // [total_tokens][q_heads][128]
     const int* block_table;      // [n_seqs][max_blocks]; entries past a prompt's pages must name valid blocks (0 is fine)
-    const int* seq_start;        // [n_seqs + 1]: token offset of every prompt in q / out (prefix sums of the lengths)
+    const int* seq_start;        // [n_seqs + 1]: token offset of every prompt (or piece of a prompt) in q / out
     long long block_stride;      // elements between consecutive blocks of the pool
     long long kv_stride;         // elements from a block's K page to its V page
     long long head_stride;       // elements between KV heads inside a page
     long long tok_stride;        // elements between tokens inside a page (128 head-major, kv_heads*128 token-major)
     int n_seqs, q_heads, kv_heads, max_blocks;
-    int max_len;                 // longest prompt (sizes the grid)
+    int max_len;                 // most queries of one sequence in this launch (sizes the grid)
     int total_tokens;
     float scale;
-    int two_tiles;               // 1: two query tiles per CTA working in alternation (prefill_attn_tc2_kernel); 0: one tile per CTA;
-                                 // 2: two tiles with key steps of 64 and double-buffered scores (prefill_attn_tc3_kernel);
-                                 // 3-6: the two-tile kernel with part of the exponentials on the FMA pipe and/or P kept in TMEM
-                                 // (3: 1 of 4 exponentials; 4: P in TMEM; 5: both; 6: 2 of 4 exponentials and P in TMEM)
+    const int* pos0;             // [n_seqs] or nullptr: tokens of each sequence that precede its queries of this launch; their K/V are in
+                                 // the pool already and every query attends to them (chunked prefill)
     LaunchStatus* status;
 };
 

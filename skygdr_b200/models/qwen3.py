@@ -157,23 +157,6 @@ class Qwen3Weights:
         self.final_norm = t("model.norm.weight", (H,)).clone()
         return self
 
-    def fold_norms(self) -> "Qwen3Weights":
-        """Multiplies the gains of the three RMSNorms that feed a projection (ln1 -> qkv, ln2 -> gate_up, final norm -> lm_head)
-        into that projection's columns, in place, and sets the gains to one. The model is the same function of its inputs up
-        to bf16 rounding of the products; what is left of each norm is one factor per token, which the GEMM epilogues can apply
-        (``Qwen3Decoder(fuse_norm=True)``). Every other path keeps working on the folded weights, with gains of one."""
-        if getattr(self, "norms_folded", False):
-            return self
-        for w in self.layers:
-            w.qkv.mul_(w.ln1[None, :])
-            w.gate_up.mul_(w.ln2[None, :])
-            w.ln1.fill_(1.0)
-            w.ln2.fill_(1.0)
-        self.lm_head.mul_(self.final_norm[None, :])
-        self.final_norm.fill_(1.0)
-        self.norms_folded = True
-        return self
-
     def nbytes(self) -> int:
         n = self.embed.numel() + self.lm_head.numel() + self.final_norm.numel()
         for w in self.layers:
@@ -185,24 +168,12 @@ class Qwen3Decoder:
     """Single-GPU decode engine: fixed-capacity batch, preallocated activations, optional CUDA graph."""
 
     def __init__(self, cfg: Qwen3Config, weights: Qwen3Weights, pool: PagedKVPool, max_batch: int, max_ctx: int,
-                 attn_chunk: int = 1024, attn_impl: str = "tc", prefill_attn: str = "tc", fuse_norm: bool = False,
-                 attn_tail_order: bool = False):
-        """fuse_norm: no norm kernels in the decode step. The O and down projections add their result to the residual stream in
-        their epilogue and leave each row's sum of squares behind; the QKV, gate/up and lm_head GEMMs read the residual stream
-        as it is and scale their output rows by rsqrt(mean square + eps). Needs ``weights.fold_norms()`` (done here if it has
-        not been). 6 kernels per layer instead of 8. Compiled and checked against the model's arithmetic on the CPU; not yet
-        run on a GPU, so it is off by default."""
+                 attn_chunk: int = 1024, attn_impl: str = "tc", prefill_attn: str = "tc"):
         assert pool.layout == "hnd" and prefill_attn in ("tc", "sdpa")
-        self.fuse_norm = fuse_norm
-        if fuse_norm:
-            weights.fold_norms()
         self.cfg, self.w, self.pool = cfg, weights, pool
         self.prefill_attn = prefill_attn              # default of prefill(): this package's kernel or the library arm
-        # prefill(): True runs its projections (more than 256 tokens) through the persistent GEMM with two TMEM accumulators
-        # (compiled, not yet run on a GPU, hence off)
-        self.prefill_gemm_persistent = False
         # decode sampling: 0 = greedy (argmax); > 0 draws from softmax(logits / temperature), noise keyed by (sample_seed, position).
-        # Set before capture(): a captured graph keeps the choice it was captured with. Sampling has not run on a GPU yet.
+        # Set before capture(): a captured graph keeps the choice it was captured with.
         self.temperature, self.sample_seed = 0.0, 0
         self._prefill_attn = None
         dev = pool.data.device
@@ -225,14 +196,10 @@ class Qwen3Decoder:
         self.max_blocks = (max_ctx + 15) // 16
         self.block_table = torch.zeros((B, self.max_blocks), dtype=torch.int32, device=dev)
         self.inv_freq = ops.rope_inv_freq(cfg.rope_theta, dev, cfg.head_dim)
-        self.attn = ops.PagedAttention(dev, B, cfg.q_heads, cfg.kv_heads, max_ctx, attn_chunk, impl=attn_impl, tail_order=attn_tail_order)
+        self.attn = ops.PagedAttention(dev, B, cfg.q_heads, cfg.kv_heads, max_ctx, attn_chunk, impl=attn_impl)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.graph_batch = 0
         self.kernels_per_step = 1 + 8 * cfg.layers + 3   # embedding, 8 per layer, final norm, lm_head, argmax
-        if fuse_norm:
-            # one slot per norm of the step: ln1 and ln2 of every layer, then the final norm
-            self.row_ss = torch.zeros((2 * cfg.layers + 1, B), dtype=torch.float32, device=dev)
-            self.kernels_per_step = 1 + 6 * cfg.layers + 2
 
     # ---- state ----
     def set_batch(self, ids: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor) -> None:
@@ -245,25 +212,7 @@ class Qwen3Decoder:
         self.block_table[:b, :block_table.shape[1]].copy_(block_table)
 
     # ---- one decode step for the first `b` slots ----
-    def _step_fused_norm(self, b: int, max_ctx: int) -> None:
-        cfg, w, ss = self.cfg, self.w, self.row_ss
-        resid = self.resid[:b]
-        qkv, q, ao, act = self.qkv[:b], self.q[:b], self.attn_out[:b], self.act[:b]
-        pos, ctx, table = self.positions[:b], self.ctx_lens[:b], self.block_table[:b]
-        ops.embedding(self.ids[:b], w.embed, out=resid, row_ss=ss)           # slot 0 filled, the others zeroed
-        for li, lw in enumerate(w.layers):
-            ops.gemm(resid, lw.qkv, out=qkv, ss_in=ss[2 * li], eps=cfg.eps)
-            ops.rope_append(qkv, lw.q_norm, lw.k_norm, self.pool, li, self.inv_freq, table, pos, cfg.q_heads, cfg.eps, q_out=q)
-            self.attn(q, self.pool, li, table, ctx, max_ctx=max_ctx, out=ao)
-            ops.gemm(ao.view(b, -1), lw.o, out=resid, residual=True, ss_out=ss[2 * li + 1])
-            ops.gemm(resid, lw.gate_up, out=act, gated=True, ss_in=ss[2 * li + 1], eps=cfg.eps)
-            ops.gemm(act, lw.down, out=resid, residual=True, ss_out=ss[2 * li + 2])
-        ops.gemm(resid, w.lm_head, out=self.logits[:b], ss_in=ss[2 * cfg.layers], eps=cfg.eps)
-        self._pick(b)
-
     def _step(self, b: int, max_ctx: int) -> None:
-        if self.fuse_norm:
-            return self._step_fused_norm(b, max_ctx)
         cfg, w = self.cfg, self.w
         resid, xn, h = self.resid[:b], self.xn[:b], self.h[:b]
         qkv, q, ao, act = self.qkv[:b], self.q[:b], self.attn_out[:b], self.act[:b]
@@ -343,71 +292,102 @@ class Qwen3Decoder:
         return weights + kv
 
     # ---- prefill: whole prompts, token-major or head-major pool, returns last-position logits ----
+    @staticmethod
+    def prefill_plan(seq_lens: List[int], chunk: int) -> List[List[tuple]]:
+        """Cuts the prompts into passes of at most ``chunk`` tokens: a list of passes, each a list of (sequence, first token,
+        end token). A prompt longer than the room left in a pass continues in the next one, so a sequence appears at most
+        once per pass and its pieces run in order."""
+        assert chunk >= 1
+        passes, cur, room = [], [], chunk
+        for s, n in enumerate(seq_lens):
+            p = 0
+            while p < n:
+                take = min(n - p, room)
+                cur.append((s, p, p + take))
+                p += take
+                room -= take
+                if room == 0:
+                    passes.append(cur)
+                    cur, room = [], chunk
+        if cur:
+            passes.append(cur)
+        return passes
+
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor, seq_lens: List[int], block_table: torch.Tensor, pool: Optional[PagedKVPool] = None,
-                chunk: int = 2048, attn: Optional[str] = None) -> torch.Tensor:
-        """Runs the prompts through the stack, writing K/V into ``pool`` (default: the decode pool).
+                chunk: int = 8192, attn: Optional[str] = None) -> torch.Tensor:
+        """Runs the prompts through the stack, writing K/V into ``pool`` (default: the decode pool); returns the logits of
+        every prompt's last position, [n_seqs][vocab].
 
-        GEMMs and K/V append use this package's kernels. The causal attention over the prompt is this package's tcgen05
-        kernel reading the pages in place (``attn="tc"``, csrc/kernels/prefill_attn_tc.cu) or torch's
-        scaled_dot_product_attention over gathered copies of K and V (``attn="sdpa"``, a library kernel, kept as the
-        comparison arm). Default: ``self.prefill_attn``."""
+        At most ``chunk`` tokens go through the stack at once, so the activations stay bounded whatever the prompt lengths: a
+        long prompt is processed in pieces, each piece attending to the K/V that the earlier pieces left in the pool.
+        GEMMs and K/V append use this package's kernels. The causal attention is this package's tcgen05 kernel reading the
+        pages in place (``attn="tc"``, csrc/kernels/prefill_attn_tc.cu) or torch's scaled_dot_product_attention over gathered
+        copies of K and V (``attn="sdpa"``, a library kernel, kept as the comparison arm). Default: ``self.prefill_attn``."""
         attn = attn or self.prefill_attn
         assert attn in ("tc", "sdpa")
         cfg, w = self.cfg, self.w
         pool = pool or self.pool
         dev = ids.device
-        T = int(ids.numel())
-        seq_ids = torch.repeat_interleave(torch.arange(len(seq_lens), device=dev, dtype=torch.int32),
-                                          torch.tensor(seq_lens, device=dev))
-        starts = torch.cumsum(torch.tensor([0] + seq_lens[:-1], device=dev), 0)
-        positions = (torch.arange(T, device=dev) - torch.repeat_interleave(starts, torch.tensor(seq_lens, device=dev))).int()
-        resid = ops.embedding(ids.int(), w.embed)
-        h = None
         D = cfg.head_dim
-        persistent = self.prefill_gemm_persistent and T > 256
-
-        def proj(x, wt, gated=False):
-            return ops.gemm(x, wt, gated=gated, persistent=True) if persistent else ops.gemm(x, wt, gated=gated)
-
-        for li, lw in enumerate(w.layers):
-            xn = ops.rmsnorm(resid, lw.ln1, cfg.eps) if h is None else ops.rmsnorm(h, lw.ln1, cfg.eps, residual=resid)
-            qkv = proj(xn, lw.qkv)
-            q = ops.rope_append(qkv, lw.q_norm, lw.k_norm, pool, li, self.inv_freq, block_table, positions, cfg.q_heads, cfg.eps,
-                                seq_ids=seq_ids)
-            ao = torch.empty_like(q)
-            if attn == "tc":
-                if li == 0:
-                    if self._prefill_attn is None:
-                        self._prefill_attn = ops.PrefillAttention(dev)
-                    seq_start = torch.tensor([0] + list(torch.tensor(seq_lens).cumsum(0).tolist()), dtype=torch.int32, device=dev)
-                self._prefill_attn(q, pool, li, block_table, seq_start, max(seq_lens), out=ao)
-                h = proj(ao.view(T, -1), lw.o)
-                xn = ops.rmsnorm(h, lw.ln2, cfg.eps, residual=resid)
-                act = proj(xn, lw.gate_up, gated=True)
-                h = proj(act, lw.down)
-                continue
-            o = 0
-            for si, n in enumerate(seq_lens):
-                nb = (n + 15) // 16
-                kvb = pool.data[block_table[si, :nb].long(), li]        # [nb][2][...]
-                if pool.layout == "hnd":
-                    k = kvb[:, 0].permute(1, 0, 2, 3).reshape(cfg.kv_heads, nb * 16, D)[:, :n]
-                    v = kvb[:, 1].permute(1, 0, 2, 3).reshape(cfg.kv_heads, nb * 16, D)[:, :n]
+        starts = [0]
+        for n in seq_lens[:-1]:
+            starts.append(starts[-1] + int(n))
+        if attn == "tc" and self._prefill_attn is None:
+            self._prefill_attn = ops.PrefillAttention(dev)
+        last_hidden = [None] * len(seq_lens)
+        for pieces in self.prefill_plan([int(n) for n in seq_lens], int(chunk)):
+            lens = [e - b for _, b, e in pieces]
+            T = sum(lens)
+            tok = torch.cat([torch.arange(starts[s] + b, starts[s] + e, device=dev) for s, b, e in pieces])
+            positions = torch.cat([torch.arange(b, e, device=dev) for _, b, e in pieces]).int()
+            seq_ids = torch.repeat_interleave(torch.tensor([s for s, _, _ in pieces], device=dev, dtype=torch.int32),
+                                              torch.tensor(lens, device=dev))
+            seq_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32, device=dev)
+            pos0 = torch.tensor([b for _, b, _ in pieces], dtype=torch.int32, device=dev)
+            rows = block_table[torch.tensor([s for s, _, _ in pieces], device=block_table.device)].contiguous()
+            resid = ops.embedding(ids[tok].int(), w.embed)
+            h = None
+            for li, lw in enumerate(w.layers):
+                xn = ops.rmsnorm(resid, lw.ln1, cfg.eps) if h is None else ops.rmsnorm(h, lw.ln1, cfg.eps, residual=resid)
+                qkv = ops.gemm(xn, lw.qkv)
+                q = ops.rope_append(qkv, lw.q_norm, lw.k_norm, pool, li, self.inv_freq, block_table, positions, cfg.q_heads, cfg.eps,
+                                    seq_ids=seq_ids)
+                ao = torch.empty_like(q)
+                if attn == "tc":
+                    self._prefill_attn(q, pool, li, rows, seq_start, max(lens), out=ao, pos0=pos0)
                 else:
-                    k = kvb[:, 0].reshape(nb * 16, cfg.kv_heads, D)[:n].transpose(0, 1)
-                    v = kvb[:, 1].reshape(nb * 16, cfg.kv_heads, D)[:n].transpose(0, 1)
-                qs = q[o:o + n].transpose(0, 1)                         # [Hq][n][D]
-                out = torch.nn.functional.scaled_dot_product_attention(qs[None], k[None], v[None], is_causal=True, enable_gqa=True)
-                ao[o:o + n] = out[0].transpose(0, 1)
+                    o = 0
+                    for (s, b, e), n in zip(pieces, lens):
+                        nb = (e + 15) // 16
+                        kvb = pool.data[block_table[s, :nb].long(), li]        # [nb][2][...]
+                        if pool.layout == "hnd":
+                            k = kvb[:, 0].permute(1, 0, 2, 3).reshape(cfg.kv_heads, nb * 16, D)[:, :e]
+                            v = kvb[:, 1].permute(1, 0, 2, 3).reshape(cfg.kv_heads, nb * 16, D)[:, :e]
+                        else:
+                            k = kvb[:, 0].reshape(nb * 16, cfg.kv_heads, D)[:e].transpose(0, 1)
+                            v = kvb[:, 1].reshape(nb * 16, cfg.kv_heads, D)[:e].transpose(0, 1)
+                        qs = q[o:o + n].transpose(0, 1)                         # [Hq][n][D]
+                        if b == 0:
+                            out = torch.nn.functional.scaled_dot_product_attention(qs[None], k[None], v[None], is_causal=True, enable_gqa=True)
+                        else:
+                            mask = torch.ones((n, e), dtype=torch.bool, device=dev).tril(diagonal=b)
+                            out = torch.nn.functional.scaled_dot_product_attention(qs[None], k[None], v[None], attn_mask=mask, enable_gqa=True)
+                        ao[o:o + n] = out[0].transpose(0, 1)
+                        o += n
+                h = ops.gemm(ao.view(T, -1), lw.o)
+                xn = ops.rmsnorm(h, lw.ln2, cfg.eps, residual=resid)
+                act = ops.gemm(xn, lw.gate_up, gated=True)
+                h = ops.gemm(act, lw.down)
+            o = 0
+            for (s, b, e), n in zip(pieces, lens):
+                if e == int(seq_lens[s]):                                       # this piece ends its prompt: keep the last row
+                    last_hidden[s] = (h[o + n - 1] if h is not None else torch.zeros_like(resid[0]), resid[o + n - 1])
                 o += n
-            h = proj(ao.view(T, -1), lw.o)
-            xn = ops.rmsnorm(h, lw.ln2, cfg.eps, residual=resid)
-            act = proj(xn, lw.gate_up, gated=True)
-            h = proj(act, lw.down)
-        xn = ops.rmsnorm(h, w.final_norm, cfg.eps, residual=resid)
-        last = torch.cumsum(torch.tensor(seq_lens, device=dev), 0) - 1
-        return ops.gemm(xn[last].contiguous(), w.lm_head)
+        hs = torch.stack([x[0] for x in last_hidden])
+        rs = torch.stack([x[1] for x in last_hidden])
+        xn = ops.rmsnorm(hs, w.final_norm, cfg.eps, residual=rs)
+        return ops.gemm(xn, w.lm_head)
 
 
 # ---------------------------------------------------------------------------

@@ -14,32 +14,21 @@ from .kv_cache import PagedKVPool
 class PagedAttention:
     """Holds the split-KV scratch (partials, statistics, counters) for a maximum batch and context."""
 
-    def __init__(self, device, max_batch: int, q_heads: int, kv_heads: int, max_ctx: int, chunk_tokens: int = 512, impl: str = "simt",
-                 tail_order=False):
-        """impl: "simt" (CUDA cores, paged_attn.cu), "tc" (tcgen05 tensor cores, one CTA per (sequence, split, KV head);
-        chunk_tokens % 128 == 0) or "tcp" (the same engine as a persistent kernel of two CTAs per SM that walk the work items;
-        chunk_tokens <= 1024, batch <= 256; meant for small batches, where it can use 512-token items without paying a CTA
-        start-up per item). tail_order ("tc" only): True = every sequence's last, partial chunk is scheduled after all full
-        chunks, so the CTAs that finish the launch alone on their SMs are short ones; "fine" = that last part is also cut into
-        quarter chunks (chunk_tokens % 512 == 0; up to three partials more per sequence), so they are shorter still. Neither has
-        run on a GPU yet."""
-        assert tail_order in (False, True, "fine") and (not tail_order or impl == "tc")
-        assert tail_order != "fine" or chunk_tokens % 512 == 0
-        self.tail_order = 2 if tail_order == "fine" else int(bool(tail_order))
-        assert impl in ("simt", "tc", "tcp") and (impl == "simt" or chunk_tokens % 128 == 0)
-        assert impl != "tcp" or (chunk_tokens <= 1024 and max_batch <= 256)
+    def __init__(self, device, max_batch: int, q_heads: int, kv_heads: int, max_ctx: int, chunk_tokens: int = 512, impl: str = "simt"):
+        """impl: "tc" (tcgen05 tensor cores, one CTA per (sequence, split, KV head); chunk_tokens % 128 == 0) or "simt" (CUDA
+        cores, paged_attn.cu: the second implementation and the oracle of the first)."""
+        assert impl in ("simt", "tc") and (impl == "simt" or chunk_tokens % 128 == 0)
         self.impl = impl
         self._C = load()
         self.device = torch.device(device)
         self.q_heads, self.kv_heads, self.chunk_tokens, self.max_ctx = q_heads, kv_heads, chunk_tokens, max_ctx
-        self.max_splits = max_ctx // chunk_tokens + 4 if self.tail_order == 2 else (max_ctx + chunk_tokens - 1) // chunk_tokens
+        self.max_splits = (max_ctx + chunk_tokens - 1) // chunk_tokens
         self.part_o = torch.empty((max_batch, q_heads, self.max_splits, 128), dtype=torch.float32, device=self.device)
         self.part_m = torch.empty((max_batch, q_heads, self.max_splits), dtype=torch.float32, device=self.device)
         self.part_l = torch.empty_like(self.part_m)
         self.counters = torch.zeros((max_batch * kv_heads,), dtype=torch.int32, device=self.device)
         self.status = new_status(self.device)
         self.max_batch = max_batch
-        self._persistent = 2 * torch.cuda.get_device_properties(self.device).multi_processor_count if impl == "tcp" else 0
 
     def __call__(self, q: torch.Tensor, pool: PagedKVPool, layer: int, block_table: torch.Tensor, ctx_lens: torch.Tensor,
                  max_ctx: Optional[int] = None, out: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
@@ -48,35 +37,31 @@ class PagedAttention:
             out = torch.empty_like(q)
         bs, ls, ks = pool.strides
         self._C.paged_attn_decode(q, pool.layer_base(layer), out, block_table, ctx_lens, bs, ks, pool.head_stride, self.kv_heads,
-                                  min(max_ctx or self.max_ctx, self.max_ctx), self.chunk_tokens,
+                                  min(max_ctx or self.max_ctx, self.max_ctx, block_table.shape[1] * 16), self.chunk_tokens,
                                   scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]),
                                   self.part_o, self.part_m, self.part_l, self.counters, self.status,
                                   (pool.data.numel() - layer * ls) // 128 if self.impl != "simt" else 0,
-                                  **({"persistent_ctas": self._persistent} if self._persistent else {}),
-                                  **({"tail_order": self.tail_order} if self.tail_order else {}))
+                                  num_blocks=pool.data.shape[0])
         return out
 
 
 class PrefillAttention:
-    """Causal attention of whole prompts against their own K/V in the paged pool (prefill_attn_tc.cu): tcgen05 MMAs with the
-    accumulators in TMEM, K/V pages fetched by TMA straight from the pool in either layout, one CTA per 128-token query tile.
-    Pages must hold finite values past a prompt's last token (a fresh pool is zeroed); block-table entries past a prompt's
-    pages must name valid blocks."""
+    """Causal attention of prompts, or of the next piece of each prompt, against their K/V in the paged pool
+    (prefill_attn_tc.cu): tcgen05 MMAs with the accumulators in TMEM, K/V pages fetched by TMA straight from the pool in
+    either layout, two 128-token query tiles per CTA. Pages must hold finite values past a prompt's last token (a fresh
+    pool is zeroed); block-table entries past a prompt's pages must name valid blocks."""
 
-    def __init__(self, device, two_tiles=True):
-        """two_tiles: True = two query tiles per CTA working in alternation with the tensor core (the faster variant); False = one
-        query tile per CTA with two softmax warpgroups per tile; 2 = two tiles with key steps of 64 and double-buffered scores
-        (compiled, not yet run on a GPU); 3-6 = the two-tile kernel with one of every four exponentials computed by a cubic on
-        the FMA pipe (3), with P written to TMEM over its own scores and taken from there by the P.V MMA (4), both (5), or two
-        of every four exponentials and P in TMEM (6). 3-6 are compiled, not yet run on a GPU."""
+    def __init__(self, device):
         self._C = load()
         self.device = torch.device(device)
         self.status = new_status(self.device)
-        self.two_tiles = two_tiles
 
     def __call__(self, q: torch.Tensor, pool: PagedKVPool, layer: int, block_table: torch.Tensor, seq_start: torch.Tensor, max_len: int,
-                 out: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
-        """q: [tokens][q_heads][128] with the prompts packed back to back; seq_start: int32 [n_seqs + 1] token offsets."""
+                 out: Optional[torch.Tensor] = None, scale: Optional[float] = None, pos0: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """q: [tokens][q_heads][128] with the prompts (or pieces of prompts) packed back to back; seq_start: int32
+        [n_seqs + 1] token offsets into q; max_len: the longest piece. pos0 (int32 [n_seqs], optional): how many tokens of
+        each sequence precede its first query here; their K/V are already in the pool and every query attends to them
+        (chunked prefill). Without it every sequence starts at position 0."""
         if out is None:
             out = torch.empty_like(q)
         bs, ls, ks = pool.strides
@@ -87,12 +72,14 @@ class PrefillAttention:
             head_stride, tok_stride = g.head_dim, g.kv_heads * g.head_dim
         self._C.prefill_attn(q, pool.layer_base(layer), out, block_table, seq_start, bs, ks, head_stride, tok_stride, g.kv_heads, int(max_len),
                              scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]), self.status,
-                             (pool.data.numel() - layer * ls) // 128, int(self.two_tiles))
+                             (pool.data.numel() - layer * ls) // 128, pos0)
         return out
 
 
-def prefill_attn_reference(q: torch.Tensor, pool: PagedKVPool, layer: int, block_table: torch.Tensor, seq_lens, scale: Optional[float] = None) -> torch.Tensor:
-    """Plain fp32 causal softmax attention of packed prompts over the gathered pages (test oracle)."""
+def prefill_attn_reference(q: torch.Tensor, pool: PagedKVPool, layer: int, block_table: torch.Tensor, seq_lens, scale: Optional[float] = None,
+                           pos0=None) -> torch.Tensor:
+    """Plain fp32 causal softmax attention of packed prompts over the gathered pages (test oracle). ``seq_lens``: queries per
+    sequence in ``q``; ``pos0``: tokens of each sequence that precede them (already in the pool), default none."""
     T, Hq, D = q.shape
     Hkv = pool.geom.kv_heads
     G = Hq // Hkv
@@ -101,15 +88,17 @@ def prefill_attn_reference(q: torch.Tensor, pool: PagedKVPool, layer: int, block
     o = 0
     for s, n in enumerate(seq_lens):
         n = int(n)
-        nb = (n + 15) // 16
+        p0 = int(pos0[s]) if pos0 is not None else 0
+        nk = p0 + n
+        nb = (nk + 15) // 16
         kv = pool.data[block_table[s, :nb].long(), layer]
         if pool.layout == "nhd":
             kv = kv.permute(0, 1, 3, 2, 4)                 # -> [nb][2][H][16][D]
-        k = kv[:, 0].permute(1, 0, 2, 3).reshape(Hkv, nb * 16, D)[:, :n].float()
-        v = kv[:, 1].permute(1, 0, 2, 3).reshape(Hkv, nb * 16, D)[:, :n].float()
+        k = kv[:, 0].permute(1, 0, 2, 3).reshape(Hkv, nb * 16, D)[:, :nk].float()
+        v = kv[:, 1].permute(1, 0, 2, 3).reshape(Hkv, nb * 16, D)[:, :nk].float()
         qs = q[o:o + n].float().view(n, Hkv, G, D).permute(1, 2, 0, 3)          # [Hkv][G][n][D]
         sc = torch.einsum("hgqd,hkd->hgqk", qs, k) * scale
-        mask = torch.ones((n, n), dtype=torch.bool, device=q.device).tril()
+        mask = torch.ones((n, nk), dtype=torch.bool, device=q.device).tril(diagonal=p0)     # query i sees keys 0 .. p0 + i
         sc = sc.masked_fill(~mask, float("-inf"))
         pr = torch.softmax(sc, dim=-1)
         out[o:o + n] = torch.einsum("hgqk,hkd->hgqd", pr, v).permute(2, 0, 1, 3).reshape(n, Hq, D)

@@ -37,11 +37,13 @@ class GemmCostModel:
     hbm_rate: float = 5.5e6
 
 
-# Fitted to a measured sweep of the decoder's GEMM shapes run alone on B200 (token tiles 16-128, 1-16 splits, L2 flushed).
-STANDALONE = GemmCostModel(3.0, 2.0, 55e3, 45e3, True, float("inf"), 50e3)
-# The fused tensor-parallel GEMMs wait for all-gather arrivals and raise reduce-scatter arrivals per token tile and finish a split
-# tile with one more dependent step before the push, so fewer, larger CTAs win there. These are the constants under which the
-# tensor-parallel decode step was tuned end to end (TP 2 / 4 / 8); the stand-alone fit costs it 3 % at TP 2 and 15 % at TP 8.
+# Fitted to a measured sweep on B200 of the decoder's GEMM shapes at 1, 2, 4 and 8-way tensor parallelism (16 to 128 token rows):
+# every shape as a chain of launches inside a CUDA graph, each launch on its own copy of the weights (cold in HBM), token tiles
+# 16-128 and 1-16 splits. Summed over the 16 shapes the chosen configurations are 3.4 us slower than the best measured ones.
+STANDALONE = GemmCostModel(1.56, 1.75, 36.4e3, 57.4e3, True, float("inf"), 26.2e3, hbm_rate=5.76e6)
+# The GEMMs that wait for an all-gather (reduce-scatter + all-gather form of the tensor-parallel step) run one CTA per SM and
+# raise arrivals per token tile, so fewer, larger CTAs win there. These are the constants under which that form was tuned end
+# to end (TP 2 / 4 / 8).
 FUSED_TP = GemmCostModel(6.0, 6.0, 55e3, 55e3, False, 100e3, 200e3)
 
 
@@ -109,35 +111,32 @@ def workspace_for(device) -> GemmWorkspace:
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, gated: bool = False,
-         splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, ntok: int = 0, ss_in: Optional[torch.Tensor] = None,
-         eps: float = 1e-6, residual: bool = False, ss_out: Optional[torch.Tensor] = None, persistent: bool = False) -> torch.Tensor:
+         splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, ntok: int = 0, persistent: Optional[bool] = None) -> torch.Tensor:
     """y = x @ w.T (w is [N][K]); gated: w is [2N][K] and y = silu(x @ w[:N].T) * (x @ w[N:].T).
 
-    RMSNorm folded into the epilogues (the gain is expected inside ``w`` already, see ``Qwen3Weights.fold_norms``):
-    ``ss_in`` (fp32, one sum of squares per row of x) scales output row t by rsqrt(ss_in[t] / K + eps); ``residual`` makes ``out``
-    the residual stream, updated in place (out += x @ w.T), and ``ss_out`` then receives the sums of squares of the new rows
-    (added to what it holds: zero it first).
-
-    ``persistent`` (many-token shapes, plain projection): one CTA per SM walks the output tiles with two accumulators in TMEM,
-    so a tile's epilogue overlaps the next tile's MMAs (tiles of 256 tokens, 128 when gated). Compiled, not yet run on a GPU."""
+    Few tokens (M <= 256, decode): one CTA per output tile with split-K, tile and split chosen by ``pick_config``.
+    Many tokens (prefill): the persistent form, one CTA per SM walking tiles of 256 tokens (128 when gated) with two
+    accumulators in TMEM, so that a tile's epilogue overlaps the next tile's MMAs. ``persistent`` overrides the choice
+    (False = one tile per CTA at any M, kept for comparison)."""
     C = load()
     M, K = x.shape
     N = w.shape[0] // 2 if gated else w.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    ws = ws or workspace_for(x.device)
+    if persistent is None:
+        persistent = M > 256 and splits in (None, 1)
+    if persistent:
+        C.gemm(x, w, out, 1, gated, None, None, ws.status, 128 if (gated or ntok == 128) else 256, True)
+        return out
     if splits is None:
         if ntok == 0 and M <= 256:
             ntok, splits = pick_config(M, N, K, _sms(x.device), gated)
         else:
             splits = 1 if M > 256 else pick_config(M, N, K, _sms(x.device), gated, fixed_ntok=ntok)[1]
-    ws = ws or workspace_for(x.device)
-    if persistent:
-        assert not residual and ss_in is None, "the persistent form is the plain projection"
-        C.gemm(x, w, out, 1, gated, None, None, ws.status, 128 if (gated or ntok == 128) else 256, None, eps, False, None, True)
-        return out
     if splits > 1:
         ws.ensure(C.gemm_workspace_floats(M, N, splits, gated, ntok), C.gemm_counter_count(M, N, gated, ntok))
-        C.gemm(x, w, out, splits, gated, ws.ws, ws.counters, ws.status, ntok, ss_in, eps, residual, ss_out)
+        C.gemm(x, w, out, splits, gated, ws.ws, ws.counters, ws.status, ntok)
     else:
-        C.gemm(x, w, out, 1, gated, None, None, ws.status, ntok, ss_in, eps, residual, ss_out)
+        C.gemm(x, w, out, 1, gated, None, None, ws.status, ntok)
     return out

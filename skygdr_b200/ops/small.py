@@ -46,12 +46,11 @@ def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch
     return out
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, row_ss: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Gathers table rows. ``row_ss`` (fp32 [slots][>= tokens]): slot 0 receives every gathered row's sum of squares and the other
-    slots are zeroed, ready for the GEMM epilogues that accumulate into them."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gathers table rows."""
     if out is None:
         out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
-    load().embedding(ids, table, out, row_ss)
+    load().embedding(ids, table, out)
     return out
 
 
@@ -66,7 +65,7 @@ def sample(logits: torch.Tensor, temperature: float, seed: int, positions: Optio
            out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Draws one token per row from softmax(logits / temperature) (Gumbel-max over hashed noise, one pass, no normalisation).
     Deterministic for a given (seed, positions): ``positions`` (int32, one per row) makes a replayed CUDA graph draw fresh
-    noise every step, since a sequence's position advances. Greedy decoding is ``argmax``. Compiled, not yet run on a GPU."""
+    noise every step, since a sequence's position advances. Greedy decoding is ``argmax``."""
     if out is None:
         out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
     load().sample(logits, out, float(temperature), int(seed) & 0xFFFFFFFF, positions)

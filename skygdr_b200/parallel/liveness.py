@@ -45,7 +45,12 @@ class Health:
 
 
 class RankWatch:
-    def __init__(self, rank: int, world: int, store=None, beat_s: float = 0.1, stale_after_s: float = 1.5, name: str = "engine"):
+    def __init__(self, rank: int, world: int, store=None, beat_s: float = 0.1, stale_after_s: float = 1.5, name: str = "engine",
+                 store_host_rank: int = 0):
+        """store_host_rank: the rank whose process serves the store (rank 0 for a store created by ``init_process_group`` from
+        a tcp:// address; under torchrun the launcher serves it and it outlives every rank). When the store stops answering,
+        that rank is what has gone, and ``check`` reports it as stale instead of raising the store's own error."""
+        self.store_host_rank = store_host_rank
         if store is None:
             store = dist.distributed_c10d._get_default_store()
         self.store = dist.PrefixStore(f"skygdr_live/{name}", store)
@@ -97,17 +102,25 @@ class RankWatch:
 
     # ---- the others' side ----
     def check(self) -> Health:
-        """One pass over the peers' markers and heartbeats; does not block."""
+        """One pass over the peers' markers and heartbeats; does not block. A store that no longer answers (its host process
+        is gone) is not an error of this rank: the host rank is reported as stale, so that ``guard`` raises ``PeerLost``."""
         h, now = Health(), time.time()
-        for r in range(self.world):
-            if r == self.rank:
-                continue
-            if self.store.check([f"left/{r}"]):
-                h.left[r] = self.store.get(f"left/{r}").decode()
-            elif not self.store.check([f"hb/{r}"]):
-                h.missing.append(r)
-            elif now - float(self.store.get(f"hb/{r}").decode()) > self.stale_after_s:
-                h.stale.append(r)
+        try:
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                if self.store.check([f"left/{r}"]):
+                    h.left[r] = self.store.get(f"left/{r}").decode()
+                elif not self.store.check([f"hb/{r}"]):
+                    h.missing.append(r)
+                elif now - float(self.store.get(f"hb/{r}").decode()) > self.stale_after_s:
+                    h.stale.append(r)
+        except Exception:               # connection reset / broken pipe / store timeout: the store's host has gone
+            lost = self.store_host_rank if self.store_host_rank != self.rank else None
+            if lost is not None and lost not in h.stale and lost not in h.left:
+                h.stale.append(lost)
+            elif lost is None:          # this rank hosts the store and cannot read it: nothing about the peers can be known
+                h.stale = [r for r in range(self.world) if r != self.rank and r not in h.left]
         return h
 
     def guard(self) -> None:

@@ -2,8 +2,9 @@
 
 all-gather and reduce-scatter are torch.distributed calls (NCCL over NVLink), GEMMs are torch.matmul (cuBLAS);
 norms, RoPE + KV append, paged attention, SiLU*mul and sampling stay this package's kernels, so the difference to
-``TPDecoder`` is exactly what fusing the collectives into the GEMM and norm kernels buys. This is the baseline
-mechanism (a library call per collective), not the product path.
+``TPDecoder`` is exactly what this package's GEMMs and the collectives fused into them buy. This is the baseline
+mechanism (a library call per collective and per GEMM), not the product path. With one rank there is no collective
+and the arm is the decoder on cuBLAS GEMMs.
 """
 from __future__ import annotations
 
@@ -15,7 +16,12 @@ from ..models.qwen3 import Qwen3Decoder
 
 
 class NcclTPDecoder:
-    def __init__(self, cfg, weights, pool, batch, max_ctx, rank, world, attn, group=None):
+    def __init__(self, cfg, weights, pool, batch, max_ctx, rank, world, attn, group=None, collective: str = "rs_ag"):
+        """collective: "rs_ag" = reduce-scatter + all-gather around a token-sharded residual stream (four library collectives per
+        layer); "allreduce" = one all-reduce after each row-parallel GEMM with the residual stream replicated (two per layer, the
+        form inference servers use for decode)."""
+        assert collective in ("rs_ag", "allreduce")
+        self.collective = collective
         self.cfg, self.w, self.pool, self.batch, self.max_ctx, self.rank, self.world, self.attn, self.group = \
             cfg, weights, pool, batch, max_ctx, rank, world, attn, group
         dev = pool.data.device
@@ -41,15 +47,67 @@ class NcclTPDecoder:
         self.inv_freq = ops.rope_inv_freq(cfg.rope_theta, dev, cfg.head_dim)
         self.graph, self.graph_batch = None, batch
         self.max_batch = batch
+        self.logits = None                      # this rank's vocabulary slice of the last step's logits
+        if collective == "allreduce":
+            self.resid_full = torch.zeros((batch, H), **bf)
+            self.xn_full = torch.empty((batch, H), **bf)
+
+    def _all_gather(self, out, x):
+        if self.world > 1:
+            dist.all_gather_into_tensor(out, x, group=self.group)
+        else:
+            out.copy_(x)
+
+    def _reduce_scatter(self, out, x):
+        if self.world > 1:
+            dist.reduce_scatter_tensor(out, x, group=self.group)
+        else:
+            out.copy_(x)
 
     @classmethod
-    def from_engine(cls, eng) -> "NcclTPDecoder":
-        b = cls(eng.cfg, eng.w, eng.pool, eng.batch, eng.max_ctx, eng.rank, eng.world, eng.attn)
+    def from_engine(cls, eng, collective: str = "rs_ag") -> "NcclTPDecoder":
+        b = cls(eng.cfg, eng.w, eng.pool, eng.max_batch, eng.max_ctx, getattr(eng, "rank", 0), getattr(eng, "world", 1), eng.attn,
+                collective=collective)
         b.ids.copy_(eng.ids); b.positions.copy_(eng.positions); b.ctx_lens.copy_(eng.ctx_lens)
         b.block_table = eng.block_table
         return b
 
+    def _pick(self, x_full) -> None:
+        """lm_head on this rank's vocabulary slice, then the global argmax through two all-gathers."""
+        w = self.w
+        logits = self.logits = torch.matmul(x_full, w.lm_head.t())
+        val, idx = logits.float().max(-1)
+        self._all_gather(self.max_val.view(-1), val)
+        self._all_gather(self.max_idx.view(-1), idx + w.vocab_lo)
+        best = self.max_val.argmax(0)
+        self.next_ids.copy_(self.max_idx.gather(0, best[None])[0].int())
+
+    def _step_allreduce(self, b: int, max_ctx: int) -> None:
+        cfg, w = self.cfg, self.w
+        resid, xn, part = self.resid_full, self.xn_full, self.partial
+        ops.embedding(self.ids, w.embed, out=resid)
+        for li, lw in enumerate(w.layers):
+            if li == 0:
+                ops.rmsnorm(resid, lw.ln1, cfg.eps, out=xn)
+            else:
+                ops.rmsnorm(part, lw.ln1, cfg.eps, residual=resid, out=xn)
+            qkv = torch.matmul(xn, lw.qkv.t())
+            ops.rope_append(qkv, lw.q_norm, lw.k_norm, self.pool, li, self.inv_freq, self.block_table, self.positions, self.qh, cfg.eps, q_out=self.q)
+            self.attn(self.q, self.pool, li, self.block_table, self.ctx_lens, max_ctx=max_ctx, out=self.attn_out)
+            torch.matmul(self.attn_out.view(b, -1), lw.o.t(), out=part)
+            if self.world > 1:
+                dist.all_reduce(part, group=self.group)
+            ops.rmsnorm(part, lw.ln2, cfg.eps, residual=resid, out=xn)
+            act = ops.silu_mul(torch.matmul(xn, lw.gate_up.t()))
+            torch.matmul(act, lw.down.t(), out=part)
+            if self.world > 1:
+                dist.all_reduce(part, group=self.group)
+        ops.rmsnorm(part, w.final_norm, cfg.eps, residual=resid, out=xn)
+        self._pick(xn)
+
     def _step(self, b: int, max_ctx: int) -> None:
+        if self.collective == "allreduce":
+            return self._step_allreduce(b, max_ctx)
         cfg, w = self.cfg, self.w
         r0 = self.rank * self.rows
         ops.embedding(self.ids[r0:r0 + self.rows], w.embed, out=self.resid)
@@ -60,26 +118,21 @@ class NcclTPDecoder:
                 first = False
             else:
                 ops.rmsnorm(self.h_local, lw.ln1, cfg.eps, residual=self.resid, out=self.xn_local)
-            dist.all_gather_into_tensor(self.x_full, self.xn_local, group=self.group)
+            self._all_gather(self.x_full, self.xn_local)
             qkv = torch.matmul(self.x_full, lw.qkv.t())
             ops.rope_append(qkv, lw.q_norm, lw.k_norm, self.pool, li, self.inv_freq, self.block_table, self.positions, self.qh, cfg.eps, q_out=self.q)
             self.attn(self.q, self.pool, li, self.block_table, self.ctx_lens, max_ctx=max_ctx, out=self.attn_out)
             torch.matmul(self.attn_out.view(b, -1), lw.o.t(), out=self.partial)
-            dist.reduce_scatter_tensor(self.h_local, self.partial, group=self.group)
+            self._reduce_scatter(self.h_local, self.partial)
             ops.rmsnorm(self.h_local, lw.ln2, cfg.eps, residual=self.resid, out=self.xn_local)
-            dist.all_gather_into_tensor(self.x_full, self.xn_local, group=self.group)
+            self._all_gather(self.x_full, self.xn_local)
             gu = torch.matmul(self.x_full, lw.gate_up.t())
             act = ops.silu_mul(gu)
             torch.matmul(act, lw.down.t(), out=self.partial)
-            dist.reduce_scatter_tensor(self.h_local, self.partial, group=self.group)
+            self._reduce_scatter(self.h_local, self.partial)
         ops.rmsnorm(self.h_local, w.final_norm, cfg.eps, residual=self.resid, out=self.xn_local)
-        dist.all_gather_into_tensor(self.x_full, self.xn_local, group=self.group)
-        logits = torch.matmul(self.x_full, w.lm_head.t())
-        val, idx = logits.float().max(-1)
-        dist.all_gather_into_tensor(self.max_val, val, group=self.group)
-        dist.all_gather_into_tensor(self.max_idx, idx + w.vocab_lo, group=self.group)
-        best = self.max_val.argmax(0)
-        self.next_ids.copy_(self.max_idx.gather(0, best[None])[0].int())
+        self._all_gather(self.x_full, self.xn_local)
+        self._pick(self.x_full)
 
     _advance = Qwen3Decoder._advance
     step = Qwen3Decoder.step

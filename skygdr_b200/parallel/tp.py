@@ -31,12 +31,11 @@ TIMEOUT_NS = 2_000_000_000
 
 class TPDecoder:
     def __init__(self, cfg: Qwen3Config, weights: Qwen3Weights, pool: PagedKVPool, batch: int, max_ctx: int, rank: int, world: int,
-                 attn_chunk: int = 1024, group=None, attn_impl: str = "tc", collective: str = "rs_ag",
-                 attn_tail_order: bool = False):
-        """collective: "rs_ag" = GEMM -> reduce-scatter and all-gather -> GEMM with a token-sharded residual stream (4 hops per
-        layer); "oneshot" = every rank pushes its full partial tile to every peer and the norm kernel sums `world` partials, with
-        the residual stream and the normed activations replicated (2 hops per layer, world-1 times the bytes; built for
-        latency-bound decode sizes, not yet run on GPUs)."""
+                 attn_chunk: int = 1024, group=None, attn_impl: str = "tc", collective: str = "oneshot"):
+        """collective: "oneshot" = every rank pushes its full partial tile to every peer in the GEMM epilogue and the norm kernel
+        sums `world` partials, with the residual stream and the normed activations replicated (2 hops per layer, world-1 times
+        the bytes: decode tiles are small enough for that); "rs_ag" = GEMM -> reduce-scatter and all-gather -> GEMM with a
+        token-sharded residual stream (4 hops per layer, the fewest bytes)."""
         assert batch % world == 0 and pool.layout == "hnd" and collective in ("rs_ag", "oneshot")
         self.collective = collective
         self._C = load()
@@ -78,7 +77,7 @@ class TPDecoder:
         self.max_blocks = (max_ctx + 15) // 16
         self.block_table = torch.zeros((B, self.max_blocks), dtype=torch.int32, device=dev)
         self.inv_freq = ops.rope_inv_freq(cfg.rope_theta, dev, D)
-        self.attn = ops.PagedAttention(dev, B, self.qh, self.kh, max_ctx, attn_chunk, impl=attn_impl, tail_order=attn_tail_order)
+        self.attn = ops.PagedAttention(dev, B, self.qh, self.kh, max_ctx, attn_chunk, impl=attn_impl)
         self.step_ctr = torch.zeros(1, dtype=torch.int32, device=dev)
         self.status = new_status(dev)
         self.ws = GemmWorkspace(dev)
@@ -113,10 +112,14 @@ class TPDecoder:
         self._C.tp_norm(rs_buf, rs_ctr, seq, self.resid, w, self.heap.all_ptrs(ag_name),
                         self.heap.all_ptrs("counters", ag_off + 4 * self.rank), self.rank, self.cfg.eps, TIMEOUT_NS, self.status)
 
+    def _config(self, M: int, N: int, K: int, gated: bool = False) -> Tuple[int, int]:
+        """(token tile, splits) of a GEMM of this engine; the arrival counts of the collectives are derived from the same choice."""
+        return pick_config(M, N, K, 148, gated, model=FUSED_TP if self.collective == "rs_ag" else STANDALONE)
+
     def _gemm(self, x, w, y, gated=False, ag=(), rs=()):
         M, K = x.shape
         N = w.shape[0] // 2 if gated else w.shape[0]
-        ntok, splits = pick_config(M, N, K, 148, gated, model=FUSED_TP if (ag or rs) else STANDALONE)
+        ntok, splits = self._config(M, N, K, gated)
         if splits > 1:
             self.ws.ensure(self._C.gemm_workspace_floats(M, N, splits, gated, ntok), self._C.gemm_counter_count(M, N, gated, ntok))
             self._C.gemm_tp(x, w, y, splits, gated, self.ws.ws, self.ws.counters, self.status, ag, rs, ntok)
@@ -125,7 +128,7 @@ class TPDecoder:
 
     def _rs_arrivals(self, K: int) -> int:
         """Arrivals one reduce-scatter adds to a rank's counter: every output tile of every rank's GEMM."""
-        ntok, _ = pick_config(self.batch, self.cfg.hidden, K, 148, False, model=FUSED_TP)
+        ntok, _ = self._config(self.batch, self.cfg.hidden, K)
         return self.world * self.tiles_h * ((self.batch + ntok - 1) // ntok)
 
     def set_batch(self, ids: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor) -> None:
@@ -266,9 +269,13 @@ class TPDecoder:
         return Qwen3Decoder.replay(self)
 
     def check_status(self) -> str:
+        """"OK", or the first non-OK status a kernel of this engine left behind: the GEMM, norm and argmax kernels share one
+        status word, the attention kernels have their own."""
         torch.cuda.synchronize(self.device)
-        st = read_status(self.status)
-        return st["status_name"] if st["status"] == 0 else f"{st['status_name']}:{st['detail']}"
+        for st in (read_status(self.status), read_status(self.attn.status)):
+            if st["status"] != 0:
+                return f"{st['status_name']}:{st['detail']}"
+        return "OK"
 
     def bytes_per_step(self, ctx: torch.Tensor) -> int:
         return _bytes_per_step(self.cfg, self.w, ctx, self.kh, self.batch)
@@ -282,7 +289,7 @@ def _bytes_per_step(cfg: Qwen3Config, w: Qwen3Weights, ctx: torch.Tensor, kv_hea
 
 def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world: int, ctx: torch.Tensor, extra_tokens: int,
                         seed: int = 0, kv_init: str = "normal", attn_chunk: int = 1024, attn_impl: str = "tc",
-                        collective: str = "rs_ag", fuse_norm: bool = False, attn_tail_order: bool = False):
+                        collective: str = "oneshot"):
     """Weights shard, KV pool sized for ``ctx`` (+ ``extra_tokens`` of growth per sequence), randomly permuted block
     table, and the decode engine for this rank. Every rank passes the same ``ctx`` and ``seed``."""
     batch = ctx.numel()
@@ -306,9 +313,7 @@ def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world
         table[i, :nb] = perm[o:o + nb]
         o += nb
     if world == 1:
-        eng = Qwen3Decoder(cfg, weights, pool, batch, max_ctx, attn_chunk, attn_impl, fuse_norm=fuse_norm, attn_tail_order=attn_tail_order)
+        eng = Qwen3Decoder(cfg, weights, pool, batch, max_ctx, attn_chunk, attn_impl)
     else:
-        assert not fuse_norm, "the norm-free step exists for the single-GPU engine (the tensor-parallel norm kernel is also the collective)"
-        eng = TPDecoder(cfg, weights, pool, batch, max_ctx, rank, world, attn_chunk, attn_impl=attn_impl, collective=collective,
-                        attn_tail_order=attn_tail_order)
+        eng = TPDecoder(cfg, weights, pool, batch, max_ctx, rank, world, attn_chunk, attn_impl=attn_impl, collective=collective)
     return eng, table

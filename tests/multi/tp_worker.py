@@ -1,9 +1,10 @@
 """Child process of tests/test_gpu_multi.py (one per GPU, started by torch.distributed.run).
 
-Checks, on 2+ GPUs: (1) the tensor-parallel decoder (fused all-gather->GEMM, GEMM->reduce-scatter,
-vocabulary-parallel argmax over peer memory) reproduces the single-GPU decoder step by step, eagerly and
-as a replayed CUDA graph; (2) a paged KV transfer from rank 0's token-major pool into rank 1's head-major
-pool through a peer mapping is bit-exact and sets the ready flag.
+Checks, on 2+ GPUs: (1) the tensor-parallel decoder (collectives fused into the GEMM and norm kernels over peer
+memory, vocabulary-parallel argmax) reproduces the single-GPU decoder step by step, eagerly and as a replayed
+CUDA graph, on a small configuration or (SKYGDR_TP_SHAPE=real) on two layers of the Qwen3-8B widths at 16 sequences
+per rank; (2) a paged KV transfer from rank 0's token-major pool into rank 1's head-major pool through a peer
+mapping is bit-exact and sets the ready flag. SKYGDR_TP_COLLECTIVE picks the collective form (oneshot / rs_ag).
 """
 import json
 import os
@@ -29,13 +30,18 @@ def main():
     report = {}
 
     # ---- (1) tensor-parallel decode vs single GPU ----
-    cfg = Qwen3Config.tiny(layers=3)
-    cfg.kv_heads, cfg.q_heads = 2 * world if world <= 2 else world, 4 * (2 * world if world <= 2 else world)
-    cfg.ffn = 128 * world * 2
-    cfg.vocab = 128 * world * 3 + 64          # not a multiple of 128 per rank: exercises the N tail
-    full_w = Qwen3Weights(cfg, dev, seed=3, std=0.05)
-    shard_w = Qwen3Weights(cfg, dev, seed=3, std=0.05, tp_rank=rank, tp_world=world)
-    rows = 3
+    real = os.environ.get("SKYGDR_TP_SHAPE", "small") == "real"
+    if real:
+        cfg = Qwen3Config(layers=2, vocab=1024 * world + 64, name="qwen3-8b-2L")      # hidden 4096, 32/8 heads, FFN 12288
+        std, rows = 0.02, 16
+    else:
+        cfg = Qwen3Config.tiny(layers=3)
+        cfg.kv_heads, cfg.q_heads = 2 * world if world <= 2 else world, 4 * (2 * world if world <= 2 else world)
+        cfg.ffn = 128 * world * 2
+        cfg.vocab = 128 * world * 3 + 64          # not a multiple of 128 per rank: exercises the N tail
+        std, rows = 0.05, 3
+    full_w = Qwen3Weights(cfg, dev, seed=3, std=std)
+    shard_w = Qwen3Weights(cfg, dev, seed=3, std=std, tp_rank=rank, tp_world=world)
     B = rows * world
     g = torch.Generator().manual_seed(5)
     ctx = torch.randint(1, 200, (B,), generator=g)
@@ -57,7 +63,8 @@ def main():
         o += nb
     ids = torch.randint(0, cfg.vocab, (B,), generator=g).int()
     full = Qwen3Decoder(cfg, full_w, full_pool, B, max_ctx, attn_chunk=64, attn_impl="simt")
-    collective = os.environ.get("SKYGDR_TP_COLLECTIVE", "rs_ag")          # "oneshot": the one-shot all-reduce form
+    collective = os.environ.get("SKYGDR_TP_COLLECTIVE", "oneshot")
+    tol = 0.02                        # relative to the largest logit: bf16 partial products summed in a different order
     tp = TPDecoder(cfg, shard_w, tp_pool, B, max_ctx, rank, world, attn_chunk=128, collective=collective)
     full.set_batch(ids.to(dev), ctx.int().to(dev), table.to(dev))
     tp.set_batch(ids.to(dev), ctx.int().to(dev), table.to(dev))
@@ -69,10 +76,10 @@ def main():
         lt = tp.logits.float()
         err = float((lf - lt).abs().max() / lf.abs().max())
         worst = max(worst, err)
-        assert err < 0.05, (step, err)
+        assert err < tol, (step, err)
         # near-ties may flip between the two reduction orders; the value picked must be (almost) the maximum
         picked = full.logits.float().gather(1, b.long()[:, None])[:, 0]
-        assert bool((picked >= full.logits.float().max(-1).values - 0.05 * lf.abs().max()).all()), step
+        assert bool((picked >= full.logits.float().max(-1).values - tol * lf.abs().max()).all()), step
         # feed both engines the same token so that they stay on one trajectory
         full.next_ids.copy_(a); tp.next_ids.copy_(a)
         full._advance(B); tp._advance(B)
@@ -89,10 +96,11 @@ def main():
         lf = full.logits[:, shard_w.vocab_lo:shard_w.vocab_hi].float()
         err = float((lf - tp.logits.float()).abs().max() / lf.abs().max())
         worst = max(worst, err)
-        assert err < 0.05, ("graph", step, err)
+        assert err < tol, ("graph", step, err)
         tp.ids.copy_(a)      # the graph advanced with its own pick; realign with the reference trajectory
     assert tp.check_status() == "OK", tp.check_status()
     report["tp_logit_rel_err"] = worst
+    report["collective"], report["shape"], report["world"] = collective, "real" if real else "small", world
 
     # ---- (2) paged KV transfer rank 0 -> rank 1 over a peer mapping ----
     geom = ops.KVGeometry(layers=4, kv_heads=8)

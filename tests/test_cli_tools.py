@@ -186,6 +186,55 @@ def test_policy_loop_program_end_to_end(tmp_path):
     assert "bg_control_mode" in open(tmp_path / "merged.csv").readline()
 
 
+@pytest.mark.realtime
+def test_controller_releases_the_background_flow_when_the_protected_flow_dies_mid_run(tmp_path):
+    """The protected flow writes a few progress rows, none of them done, and exits (a crash half way). The loop must not poll
+    on for ever: it sends HIGH, then STOP, to the background flow's control port, records the decision and returns 3."""
+    cport = free_port()
+    env = dict(ENV, SKYGDR_CTRL_PORT=str(cport), SKYGDR_CTRL_LOW_SLEEP_US="500", SKYGDR_CTRL_BIND_IP="127.0.0.1")
+    bg = subprocess.Popen([f"{BIN}/cpu_client", "-", "0", "sim:2", "100000000", "64K", "write", "1", "0", "64", "0", "random", "256", "1024",
+                           "1", "1000", "50"], stdout=subprocess.PIPE, text=True, env=env)
+    restore = tmp_path / "dying_restore.py"
+    restore.write_text(textwrap.dedent("""
+        import sys, time
+        hdr = "ts_unix_ms,elapsed_ms,issued_bytes,completed_bytes,remaining_bytes,window_bytes,inst_bw_gib_s,smooth_bw_gib_s,avg_bw_gib_s,done"
+        t0 = time.time()
+        with open(sys.argv[1], "w") as f:
+            f.write(hdr + "\\n"); f.flush()
+            for i in range(1, 21):
+                time.sleep(0.05)
+                f.write(f"{int(time.time()*1000)},{int((time.time()-t0)*1000)},{40*i},{40*i},{1000-40*i},40,5.0,5.0,5.0,0\\n"); f.flush()
+        sys.exit(7)
+    """))
+    metrics = tmp_path / "fake_metrics.py"
+    metrics.write_text(textwrap.dedent("""
+        import sys, time
+        with open(sys.argv[1], "w") as f:
+            f.write("ts_unix_ms,t_ms,pcie_tx_GiB_s,pcie_rx_GiB_s,pcie_tx_util_pct,pcie_rx_util_pct,pcie_tx_peak_util_pct,pcie_rx_peak_util_pct\\n")
+            t0 = time.time()
+            while time.time() - t0 < 10:
+                f.write(f"{int(time.time()*1000)},{(time.time()-t0)*1000:.1f},1,25,5,95,5,95\\n"); f.flush(); time.sleep(0.01)
+    """))
+    try:
+        wait_for_control("127.0.0.1", cport, 5.0)
+        r = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.controller", "--cpu_control_host", "127.0.0.1", "--cpu_control_port", str(cport),
+                            "--baseline_restore_gib_s", "20", "--log_dir", str(tmp_path), "--tag", "d", "--poll_ms", "20", "--warmup_ms", "50",
+                            "--restore_total_bytes", "1000", "--policy", "ladder",
+                            "--restore_cmd", f"{sys.executable} {restore} {{progress}}", "--metrics_cmd", f"{sys.executable} {metrics} {{metrics}}"],
+                           capture_output=True, text=True, env=ENV, timeout=30)
+        assert r.returncode == 3, (r.returncode, r.stderr)
+        out, _ = bg.communicate(timeout=10)
+    finally:
+        if bg.poll() is None:
+            bg.kill()
+    import csv
+
+    rows = list(csv.DictReader(open(tmp_path / "d_controller.csv")))
+    assert rows[-1]["decision"] == "RESTORE_DIED_STOP" and rows[-1]["restore_done"] == "0"
+    assert any(x["mode"].startswith("LOW") for x in rows)            # it had been throttling the background flow
+    assert "control_stop=1" in out                                   # ... and let go of it before leaving
+
+
 def test_controller_gives_up_when_the_end_point_is_unreachable(tmp_path):
     r = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.controller", "--cpu_control_host", "127.0.0.1", "--cpu_control_port", str(free_port()),
                         "--baseline_restore_gib_s", "20", "--log_dir", str(tmp_path), "--control_timeout_s", "1"],
@@ -523,40 +572,6 @@ def test_tools_accept_every_flag_of_the_reference_program(tool):
     assert r.returncode == 0, r.stderr[-500:]
     missing = [f for f in _REFERENCE_FLAGS[tool].split() if f not in r.stdout]
     assert not missing, (tool, missing)
-
-
-def test_decode_variants_driver_isolates_failures_and_resumes(tmp_path):
-    """benchmarks/decode_variants.py runs every variant as its own process; here bench.py is replaced by a stand-in that
-    succeeds for the default engine, crashes for one option and is never started for an option that does not apply."""
-    import json
-
-    fake = tmp_path / "fake_bench.py"
-    fake.write_text(textwrap.dedent("""
-        import json, sys
-        a = sys.argv[1:]
-        if "--attn-order" in a and a[a.index("--attn-order") + 1] == "tail":
-            sys.exit(3)                                   # this variant dies
-        v = 2100.0 if "--fuse-norm" in a else 2000.0
-        print("noise before the line")
-        print(json.dumps({"value": v, "ms_per_step": 16000 / v, "e2e": {"value": v - 10}, "kernel_status": "OK", "gpu_launches": 330,
-                          "roofline": {"hbm_frac_of_measured": 0.7}, "clocks": {"sm_mhz": 1965}}))
-    """))
-    out = tmp_path / "variants.json"
-    cmd = [sys.executable, os.path.join(ROOT, "benchmarks", "decode_variants.py"), "--variants", "default,fuse_norm,tail,oneshot",
-           "--bench-cmd", f"{sys.executable} {fake}", "--out", str(out)]
-    r = subprocess.run(cmd, capture_output=True, text=True, env=ENV, timeout=120)
-    assert r.returncode == 0, r.stderr
-    rows = json.load(open(out))["variants"]
-    assert rows["default"]["tok_s"] == 2000.0 and rows["fuse_norm"]["tok_s"] == 2100.0
-    assert rows["tail"]["error"] == "exit code 3" and rows["oneshot"]["skipped"] == "needs two or more GPUs"
-    assert "fuse_norm" in r.stdout and "1.050" in r.stdout                         # the table gives the ratio to the default engine
-    # resume: finished variants are kept, the failed one is tried again
-    fake.write_text(fake.read_text().replace("sys.exit(3)", "pass").replace("2000.0", "1.0"))
-    r = subprocess.run(cmd + ["--resume"], capture_output=True, text=True, env=ENV, timeout=120)
-    rows = json.load(open(out))["variants"]
-    assert rows["default"]["tok_s"] == 2000.0 and rows["tail"]["tok_s"] == 1.0
-    bad = subprocess.run(cmd[:3] + ["nonsense"], capture_output=True, text=True, env=ENV, timeout=60)
-    assert bad.returncode != 0 and "unknown variant" in bad.stderr
 
 
 @pytest.mark.realtime

@@ -224,8 +224,7 @@ def test_memhog_duty_cycle_and_time_limit(ops):
     assert 0.3 < half["bytes_done"] / full["bytes_done"] < 0.75
 
 
-# "tc-tail" (partial chunks scheduled last) and "tc-fine" (in quarter-chunk pieces) have not run on a GPU yet: opt in
-@pytest.mark.parametrize("impl", ["simt", "tc", "tcp"] + (["tc-tail", "tc-fine"] if os.environ.get("SKYGDR_TEST_ATTN_TAIL") == "1" else []))
+@pytest.mark.parametrize("impl", ["simt", "tc"])
 @pytest.mark.parametrize("kv_heads,q_heads", [(8, 32), (1, 4), (2, 4), (4, 4), (1, 8)])
 def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
     torch.manual_seed(1)
@@ -244,8 +243,7 @@ def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
         table[b, :nb] = perm[o:o + nb]
         o += nb
     q = torch.randn((B, q_heads, 128), dtype=torch.bfloat16, device="cuda")
-    attn = ops.PagedAttention("cuda", B, q_heads, kv_heads, max_ctx=4096, chunk_tokens=512, impl=impl.split("-")[0],
-                              tail_order={"tc-tail": True, "tc-fine": "fine"}.get(impl, False))
+    attn = ops.PagedAttention("cuda", B, q_heads, kv_heads, max_ctx=4096, chunk_tokens=512, impl=impl)
     for layer in (0, 1):
         out = attn(q, pool, layer, table, ctx, max_ctx=int(ctx.max()))
         ref = ops.paged_attn_reference(q, pool, layer, table, ctx)
@@ -256,15 +254,42 @@ def test_paged_attention_matches_reference(ops, kv_heads, q_heads, impl):
     assert int(attn.counters.abs().sum()) == 0
 
 
-# variants 2 (64-key steps) and 3-6 (exp2 on the FMA pipe, P in TMEM) have not run on a GPU yet: opt in one at a time
-_PREFILL_EXTRA = ([2] if os.environ.get("SKYGDR_TEST_PREFILL_64") == "1" else []) + \
-    [int(v) for v in os.environ.get("SKYGDR_TEST_PREFILL_VARIANTS", "").split(",") if v]
+@pytest.mark.parametrize("impl", ["simt", "tc"])
+def test_paged_attention_reports_lengths_and_block_ids_it_cannot_trust(ops, impl):
+    """A context length beyond max_ctx is cut to it and reported (the split count the combine waits for stays inside the
+    grid, so the self-resetting counters end at zero); a block id outside the pool is reported and never dereferenced."""
+    torch.manual_seed(3)
+    g = ops.KVGeometry(layers=1, kv_heads=2)
+    ctx = torch.tensor([300, 520, 77], dtype=torch.int32, device="cuda")
+    mb = (520 + 15) // 16
+    pool = ops.PagedKVPool(g, 3 * mb + 2, "hnd")
+    pool.data.normal_()
+    table = (torch.randperm(3 * mb, device="cuda") + 1).int().view(3, mb).contiguous()
+    q = torch.randn((3, 8, 128), dtype=torch.bfloat16, device="cuda")
+    ref = ops.paged_attn_reference(q, pool, 0, table, ctx)
+    attn = ops.PagedAttention("cuda", 3, 8, 2, max_ctx=520, chunk_tokens=256, impl=impl)
+    bad_ctx = ctx.clone()
+    bad_ctx[1] = 9000
+    out = attn(q, pool, 0, table, bad_ctx, max_ctx=520)
+    torch.cuda.synchronize()
+    st = ops.read_status(attn.status)
+    assert st["status_name"] == "BAD_INDEX" and st["detail"] == (0x40000000 | 1)
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2)
+    assert int(attn.counters.abs().sum()) == 0
+    if impl == "simt":                                      # the tensor-core kernel's loads are bounded by its tensor map instead
+        attn2 = ops.PagedAttention("cuda", 3, 8, 2, max_ctx=520, chunk_tokens=256, impl=impl)
+        bad_table = table.clone()
+        bad_table[2, 1] = 1 << 20
+        out = attn2(q, pool, 0, bad_table, ctx, max_ctx=520)
+        torch.cuda.synchronize()
+        st = ops.read_status(attn2.status)
+        assert st["status_name"] == "BAD_INDEX" and st["detail"] == ((2 << 16) | 1)
+        assert torch.allclose(out[:2].float(), ref[:2], atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("two_tiles", [True, False] + _PREFILL_EXTRA)
 @pytest.mark.parametrize("layout", ["hnd", "nhd"])
 @pytest.mark.parametrize("kv_heads,q_heads", [(8, 32), (2, 4), (1, 1)])
-def test_prefill_attention_matches_reference(ops, layout, kv_heads, q_heads, two_tiles):
+def test_prefill_attention_matches_reference(ops, layout, kv_heads, q_heads):
     """Causal attention of packed prompts read in place from the paged pool, against fp32 softmax attention in PyTorch.
     Lengths straddle the 128-token tile (1, 127, 128, 129), the page (16) and several key tiles (700)."""
     torch.manual_seed(4)
@@ -284,7 +309,7 @@ def test_prefill_attention_matches_reference(ops, layout, kv_heads, q_heads, two
     T = sum(lens)
     q = torch.randn((T, q_heads, 128), dtype=torch.bfloat16, device="cuda")
     seq_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32, device="cuda")
-    attn = ops.PrefillAttention("cuda", two_tiles=two_tiles)
+    attn = ops.PrefillAttention("cuda")
     for layer in (0, 1):
         out = attn(q, pool, layer, table, seq_start, max(lens))
         torch.cuda.synchronize()
@@ -292,37 +317,27 @@ def test_prefill_attention_matches_reference(ops, layout, kv_heads, q_heads, two
         ref = ops.prefill_attn_reference(q, pool, layer, table, lens)
         err = (out.float() - ref).abs().max()
         assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float(err)
-
-
-@pytest.mark.parametrize("chunk", [512, 1024])
-def test_persistent_attention_walks_many_items_per_cta(ops, chunk):
-    """More work items than CTAs (48 sequences x up to 5 splits x 8 KV heads against 296 CTAs): every CTA runs several items
-    back to back, so barrier phases, the K/V ring and the Q tile carry over item boundaries. Two launches in a row."""
-    torch.manual_seed(3)
-    g = ops.KVGeometry(layers=1, kv_heads=8)
-    ctx = torch.randint(1, 2400, (48,), dtype=torch.int32, device="cuda")
-    ctx[:4] = torch.tensor([1, 128, 129, 2399], dtype=torch.int32)
-    B = ctx.numel()
-    max_blocks = (2400 + 15) // 16 + 8
-    nblk = int(((ctx + 15) // 16).sum()) + 4
-    pool = ops.PagedKVPool(g, nblk, "hnd")
-    pool.data.normal_()
-    perm = torch.randperm(nblk, device="cuda").int()
-    table = torch.zeros((B, max_blocks), dtype=torch.int32, device="cuda")
+    # the next piece of every prompt: queries start pos0 tokens into the sequence (on and off the 128-token tile and the
+    # 16-token page) and attend to everything before them as well
+    pos0 = [1, 127, 128, 129, 300, 700, 16, 17, 256, 257, 385]
+    tails = [200, 1, 128, 130, 77, 260, 16, 300, 129, 5, 127]
+    table2 = torch.zeros((len(lens), ((max(p + t for p, t in zip(pos0, tails)) + 127) // 128) * 8 + 8), dtype=torch.int32, device="cuda")
+    nblk2 = sum((p + t + 15) // 16 for p, t in zip(pos0, tails)) + 3
+    pool2 = ops.PagedKVPool(g, nblk2, layout)
+    pool2.data.normal_()
+    perm2 = (torch.randperm(nblk2 - 1, device="cuda") + 1).int()
     o = 0
-    for b in range(B):
-        nb = (int(ctx[b]) + 15) // 16
-        table[b, :nb] = perm[o:o + nb]
+    for s_, (p_, t_) in enumerate(zip(pos0, tails)):
+        nb = (p_ + t_ + 15) // 16
+        table2[s_, :nb] = perm2[o:o + nb]
         o += nb
-    q = torch.randn((B, 32, 128), dtype=torch.bfloat16, device="cuda")
-    attn = ops.PagedAttention("cuda", B, 32, 8, max_ctx=2400, chunk_tokens=chunk, impl="tcp")
-    ref = ops.paged_attn_reference(q, pool, 0, table, ctx)
-    for _ in range(2):
-        out = attn(q, pool, 0, table, ctx)
-        torch.cuda.synchronize()
-        assert ops.read_status(attn.status)["status"] == 0
-        assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
-    assert int(attn.counters.abs().sum()) == 0
+    q2 = torch.randn((sum(tails), q_heads, 128), dtype=torch.bfloat16, device="cuda")
+    start2 = torch.tensor([0] + list(torch.tensor(tails).cumsum(0).tolist()), dtype=torch.int32, device="cuda")
+    out = attn(q2, pool2, 1, table2, start2, max(tails), pos0=torch.tensor(pos0, dtype=torch.int32, device="cuda"))
+    torch.cuda.synchronize()
+    assert ops.read_status(attn.status)["status"] == 0, ops.read_status(attn.status)
+    ref = ops.prefill_attn_reference(q2, pool2, 1, table2, tails, pos0=pos0)
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
 
 
 @pytest.mark.parametrize("M,N,K,splits", [(16, 256, 512, 1), (16, 6144, 4096, 4), (13, 384, 1024, 2), (64, 512, 4096, 1),
@@ -508,7 +523,6 @@ def test_cli_programs_run(ops):
     assert "Effective sequence-throughput:" in out and "Approx bandwidth:" in out
 
 
-@pytest.mark.skipif(os.environ.get("SKYGDR_TEST_GEMM_PERSISTENT") != "1", reason="the persistent GEMM has not run on a GPU yet: opt in")
 @pytest.mark.parametrize("M,N,K,gated,ntok", [(2048, 1024, 1024, False, 0), (300, 640, 512, False, 0), (1000, 200, 256, False, 128),
                                               (777, 384, 1024, True, 0), (40000, 256, 128, False, 0)])
 def test_persistent_gemm_matches_reference(ops, M, N, K, gated, ntok):
@@ -532,7 +546,6 @@ def test_persistent_gemm_matches_reference(ops, M, N, K, gated, ntok):
     assert (y.float() - y2.float()).abs().max() < 2e-2 * max(1.0, float(ref.abs().max()))
 
 
-@pytest.mark.skipif(os.environ.get("SKYGDR_TEST_SAMPLING") != "1", reason="the sampling kernel has not run on a GPU yet: opt in")
 def test_temperature_sampling_matches_the_cpu_restatement(ops):
     """Gumbel-max sampling: the kernel's pick must be the CPU oracle's pick (same hash, fp32 arithmetic), except where the two
     best perturbed values are within rounding of each other; positions change the draw, the seed changes the stream."""

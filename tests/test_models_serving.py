@@ -125,4 +125,4 @@ def test_batcher_drives_the_real_engine_class_with_stubbed_kernels(monkeypatch):
     out = b.run_until_idle(max_steps=50)
     assert {k: len(v) for k, v in out.items()} == {0: 3, 1: 6, 2: 2, 3: 4}
     assert b.alloc.free_blocks == b.alloc.capacity and b.idle()
-    assert sum(1 for c in calls if c == "prefill_attn") == 4 * cfg.layers   # one prefill per request
+    assert sum(1 for c in calls if c[0] == "prefill_attn") == 4 * cfg.layers   # one prefill per request

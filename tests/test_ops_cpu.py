@@ -126,68 +126,6 @@ def test_prefill_oracle_matches_torch_sdpa(layout):
         o += n
 
 
-def test_exp2_cubic_of_the_prefill_kernel_is_accurate_enough_for_bf16():
-    """The prefill kernel's opt-in exp2 on the FMA pipe (pf_exp2_poly in prefill_attn_tc.cu): the same arithmetic in fp32 on the
-    CPU, with the coefficients read from the kernel source, stays within 2e-4 of 2^x over the range the softmax feeds it."""
-    import pathlib
-    import re
-
-    src = (pathlib.Path(__file__).resolve().parent.parent / "skygdr_b200" / "csrc" / "kernels" / "prefill_attn_tc.cu").read_text()
-    body = src[src.index("float pf_exp2_poly(float x)"):]
-    body = body[:body.index("\n}\n")]
-    c3, c2, c1 = (float(v) for v in re.search(r"fmaf\(fmaf\(fmaf\(([0-9.]+)f, f, ([0-9.]+)f\), f, ([0-9.]+)f\), f, 1\.0f\)", body).groups())
-    assert "12582912.0f" in body and "<< 23" in body and "-126.0f" in body
-    x = torch.cat([torch.linspace(-126.0, 8.0, 200001), torch.tensor([-1e30, -float("inf"), 0.0, -0.0, 1.0, -1.0])]).float()
-    xc = x.clamp(min=-126.0)
-    fl = torch.floor(xc)                               # add.rm of 1.5 * 2^23, minus the same constant
-    f = xc - fl
-    pl = ((c3 * f + c2) * f + c1) * f + 1.0
-    got = (pl.view(torch.int32) + (fl.to(torch.int32) << 23)).view(torch.float32)
-    want = torch.exp2(xc.double())
-    rel = ((got.double() - want) / want).abs().max().item()
-    assert rel < 2e-4, rel
-    assert got[-6].item() == got[-5].item() == 2.0 ** -126      # masked scores: 1e-38, nothing in a bf16 row
-
-
-def test_folding_the_norm_gain_into_the_next_projection_keeps_the_function():
-    """What `Qwen3Weights.fold_norms` and the GEMM epilogue options rely on: rmsnorm(x) * g @ W.T equals
-    (x @ (W * g).T) * rsqrt(mean(x^2) + eps) row by row, up to bf16 rounding of the folded weight."""
-    torch.manual_seed(0)
-    M, K, N, eps = 16, 512, 256, 1e-6
-    x = torch.randn(M, K).bfloat16()
-    g = (1.0 + 0.1 * torch.randn(K)).bfloat16()
-    W = (0.02 * torch.randn(N, K)).bfloat16()
-    xf = x.float()
-    inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
-    ref = ((xf * inv * g.float()).bfloat16().float() @ W.float().T)
-    Wf = (W * g[None, :])                                   # what fold_norms does, in place and in bf16
-    fused = (xf @ Wf.float().T) * inv
-    err = (fused - ref).abs().max() / ref.abs().max()
-    assert err < 0.02, float(err)
-    # the gated form scales gate and up before the SiLU
-    Wg, Wu = (0.02 * torch.randn(N, K)).bfloat16(), (0.02 * torch.randn(N, K)).bfloat16()
-    xn = (xf * inv * g.float()).bfloat16().float()
-    ref_g = torch.nn.functional.silu(xn @ Wg.float().T) * (xn @ Wu.float().T)
-    a, b = (xf @ (Wg * g[None, :]).float().T) * inv, (xf @ (Wu * g[None, :]).float().T) * inv
-    err = (torch.nn.functional.silu(a) * b - ref_g).abs().max() / ref_g.abs().max()
-    assert err < 0.02, float(err)
-
-
-def test_fold_norms_on_cpu_weights_keeps_the_reference_logits():
-    from skygdr_b200.models import Qwen3Config, Qwen3Weights, reference_forward
-
-    cfg = Qwen3Config.tiny(layers=2)
-    w = Qwen3Weights(cfg, "cpu", seed=3, std=0.05)
-    ids = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(1))
-    before = reference_forward(cfg, w, ids)
-    w.fold_norms()
-    assert w.norms_folded and bool((w.layers[1].ln2 == 1).all()) and bool((w.final_norm == 1).all())
-    after = reference_forward(cfg, w, ids)
-    err = (after - before).abs().max() / before.abs().max()
-    assert err < 0.03, float(err)
-    assert w.fold_norms() is w                              # idempotent
-
-
 def test_library_send_recv_handoff_moves_paged_kv_between_two_ranks(tmp_path):
     """The comparison arm for the transfer kernel (gather + layout change, library send / recv, scatter) as two gloo
     ranks: the receiver must end up with head-major copies of exactly the sender's blocks, in its own block order."""
@@ -234,57 +172,6 @@ def test_tensor_parallel_shards_reproduce_the_unsharded_forward_on_cpu_ranks(wor
     d = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
     assert d["world"] == world and d["covered"] and d["argmax_agrees"] and d["clear_rows"] > 0
     assert d["rel_err_max"] < 0.03, d             # bf16 rounding of per-rank partial sums is the only difference
-
-
-def _decode_attention_items(ctx, chunk, grid_z, mode):
-    """The (split, tok0, tok1) of every grid slot z of one sequence, as paged_attn_tc_kernel computes them
-    (skygdr_b200/csrc/kernels/paged_attn_tc.cu), and the number of partials the combine waits for."""
-    items, n_splits = [], (ctx + chunk - 1) // chunk
-    if mode == 2:
-        small, n_full = chunk // 4, ctx // chunk
-        n_small = (ctx - n_full * chunk + small - 1) // small
-        n_splits = n_full + n_small
-        for z in range(grid_z):
-            j = z - (grid_z - 4)
-            if j < 0 and z < n_full:
-                items.append((z, z * chunk, z * chunk + chunk))
-            elif 0 <= j < n_small:
-                items.append((n_full + j, n_full * chunk + j * small, min(ctx, n_full * chunk + (j + 1) * small)))
-    else:
-        for z in range(grid_z):
-            if mode == 1:
-                if z < n_splits - 1:
-                    split = z
-                elif z == grid_z - 1:
-                    split = n_splits - 1
-                else:
-                    continue
-            else:
-                split = z
-            if split * chunk < ctx:
-                items.append((split, split * chunk, min(ctx, (split + 1) * chunk)))
-    return items, n_splits
-
-
-@pytest.mark.parametrize("mode", [0, 1, 2])
-def test_decode_attention_grid_orders_cover_every_token_once(mode):
-    """Default order, partial-chunk-last and quarter-chunk-pieces-last must all cut a sequence into the number of partials the
-    combine waits for, with distinct split indices below the scratch's max_splits and every token in exactly one piece."""
-    chunk, max_ctx = 1024, 16384 + 100
-    grid_z = max_ctx // chunk + 4 if mode == 2 else (max_ctx + chunk - 1) // chunk
-    max_splits = grid_z
-    longest_late = 0
-    for ctx in [1, 15, 127, 128, 129, 255, 256, 257, 1023, 1024, 1025, 1280, 1281, 2048, 2049, 3000, 5000, 16384, max_ctx]:
-        items, n_splits = _decode_attention_items(ctx, chunk, grid_z, mode)
-        assert len(items) == n_splits and sorted(i[0] for i in items) == list(range(n_splits)) and n_splits <= max_splits
-        covered = sorted((t0, t1) for _, t0, t1 in items)
-        assert covered[0][0] == 0 and covered[-1][1] == ctx and all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
-        assert all(t0 % 128 == 0 and 0 < t1 - t0 <= chunk for _, t0, t1 in items)        # whole key tiles, whole pages
-        if mode == 2:
-            late = [t1 - t0 for s, t0, t1 in items if s >= ctx // chunk]
-            longest_late = max([longest_late] + late)
-    if mode == 2:
-        assert longest_late == chunk // 4                                                # what runs last is at most a quarter chunk
 
 
 def _simulate_persistent_gemm_pipeline(n_my_tiles, nkb, stages, seed):
@@ -523,164 +410,6 @@ def test_tensor_parallel_counter_protocol_has_no_deadlock_and_no_overwrite(colle
         assert _simulate_tp_collectives(collective, world, layers=3, steps=3, seed=seed) > 0
 
 
-def _simulate_prefill_64key_pipeline(nkt0, nkt1, seed, units=3):
-    """The barrier protocol of the prefill attention variant with 64-key steps and double-buffered scores
-    (prefill_attn_tc3_kernel in skygdr_b200/csrc/kernels/prefill_attn_tc.cu) as a model: TMA producer over a ring of
-    `units` K/V tiles, one MMA issuer, one softmax warpgroup per query tile. nkt0 / nkt1 = 128-token key tiles of the two
-    query tiles (nkt1 = nkt0 + 1, or 0 when the second tile does not exist). Tensor-core work completes asynchronously and
-    in issue order (a commit covers everything issued before it); TMA loads complete asynchronously. Softmax decides at
-    random whether a step raises the running maximum (the branch that rescales the accumulator). Raises on any hazard:
-    scores or P overwritten before they were consumed, a ring unit reloaded while a pending MMA still needs it, an
-    accumulator rescaled while a P.V is in flight. Returns the number of softmax steps done per query tile."""
-    import random
-
-    rng = random.Random(seed)
-    nkt = [nkt0, nkt1]
-    n_kt = max(nkt)
-    steps_x = [2 * nkt0, 2 * nkt1]
-    names = [("full", s) for s in range(units)] + [("empty", s) for s in range(units)] + \
-            [(k, x, par) for k in ("s_ready", "p_ready", "o_done") for x in range(2) for par in range(2)]
-    phase = {n: 0 for n in names}
-    ring = [None] * units                      # unit index u held by the slot (None while a load is in flight)
-    unit_reads_left = {}                       # u -> MMAs that still have to finish reading it
-    S = [[None, None], [None, None]]           # S[x][par] = step whose scores the buffer holds
-    P = [[None, None], [None, None]]           # P[x][par] = step whose probabilities the buffer holds
-    pv_in_flight = [0, 0]
-    tc_fifo, tma_fifo = [], []                 # asynchronous completions, each in issue order
-    done_steps = [0, 0]
-
-    def passed(bar, parity):
-        return (phase[bar] & 1) != parity
-
-    def users(u):                              # how many MMAs read ring unit u: both 64-key halves for every tile that has key tile j
-        j = u >> 1
-        return 2 * sum(1 for x in range(2) if j < nkt[x])
-
-    def producer():
-        for u in range(2 * n_kt):
-            s = u % units
-            if u >= units:
-                while not passed(("empty", s), ((u // units) - 1) & 1):
-                    yield
-                old = ring[s]
-                assert old is not None and unit_reads_left[old] == 0, ("ring unit reloaded while still needed", old, unit_reads_left.get(old))
-            ring[s] = None
-            unit_reads_left[u] = users(u)
-
-            def land(s=s, u=u):
-                ring[s] = u
-                phase[("full", s)] += 1
-            tma_fifo.append(land)
-            yield
-
-    def mma():
-        def issue_s(x, t):
-            j, hb = t >> 1, t & 1
-            u = 2 * j
-            s = u % units
-            while not passed(("full", s), (u // units) & 1):
-                yield
-            assert ring[s] == u, ("score MMA on a unit that does not hold its K tile", x, t, ring[s])
-            assert S[x][t & 1] is None or S[x][t & 1] < 0, ("scores overwritten before softmax took them", x, t, S[x][t & 1])
-
-            def fin(x=x, t=t, s=s, u=u):
-                assert ring[s] == u, ("K tile replaced while its MMA was in flight", x, t)
-                unit_reads_left[u] -= 1
-                S[x][t & 1] = t
-            tc_fifo.append(fin)
-            if hb == 1 and (x == 1 or j >= nkt[1]):
-                tc_fifo.append(lambda s=s: phase.__setitem__(("empty", s), phase[("empty", s)] + 1))
-            tc_fifo.append(lambda x=x, t=t: phase.__setitem__(("s_ready", x, t & 1), phase[("s_ready", x, t & 1)] + 1))
-
-        def issue_pv(x, t):
-            j, hb = t >> 1, t & 1
-            while not passed(("p_ready", x, t & 1), (t >> 1) & 1):
-                yield
-            u = 2 * j + 1
-            s = u % units
-            while not passed(("full", s), (u // units) & 1):
-                yield
-            assert ring[s] == u and P[x][t & 1] == t, ("P.V without its operands", x, t, ring[s], P[x][t & 1])
-            pv_in_flight[x] += 1
-
-            def fin(x=x, t=t, s=s, u=u):
-                assert ring[s] == u and P[x][t & 1] == t, ("V tile or P replaced while the P.V was in flight", x, t)
-                unit_reads_left[u] -= 1
-                pv_in_flight[x] -= 1
-                P[x][t & 1] = -1 - t               # consumed
-            tc_fifo.append(fin)
-            if hb == 1 and (x == 1 or j >= nkt[1]):
-                tc_fifo.append(lambda s=s: phase.__setitem__(("empty", s), phase[("empty", s)] + 1))
-            tc_fifo.append(lambda x=x, t=t: phase.__setitem__(("o_done", x, t & 1), phase[("o_done", x, t & 1)] + 1))
-
-        for t in range(2):
-            for x in range(2):
-                if t < steps_x[x]:
-                    yield from issue_s(x, t)
-                    yield
-        for t in range(max(steps_x)):
-            for x in range(2):
-                if t >= steps_x[x]:
-                    continue
-                yield from issue_pv(x, t)
-                yield
-                if t + 2 < steps_x[x]:
-                    yield from issue_s(x, t + 2)
-                    yield
-
-    def softmax(x):
-        for t in range(steps_x[x]):
-            par = t & 1
-            while not passed(("s_ready", x, par), (t >> 1) & 1):
-                yield
-            assert S[x][par] == t, ("softmax read other scores than its step's", x, t, S[x][par])
-            S[x][par] = -1 - t                     # taken into registers
-            yield
-            if rng.random() < 0.4 and t > 0:       # the running maximum rises: rescale the accumulator
-                while not passed(("o_done", x, (t - 1) & 1), ((t - 1) >> 1) & 1):
-                    yield
-                assert pv_in_flight[x] == 0, ("accumulator rescaled while a P.V was in flight", x, t)
-            elif t > 1:
-                while not passed(("o_done", x, par), ((t - 2) >> 1) & 1):
-                    yield
-            assert P[x][par] is None or P[x][par] < 0, ("P overwritten before its P.V had read it", x, t, P[x][par])
-            P[x][par] = t
-            phase[("p_ready", x, par)] += 1
-            done_steps[x] += 1
-            yield
-        if steps_x[x] > 0:
-            tl = steps_x[x] - 1
-            while not passed(("o_done", x, tl & 1), (tl >> 1) & 1):
-                yield
-            assert pv_in_flight[x] == 0
-
-    live = [producer(), mma(), softmax(0), softmax(1)]
-    spins = 0
-    while live or tc_fifo or tma_fifo:
-        spins += 1
-        assert spins < 400000, "the pipeline stopped making progress"
-        pick = rng.random()
-        if tc_fifo and (pick < 0.3 or not live):
-            tc_fifo.pop(0)()
-        elif tma_fifo and (pick < 0.5 or not live):
-            tma_fifo.pop(0)()
-        elif live:
-            g = rng.choice(live)
-            try:
-                next(g)
-            except StopIteration:
-                live.remove(g)
-    return done_steps
-
-
-@pytest.mark.parametrize("nkt0,nkt1", [(1, 0), (1, 2), (2, 3), (3, 4), (5, 6), (9, 0), (8, 9)])
-def test_prefill_64key_pipeline_protocol(nkt0, nkt1):
-    """The 64-key-step prefill variant has twelve barriers with per-parity phases and a three-unit ring shared by two query
-    tiles of different length; this runs its protocol under many random interleavings (and random rescale decisions)."""
-    for seed in range(40):
-        assert _simulate_prefill_64key_pipeline(nkt0, nkt1, seed) == [2 * nkt0, 2 * nkt1]
-
-
 def test_gumbel_max_reference_samples_the_softmax():
     """The sampling rule restated on the CPU (hash -> uniform -> Gumbel noise -> argmax): over many positions the picked tokens
     follow softmax(logits / T), the same (seed, position) always picks the same token, and a low temperature approaches greedy."""
@@ -817,8 +546,8 @@ def _stub_kernels(monkeypatch, calls):
         def __init__(self, dev, *a, **k):
             pass
 
-        def __call__(self, q, pool, li, table, seq_start, max_len, out=None):
-            calls.append("prefill_attn")
+        def __call__(self, q, pool, li, table, seq_start, max_len, out=None, pos0=None):
+            calls.append(("prefill_attn", {"pos0": pos0.tolist(), "seq_start": seq_start.tolist(), "rows": table.shape[0], "max_len": max_len}))
             return out
 
     monkeypatch.setattr(ops, "PagedAttention", Attn)
@@ -829,9 +558,8 @@ def _stub_kernels(monkeypatch, calls):
 
 
 def test_decode_engine_issues_the_expected_kernel_sequence(monkeypatch):
-    """The decode engine's host side with the kernels stubbed out: the default step is embedding, eight kernels per layer, final
-    norm, lm_head, argmax; the norm-free step has six per layer and passes the row sums from producer to consumer; a positive
-    temperature swaps argmax for the sampling kernel keyed by the positions."""
+    """The decode engine's host side with the kernels stubbed out: a step is embedding, eight kernels per layer, final norm,
+    lm_head, argmax; a positive temperature swaps argmax for the sampling kernel keyed by the positions."""
     from skygdr_b200 import ops
     from skygdr_b200.models import Qwen3Config, Qwen3Decoder, Qwen3Weights
 
@@ -853,24 +581,11 @@ def test_decode_engine_issues_the_expected_kernel_sequence(monkeypatch):
     eng.step(max_ctx=64)
     assert calls[-1][0] == "sample" and calls[-1][1] == {"positions": "tensor"}
 
-    calls.clear()
-    fused = Qwen3Decoder(cfg, Qwen3Weights(cfg, "cpu", seed=0), pool, max_batch=2, max_ctx=64, attn_chunk=64, fuse_norm=True)
-    assert fused.w.norms_folded and fused.row_ss.shape == (2 * cfg.layers + 1, 2)
-    fused.set_batch(torch.tensor([1, 2], dtype=torch.int32), torch.tensor([3, 4], dtype=torch.int32), torch.zeros((2, 4), dtype=torch.int32))
-    fused.step(max_ctx=64)
-    names = [c if isinstance(c, str) else c[0] for c in calls]
-    assert names == ["embedding"] + ["gemm", "rope_append", "attn", "gemm", "gemm", "gemm"] * 2 + ["gemm", "argmax"]
-    assert len(names) == fused.kernels_per_step
-    gemms = [c[1] for c in calls if not isinstance(c, str) and c[0] == "gemm"]
-    # consumer, producer, consumer (gated), producer per layer, then the lm_head as a consumer
-    assert ["ss_in" in g for g in gemms] == [True, False, True, False] * 2 + [True]
-    assert [bool(g.get("residual")) and "ss_out" in g for g in gemms] == [False, True, False, True] * 2 + [False]
-
 
 def test_prefill_issues_the_expected_kernel_sequence(monkeypatch):
     """The prefill path's host side with the kernels stubbed out: per layer norm, QKV, RoPE + append, the prefill attention
-    kernel, O, norm, gate/up, down; logits only for each prompt's last token; the persistent GEMM only when asked for and only
-    above 256 tokens."""
+    kernel, O, norm, gate/up, down; logits only for each prompt's last token. With a chunk smaller than the prompts the stack
+    runs once per pass, and a prompt that continues in a later pass tells the attention kernel how many tokens precede it."""
     from skygdr_b200 import ops
     from skygdr_b200.models import Qwen3Config, Qwen3Decoder, Qwen3Weights
 
@@ -886,13 +601,19 @@ def test_prefill_issues_the_expected_kernel_sequence(monkeypatch):
     names = [c if isinstance(c, str) else c[0] for c in calls]
     layer = ["rmsnorm", "gemm", "rope_append", "prefill_attn", "gemm", "rmsnorm", "gemm", "gemm"]
     assert names == ["embedding"] + layer * 2 + ["rmsnorm", "gemm"]
-    assert not any(c[1].get("persistent") for c in calls if not isinstance(c, str))
-    for persistent, n_tokens, want in ((True, 300, True), (True, 200, False), (False, 300, False)):
-        calls.clear()
-        eng.prefill_gemm_persistent = persistent
-        eng.prefill(torch.randint(0, cfg.vocab, (n_tokens,)), [n_tokens], table[:1])
-        flags = [bool(c[1].get("persistent")) for c in calls if not isinstance(c, str) and c[0] == "gemm"]
-        assert flags == [want] * 8 + [False], (persistent, n_tokens, flags)       # the lm_head over one row per prompt stays as it is
+    assert [c[1] for c in calls if c[0] == "prefill_attn"][0] == {"pos0": [0, 0], "seq_start": [0, 20, 29], "rows": 2, "max_len": 20}
+    # the plan: passes of at most `chunk` tokens, a sequence at most once per pass, pieces in order
+    assert Qwen3Decoder.prefill_plan([20, 9], 16) == [[(0, 0, 16)], [(0, 16, 20), (1, 0, 9)]]
+    assert Qwen3Decoder.prefill_plan([5, 40, 3], 16) == [[(0, 0, 5), (1, 0, 11)], [(1, 11, 27)], [(1, 27, 40), (2, 0, 3)]]
+    assert Qwen3Decoder.prefill_plan([8], 8) == [[(0, 0, 8)]]
+    calls.clear()
+    logits = eng.prefill(torch.randint(0, cfg.vocab, (sum(seq_lens),)), seq_lens, table, chunk=16)
+    assert logits.shape == (2, cfg.vocab)
+    names = [c if isinstance(c, str) else c[0] for c in calls]
+    assert names == (["embedding"] + layer * 2) * 2 + ["rmsnorm", "gemm"]               # two passes through the stack, one lm_head
+    attn = [c[1] for c in calls if c[0] == "prefill_attn"]
+    assert attn[0] == {"pos0": [0], "seq_start": [0, 16], "rows": 1, "max_len": 16}
+    assert attn[2] == {"pos0": [16, 0], "seq_start": [0, 4, 13], "rows": 2, "max_len": 9}
 
 
 class _FakeHeap:
@@ -984,9 +705,10 @@ def test_tensor_parallel_engine_issues_the_expected_kernel_sequence(monkeypatch,
         assert all(n[2].get("rs_world") == world for n in norms) and all(n[1][6] == [0] for n in norms)   # local destination, no arrival
 
 
-def test_paged_attention_wrapper_sizes_scratch_and_passes_the_grid_order(monkeypatch):
-    """The Python face of the decode attention with the launch stubbed out: scratch sizes for the three grid orders and exactly
-    which keyword arguments reach the extension (none of the optional ones in the default configuration)."""
+def test_paged_attention_wrapper_sizes_scratch_and_passes_the_bounds(monkeypatch):
+    """The Python face of the decode attention with the launch stubbed out: scratch sizes, and what reaches the extension: the
+    max_ctx of the call cut to what the engine and the block-table row cover, the tensor map's row count for the tensor-core
+    kernel, and the pool's block count that the CUDA-core kernel checks block ids against."""
     import sys
 
     from skygdr_b200 import ops
@@ -1002,28 +724,28 @@ def test_paged_attention_wrapper_sizes_scratch_and_passes_the_grid_order(monkeyp
 
     pool = ops.PagedKVPool(ops.KVGeometry(layers=2, kv_heads=2), 8, "hnd", device="cpu")
     q = torch.zeros((3, 4, 128), dtype=torch.bfloat16)
-    table, ctx = torch.zeros((3, 4), dtype=torch.int32), torch.tensor([5, 40, 64], dtype=torch.int32)
-    for order, want_kw, want_splits in ((False, {}, 5), (True, {"tail_order": 1}, 5), ("fine", {"tail_order": 2}, 8)):
-        a = ops.PagedAttention("cpu", 3, 4, 2, max_ctx=2300, chunk_tokens=512, impl="tc", tail_order=order)
-        a._C = C
-        assert a.max_splits == want_splits and a.part_o.shape == (3, 4, want_splits, 128) and a.part_m.shape == (3, 4, want_splits)
-        out = a(q, pool, 1, table, ctx, max_ctx=100)
-        assert out.shape == q.shape and seen["kw"] == want_kw
-        assert seen["args"][9] == 100 and seen["args"][10] == 512                  # max_ctx of this call, chunk size
-        assert seen["args"][-1] == (pool.data.numel() - 1 * pool.strides[1]) // 128     # rows from this layer's first page to the end
+    table, ctx = torch.zeros((3, 8), dtype=torch.int32), torch.tensor([5, 40, 64], dtype=torch.int32)
+    a = ops.PagedAttention("cpu", 3, 4, 2, max_ctx=2300, chunk_tokens=512, impl="tc")
+    a._C = C
+    assert a.max_splits == 5 and a.part_o.shape == (3, 4, 5, 128) and a.part_m.shape == (3, 4, 5)
+    out = a(q, pool, 1, table, ctx, max_ctx=100)
+    assert out.shape == q.shape and seen["kw"] == {"num_blocks": 8}
+    assert seen["args"][9] == 100 and seen["args"][10] == 512                  # max_ctx of this call, chunk size
+    assert seen["args"][-1] == (pool.data.numel() - 1 * pool.strides[1]) // 128     # rows from this layer's first page to the end
+    a(q, pool, 1, table, ctx, max_ctx=1000)
+    assert seen["args"][9] == 8 * 16                                           # a table row of 8 blocks covers 128 tokens, no more
     simt = ops.PagedAttention("cpu", 3, 4, 2, max_ctx=2300, chunk_tokens=500, impl="simt")
     simt._C = C
-    simt(q, pool, 0, table, ctx)
-    assert seen["kw"] == {} and seen["args"][-1] == 0 and seen["args"][9] == 2300
+    simt(q, pool, 0, torch.zeros((3, 200), dtype=torch.int32), ctx)
+    assert seen["kw"] == {"num_blocks": 8} and seen["args"][-1] == 0 and seen["args"][9] == 2300
     with pytest.raises(AssertionError):
-        ops.PagedAttention("cpu", 3, 4, 2, max_ctx=2300, chunk_tokens=384, impl="tc", tail_order="fine")     # needs chunk % 512 == 0
-    with pytest.raises(AssertionError):
-        ops.PagedAttention("cpu", 3, 4, 2, max_ctx=2300, chunk_tokens=512, impl="simt", tail_order=True)
+        ops.PagedAttention("cpu", 3, 4, 2, max_ctx=2300, chunk_tokens=500, impl="tc")       # whole key tiles of 128 tokens
 
 
 def test_gemm_wrapper_argument_order_matches_the_extension(monkeypatch):
-    """ops.gemm with the launch stubbed out: which positional arguments reach the extension for the plain, split-K, folded-norm
-    and persistent forms. The binding's own signature is read from the built module, so a mismatch in count shows here."""
+    """ops.gemm with the launch stubbed out: which positional arguments reach the extension for the plain, split-K and persistent
+    forms, and that many-token shapes take the persistent form on their own. The binding's own signature is read from the built
+    module, so a mismatch in count shows here."""
     import sys
 
     import skygdr_b200.ops  # noqa: F401  (makes sure the submodule is loaded; its name in the package is shadowed by the function)
@@ -1034,8 +756,8 @@ def test_gemm_wrapper_argument_order_matches_the_extension(monkeypatch):
     monkeypatch.setattr(g, "_sms", lambda dev: 148)
     g._WS.clear()
     sig = load().gemm.__doc__
-    names = ["x", "w", "y", "splits", "gated", "workspace", "counters", "status", "ntok", "ss_in", "eps", "residual", "ss_out", "persistent"]
-    assert all(f"{n}:" in sig for n in names) and [sig.index(f"{a}:") < sig.index(f"{b}:") for a, b in zip(names, names[1:])] == [True] * 13
+    names = ["x", "w", "y", "splits", "gated", "workspace", "counters", "status", "ntok", "persistent"]
+    assert all(f"{n}:" in sig for n in names) and [sig.index(f"{a}:") < sig.index(f"{b}:") for a, b in zip(names, names[1:])] == [True] * 9
     seen = []
 
     class C:
@@ -1047,21 +769,20 @@ def test_gemm_wrapper_argument_order_matches_the_extension(monkeypatch):
     x, w = torch.zeros((16, 1024), dtype=torch.bfloat16), torch.zeros((512, 1024), dtype=torch.bfloat16)
     y = g.gemm(x, w)
     a = seen[-1]
-    assert y.shape == (16, 512) and len(a) == 13 and a[3] >= 1 and a[4] is False and a[9] is None and a[11] is False
+    assert y.shape == (16, 512) and len(a) == 9 and a[3] >= 1 and a[4] is False
     g.gemm(x, w, splits=4, ntok=16)
     a = seen[-1]
     assert a[3] == 4 and a[5] is not None and a[6] is not None and a[8] == 16
-    ss = torch.zeros(16)
-    g.gemm(x, w, splits=1, ss_in=ss, eps=1e-5)
-    assert seen[-1][9] is ss and seen[-1][10] == 1e-5
-    g.gemm(x, torch.zeros((1024, 1024), dtype=torch.bfloat16), out=torch.zeros((16, 1024), dtype=torch.bfloat16), splits=1, residual=True, ss_out=ss)
-    assert seen[-1][11] is True and seen[-1][12] is ss
     big = torch.zeros((700, 1024), dtype=torch.bfloat16)
-    g.gemm(big, w, persistent=True)
+    g.gemm(big, w)                                                             # more than 256 tokens: persistent on its own
     a = seen[-1]
-    assert len(a) == 14 and a[3] == 1 and a[8] == 256 and a[13] is True
-    g.gemm(big, torch.zeros((1024, 1024), dtype=torch.bfloat16), gated=True, persistent=True)
-    assert seen[-1][8] == 128 and seen[-1][4] is True
+    assert len(a) == 10 and a[3] == 1 and a[8] == 256 and a[9] is True
+    g.gemm(big, torch.zeros((1024, 1024), dtype=torch.bfloat16), gated=True)
+    assert seen[-1][8] == 128 and seen[-1][4] is True and seen[-1][9] is True
+    g.gemm(big, w, persistent=False)                                           # the comparison form: one tile per CTA
+    assert len(seen[-1]) == 9 and seen[-1][3] == 1
+    g.gemm(x, w, persistent=None)
+    assert len(seen[-1]) == 9                                                  # few tokens: never persistent by default
     g._WS.clear()
 
 
@@ -1070,9 +791,9 @@ def test_bindings_expose_the_keywords_the_python_side_uses():
     from skygdr_b200._ext import load
 
     C = load()
-    for fn, words in {"paged_attn_decode": ["persistent_ctas:", "tail_order:", "pool_rows:"],
-                      "embedding": ["row_ss:"], "sample": ["temperature:", "seed:", "positions:"],
-                      "gemm": ["persistent: bool = False", "ss_in:", "ss_out:", "residual: bool = False"],
+    for fn, words in {"paged_attn_decode": ["num_blocks:", "pool_rows:"],
+                      "prefill_attn": ["pos0:"], "sample": ["temperature:", "seed:", "positions:"],
+                      "gemm": ["persistent: bool = False"],
                       "tp_norm": ["rs_world:"]}.items():
         doc = getattr(C, fn).__doc__
         assert all(w in doc for w in words), (fn, doc)
@@ -1088,14 +809,14 @@ def test_build_decode_engine_lays_out_pool_and_tables(monkeypatch):
     _stub_kernels(monkeypatch, calls)
     cfg = Qwen3Config.tiny(layers=2)
     ctx = torch.tensor([40, 7, 130, 64])
-    eng, table = build_decode_engine(cfg, torch.device("cpu"), 0, 1, ctx, extra_tokens=20, seed=1, attn_chunk=512, attn_tail_order="fine")
+    eng, table = build_decode_engine(cfg, torch.device("cpu"), 0, 1, ctx, extra_tokens=20, seed=1, attn_chunk=512)
     need = [(int(c) + 20 + 15) // 16 for c in ctx]
     used = [table[i, :need[i]].tolist() for i in range(4)]
     flat = [b for row in used for b in row]
     assert len(flat) == len(set(flat)) and 0 not in flat and max(flat) < eng.pool.num_blocks == sum(need) + 1
     assert all(int(table[i, need[i]:].abs().sum()) == 0 for i in range(4))
     assert eng.max_ctx == 130 + 20 + 1 and table.shape == (4, eng.max_blocks) and eng.max_batch == 4
-    assert eng.attn.kw["tail_order"] == "fine" and eng.attn.kw["impl"] == "tc"
+    assert eng.attn.kw["impl"] == "tc"
     assert float(eng.pool.data.float().std()) > 0.5                      # N(0, 1) cache contents, as the benchmark states
     eng.set_batch(torch.zeros(4, dtype=torch.int32), ctx.int(), table)
     eng.step()

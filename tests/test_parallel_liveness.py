@@ -77,3 +77,33 @@ def test_a_rank_that_never_starts_is_reported_missing_instead_of_waited_for():
         rc, out, err = res[r]
         assert rc == 0 and out is not None, err
         assert out["seen"]["missing"] == [1] and out["steps"] == 0, out
+
+
+def test_a_store_that_stops_answering_is_reported_as_its_host_rank_gone():
+    """When the process that serves the store dies, every call on the store raises (connection reset, broken pipe). The watch
+    turns that into a named rank: the store's host as seen from the others, everybody as seen from the host itself."""
+    from skygdr_b200.parallel.liveness import PeerLost, RankWatch
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    store = dist.TCPStore("127.0.0.1", port, is_master=True, wait_for_workers=False, timeout=datetime.timedelta(seconds=5))
+
+    class Gone:
+        def check(self, keys):
+            raise RuntimeError("Connection reset by peer")
+
+        get = set = check
+
+    w = RankWatch(1, 3, store=store, beat_s=0.05, stale_after_s=0.5, name="gone")
+    w.store = Gone()
+    h = w.check()
+    assert h.stale == [0] and not h.left and not h.missing
+    with pytest.raises(PeerLost) as e:
+        w.guard()
+    assert e.value.health.stale == [0]
+    w2 = RankWatch(2, 3, store=store, name="gone2", store_host_rank=2)        # the host itself cannot read its own store any more
+    w2.store = Gone()
+    assert w2.check().stale == [0, 1]
+    w2.leave("x")                                                              # writing the marker fails quietly
+    del store
