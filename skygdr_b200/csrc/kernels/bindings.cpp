@@ -16,6 +16,7 @@
 #include "multicast.h"
 #include "paged_attn.h"
 #include "pcie_task.h"
+#include "peer_store_probe.h"
 #include "prefill_attn.h"
 #include "tp_fused.h"
 
@@ -150,6 +151,26 @@ static torch::Tensor tensor_from_ptr(uint64_t ptr, std::vector<int64_t> shape, p
     return torch::from_blob((void*)ptr, shape, torch::TensorOptions().dtype(st).device(torch::kCUDA, device));
 }
 // Single-process multi-GPU (tests): lets `device` reach `peer`'s memory.
+// Store-only probe of the SM write path: launches on `device` (its current stream), writes to `dst_ptr` (a peer pointer or a
+// multicast address), returns the device time of the launch in milliseconds (CUDA events around it).
+static double peer_store_probe(int device, uint64_t dst_ptr, uint64_t total_bytes, int mode, int store_bytes, int inflight, int ctas, int iters) {
+    c10::cuda::CUDAGuard g(c10::Device(c10::kCUDA, (c10::DeviceIndex)device));
+    cudaStream_t s = cur_stream();
+    cudaEvent_t e0, e1;
+    SKY_CUDA_CHECK(cudaEventCreate(&e0));
+    SKY_CUDA_CHECK(cudaEventCreate(&e1));
+    SKY_CUDA_CHECK(cudaEventRecord(e0, s));
+    cudaError_t err = launch_peer_store_probe((void*)dst_ptr, total_bytes, mode, (unsigned)store_bytes, inflight, ctas, iters, s);
+    cudaEventRecord(e1, s);
+    cudaEventSynchronize(e1);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    SKY_CUDA_CHECK(err);
+    return (double)ms;
+}
+
 static bool enable_peer_access(int device, int peer) {
     int can = 0;
     SKY_CUDA_CHECK(cudaDeviceCanAccessPeer(&can, device, peer));
@@ -470,6 +491,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("ipc_free", &ipc_free);
     m.def("tensor_from_ptr", &tensor_from_ptr);
     m.def("enable_peer_access", &enable_peer_access);
+    m.def("peer_store_probe", &peer_store_probe, py::arg("device"), py::arg("dst_ptr"), py::arg("total_bytes"), py::arg("mode"),
+          py::arg("store_bytes") = 32768, py::arg("inflight") = 4, py::arg("ctas") = 148, py::arg("iters") = 1,
+          py::call_guard<py::gil_scoped_release>());
     m.def("kv_transfer", &kv_transfer, py::call_guard<py::gil_scoped_release>(), py::arg("src_pool"), py::arg("dst_ptrs"),
           py::arg("dst_scale_ptrs"), py::arg("done_flag_ptrs"), py::arg("src_blocks"), py::arg("dst_blocks"), py::arg("layers"),
           py::arg("heads"), py::arg("block_tokens"), py::arg("head_dim"), py::arg("src_strides"), py::arg("dst_strides"),

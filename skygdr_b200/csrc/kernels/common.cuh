@@ -72,12 +72,14 @@ __device__ __forceinline__ void st_cs_v4(void* p, uint4 v) {
 
 // Waits until *flag >= want (acquire, system scope) or `timeout_ns` passes.
 __device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned int want, unsigned long long timeout_ns) {
-    // poll relaxed, then one acquire fence: an acquire per poll would fence every iteration
-    if ((int)(ld_sys_u32(flag) - want) >= 0) { __threadfence_system(); return true; }
+    // Poll relaxed; once the value is there, read it once more with acquire semantics. That load is what orders the reads
+    // that follow behind the producer's release, and unlike a system-scope fence it does not have to wait for this SM's own
+    // outstanding writes.
+    if ((int)(ld_sys_u32(flag) - want) >= 0) return (int)(ld_acquire_sys_u32(flag) - want) >= 0;
     unsigned long long t0 = globaltimer_ns();
     unsigned ns = 32;
     for (;;) {
-        if ((int)(ld_sys_u32(flag) - want) >= 0) { __threadfence_system(); return true; }
+        if ((int)(ld_sys_u32(flag) - want) >= 0) return (int)(ld_acquire_sys_u32(flag) - want) >= 0;
         if (globaltimer_ns() - t0 > timeout_ns) return false;
         __nanosleep(ns);
         if (ns < 256) ns <<= 1;
@@ -106,6 +108,8 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 // cached in *cache so that an unpaced or generously paced flow touches host
 // memory only once in a while. Returns false when the deadline passed or the
 // page's stop flag is set (then *stopped tells which).
+constexpr unsigned long long SKY_UNLIMITED_RECHECK_BYTES = 256ull << 20;
+
 __device__ __forceinline__ bool credit_acquire(const SkyCreditPage* page, unsigned long long need,
                                                unsigned long long* cache, unsigned long long max_wait_ns,
                                                unsigned long long* stall_ns, bool* stopped, bool* control_lost = nullptr) {
@@ -125,7 +129,10 @@ __device__ __forceinline__ bool credit_acquire(const SkyCreditPage* page, unsign
     if (dead) t_dead = ld_sys_u64((const unsigned long long*)&page->heartbeat_lost_ns);
     for (;;) {
         if (ld_sys_u32(&page->stop)) { *stopped = true; *stall_ns += globaltimer_ns() - t0; return false; }
-        if (ld_sys_u32(&page->unlimited)) { *cache = ~0ull; break; }
+        // "unlimited" is not cached for the rest of the launch: the control side may start pacing this flow at any window, and a
+        // launch can last many windows. The page is read again after SKY_UNLIMITED_RECHECK_BYTES more of the flow's bytes
+        // (a fraction of a millisecond at link rate), which costs an unpaced flow one host-memory read per few chunks per CTA.
+        if (ld_sys_u32(&page->unlimited)) { *cache = need + SKY_UNLIMITED_RECHECK_BYTES; break; }
         unsigned long long g = ld_sys_u64((const unsigned long long*)&page->granted_bytes);
         *cache = g;
         if (need <= g) break;

@@ -563,3 +563,52 @@ def test_temperature_sampling_matches_the_cpu_restatement(ops):
     assert not torch.equal(ops.sample(logits, 0.7, seed=100, positions=pos).cpu(), got)
     greedy = ops.argmax(logits).cpu()
     assert float((ops.sample(logits, 1e-3, seed=1, positions=pos).cpu() == greedy).float().mean()) > 0.95
+
+
+def test_kernel_is_paced_by_the_daemon_process_through_the_page_it_owns(ops):
+    """The product's minimum slice on one GPU: a `fabricd` process owns the credit page (a file under /dev/shm), a flow registers
+    over TCP, maps that page into the device's address space (CreditPage.attach) and launches the paged transfer kernel, which
+    reads the daemon's grants chunk by chunk. Under the `static` policy a best-effort flow gets half of its link's capacity:
+    the kernel runs out of credit, yields, is relaunched from its cursor, and ends up moving its bytes at the granted rate,
+    bit-exact. Unpaced (policy none), the same transfer is many times faster."""
+    import struct
+    import time
+
+    from skygdr_b200.control import FabricClient, FabricDaemon
+
+    geom = ops.KVGeometry(layers=8, kv_heads=8)
+    nb = 256                                                   # 256 blocks x 512 KiB = 134 MB
+    src = ops.PagedKVPool(geom, nb, "nhd")
+    src.data.normal_()
+    dst = ops.PagedKVPool(geom, nb, "hnd")
+    g = torch.Generator().manual_seed(2)
+    sb = torch.randperm(nb, generator=g).int().cuda()
+    db = torch.randperm(nb, generator=g).int().cuda()
+    total = ops.link_bytes(geom, nb)
+    rates = {}
+    for policy, cap in (("static", 8.0), ("none", 8.0)):       # static: LOW1 = half of the 8 GB/s link = 4 GB/s
+        with FabricDaemon(policy=policy, window_us=1000, lease_ms=60000, extra=["--link", f"test={cap}"]) as d, FabricClient(port=d.port) as c:
+            h = c.register("kv_bulk", 0, 0.0, kind="kv_offload", link="test")
+            assert h.page_path and h.page_path.startswith("/dev/shm/")
+            page = ops.CreditPage.attach(h.page_path)
+            try:
+                struct.pack_into("<Q", h._mm, 128 + 56, total)          # backlog: the flow has this much to send
+                flow = ops.KvTransferFlow("cuda", page=page, max_wait_ms=2.0)
+                dst.data.zero_()
+                t0 = time.perf_counter()
+                st = flow.transfer_to_completion(src, [ops.RemotePool.of(dst)], sb, db)
+                dt = time.perf_counter() - t0
+                assert st["status"] == 0 and st["bytes_done"] == total, st
+                assert torch.equal(dst.data[db.long()], ops.reference_transfer(src, sb))
+                rates[policy] = (total / dt / 1e9, st["launches"])
+                usage = h.usage()
+                assert usage["completed_bytes"] >= total                # the kernel wrote its progress into the daemon's page
+                if policy == "static":
+                    assert h.grant()["unlimited"] == 0 and h.grant()["granted_bytes"] >= total
+            finally:
+                page.close()
+                c.unregister(h)
+    paced, launches = rates["static"]
+    assert 2.5 < paced < 5.0, rates                            # 4 GB/s granted; start-up and relaunch gaps cost a little
+    assert launches > 3, rates                                 # it yielded and resumed
+    assert rates["none"][0] > 10 * paced, rates
