@@ -15,14 +15,17 @@ rank i % D, in one of that rank's KV slots. Per request:
           -> decode rank sees the flag (acquire) and adds the sequence to its running batch -> first decode step = TTFT
 
 Arms (the reference's three: src/tools/pcie_case_study_analyze.py:140-154): `always_high` = offload unpaced;
-`always_low` = offload statically throttled to a quarter of its offered rate; `controlled` = the C++ control core
-(`target_track`, 2 ms windows) on every prefill rank cuts the offload's byte grants while a hand-off is in flight and
-releases them afterwards. Reported per arm: kv_transfer flow time p50/p99 (prefill done -> last byte visible), mean TTFT,
+`always_low` = offload statically throttled to a quarter of its offered rate; `controlled` = `target_track` with 2 ms windows
+cuts the offload's byte grants while a hand-off is in flight and releases them afterwards. The control side of the controlled
+arm is a `fabricd` process (`--daemon`, the default): rank 0 starts it, every prefill rank registers its two flows over TCP on
+a link of its own (`gpu<r>`), maps the pages the daemon created under /dev/shm, and its transfer kernel and offload worker
+read the daemon's grants from there. `--no-daemon` keeps the control core inside each prefill rank's process instead. Reported per arm: kv_transfer flow time p50/p99 (prefill done -> last byte visible), mean TTFT,
 decode tokens/s, offload GB/s. Times across ranks use one wall clock (single node); transfer times are also device-timed.
 """
 import argparse
 import json
 import os
+import struct
 import sys
 import threading
 import time
@@ -38,6 +41,11 @@ from skygdr_b200.cli.common import env_info  # noqa: E402
 from skygdr_b200.control import ctl  # noqa: E402
 from skygdr_b200.models import Qwen3Config, Qwen3Decoder, Qwen3Weights  # noqa: E402
 from skygdr_b200.parallel.symm import SymmetricHeap  # noqa: E402
+
+
+def set_backlog(handle, n):
+    """Writes a flow's backlog into the usage half of its credit page (SkyCreditPage.backlog_bytes, csrc/ctl/credit_page.h)."""
+    struct.pack_into("<Q", handle._mm, 128 + 56, int(n))
 
 
 def make_requests(a, P, D):
@@ -72,6 +80,8 @@ def main():
     ap.add_argument("--slots", type=int, default=8)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--out", default="results/config4.json")
+    ap.add_argument("--daemon", dest="daemon", action="store_true", default=True)
+    ap.add_argument("--no-daemon", dest="daemon", action="store_false")
     a = ap.parse_args()
     C = load()
     world, rank, local = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
@@ -96,6 +106,17 @@ def main():
     dist.barrier()
     weights = Qwen3Weights(cfg, dev, seed=1)
     result = {}
+    daemon = None
+    if a.arm == "controlled" and a.daemon:
+        from skygdr_b200.control import FabricClient, FabricDaemon
+
+        if rank == 0:
+            # one link per prefill GPU: its hand-off and its offload compete for that GPU (copy engines, HBM), not across GPUs
+            extra = [x for r in range(P) for x in ("--link", f"gpu{r}={a.offload_gbps + 40.0}")] + ["--util_threshold_pct", "0"]
+            daemon = FabricDaemon(policy="target_track", window_us=2000, lease_ms=3600 * 1000, extra=extra)
+            store.set("fabricd_port", str(daemon.port))
+        dist.barrier()
+        fabricd_port = int(store.get("fabricd_port").decode())
 
     if is_prefill:
         mine = [r for r in reqs if r["prefill"] == rank]
@@ -103,13 +124,25 @@ def main():
         pool = ops.PagedKVPool(geom, nblk, "nhd", device=dev)
         scratch_dec = ops.PagedKVPool(geom, 2, "hnd", device=dev)
         eng = Qwen3Decoder(cfg, weights, scratch_dec, max_batch=1, max_ctx=256, attn_chunk=128)
-        t_page = ops.CreditPage(flow_id=1, unlimited=True)
+        client = None
+        if a.arm == "controlled" and a.daemon:
+            client = FabricClient(port=fabricd_port)
+            h_t = client.register(f"kv_transfer{rank}", "high", 40.0, kind="kv_transfer", link=f"gpu{rank}")
+            h_o = client.register(f"kv_offload{rank}", 0, 0.0, kind="kv_offload", link=f"gpu{rank}")
+            t_page, o_page = ops.CreditPage.attach(h_t.page_path), ops.CreditPage.attach(h_o.page_path)
+        else:
+            t_page = ops.CreditPage(flow_id=1, unlimited=True)
+            o_page = ops.CreditPage(flow_id=2, unlimited=True)
         flow = ops.KvTransferFlow(dev, page=t_page, max_wait_ms=20.0)
-        o_page = ops.CreditPage(flow_id=2, unlimited=True)
         # background offload of "prefix KV": chunked async copies, credit-gated
         pc = C.PcieTaskConfig()
         pc.device, pc.h2d, pc.chunk_bytes, pc.streams, pc.batch, pc.inflight = local, False, 32 << 20, 4, 2, 4
         pc.seconds, pc.progress_ms = a.duration + 60.0, 100
+        if client is not None:
+            # the daemon leaves an unprotected flow unpaced while nothing needs protecting; the emulated offload only ever has
+            # its offered rate to send, which a duty cycle of the copy loop stands for (the link moves about 55 GB/s)
+            duty = max(0.05, min(1.0, a.offload_gbps / 55.0))
+            pc.duty_on_ms, pc.duty_off_ms = max(1, int(round(20 * duty))), max(0, int(round(20 * (1 - duty))))
         pc.set_credit_page(o_page.host_ptr)
         task = C.PcieTask(pc)
         task.setup()
@@ -119,6 +152,9 @@ def main():
             pacer = ops.LocalPacer(o_page, a.offload_gbps * 0.25, window_ms=2.0).start(base=0)
         elif a.arm == "always_high":
             pacer = ops.LocalPacer(o_page, a.offload_gbps, window_ms=2.0).start(base=0)       # offered rate, never cut
+        elif client is not None:
+            pacer = None
+            set_backlog(h_o, 1 << 40)                         # the offload is always backlogged
         else:
             pacer = None
             dc = ctl.DaemonConfig()
@@ -176,9 +212,13 @@ def main():
             remote = ops.RemotePool(heap.ptr("pool", drank), (geom.block_elems, 2 * geom.page_elems, geom.page_elems), geom.kv_heads,
                                     0, heap.ptr("flags", drank, 4 * r["id"]))
             in_flight["bytes"] = nb * geom.block_elems * 2
+            if client is not None:
+                set_backlog(h_t, in_flight["bytes"])          # what the daemon reads as "the protected flow has work"
             flow.seq = first                                         # the ready flag carries first_token + 1
             st = flow.transfer_to_completion(pool, [remote], table.view(-1), dst_blocks)
             in_flight["bytes"] = 0
+            if client is not None:
+                set_backlog(h_t, 0)
             t_done = time.perf_counter() - t0
             recs.append(dict(id=r["id"], n_in=r["n_in"], t_arrival=r["t"], t_start=t_start, t_prefill_done=t_prefill, t_transfer_done=t_done,
                              flow_time_ms=(t_done - t_prefill) * 1e3, transfer_device_ms=st["device_time_ms"], launches=st["launches"],
@@ -188,7 +228,11 @@ def main():
         task.join()
         if pacer:
             pacer.stop()
-        result = {"role": "prefill", "requests": recs, "offload_gb_s": task.progress().avg_bw_gib_s * 1.073741824}
+        result = {"role": "prefill", "requests": recs, "offload_gb_s": task.progress().avg_bw_gib_s * 1.073741824,
+                  "control": "fabricd process" if client is not None else "in-process"}
+        if client is not None:
+            result["offload_page"] = {k: h_o.usage()[k] for k in ("consumed_bytes", "completed_bytes")}
+            client.close()
     else:
         drank = rank - P
         mine = [r for r in reqs if r["decode"] == drank]
@@ -266,6 +310,8 @@ def main():
         json.dump(out, open(a.out, "w"), indent=1)
         print(json.dumps(summary, indent=1))
     dist.barrier()
+    if daemon is not None:
+        daemon.stop()
     sys.stdout.flush()
     os._exit(0)
 

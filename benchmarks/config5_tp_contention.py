@@ -5,6 +5,9 @@ and offloads KV to pinned host memory.
         benchmarks/config5_tp_contention.py [--seconds 3] [--burst-gb 2 --burst-every-ms 500] [--offload-gbps 16]
         [--baseline nccl] [--out results/config5.json]
 
+Every phase is run --repeats times in a row (median reported, all runs kept), with one CUDA event per replay (per-step device
+times of this rank: p50 / p99 / max and the share of steps more than 20 % over the median) and the SM clocks and throttle
+reasons sampled while it ran, so that a slow mode can be told from sparse stalls and from a clock change.
 Phases per run: clean decode; contended, unscheduled (bursts and offload unpaced); contended, scheduled (the offload is
 held to its offered rate by its credit page, the bursts are paced to `--burst-budget-gbps`). Each rank r receives bursts
 from rank (r+1) % N through the paged transfer kernel and runs one offload task (chunked async copies, low-priority
@@ -33,7 +36,12 @@ from skygdr_b200.parallel.symm import SymmetricHeap  # noqa: E402
 from skygdr_b200.parallel.tp import build_decode_engine  # noqa: E402
 
 
-def timed_decode(eng, seconds, world, dev, state=None):
+def timed_decode(eng, seconds, world, dev, state=None, local=0):
+    """Replays the decode graph for `seconds`; returns (steps, device milliseconds as the max over ranks, detail). Every replay
+    is followed by a CUDA event, so `detail` has this rank's per-step device times (a slow mode shows as a shifted median, sparse
+    stalls as a long tail) and the SM clocks and throttle reasons sampled while the phase ran."""
+    from skygdr_b200.utils.clocks import ClockSampler
+
     if state is not None:                       # every phase starts from the same context lengths
         eng.ids.copy_(state[0]); eng.positions.copy_(state[1]); eng.ctx_lens.copy_(state[2])
     for _ in range(3):
@@ -41,28 +49,35 @@ def timed_decode(eng, seconds, world, dev, state=None):
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(dev)
-    steps, ms = 0, 0.0
+    steps = 0
     n = torch.zeros(1, device=dev)
-    t0 = time.perf_counter()
-    while True:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(8):
-            eng.replay()
-        e1.record()
-        e1.synchronize()
-        ms += e0.elapsed_time(e1)
-        steps += 8
-        # all ranks must stop after the same number of steps: rank 0 decides
-        n[0] = 1.0 if time.perf_counter() - t0 >= seconds else 0.0
-        if world > 1:
-            dist.broadcast(n, 0)
-        if float(n[0]) > 0:
-            break
+    marks = [torch.cuda.Event(enable_timing=True)]
+    with ClockSampler(local, period_s=0.02) as clocks:
+        marks[0].record()
+        t0 = time.perf_counter()
+        while True:
+            for _ in range(8):
+                eng.replay()
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append(e)
+            marks[-1].synchronize()
+            steps += 8
+            # all ranks must stop after the same number of steps: rank 0 decides
+            n[0] = 1.0 if time.perf_counter() - t0 >= seconds else 0.0
+            if world > 1:
+                dist.broadcast(n, 0)
+            if float(n[0]) > 0:
+                break
+    per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(len(marks) - 1))
+    ms = marks[0].elapsed_time(marks[-1])
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return steps, float(t[0])
+    med = per_step[len(per_step) // 2]
+    detail = {"step_ms_p50": med, "step_ms_p99": per_step[min(len(per_step) - 1, int(0.99 * len(per_step)))], "step_ms_max": per_step[-1],
+              "steps_over_1.2x_median": sum(1 for x in per_step if x > 1.2 * med) / len(per_step), "clocks": clocks.summary()}
+    return steps, float(t[0]), detail
 
 
 def main():
@@ -76,6 +91,7 @@ def main():
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--baseline", default="", choices=["", "nccl"])
     ap.add_argument("--diagnose", action="store_true", help="also run each background flow alone, paced and unpaced")
+    ap.add_argument("--repeats", type=int, default=3, help="every phase is run this many times in a row; all runs are reported")
     ap.add_argument("--out", default="results/config5.json")
     a = ap.parse_args()
     C = load()
@@ -96,10 +112,22 @@ def main():
     res = {"env": env_info(), "config": vars(a), "world": world, "phases": {}}
 
     state0 = (eng.ids.clone(), eng.positions.clone(), eng.ctx_lens.clone())
+    def repeated(fn):
+        """A phase `a.repeats` times in a row: the median run is the phase's figure, all runs are kept beside it."""
+        runs = [fn() for _ in range(max(1, a.repeats))]
+        mid = sorted(runs, key=lambda r: r["tok_s"])[len(runs) // 2]
+        out = dict(mid)
+        out["runs_tok_s"] = [r["tok_s"] for r in runs]
+        out["spread_pct"] = 100.0 * (max(out["runs_tok_s"]) - min(out["runs_tok_s"])) / mid["tok_s"]
+        return out
+
     # ---- clean ----
-    steps, ms = timed_decode(eng, a.seconds, world, dev, state0)
-    clean = batch * steps / (ms * 1e-3)
-    res["phases"]["clean"] = {"tok_s": clean, "ms_per_step": ms / steps}
+    def clean_run():
+        steps, ms, detail = timed_decode(eng, a.seconds, world, dev, state0, local)
+        return {"tok_s": batch * steps / (ms * 1e-3), "ms_per_step": ms / steps, **detail}
+
+    res["phases"]["clean"] = repeated(clean_run)
+    clean = res["phases"]["clean"]["tok_s"]
 
     # ---- background flows ----
     geom = ops.KVGeometry()
@@ -158,7 +186,7 @@ def main():
 
         th = threading.Thread(target=bursts if do_bursts else (lambda: None), daemon=True)
         th.start()
-        steps, ms = timed_decode(eng, a.seconds, world, dev, state0)
+        steps, ms, detail = timed_decode(eng, a.seconds, world, dev, state0, local)
         stop.set()
         th.join()
         task.stop()
@@ -169,26 +197,26 @@ def main():
         return {"tok_s": batch * steps / (ms * 1e-3), "vs_clean": batch * steps / (ms * 1e-3) / clean, "ms_per_step": ms / steps,
                 "burst_ms_mean": sum(xfer_ms) / max(1, len(xfer_ms)), "bursts": len(xfer_ms),
                 "burst_gbs": nb * geom.block_elems * 2 / 1e6 / (sum(xfer_ms) / max(1, len(xfer_ms))) if xfer_ms else None,
-                "offload_gb_s": pr.avg_bw_gib_s * 1.073741824}
+                "offload_gb_s": pr.avg_bw_gib_s * 1.073741824, **detail}
 
     if a.diagnose:
         for name, kw in (("only_pacer_threads", dict(do_bursts=False, do_offload=False)), ("only_offload_unpaced", dict(do_bursts=False)),
                          ("only_bursts_unpaced", dict(do_offload=False))):
-            res["phases"][name] = contended(name == "only_pacer_threads", **kw)
-        res["phases"]["only_offload_paced"] = contended(True, do_bursts=False)
-        res["phases"]["only_bursts_paced"] = contended(True, do_offload=False)
-    res["phases"]["contended_unscheduled"] = contended(False)
+            res["phases"][name] = repeated(lambda: contended(name == "only_pacer_threads", **kw))
+        res["phases"]["only_offload_paced"] = repeated(lambda: contended(True, do_bursts=False))
+        res["phases"]["only_bursts_paced"] = repeated(lambda: contended(True, do_offload=False))
+    res["phases"]["contended_unscheduled"] = repeated(lambda: contended(False))
     if world > 1:
         dist.barrier()
-    res["phases"]["contended_scheduled"] = contended(True)
+    res["phases"]["contended_scheduled"] = repeated(lambda: contended(True))
     res["kernel_status"] = eng.check_status()
 
     if a.baseline == "nccl" and world > 1:
         base = NcclTPDecoder.from_engine(eng)
         base.capture(batch, eng.max_ctx)
-        steps, ms = timed_decode(base, a.seconds, world, dev, state0)
+        steps, ms, detail = timed_decode(base, a.seconds, world, dev, state0, local)
         res["phases"]["nccl_cublas_baseline_clean"] = {"tok_s": batch * steps / (ms * 1e-3), "ms_per_step": ms / steps,
-                                                       "fused_speedup": clean / (batch * steps / (ms * 1e-3))}
+                                                       "fused_speedup": clean / (batch * steps / (ms * 1e-3)), **detail}
     if rank == 0:
         os.makedirs(os.path.dirname(os.path.abspath(a.out)), exist_ok=True)
         json.dump(res, open(a.out, "w"), indent=1)

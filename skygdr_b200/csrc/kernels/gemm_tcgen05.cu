@@ -281,12 +281,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const bool wrote = p.splits == 1 || s_last;
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (wrote && threadIdx.x == 64) {
-            if (p.rs.signal == 1) {
-                for (int j = 0; j < p.rs.world; ++j) red_release_sys_add_u32(p.rs.counters[j], 1u);
-            } else {
-                __threadfence_system();
-                for (int j = 0; j < p.rs.world; ++j) red_relaxed_sys_add_u32(p.rs.counters[j], 1u);
-            }
+            __threadfence_system();
+            for (int j = 0; j < p.rs.world; ++j) red_relaxed_sys_add_u32(p.rs.counters[j], 1u);
         }
     }
     tc_fence_before();
@@ -521,12 +517,7 @@ size_t gemm_counter_count(int M, int N, bool gated, int ntok) {
     return (size_t)((N + BM - 1) / BM) * ((M + ntok - 1) / ntok);
 }
 
-cudaError_t launch_gemm(const GemmParams& p_in, cudaStream_t stream) {
-    GemmParams p = p_in;
-    static const int signal_mode = [] { const char* v = getenv("SKYGDR_PUSH_SIGNAL"); return v && v[0] == 'r' ? 1 : 0; }();
-    static const int deep_mode = [] { const char* v = getenv("SKYGDR_GEMM_DEEP"); return v ? atoi(v) : 0; }();
-    p.rs.signal = signal_mode;
-    if (!p.deep && deep_mode) p.deep = deep_mode;
+cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream) {
     if (p.K % BK || p.M <= 0 || p.N <= 0 || p.splits < 1 || p.splits > p.K / BK) return cudaErrorInvalidValue;
     if (p.splits > 1 && (!p.workspace || !p.counters)) return cudaErrorInvalidValue;
     const int ntok = p.ntok > 0 ? p.ntok : gemm_pick_ntok(p.M, p.gated != 0);
@@ -545,8 +536,9 @@ cudaError_t launch_gemm(const GemmParams& p_in, cudaStream_t stream) {
     // A GEMM that waits for an all-gather runs one CTA per SM with the deepest pipeline (more weight traffic hidden behind the
     // wait). Everything else, the GEMMs that only push their tiles to peers included, keeps the small pipeline: two CTAs per
     // SM, which also leaves room on the SM for the next kernel's CTAs to start early (measured in a chain of launches inside
-    // a CUDA graph: 5.5 us per launch against 9.8 us for the O projection of one rank at TP 8).
-    const bool deep = p.deep ? p.deep == 2 : p.ag.n_src > 0;
+    // a CUDA graph, every decode GEMM shape at TP 1 / 2 / 4 / 8 and every tile and split: the deep layout was never faster, and
+    // slower by 1 - 2 us per launch for most).
+    const bool deep = p.ag.n_src > 0;
 #define SKY_GEMM_CASE(NT)                                                                   \
     case NT: return deep ? (p.gated ? launch_t<NT, true, true>(p, tw, tx, stream) : launch_t<NT, false, true>(p, tw, tx, stream))   \
                          : (p.gated ? launch_t<NT, true, false>(p, tw, tx, stream) : launch_t<NT, false, false>(p, tw, tx, stream));

@@ -39,7 +39,6 @@ struct TpRsPush {
     int world;                                    // 0: off
     int src_rank, rows_per_rank;
     int all;
-    int signal;                                   // 0: one system fence, then relaxed arrivals; 1: a release arrival per destination
     __nv_bfloat16* dst[TP_MAX_RANKS];             // peers' receive buffers (peer-mapped)
     unsigned int* counters[TP_MAX_RANKS];         // peers' arrival counters (peer-mapped)
 };
@@ -58,8 +57,6 @@ struct GemmParams {
     LaunchStatus* status;
     TpAgWait ag;
     TpRsPush rs;
-    int deep;                 // pipeline layout: 0 = chosen by the launcher, 1 = two CTAs per SM (small pipeline), 2 = one CTA per SM with
-                              // the deepest pipeline that fits
     int persistent;           // 1: one CTA per SM walks the output tiles with two accumulators in TMEM (many-token shapes; needs
                               // splits == 1, ntok 256 or 128, neither ag nor rs)
 };
