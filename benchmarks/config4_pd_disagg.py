@@ -143,6 +143,7 @@ def main():
             # its offered rate to send, which a duty cycle of the copy loop stands for (the link moves about 55 GB/s)
             duty = max(0.05, min(1.0, a.offload_gbps / 55.0))
             pc.duty_on_ms, pc.duty_off_ms = max(1, int(round(20 * duty))), max(0, int(round(20 * (1 - duty))))
+            pc.max_outstanding_bytes = 64 << 20               # a short queue, so that the off phase really is off
         pc.set_credit_page(o_page.host_ptr)
         task = C.PcieTask(pc)
         task.setup()

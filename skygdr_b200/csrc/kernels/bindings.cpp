@@ -354,7 +354,7 @@ static void sample(torch::Tensor logits, torch::Tensor out, double temperature, 
 // ---- GEMM ----
 // ss_in / ss_out: fp32 vectors of at least M entries (see GemmNormFuse); residual: y is the residual stream, updated in place.
 static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, bool gated, c10::optional<torch::Tensor> workspace,
-                 c10::optional<torch::Tensor> counters, torch::Tensor status, int ntok, bool persistent) {
+                 c10::optional<torch::Tensor> counters, torch::Tensor status, int ntok, bool persistent, bool cluster_split) {
     c10::cuda::CUDAGuard g(x.device());
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1, "row-major 2-D tensors");
     GemmParams p;
@@ -364,8 +364,8 @@ static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, 
     p.N = gated ? (int)w.size(0) / 2 : (int)w.size(0);
     TORCH_CHECK(w.size(1) == p.K && y.size(0) == p.M && y.size(1) == p.N, "shape mismatch");
     p.ldx = x.stride(0); p.ldw = w.stride(0); p.ldy = y.stride(0);
-    p.splits = splits; p.gated = gated; p.ntok = ntok;
-    if (splits > 1) {
+    p.splits = splits; p.gated = gated; p.ntok = ntok; p.cluster_split = cluster_split ? 1 : 0;
+    if (splits > 1 && !cluster_split) {
         TORCH_CHECK(workspace.has_value() && counters.has_value(), "split-K needs workspace and counters");
         TORCH_CHECK((size_t)workspace->numel() >= gemm_workspace_floats(p.M, p.N, splits, gated, ntok), "workspace too small");
         TORCH_CHECK((size_t)counters->numel() >= gemm_counter_count(p.M, p.N, gated, ntok), "counters too small");
@@ -388,7 +388,7 @@ static TpSeq make_seq(uint64_t step_ptr, unsigned uses_per_step, unsigned use_in
 // ag = (n_src, counters_ptr, step_ptr, uses_per_step, use_index, arrivals_per_use, timeout_ns) or empty
 // rs = (world, src_rank, rows_per_rank, [dst ptrs], [counter ptrs]) or empty
 static void gemm_tp(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, bool gated, c10::optional<torch::Tensor> workspace,
-                    c10::optional<torch::Tensor> counters, torch::Tensor status, py::tuple ag, py::tuple rs, int ntok) {
+                    c10::optional<torch::Tensor> counters, torch::Tensor status, py::tuple ag, py::tuple rs, int ntok, bool cluster_split) {
     c10::cuda::CUDAGuard g(x.device());
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "row-major 2-D tensors");
     GemmParams p;
@@ -402,8 +402,8 @@ static void gemm_tp(torch::Tensor x, torch::Tensor w, torch::Tensor y, int split
         TORCH_CHECK(y.dim() == 2 && y.size(0) == p.M && y.size(1) == p.N && y.stride(1) == 1, "y shape");
         p.y = bf16_mut(y); p.ldy = y.stride(0);
     }
-    p.splits = splits; p.gated = gated; p.ntok = ntok;
-    if (splits > 1) {
+    p.splits = splits; p.gated = gated; p.ntok = ntok; p.cluster_split = cluster_split ? 1 : 0;
+    if (splits > 1 && !cluster_split) {
         TORCH_CHECK(workspace.has_value() && counters.has_value(), "split-K needs workspace and counters");
         TORCH_CHECK((size_t)workspace->numel() >= gemm_workspace_floats(p.M, p.N, splits, gated, ntok), "workspace too small");
         TORCH_CHECK((size_t)counters->numel() >= gemm_counter_count(p.M, p.N, gated, ntok), "counters too small");
@@ -533,8 +533,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("argmax", &argmax);
     m.def("sample", &sample, py::arg("logits"), py::arg("out"), py::arg("temperature"), py::arg("seed"), py::arg("positions") = py::none());
     m.def("gemm", &gemm, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("splits"), py::arg("gated"), py::arg("workspace"), py::arg("counters"),
-          py::arg("status"), py::arg("ntok"), py::arg("persistent") = false);
-    m.def("gemm_tp", &gemm_tp);
+          py::arg("status"), py::arg("ntok"), py::arg("persistent") = false, py::arg("cluster_split") = false);
+    m.def("gemm_tp", &gemm_tp, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("splits"), py::arg("gated"), py::arg("workspace"), py::arg("counters"),
+          py::arg("status"), py::arg("ag"), py::arg("rs"), py::arg("ntok"), py::arg("cluster_split") = false);
     m.def("tp_norm", &tp_norm, py::arg("rs_buf"), py::arg("rs_counter"), py::arg("rs_seq"), py::arg("resid"), py::arg("w"), py::arg("ag_dst"),
           py::arg("ag_counter"), py::arg("rank"), py::arg("eps"), py::arg("timeout_ns"), py::arg("status"), py::arg("rs_world") = 0);
     m.def("tp_argmax", &tp_argmax);

@@ -32,7 +32,8 @@ bool pdl_enabled() {
 // Writes a chunk of 16 token rows x 128 columns. Thread r (0..127 of the epilogue warps) holds column n0+r of the 16
 // rows. The values are staged through shared memory so that each row leaves as 16-byte pieces, 256 contiguous bytes
 // per row, instead of one 2-byte store per element: that matters most when the destination is a peer over NVLink.
-__device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16* stage, int t_base, int n0, int r, float* vals) {
+// Only the first `count` rows are stored (the cluster form hands a CTA fewer than 16 token columns at a time).
+__device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16* stage, int t_base, int n0, int r, float* vals, int count = 16) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) stage[j * 128 + r] = __float2bfloat16(vals[j]);
     asm volatile("bar.sync 3, 128;" ::: "memory");
@@ -40,7 +41,7 @@ __device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16
     for (int k = 0; k < 2; ++k) {
         const int idx = r + 128 * k, j = idx >> 4, ch = idx & 15;
         const int t = t_base + j, n = n0 + ch * 8;
-        if (t < p.M && n < p.N) {
+        if (j < count && t < p.M && n < p.N) {
             __nv_bfloat16* dst;
             const uint4 v = *reinterpret_cast<const uint4*>(stage + j * 128 + ch * 8);
             if (p.rs.world > 0 && p.rs.all) {                       // one-shot all-reduce: the same row to every rank
@@ -69,6 +70,23 @@ __device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16
     asm volatile("bar.sync 3, 128;" ::: "memory");
 }
 
+// Thread-block cluster pieces of the split-K form below: the CTAs of one output tile (one per K range) form a cluster and
+// reduce their partial accumulators through each other's shared memory instead of through global memory.
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_smem_addr, uint32_t cta_rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_smem_addr), "r"(cta_rank));
+    return a;
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
 constexpr int GEMM_THREADS = 192;
 constexpr int BM = 128;   // weight rows per tile (MMA M)
 constexpr int BK = 64;    // K per stage: 64 bf16 = 128 bytes = one swizzle row
@@ -91,10 +109,16 @@ struct GemmSmem {
     static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;
 };
 
-template <int NTOK, bool GATED, bool DEEP>
+// CSPLIT: split-K inside a thread-block cluster. The `splits` CTAs of an output tile are launched as one cluster (cluster
+// dimension z); each leaves its fp32 partial accumulator in its own shared memory (over the pipeline stages, which are idle by
+// then), the cluster synchronises, and CTA s sums and stores the token columns [s * NTOK / splits, (s + 1) * NTOK / splits) of the
+// tile, reading all partials through distributed shared memory. No workspace in global memory, no counters, no last CTA that
+// re-reads every partial on its own: that is what made splits of 128-token tiles too expensive to use.
+template <int NTOK, bool GATED, bool DEEP, bool CSPLIT>
 __global__ void __launch_bounds__(GEMM_THREADS, (GemmSmem<NTOK, GATED, DEEP>::TWO_PER_SM ? 2 : 1))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     using S = GemmSmem<NTOK, GATED, DEEP>;
+    static_assert(!CSPLIT || S::ACC_COLS * BM * 4 <= S::STAGES * S::STAGE_BYTES, "the partial accumulator must fit over the pipeline stages");
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint64_t full_bar[8], empty_bar[8], acc_bar;
     __shared__ uint32_t tmem_slot;
@@ -202,7 +226,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const uint32_t taddr = tmem_base + ((uint32_t)(slice * 32) << 16);
         const bool direct = p.splits == 1;
         float* ws = nullptr;
-        if (!direct) {
+        if constexpr (CSPLIT) {
+            ws = reinterpret_cast<float*>(smem);                   // [ACC_COLS][128] floats of this CTA, read by the cluster below
+        } else if (!direct) {
             const long long tile_id = (long long)tile_m * gridDim.x + tile_n;
             ws = p.workspace + ((tile_id * p.splits + split) * S::ACC_COLS) * BM;
         }
@@ -217,7 +243,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 #pragma unroll
                 for (int i = 0; i < 16; ++i) { v[i] = 0; u[i] = 0; }
             }
-            if (direct) {
+            if (direct && !CSPLIT) {
                 float vals[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -234,7 +260,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 }
             }
         }
-        if (!direct) {
+        if (!direct && !CSPLIT) {
             // last-arriving split of this tile sums all partials
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -276,7 +302,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             }
         }
     }
-    if (p.rs.world > 0 && warp >= 2) {
+    if constexpr (CSPLIT) {
+        tc_fence_before();
+        cluster_sync_all();                                        // every CTA's partial is in its shared memory
+        const uint32_t crank = cluster_ctarank();
+        if (warp >= 2) {
+            const int r = (warp & 3) * 32 + lane;
+            const int c_lo = (int)(crank * NTOK / p.splits), c_hi = (int)((crank + 1) * NTOK / p.splits);
+            const uint32_t part = smem_u32(smem);
+#pragma unroll 1
+            for (int c0 = c_lo; c0 < c_hi; c0 += 16) {
+                const int cnt = min(16, c_hi - c0);
+                float g[16], up[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) { g[j] = 0.f; up[j] = 0.f; }
+                if (t0 + c0 < p.M) {
+                    for (int s2 = 0; s2 < p.splits; ++s2) {
+                        const uint32_t base = dsmem_addr(part, (uint32_t)s2) + (uint32_t)(c0 * BM + r) * 4u;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (j < cnt) {
+                                g[j] += ld_dsmem_f32(base + (uint32_t)(j * BM) * 4u);
+                                if (GATED) up[j] += ld_dsmem_f32(base + (uint32_t)((NTOK + j) * BM) * 4u);
+                            }
+                        }
+                    }
+                    if (GATED) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * up[j];
+                    }
+                }
+                store_chunk16(p, stage, t0 + c0, n0, r, g, cnt);
+            }
+        }
+        // nobody leaves while a peer may still read its partial; and every CTA's stores come before rank 0's fence below
+        cluster_sync_all();
+        if (p.rs.world > 0 && crank == 0 && threadIdx.x == 64) {   // one arrival per destination and output tile, as without splits
+            __threadfence_system();
+            for (int j = 0; j < p.rs.world; ++j) red_relaxed_sys_add_u32(p.rs.counters[j], 1u);
+        }
+    } else if (p.rs.world > 0 && warp >= 2) {
         // one arrival per destination from the CTA that wrote this tile's rows (with split-K: the last split)
         const bool wrote = p.splits == 1 || s_last;
         asm volatile("bar.sync 2, 128;" ::: "memory");
@@ -470,10 +535,10 @@ bool make_tmap_bf16_2d(CUtensorMap* m, const void* base, long long rows, long lo
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int NTOK, bool GATED, bool DEEP>
+template <int NTOK, bool GATED, bool DEEP, bool CSPLIT = false>
 static cudaError_t launch_t(const GemmParams& p, const CUtensorMap& tw, const CUtensorMap& tx, cudaStream_t stream) {
     using S = GemmSmem<NTOK, GATED, DEEP>;
-    auto kern = gemm_tcgen05_kernel<NTOK, GATED, DEEP>;
+    auto kern = gemm_tcgen05_kernel<NTOK, GATED, DEEP, CSPLIT>;
     // SKYGDR_GEMM_ONE_PER_SM=1 pads the request of the small-stage kernels so that only one CTA fits on an SM (a switch for
     // measuring what co-residency is worth; the kernel itself does not change).
     static const bool one_per_sm = [] { const char* v = getenv("SKYGDR_GEMM_ONE_PER_SM"); return v && v[0] == '1'; }();
@@ -481,7 +546,7 @@ static cudaError_t launch_t(const GemmParams& p, const CUtensorMap& tw, const CU
     static unsigned long long attr_mask = 0;
     if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), dyn, &attr_mask); e != cudaSuccess) return e;
     dim3 grid((p.N + BM - 1) / BM, (p.M + NTOK - 1) / NTOK, p.splits);
-    return launch_pdl(kern, grid, dim3(GEMM_THREADS), (size_t)dyn, stream, tw, tx, p);
+    return launch_pdl_cluster(kern, grid, dim3(GEMM_THREADS), (size_t)dyn, stream, CSPLIT ? p.splits : 0, tw, tx, p);
 }
 
 template <int NTOK, bool GATED>
@@ -519,7 +584,9 @@ size_t gemm_counter_count(int M, int N, bool gated, int ntok) {
 
 cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream) {
     if (p.K % BK || p.M <= 0 || p.N <= 0 || p.splits < 1 || p.splits > p.K / BK) return cudaErrorInvalidValue;
-    if (p.splits > 1 && (!p.workspace || !p.counters)) return cudaErrorInvalidValue;
+    const bool csplit = p.cluster_split && p.splits > 1;
+    if (csplit && (p.splits > 8 || p.ag.n_src > 0)) return cudaErrorInvalidValue;        // a portable cluster holds at most 8 CTAs
+    if (p.splits > 1 && !csplit && (!p.workspace || !p.counters)) return cudaErrorInvalidValue;
     const int ntok = p.ntok > 0 ? p.ntok : gemm_pick_ntok(p.M, p.gated != 0);
     if (ntok != 16 && ntok != 32 && ntok != 64 && ntok != 128 && ntok != 256) return cudaErrorInvalidValue;
     CUtensorMap tw, tx;
@@ -539,6 +606,18 @@ cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream) {
     // a CUDA graph, every decode GEMM shape at TP 1 / 2 / 4 / 8 and every tile and split: the deep layout was never faster, and
     // slower by 1 - 2 us per launch for most).
     const bool deep = p.ag.n_src > 0;
+#define SKY_GEMM_CLUSTER_CASE(NT) \
+    case NT: return p.gated ? launch_t<NT, true, false, true>(p, tw, tx, stream) : launch_t<NT, false, false, true>(p, tw, tx, stream);
+    if (csplit) {
+        switch (ntok) {
+            SKY_GEMM_CLUSTER_CASE(16)
+            SKY_GEMM_CLUSTER_CASE(32)
+            SKY_GEMM_CLUSTER_CASE(64)
+            SKY_GEMM_CLUSTER_CASE(128)
+            default: return p.gated ? cudaErrorInvalidValue : launch_t<256, false, false, true>(p, tw, tx, stream);
+        }
+    }
+#undef SKY_GEMM_CLUSTER_CASE
 #define SKY_GEMM_CASE(NT)                                                                   \
     case NT: return deep ? (p.gated ? launch_t<NT, true, true>(p, tw, tx, stream) : launch_t<NT, false, true>(p, tw, tx, stream))   \
                          : (p.gated ? launch_t<NT, true, false>(p, tw, tx, stream) : launch_t<NT, false, false>(p, tw, tx, stream));

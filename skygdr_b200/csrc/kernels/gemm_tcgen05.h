@@ -57,6 +57,8 @@ struct GemmParams {
     LaunchStatus* status;
     TpAgWait ag;
     TpRsPush rs;
+    int cluster_split;        // 1 (with 2 <= splits <= 8): the splits of a tile form a thread-block cluster and reduce through distributed
+                              // shared memory; workspace and counters are not used
     int persistent;           // 1: one CTA per SM walks the output tiles with two accumulators in TMEM (many-token shapes; needs
                               // splits == 1, ntok 256 or 128, neither ag nor rs)
 };

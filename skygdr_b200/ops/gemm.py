@@ -47,9 +47,38 @@ STANDALONE = GemmCostModel(1.56, 1.75, 36.4e3, 57.4e3, True, float("inf"), 26.2e
 FUSED_TP = GemmCostModel(6.0, 6.0, 55e3, 55e3, False, 100e3, 200e3)
 
 
+_TUNED: Optional[Dict[str, list]] = None
+
+
+def tuned_config(M: int, N: int, K: int, gated: bool) -> Optional[Tuple[int, int, bool]]:
+    """(token tile, splits, cluster) measured fastest for exactly this shape by benchmarks/gemm_tune.py, or None. The table
+    (ops/gemm_tuned.json) holds the decoder's projections at the tensor-parallel degrees and batch sizes of the benchmark."""
+    global _TUNED
+    if _TUNED is None:
+        import json
+        import os
+
+        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "gemm_tuned.json")
+        try:
+            _TUNED = json.load(open(path))["table"]
+        except (OSError, ValueError, KeyError):
+            _TUNED = {}
+    e = _TUNED.get(f"{M},{N},{K},{int(gated)}")
+    return (int(e[0]), int(e[1]), bool(e[2])) if e else None
+
+
+def choose_config(M: int, N: int, K: int, sms: int, gated: bool = False) -> Tuple[int, int, bool]:
+    """(token tile, splits, cluster) for a decode GEMM: the measured best where the shape was tuned, the cost model otherwise."""
+    t = tuned_config(M, N, K, gated)
+    if t:
+        return t
+    ntok, splits = pick_config(M, N, K, sms, gated)
+    return ntok, splits, False
+
+
 def pick_config(M: int, N: int, K: int, sms: int, gated: bool = False, fixed_ntok: int = 0,
                 model: GemmCostModel = STANDALONE) -> Tuple[int, int]:
-    """(token tile, split-K factor) for y[M][N] = x[M][K] w[N][K]^T with small M.
+    """(token tile, split-K factor) for y[M][N] = x[M][K] w[N][K]^T with small M, from the cost model.
 
     The time is about waves x (fixed cost per CTA + bytes per CTA / stream rate of a CTA), bounded below by total bytes
     over the HBM rate; a split adds its fp32 partial (written, then re-read by the last CTA of the tile). A pipeline of
@@ -111,13 +140,15 @@ def workspace_for(device) -> GemmWorkspace:
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, gated: bool = False,
-         splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, ntok: int = 0, persistent: Optional[bool] = None) -> torch.Tensor:
+         splits: Optional[int] = None, ws: Optional[GemmWorkspace] = None, ntok: int = 0, persistent: Optional[bool] = None,
+         cluster: bool = False) -> torch.Tensor:
     """y = x @ w.T (w is [N][K]); gated: w is [2N][K] and y = silu(x @ w[:N].T) * (x @ w[N:].T).
 
     Few tokens (M <= 256, decode): one CTA per output tile with split-K, tile and split chosen by ``pick_config``.
     Many tokens (prefill): the persistent form, one CTA per SM walking tiles of 256 tokens (128 when gated) with two
     accumulators in TMEM, so that a tile's epilogue overlaps the next tile's MMAs. ``persistent`` overrides the choice
-    (False = one tile per CTA at any M, kept for comparison)."""
+    (False = one tile per CTA at any M, kept for comparison). ``cluster`` (2 to 8 splits): the splits of a tile run as a
+    thread-block cluster and sum their partial accumulators through distributed shared memory instead of a workspace."""
     C = load()
     M, K = x.shape
     N = w.shape[0] // 2 if gated else w.shape[0]
@@ -131,10 +162,13 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, g
         return out
     if splits is None:
         if ntok == 0 and M <= 256:
-            ntok, splits = pick_config(M, N, K, _sms(x.device), gated)
+            ntok, splits, cluster = choose_config(M, N, K, _sms(x.device), gated)
         else:
             splits = 1 if M > 256 else pick_config(M, N, K, _sms(x.device), gated, fixed_ntok=ntok)[1]
-    if splits > 1:
+    if splits > 1 and cluster:
+        assert splits <= 8, "a cluster holds at most 8 CTAs"
+        C.gemm(x, w, out, splits, gated, None, None, ws.status, ntok, False, True)
+    elif splits > 1:
         ws.ensure(C.gemm_workspace_floats(M, N, splits, gated, ntok), C.gemm_counter_count(M, N, gated, ntok))
         C.gemm(x, w, out, splits, gated, ws.ws, ws.counters, ws.status, ntok)
     else:

@@ -22,7 +22,7 @@ from .. import ops
 from .._ext import load
 from ..models.qwen3 import Qwen3Config, Qwen3Decoder, Qwen3Weights
 from ..ops.flow import new_status, read_status
-from ..ops.gemm import FUSED_TP, STANDALONE, GemmWorkspace, pick_config
+from ..ops.gemm import FUSED_TP, GemmWorkspace, choose_config, pick_config
 from ..ops.kv_cache import KVGeometry, PagedKVPool
 from .symm import SymmetricHeap
 
@@ -112,15 +112,20 @@ class TPDecoder:
         self._C.tp_norm(rs_buf, rs_ctr, seq, self.resid, w, self.heap.all_ptrs(ag_name),
                         self.heap.all_ptrs("counters", ag_off + 4 * self.rank), self.rank, self.cfg.eps, TIMEOUT_NS, self.status)
 
-    def _config(self, M: int, N: int, K: int, gated: bool = False) -> Tuple[int, int]:
-        """(token tile, splits) of a GEMM of this engine; the arrival counts of the collectives are derived from the same choice."""
-        return pick_config(M, N, K, 148, gated, model=FUSED_TP if self.collective == "rs_ag" else STANDALONE)
+    def _config(self, M: int, N: int, K: int, gated: bool = False) -> Tuple[int, int, bool]:
+        """(token tile, splits, cluster) of a GEMM of this engine; the arrival counts of the collectives are derived from the
+        same choice."""
+        if self.collective == "rs_ag":
+            return (*pick_config(M, N, K, 148, gated, model=FUSED_TP), False)
+        return choose_config(M, N, K, 148, gated)
 
     def _gemm(self, x, w, y, gated=False, ag=(), rs=()):
         M, K = x.shape
         N = w.shape[0] // 2 if gated else w.shape[0]
-        ntok, splits = self._config(M, N, K, gated)
-        if splits > 1:
+        ntok, splits, cluster = self._config(M, N, K, gated)
+        if splits > 1 and cluster:
+            self._C.gemm_tp(x, w, y, splits, gated, None, None, self.status, ag, rs, ntok, True)
+        elif splits > 1:
             self.ws.ensure(self._C.gemm_workspace_floats(M, N, splits, gated, ntok), self._C.gemm_counter_count(M, N, gated, ntok))
             self._C.gemm_tp(x, w, y, splits, gated, self.ws.ws, self.ws.counters, self.status, ag, rs, ntok)
         else:
@@ -128,7 +133,7 @@ class TPDecoder:
 
     def _rs_arrivals(self, K: int) -> int:
         """Arrivals one reduce-scatter adds to a rank's counter: every output tile of every rank's GEMM."""
-        ntok, _ = self._config(self.batch, self.cfg.hidden, K)
+        ntok = self._config(self.batch, self.cfg.hidden, K)[0]
         return self.world * self.tiles_h * ((self.batch + ntok - 1) // ntok)
 
     def set_batch(self, ids: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor) -> None:

@@ -368,6 +368,32 @@ def test_gemm_gated_matches_reference(ops, M, F, K, splits):
     assert err < 2e-2 * max(1.0, float(ref.abs().max())), float(err)
 
 
+@pytest.mark.parametrize("M,N,K,gated,ntok,splits", [
+    (128, 768, 4096, False, 128, 8), (128, 768, 4096, False, 64, 4), (128, 4096, 1536, False, 128, 4), (128, 1536, 4096, True, 128, 8),
+    (16, 6144, 4096, False, 16, 4), (16, 12288, 4096, True, 16, 2), (32, 4096, 6144, False, 32, 6), (100, 1000, 512, False, 64, 3),
+    (37, 256, 1024, True, 64, 5), (3, 130, 2048, False, 16, 7), (256, 512, 2048, False, 256, 8)])
+def test_gemm_cluster_split_matches_reference(ops, M, N, K, gated, ntok, splits):
+    """Split-K inside a thread-block cluster (partials summed through distributed shared memory): every token tile width, splits
+    that do and do not divide the tile and the K range, the gated epilogue, row and column tails; against fp32 PyTorch and
+    against the workspace form of the same split."""
+    torch.manual_seed(5)
+    x = torch.randn((M, K), dtype=torch.bfloat16, device="cuda")
+    w = (torch.randn(((2 if gated else 1) * N, K), dtype=torch.bfloat16, device="cuda") / math.sqrt(K)).contiguous()
+    y = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(x, w, out=y, gated=gated, splits=splits, ntok=ntok, cluster=True)
+    ref = x.float() @ w.float().t()
+    if gated:
+        ref = torch.nn.functional.silu(ref[:, :N]) * ref[:, N:]
+    torch.cuda.synchronize()
+    from skygdr_b200.ops.gemm import workspace_for
+
+    assert ops.read_status(workspace_for("cuda").status)["status"] == 0
+    err = (y.float() - ref).abs().max()
+    assert err < 2e-2 * max(1.0, float(ref.abs().max())), float(err)
+    y2 = ops.gemm(x, w, gated=gated, splits=splits, ntok=ntok)
+    assert (y.float() - y2.float()).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
+
+
 def test_rmsnorm_and_residual(ops):
     torch.manual_seed(4)
     x = torch.randn((37, 4096), dtype=torch.bfloat16, device="cuda")
@@ -598,7 +624,9 @@ def test_kernel_is_paced_by_the_daemon_process_through_the_page_it_owns(ops):
                 t0 = time.perf_counter()
                 st = flow.transfer_to_completion(src, [ops.RemotePool.of(dst)], sb, db)
                 dt = time.perf_counter() - t0
-                assert st["status"] == 0 and st["bytes_done"] == total, st
+                # a launch that ran out of credit is resumed from the lowest unfinished chunk: chunks past it that other CTAs had
+                # already moved are moved again, so the byte count may exceed the payload by a few chunks
+                assert st["status"] == 0 and total <= st["bytes_done"] <= total * 1.1, st
                 assert torch.equal(dst.data[db.long()], ops.reference_transfer(src, sb))
                 rates[policy] = (total / dt / 1e9, st["launches"])
                 usage = h.usage()
