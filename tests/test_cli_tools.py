@@ -235,6 +235,53 @@ def test_controller_releases_the_background_flow_when_the_protected_flow_dies_mi
     assert "control_stop=1" in out                                   # ... and let go of it before leaving
 
 
+def test_contention_analyze_redraws_the_six_figures_from_the_two_summaries(tmp_path):
+    """The figure tool of the PCIe contention study: same --base_dir layout and figure names as the reference's script; every
+    figure comes out as its numbers (CSV) and as an SVG drawing; ratios are computed where the summary leaves them out; the raw
+    readers turn worker logs and sweep CSVs into the summaries."""
+    import csv
+
+    base = tmp_path / "study"
+    (base / "summary").mkdir(parents=True)
+    (base / "summary" / "partA_memcpy_impact.csv").write_text(
+        "direction,baseline_mean_bw_gib_s,baseline_median_bw_gib_s,baseline_p95_bw_gib_s,baseline_n,contended_mean_bw_gib_s,"
+        "contended_median_bw_gib_s,contended_p95_bw_gib_s,contended_n,degradation_pct\n"
+        "h2d,24.0,24.1,24.5,50,18.0,18.2,19.0,50,25.0\nd2h,25.0,25.0,25.6,50,22.5,22.4,23.0,50,10.0\n")
+    (base / "summary" / "partB_size_impact.csv").write_text(
+        "msg_bytes,write_none_thr,write_h2d_thr,read_none_thr,read_d2h_thr\n"
+        "4096,1.0,0.9,0.8,0.8\n65536,6.0,4.5,5.0,4.0\n1048576,10.0,6.0,9.0,8.1\n")
+    r = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.contention_analyze", "--base_dir", str(base)], capture_output=True, text=True, env=ENV, timeout=60)
+    assert r.returncode == 0 and "[ok] fig:" in r.stdout, r.stdout + r.stderr
+    names = ["partA_memcpy_impact_bar", "partB_write_sweep_throughput", "partB_read_sweep_throughput", "partB_ratio_vs_size",
+             "partB_fourcases_throughput", "pcie_contention_combined"]
+    for n in names:
+        assert (base / "fig" / (n + ".csv")).exists() and (base / "fig" / (n + ".svg")).read_text().startswith("<svg"), n
+    ratio = list(csv.DictReader(open(base / "fig" / "partB_ratio_vs_size.csv")))
+    assert [float(x["write_thr_ratio"]) for x in ratio] == [0.9, 0.75, 0.6] and abs(float(ratio[2]["read_thr_ratio"]) - 0.9) < 1e-9
+    svg = (base / "fig" / "partA_memcpy_impact_bar.svg").read_text()
+    assert "-25.0%" in svg and "H2D" in svg and svg.count("<rect") >= 5
+    # raw readers -> summaries
+    raw = tmp_path / "raw"
+    raw.mkdir()
+    for d, (b, c) in {"h2d": (20.0, 15.0), "d2h": (22.0, 21.0)}.items():
+        (raw / f"partA_{d}_baseline.log").write_text("".join(f"[pcie] t={i}.0s issued=1 bw_gib_s={b + 0.1 * (i % 3):.2f}\n" for i in range(1, 11)))
+        (raw / f"partA_{d}_contended.log").write_text("".join(f"[pcie] t={i}.0s issued=1 bw_gib_s={c:.2f}\n" for i in range(1, 11)))
+    hdr = "MsgBytes,Throughput_GiB_per_s,P50_us,P99_us,RetCode\n"
+    for name, scale in (("write_none", 1.0), ("write_h2d", 0.7), ("read_none", 0.9), ("read_d2h", 0.8)):
+        (raw / f"partB_{name}.csv").write_text(hdr + "".join(f"{s},{scale * t},10,20,0\n" for s, t in ((4096, 1.0), (65536, 5.0))) + "1048576,9,1,1,3\n")
+    out = tmp_path / "fromraw"
+    r = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.contention_analyze", "--base_dir", str(out), "--from_raw", str(raw)],
+                       capture_output=True, text=True, env=ENV, timeout=60)
+    assert r.returncode == 0, r.stderr
+    a_rows = list(csv.DictReader(open(out / "summary" / "partA_memcpy_impact.csv")))
+    assert a_rows[0]["direction"] == "h2d" and abs(float(a_rows[0]["degradation_pct"]) - 100 * (1 - 15.0 / 20.09)) < 0.5
+    b_rows = list(csv.DictReader(open(out / "summary" / "partB_size_impact.csv")))
+    assert [int(x["msg_bytes"]) for x in b_rows] == [4096, 65536]           # the size whose run failed (RetCode 3) is left out
+    assert abs(float(b_rows[1]["write_thr_ratio"]) - 0.7) < 1e-9
+    missing = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.contention_analyze", "--base_dir", str(tmp_path / "none")], capture_output=True, text=True, env=ENV)
+    assert missing.returncode == 1 and "missing summary csv" in missing.stderr
+
+
 def test_controller_gives_up_when_the_end_point_is_unreachable(tmp_path):
     r = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.controller", "--cpu_control_host", "127.0.0.1", "--cpu_control_port", str(free_port()),
                         "--baseline_restore_gib_s", "20", "--log_dir", str(tmp_path), "--control_timeout_s", "1"],
