@@ -65,6 +65,7 @@ def main():
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--gated", action="store_true")
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--ntok", type=int, default=0, help="gemm: token tile (0 = chosen by the package)")
     ap.add_argument("--one-tile-per-cta", action="store_true", help="gemm with more than 256 tokens: the one-tile-per-CTA kernel instead of the persistent form")
     ap.add_argument("--blocks", type=int, default=256)
     ap.add_argument("--ctas", type=int, default=0)
@@ -132,7 +133,7 @@ def main():
         x = torch.randn((a.m, a.k), dtype=torch.bfloat16, device=dev)
         w = torch.randn((a.n * (2 if a.gated else 1), a.k), dtype=torch.bfloat16, device=dev) / 64
         y = torch.empty((a.m, a.n), dtype=torch.bfloat16, device=dev)
-        ms, best = timed(lambda: ops.gemm(x, w, out=y, gated=a.gated, splits=a.splits or None, persistent=False if a.one_tile_per_cta else None),
+        ms, best = timed(lambda: ops.gemm(x, w, out=y, gated=a.gated, splits=a.splits or None, ntok=a.ntok, persistent=False if a.one_tile_per_cta else None),
                          a.warm, a.iters, flush)
         from skygdr_b200.ops.gemm import workspace_for
 

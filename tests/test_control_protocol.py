@@ -258,13 +258,15 @@ def test_window_step_cost_leaves_room_in_a_one_millisecond_window(ctl):
         for i in range(1, 257):
             d.report_usage(i, w * 100_000, w * 100_000, 1 << 20)
         d.step_window(now)
-    t0 = time.perf_counter()
-    n = 400
-    for w in range(n):
-        now += 1_000_000
-        d.step_window(now)
-    per_window_us = (time.perf_counter() - t0) / n * 1e6
-    assert per_window_us < 250.0, per_window_us                     # a quarter of the shortest window, with 256 flows
+    best = float("inf")
+    for _ in range(5):                                               # best of five batches: a busy host only ever adds time
+        t0 = time.perf_counter()
+        n = 100
+        for w in range(n):
+            now += 1_000_000
+            d.step_window(now)
+        best = min(best, (time.perf_counter() - t0) / n * 1e6)
+    assert best < 250.0, best                                        # a quarter of the shortest window, with 256 flows
 
 
 def test_native_page_pacer_grants_at_its_rate_and_lets_a_flow_catch_up(ctl):
