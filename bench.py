@@ -149,8 +149,10 @@ def main() -> int:
     status = eng.check_status()
 
     # ---- the library arm on the same GPUs, weights and cache, and the numeric check against it ----
-    baseline, check = None, None
-    if not args.no_baseline:
+    baseline, check, baseline_error = None, None, None
+
+    def library_arm_and_check():
+        nonlocal baseline, check
         forms, libs = {}, {}
         for form in (("allreduce", "rs_ag") if world > 1 else ("allreduce",)):
             libs[form] = NcclTPDecoder.from_engine(eng, collective=form)
@@ -190,8 +192,21 @@ def main() -> int:
             other_logits, other_ids = logits_of(libs["rs_ag"], state)
             check["library_forms_against_each_other"] = {**compare(other_logits, ref_logits),
                                                          "sampled_ids_equal": float((other_ids == ref_ids).float().mean())}
+        # The floor at every N: the library arm with each GEMM summed in fp32 in another order (same bf16 rounding points).
+        lib32 = NcclTPDecoder.from_engine(eng, collective="allreduce", fp32_matmul=True)
+        l32, _ = logits_of(lib32, state)
+        check["rounding_floor"] = {"what": "the library arm with every GEMM as an fp32 matmul of the same bf16 operands (another summation order, same "
+                                           "rounding points): how far correct implementations drift apart over the layers",
+                                   "library_against_it": compare(ref_logits, l32), "ours_against_it": compare(ours_logits, l32)}
+        del lib32
         check["status_after"] = eng.check_status()
         del libs
+
+    if not args.no_baseline:
+        try:
+            library_arm_and_check()
+        except Exception as e:          # the headline above stands on its own; a library arm that cannot run is reported, not fatal
+            baseline_error = f"{type(e).__name__}: {e}"[:300]
 
     prof = None
     if args.profile_step and hasattr(eng, "profile_step"):
@@ -223,7 +238,10 @@ def main() -> int:
         }
         if baseline:
             out["baseline"] = baseline
+        if check:
             out["check"] = check
+        if baseline_error:
+            out["baseline_error"] = baseline_error
         if prof:
             out["eager_step_profile_ms"] = prof
         print(json.dumps(out), flush=True)

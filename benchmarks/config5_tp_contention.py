@@ -91,6 +91,7 @@ def main():
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--baseline", default="", choices=["", "nccl"])
     ap.add_argument("--diagnose", action="store_true", help="also run each background flow alone, paced and unpaced")
+    ap.add_argument("--diagnose-offload", action="store_true", help="the offload alone under several pacing forms, each with an eager per-kernel profile")
     ap.add_argument("--repeats", type=int, default=3, help="every phase is run this many times in a row; all runs are reported")
     ap.add_argument("--out", default="results/config5.json")
     a = ap.parse_args()
@@ -151,7 +152,8 @@ def main():
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     quota = max(8, int(2 * sms * min(1.0, a.burst_budget_gbps / 700.0)))
 
-    def contended(scheduled: bool, do_bursts: bool = True, do_offload: bool = True, do_pacers: bool = True):
+    def contended(scheduled: bool, do_bursts: bool = True, do_offload: bool = True, do_pacers: bool = True, offload_gbps: float = 0.0,
+                  chunk_mb: int = 32, duty_ms=None, profile: bool = False):
         stop = threading.Event()
         xfer_ms = []
         pacers = []
@@ -159,12 +161,14 @@ def main():
             t_page.grant(t_flow.consumed, unlimited=False)
             pacers.append(ops.LocalPacer(t_page, a.burst_budget_gbps, window_ms=1.0).start(base=t_flow.consumed))
             base = o_page.read()["consumed_bytes"]
-            pacers.append(ops.LocalPacer(o_page, a.offload_gbps, window_ms=2.0).start(base=base))
+            pacers.append(ops.LocalPacer(o_page, offload_gbps or a.offload_gbps, window_ms=2.0).start(base=base))
         else:
             t_page.set_unlimited()
             o_page.set_unlimited()
         pc = C.PcieTaskConfig()
-        pc.device, pc.h2d, pc.chunk_bytes, pc.streams, pc.batch, pc.inflight = local, False, 32 << 20, 4, 2, 4
+        pc.device, pc.h2d, pc.chunk_bytes, pc.streams, pc.batch, pc.inflight = local, False, chunk_mb << 20, 4, 2, 4
+        if duty_ms:
+            pc.duty_on_ms, pc.duty_off_ms = duty_ms
         pc.seconds, pc.progress_ms = a.seconds + 2.0, 100
         pc.consumed_base = o_page.read()["consumed_bytes"]
         pc.set_credit_page(o_page.host_ptr)
@@ -187,6 +191,9 @@ def main():
         th = threading.Thread(target=bursts if do_bursts else (lambda: None), daemon=True)
         th.start()
         steps, ms, detail = timed_decode(eng, a.seconds, world, dev, state0, local)
+        if profile:                                # per-kernel-kind times of an eager step while the background flows still run
+            eng.profile_step(eng.max_ctx)
+            detail["eager_step_profile_ms"] = eng.profile_step(eng.max_ctx)
         stop.set()
         th.join()
         task.stop()
@@ -211,6 +218,15 @@ def main():
             res["phases"][name] = repeated(lambda: contended(name == "only_pacer_threads", **kw))
         res["phases"]["only_offload_paced"] = repeated(lambda: contended(True, do_bursts=False))
         res["phases"]["only_bursts_paced"] = repeated(lambda: contended(True, do_offload=False))
+    if a.diagnose_offload:
+        # what about a paced offload slows the decode step: its copy size, its sparseness, or the credit path itself
+        eng.profile_step(eng.max_ctx)
+        res["clean_eager_step_profile_ms"] = eng.profile_step(eng.max_ctx)
+        for name, kw in (("offload_paced_16gbps_32mb", dict()), ("offload_paced_16gbps_8mb", dict(chunk_mb=8)),
+                         ("offload_paced_100gbps_32mb", dict(offload_gbps=100.0))):
+            res["phases"][name] = contended(True, do_bursts=False, profile=True, **kw)
+        res["phases"]["offload_unpaced_duty_1ms_on_1ms_off"] = contended(False, do_bursts=False, duty_ms=(1, 1), profile=True)
+        res["phases"]["offload_unpaced"] = contended(False, do_bursts=False, profile=True)
     res["phases"]["contended_unscheduled"] = repeated(lambda: contended(False))
     if world > 1:
         dist.barrier()

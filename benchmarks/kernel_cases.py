@@ -32,7 +32,13 @@ def peaks():
     return 6650.0, 1590.0, "fallback"
 
 
+REPS = 1
+
+
 def timed(fn, warm, iters, flush):
+    """Median and best time of one call of fn in ms. With --reps R > 1 an event pair brackets R back-to-back calls (for inputs
+    larger than L2, with --no-flush): the first call absorbs the host's launch latency, which otherwise sits inside the interval
+    of a kernel that is shorter than the Python path that launches it."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
@@ -42,10 +48,11 @@ def timed(fn, warm, iters, flush):
             flush.zero_()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        fn()
+        for _ in range(REPS):
+            fn()
         b.record()
         torch.cuda.synchronize()
-        ts.append(a.elapsed_time(b))
+        ts.append(a.elapsed_time(b) / REPS)
     ts.sort()
     return ts[len(ts) // 2], ts[0]
 
@@ -66,6 +73,7 @@ def main():
     ap.add_argument("--gated", action="store_true")
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--ntok", type=int, default=0, help="gemm: token tile (0 = chosen by the package)")
+    ap.add_argument("--cluster", action="store_true", help="gemm with --splits: the K slices form a thread-block cluster and sum through distributed shared memory")
     ap.add_argument("--one-tile-per-cta", action="store_true", help="gemm with more than 256 tokens: the one-tile-per-CTA kernel instead of the persistent form")
     ap.add_argument("--blocks", type=int, default=256)
     ap.add_argument("--ctas", type=int, default=0)
@@ -73,8 +81,11 @@ def main():
     ap.add_argument("--op", default="axpy")
     ap.add_argument("--rows", type=int, default=16)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--reps", type=int, default=1, help="calls per event pair (see timed)")
     ap.add_argument("--impl", default="simt", choices=["simt", "tc", "sdpa"])
     a = ap.parse_args()
+    global REPS
+    REPS = max(1, a.reps)
     dev = "cuda"
     hbm, tf, src = peaks()
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -133,12 +144,12 @@ def main():
         x = torch.randn((a.m, a.k), dtype=torch.bfloat16, device=dev)
         w = torch.randn((a.n * (2 if a.gated else 1), a.k), dtype=torch.bfloat16, device=dev) / 64
         y = torch.empty((a.m, a.n), dtype=torch.bfloat16, device=dev)
-        ms, best = timed(lambda: ops.gemm(x, w, out=y, gated=a.gated, splits=a.splits or None, ntok=a.ntok, persistent=False if a.one_tile_per_cta else None),
+        ms, best = timed(lambda: ops.gemm(x, w, out=y, gated=a.gated, splits=a.splits or None, ntok=a.ntok, persistent=False if a.one_tile_per_cta else None, cluster=a.cluster),
                          a.warm, a.iters, flush)
         from skygdr_b200.ops.gemm import workspace_for
 
         out["status"] = ops.read_status(workspace_for(dev).status)["status_name"]
-        out["form"] = "one tile per CTA" if (a.one_tile_per_cta or a.m <= 256) else "persistent, two accumulators in TMEM"
+        out["form"] = ("one tile per CTA" + (", split-K inside a cluster" if a.cluster else "")) if (a.one_tile_per_cta or a.m <= 256) else "persistent, two accumulators in TMEM"
         byt = (w.numel() + x.numel() + y.numel()) * 2
         fl = 2.0 * a.m * w.shape[0] * a.k
         out.update(ms=ms, best_ms=best, bytes=byt, gbs=byt / ms / 1e6, frac_hbm=byt / ms / 1e6 / hbm, tflops=fl / ms / 1e9,

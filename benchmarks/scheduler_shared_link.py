@@ -183,22 +183,24 @@ def pct(xs, q):
 
 
 def pacing_error(log_path, flow_name, window_s):
-    """Achieved / granted for a paced flow, from the daemon's window log: bytes it moved in the windows in which it had a
-    budget, over the bytes those budgets added up to."""
+    """Achieved / granted for a paced flow, from the daemon's window log. A row holds the budget decided for the window that
+    begins and the rate measured over the window that just ended, so a budget is set against the rate of the flow's next row.
+    Windows in which the flow had nothing to send (no backlog, no bytes) are left out."""
     import csv
 
-    moved = granted = 0.0
-    windows = 0
     if not os.path.exists(log_path):
         return None
-    for r in csv.DictReader(open(log_path)):
-        if r["flow"] != flow_name:
+    rows = [r for r in csv.DictReader(open(log_path)) if r["flow"] == flow_name]
+    moved = granted = 0.0
+    windows = 0
+    for cur, nxt in zip(rows, rows[1:]):
+        b = float(cur["budget_bytes"])
+        got = float(nxt["inst_gbps"]) * 1e9 * window_s
+        if b < 0 or (got <= 0 and int(nxt["backlog_bytes"]) == 0):
             continue
-        b = float(r["budget_bytes"])
-        if b >= 0:
-            granted += b
-            moved += float(r["inst_gbps"]) * 1e9 * window_s
-            windows += 1
+        granted += b
+        moved += got
+        windows += 1
     return {"paced_windows": windows, "granted_gb": granted / 1e9, "moved_gb": moved / 1e9,
             "achieved_over_granted": (moved / granted) if granted else None}
 

@@ -357,7 +357,7 @@ static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, 
                  c10::optional<torch::Tensor> counters, torch::Tensor status, int ntok, bool persistent, bool cluster_split) {
     c10::cuda::CUDAGuard g(x.device());
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1, "row-major 2-D tensors");
-    GemmParams p;
+    GemmParams p{};
     memset(&p, 0, sizeof p);
     p.x = bf16_ptr(x); p.w = bf16_ptr(w); p.y = bf16_mut(y);
     p.M = (int)x.size(0); p.K = (int)x.size(1);
@@ -391,7 +391,7 @@ static void gemm_tp(torch::Tensor x, torch::Tensor w, torch::Tensor y, int split
                     c10::optional<torch::Tensor> counters, torch::Tensor status, py::tuple ag, py::tuple rs, int ntok, bool cluster_split) {
     c10::cuda::CUDAGuard g(x.device());
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "row-major 2-D tensors");
-    GemmParams p;
+    GemmParams p{};
     memset(&p, 0, sizeof p);
     p.x = bf16_ptr(x); p.w = bf16_ptr(w);
     p.M = (int)x.size(0); p.K = (int)x.size(1);

@@ -16,12 +16,17 @@ from ..models.qwen3 import Qwen3Decoder
 
 
 class NcclTPDecoder:
-    def __init__(self, cfg, weights, pool, batch, max_ctx, rank, world, attn, group=None, collective: str = "rs_ag"):
+    def __init__(self, cfg, weights, pool, batch, max_ctx, rank, world, attn, group=None, collective: str = "rs_ag", fp32_matmul: bool = False):
         """collective: "rs_ag" = reduce-scatter + all-gather around a token-sharded residual stream (four library collectives per
         layer); "allreduce" = one all-reduce after each row-parallel GEMM with the residual stream replicated (two per layer, the
-        form inference servers use for decode)."""
+        form inference servers use for decode).
+        fp32_matmul: every GEMM as torch.matmul on fp32 copies of the same bf16 operands, the result rounded to bf16 where the
+        bf16 GEMM rounds it. Products of bf16 numbers are exact in fp32, so this differs from the bf16 GEMM only in the order of
+        the fp32 sums: a third implementation with the same rounding points, used to measure how far two correct implementations
+        drift apart over the layers. Slow; for checks, not for timing."""
         assert collective in ("rs_ag", "allreduce")
         self.collective = collective
+        self.fp32_matmul = fp32_matmul
         self.cfg, self.w, self.pool, self.batch, self.max_ctx, self.rank, self.world, self.attn, self.group = \
             cfg, weights, pool, batch, max_ctx, rank, world, attn, group
         dev = pool.data.device
@@ -64,10 +69,20 @@ class NcclTPDecoder:
         else:
             out.copy_(x)
 
+    def _mm(self, x, w, out=None):
+        """x @ w^T in bf16 (cuBLAS), or with fp32_matmul on fp32 copies."""
+        if not self.fp32_matmul:
+            return torch.matmul(x, w.t(), out=out) if out is not None else torch.matmul(x, w.t())
+        r = torch.matmul(x.float(), w.float().t()).to(torch.bfloat16)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+
     @classmethod
-    def from_engine(cls, eng, collective: str = "rs_ag") -> "NcclTPDecoder":
+    def from_engine(cls, eng, collective: str = "rs_ag", fp32_matmul: bool = False) -> "NcclTPDecoder":
         b = cls(eng.cfg, eng.w, eng.pool, eng.max_batch, eng.max_ctx, getattr(eng, "rank", 0), getattr(eng, "world", 1), eng.attn,
-                collective=collective)
+                collective=collective, fp32_matmul=fp32_matmul)
         b.ids.copy_(eng.ids); b.positions.copy_(eng.positions); b.ctx_lens.copy_(eng.ctx_lens)
         b.block_table = eng.block_table
         return b
@@ -75,7 +90,7 @@ class NcclTPDecoder:
     def _pick(self, x_full) -> None:
         """lm_head on this rank's vocabulary slice, then the global argmax through two all-gathers."""
         w = self.w
-        logits = self.logits = torch.matmul(x_full, w.lm_head.t())
+        logits = self.logits = self._mm(x_full, w.lm_head)
         val, idx = logits.float().max(-1)
         self._all_gather(self.max_val.view(-1), val)
         self._all_gather(self.max_idx.view(-1), idx + w.vocab_lo)
@@ -91,15 +106,15 @@ class NcclTPDecoder:
                 ops.rmsnorm(resid, lw.ln1, cfg.eps, out=xn)
             else:
                 ops.rmsnorm(part, lw.ln1, cfg.eps, residual=resid, out=xn)
-            qkv = torch.matmul(xn, lw.qkv.t())
+            qkv = self._mm(xn, lw.qkv)
             ops.rope_append(qkv, lw.q_norm, lw.k_norm, self.pool, li, self.inv_freq, self.block_table, self.positions, self.qh, cfg.eps, q_out=self.q)
             self.attn(self.q, self.pool, li, self.block_table, self.ctx_lens, max_ctx=max_ctx, out=self.attn_out)
-            torch.matmul(self.attn_out.view(b, -1), lw.o.t(), out=part)
+            self._mm(self.attn_out.view(b, -1), lw.o, out=part)
             if self.world > 1:
                 dist.all_reduce(part, group=self.group)
             ops.rmsnorm(part, lw.ln2, cfg.eps, residual=resid, out=xn)
-            act = ops.silu_mul(torch.matmul(xn, lw.gate_up.t()))
-            torch.matmul(act, lw.down.t(), out=part)
+            act = ops.silu_mul(self._mm(xn, lw.gate_up))
+            self._mm(act, lw.down, out=part)
             if self.world > 1:
                 dist.all_reduce(part, group=self.group)
         ops.rmsnorm(part, w.final_norm, cfg.eps, residual=resid, out=xn)
@@ -119,16 +134,16 @@ class NcclTPDecoder:
             else:
                 ops.rmsnorm(self.h_local, lw.ln1, cfg.eps, residual=self.resid, out=self.xn_local)
             self._all_gather(self.x_full, self.xn_local)
-            qkv = torch.matmul(self.x_full, lw.qkv.t())
+            qkv = self._mm(self.x_full, lw.qkv)
             ops.rope_append(qkv, lw.q_norm, lw.k_norm, self.pool, li, self.inv_freq, self.block_table, self.positions, self.qh, cfg.eps, q_out=self.q)
             self.attn(self.q, self.pool, li, self.block_table, self.ctx_lens, max_ctx=max_ctx, out=self.attn_out)
-            torch.matmul(self.attn_out.view(b, -1), lw.o.t(), out=self.partial)
+            self._mm(self.attn_out.view(b, -1), lw.o, out=self.partial)
             self._reduce_scatter(self.h_local, self.partial)
             ops.rmsnorm(self.h_local, lw.ln2, cfg.eps, residual=self.resid, out=self.xn_local)
             self._all_gather(self.x_full, self.xn_local)
-            gu = torch.matmul(self.x_full, lw.gate_up.t())
+            gu = self._mm(self.x_full, lw.gate_up)
             act = ops.silu_mul(gu)
-            torch.matmul(act, lw.down.t(), out=self.partial)
+            self._mm(act, lw.down, out=self.partial)
             self._reduce_scatter(self.h_local, self.partial)
         ops.rmsnorm(self.h_local, w.final_norm, cfg.eps, residual=self.resid, out=self.xn_local)
         self._all_gather(self.x_full, self.xn_local)
