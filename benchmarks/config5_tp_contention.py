@@ -18,6 +18,7 @@ torch.distributed all-gather / reduce-scatter (NCCL) and torch.matmul (cuBLAS) i
 import argparse
 import json
 import os
+import subprocess
 import sys
 import threading
 import time
@@ -153,7 +154,7 @@ def main():
     quota = max(8, int(2 * sms * min(1.0, a.burst_budget_gbps / 700.0)))
 
     def contended(scheduled: bool, do_bursts: bool = True, do_offload: bool = True, do_pacers: bool = True, offload_gbps: float = 0.0,
-                  chunk_mb: int = 32, duty_ms=None, profile: bool = False):
+                  chunk_mb: int = 32, duty_ms=None, profile: bool = False, window_ms: float = 2.0, offload_in_child: bool = False):
         stop = threading.Event()
         xfer_ms = []
         pacers = []
@@ -161,23 +162,38 @@ def main():
             t_page.grant(t_flow.consumed, unlimited=False)
             pacers.append(ops.LocalPacer(t_page, a.burst_budget_gbps, window_ms=1.0).start(base=t_flow.consumed))
             base = o_page.read()["consumed_bytes"]
-            pacers.append(ops.LocalPacer(o_page, offload_gbps or a.offload_gbps, window_ms=2.0).start(base=base))
+            if not offload_in_child:
+                pacers.append(ops.LocalPacer(o_page, offload_gbps or a.offload_gbps, window_ms=window_ms).start(base=base))
         else:
             t_page.set_unlimited()
             o_page.set_unlimited()
         pc = C.PcieTaskConfig()
         pc.device, pc.h2d, pc.chunk_bytes, pc.streams, pc.batch, pc.inflight = local, False, chunk_mb << 20, 4, 2, 4
+        pc.min_issue_bytes = min(8 << 20, chunk_mb << 20)
         if duty_ms:
             pc.duty_on_ms, pc.duty_off_ms = duty_ms
         pc.seconds, pc.progress_ms = a.seconds + 2.0, 100
         pc.consumed_base = o_page.read()["consumed_bytes"]
         pc.set_credit_page(o_page.host_ptr)
         task = C.PcieTask(pc)
-        if do_offload:
+        child = None
+        if do_offload and offload_in_child:
+            # the same paced copy worker, but in a process (and CUDA context) of its own on this GPU
+            code = ("import sys,time; sys.path.insert(0, %r)\n"
+                    "from skygdr_b200 import ops\nfrom skygdr_b200._ext import load\nC = load()\n"
+                    "page = ops.CreditPage(flow_id=2, unlimited=False)\n"
+                    "pc = C.PcieTaskConfig(); pc.device, pc.h2d, pc.chunk_bytes, pc.streams, pc.batch, pc.inflight = %d, False, %d, 4, 2, 4\n"
+                    "pc.seconds, pc.progress_ms = %f, 100; pc.set_credit_page(page.host_ptr)\n"
+                    "t = C.PcieTask(pc); t.setup(); pacer = ops.LocalPacer(page, %f, window_ms=%f).start(base=0)\n"
+                    "print('READY', flush=True); t.start(); t.join(); pacer.stop(); print('BW', t.progress().avg_bw_gib_s * 1.073741824, flush=True)\n"
+                    % (ROOT, local, chunk_mb << 20, a.seconds + 1.0, offload_gbps or a.offload_gbps, window_ms))
+            child = subprocess.Popen([sys.executable, "-c", code], stdout=subprocess.PIPE, text=True)
+            child.stdout.readline()                                     # READY: its allocations are done
+        elif do_offload:
             task.setup()                       # pinned allocations stall the device: do them before anyone is timed
         if world > 1:
             dist.barrier()
-        if do_offload:
+        if do_offload and not offload_in_child:
             task.start()
 
         def bursts():
@@ -201,6 +217,9 @@ def main():
         for p in pacers:
             p.stop()
         pr = task.progress()
+        if child is not None:
+            tail = child.communicate(timeout=30)[0]
+            detail["offload_child_gb_s"] = float(tail.split("BW")[-1]) if "BW" in tail else None
         return {"tok_s": batch * steps / (ms * 1e-3), "vs_clean": batch * steps / (ms * 1e-3) / clean, "ms_per_step": ms / steps,
                 "burst_ms_mean": sum(xfer_ms) / max(1, len(xfer_ms)), "bursts": len(xfer_ms),
                 "burst_gbs": nb * geom.block_elems * 2 / 1e6 / (sum(xfer_ms) / max(1, len(xfer_ms))) if xfer_ms else None,
@@ -223,6 +242,8 @@ def main():
         eng.profile_step(eng.max_ctx)
         res["clean_eager_step_profile_ms"] = eng.profile_step(eng.max_ctx)
         for name, kw in (("offload_paced_16gbps_32mb", dict()), ("offload_paced_16gbps_8mb", dict(chunk_mb=8)),
+                         ("offload_paced_16gbps_4mb_quarter_ms_windows", dict(chunk_mb=4, window_ms=0.25)),
+                         ("offload_paced_16gbps_32mb_in_a_process_of_its_own", dict(offload_in_child=True)),
                          ("offload_paced_100gbps_32mb", dict(offload_gbps=100.0))):
             res["phases"][name] = contended(True, do_bursts=False, profile=True, **kw)
         res["phases"]["offload_unpaced_duty_1ms_on_1ms_off"] = contended(False, do_bursts=False, duty_ms=(1, 1), profile=True)

@@ -219,10 +219,6 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, in
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
 }
-// Asks for one box of a 2-D tensor map to be brought into L2 (no shared-memory destination, nothing to wait for).
-__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
-}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

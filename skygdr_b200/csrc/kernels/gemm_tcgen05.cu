@@ -366,7 +366,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 // on the MMA's M, tokens on N); no split-K, no tensor-parallel hooks: this is the plain projection of a prefill step.
 // Tiles are numbered token tile fastest, so the CTAs that run side by side share a few weight panels and the x tiles
 // stay in L2. Measured on B200 against the one-tile-per-CTA kernel above: 1118 against 790 TFLOP/s at 2048 x 4096 x 4096,
-// 1244 against 889 at 8192 x 12288 x 4096 gated.
+// 1244 against 889 at 8192 x 12288 x 4096 gated. The tensor pipe is busy 69-75 % of the active cycles: the ring holds three to
+// five stages in flight, about what a load from L2 takes under this traffic. Asking for every k-block into L2 a ring's depth
+// ahead of its load (cp.async.bulk.prefetch.tensor) was measured and made it slower (849 against 1082 TFLOP/s at
+// 2048 x 4096 x 4096, 1013 against 1335 at 8192 x 4096 x 4096), so the producer issues loads only.
 template <int NTOK, bool GATED>
 struct GemmPersistSmem {
     static constexpr int W_BYTES = BM * BK * 2;
@@ -411,28 +414,12 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
             tma_prefetch_desc(&tmap_w);
             tma_prefetch_desc(&tmap_x);
             pdl_wait();                                    // x is the previous kernel's output
-            // The ring holds STAGES - 1 stages in flight, which at one stage per 512 tensor-core cycles is less than a load takes
-            // when part of it comes from DRAM. So every k-block is also asked into L2 a ring's depth before its load is issued:
-            // by then the load is an L2 hit.
-            constexpr int PF_DIST = 2 * S::STAGES;
-            auto prefetch_l2 = [&](long long itx) {
-                const long long j = itx / nkb;
-                const long long tile = (long long)blockIdx.x + j * gridDim.x;
-                if (tile >= n_tiles || p.l2_prefetch_off) return;
-                const int kb = (int)(itx - j * nkb);
-                const int n0 = (int)(tile / tiles_m) * BM, t0 = (int)(tile % tiles_m) * NTOK;
-                tma_prefetch_l2_2d(&tmap_w, kb * BK, n0);
-                if (GATED) tma_prefetch_l2_2d(&tmap_w, kb * BK, p.N + n0);
-                tma_prefetch_l2_2d(&tmap_x, kb * BK, t0);
-            };
-            for (int i = S::STAGES; i < PF_DIST; ++i) prefetch_l2(i);
             long long it = 0;                              // k-blocks issued so far, over all tiles of this CTA
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const int n0 = (tile / tiles_m) * BM, t0 = (tile % tiles_m) * NTOK;
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = (int)(it % S::STAGES);
-                    prefetch_l2(it + PF_DIST);
                     if (it >= S::STAGES && !mbar_wait(&empty_bar[s], (uint32_t)((it / S::STAGES) - 1) & 1)) {
                         set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 61);
                         ok = false;
@@ -580,10 +567,7 @@ static cudaError_t launch_persistent_t(const GemmParams& p, const CUtensorMap& t
     if (cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); e != cudaSuccess) return e;
     const long long tiles = (long long)((p.N + BM - 1) / BM) * ((p.M + NTOK - 1) / NTOK);
     const int ctas = (int)std::min<long long>(tiles, sms > 0 ? sms : 1);     // one CTA per SM, each walks tiles cta, cta + ctas, ...
-    static const bool pf_off = [] { const char* v = getenv("SKYGDR_GEMM_L2_PREFETCH"); return v && v[0] == '0'; }();
-    GemmParams q = p;
-    q.l2_prefetch_off = pf_off ? 1 : 0;
-    return launch_pdl(kern, dim3(ctas), dim3(GEMM_THREADS), (size_t)S::TOTAL, stream, tw, tx, q);
+    return launch_pdl(kern, dim3(ctas), dim3(GEMM_THREADS), (size_t)S::TOTAL, stream, tw, tx, p);
 }
 
 int gemm_pick_ntok(int M, bool gated) {

@@ -61,8 +61,6 @@ struct GemmParams {
                               // shared memory; workspace and counters are not used
     int persistent;           // 1: one CTA per SM walks the output tiles with two accumulators in TMEM (many-token shapes; needs
                               // splits == 1, ntok 256 or 128, neither ag nor rs)
-    int l2_prefetch_off;      // persistent form: 1 = do not ask for k-blocks into L2 ahead of their loads (set from SKYGDR_GEMM_L2_PREFETCH=0,
-                              // a switch for measuring what the prefetch is worth)
 };
 
 int gemm_pick_ntok(int M, bool gated);

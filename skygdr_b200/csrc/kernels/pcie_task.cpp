@@ -191,7 +191,12 @@ void PcieTask::run() {
                         // Do not shred the flow into tiny copies when credit trickles in: wait for a worthwhile piece.
                         const uint64_t piece = std::min<uint64_t>(n, cfg_.min_issue_bytes);
                         if (granted - used < piece) break;
-                        n = std::min<uint64_t>(n, granted - used);
+                        // A copy cut to the credit at hand keeps a size that is a multiple of 1 MiB, of 4 KiB under a smaller
+                        // min_issue_bytes; the rest of the credit stays for the next copy.
+                        if (granted - used < n) {                                   // (never the final tail: that one is not cut)
+                            const uint64_t unit = piece >= (1ull << 20) ? (1ull << 20) : (piece >= 4096 ? 4096 : 1);
+                            n = (granted - used) / unit * unit;
+                        }
                     }
                     if (n == 0) break;
                     void* h = ln.host;

@@ -24,6 +24,12 @@ def _run(world, script, timeout=240, **extra_env):
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
 
 
+def _why(r) -> str:
+    """What a failed child run said: its own TP_WORKER_FAIL lines first (the launcher's summary hides them), then the tails."""
+    own = [ln for ln in r.stdout.splitlines() if "TP_WORKER_FAIL" in ln]
+    return "\n".join(own[:8]) + "\n" + r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def _gpus() -> int:
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
@@ -36,7 +42,7 @@ def test_tensor_parallel_decode_and_peer_kv_transfer(world, collective):
     if _gpus() < world:
         pytest.skip(f"needs {world} GPUs")
     r = _run(world, "tp_worker.py", SKYGDR_TP_COLLECTIVE=collective)
-    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, _why(r)
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
@@ -46,7 +52,7 @@ def test_tensor_parallel_decode_at_the_model_widths(world):
     if _gpus() < world:
         pytest.skip(f"needs {world} GPUs")
     r = _run(world, "tp_worker.py", timeout=400, SKYGDR_TP_SHAPE="real")
-    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, _why(r)
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
