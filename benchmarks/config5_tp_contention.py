@@ -8,10 +8,14 @@ and offloads KV to pinned host memory.
 Every phase is run --repeats times in a row (median reported, all runs kept), with one CUDA event per replay (per-step device
 times of this rank: p50 / p99 / max and the share of steps more than 20 % over the median) and the SM clocks and throttle
 reasons sampled while it ran, so that a slow mode can be told from sparse stalls and from a clock change.
-Phases per run: clean decode; contended, unscheduled (bursts and offload unpaced); contended, scheduled (the offload is
-held to its offered rate by its credit page, the bursts are paced to `--burst-budget-gbps`). Each rank r receives bursts
-from rank (r+1) % N through the paged transfer kernel and runs one offload task (chunked async copies, low-priority
-streams). Decode tokens/s is device-timed (CUDA events around graph replays), max over ranks.
+Phases per run, the three arms of the reference's case study (src/tools/pcie_case_study_analyze.py:140-154) after a clean one:
+clean decode; contended, unscheduled = always HIGH (bursts and offload unpaced); contended, always LOW (static pacing: the
+offload is held to `--offload-gbps` by its credit page, the bursts to `--burst-budget-gbps`); contended, controlled (a daemon
+core per rank, policy target_track, 20 ms windows: the decode step is the protected flow with 95 % of its clean HBM rate as
+target, bursts and offload are best effort on the same capacity, this GPU's HBM, and get what the policy leaves them).
+Each rank r receives bursts from rank (r+1) % N through the paged transfer kernel and runs one offload task (chunked async
+copies). Decode tokens/s is device-timed (CUDA events around graph replays), max over ranks. `--diagnose` and
+`--diagnose-offload` run the background flows one at a time and the offload under several pacing forms.
 `--baseline nccl` adds the comparison arm the fused collectives are measured against: the same decoder with
 torch.distributed all-gather / reduce-scatter (NCCL) and torch.matmul (cuBLAS) in place of the fused kernels.
 """
@@ -37,7 +41,7 @@ from skygdr_b200.parallel.symm import SymmetricHeap  # noqa: E402
 from skygdr_b200.parallel.tp import build_decode_engine  # noqa: E402
 
 
-def timed_decode(eng, seconds, world, dev, state=None, local=0):
+def timed_decode(eng, seconds, world, dev, state=None, local=0, progress=None):
     """Replays the decode graph for `seconds`; returns (steps, device milliseconds as the max over ranks, detail). Every replay
     is followed by a CUDA event, so `detail` has this rank's per-step device times (a slow mode shows as a shifted median, sparse
     stalls as a long tail) and the SM clocks and throttle reasons sampled while the phase ran."""
@@ -45,6 +49,12 @@ def timed_decode(eng, seconds, world, dev, state=None, local=0):
 
     if state is not None:                       # every phase starts from the same context lengths
         eng.ids.copy_(state[0]); eng.positions.copy_(state[1]); eng.ctx_lens.copy_(state[2])
+    if world > 1:
+        dist.barrier()                          # enter together: a step's kernels wait for their peers for two seconds at most
+    if hasattr(eng, "clear_status"):
+        eng.clear_status()                      # an earlier phase's give-up must not switch this phase's waits off (each phase reports its own status)
+        if world > 1:
+            dist.barrier()
     for _ in range(3):
         eng.replay()
     if world > 1:
@@ -64,6 +74,8 @@ def timed_decode(eng, seconds, world, dev, state=None, local=0):
                 marks.append(e)
             marks[-1].synchronize()
             steps += 8
+            if progress is not None:
+                progress(steps)
             # all ranks must stop after the same number of steps: rank 0 decides
             n[0] = 1.0 if time.perf_counter() - t0 >= seconds else 0.0
             if world > 1:
@@ -76,7 +88,8 @@ def timed_decode(eng, seconds, world, dev, state=None, local=0):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     med = per_step[len(per_step) // 2]
-    detail = {"step_ms_p50": med, "step_ms_p99": per_step[min(len(per_step) - 1, int(0.99 * len(per_step)))], "step_ms_max": per_step[-1],
+    status = eng.check_status() if hasattr(eng, "check_status") else "OK"     # a wait that gave up makes later kernels skip theirs: such a phase does not count
+    detail = {"kernel_status": status, "step_ms_p50": med, "step_ms_p99": per_step[min(len(per_step) - 1, int(0.99 * len(per_step)))], "step_ms_max": per_step[-1],
               "steps_over_1.2x_median": sum(1 for x in per_step if x > 1.2 * med) / len(per_step), "clocks": clocks.summary()}
     return steps, float(t[0]), detail
 
@@ -92,6 +105,7 @@ def main():
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--baseline", default="", choices=["", "nccl"])
     ap.add_argument("--diagnose", action="store_true", help="also run each background flow alone, paced and unpaced")
+    ap.add_argument("--offload-ctas", type=int, default=8, help="CTAs of the offload when it runs as a kernel")
     ap.add_argument("--diagnose-offload", action="store_true", help="the offload alone under several pacing forms, each with an eager per-kernel profile")
     ap.add_argument("--repeats", type=int, default=3, help="every phase is run this many times in a row; all runs are reported")
     ap.add_argument("--out", default="results/config5.json")
@@ -130,6 +144,10 @@ def main():
 
     res["phases"]["clean"] = repeated(clean_run)
     clean = res["phases"]["clean"]["tok_s"]
+    step_bytes = eng.bytes_per_step(ctx)
+    clean_gbs = step_bytes / (res["phases"]["clean"]["ms_per_step"] * 1e-3) / 1e9          # the decode step as a flow: HBM bytes per second
+    peaks = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    hbm_gbs = json.load(open(peaks))["hbm_gbs"] if os.path.exists(peaks) else 6650.0
 
     # ---- background flows ----
     geom = ops.KVGeometry()
@@ -149,24 +167,90 @@ def main():
     t_flow = ops.KvTransferFlow(dev, page=t_page, max_wait_ms=20.0)
     xfer_stream = torch.cuda.Stream(dev)
     o_page = ops.CreditPage(flow_id=2, unlimited=True)
+    # the offload's other engine: the transfer kernel with a mapped host buffer as its destination (same layout, a few CTAs)
+    n_off = min(nb, max(8, int(256e6 / (geom.block_elems * 2))))
+    off_hptr, off_dptr = C.host_alloc_mapped(n_off * geom.block_elems * 2)
+    host_pool = ops.RemotePool(off_dptr, src.strides, geom.kv_heads)
+    off_sb, off_db = torch.randperm(nb)[:n_off].int().to(dev), torch.arange(n_off).int().to(dev)
+    ok_page = ops.CreditPage(flow_id=3, unlimited=True)          # a page of its own: each engine keeps its own byte counters
+    o_flow = ops.KvTransferFlow(dev, page=ok_page, max_wait_ms=20.0)
+    off_stream = torch.cuda.Stream(dev)
 
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     quota = max(8, int(2 * sms * min(1.0, a.burst_budget_gbps / 700.0)))
 
     def contended(scheduled: bool, do_bursts: bool = True, do_offload: bool = True, do_pacers: bool = True, offload_gbps: float = 0.0,
-                  chunk_mb: int = 32, duty_ms=None, profile: bool = False, window_ms: float = 2.0, offload_in_child: bool = False):
+                  chunk_mb: int = 32, duty_ms=None, profile: bool = False, window_ms: float = 2.0, offload_in_child: bool = False, offload_engine: str = "copy", controlled: bool = False):
         stop = threading.Event()
-        xfer_ms = []
+        xfer_ms, xfer_detail = [], []
         pacers = []
-        if scheduled and do_pacers:
+        decode_steps = {"n": 0}
+        ctl_log = {"windows": 0, "paced_windows": 0, "decisions": {}}
+        if controlled:
+            # The closed loop: the decode step is the protected flow (its bytes are the HBM bytes of its steps, its target 95 % of
+            # the clean rate), bursts and offload are best effort on the same capacity, this GPU's HBM. The daemon core runs in
+            # this process (one per rank) with policy target_track and 20 ms windows; its decisions become the flows' grants.
+            from skygdr_b200.control import ctl
+
+            dc = ctl.DaemonConfig()
+            # 20 ms windows and a 200 ms smoothing span: the decode flow's progress is known at every eighth step (60 ms)
+            dc.page_dir, dc.capacity_gbps, dc.window_ns, dc.policy = "", hbm_gbs, 20_000_000, "target_track"
+            dc.smooth_windows = 10
+            dc.lease_ns = 3600 * 10**9
+            dc.pcfg.util_threshold_pct = 0.0
+            core = ctl.DaemonCore(dc)
+            now0 = time.perf_counter_ns()
+            core.handle_line("REGISTER decode high %.1f decode" % (0.95 * clean_gbs), now0)
+            core.handle_line("REGISTER kv_burst besteffort 0 kv_transfer", now0)
+            core.handle_line("REGISTER kv_offload besteffort 0 kv_offload", now0)
+            t_page.grant(t_flow.consumed, unlimited=True)
+            o_page.set_unlimited()
+
+            def control():
+                t_prev = time.perf_counter()
+                granted = {2: float(t_flow.consumed), 3: float(o_page.read()["consumed_bytes"])}
+                while not stop.is_set():
+                    now = time.perf_counter()
+                    dt, t_prev = now - t_prev, now
+                    done = decode_steps["n"] * step_bytes
+                    core.report_usage(1, done, done, 1 << 40)
+                    for fid, page in ((2, t_page), (3, o_page)):
+                        u = page.read()
+                        core.report_usage(fid, u["consumed_bytes"], u["completed_bytes"], 1 << 30)
+                    core.step_window(time.perf_counter_ns())
+                    ctl_log["windows"] += 1
+                    for fid, page in ((2, t_page), (3, o_page)):
+                        f = core.page_fields(fid)
+                        if f["unlimited"]:
+                            page.set_unlimited()
+                        else:
+                            ctl_log["paced_windows"] += 1
+                            rate = f["budget_per_window"] / 0.020
+                            used = float(page.read()["consumed_bytes"])
+                            # never less than a window's worth ahead of what the flow has used: a launch that is in flight when the
+                            # first budget arrives must not find the page empty
+                            granted[fid] = min(max(granted[fid], used) + rate * max(dt, 0.020), used + rate * 0.060 + (8 << 20))
+                            page.grant(int(granted[fid]), unlimited=False)
+                            ctl_log["decisions"][fid] = round(rate / 1e9, 1)          # the last budget of this flow, GB/s
+                            lo = ctl_log.setdefault("lowest_budget_gbps", {})
+                            lo[fid] = min(lo.get(fid, 1e30), round(rate / 1e9, 1))
+                            hd = ctl_log.setdefault("least_headroom_gb", {})
+                            hd[fid] = min(hd.get(fid, 1e30), round((granted[fid] - used) / 1e9, 3))
+                    time.sleep(0.020)
+
+        elif scheduled and do_pacers:
             t_page.grant(t_flow.consumed, unlimited=False)
             pacers.append(ops.LocalPacer(t_page, a.burst_budget_gbps, window_ms=1.0).start(base=t_flow.consumed))
             base = o_page.read()["consumed_bytes"]
-            if not offload_in_child:
+            if offload_engine == "kernel":
+                ok_page.grant(o_flow.consumed, unlimited=False)
+                pacers.append(ops.LocalPacer(ok_page, offload_gbps or a.offload_gbps, window_ms=window_ms).start(base=o_flow.consumed))
+            elif not offload_in_child:
                 pacers.append(ops.LocalPacer(o_page, offload_gbps or a.offload_gbps, window_ms=window_ms).start(base=base))
         else:
             t_page.set_unlimited()
             o_page.set_unlimited()
+            ok_page.set_unlimited()
         pc = C.PcieTaskConfig()
         pc.device, pc.h2d, pc.chunk_bytes, pc.streams, pc.batch, pc.inflight = local, False, chunk_mb << 20, 4, 2, 4
         pc.min_issue_bytes = min(8 << 20, chunk_mb << 20)
@@ -189,11 +273,11 @@ def main():
                     % (ROOT, local, chunk_mb << 20, a.seconds + 1.0, offload_gbps or a.offload_gbps, window_ms))
             child = subprocess.Popen([sys.executable, "-c", code], stdout=subprocess.PIPE, text=True)
             child.stdout.readline()                                     # READY: its allocations are done
-        elif do_offload:
+        elif do_offload and offload_engine == "copy":
             task.setup()                       # pinned allocations stall the device: do them before anyone is timed
         if world > 1:
             dist.barrier()
-        if do_offload and not offload_in_child:
+        if do_offload and not offload_in_child and offload_engine == "copy":
             task.start()
 
         def bursts():
@@ -202,16 +286,44 @@ def main():
                     # scheduled: the paced flow also gets an SM quota in proportion to its budget
                     st = t_flow.transfer_to_completion(src, [remote], sp, dp, ctas=quota if scheduled else None)
                 xfer_ms.append(st["device_time_ms"])
+                xfer_detail.append((round(st["device_time_ms"], 3), st["launches"], st["status"], round(st["stall_ns"] * 1e-6, 3)))
                 stop.wait(a.burst_every_ms / 1e3)
+
+        koff = {"bytes": 0, "seconds": 0.0}
+
+        def kernel_offload():
+            # the offload as a kernel: a few CTAs store pages into mapped host memory and check the credit page chunk by chunk
+            t0k = time.perf_counter()
+            while not stop.is_set():
+                with torch.cuda.stream(off_stream):
+                    st = o_flow.transfer_to_completion(src, [host_pool], off_sb, off_db, keep_layout=True, ctas=a.offload_ctas)
+                koff["bytes"] += st["bytes_done"]
+            koff["seconds"] = time.perf_counter() - t0k
 
         th = threading.Thread(target=bursts if do_bursts else (lambda: None), daemon=True)
         th.start()
-        steps, ms, detail = timed_decode(eng, a.seconds, world, dev, state0, local)
+        th_k = None
+        if do_offload and offload_engine == "kernel":
+            th_k = threading.Thread(target=kernel_offload, daemon=True)
+            th_k.start()
+        th_c = None
+        if controlled:
+            th_c = threading.Thread(target=control, daemon=True)
+            th_c.start()
+        steps, ms, detail = timed_decode(eng, a.seconds, world, dev, state0, local,
+                                         progress=(lambda n: decode_steps.__setitem__("n", n)) if controlled else None)
+        if controlled:
+            detail["control_loop"] = dict(ctl_log)
         if profile:                                # per-kernel-kind times of an eager step while the background flows still run
             eng.profile_step(eng.max_ctx)
             detail["eager_step_profile_ms"] = eng.profile_step(eng.max_ctx)
         stop.set()
         th.join()
+        if th_c is not None:
+            th_c.join()
+        if th_k is not None:
+            th_k.join()
+            detail["offload_kernel_gb_s"] = koff["bytes"] / max(koff["seconds"], 1e-9) / 1e9
         task.stop()
         task.join()
         for p in pacers:
@@ -221,8 +333,8 @@ def main():
             tail = child.communicate(timeout=30)[0]
             detail["offload_child_gb_s"] = float(tail.split("BW")[-1]) if "BW" in tail else None
         return {"tok_s": batch * steps / (ms * 1e-3), "vs_clean": batch * steps / (ms * 1e-3) / clean, "ms_per_step": ms / steps,
-                "burst_ms_mean": sum(xfer_ms) / max(1, len(xfer_ms)), "bursts": len(xfer_ms),
-                "burst_gbs": nb * geom.block_elems * 2 / 1e6 / (sum(xfer_ms) / max(1, len(xfer_ms))) if xfer_ms else None,
+                "burst_ms_mean": sum(xfer_ms) / max(1, len(xfer_ms)), "bursts": len(xfer_ms), "burst_ms_launches_status_stall_ms": xfer_detail,
+                "burst_gbs": nb * geom.block_elems * 2 / 1e6 / sorted(xfer_ms)[len(xfer_ms) // 2] if xfer_ms else None,       # of the median burst
                 "offload_gb_s": pr.avg_bw_gib_s * 1.073741824, **detail}
 
     # one untimed pass of both background flows: the transfer kernel's first launch loads its module and the copy worker's set-up
@@ -241,17 +353,22 @@ def main():
         # what about a paced offload slows the decode step: its copy size, its sparseness, or the credit path itself
         eng.profile_step(eng.max_ctx)
         res["clean_eager_step_profile_ms"] = eng.profile_step(eng.max_ctx)
-        for name, kw in (("offload_paced_16gbps_32mb", dict()), ("offload_paced_16gbps_8mb", dict(chunk_mb=8)),
+        for name, kw in (("offload_kernel_paced_16gbps", dict(offload_engine="kernel")),
+                         ("offload_paced_16gbps_32mb", dict()), ("offload_paced_16gbps_8mb", dict(chunk_mb=8)),
                          ("offload_paced_16gbps_4mb_quarter_ms_windows", dict(chunk_mb=4, window_ms=0.25)),
-                         ("offload_paced_16gbps_32mb_in_a_process_of_its_own", dict(offload_in_child=True)),
-                         ("offload_paced_100gbps_32mb", dict(offload_gbps=100.0))):
+                         ("offload_paced_100gbps_32mb", dict(offload_gbps=100.0)),
+                         ("offload_paced_16gbps_32mb_in_a_process_of_its_own", dict(offload_in_child=True))):
             res["phases"][name] = contended(True, do_bursts=False, profile=True, **kw)
         res["phases"]["offload_unpaced_duty_1ms_on_1ms_off"] = contended(False, do_bursts=False, duty_ms=(1, 1), profile=True)
+        res["phases"]["offload_kernel_unpaced"] = contended(False, do_bursts=False, profile=True, offload_engine="kernel")
         res["phases"]["offload_unpaced"] = contended(False, do_bursts=False, profile=True)
     res["phases"]["contended_unscheduled"] = repeated(lambda: contended(False))
     if world > 1:
         dist.barrier()
-    res["phases"]["contended_scheduled"] = repeated(lambda: contended(True))
+    res["phases"]["contended_always_low"] = repeated(lambda: contended(True))
+    if world > 1:
+        dist.barrier()
+    res["phases"]["contended_controlled"] = repeated(lambda: contended(False, controlled=True))
     res["kernel_status"] = eng.check_status()
 
     if a.baseline == "nccl" and world > 1:

@@ -282,6 +282,14 @@ class TPDecoder:
                 return f"{st['status_name']}:{st['detail']}"
         return "OK"
 
+    def clear_status(self) -> None:
+        """Back to "OK" after a wait that gave up. Kernels skip their peer waits while the status is not OK (one lost peer must
+        not cost a timeout per kernel), so a job that carries on after such an event clears it on every rank between two steps.
+        Arrival counters keep counting through a skipped wait, so the ranks stay in step."""
+        torch.cuda.synchronize(self.device)
+        self.status.zero_()
+        self.attn.status.zero_()
+
     def bytes_per_step(self, ctx: torch.Tensor) -> int:
         return _bytes_per_step(self.cfg, self.w, ctx, self.kh, self.batch)
 
