@@ -73,6 +73,7 @@ def main():
     ap.add_argument("--gated", action="store_true")
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--ntok", type=int, default=0, help="gemm: token tile (0 = chosen by the package)")
+    ap.add_argument("--tile", default="", choices=["", "wide", "narrow"], help="gemm with more than 256 tokens: 256 x 256 or 128 x 256 tiles (default: chosen by the package)")
     ap.add_argument("--cluster", action="store_true", help="gemm with --splits: the K slices form a thread-block cluster and sum through distributed shared memory")
     ap.add_argument("--one-tile-per-cta", action="store_true", help="gemm with more than 256 tokens: the one-tile-per-CTA kernel instead of the persistent form")
     ap.add_argument("--blocks", type=int, default=256)
@@ -144,12 +145,12 @@ def main():
         x = torch.randn((a.m, a.k), dtype=torch.bfloat16, device=dev)
         w = torch.randn((a.n * (2 if a.gated else 1), a.k), dtype=torch.bfloat16, device=dev) / 64
         y = torch.empty((a.m, a.n), dtype=torch.bfloat16, device=dev)
-        ms, best = timed(lambda: ops.gemm(x, w, out=y, gated=a.gated, splits=a.splits or None, ntok=a.ntok, persistent=False if a.one_tile_per_cta else None, cluster=a.cluster),
+        ms, best = timed(lambda: ops.gemm(x, w, out=y, gated=a.gated, splits=a.splits or None, ntok=a.ntok, persistent=False if a.one_tile_per_cta else (a.tile or None), cluster=a.cluster),
                          a.warm, a.iters, flush)
         from skygdr_b200.ops.gemm import workspace_for
 
         out["status"] = ops.read_status(workspace_for(dev).status)["status_name"]
-        out["form"] = ("one tile per CTA" + (", split-K inside a cluster" if a.cluster else "")) if (a.one_tile_per_cta or a.m <= 256) else "persistent, two accumulators in TMEM"
+        out["form"] = ("one tile per CTA" + (", split-K inside a cluster" if a.cluster else "")) if (a.one_tile_per_cta or a.m <= 256) else "persistent, " + (a.tile or "tile chosen by the package")
         byt = (w.numel() + x.numel() + y.numel()) * 2
         fl = 2.0 * a.m * w.shape[0] * a.k
         out.update(ms=ms, best_ms=best, bytes=byt, gbs=byt / ms / 1e6, frac_hbm=byt / ms / 1e6 / hbm, tflops=fl / ms / 1e9,

@@ -354,7 +354,7 @@ static void sample(torch::Tensor logits, torch::Tensor out, double temperature, 
 // ---- GEMM ----
 // ss_in / ss_out: fp32 vectors of at least M entries (see GemmNormFuse); residual: y is the residual stream, updated in place.
 static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, bool gated, c10::optional<torch::Tensor> workspace,
-                 c10::optional<torch::Tensor> counters, torch::Tensor status, int ntok, bool persistent, bool cluster_split) {
+                 c10::optional<torch::Tensor> counters, torch::Tensor status, int ntok, int persistent, bool cluster_split) {
     c10::cuda::CUDAGuard g(x.device());
     TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1, "row-major 2-D tensors");
     GemmParams p{};
@@ -374,7 +374,7 @@ static void gemm(torch::Tensor x, torch::Tensor w, torch::Tensor y, int splits, 
     }
     p.status = status_ptr(status);
     TORCH_CHECK(!persistent || splits == 1, "the persistent form is the plain projection without split-K");
-    p.persistent = persistent ? 1 : 0;
+    p.persistent = persistent;          // 0: one tile per CTA, 1: persistent with 128-row tiles, 2: persistent with 256 x 256 tiles
     SKY_CUDA_CHECK(launch_gemm(p, cur_stream()));
 }
 
@@ -533,7 +533,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("argmax", &argmax);
     m.def("sample", &sample, py::arg("logits"), py::arg("out"), py::arg("temperature"), py::arg("seed"), py::arg("positions") = py::none());
     m.def("gemm", &gemm, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("splits"), py::arg("gated"), py::arg("workspace"), py::arg("counters"),
-          py::arg("status"), py::arg("ntok"), py::arg("persistent") = false, py::arg("cluster_split") = false);
+          py::arg("status"), py::arg("ntok"), py::arg("persistent") = 0, py::arg("cluster_split") = false);
     m.def("gemm_tp", &gemm_tp, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("splits"), py::arg("gated"), py::arg("workspace"), py::arg("counters"),
           py::arg("status"), py::arg("ag"), py::arg("rs"), py::arg("ntok"), py::arg("cluster_split") = false);
     m.def("tp_norm", &tp_norm, py::arg("rs_buf"), py::arg("rs_counter"), py::arg("rs_seq"), py::arg("resid"), py::arg("w"), py::arg("ag_dst"),

@@ -33,10 +33,11 @@ bool pdl_enabled() {
 // rows. The values are staged through shared memory so that each row leaves as 16-byte pieces, 256 contiguous bytes
 // per row, instead of one 2-byte store per element: that matters most when the destination is a peer over NVLink.
 // Only the first `count` rows are stored (the cluster form hands a CTA fewer than 16 token columns at a time).
-__device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16* stage, int t_base, int n0, int r, float* vals, int count = 16) {
+__device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16* stage, int t_base, int n0, int r, float* vals, int count = 16,
+                                              int bar = 3) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) stage[j * 128 + r] = __float2bfloat16(vals[j]);
-    asm volatile("bar.sync 3, 128;" ::: "memory");
+    asm volatile("bar.sync %0, 128;" ::"r"(bar) : "memory");
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
         const int idx = r + 128 * k, j = idx >> 4, ch = idx & 15;
@@ -67,7 +68,7 @@ __device__ __forceinline__ void store_chunk16(const GemmParams& p, __nv_bfloat16
             }
         }
     }
-    asm volatile("bar.sync 3, 128;" ::: "memory");
+    asm volatile("bar.sync %0, 128;" ::"r"(bar) : "memory");
 }
 
 // Thread-block cluster pieces of the split-K form below: the CTAs of one output tile (one per K range) form a cluster and
@@ -510,6 +511,142 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
 }
 
 // ---------------------------------------------------------------------------
+// Persistent form with a tile of 256 weight rows x 256 tokens per CTA: two 128-row MMAs per k-block share one token operand, so
+// a stage of 64 KB feeds 1024 tensor-core cycles (64 bytes per cycle and SM from L2 instead of 96) and the three stages that
+// fit cover the load latency that bounds the kernel above. The two accumulators fill all 512 TMEM columns, so a tile's
+// epilogue is not overlapped with the next tile's MMAs (its loads are: the producer runs on); two groups of four epilogue
+// warps, one per accumulator, keep it short. Ungated, N a multiple of 256. Measured on B200 against the kernel above (TFLOP/s):
+// 1220 / 1137 at 2048 x 4096 x 4096, 1420 / 1333 at 8192 x 4096 x 12288, 1362 / 1391 at 8192 x 4096 x 4096 (half as many tiles
+// leave the last round emptier there); ops.gemm.wide_tiles_pay chooses between the two per shape.
+struct GemmWideSmem {
+    static constexpr int W_BYTES = BM * BK * 2;                 // one 128-row weight block
+    static constexpr int X_BYTES = 256 * BK * 2;
+    static constexpr int STAGE_BYTES = 2 * W_BYTES + X_BYTES;   // 64 KB
+    static constexpr int STAGES = 3;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024;
+    static constexpr int THREADS = 64 + 256;                    // producer warp, MMA warp, two epilogue groups of four warps
+};
+
+__global__ void __launch_bounds__(GemmWideSmem::THREADS, 1)
+gemm_persistent_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+    using S = GemmWideSmem;
+    constexpr int NTOK = 256;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], acc_full, acc_empty;
+    __shared__ uint32_t tmem_slot;
+    __shared__ __align__(16) __nv_bfloat16 stage[2][16 * 128];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (p.M + NTOK - 1) / NTOK, tiles_n = p.N / (2 * BM);
+    const int n_tiles = tiles_m * tiles_n;
+    const int nkb = p.K / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&acc_full, 1);
+        mbar_init(&acc_empty, 2);                          // one arrival per epilogue group
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_w);
+            tma_prefetch_desc(&tmap_x);
+            pdl_wait();                                    // x is the previous kernel's output
+            long long it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int n0 = (tile / tiles_m) * 2 * BM, t0 = (tile % tiles_m) * NTOK;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % S::STAGES);
+                    if (it >= S::STAGES && !mbar_wait(&empty_bar[s], (uint32_t)((it / S::STAGES) - 1) & 1)) {
+                        set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 71);
+                        ok = false;
+                        break;
+                    }
+                    unsigned char* st = smem + s * S::STAGE_BYTES;
+                    mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+                    tma_load_2d(st, &tmap_w, kb * BK, n0, &full_bar[s]);
+                    tma_load_2d(st + S::W_BYTES, &tmap_w, kb * BK, n0 + BM, &full_bar[s]);
+                    tma_load_2d(st + 2 * S::W_BYTES, &tmap_x, kb * BK, t0, &full_bar[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, NTOK);
+            long long it = 0;
+            int j = 0;
+            bool ok = true;
+            pdl_wait();                                    // bounded waits start when the previous kernel is done
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
+                // both epilogue groups must have drained the accumulators of the previous tile
+                if (j >= 1 && !mbar_wait(&acc_empty, (uint32_t)(j - 1) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 72); break; }
+                tc_fence_after();
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % S::STAGES);
+                    if (!mbar_wait(&full_bar[s], (uint32_t)(it / S::STAGES) & 1)) { set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 73); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t st = smem_u32(smem + s * S::STAGE_BYTES);
+                    const uint64_t a0 = umma_desc_k_sw128(st);
+                    const uint64_t a1 = umma_desc_k_sw128(st + S::W_BYTES);
+                    const uint64_t b = umma_desc_k_sw128(st + 2 * S::W_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint32_t accum = (kb | k) ? 1u : 0u;
+                        tc_mma_f16(tmem_base, a0 + 2 * k, b + 2 * k, idesc, accum);
+                        tc_mma_f16(tmem_base + NTOK, a1 + 2 * k, b + 2 * k, idesc, accum);
+                    }
+                    tc_commit(&empty_bar[s]);
+                }
+                if (ok) tc_commit(&acc_full);
+            }
+        }
+    } else {
+        // ---- epilogue: group g = accumulator g = weight rows n0 + 128 g ..; warp w reads TMEM lanes 32 (w % 4) .. +31 ----
+        const int g = (warp - 2) >> 2;
+        const int slice = warp & 3;
+        const int r = slice * 32 + lane;
+        const int bar = 3 + g;
+        pdl_wait();
+        int j = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
+            const int n0 = (tile / tiles_m) * 2 * BM + g * BM, t0 = (tile % tiles_m) * NTOK;
+            const uint32_t mine = mbar_wait(&acc_full, (uint32_t)j & 1) ? 1u : 0u;
+            uint32_t n_ok;
+            asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.popc.u32 %0, %2, 128, q;\n\t}" : "=r"(n_ok) : "r"(mine), "r"(bar) : "memory");
+            if (n_ok != 128u) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 74); break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (uint32_t)(g * NTOK) + ((uint32_t)(slice * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < NTOK; c += 16) {
+                if (t0 + c >= p.M) break;                  // uniform over the group: rows past M are never stored
+                uint32_t v[16];
+                tmem_ld_x16(taddr + c, v);
+                tc_wait_ld();
+                float vals[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) vals[i] = __uint_as_float(v[i]);
+                store_chunk16(p, stage[g], t0 + c, n0, r, vals, 16, bar);
+            }
+            tc_fence_before();
+            asm volatile("bar.sync %0, 128;" ::"r"(bar) : "memory");
+            if (r == 0) mbar_arrive(&acc_empty);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------------------
 // Host side: tensor maps and dispatch.
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -570,6 +707,19 @@ static cudaError_t launch_persistent_t(const GemmParams& p, const CUtensorMap& t
     return launch_pdl(kern, dim3(ctas), dim3(GEMM_THREADS), (size_t)S::TOTAL, stream, tw, tx, p);
 }
 
+static cudaError_t launch_persistent_wide(const GemmParams& p, const CUtensorMap& tw, const CUtensorMap& tx, cudaStream_t stream) {
+    using S = GemmWideSmem;
+    auto kern = gemm_persistent_wide_kernel;
+    static unsigned long long attr_mask = 0;
+    if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), S::TOTAL, &attr_mask); e != cudaSuccess) return e;
+    int dev = 0, sms = 0;
+    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
+    if (cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); e != cudaSuccess) return e;
+    const long long tiles = (long long)(p.N / (2 * BM)) * ((p.M + 255) / 256);
+    const int ctas = (int)std::min<long long>(tiles, sms > 0 ? sms : 1);
+    return launch_pdl(kern, dim3(ctas), dim3(S::THREADS), (size_t)S::TOTAL, stream, tw, tx, p);
+}
+
 int gemm_pick_ntok(int M, bool gated) {
     if (M <= 16) return 16;
     if (M <= 32) return 32;
@@ -603,6 +753,10 @@ cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream) {
     if (p.persistent) {
         // the persistent form is the plain projection at many-token shapes: 256-token tiles (128 when gated or asked for)
         if (p.splits != 1 || p.ag.n_src > 0 || p.rs.world > 0) return cudaErrorInvalidValue;
+        if (p.persistent == 2) {                           // 256 x 256 tiles
+            if (p.gated || ntok != 256 || p.N % (2 * BM)) return cudaErrorInvalidValue;
+            return launch_persistent_wide(p, tw, tx, stream);
+        }
         if (ntok == 256 && !p.gated) return launch_persistent_t<256, false>(p, tw, tx, stream);
         if (ntok == 128) return p.gated ? launch_persistent_t<128, true>(p, tw, tx, stream) : launch_persistent_t<128, false>(p, tw, tx, stream);
         return cudaErrorInvalidValue;

@@ -60,7 +60,8 @@ struct GemmParams {
     int cluster_split;        // 1 (with 2 <= splits <= 8): the splits of a tile form a thread-block cluster and reduce through distributed
                               // shared memory; workspace and counters are not used
     int persistent;           // 1: one CTA per SM walks the output tiles with two accumulators in TMEM (many-token shapes; needs
-                              // splits == 1, ntok 256 or 128, neither ag nor rs)
+                              // splits == 1, ntok 256 or 128, neither ag nor rs); 2: the same walk over tiles of 256 rows x 256 tokens
+                              // (ungated, N a multiple of 256)
 };
 
 int gemm_pick_ntok(int M, bool gated);

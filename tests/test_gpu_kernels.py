@@ -572,6 +572,26 @@ def test_persistent_gemm_matches_reference(ops, M, N, K, gated, ntok):
     assert (y.float() - y2.float()).abs().max() < 2e-2 * max(1.0, float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 1024, 1024), (300, 512, 512), (1000, 256, 256), (40000, 256, 128)])
+def test_persistent_gemm_with_wide_tiles_matches_reference(ops, M, N, K):
+    """Tiles of 256 weight rows x 256 tokens (two MMAs per token operand, both accumulators of TMEM in one tile, two epilogue
+    groups): full tiles, ragged tokens, and far more tiles than CTAs (accumulators and ring slots reused many times)."""
+    from skygdr_b200.ops.gemm import workspace_for
+
+    torch.manual_seed(13)
+    x = torch.randn((M, K), dtype=torch.bfloat16, device="cuda")
+    w = (torch.randn((N, K), dtype=torch.bfloat16, device="cuda") / math.sqrt(K)).contiguous()
+    y = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(x, w, out=y, persistent="wide")
+    ref = x.float() @ w.float().t()
+    torch.cuda.synchronize()
+    assert ops.read_status(workspace_for("cuda").status)["status"] == 0
+    err = (y.float() - ref).abs().max()
+    assert err < 2e-2 * max(1.0, float(ref.abs().max())), float(err)
+    y2 = ops.gemm(x, w, persistent="narrow")
+    assert (y.float() - y2.float()).abs().max() < 2e-2 * max(1.0, float(ref.abs().max()))
+
+
 def test_temperature_sampling_matches_the_cpu_restatement(ops):
     """Gumbel-max sampling: the kernel's pick must be the CPU oracle's pick (same hash, fp32 arithmetic), except where the two
     best perturbed values are within rounding of each other; positions change the draw, the seed changes the stream."""

@@ -776,13 +776,21 @@ def test_gemm_wrapper_argument_order_matches_the_extension(monkeypatch):
     big = torch.zeros((700, 1024), dtype=torch.bfloat16)
     g.gemm(big, w)                                                             # more than 256 tokens: persistent on its own
     a = seen[-1]
-    assert len(a) == 10 and a[3] == 1 and a[8] == 256 and a[9] is True
+    assert len(a) == 10 and a[3] == 1 and a[8] == 256 and a[9] in (1, 2)      # 1: 128-row tiles, 2: 256 x 256 tiles
+    g.gemm(big, w, persistent="wide")
+    assert seen[-1][9] == 2
+    g.gemm(big, w, persistent="narrow")
+    assert seen[-1][9] == 1
     g.gemm(big, torch.zeros((1024, 1024), dtype=torch.bfloat16), gated=True)
-    assert seen[-1][8] == 128 and seen[-1][4] is True and seen[-1][9] is True
+    assert seen[-1][8] == 128 and seen[-1][4] is True and seen[-1][9] == 1     # the gated form has no wide tile
     g.gemm(big, w, persistent=False)                                           # the comparison form: one tile per CTA
     assert len(seen[-1]) == 9 and seen[-1][3] == 1
     g.gemm(x, w, persistent=None)
     assert len(seen[-1]) == 9                                                  # few tokens: never persistent by default
+    # the tile rule picks what was measured faster on B200 at each of these shapes
+    assert [g.wide_tiles_pay(M, N, K, 148, False) for M, N, K in ((2048, 4096, 4096), (4096, 4096, 4096), (8192, 4096, 4096),
+                                                                 (8192, 6144, 4096), (8192, 4096, 12288))] == [True, True, False, True, True]
+    assert not g.wide_tiles_pay(8192, 12288, 4096, 148, True) and not g.wide_tiles_pay(2048, 151936, 4096, 148, False)
     g._WS.clear()
 
 
@@ -793,7 +801,7 @@ def test_bindings_expose_the_keywords_the_python_side_uses():
     C = load()
     for fn, words in {"paged_attn_decode": ["num_blocks:", "pool_rows:"],
                       "prefill_attn": ["pos0:"], "sample": ["temperature:", "seed:", "positions:"],
-                      "gemm": ["persistent: bool = False"],
+                      "gemm": ["persistent: typing.SupportsInt = 0"],
                       "tp_norm": ["rs_world:"]}.items():
         doc = getattr(C, fn).__doc__
         assert all(w in doc for w in words), (fn, doc)
