@@ -515,9 +515,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
 // a stage of 64 KB feeds 1024 tensor-core cycles (64 bytes per cycle and SM from L2 instead of 96) and the three stages that
 // fit cover the load latency that bounds the kernel above. The two accumulators fill all 512 TMEM columns, so a tile's
 // epilogue is not overlapped with the next tile's MMAs (its loads are: the producer runs on); two groups of four epilogue
-// warps, one per accumulator, keep it short. Ungated, N a multiple of 256. Measured on B200 against the kernel above (TFLOP/s):
+// warps keep it short. Ungated (256 weight rows per tile, N a multiple of 256) or gated (a gate block and an up block per tile,
+// 128 output rows). Measured on B200 against the kernel above (TFLOP/s):
 // 1220 / 1137 at 2048 x 4096 x 4096, 1420 / 1333 at 8192 x 4096 x 12288, 1362 / 1391 at 8192 x 4096 x 4096 (half as many tiles
-// leave the last round emptier there); ops.gemm.wide_tiles_pay chooses between the two per shape.
+// leave the last round emptier there); gated 1463 / 1236 at 8192 x 12288 x 4096, 1505 / 1335 at 4096 tokens, 1418 / 1270 at 2048.
+// ops.gemm.wide_tiles_pay chooses between the two per shape.
 struct GemmWideSmem {
     static constexpr int W_BYTES = BM * BK * 2;                 // one 128-row weight block
     static constexpr int X_BYTES = 256 * BK * 2;
@@ -527,6 +529,7 @@ struct GemmWideSmem {
     static constexpr int THREADS = 64 + 256;                    // producer warp, MMA warp, two epilogue groups of four warps
 };
 
+template <bool GATED>
 __global__ void __launch_bounds__(GemmWideSmem::THREADS, 1)
 gemm_persistent_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     using S = GemmWideSmem;
@@ -539,7 +542,9 @@ gemm_persistent_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_m = (p.M + NTOK - 1) / NTOK, tiles_n = p.N / (2 * BM);
+    // output rows per tile: 256 (two weight blocks), or 128 when gated (a gate block and an up block give one block of outputs)
+    constexpr int ROWS = GATED ? BM : 2 * BM;
+    const int tiles_m = (p.M + NTOK - 1) / NTOK, tiles_n = (p.N + ROWS - 1) / ROWS;
     const int n_tiles = tiles_m * tiles_n;
     const int nkb = p.K / BK;
 
@@ -563,7 +568,8 @@ gemm_persistent_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __
             long long it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int n0 = (tile / tiles_m) * 2 * BM, t0 = (tile % tiles_m) * NTOK;
+                const int n0 = (tile / tiles_m) * ROWS, t0 = (tile % tiles_m) * NTOK;
+                const int n1 = GATED ? p.N + n0 : n0 + BM;             // second weight block: the up rows, or the next 128 rows
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = (int)(it % S::STAGES);
                     if (it >= S::STAGES && !mbar_wait(&empty_bar[s], (uint32_t)((it / S::STAGES) - 1) & 1)) {
@@ -574,7 +580,7 @@ gemm_persistent_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __
                     unsigned char* st = smem + s * S::STAGE_BYTES;
                     mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
                     tma_load_2d(st, &tmap_w, kb * BK, n0, &full_bar[s]);
-                    tma_load_2d(st + S::W_BYTES, &tmap_w, kb * BK, n0 + BM, &full_bar[s]);
+                    tma_load_2d(st + S::W_BYTES, &tmap_w, kb * BK, n1, &full_bar[s]);
                     tma_load_2d(st + 2 * S::W_BYTES, &tmap_x, kb * BK, t0, &full_bar[s]);
                 }
             }
@@ -610,7 +616,9 @@ gemm_persistent_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __
             }
         }
     } else {
-        // ---- epilogue: group g = accumulator g = weight rows n0 + 128 g ..; warp w reads TMEM lanes 32 (w % 4) .. +31 ----
+        // ---- epilogue: two groups of four warps; warp w reads TMEM lanes 32 (w % 4) .. +31. Ungated: group g drains accumulator g
+        // (weight rows n0 + 128 g ..). Gated: both accumulators hold the same 128 output rows (gate and up), and group g takes
+        // the token columns 128 g .. 128 g + 127 of both. ----
         const int g = (warp - 2) >> 2;
         const int slice = warp & 3;
         const int r = slice * 32 + lane;
@@ -618,22 +626,28 @@ gemm_persistent_wide_kernel(const __grid_constant__ CUtensorMap tmap_w, const __
         pdl_wait();
         int j = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
-            const int n0 = (tile / tiles_m) * 2 * BM + g * BM, t0 = (tile % tiles_m) * NTOK;
+            const int n0 = (tile / tiles_m) * ROWS + (GATED ? 0 : g * BM), t0 = (tile % tiles_m) * NTOK;
             const uint32_t mine = mbar_wait(&acc_full, (uint32_t)j & 1) ? 1u : 0u;
             uint32_t n_ok;
             asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.popc.u32 %0, %2, 128, q;\n\t}" : "=r"(n_ok) : "r"(mine), "r"(bar) : "memory");
             if (n_ok != 128u) { if (r == 0) set_status(p.status, SKY_STATUS_TIMEOUT_MBAR, 74); break; }
             tc_fence_after();
-            const uint32_t taddr = tmem_base + (uint32_t)(g * NTOK) + ((uint32_t)(slice * 32) << 16);
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(slice * 32) << 16);
+            const int c_lo = GATED ? g * (NTOK / 2) : 0, c_hi = GATED ? c_lo + NTOK / 2 : NTOK;
 #pragma unroll 1
-            for (int c = 0; c < NTOK; c += 16) {
+            for (int c = c_lo; c < c_hi; c += 16) {
                 if (t0 + c >= p.M) break;                  // uniform over the group: rows past M are never stored
-                uint32_t v[16];
-                tmem_ld_x16(taddr + c, v);
+                uint32_t v[16], u[16];
+                tmem_ld_x16(lane_addr + (uint32_t)((GATED ? 0 : g * NTOK) + c), v);
+                if (GATED) tmem_ld_x16(lane_addr + (uint32_t)(NTOK + c), u);
                 tc_wait_ld();
                 float vals[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) vals[i] = __uint_as_float(v[i]);
+                for (int i = 0; i < 16; ++i) {
+                    float val = __uint_as_float(v[i]);
+                    if (GATED) { const float up = __uint_as_float(u[i]); val = val / (1.0f + __expf(-val)) * up; }
+                    vals[i] = val;
+                }
                 store_chunk16(p, stage[g], t0 + c, n0, r, vals, 16, bar);
             }
             tc_fence_before();
@@ -707,15 +721,17 @@ static cudaError_t launch_persistent_t(const GemmParams& p, const CUtensorMap& t
     return launch_pdl(kern, dim3(ctas), dim3(GEMM_THREADS), (size_t)S::TOTAL, stream, tw, tx, p);
 }
 
+template <bool GATED>
 static cudaError_t launch_persistent_wide(const GemmParams& p, const CUtensorMap& tw, const CUtensorMap& tx, cudaStream_t stream) {
     using S = GemmWideSmem;
-    auto kern = gemm_persistent_wide_kernel;
+    auto kern = gemm_persistent_wide_kernel<GATED>;
     static unsigned long long attr_mask = 0;
     if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(kern), S::TOTAL, &attr_mask); e != cudaSuccess) return e;
     int dev = 0, sms = 0;
     if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
     if (cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); e != cudaSuccess) return e;
-    const long long tiles = (long long)(p.N / (2 * BM)) * ((p.M + 255) / 256);
+    const int rows = GATED ? BM : 2 * BM;
+    const long long tiles = (long long)((p.N + rows - 1) / rows) * ((p.M + 255) / 256);
     const int ctas = (int)std::min<long long>(tiles, sms > 0 ? sms : 1);
     return launch_pdl(kern, dim3(ctas), dim3(S::THREADS), (size_t)S::TOTAL, stream, tw, tx, p);
 }
@@ -744,7 +760,8 @@ cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream) {
     const bool csplit = p.cluster_split && p.splits > 1;
     if (csplit && (p.splits > 8 || p.ag.n_src > 0)) return cudaErrorInvalidValue;        // a portable cluster holds at most 8 CTAs
     if (p.splits > 1 && !csplit && (!p.workspace || !p.counters)) return cudaErrorInvalidValue;
-    const int ntok = p.ntok > 0 ? p.ntok : gemm_pick_ntok(p.M, p.gated != 0);
+    // the form with two weight blocks per token operand always takes 256 tokens (its x box and its stage size are built on that)
+    const int ntok = p.persistent == 2 ? 256 : (p.ntok > 0 ? p.ntok : gemm_pick_ntok(p.M, p.gated != 0));
     if (ntok != 16 && ntok != 32 && ntok != 64 && ntok != 128 && ntok != 256) return cudaErrorInvalidValue;
     CUtensorMap tw, tx;
     const long long w_rows = p.gated ? 2LL * p.N : p.N;
@@ -753,9 +770,10 @@ cudaError_t launch_gemm(const GemmParams& p, cudaStream_t stream) {
     if (p.persistent) {
         // the persistent form is the plain projection at many-token shapes: 256-token tiles (128 when gated or asked for)
         if (p.splits != 1 || p.ag.n_src > 0 || p.rs.world > 0) return cudaErrorInvalidValue;
-        if (p.persistent == 2) {                           // 256 x 256 tiles
-            if (p.gated || ntok != 256 || p.N % (2 * BM)) return cudaErrorInvalidValue;
-            return launch_persistent_wide(p, tw, tx, stream);
+        if (p.persistent == 2) {                           // two weight blocks per 256-token operand
+            if (p.gated) return launch_persistent_wide<true>(p, tw, tx, stream);
+            if (p.N % (2 * BM)) return cudaErrorInvalidValue;
+            return launch_persistent_wide<false>(p, tw, tx, stream);
         }
         if (ntok == 256 && !p.gated) return launch_persistent_t<256, false>(p, tw, tx, stream);
         if (ntok == 128) return p.gated ? launch_persistent_t<128, true>(p, tw, tx, stream) : launch_persistent_t<128, false>(p, tw, tx, stream);

@@ -145,11 +145,15 @@ def wide_tiles_pay(M: int, N: int, K: int, sms: int, gated: bool, ntok: int = 0)
     (7 % of a tile at K = 4096, less at larger K) and there are half as many tiles to spread over the SMs; it pays when its rounds
     of tiles are not much emptier than the narrow form's. Measured on B200 (TFLOP/s, wide against narrow): 2048 x 4096 x 4096
     1220 / 1137, 4096 x 4096 x 4096 1315 / 1303, 8192 x 4096 x 4096 1362 / 1391, 8192 x 6144 x 4096 1351 / 1329,
-    8192 x 4096 x 12288 1420 / 1333; the rule below picks the faster one in all five."""
-    if gated or ntok == 128 or N % 256:
+    8192 x 4096 x 12288 1420 / 1333; gated (a gate and an up block per 256 tokens against 128-token tiles) 8192 x 12288 x 4096
+    1463 / 1236, 4096 tokens 1505 / 1335, 2048 tokens 1418 / 1270. The rule below picks the faster one in all eight."""
+    if ntok == 128 or (not gated and N % 256):
         return False
     tm = (M + 255) // 256
-    narrow, wide = (N // 128) * tm, (N // 256) * tm
+    if gated:       # narrow: 128 outputs x 128 tokens per tile; wide: 128 outputs x 256 tokens
+        narrow, wide = ((N + 127) // 128) * ((M + 127) // 128), ((N + 127) // 128) * tm
+    else:
+        narrow, wide = (N // 128) * tm, (N // 256) * tm
 
     def fill(tiles):
         return tiles / (sms * ((tiles + sms - 1) // sms))
@@ -179,7 +183,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, g
         persistent = M > 256 and splits in (None, 1)
     if persistent:
         wide = persistent == "wide" or (persistent is True and wide_tiles_pay(M, N, K, _sms(x.device), gated, ntok))
-        C.gemm(x, w, out, 1, gated, None, None, ws.status, 128 if (gated or ntok == 128) else 256, 2 if wide else 1)
+        C.gemm(x, w, out, 1, gated, None, None, ws.status, 256 if wide else (128 if (gated or ntok == 128) else 256), 2 if wide else 1)
         return out
     if splits is None:
         if ntok == 0 and M <= 256:

@@ -572,23 +572,27 @@ def test_persistent_gemm_matches_reference(ops, M, N, K, gated, ntok):
     assert (y.float() - y2.float()).abs().max() < 2e-2 * max(1.0, float(ref.abs().max()))
 
 
-@pytest.mark.parametrize("M,N,K", [(2048, 1024, 1024), (300, 512, 512), (1000, 256, 256), (40000, 256, 128)])
-def test_persistent_gemm_with_wide_tiles_matches_reference(ops, M, N, K):
-    """Tiles of 256 weight rows x 256 tokens (two MMAs per token operand, both accumulators of TMEM in one tile, two epilogue
-    groups): full tiles, ragged tokens, and far more tiles than CTAs (accumulators and ring slots reused many times)."""
+@pytest.mark.parametrize("M,N,K,gated", [(2048, 1024, 1024, False), (300, 512, 512, False), (1000, 256, 256, False), (40000, 256, 128, False),
+                                         (2048, 1024, 1024, True), (777, 384, 1024, True), (300, 200, 512, True), (40000, 128, 128, True)])
+def test_persistent_gemm_with_wide_tiles_matches_reference(ops, M, N, K, gated):
+    """Two weight blocks per 256-token operand (both accumulators of TMEM in one tile, two epilogue groups): 256 x 256 tiles, or a
+    gate and an up block for 128 gated outputs; full tiles, ragged tokens and features, and far more tiles than CTAs
+    (accumulators and ring slots reused many times)."""
     from skygdr_b200.ops.gemm import workspace_for
 
     torch.manual_seed(13)
     x = torch.randn((M, K), dtype=torch.bfloat16, device="cuda")
-    w = (torch.randn((N, K), dtype=torch.bfloat16, device="cuda") / math.sqrt(K)).contiguous()
+    w = (torch.randn((N * (2 if gated else 1), K), dtype=torch.bfloat16, device="cuda") / math.sqrt(K)).contiguous()
     y = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
-    ops.gemm(x, w, out=y, persistent="wide")
+    ops.gemm(x, w, out=y, gated=gated, persistent="wide")
     ref = x.float() @ w.float().t()
+    if gated:
+        ref = torch.nn.functional.silu(ref[:, :N]) * ref[:, N:]
     torch.cuda.synchronize()
     assert ops.read_status(workspace_for("cuda").status)["status"] == 0
     err = (y.float() - ref).abs().max()
     assert err < 2e-2 * max(1.0, float(ref.abs().max())), float(err)
-    y2 = ops.gemm(x, w, persistent="narrow")
+    y2 = ops.gemm(x, w, gated=gated, persistent="narrow")
     assert (y.float() - y2.float()).abs().max() < 2e-2 * max(1.0, float(ref.abs().max()))
 
 
