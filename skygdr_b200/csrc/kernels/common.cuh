@@ -75,7 +75,9 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned 
     // Poll relaxed; once the value is there, read it once more with acquire semantics. That load is what orders the reads
     // that follow behind the producer's release, and unlike a system-scope fence it does not have to wait for this SM's own
     // outstanding writes.
-    if ((int)(ld_sys_u32(flag) - want) >= 0) return (int)(ld_acquire_sys_u32(flag) - want) >= 0;
+    // The first look is the acquire load itself: when the value is already there (the common case for a kernel that starts
+    // after its producers), one round trip instead of two.
+    if ((int)(ld_acquire_sys_u32(flag) - want) >= 0) return true;
     unsigned long long t0 = globaltimer_ns();
     unsigned ns = 32;
     for (;;) {

@@ -36,6 +36,17 @@ __global__ void __launch_bounds__(256) tp_norm_kernel(const TpNormParams p) {
     pdl_wait();
     const int row = blockIdx.x;
     const int nvec = p.hidden / 8;
+    // The residual row (written by the previous launch of this kernel, complete after pdl_wait) and the norm weights do not
+    // depend on the arrivals: their loads are in flight while thread 0 waits.
+    uint4 res_raw[4], w_raw[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int v = threadIdx.x + k * 256;
+        if (v < nvec) {
+            res_raw[k] = *reinterpret_cast<const uint4*>(p.resid + (long long)row * p.hidden + v * 8);
+            w_raw[k] = __ldg(reinterpret_cast<const uint4*>(p.w + v * 8));
+        }
+    }
     if (threadIdx.x == 0) {
         int ok = 1;
         if (p.rs_buf && *(volatile unsigned int*)&p.status->status == SKY_STATUS_OK) {
@@ -54,7 +65,7 @@ __global__ void __launch_bounds__(256) tp_norm_kernel(const TpNormParams p) {
     for (int k = 0; k < 4; ++k) {
         const int v = threadIdx.x + k * 256;
         if (v < nvec) {
-            unpack8f(*reinterpret_cast<const uint4*>(p.resid + (long long)row * p.hidden + v * 8), vals[k]);
+            unpack8f(res_raw[k], vals[k]);
             if (p.rs_buf) {
                 // all partials of this piece are requested before the first one is used: one L2 round trip, not `world` of them
                 uint4 raw[TP_MAX_RANKS];
@@ -90,7 +101,7 @@ __global__ void __launch_bounds__(256) tp_norm_kernel(const TpNormParams p) {
         const int v = threadIdx.x + k * 256;
         if (v < nvec) {
             float g[8], o[8];
-            unpack8f(*reinterpret_cast<const uint4*>(p.w + v * 8), g);
+            unpack8f(w_raw[k], g);
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = vals[k][i] * inv * g[i];
             const uint4 packed = pack8f(o);
