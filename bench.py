@@ -52,7 +52,7 @@ def parse():
     ap.add_argument("--attn-impl", default="tc", choices=["tc", "simt"])
     ap.add_argument("--tp-collective", default="oneshot", choices=["oneshot", "rs_ag"],
                     help="tensor-parallel form: one-shot all-reduce (default) or reduce-scatter + all-gather")
-    ap.add_argument("--attn-chunk", type=int, default=1024)
+    ap.add_argument("--attn-chunk", type=int, default=0, help="tokens per attention CTA; 0 = planned from the batch's context lengths")
     ap.add_argument("--no-baseline", action="store_true", help="skip the library (cuBLAS + NCCL) arm and the numeric check")
     ap.add_argument("--profile-step", action="store_true", help="also print per-kernel-kind times of one eager step (tensor-parallel engine)")
     return ap.parse_args()
@@ -226,7 +226,7 @@ def main() -> int:
             "config": {"model": cfg.name if args.layers == 36 else f"{cfg.name}-{args.layers}L", "global_batch": batch,
                        "seq_len": f"context uniform {args.ctx_lo}-{args.ctx_hi}, 1 new token per step",
                        "parallelism": f"tp{world}" + (f" ({args.tp_collective})" if world > 1 else ""), "kv_block_tokens": 16, "sampling": "greedy",
-                       "attention": f"{args.attn_impl}, {args.attn_chunk}-token splits",
+                       "attention": f"{args.attn_impl}, {eng.attn.chunk_tokens}-token splits" + ("" if args.attn_chunk else " (planned from the context lengths)"),
                        "l2": "inputs larger than L2: each step streams %.1f GB of weights and KV per GPU" % (step_bytes / 1e9)},
             "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": sess.h2d_bytes_per_step, "d2h_bytes_per_step": sess.d2h_bytes_per_step},

@@ -141,6 +141,9 @@ def main():
         byt = int(ctx.sum()) * a.kv_heads * 128 * 2 * 2
         out.update(ms=ms, best_ms=best, kv_bytes=byt, gbs=byt / ms / 1e6, frac_hbm=byt / ms / 1e6 / hbm, tokens=int(ctx.sum()), impl=a.impl,
                    status=ops.read_status(attn.status)["status_name"])
+        if a.impl == "tc":
+            from skygdr_b200._ext import load
+            out["one_tma_request_per_page"] = bool(load().paged_attn_tc_page_box() == 1)
     elif a.case == "gemm":
         x = torch.randn((a.m, a.k), dtype=torch.bfloat16, device=dev)
         w = torch.randn((a.n * (2 if a.gated else 1), a.k), dtype=torch.bfloat16, device=dev) / 64

@@ -482,6 +482,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("host_register", &host_register);
     m.def("host_unregister", &host_unregister);
     m.def("credit_page_init", &credit_page_init);
+    m.def("paged_attn_tc_page_box", &sky::paged_attn_tc_page_box);
     m.def("credit_page_grant", &credit_page_grant);
     m.def("credit_page_read", &credit_page_read);
     m.def("credit_page_heartbeat", &credit_page_heartbeat);

@@ -35,5 +35,6 @@ cudaError_t launch_paged_attn_decode(const PagedAttnParams& p, cudaStream_t stre
 cudaError_t prepare_paged_attn_decode();
 // Tensor-core version (paged_attn_tc.cu). pool_rows: 128-element rows from p.kv to the end of the pool allocation;
 // chunk_tokens must be a multiple of 128.
+int paged_attn_tc_page_box();
 cudaError_t launch_paged_attn_decode_tc(const PagedAttnParams& p, long long pool_rows, cudaStream_t stream);
 }  // namespace sky

@@ -11,6 +11,53 @@ from .flow import new_status
 from .kv_cache import PagedKVPool
 
 
+def simulate_decode_launch(ctx_lens, kv_heads: int, chunk_tokens: int, slots: int = 296, hbm_bytes_per_us: float = 6.0e6,
+                           cta_bytes_per_us: float = 80e3, setup_us: float = 1.5, finish_us: float = 1.0) -> float:
+    """Microseconds one launch of the tcgen05 decode kernel takes, by a fluid model: one CTA per (sequence, KV head, chunk) in the
+    kernel's dispatch order (chunks fastest, then heads, then sequences), `slots` of them resident (two per SM), each setting
+    up, then streaming its tiles of 128 tokens (64 KB of K and V) at an equal share of the memory bandwidth but no faster than
+    one CTA's ring allows, then finishing. The absolute figure is about 35 us short of a measured launch; what it is used for is
+    the order of the candidates, which it got right where it was checked on B200 (contexts 8k-16k: 2048 < 1536 < 1024 < 768 < 512
+    tokens per chunk, measured 167.7 / 170.6 / 171.5 / 173.3 / 183.6 us; the benchmark's contexts 2k-16k: 1536 ahead of 1024 and
+    2048 by 2.4 % of the decode step)."""
+    items = []
+    for c in ctx_lens:
+        c = int(c)
+        n = (c + chunk_tokens - 1) // chunk_tokens
+        sizes = [((min(c, (s + 1) * chunk_tokens) - s * chunk_tokens + 127) // 128) * 65536.0 for s in range(n)]
+        for _ in range(kv_heads):
+            items.extend(sizes)
+    t, nxt = 0.0, 0
+    active = []                                  # [bytes left, set-up left, finish left]
+    while nxt < len(items) or active:
+        while len(active) < slots and nxt < len(items):
+            active.append([items[nxt], setup_us, finish_us])
+            nxt += 1
+        streaming = sum(1 for a in active if a[1] <= 0 and a[0] > 0)
+        rate = min(cta_bytes_per_us, hbm_bytes_per_us / max(1, streaming))
+        dt = min(a[1] if a[1] > 0 else (a[0] / rate if a[0] > 0 else a[2]) for a in active)
+        for a in active:
+            if a[1] > 0:
+                a[1] = a[1] - dt if a[1] - dt > 1e-9 else 0.0
+            elif a[0] > 0:
+                a[0] = a[0] - dt * rate if a[0] - dt * rate > 1e-6 else 0.0
+            else:
+                a[2] -= dt
+        active = [a for a in active if a[1] > 0 or a[0] > 0 or a[2] > 1e-9]
+        t += dt
+    return t
+
+
+def plan_chunk_tokens(ctx_lens, kv_heads: int, sms: int = 148, candidates=(768, 1024, 1280, 1536, 1792, 2048)) -> int:
+    """Tokens per CTA for a batch with these context lengths: the candidate whose launch the model above finishes first. How the
+    chunks of a batch fall into rounds of resident CTAs moves a launch by a few per cent, and which size is best depends on the
+    lengths; the choice is made where a step is captured (lengths grow by one token per step, so it holds for many steps)."""
+    ctx = [int(c) for c in ctx_lens]
+    if not ctx or kv_heads <= 0:
+        return 1024
+    return min(candidates, key=lambda c: (simulate_decode_launch(ctx, kv_heads, c, slots=2 * sms), c))
+
+
 class PagedAttention:
     """Holds the split-KV scratch (partials, statistics, counters) for a maximum batch and context."""
 

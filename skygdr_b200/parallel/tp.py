@@ -301,11 +301,17 @@ def _bytes_per_step(cfg: Qwen3Config, w: Qwen3Weights, ctx: torch.Tensor, kv_hea
 
 
 def build_decode_engine(cfg: Qwen3Config, device: torch.device, rank: int, world: int, ctx: torch.Tensor, extra_tokens: int,
-                        seed: int = 0, kv_init: str = "normal", attn_chunk: int = 1024, attn_impl: str = "tc",
+                        seed: int = 0, kv_init: str = "normal", attn_chunk: int = 0, attn_impl: str = "tc",
                         collective: str = "oneshot"):
     """Weights shard, KV pool sized for ``ctx`` (+ ``extra_tokens`` of growth per sequence), randomly permuted block
-    table, and the decode engine for this rank. Every rank passes the same ``ctx`` and ``seed``."""
+    table, and the decode engine for this rank. Every rank passes the same ``ctx`` and ``seed``. ``attn_chunk`` 0: the tokens
+    per attention CTA are planned from the context lengths (``ops.attention.plan_chunk_tokens``)."""
     batch = ctx.numel()
+    if not attn_chunk:
+        from ..ops.attention import plan_chunk_tokens
+
+        sms = torch.cuda.get_device_properties(device).multi_processor_count if torch.cuda.is_available() else 148
+        attn_chunk = plan_chunk_tokens([int(c) + extra_tokens // 2 for c in ctx], cfg.kv_heads // world, sms) if attn_impl == "tc" else 1024
     weights = Qwen3Weights(cfg, device, seed=seed, tp_rank=rank, tp_world=world)
     geom = KVGeometry(cfg.layers, cfg.kv_heads // world, cfg.head_dim)
     blocks_per_seq = [(int(c) + extra_tokens + 15) // 16 for c in ctx]

@@ -829,3 +829,23 @@ def test_build_decode_engine_lays_out_pool_and_tables(monkeypatch):
     eng.set_batch(torch.zeros(4, dtype=torch.int32), ctx.int(), table)
     eng.step()
     assert len(calls) == eng.kernels_per_step
+
+
+def test_attention_chunk_planner_orders_candidates_as_measured():
+    """The fluid model behind the chunk planner: on the two batches where launches were timed on B200 it must put the candidates
+    in the measured order (contexts 8k-16k: larger chunks faster, 512 tokens slowest; the benchmark's contexts 2k-16k: 1536 ahead
+    of 1024 and 2048), and the planner must return a multiple of 128 from its candidates."""
+    import torch
+
+    from skygdr_b200.ops.attention import plan_chunk_tokens, simulate_decode_launch
+
+    g = torch.Generator().manual_seed(0)
+    long_ctx = torch.randint(8192, 16385, (16,), generator=g).tolist()
+    t = {c: simulate_decode_launch(long_ctx, 8, c) for c in (512, 768, 1024, 1536, 2048)}
+    assert t[512] > t[768] > t[1024] >= t[1536] > t[2048]
+    g = torch.Generator().manual_seed(0)
+    bench_ctx = (torch.randint(2048, 16385, (16,), generator=g) + 20).tolist()
+    t = {c: simulate_decode_launch(bench_ctx, 8, c) for c in (1024, 1536, 2048)}
+    assert t[1536] < t[1024] and t[1536] < t[2048]
+    assert plan_chunk_tokens(bench_ctx, 8) == 1536
+    assert plan_chunk_tokens([], 8) == 1024 and plan_chunk_tokens([100, 200], 8) % 128 == 0
