@@ -226,7 +226,7 @@ def main() -> int:
             "config": {"model": cfg.name if args.layers == 36 else f"{cfg.name}-{args.layers}L", "global_batch": batch,
                        "seq_len": f"context uniform {args.ctx_lo}-{args.ctx_hi}, 1 new token per step",
                        "parallelism": f"tp{world}" + (f" ({args.tp_collective})" if world > 1 else ""), "kv_block_tokens": 16, "sampling": "greedy",
-                       "attention": f"{args.attn_impl}, {eng.attn.chunk_tokens}-token splits" + ("" if args.attn_chunk else " (planned from the context lengths)"),
+                       "attention": f"{args.attn_impl}, {eng.attn.chunk_tokens}-token splits" + ("" if args.attn_chunk or eng.attn.chunk_tokens == 1024 else " (planned from the context lengths)"),
                        "l2": "inputs larger than L2: each step streams %.1f GB of weights and KV per GPU" % (step_bytes / 1e9)},
             "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": sess.h2d_bytes_per_step, "d2h_bytes_per_step": sess.d2h_bytes_per_step},

@@ -26,6 +26,7 @@ struct PrefillAttnParams {
     const int* pos0;             // [n_seqs] or nullptr: tokens of each sequence that precede its queries of this launch; their K/V are in
                                  // the pool already and every query attends to them (chunked prefill)
     LaunchStatus* status;
+    int page_box;                // set by the launcher: 1 = the K/V map fetches a whole page per request (see prefill_attn_tc.cu)
 };
 
 // pool_rows: 128-element rows from p.kv to the end of the pool allocation (bounds of the tensor map).

@@ -120,7 +120,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
             unsigned char* st = ring + s * PF_TILE_BYTES;
             if (lane == 0) mbar_expect_tx(&full_bar[s], PF_TILE_BYTES);
             __syncwarp();
-            if (lane < 16) {
+            if (p.page_box) {
+                // One request per page: the five-dimensional map (64 dims, 8 tokens, 2 halves of head_dim, 2 token groups, 256-byte
+                // row of the pool) lays a page down as [token group][half][8 tokens][128 bytes]. The SM's TMA unit takes a request
+                // about every 37 ns whatever its size; 32 boxes per key tile took as long to issue as the tile takes to compute.
+                if (lane < 8) {
+                    const int e = (u >> 1) * 8 + lane;
+                    const int blk = e < p.max_blocks ? __ldg(table + e) : 0;
+                    const long long row0 = ((long long)blk * p.block_stride >> 7) + ((u & 1) ? (p.kv_stride >> 7) : 0) + head_row;
+                    tma_load_5d(st + lane * 4096, &tmap_kv, 0, 0, 0, 0, (int)row0, &full_bar[s]);
+                }
+            } else if (lane < 16) {
                 const int e = (u >> 1) * 8 + pg;
                 const int blk = e < p.max_blocks ? __ldg(table + e) : 0;
                 const long long row0 = ((long long)blk * p.block_stride >> 7) + ((u & 1) ? (p.kv_stride >> 7) : 0) + head_row;
@@ -143,7 +153,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const uint64_t a = umma_desc_k_sw128(q_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
-                    const uint64_t b = umma_desc_k_sw128(k_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
+                    const uint64_t b = p.page_box ? umma_desc_k_sw128_sbo(k_addr + (k >> 2) * 1024 + (k & 3) * 32, 2048)
+                                                  : umma_desc_k_sw128(k_addr + (k >> 2) * PF_HALF + (k & 3) * 32);
                     tc_mma_f16(tmem_base + x * 128, a, b, idesc_s, k ? 1u : 0u);
                 }
                 const bool last_user = x == 1 || j >= nkt_x[1];
@@ -159,7 +170,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_attn_tc_kernel(const __
                 const uint32_t v_addr = smem_u32(ring + s * PF_TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {                           // 16 keys of P = 8 columns of packed bf16 in the score buffer
-                    const uint64_t b = umma_desc_mn_sw128(v_addr + k * 2048, PF_HALF, 1024);
+                    const uint64_t b = p.page_box ? umma_desc_mn_sw128(v_addr + k * 4096, 1024, 2048) : umma_desc_mn_sw128(v_addr + k * 2048, PF_HALF, 1024);
                     tc_mma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + k * 8, b, idesc_o, (j | k) ? 1u : 0u);
                 }
                 const bool last_user = x == 1 || j >= nkt_x[1];
@@ -318,6 +329,26 @@ bool pf_make_tmap(CUtensorMap* m, const void* base, long long mid, long long out
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Pages of 16 tokens x 128 dims as one box: dimensions (64 dims, 8 tokens at the token pitch, 2 halves of head_dim, 2 groups of 8
+// tokens, 256-byte row of the pool from which the page starts). The last dimension steps by one pool row, so any page start
+// (block, K or V, head) is a coordinate; the dimensions overlap in memory, which the address arithmetic does not mind.
+bool pf_make_tmap_pages(CUtensorMap* m, const void* base, long long tok_pitch_bytes, long long pool_rows) {
+    static PfEncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) return false;
+        fn = reinterpret_cast<PfEncodeFn>(ptr);
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || pool_rows < 16 || pool_rows > 0x7fffffffLL) return false;
+    const cuuint64_t dims[5] = {64, 8, 2, 2, (cuuint64_t)pool_rows};
+    const cuuint64_t strides[4] = {(cuuint64_t)tok_pitch_bytes, 128, (cuuint64_t)(8 * tok_pitch_bytes), 256};
+    const cuuint32_t box[5] = {64, 8, 2, 2, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 cudaError_t launch_prefill_attn_tc(const PrefillAttnParams& p, long long pool_rows, cudaStream_t stream) {
@@ -330,12 +361,16 @@ cudaError_t launch_prefill_attn_tc(const PrefillAttnParams& p, long long pool_ro
     if ((long long)p.kv_heads * (p.head_stride >> 7) > ts_rows && ts_rows != 1) return cudaErrorInvalidValue;
     CUtensorMap tq, tkv;
     if (!pf_make_tmap(&tq, p.q, p.q_heads, p.total_tokens, PF_TILE)) return cudaErrorInvalidValue;
-    if (!pf_make_tmap(&tkv, p.kv, ts_rows, pool_rows / ts_rows, 16)) return cudaErrorInvalidValue;
+    PrefillAttnParams q = p;
+    static const bool two_boxes = [] { const char* v = getenv("SKYGDR_ATTN_TWO_BOXES"); return v && v[0] == '1'; }();
+    // the last page may not reach past the allocation: its last token row starts 15 token pitches after its first
+    q.page_box = (!two_boxes && pf_make_tmap_pages(&tkv, p.kv, ts_rows * 256, pool_rows - 15 * ts_rows)) ? 1 : 0;
+    if (!q.page_box && !pf_make_tmap(&tkv, p.kv, ts_rows, pool_rows / ts_rows, 16)) return cudaErrorInvalidValue;
     static unsigned long long attr_mask = 0;
     if (cudaError_t e = set_max_dynamic_smem_once(reinterpret_cast<const void*>(prefill_attn_tc_kernel), PF_SMEM, &attr_mask); e != cudaSuccess) return e;
     const int q_tiles = (p.max_len + PF_TILE - 1) / PF_TILE;
     const dim3 grid(p.q_heads, (q_tiles + 1) / 2, p.n_seqs);
-    prefill_attn_tc_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(tq, tkv, p);
+    prefill_attn_tc_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(tq, tkv, q);
     return cudaGetLastError();
 }
 
