@@ -518,7 +518,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
 // warps keep it short. Ungated (256 weight rows per tile, N a multiple of 256) or gated (a gate block and an up block per tile,
 // 128 output rows). Measured on B200 against the kernel above (TFLOP/s):
 // 1220 / 1137 at 2048 x 4096 x 4096, 1420 / 1333 at 8192 x 4096 x 12288, 1362 / 1391 at 8192 x 4096 x 4096 (half as many tiles
-// leave the last round emptier there); gated 1463 / 1236 at 8192 x 12288 x 4096, 1505 / 1335 at 4096 tokens, 1418 / 1270 at 2048.
+// leave the last wave emptier there); gated 1463 / 1236 at 8192 x 12288 x 4096, 1505 / 1335 at 4096 tokens, 1418 / 1270 at 2048.
 // ops.gemm.wide_tiles_pay chooses between the two per shape.
 struct GemmWideSmem {
     static constexpr int W_BYTES = BM * BK * 2;                 // one 128-row weight block

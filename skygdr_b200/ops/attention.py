@@ -50,7 +50,7 @@ def simulate_decode_launch(ctx_lens, kv_heads: int, chunk_tokens: int, slots: in
 
 def plan_chunk_tokens(ctx_lens, kv_heads: int, sms: int = 148, candidates=(768, 1024, 1280, 1536, 1792, 2048)) -> int:
     """Tokens per CTA for a batch with these context lengths: the candidate whose launch the model above finishes first. How the
-    chunks of a batch fall into rounds of resident CTAs moves a launch by a few per cent, and which size is best depends on the
+    chunks of a batch fall into waves of resident CTAs moves a launch by a few per cent, and which size is best depends on the
     lengths; the choice is made where a step is captured (lengths grow by one token per step, so it holds for many steps)."""
     ctx = [int(c) for c in ctx_lens]
     if not ctx or kv_heads <= 0:

@@ -142,7 +142,7 @@ def workspace_for(device) -> GemmWorkspace:
 def wide_tiles_pay(M: int, N: int, K: int, sms: int, gated: bool, ntok: int = 0) -> bool:
     """Whether the persistent form should walk tiles of 256 rows x 256 tokens instead of 128 x 256. The wide tile's main loop is
     about a fifth faster (two MMAs per token operand: a third less traffic from L2 per MMA), but its epilogue is not overlapped
-    (7 % of a tile at K = 4096, less at larger K) and there are half as many tiles to spread over the SMs; it pays when its rounds
+    (7 % of a tile at K = 4096, less at larger K) and there are half as many tiles to spread over the SMs; it pays when its waves
     of tiles are not much emptier than the narrow form's. Measured on B200 (TFLOP/s, wide against narrow): 2048 x 4096 x 4096
     1220 / 1137, 4096 x 4096 x 4096 1315 / 1303, 8192 x 4096 x 4096 1362 / 1391, 8192 x 6144 x 4096 1351 / 1329,
     8192 x 4096 x 12288 1420 / 1333; gated (a gate and an up block per 256 tokens against 128-token tiles) 8192 x 12288 x 4096
