@@ -656,3 +656,28 @@ def test_topology_turns_a_gpu_into_link_definitions_the_daemon_accepts():
         assert c.register("kv_transfer", "high", 600.0, link="nvlink:gpu3").flow_id == 1
     r = subprocess.run([sys.executable, "-m", "skygdr_b200.cli.topology"], capture_output=True, text=True, env=ENV, timeout=60)
     assert (r.returncode == 0 and "--link" in r.stdout) or (r.returncode == 1 and "NVML" in r.stderr)     # with or without a GPU
+
+
+def test_pacing_accuracy_sets_a_budget_against_the_next_window(tmp_path):
+    """benchmarks/scheduler_shared_link.py, pacing_error: a row of the daemon's window log holds the budget decided for the window
+    that begins and the rate measured over the window that ended, so a budget is compared with the rate of the flow's next
+    row; unpaced windows (budget -1) and windows without backlog or bytes are left out."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("scheduler_shared_link", os.path.join(ROOT, "benchmarks", "scheduler_shared_link.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    log = tmp_path / "windows.csv"
+    hdr = "ts_unix_ms,window_id,flow_id,flow,mode,decision,budget_bytes,inst_gbps,smooth_gbps,backlog_bytes,link_util_pct,granted_bytes"
+    rows = [hdr]
+    # 1 ms windows. kv_bulk: unpaced at 500 GB/s, then three paced windows of 150 MB each which it uses fully, then idle.
+    seq = [(-1, 500.0, 1), (150e6, 500.0, 1), (150e6, 150.0, 1), (150e6, 150.0, 1), (-1, 150.0, 1), (-1, 0.0, 0), (150e6, 0.0, 0), (150e6, 0.0, 0)]
+    for w, (budget, inst, backlog) in enumerate(seq):
+        rows.append(f"{1000 + w},{w},1,kv_bulk,CUSTOM,HOLD,{budget:.0f},{inst:.6f},{inst:.6f},{backlog << 30},50.0,0")
+        rows.append(f"{1000 + w},{w},2,other,HIGH,HOLD,-1,10.000000,10.000000,0,50.0,0")
+    log.write_text("\n".join(rows) + "\n")
+    r = mod.pacing_error(str(log), "kv_bulk", 1e-3)
+    # budgets of windows 1, 2, 3 against the rates of rows 2, 3, 4 (150 GB/s each); the first paced row's own 500 GB/s belongs to
+    # the unpaced window before it, and the idle windows at the end do not count
+    assert r["paced_windows"] == 3 and abs(r["achieved_over_granted"] - 1.0) < 1e-9, r
+    assert mod.pacing_error(str(tmp_path / "missing.csv"), "kv_bulk", 1e-3) is None
